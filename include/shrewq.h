@@ -1,0 +1,164 @@
+/*
+ * shrewq.h — C ABI of libshrewq, the B200 (sm_100a) implementation of Shrew's INT8
+ * symmetric quantization path: quantize / dequantize of f32 weights and the forward of
+ * a quantized Linear.
+ *
+ * The reference has no C ABI: its boundary is the Rust API of the facade crate's
+ * `quantize` module (crates/shrew/src/quantize.rs; re-exported at
+ * crates/shrew/src/lib.rs:120-124).  Each entry point below names the Rust item whose
+ * work it performs on the device; a Rust shim binds them with `extern "C"` and keeps the
+ * `Tensor<B>` / `Module::forward` surface unchanged.
+ *
+ * Conventions
+ *  - Every function returns an int status (SHREWQ_OK == 0, negative on error), never
+ *    throws or aborts.  `shrewq_last_error` returns the message of the last failure on
+ *    the given context (or of the last failed create call on this thread when ctx is NULL).
+ *  - Pointers named *_dev are device pointers owned by the caller, valid on the context's
+ *    device; pointers named *_host are ordinary host memory.  The library allocates only
+ *    its own workspaces, inside contexts and handles.
+ *  - Device entry points enqueue work on the context's stream and return without
+ *    synchronising.  Host entry points (suffix _host) copy in, run, copy out and
+ *    synchronise the stream before returning.
+ *  - A context belongs to one host thread at a time.  A shrewq_linear is immutable after
+ *    creation.
+ *  - There is no CPU fallback: without a CUDA device every compute call fails with
+ *    SHREWQ_ERR_NO_DEVICE.
+ */
+#ifndef SHREWQ_H
+#define SHREWQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define SHREWQ_API __attribute__((visibility("default")))
+#else
+#define SHREWQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------ */
+#define SHREWQ_OK 0
+#define SHREWQ_ERR_INVALID_ARG (-1) /* null pointer, bad enum, misaligned or mismatched shape */
+#define SHREWQ_ERR_CUDA (-2)        /* a CUDA runtime / driver call failed                     */
+#define SHREWQ_ERR_UNSUPPORTED (-3) /* valid request this build has no kernel for             */
+#define SHREWQ_ERR_NO_DEVICE (-4)   /* no CUDA device / wrong architecture                    */
+#define SHREWQ_ERR_TIMEOUT (-5)     /* a bounded device-side wait ran out (kernel gave up)    */
+#define SHREWQ_ERR_ALLOC (-6)       /* out of device or host memory                           */
+
+/* ---- enums (ints in the ABI) -------------------------------------------------------- */
+/* QuantGranularity — quantize.rs:55-61 */
+#define SHREWQ_PER_TENSOR 0
+#define SHREWQ_PER_CHANNEL 1
+/* element types of activations / outputs (shrew_core DType F32 and BF16) */
+#define SHREWQ_F32 0
+#define SHREWQ_BF16 1
+/* elementwise op fused after the bias add (the tensor op a caller applies next) */
+#define SHREWQ_EPILOGUE_NONE 0
+#define SHREWQ_EPILOGUE_RELU 1
+
+typedef struct shrewq_ctx shrewq_ctx;
+typedef struct shrewq_linear shrewq_linear;
+
+/* ---- context ------------------------------------------------------------------------ */
+/* Plays the role of the reference's `B::Device` (QuantizedLinear::device,
+ * quantize.rs:389-390): which GPU, and here also which stream.  `stream` is a
+ * cudaStream_t (NULL = the default stream). */
+SHREWQ_API int shrewq_ctx_create(int device, void *stream, shrewq_ctx **out);
+SHREWQ_API int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream);
+SHREWQ_API int shrewq_ctx_synchronize(shrewq_ctx *ctx);
+SHREWQ_API void shrewq_ctx_destroy(shrewq_ctx *ctx);
+SHREWQ_API const char *shrewq_last_error(const shrewq_ctx *ctx);
+/* Library version and the architecture it was compiled for, e.g. "shrewq 0.1 sm_100a". */
+SHREWQ_API const char *shrewq_version(void);
+
+/* ---- quantize / dequantize ---------------------------------------------------------- */
+/*
+ * quantize_tensor for an F32 tensor — quantize.rs:194-205 (with quantize_per_tensor
+ * :229-260, quantize_per_channel :270-318, compute_scale_zp :339-352).
+ * rows = shape[0], cols = product(shape[1..]).  Writes rows*cols INT8 codes in the
+ * source order and 1 (per-tensor) or `rows` (per-channel) f64 scales; zero points are
+ * all 0.0 in symmetric mode and are not materialised.  Codes and scales are bit-exact
+ * with the reference's f64 host arithmetic.
+ */
+SHREWQ_API int shrewq_quantize_f32(shrewq_ctx *ctx, const float *w_dev, size_t rows, size_t cols,
+                        int granularity, int8_t *q_dev, double *scales_dev);
+/* Same with host buffers: what `quantize_tensor(&tensor, &cfg)` does for a caller whose
+ * tensor lives on the host (upload, quantize on the GPU, download codes and scales). */
+SHREWQ_API int shrewq_quantize_f32_host(shrewq_ctx *ctx, const float *w_host, size_t rows, size_t cols,
+                             int granularity, int8_t *q_host, double *scales_host);
+
+/*
+ * dequantize_tensor — quantize.rs:210-225 (dequantize_per_tensor :262-266,
+ * dequantize_per_channel :320-335): out = narrow((q as f64 - 0.0) * scale) to
+ * out_dtype (SHREWQ_F32 or SHREWQ_BF16), bit-exact with the reference.
+ */
+SHREWQ_API int shrewq_dequantize(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
+                      size_t rows, size_t cols, int granularity, int out_dtype, void *out_dev);
+
+/* ---- quantized Linear --------------------------------------------------------------- */
+/*
+ * QuantizedLinear::new — quantize.rs:437-447 (from_linear, :413-434, is
+ * shrewq_quantize_f32 followed by this).  q_dev is [out_features, in_features] row-major,
+ * scales_dev holds 1 or out_features f64 values, bias_dev is NULL or out_features f32
+ * values (the reference's [1,out] bias, kept in float: quantize.rs:387-388).
+ * The handle keeps the caller's q_dev and bias_dev pointers (they must outlive it) and
+ * owns a small f32 copy of the scales.
+ * A row shard of a larger layer is simply a Linear over rows [n0,n1): pass the shard's
+ * pointers and out_features = n1-n0.
+ */
+SHREWQ_API int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
+                         const float *bias_dev, size_t out_features, size_t in_features,
+                         int granularity, shrewq_linear **out);
+SHREWQ_API void shrewq_linear_destroy(shrewq_linear *lin);
+
+/*
+ * <QuantizedLinear as Module>::forward — quantize.rs:463-476:
+ *   y[m, n] = sum_k x[m,k] * dequant(W)[n,k] + bias[n],   then the optional epilogue.
+ * x_dev is [M, in_features] row-major of x_dtype; y_dev has M rows of out_features
+ * values of y_dtype with a row stride of ldy elements (ldy >= out_features; pass
+ * out_features for a dense output, or the full layer width when a shard writes its
+ * column slice of a wider buffer).  The weight is never expanded in memory: the INT8
+ * codes are streamed and the per-channel scale is applied to the f32 accumulator.
+ * Accumulation is f32; with bf16 activations products are exact bf16 x int8 products.
+ */
+SHREWQ_API int shrewq_linear_forward(shrewq_linear *lin, const void *x_dev, int x_dtype, size_t M,
+                          void *y_dev, int y_dtype, size_t ldy, int epilogue);
+/* Same with host activations and host output (dense, ldy = out_features): the call a
+ * host-tensor caller of `qlinear.forward(&x)` makes. */
+SHREWQ_API int shrewq_linear_forward_host(shrewq_linear *lin, const void *x_host, int x_dtype, size_t M,
+                               void *y_host, int y_dtype, int epilogue);
+
+/*
+ * Two forwards sharing one activation read, for a gated MLP block:
+ *   h[m,n] = silu(gate.forward(x)[m,n]) * up.forward(x)[m,n]
+ * (the reference composes this from two QuantizedLinear::forward calls and the tensor ops
+ * silu and mul).  gate and up must have identical shapes and the same context.
+ */
+SHREWQ_API int shrewq_linear_forward_gate_up_silu(shrewq_linear *gate, shrewq_linear *up, const void *x_dev,
+                                       int x_dtype, size_t M, void *h_dev, int h_dtype, size_t ldh);
+
+/* Accessors mirroring QuantizedLinear's public fields / methods (quantize.rs:392-394,
+ * :455-459). */
+SHREWQ_API size_t shrewq_linear_in_features(const shrewq_linear *lin);
+SHREWQ_API size_t shrewq_linear_out_features(const shrewq_linear *lin);
+SHREWQ_API size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin);
+
+/* Name of the kernel family the last forward on this handle dispatched to ("gemv",
+ * "tcgen05", "simt"); for tests and benchmarks. */
+SHREWQ_API const char *shrewq_linear_last_kernel(const shrewq_linear *lin);
+/* Forces the kernel family used by forwards issued from the calling thread: "gemv",
+ * "tcgen05", "simt", or "auto"/NULL to restore the built-in choice.  A forced kernel that
+ * cannot take a shape makes the forward fail with SHREWQ_ERR_UNSUPPORTED (it never falls
+ * back silently).  For tests and benchmarks; no counterpart in the reference. */
+SHREWQ_API int shrewq_force_kernel(const char *name);
+/* Number of kernels this context has launched since creation (for benchmark accounting). */
+SHREWQ_API uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHREWQ_H */

@@ -1,0 +1,352 @@
+// C ABI of libshrewq: contexts, argument validation, kernel dispatch, host-buffer
+// entry points.  See include/shrewq.h for the contract of each function.
+#include <new>
+
+#include "common.cuh"
+
+namespace shrewq {
+
+static thread_local char g_create_err[kErrLen] = {0};
+
+int set_err(shrewq_ctx *ctx, int code, const char *fmt, ...) {
+    char *dst = ctx ? ctx->err : g_create_err;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(dst, kErrLen, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+static int grow(shrewq_ctx *ctx, void **p, size_t *have, size_t want, bool pinned) {
+    if (*have >= want) return SHREWQ_OK;
+    // work already enqueued may still use the old buffer
+    SHREWQ_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*p) {
+        if (pinned) cudaFreeHost(*p); else cudaFree(*p);
+        *p = nullptr;
+        *have = 0;
+    }
+    size_t sz = want + want / 4 + 4096;
+    cudaError_t e = pinned ? cudaMallocHost(p, sz) : cudaMalloc(p, sz);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return set_err(ctx, SHREWQ_ERR_ALLOC, "allocation of %zu bytes failed: %s", sz, cudaGetErrorString(e));
+    }
+    *have = sz;
+    return SHREWQ_OK;
+}
+
+int ensure_scratch(shrewq_ctx *ctx, size_t bytes) { return grow(ctx, &ctx->scratch, &ctx->scratch_bytes, bytes, false); }
+
+int ensure_stage(shrewq_ctx *ctx, size_t dev_bytes, size_t pinned_bytes) {
+    int rc = grow(ctx, &ctx->stage_dev, &ctx->stage_dev_bytes, dev_bytes, false);
+    if (rc != SHREWQ_OK) return rc;
+    if (pinned_bytes) rc = grow(ctx, &ctx->stage_pinned, &ctx->stage_pinned_bytes, pinned_bytes, true);
+    return rc;
+}
+
+static int bind(shrewq_ctx *ctx) {
+    SHREWQ_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return SHREWQ_OK;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt };
+
+}  // namespace shrewq
+
+using namespace shrewq;
+
+// kernel family forced by shrewq_force_kernel for this thread (tests and benchmarks)
+static thread_local int g_forced_kernel = kAuto;
+
+extern "C" {
+
+const char *shrewq_version(void) { return "shrewq 0.1 sm_100a"; }
+
+int shrewq_ctx_create(int device, void *stream, shrewq_ctx **out) {
+    if (!out) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "ctx_create: out is NULL");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return set_err(nullptr, SHREWQ_ERR_NO_DEVICE, "no CUDA device available (%s); this library has no CPU path",
+                       e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+    }
+    if (device < 0 || device >= count)
+        return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "ctx_create: device %d out of range [0,%d)", device, count);
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess)
+        return set_err(nullptr, SHREWQ_ERR_CUDA, "cudaGetDeviceProperties failed");
+    if (prop.major != 10)
+        return set_err(nullptr, SHREWQ_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
+                       device, prop.major, prop.minor);
+    shrewq_ctx *ctx = new (std::nothrow) shrewq_ctx();
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_ALLOC, "out of host memory");
+    ctx->device = device;
+    ctx->stream = static_cast<cudaStream_t>(stream);
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaSetDevice(device) != cudaSuccess || cudaMalloc(&ctx->dev_status, sizeof(DeviceStatus)) != cudaSuccess ||
+        cudaMemset(ctx->dev_status, 0, sizeof(DeviceStatus)) != cudaSuccess) {
+        int rc = set_err(nullptr, SHREWQ_ERR_CUDA, "ctx_create: device setup failed: %s",
+                         cudaGetErrorString(cudaGetLastError()));
+        delete ctx;
+        return rc;
+    }
+    *out = ctx;
+    return SHREWQ_OK;
+}
+
+int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "set_stream: ctx is NULL");
+    ctx->stream = static_cast<cudaStream_t>(stream);
+    return SHREWQ_OK;
+}
+
+int shrewq_ctx_synchronize(shrewq_ctx *ctx) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "synchronize: ctx is NULL");
+    int rc = bind(ctx);
+    if (rc != SHREWQ_OK) return rc;
+    SHREWQ_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    DeviceStatus st;
+    SHREWQ_CUDA_TRY(ctx, cudaMemcpy(&st, ctx->dev_status, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st.timeout_flag) {
+        cudaMemset(ctx->dev_status, 0, sizeof(DeviceStatus));
+        return set_err(ctx, SHREWQ_ERR_TIMEOUT,
+                       "a kernel gave up a bounded wait: block %u role %u stage %u parity %u (results are invalid)",
+                       st.where >> 8, st.where & 0xFF, st.stage, st.parity);
+    }
+    return SHREWQ_OK;
+}
+
+void shrewq_ctx_destroy(shrewq_ctx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->stage_dev) cudaFree(ctx->stage_dev);
+    if (ctx->stage_pinned) cudaFreeHost(ctx->stage_pinned);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    delete ctx;
+}
+
+const char *shrewq_last_error(const shrewq_ctx *ctx) { return ctx ? ctx->err : g_create_err; }
+
+uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+int shrewq_force_kernel(const char *name) {
+    if (!name || !*name || !strcmp(name, "auto")) g_forced_kernel = kAuto;
+    else if (!strcmp(name, "gemv")) g_forced_kernel = kForceGemv;
+    else if (!strcmp(name, "tcgen05")) g_forced_kernel = kForceTc;
+    else if (!strcmp(name, "simt")) g_forced_kernel = kForceSimt;
+    else return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "force_kernel: unknown kernel '%s'", name);
+    return SHREWQ_OK;
+}
+
+// ---- quantize / dequantize --------------------------------------------------------------
+static int check_gran(shrewq_ctx *ctx, int g, const char *who) {
+    if (g != SHREWQ_PER_TENSOR && g != SHREWQ_PER_CHANNEL)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: granularity must be SHREWQ_PER_TENSOR or SHREWQ_PER_CHANNEL", who);
+    return SHREWQ_OK;
+}
+
+int shrewq_quantize_f32(shrewq_ctx *ctx, const float *w_dev, size_t rows, size_t cols, int granularity,
+                        int8_t *q_dev, double *scales_dev) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "quantize: ctx is NULL");
+    int rc = check_gran(ctx, granularity, "quantize");
+    if (rc != SHREWQ_OK) return rc;
+    const size_t n = rows * cols;
+    if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize: rows*cols overflows");
+    if (!scales_dev && (granularity == SHREWQ_PER_TENSOR || rows > 0))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize: scales_dev is NULL");
+    if (n > 0 && (!w_dev || !q_dev)) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize: w_dev / q_dev is NULL");
+    if ((reinterpret_cast<uintptr_t>(w_dev) & 3) || (reinterpret_cast<uintptr_t>(scales_dev) & 7))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize: w_dev must be 4-byte and scales_dev 8-byte aligned");
+    if ((rc = bind(ctx)) != SHREWQ_OK) return rc;
+    return launch_quantize(ctx, w_dev, rows, cols, granularity, q_dev, scales_dev);
+}
+
+int shrewq_quantize_f32_host(shrewq_ctx *ctx, const float *w_host, size_t rows, size_t cols, int granularity,
+                             int8_t *q_host, double *scales_host) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "quantize_host: ctx is NULL");
+    int rc = check_gran(ctx, granularity, "quantize_host");
+    if (rc != SHREWQ_OK) return rc;
+    const size_t n = rows * cols;
+    if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_host: rows*cols overflows");
+    const size_t ns = granularity == SHREWQ_PER_CHANNEL ? rows : 1;
+    if ((n > 0 && (!w_host || !q_host)) || (ns > 0 && !scales_host))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_host: NULL buffer");
+    if ((rc = bind(ctx)) != SHREWQ_OK) return rc;
+    const size_t off_q = align_up(n * 4, 256), off_s = off_q + align_up(n, 256);
+    if ((rc = ensure_stage(ctx, off_s + ns * 8 + 256, 0)) != SHREWQ_OK) return rc;
+    char *base = static_cast<char *>(ctx->stage_dev);
+    float *w_dev = reinterpret_cast<float *>(base);
+    int8_t *q_dev = reinterpret_cast<int8_t *>(base + off_q);
+    double *s_dev = reinterpret_cast<double *>(base + off_s);
+    if (n) SHREWQ_CUDA_TRY(ctx, cudaMemcpyAsync(w_dev, w_host, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    if ((rc = launch_quantize(ctx, w_dev, rows, cols, granularity, q_dev, s_dev)) != SHREWQ_OK) return rc;
+    if (n) SHREWQ_CUDA_TRY(ctx, cudaMemcpyAsync(q_host, q_dev, n, cudaMemcpyDeviceToHost, ctx->stream));
+    if (ns) SHREWQ_CUDA_TRY(ctx, cudaMemcpyAsync(scales_host, s_dev, ns * 8, cudaMemcpyDeviceToHost, ctx->stream));
+    SHREWQ_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return SHREWQ_OK;
+}
+
+int shrewq_dequantize(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev, size_t rows, size_t cols,
+                      int granularity, int out_dtype, void *out_dev) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "dequantize: ctx is NULL");
+    int rc = check_gran(ctx, granularity, "dequantize");
+    if (rc != SHREWQ_OK) return rc;
+    if (out_dtype != SHREWQ_F32 && out_dtype != SHREWQ_BF16)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize: out_dtype must be SHREWQ_F32 or SHREWQ_BF16");
+    const size_t n = rows * cols;
+    if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize: rows*cols overflows");
+    if (n > 0 && (!q_dev || !scales_dev || !out_dev)) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize: NULL buffer");
+    if ((rc = bind(ctx)) != SHREWQ_OK) return rc;
+    return launch_dequantize(ctx, q_dev, scales_dev, rows, cols, granularity, out_dtype, out_dev);
+}
+
+// ---- quantized Linear ---------------------------------------------------------------------
+int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev, const float *bias_dev,
+                         size_t out_features, size_t in_features, int granularity, shrewq_linear **out) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "linear_create: ctx is NULL");
+    if (!out) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_create: out is NULL");
+    *out = nullptr;
+    int rc = check_gran(ctx, granularity, "linear_create");
+    if (rc != SHREWQ_OK) return rc;
+    if (out_features == 0 || in_features == 0)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_create: out_features and in_features must be positive");
+    if (!q_dev || !scales_dev) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_create: q_dev / scales_dev is NULL");
+    if (out_features > 0x7FFFFFFFull || in_features > 0x7FFFFFFFull)
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "linear_create: dimensions above 2^31-1");
+    if ((rc = bind(ctx)) != SHREWQ_OK) return rc;
+    shrewq_linear *lin = new (std::nothrow) shrewq_linear();
+    if (!lin) return set_err(ctx, SHREWQ_ERR_ALLOC, "out of host memory");
+    lin->ctx = ctx;
+    lin->q = q_dev;
+    lin->bias = bias_dev;
+    lin->n = out_features;
+    lin->k = in_features;
+    lin->granularity = granularity;
+    cudaError_t e = cudaMalloc(&lin->scales_f32, out_features * sizeof(float));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        delete lin;
+        return set_err(ctx, SHREWQ_ERR_ALLOC, "linear_create: cudaMalloc of scales failed: %s", cudaGetErrorString(e));
+    }
+    rc = launch_scales_to_f32(ctx, scales_dev, granularity, out_features, lin->scales_f32);
+    if (rc == SHREWQ_OK && (in_features % 16) == 0 && (reinterpret_cast<uintptr_t>(q_dev) & 15) == 0) {
+        if (encode_weight_tmap(ctx, q_dev, out_features, in_features, lin->w_tmap) == SHREWQ_OK) lin->tmap_ok = true;
+    }
+    if (rc != SHREWQ_OK) {
+        cudaFree(lin->scales_f32);
+        delete lin;
+        return rc;
+    }
+    *out = lin;
+    return SHREWQ_OK;
+}
+
+void shrewq_linear_destroy(shrewq_linear *lin) {
+    if (!lin) return;
+    cudaSetDevice(lin->ctx->device);
+    cudaStreamSynchronize(lin->ctx->stream);
+    if (lin->scales_f32) cudaFree(lin->scales_f32);
+    delete lin;
+}
+
+size_t shrewq_linear_in_features(const shrewq_linear *lin) { return lin ? lin->k : 0; }
+size_t shrewq_linear_out_features(const shrewq_linear *lin) { return lin ? lin->n : 0; }
+/* fp32 size minus INT8 size — quantize.rs:455-459 */
+size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin) { return lin ? lin->n * lin->k * 4 - lin->n * lin->k : 0; }
+const char *shrewq_linear_last_kernel(const shrewq_linear *lin) { return lin ? lin->last_kernel : "none"; }
+
+static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev, int x_dtype, size_t M, void *y_dev,
+                        int y_dtype, size_t ldy, int epilogue, const char *who) {
+    if (!lin) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "%s: handle is NULL", who);
+    shrewq_ctx *ctx = lin->ctx;
+    if (up && (up->ctx != ctx || up->n != lin->n || up->k != lin->k))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: gate and up must share context and shape", who);
+    if ((x_dtype != SHREWQ_F32 && x_dtype != SHREWQ_BF16) || (y_dtype != SHREWQ_F32 && y_dtype != SHREWQ_BF16))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: dtype must be SHREWQ_F32 or SHREWQ_BF16", who);
+    if (epilogue != SHREWQ_EPILOGUE_NONE && epilogue != SHREWQ_EPILOGUE_RELU)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: unknown epilogue %d", who, epilogue);
+    if (M == 0) return SHREWQ_OK;
+    if (!x_dev || !y_dev) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: x / y is NULL", who);
+    if (ldy < lin->n) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: ldy (%zu) smaller than out_features (%zu)", who, ldy, lin->n);
+    const size_t xal = x_dtype == SHREWQ_BF16 ? 2 : 4, yal = y_dtype == SHREWQ_BF16 ? 2 : 4;
+    if ((reinterpret_cast<uintptr_t>(x_dev) % xal) || (reinterpret_cast<uintptr_t>(y_dev) % yal))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: x / y not aligned to their element size", who);
+    if (M > 0x7FFFFFFFull) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: M above 2^31-1", who);
+    int rc = bind(ctx);
+    if (rc != SHREWQ_OK) return rc;
+
+    ForwardArgs a;
+    a.q = lin->q; a.scales = lin->scales_f32; a.bias = lin->bias;
+    a.x = x_dev; a.x_dtype = x_dtype; a.y = y_dev; a.y_dtype = y_dtype;
+    a.M = M; a.N = lin->n; a.K = lin->k; a.ldy = ldy; a.epilogue = epilogue;
+    if (up) { a.q_up = up->q; a.scales_up = up->scales_f32; a.bias_up = up->bias; }
+
+    const bool vec16 = (lin->k % 16) == 0 && (reinterpret_cast<uintptr_t>(lin->q) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 &&
+                       (!up || (reinterpret_cast<uintptr_t>(up->q) & 15) == 0);
+    const bool gemv_ok = vec16 && M <= 16;
+    const bool tc_ok = tcgen05_supported(a) && lin->tmap_ok && (!up || up->tmap_ok);
+    int choice;
+    switch (g_forced_kernel) {
+        case kForceGemv:
+            if (!gemv_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced gemv cannot take this shape", who);
+            choice = kForceGemv; break;
+        case kForceTc:
+            if (!tc_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05 cannot take this shape/dtype", who);
+            choice = kForceTc; break;
+        case kForceSimt: choice = kForceSimt; break;
+        default:
+            // CUDA-core GEMV keeps up with HBM only for a few tokens; beyond that the tensor
+            // cores take over (bf16 activations), else the general f32 kernel.
+            if (gemv_ok && (M <= 4 || !tc_ok)) choice = kForceGemv;
+            else if (tc_ok) choice = kForceTc;
+            else choice = kForceSimt;
+    }
+    const char *name;
+    if (choice == kForceGemv) { rc = launch_gemv(ctx, a); name = "gemv"; }
+    else if (choice == kForceTc) { rc = launch_gemm_tcgen05(ctx, a, lin->w_tmap, up ? up->w_tmap : nullptr); name = "tcgen05"; }
+    else { rc = launch_gemm_simt(ctx, a); name = "simt"; }
+    lin->last_kernel = name;
+    return rc;
+}
+
+int shrewq_linear_forward(shrewq_linear *lin, const void *x_dev, int x_dtype, size_t M, void *y_dev, int y_dtype,
+                          size_t ldy, int epilogue) {
+    return forward_impl(lin, nullptr, x_dev, x_dtype, M, y_dev, y_dtype, ldy, epilogue, "linear_forward");
+}
+
+int shrewq_linear_forward_gate_up_silu(shrewq_linear *gate, shrewq_linear *up, const void *x_dev, int x_dtype,
+                                       size_t M, void *h_dev, int h_dtype, size_t ldh) {
+    if (!up) return set_err(gate ? gate->ctx : nullptr, SHREWQ_ERR_INVALID_ARG, "gate_up_silu: up handle is NULL");
+    return forward_impl(gate, up, x_dev, x_dtype, M, h_dev, h_dtype, ldh, SHREWQ_EPILOGUE_NONE, "gate_up_silu");
+}
+
+int shrewq_linear_forward_host(shrewq_linear *lin, const void *x_host, int x_dtype, size_t M, void *y_host,
+                               int y_dtype, int epilogue) {
+    if (!lin) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "linear_forward_host: handle is NULL");
+    shrewq_ctx *ctx = lin->ctx;
+    if ((x_dtype != SHREWQ_F32 && x_dtype != SHREWQ_BF16) || (y_dtype != SHREWQ_F32 && y_dtype != SHREWQ_BF16))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_forward_host: dtype must be SHREWQ_F32 or SHREWQ_BF16");
+    if (M == 0) return SHREWQ_OK;
+    if (!x_host || !y_host) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_forward_host: x / y is NULL");
+    int rc = bind(ctx);
+    if (rc != SHREWQ_OK) return rc;
+    const size_t xb = M * lin->k * (x_dtype == SHREWQ_BF16 ? 2 : 4), yb = M * lin->n * (y_dtype == SHREWQ_BF16 ? 2 : 4);
+    const size_t off_y = align_up(xb, 256);
+    if ((rc = ensure_stage(ctx, off_y + yb + 256, 0)) != SHREWQ_OK) return rc;
+    char *base = static_cast<char *>(ctx->stage_dev);
+    SHREWQ_CUDA_TRY(ctx, cudaMemcpyAsync(base, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = forward_impl(lin, nullptr, base, x_dtype, M, base + off_y, y_dtype, lin->n, epilogue, "linear_forward_host");
+    if (rc != SHREWQ_OK) return rc;
+    SHREWQ_CUDA_TRY(ctx, cudaMemcpyAsync(y_host, base + off_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    return shrewq_ctx_synchronize(ctx);
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+// Internal declarations shared by the translation units of libshrewq.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/shrewq.h"
+
+namespace shrewq {
+
+constexpr int kErrLen = 512;
+
+// Device-visible record a kernel writes when one of its bounded waits runs out.
+struct DeviceStatus {
+    unsigned int timeout_flag;  // 0 = fine; otherwise a code naming the wait that gave up
+    unsigned int where;         // (blockIdx.x << 8) | role
+    unsigned int stage;
+    unsigned int parity;
+};
+
+}  // namespace shrewq
+
+// Opaque in the ABI.
+struct shrewq_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    char err[shrewq::kErrLen] = {0};
+    uint64_t launches = 0;
+    // scratch: per-tensor amax word, split-K partial sums and tile counters
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    // zeroed counter area at the head of a separate small allocation
+    unsigned int *counters = nullptr;
+    size_t counter_words = 0;
+    // staging for the *_host entry points
+    void *stage_dev = nullptr;
+    size_t stage_dev_bytes = 0;
+    void *stage_pinned = nullptr;
+    size_t stage_pinned_bytes = 0;
+    // device status block + pinned mirror
+    shrewq::DeviceStatus *dev_status = nullptr;
+};
+
+struct shrewq_linear {
+    shrewq_ctx *ctx = nullptr;
+    const int8_t *q = nullptr;
+    const float *bias = nullptr;
+    float *scales_f32 = nullptr;  // owned, out_features entries (per-tensor scale broadcast)
+    size_t n = 0, k = 0;
+    int granularity = 0;
+    const char *last_kernel = "none";
+    // TMA descriptor for the INT8 weight matrix (128 B, opaque CUtensorMap), valid when
+    // tmap_ok: 64-byte k boxes over 128 weight rows.
+    alignas(64) unsigned char w_tmap[128];
+    bool tmap_ok = false;
+};
+
+namespace shrewq {
+
+int set_err(shrewq_ctx *ctx, int code, const char *fmt, ...);
+int ensure_scratch(shrewq_ctx *ctx, size_t bytes);
+int ensure_stage(shrewq_ctx *ctx, size_t dev_bytes, size_t pinned_bytes);
+
+#define SHREWQ_CUDA_TRY(ctx, expr)                                                         \
+    do {                                                                                   \
+        cudaError_t e__ = (expr);                                                          \
+        if (e__ != cudaSuccess)                                                            \
+            return shrewq::set_err((ctx), SHREWQ_ERR_CUDA, "%s failed: %s", #expr,          \
+                                   cudaGetErrorString(e__));                               \
+    } while (0)
+
+// ---- launchers implemented in the kernel translation units -------------------------
+int launch_quantize(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, int granularity,
+                    int8_t *q, double *scales);
+int launch_dequantize(shrewq_ctx *ctx, const int8_t *q, const double *scales, size_t rows,
+                      size_t cols, int granularity, int out_dtype, void *out);
+int launch_scales_to_f32(shrewq_ctx *ctx, const double *scales, int granularity, size_t n, float *out);
+
+struct ForwardArgs {
+    const int8_t *q;       // [N,K]
+    const float *scales;   // [N] f32
+    const float *bias;     // [N] or null
+    const void *x;         // [M,K]
+    int x_dtype;
+    void *y;               // [M, ldy]
+    int y_dtype;
+    size_t M, N, K, ldy;
+    int epilogue;
+    // gate/up fusion: when q_up != null the output is silu(gate)*up
+    const int8_t *q_up = nullptr;
+    const float *scales_up = nullptr;
+    const float *bias_up = nullptr;
+};
+
+int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a);
+int launch_gemm_simt(shrewq_ctx *ctx, const ForwardArgs &a);
+bool tcgen05_supported(const ForwardArgs &a);
+int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);
+int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, void *tmap_out);
+
+// bf16 <-> f32 helpers usable on host and device
+__host__ __device__ inline float bf16_bits_to_float(uint16_t h) {
+    uint32_t b = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &b, 4);
+    return f;
+}
+
+}  // namespace shrewq

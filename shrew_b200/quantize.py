@@ -1,0 +1,363 @@
+"""Host-side mirror of the reference's `quantize` module (crates/shrew/src/quantize.rs)
+over the libshrewq C ABI.
+
+Same names, argument meaning and error behaviour as the Rust API, so tests read like the
+reference's own.  Tensors are torch CUDA tensors (torch is plumbing here: device memory
+and streams); every computation is a libshrewq kernel.  There is no CPU path: a tensor
+that is not on a CUDA device is rejected.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import ShrewError
+
+__all__ = [
+    "QuantBits", "QuantMode", "QuantGranularity", "QuantConfig", "QuantizedTensor", "quantize_tensor",
+    "dequantize_tensor", "QuantizedLinear", "quantize_named_parameters", "QuantStats", "quantization_stats",
+    "Linear", "ShrewError", "Device",
+]
+
+
+# ---- configuration (quantize.rs:35-140) ---------------------------------------------------
+class QuantBits(enum.Enum):
+    Int8 = 8
+    Int4 = 4
+
+
+class QuantMode(enum.Enum):
+    Symmetric = 0
+    Asymmetric = 1
+
+
+class QuantGranularity(enum.Enum):
+    PerTensor = _lib.PER_TENSOR
+    PerChannel = _lib.PER_CHANNEL
+
+
+@dataclass
+class QuantConfig:
+    """quantize.rs:64-121.  Default = INT8 symmetric per-tensor."""
+    bits: QuantBits = QuantBits.Int8
+    mode: QuantMode = QuantMode.Symmetric
+    granularity: QuantGranularity = QuantGranularity.PerTensor
+
+    @staticmethod
+    def int8() -> "QuantConfig":
+        return QuantConfig()
+
+    @staticmethod
+    def int8_per_channel() -> "QuantConfig":
+        return QuantConfig(QuantBits.Int8, QuantMode.Symmetric, QuantGranularity.PerChannel)
+
+    @staticmethod
+    def int4() -> "QuantConfig":
+        return QuantConfig(QuantBits.Int4, QuantMode.Symmetric, QuantGranularity.PerTensor)
+
+    @staticmethod
+    def int4_per_channel() -> "QuantConfig":
+        return QuantConfig(QuantBits.Int4, QuantMode.Symmetric, QuantGranularity.PerChannel)
+
+    def asymmetric(self) -> "QuantConfig":
+        return QuantConfig(self.bits, QuantMode.Asymmetric, self.granularity)
+
+    def qmax(self) -> float:
+        return 127.0 if self.bits is QuantBits.Int8 else 7.0
+
+    def qmin(self) -> float:
+        if self.bits is QuantBits.Int8:
+            return -127.0 if self.mode is QuantMode.Symmetric else -128.0
+        return -7.0 if self.mode is QuantMode.Symmetric else -8.0
+
+    def _require_int8_symmetric(self) -> None:
+        if self.bits is not QuantBits.Int8 or self.mode is not QuantMode.Symmetric:
+            raise ShrewError(_lib.ERR_UNSUPPORTED,
+                             "only INT8 symmetric quantization has device kernels (INT4 and asymmetric are not built)")
+
+
+# ---- device / context ------------------------------------------------------------------------
+class Device:
+    """One libshrewq context per CUDA device (the role of `B::Device`).  Work is enqueued on
+    torch's current stream for that device."""
+    _by_index: dict = {}
+
+    def __init__(self, index: int):
+        self.index = index
+        h = ctypes.c_void_p()
+        rc = _lib.lib().shrewq_ctx_create(index, None, ctypes.byref(h))
+        _lib.check(rc, None)
+        self.handle = h
+
+    @classmethod
+    def get(cls, device) -> "Device":
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise ShrewError(_lib.ERR_NO_DEVICE, f"tensor is on '{dev}'; this path runs on CUDA devices only (no CPU fallback)")
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        d = cls._by_index.get(idx)
+        if d is None:
+            d = cls._by_index[idx] = Device(idx)
+        return d
+
+    def bind_stream(self) -> None:
+        s = torch.cuda.current_stream(self.index).cuda_stream
+        _lib.check(_lib.lib().shrewq_ctx_set_stream(self.handle, ctypes.c_void_p(s)), self.handle)
+
+    def synchronize(self) -> None:
+        """Waits for the stream and surfaces a kernel that gave up a bounded wait."""
+        self.bind_stream()
+        _lib.check(_lib.lib().shrewq_ctx_synchronize(self.handle), self.handle)
+
+    def launch_count(self) -> int:
+        return int(_lib.lib().shrewq_ctx_launch_count(self.handle))
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _rows_cols(shape: Sequence[int]) -> Tuple[int, int]:
+    """rows = shape[0], cols = product(shape[1..]) (quantize.rs:280-281); rank 0 is one
+    per-tensor element (quantize.rs:276-278)."""
+    if len(shape) == 0:
+        return 1, 1
+    cols = 1
+    for s in shape[1:]:
+        cols *= int(s)
+    return int(shape[0]), cols
+
+
+_DTYPE_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+
+
+# ---- QuantizedTensor (quantize.rs:150-185) -----------------------------------------------------
+@dataclass
+class QuantizedTensor:
+    data: torch.Tensor            # int8 codes on the device, flat, source order
+    scales: torch.Tensor          # float64 on the device, len 1 or shape[0]
+    shape: List[int]
+    original_dtype: torch.dtype
+    config: QuantConfig = field(default_factory=QuantConfig)
+
+    @property
+    def zero_points(self) -> List[float]:
+        """All 0.0 in symmetric mode (quantize.rs:351)."""
+        return [0.0] * int(self.scales.numel())
+
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= int(s)
+        return n
+
+    def size_bytes(self) -> int:
+        return self.numel() if self.config.bits is QuantBits.Int8 else (self.numel() + 1) // 2
+
+    def compression_ratio(self) -> float:
+        return (self.numel() * 4) / self.size_bytes()
+
+
+def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTensor:
+    """quantize.rs:194-205 on the GPU.  `tensor` is an f32 CUDA tensor."""
+    config._require_int8_symmetric()
+    dev = Device.get(tensor.device)
+    if tensor.dtype != torch.float32:
+        raise ShrewError(_lib.ERR_UNSUPPORTED, f"quantize_tensor: dtype {tensor.dtype} not supported (f32 only)")
+    w = tensor.contiguous()
+    shape = list(w.shape)
+    rows, cols = _rows_cols(shape)
+    gran = config.granularity
+    if len(shape) == 0:
+        gran = QuantGranularity.PerTensor
+    n_scales = rows if gran is QuantGranularity.PerChannel else 1
+    q = torch.empty(w.numel(), dtype=torch.int8, device=w.device)
+    scales = torch.empty(n_scales, dtype=torch.float64, device=w.device)
+    dev.bind_stream()
+    rc = _lib.lib().shrewq_quantize_f32(dev.handle, _ptr(w), rows, cols, gran.value, _ptr(q), _ptr(scales))
+    _lib.check(rc, dev.handle)
+    return QuantizedTensor(q, scales, shape, tensor.dtype, config)
+
+
+def dequantize_tensor(qtensor: QuantizedTensor, device=None) -> torch.Tensor:
+    """quantize.rs:210-225 on the GPU: a tensor of the original dtype and shape."""
+    dev_t = qtensor.data.device if device is None else torch.device(device)
+    dev = Device.get(dev_t)
+    out_dtype = qtensor.original_dtype
+    if out_dtype not in _DTYPE_CODE:
+        raise ShrewError(_lib.ERR_UNSUPPORTED, f"dequantize_tensor: target dtype {out_dtype} not supported")
+    rows, cols = _rows_cols(qtensor.shape)
+    gran = qtensor.config.granularity if len(qtensor.shape) else QuantGranularity.PerTensor
+    out = torch.empty(qtensor.shape, dtype=out_dtype, device=qtensor.data.device)
+    dev.bind_stream()
+    rc = _lib.lib().shrewq_dequantize(dev.handle, _ptr(qtensor.data), _ptr(qtensor.scales), rows, cols, gran.value,
+                                      _DTYPE_CODE[out_dtype], _ptr(out))
+    _lib.check(rc, dev.handle)
+    return out
+
+
+# ---- a minimal shrew_nn::Linear stand-in --------------------------------------------------------
+class Linear:
+    """Holds what QuantizedLinear::from_linear reads from shrew_nn::Linear: weight [out,in]
+    and an optional bias stored as [1,out] (crates/shrew/tests/nn_tests.rs:43-44)."""
+
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, name: str = ""):
+        assert weight.dim() == 2
+        self.weight = weight
+        self.bias = None if bias is None else bias.reshape(1, -1)
+        self.name = name
+
+    def parameters(self) -> List[torch.Tensor]:
+        return [self.weight] + ([self.bias] if self.bias is not None else [])
+
+    def named_parameters(self) -> List[Tuple[str, torch.Tensor]]:
+        p = self.name + "." if self.name else ""
+        return [(p + "weight", self.weight)] + ([(p + "bias", self.bias)] if self.bias is not None else [])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise ShrewError(_lib.ERR_UNSUPPORTED, "the float Linear forward is outside this library's path")
+
+
+# ---- QuantizedLinear (quantize.rs:384-482) --------------------------------------------------------
+class QuantizedLinear:
+    def __init__(self, weight_q: QuantizedTensor, bias: Optional[torch.Tensor], device=None):
+        """QuantizedLinear::new (quantize.rs:437-447)."""
+        weight_q.config._require_int8_symmetric()
+        if len(weight_q.shape) != 2:
+            raise ShrewError(_lib.ERR_INVALID_ARG, "QuantizedLinear needs a rank-2 weight [out,in]")
+        self.weight_q = weight_q
+        self.bias = bias
+        self.out_features, self.in_features = int(weight_q.shape[0]), int(weight_q.shape[1])
+        self.device = Device.get(weight_q.data.device if device is None else device)
+        self._bias_flat = None
+        if bias is not None:
+            if bias.numel() != self.out_features:
+                raise ShrewError(_lib.ERR_INVALID_ARG, "bias must have out_features elements")
+            self._bias_flat = bias.reshape(-1).to(torch.float32).contiguous()
+        h = ctypes.c_void_p()
+        self.device.bind_stream()
+        rc = _lib.lib().shrewq_linear_create(self.device.handle, _ptr(weight_q.data), _ptr(weight_q.scales),
+                                             _ptr(self._bias_flat), self.out_features, self.in_features,
+                                             weight_q.config.granularity.value, ctypes.byref(h))
+        _lib.check(rc, self.device.handle)
+        self._h = h
+
+    @classmethod
+    def new(cls, weight_q: QuantizedTensor, bias: Optional[torch.Tensor], device=None) -> "QuantizedLinear":
+        return cls(weight_q, bias, device)
+
+    @classmethod
+    def from_linear(cls, linear, config: QuantConfig) -> "QuantizedLinear":
+        """quantize.rs:413-434: params[0] is the weight, params[1] the bias if present."""
+        params = list(linear.parameters())
+        weight = params[0]
+        bias = params[1] if len(params) > 1 else None
+        return cls(quantize_tensor(weight.detach(), config), None if bias is None else bias.detach(), weight.device)
+
+    def weight_quantized(self) -> QuantizedTensor:
+        return self.weight_q
+
+    def memory_savings_bytes(self) -> int:
+        return int(_lib.lib().shrewq_linear_memory_savings_bytes(self._h))
+
+    def parameters(self) -> list:
+        """Inference only: no trainable parameters (quantize.rs:478-481)."""
+        return []
+
+    def last_kernel(self) -> str:
+        return _lib.lib().shrewq_linear_last_kernel(self._h).decode()
+
+    def forward(self, x: torch.Tensor, epilogue: int = _lib.EPILOGUE_NONE, out: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """Module::forward (quantize.rs:463-476).  x is [M, in_features] f32 or bf16 on the
+        layer's device; the result has x's dtype.  `out` may be a column slice of a wider
+        row-major buffer (last stride 1): the shard-writes-its-slice case."""
+        if x.dim() != 2 or x.shape[1] != self.in_features:
+            raise ShrewError(_lib.ERR_INVALID_ARG,
+                             f"forward: expected x of shape [M,{self.in_features}], got {list(x.shape)}")
+        if x.dtype not in _DTYPE_CODE:
+            raise ShrewError(_lib.ERR_UNSUPPORTED, f"forward: activation dtype {x.dtype} not supported")
+        if x.device.type != "cuda" or x.device.index != self.device.index:
+            raise ShrewError(_lib.ERR_INVALID_ARG, "forward: x is not on the layer's device")
+        x = x.contiguous()
+        M = x.shape[0]
+        if out is None:
+            out = torch.empty((M, self.out_features), dtype=out_dtype or x.dtype, device=x.device)
+        if out.dim() != 2 or out.shape[0] != M or out.shape[1] != self.out_features or (M > 0 and out.stride(1) != 1):
+            raise ShrewError(_lib.ERR_INVALID_ARG, "forward: bad output buffer")
+        ldy = out.stride(0) if M > 1 else max(out.stride(0), self.out_features)
+        self.device.bind_stream()
+        rc = _lib.lib().shrewq_linear_forward(self._h, _ptr(x), _DTYPE_CODE[x.dtype], M, _ptr(out),
+                                              _DTYPE_CODE[out.dtype], ldy, epilogue)
+        _lib.check(rc, self.device.handle)
+        return out
+
+    __call__ = forward
+
+    def forward_gate_up_silu(self, up: "QuantizedLinear", x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """silu(self.forward(x)) * up.forward(x) in one pass over x (self is the gate)."""
+        x = x.contiguous()
+        M = x.shape[0]
+        if out is None:
+            out = torch.empty((M, self.out_features), dtype=x.dtype, device=x.device)
+        ldh = out.stride(0) if M > 1 else max(out.stride(0), self.out_features)
+        self.device.bind_stream()
+        rc = _lib.lib().shrewq_linear_forward_gate_up_silu(self._h, up._h, _ptr(x), _DTYPE_CODE[x.dtype], M, _ptr(out),
+                                                           _DTYPE_CODE[out.dtype], ldh)
+        _lib.check(rc, self.device.handle)
+        return out
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            try:
+                _lib.lib().shrewq_linear_destroy(h)
+            except Exception:
+                pass
+            self._h = None
+
+    def __repr__(self) -> str:
+        return (f"QuantizedLinear(in_features={self.in_features}, out_features={self.out_features}, "
+                f"bits={self.weight_q.config.bits.name}, compression={self.weight_q.compression_ratio():.1f}x)")
+
+
+# ---- model-level helpers (quantize.rs:500-586) ------------------------------------------------------
+def quantize_named_parameters(module, config: QuantConfig) -> List[Tuple[str, QuantizedTensor]]:
+    """Every parameter of rank >= 2 is quantized — including a Linear's [1,out] bias, which
+    is rank 2 in Shrew (quantize.rs:507-513, :760-766)."""
+    out = []
+    for name, t in module.named_parameters():
+        if t.dim() >= 2:
+            out.append((name, quantize_tensor(t.detach(), config)))
+    return out
+
+
+@dataclass
+class QuantStats:
+    num_quantized: int
+    num_fp32: int
+    fp32_bytes: int
+    quantized_bytes: int
+    compression_ratio: float
+
+
+def quantization_stats(module, config: QuantConfig) -> QuantStats:
+    """quantize.rs:534-586 (pure bookkeeping, no device work)."""
+    nq = nf = fp32 = qb = 0
+    for _, t in module.named_parameters():
+        numel = t.numel()
+        fp32 += numel * 4
+        if t.dim() >= 2:
+            nq += 1
+            size = numel if config.bits is QuantBits.Int8 else (numel + 1) // 2
+            meta = 16 if config.granularity is QuantGranularity.PerTensor else (16 if t.dim() == 0 else t.shape[0] * 16)
+            qb += size + meta
+        else:
+            nf += 1
+            qb += numel * 4
+    return QuantStats(nq, nf, fp32, qb, (fp32 / qb) if qb > 0 else 1.0)
