@@ -36,7 +36,13 @@ static int grow(shrewq_ctx *ctx, void **p, size_t *have, size_t want, bool pinne
     return SHREWQ_OK;
 }
 
-int ensure_scratch(shrewq_ctx *ctx, size_t bytes) { return grow(ctx, &ctx->scratch, &ctx->scratch_bytes, bytes, false); }
+int ensure_scratch(shrewq_ctx *ctx, size_t bytes) {
+    const void *before = ctx->scratch;
+    // never smaller than the fixed head (quantizer words + split-K tile counters)
+    int rc = grow(ctx, &ctx->scratch, &ctx->scratch_bytes, bytes < 8192 ? 8192 : bytes, false);
+    if (ctx->scratch != before) ctx->counters_zeroed = false;  // new memory: counters are garbage
+    return rc;
+}
 
 int ensure_stage(shrewq_ctx *ctx, size_t dev_bytes, size_t pinned_bytes) {
     int rc = grow(ctx, &ctx->stage_dev, &ctx->stage_dev_bytes, dev_bytes, false);

@@ -35,9 +35,8 @@ struct shrewq_ctx {
     // scratch: per-tensor amax word, split-K partial sums and tile counters
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
-    // zeroed counter area at the head of a separate small allocation
-    unsigned int *counters = nullptr;
-    size_t counter_words = 0;
+    // split-K tile counters live in scratch; they are zeroed once and reset by the kernels
+    bool counters_zeroed = false;
     // staging for the *_host entry points
     void *stage_dev = nullptr;
     size_t stage_dev_bytes = 0;

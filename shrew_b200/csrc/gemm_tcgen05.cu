@@ -27,6 +27,8 @@
 // all roles fall through to the common teardown, which frees TMEM.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace shrewq {
@@ -35,7 +37,6 @@ namespace {
 constexpr int kTileN = 128;  // weight rows per CTA (MMA M, TMEM lanes)
 constexpr int kBlockK = 64;  // k per pipeline stage
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;
 constexpr uint32_t kSpinFast = 1u << 14;
 constexpr uint32_t kSpinSlow = 1u << 21;  // x ~100 ns sleeps: a fraction of a second
 
@@ -89,9 +90,9 @@ struct Ctl {  // lives in shared memory
     uint32_t tmem_base;
 };
 
-// Bounded wait.  Returns false if it gave up or another role already did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st,
-                                          uint32_t role, uint32_t stage) {
+// Slow path of the bounded wait, kept out of line so the hot loops only carry one try_wait.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st,
+                                            uint32_t role, uint32_t stage) {
     for (uint32_t i = 0; i < kSpinFast; ++i)
         if (mbar_try(bar, parity)) return true;
     for (uint32_t i = 0; i < kSpinSlow; ++i) {
@@ -106,6 +107,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl *ct
         st->parity = parity;
     }
     return false;
+}
+
+// Bounded wait.  Returns false if it gave up or another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st,
+                                          uint32_t role, uint32_t stage) {
+    if (mbar_try(bar, parity)) return true;
+    if (mbar_try(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, ctl, st, role, stage);
+}
+
+// Warp-level wait: lane 0 polls, the outcome is broadcast with a shuffle (which also
+// synchronises the warp and orders memory among its lanes).  32 lanes polling the same
+// mbarrier word serialise in the shared-memory pipe.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st,
+                                               uint32_t role, uint32_t stage) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, st, role, stage) ? 1 : 0;
+    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int c0, int c1, uint32_t bar) {
@@ -130,6 +149,27 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Predicated forms for warp-converged loops: every lane computes the (uniform) operands, one
+// lane (leader != 0) issues.
+__device__ __forceinline__ void tc_mma_ts_if(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(uint32_t leader, uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(leader)
         : "memory");
 }
 
@@ -191,14 +231,38 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16 *p, float
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
-template <int TOK, int NW, typename YT>
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+#ifdef SHREWQ_TRACE
+__device__ long long *g_trace = nullptr;  // [role 0..3][kb 0..255][tag 0..3]
+__device__ __forceinline__ void trace_rec(long long *tr, int role, int kb, int tag) {
+    if (tr && kb < 256) tr[(role * 256 + kb) * 4 + tag] = clock64();
+}
+#define TRACE(role, kb, tag) do { if ((threadIdx.x & 31) == 0) trace_rec(trace_buf, role, kb, tag); } while (0)
+#define TRACE_INIT long long *trace_buf = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? g_trace : nullptr;
+#else
+#define TRACE(role, kb, tag)
+#define TRACE_INIT
+#endif
+
+struct SplitK {
+    float *partials;         // [tile][split][TOK][128] f32, only when gridDim.z > 1
+    unsigned int *counters;  // one per (n tile, token tile), zero between launches
+    int kb_per_split;
+};
+
+// G = number of converter groups (4 warps each); group g converts k-blocks g, g+G, ...
+template <int TOK, int NW, int G, typename YT>
+__global__ void __launch_bounds__(64 + 128 * G, 1)
 linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
                          const __grid_constant__ CUtensorMap tmap_x, const float *__restrict__ scales,
                          const float *__restrict__ bias, const float *__restrict__ scales2,
                          const float *__restrict__ bias2, YT *__restrict__ y, int M, int N, int K, size_t ldy,
-                         int epilogue, DeviceStatus *status) {
+                         int epilogue, SplitK sk, DeviceStatus *status) {
     using C = Cfg<TOK, NW>;
+    TRACE_INIT
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle with base_offset 0
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -206,11 +270,14 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     uint64_t *bars = reinterpret_cast<uint64_t *>(bar_area);
     // barrier indices: full[s]=s, aready[s]=S+s, empty[s]=2S+s, accfull=3S
     Ctl *ctl = reinterpret_cast<Ctl *>(bar_area + 512);
+    int *s_is_last = reinterpret_cast<int *>(bar_area + 640);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kTileN;
     const int m0 = blockIdx.y * TOK;
-    const int num_kb = (K + kBlockK - 1) / kBlockK;
+    const int num_kb_total = (K + kBlockK - 1) / kBlockK;
+    const int kb_begin = blockIdx.z * sk.kb_per_split;
+    const int nkb = min(num_kb_total - kb_begin, sk.kb_per_split);  // >= 1 by construction of the grid
     auto bar = [&](int i) { return smem_u32(bars + i); };
     auto stage_w = [&](int s, int w) { return smem + s * C::kStageBytes + w * C::kWBytes; };
     auto stage_x = [&](int s) { return smem + s * C::kStageBytes + NW * C::kWBytes; };
@@ -236,60 +303,86 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
+    // Producer and MMA issuer are single threads whose loop time bounds the whole pipeline
+    // (every k-block passes through them), so their loops carry incrementally updated
+    // addresses instead of recomputing stage indices, and exactly one barrier wait each.
+    constexpr uint32_t kFullBar = 0, kAreadyBar = C::kStages * 8, kEmptyBar = 2 * C::kStages * 8;
+    const uint32_t bars_u32 = smem_u32(bars);
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % C::kStages;
-                const uint32_t ph = (kb / C::kStages) & 1;
-                if (!mbar_wait(bar(2 * C::kStages + s), ph ^ 1, ctl, status, 0, s)) break;
-                mbar_expect_tx(bar(s), C::kStageBytes);
-                tma_load_2d(smem_u32(stage_w(s, 0)), &tmap_w, kb * kBlockK, n0, bar(s));
-                if constexpr (NW == 2) tma_load_2d(smem_u32(stage_w(s, 1)), &tmap_w2, kb * kBlockK, n0, bar(s));
-                tma_load_2d(smem_u32(stage_x(s)), &tmap_x, kb * kBlockK, m0, bar(s));
+            uint32_t s = 0, ph = 1;  // waiting on parity 1 of a fresh barrier returns at once
+            uint32_t dst = smem_u32(smem);
+            int kc = kb_begin * kBlockK;
+            for (int i = 0; i < nkb; ++i) {
+                TRACE(0, i, 0);
+                if (!mbar_wait(bars_u32 + kEmptyBar + s * 8, ph, ctl, status, 0, s)) break;
+                TRACE(0, i, 1);
+                const uint32_t fb = bars_u32 + kFullBar + s * 8;
+                mbar_expect_tx(fb, C::kStageBytes);
+                tma_load_2d(dst, &tmap_w, kc, n0, fb);
+                if constexpr (NW == 2) tma_load_2d(dst + C::kWBytes, &tmap_w2, kc, n0, fb);
+                tma_load_2d(dst + NW * C::kWBytes, &tmap_x, kc, m0, fb);
+                TRACE(0, i, 2);
+                kc += kBlockK;
+                dst += C::kStageBytes;
+                if (++s == C::kStages) { s = 0; ph ^= 1; dst = smem_u32(smem); }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // All 32 lanes run the loop converged and compute the (warp-uniform) operands; only
+        // the leader lane's tcgen05 instructions are issued.
+        {
+            const uint32_t leader = lane == 0 ? 1u : 0u;
             // instruction descriptor: D=f32, A=bf16 (K-major, from TMEM), B=bf16 (K-major), M=128, N=TOK
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TOK >> 3) << 17) |
-                                       ((uint32_t)(kTileN >> 4) << 24);
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                       ((uint32_t)(TOK >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+            const uint64_t bdesc0 = make_b_desc(smem_u32(stage_x(0)));
+            const uint32_t a0 = tmem_base + C::kABase;
+            uint32_t s = 0, ph = 0, a_tmem = a0;
+            uint64_t bdesc = bdesc0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % C::kStages;
-                const uint32_t ph = (kb / C::kStages) & 1;
-                ok = mbar_wait(bar(s), ph, ctl, status, 1, s) &&
-                     mbar_wait(bar(C::kStages + s), ph, ctl, status, 2, s);
-                if (!ok) break;
+            for (int i = 0; i < nkb; ++i) {
+                TRACE(1, i, 0);
+                // aready[s] implies full[s]: the converters waited for the stage's TMA bytes
+                // (weights and activations share one transaction barrier) before arriving here
+                ok = mbar_wait(bars_u32 + kAreadyBar + s * 8, ph, ctl, status, 2, s);
+                if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                TRACE(1, i, 2);
                 tc_fence_after();
-                const uint64_t bdesc = make_b_desc(smem_u32(stage_x(s)));
 #pragma unroll
                 for (int w = 0; w < NW; ++w) {
 #pragma unroll
-                    for (int j = 0; j < kBlockK / kUmmaK; ++j) {
-                        const uint32_t a_tmem = tmem_base + C::kABase + s * C::kAColsPerStage + w * (kBlockK / 2) + j * (kUmmaK / 2);
-                        tc_mma_ts(tmem_base + w * TOK, a_tmem, bdesc + (uint64_t)((j * kUmmaK * 2) >> 4), idesc,
-                                  (kb > 0 || j > 0) ? 1u : 0u);
-                    }
+                    for (int j = 0; j < kBlockK / kUmmaK; ++j)
+                        tc_mma_ts_if(leader, tmem_base + w * TOK, a_tmem + w * (kBlockK / 2) + j * (kUmmaK / 2),
+                                     bdesc + (uint64_t)((j * kUmmaK * 2) >> 4), idesc, (i > 0 || j > 0) ? 1u : 0u);
                 }
-                tc_commit(bar(2 * C::kStages + s));  // frees smem stage s and TMEM A stage s
+                tc_commit_if(leader, bars_u32 + kEmptyBar + s * 8);  // frees smem stage s and TMEM A stage s
+                TRACE(1, i, 3);
+                a_tmem += C::kAColsPerStage;
+                bdesc += (uint64_t)(C::kStageBytes >> 4);
+                if (++s == C::kStages) { s = 0; ph ^= 1; a_tmem = a0; bdesc = bdesc0; }
             }
-            if (ok) tc_commit(bar(3 * C::kStages));  // accumulators complete
+            if (ok) tc_commit_if(leader, bar(3 * C::kStages));  // accumulators complete
         }
+        __syncwarp();
     } else {
         // ---------------- converters, then epilogue ----------------
+        const int group = (warp - 2) >> 2;
         const int quad = warp & 3;                 // TMEM lane quadrant this warp may access
         const int row = quad * 32 + lane;          // weight row inside the tile == TMEM lane
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        const int swz = (row >> 1) & 3;
         bool ok = true;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-            const int s = kb % C::kStages;
-            const uint32_t ph = (kb / C::kStages) & 1;
-            ok = mbar_wait(bar(s), ph, ctl, status, 3, s);
-            ok = __all_sync(0xFFFFFFFFu, ok);
+        for (int i = group; i < nkb && ok; i += G) {
+            const int s = i % C::kStages;
+            const uint32_t ph = (i / C::kStages) & 1;
+            if (((warp - 2) & 3) == 0) TRACE(2, i, 0);
+            ok = mbar_wait_warp(bar(s), ph, ctl, status, 3, s);
             if (!ok) break;
             tc_fence_after();
+            if (((warp - 2) & 3) == 0) TRACE(2, i, 1);
 #pragma unroll
             for (int w = 0; w < NW; ++w) {
                 // 64 codes of this row; TMA wrote them with the 64-byte swizzle: the 16-byte
@@ -298,7 +391,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 uint32_t packed[32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(rowp + ((c ^ ((row >> 1) & 3)) << 4));
+                    const uint4 v = *reinterpret_cast<const uint4 *>(rowp + ((c ^ swz) << 4));
                     cvt_i8x4_bf16(v.x, packed[8 * c + 0], packed[8 * c + 1]);
                     cvt_i8x4_bf16(v.y, packed[8 * c + 2], packed[8 * c + 3]);
                     cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
@@ -306,43 +399,91 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 }
                 tc_st32(tmem_base + lane_addr + C::kABase + s * C::kAColsPerStage + w * (kBlockK / 2), packed);
             }
+            if (((warp - 2) & 3) == 0) TRACE(2, i, 2);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(C::kStages + s));
+            if (((warp - 2) & 3) == 0) TRACE(2, i, 3);
         }
-        // epilogue
-        if (ok) ok = mbar_wait(bar(3 * C::kStages), 0, ctl, status, 4, 0);
-        ok = __all_sync(0xFFFFFFFFu, ok);
-        if (ok) {
-            tc_fence_after();
-            const int n = n0 + row;
-            const bool n_ok = n < N;
-            const float sc = n_ok ? scales[n] : 0.0f;
-            const float bs = (n_ok && bias) ? bias[n] : 0.0f;
-            float sc2 = 0.0f, bs2 = 0.0f;
-            if constexpr (NW == 2) {
-                sc2 = n_ok ? scales2[n] : 0.0f;
-                bs2 = (n_ok && bias2) ? bias2[n] : 0.0f;
-            }
+        // ---------------- epilogue: 16-column chunks dealt round-robin to the groups ----------------
+        if (ok) ok = mbar_wait_warp(bar(3 * C::kStages), 0, ctl, status, 4, 0);
+        const int n = n0 + row;
+        const bool n_ok = n < N;
+        const float sc = n_ok ? scales[n] : 0.0f;
+        const float bs = (n_ok && bias) ? bias[n] : 0.0f;
+        float sc2 = 0.0f, bs2 = 0.0f;
+        if constexpr (NW == 2) {
+            sc2 = n_ok ? scales2[n] : 0.0f;
+            bs2 = (n_ok && bias2) ? bias2[n] : 0.0f;
+        }
+        const int splits = gridDim.z;
+        if (splits == 1) {
+            if (ok) {
+                tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < TOK / 16; ++c) {
-                uint32_t r[16], r2[16];
-                tc_ld16(tmem_base + lane_addr + c * 16, r);
-                if constexpr (NW == 2) tc_ld16(tmem_base + lane_addr + TOK + c * 16, r2);
-                tc_wait_ld();
+                for (int c = group; c < TOK / 16; c += G) {
+                    uint32_t r[16], r2[16];
+                    tc_ld16(tmem_base + lane_addr + c * 16, r);
+                    if constexpr (NW == 2) tc_ld16(tmem_base + lane_addr + TOK + c * 16, r2);
+                    tc_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int m = m0 + c * 16 + i;
-                    float o = __uint_as_float(r[i]) * sc + bs;
-                    if constexpr (NW == 2) {
-                        const float u = __uint_as_float(r2[i]) * sc2 + bs2;
-                        o = silu_f(o) * u;
-                    } else if (epilogue == SHREWQ_EPILOGUE_RELU) {
-                        o = fmaxf(o, 0.0f);
+                    for (int i = 0; i < 16; ++i) {
+                        const int m = m0 + c * 16 + i;
+                        float o = __uint_as_float(r[i]) * sc + bs;
+                        if constexpr (NW == 2) {
+                            const float u = __uint_as_float(r2[i]) * sc2 + bs2;
+                            o = silu_f(o) * u;
+                        } else if (epilogue == SHREWQ_EPILOGUE_RELU) {
+                            o = fmaxf(o, 0.0f);
+                        }
+                        if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
                     }
-                    if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
                 }
+            }
+        } else {
+            // split-K: every CTA parks its raw accumulators in scratch; the CTA that arrives
+            // last at the tile's counter adds the slices in split order (so the sum does not
+            // depend on arrival order), applies scale / bias / op and stores.
+            const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+            float *mine = sk.partials + (tile * splits + blockIdx.z) * (size_t)(TOK * kTileN);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = group; c < TOK / 16; c += G) {
+                    uint32_t r[16];
+                    tc_ld16(tmem_base + lane_addr + c * 16, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) __stcg(mine + (c * 16 + i) * kTileN + row, __uint_as_float(r[i]));
+                }
+            }
+            __threadfence();
+            named_bar_sync(1, 128 * G);
+            if (threadIdx.x == 64) {
+                const unsigned int old = atomicAdd(sk.counters + tile, 1u);
+                *s_is_last = (old == (unsigned int)(splits - 1));
+            }
+            named_bar_sync(1, 128 * G);
+            if (*s_is_last) {
+                __threadfence();
+                const float *base = sk.partials + tile * splits * (size_t)(TOK * kTileN);
+                if (ok) {
+#pragma unroll 1
+                    for (int c = group; c < TOK / 16; c += G) {
+#pragma unroll 4
+                        for (int i = 0; i < 16; ++i) {
+                            const int ml = c * 16 + i, m = m0 + ml;
+                            float acc = 0.0f;
+                            for (int z = 0; z < splits; ++z) acc += __ldcg(base + (size_t)z * (TOK * kTileN) + ml * kTileN + row);
+                            float o = acc * sc + bs;
+                            if (epilogue == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
+                            if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
+                        }
+                    }
+                }
+                named_bar_sync(1, 128 * G);
+                if (threadIdx.x == 64) sk.counters[tile] = 0;  // ready for the next launch
             }
         }
     }
@@ -350,12 +491,36 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     // ---------------- teardown ----------------
     tc_fence_before();
     __syncthreads();
+#ifdef SHREWQ_TRACE
+    if (trace_buf && threadIdx.x == 32) {
+        // microbenchmarks on an idle CTA: cost of clock reads, of a try_wait on a completed
+        // phase, of the trace store
+        long long t0 = clock64();
+        long long t1 = clock64();
+        bool r = true;
+        for (int i = 0; i < 16; ++i) r &= mbar_try(bar(3 * C::kStages), 0);
+        long long t2 = clock64();
+        for (int i = 0; i < 16; ++i) r &= mbar_wait(bar(3 * C::kStages), 0, ctl, status, 9, 0);
+        long long t3 = clock64();
+        for (int i = 0; i < 16; ++i) trace_rec(trace_buf, 3, 250, 0);
+        long long t4 = clock64();
+        for (int i = 0; i < 16; ++i) tc_fence_after();
+        long long t5 = clock64();
+        trace_buf[(3 * 256 + 255) * 4 + 0] = t1 - t0;
+        trace_buf[(3 * 256 + 255) * 4 + 1] = (t2 - t1) + (r ? 0 : 1000000);
+        trace_buf[(3 * 256 + 255) * 4 + 2] = t3 - t2;
+        trace_buf[(3 * 256 + 255) * 4 + 3] = t4 - t3;
+        trace_buf[(3 * 256 + 254) * 4 + 0] = t5 - t4;
+    }
+    __syncthreads();
+#endif
     if (warp == 1) {
         if (ctl->abort_flag) {
             // give in-flight copies / MMAs a bounded moment to land before TMEM is released
             for (int i = 0; i < 2000; ++i) __nanosleep(1000);
         }
         tc_fence_after();
+        __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
     }
 }
@@ -393,44 +558,103 @@ int encode_2d(shrewq_ctx *ctx, CUtensorMap *out, CUtensorMapDataType dt, int ele
     return SHREWQ_OK;
 }
 
-template <int TOK, int NW, typename YT>
-int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2) {
+struct Tuning {
+    int groups;   // converter groups (1..3)
+    bool splitk;  // allow split-K when the grid would leave SMs idle
+};
+
+Tuning read_tuning() {
+    Tuning t{3, true};
+    if (const char *e = getenv("SHREWQ_TC_GROUPS")) t.groups = atoi(e);
+    if (const char *e = getenv("SHREWQ_TC_SPLITK")) t.splitk = atoi(e) != 0;
+    if (t.groups < 1) t.groups = 1;
+    if (t.groups > 3) t.groups = 3;
+    return t;
+}
+
+template <int TOK, int NW, int G, typename YT>
+int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, bool allow_split) {
     using C = Cfg<TOK, NW>;
     CUtensorMap tx;
     int rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, a.K, a.M, kBlockK, TOK,
                        CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SHREWQ_OK) return rc;
-    auto kern = linear_i8_tcgen05_kernel<TOK, NW, YT>;
+    auto kern = linear_i8_tcgen05_kernel<TOK, NW, G, YT>;
     static bool attr_set = false;  // per instantiation
     if (!attr_set) {
         SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemRequest));
         attr_set = true;
     }
-    dim3 grid((unsigned)((a.N + kTileN - 1) / kTileN), (unsigned)((a.M + TOK - 1) / TOK));
-    kern<<<grid, kThreads, C::kSmemRequest, ctx->stream>>>(tw, tw2, tx, a.scales, a.bias, a.scales_up, a.bias_up,
-                                                           static_cast<YT *>(a.y), (int)a.M, (int)a.N, (int)a.K,
-                                                           a.ldy, a.epilogue, ctx->dev_status);
+    const int n_tiles = (int)((a.N + kTileN - 1) / kTileN), m_tiles = (int)((a.M + TOK - 1) / TOK);
+    const int num_kb = (int)((a.K + kBlockK - 1) / kBlockK);
+    // split-K when the output tiles alone leave most SMs idle: as many splits as fit in one
+    // wave, each with at least 4 k-blocks
+    int splits = 1;
+    if (allow_split && NW == 1) {
+        const int tiles = n_tiles * m_tiles;
+        int want = tiles <= 1024 ? ctx->sm_count / tiles : 1;
+        if (want > num_kb / 4) want = num_kb / 4;
+        if (want > 1) splits = want;
+    }
+    int kb_per_split = (num_kb + splits - 1) / splits;
+    splits = (num_kb + kb_per_split - 1) / kb_per_split;  // no empty split
+    SplitK sk{nullptr, nullptr, kb_per_split};
+    if (splits > 1) {
+        // scratch layout: [0,4096) quantizer words, [4096,8192) tile counters (at most one per
+        // SM is ever in use), partial sums from 8192
+        const size_t tiles = (size_t)n_tiles * m_tiles;
+        const size_t part_bytes = tiles * splits * TOK * kTileN * sizeof(float);
+        const size_t ctr_off = 4096, part_off = 8192;
+        if ((rc = ensure_scratch(ctx, part_off + part_bytes)) != SHREWQ_OK) return rc;
+        if (!ctx->counters_zeroed) {
+            // fresh scratch: counters must start at zero (the kernels reset them after use)
+            SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(static_cast<char *>(ctx->scratch) + ctr_off, 0, part_off - ctr_off, ctx->stream));
+            ctx->counters_zeroed = true;
+        }
+        sk.counters = reinterpret_cast<unsigned int *>(static_cast<char *>(ctx->scratch) + ctr_off);
+        sk.partials = reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + part_off);
+    }
+    dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits);
+    kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw2, tx, a.scales, a.bias, a.scales_up, a.bias_up,
+                                                                static_cast<YT *>(a.y), (int)a.M, (int)a.N, (int)a.K,
+                                                                a.ldy, a.epilogue, sk, ctx->dev_status);
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;
 }
 
+template <int TOK, int NW, typename YT>
+int launch_tuned(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2) {
+    const Tuning t = read_tuning();
+#define SHREWQ_TC_CASE(G) return launch_cfg<TOK, NW, G, YT>(ctx, a, tw, tw2, t.splitk)
+    if (t.groups == 1) SHREWQ_TC_CASE(1);
+    if (t.groups == 2) SHREWQ_TC_CASE(2);
+    SHREWQ_TC_CASE(3);
+#undef SHREWQ_TC_CASE
+}
+
 template <typename YT>
 int launch_y(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2) {
     if (a.q_up) {
-        if (a.M <= 16) return launch_cfg<16, 2, YT>(ctx, a, tw, tw2);
-        if (a.M <= 32) return launch_cfg<32, 2, YT>(ctx, a, tw, tw2);
-        if (a.M <= 64) return launch_cfg<64, 2, YT>(ctx, a, tw, tw2);
-        return launch_cfg<128, 2, YT>(ctx, a, tw, tw2);
+        if (a.M <= 16) return launch_tuned<16, 2, YT>(ctx, a, tw, tw2);
+        if (a.M <= 32) return launch_tuned<32, 2, YT>(ctx, a, tw, tw2);
+        if (a.M <= 64) return launch_tuned<64, 2, YT>(ctx, a, tw, tw2);
+        return launch_tuned<128, 2, YT>(ctx, a, tw, tw2);
     }
-    if (a.M <= 16) return launch_cfg<16, 1, YT>(ctx, a, tw, tw2);
-    if (a.M <= 32) return launch_cfg<32, 1, YT>(ctx, a, tw, tw2);
-    if (a.M <= 64) return launch_cfg<64, 1, YT>(ctx, a, tw, tw2);
-    if (a.M <= 128) return launch_cfg<128, 1, YT>(ctx, a, tw, tw2);
-    return launch_cfg<256, 1, YT>(ctx, a, tw, tw2);
+    if (a.M <= 16) return launch_tuned<16, 1, YT>(ctx, a, tw, tw2);
+    if (a.M <= 32) return launch_tuned<32, 1, YT>(ctx, a, tw, tw2);
+    if (a.M <= 64) return launch_tuned<64, 1, YT>(ctx, a, tw, tw2);
+    if (a.M <= 128) return launch_tuned<128, 1, YT>(ctx, a, tw, tw2);
+    return launch_tuned<256, 1, YT>(ctx, a, tw, tw2);
 }
 
 }  // namespace
+
+#ifdef SHREWQ_TRACE
+extern "C" __attribute__((visibility("default"))) int shrewq_debug_set_trace(long long *dev_buf) {
+    return (int)cudaMemcpyToSymbol(g_trace, &dev_buf, sizeof(dev_buf));
+}
+#endif
 
 bool tcgen05_supported(const ForwardArgs &a) {
     return a.x_dtype == SHREWQ_BF16 && a.K >= 16 && (a.K % 16) == 0 && a.M >= 1 && a.N >= 1 &&
