@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-Linear hot path (quantize.rs:463-476 on B200).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A "step" is one pass of the hot path over one batch of synthetic input.  The default
+workload is the Llama-7B-shaped MLP block of BASELINE.json (4096 -> 11008 gate/up with
+SiLU, 11008 -> 4096 down, INT8 per-channel weights ~N(0,0.02), bf16 activations ~N(0,1),
+batch 512), output channels sharded over the N GPUs with an all-gather after each of the
+two sharded layers.  Metric: tokens/s (rows of the batch per second) for the whole job.
+
+Prints ONE JSON line on rank 0.  Timing: CUDA events on the launching stream, barrier and
+synchronize on both sides, max over ranks.  L2: every step uses a different copy of the
+weights out of a ring larger than twice the 126 MB L2.
+
+`--impl reference` times the reference's own CPU algorithm for the same step (the oracle
+port: single-threaded f64 dequantization on every call, as quantize.rs:214-224,465 does,
+then an f32 GEMM on all host cores) — the Rust reference cannot be built on this image.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+WORKLOADS = {
+    # name: (kind, M, dims...)
+    "llama_mlp_m512": dict(kind="mlp", M=512, d_model=4096, d_ff=11008),
+    "llama_mlp_m1": dict(kind="mlp", M=1, d_model=4096, d_ff=11008),
+    "linear4096_m1": dict(kind="linear", M=1, N=4096, K=4096),
+    "linear4096_m4": dict(kind="linear", M=4, N=4096, K=4096),
+    "linear4096_m16": dict(kind="linear", M=16, N=4096, K=4096),
+    "linear4096_m64": dict(kind="linear", M=64, N=4096, K=4096),
+    "linear4096_m256": dict(kind="linear", M=256, N=4096, K=4096),
+    "linear4096_m1024": dict(kind="linear", M=1024, N=4096, K=4096),
+}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tc_burst=d["bf16_tflops"], tc_sustained=d["bf16_tflops_sustained"], source="measured")
+    return dict(hbm=6650.0, tc_burst=1590.0, tc_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                smax = float(r[2])
+                for nm, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nm)
+            except Exception:
+                pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# synthetic inputs (seeded; stand in for the reference's unseeded randn — nothing is fetched)
+# ---------------------------------------------------------------------------------------------
+def gpu_weight(n, k, seed, device):
+    g = torch.Generator(device=device).manual_seed(seed)
+    return torch.randn(n, k, device=device, generator=g) * 0.02
+
+
+def host_weight(n, k, seed):
+    rng = np.random.default_rng(seed)
+    return (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+
+
+# ---------------------------------------------------------------------------------------------
+# the CPU arm: reference algorithm on host cores
+# ---------------------------------------------------------------------------------------------
+def cpu_step_factory(wl):
+    """Returns (step_fn, tokens, description).  Each call performs one forward exactly as the
+    reference does: dequantize every weight afresh (single thread, f64 then f32), then f32
+    GEMM on all cores (torch CPU as stand-in for the `gemm` crate), then bias / activation."""
+    from oracle import shrew_oracle as oracle
+    oracle.build()
+    M = wl["M"]
+    rng = np.random.default_rng(1)
+    if wl["kind"] == "mlp":
+        dm, dff = wl["d_model"], wl["d_ff"]
+        shapes = [(dff, dm), (dff, dm), (dm, dff)]
+    else:
+        shapes = [(wl["N"], wl["K"])]
+    qs = []
+    for i, (n, k) in enumerate(shapes):
+        q, s = oracle.np_quantize_f32(host_weight(n, k, i), oracle.PER_CHANNEL)
+        qs.append((q, s, np.empty((n, k), dtype=np.float32)))
+    x = torch.from_numpy(rng.standard_normal((M, shapes[0][1]), dtype=np.float32)).to(torch.bfloat16).float()
+
+    def lin(i, inp):
+        q, s, buf = qs[i]
+        oracle.dequantize_like_reference(q, s, oracle.PER_CHANNEL, buf)  # quantize.rs:465, every call
+        return inp @ torch.from_numpy(buf).t()                          # quantize.rs:468-469
+
+    def step():
+        if wl["kind"] == "mlp":
+            g, u = lin(0, x), lin(1, x)
+            h = torch.nn.functional.silu(g) * u
+            return lin(2, h)
+        return lin(0, x)
+
+    return step, M, f"full step: batch {M}, every weight dequantized per call (1 thread) + f32 GEMM on {torch.get_num_threads()} threads"
+
+
+def run_reference_arm(args, wl, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    step, tokens, sample = cpu_step_factory(wl)
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    val = tokens * args.steps / dt
+    out = {
+        "impl": "reference", "metric": "quantized_linear_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, **{k: v for k, v in wl.items() if k != "kind"}},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "Rust reference (shrew-cpu: gemm 0.18.2 + rayon) cannot be built on this image; this is the CPU port of "
+                "quantize.rs:463-476 with torch CPU matmul standing in for the gemm crate",
+    }
+    print(json.dumps(out), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------
+# the GPU arm
+# ---------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="llama_mlp_m512", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference_arm(args, wl, args.workload)
+
+    import torch.distributed as dist
+    from shrew_b200 import Linear, QuantConfig, QuantizedLinear, _lib
+    from shrew_b200.quantize import Device
+    from shrew_b200.sharded import ShardedGatedMLP, ShardedLinear, plan_shards
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device — this path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sdev = Device.get(dev)
+    cfg = QuantConfig.int8_per_channel()
+    M = wl["M"]
+
+    # ---- build the rank's shards; a ring of weight copies defeats L2 between steps ----
+    def make_shard(n, k, seed):
+        n0, n1 = plan_shards(n, world).rows(rank)
+        w = gpu_weight(n, k, seed, dev)[n0:n1].contiguous()
+        return QuantizedLinear.from_linear(Linear(w, None), cfg)
+
+    if wl["kind"] == "mlp":
+        dm, dff = wl["d_model"], wl["d_ff"]
+        shard_bytes = (2 * dff * dm + dm * dff) // world
+        in_features = dm
+        flops_step = 2 * M * (2 * dff * dm + dm * dff)
+    else:
+        shard_bytes = wl["N"] * wl["K"] // world
+        in_features = wl["K"]
+        flops_step = 2 * M * wl["N"] * wl["K"]
+    ring = max(2, -(-2 * L2_BYTES // shard_bytes) + 1)
+    models = []
+    for c in range(ring):
+        if wl["kind"] == "mlp":
+            g, u, d = make_shard(dff, dm, 0), make_shard(dff, dm, 1), make_shard(dm, dff, 2)
+            models.append(ShardedGatedMLP(g, u, d, dff, dm))
+        else:
+            q = make_shard(wl["N"], wl["K"], 0)
+            models.append(ShardedLinear(wl["N"], lambda x, out, _q=q: _q.forward(x, out=out)))
+            models[-1].shard = q
+    torch.cuda.synchronize()
+
+    gx = torch.Generator(device=dev).manual_seed(1)
+    x_dev = torch.randn(M, in_features, device=dev, generator=gx).to(torch.bfloat16)
+    x_host = x_dev.cpu().pin_memory()
+    out_features = wl["d_model"] if wl["kind"] == "mlp" else wl["N"]
+    y_host = torch.empty((M, out_features), dtype=torch.bfloat16).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(i, x):
+        return models[i % ring].forward(x)
+
+    # ---- device-resident metric ----
+    for i in range(args.warmup):
+        step(i, x_dev)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = sdev.launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i, x_dev)
+    e1.record()
+    barrier()
+    sdev.synchronize()  # also surfaces a kernel that gave up a bounded wait
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    launches = sdev.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    value = M * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end: pinned host input in, host output back, every step ----
+    for i in range(3):
+        y_host.copy_(step(i, x_host.to(dev, non_blocking=True)))
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        xd = x_host.to(dev, non_blocking=True)
+        y = step(i, xd)
+        y_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    t_e2e = torch.tensor([time.perf_counter() - t0], device=dev)
+    if world > 1:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    e2e_value = M * args.steps / float(t_e2e.item())
+
+    # ---- dominant kernel alone, for the roofline ----
+    peaks = measured_peaks()
+    iters = max(args.steps, 20)
+    if wl["kind"] == "mlp":
+        n_loc = models[0].gate.out_features
+        hbuf = torch.empty((M, n_loc), dtype=torch.bfloat16, device=dev)
+        kern = lambda i: models[i % ring].gate.forward_gate_up_silu(models[i % ring].up, x_dev, out=hbuf)  # noqa: E731
+        k_flops = 2 * 2 * M * n_loc * dm
+        k_bytes = 2 * n_loc * dm + 2 * 4 * n_loc + M * dm * 2 + M * n_loc * 2
+        kname = models[0].gate
+    else:
+        q = models[0].shard
+        ybuf = torch.empty((M, q.out_features), dtype=torch.bfloat16, device=dev)
+        kern = lambda i: models[i % ring].shard.forward(x_dev, out=ybuf)  # noqa: E731
+        k_flops = 2 * M * q.out_features * q.in_features
+        k_bytes = q.out_features * q.in_features + 4 * q.out_features + M * q.in_features * 2 + M * q.out_features * 2
+        kname = q
+    for i in range(3):
+        kern(i)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(iters):
+        kern(i)
+    e1.record()
+    torch.cuda.synchronize()
+    k_s = e0.elapsed_time(e1) * 1e-3 / iters
+    kernel_family = kname.last_kernel()
+    tensor_bound = M >= 128
+    if tensor_bound:
+        roof = {"bound": "tensor", "achieved": k_flops / k_s / 1e12, "peak": peaks["tc_sustained"], "unit": "TFLOP/s",
+                "peak_burst": peaks["tc_burst"]}
+    else:
+        roof = {"bound": "hbm", "achieved": k_bytes / k_s / 1e9, "peak": peaks["hbm"], "unit": "GB/s"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof.update({"traffic": None, "kernel": kernel_family, "kernel_us": k_s * 1e6, "peaks": peaks["source"],
+                 "timing": "CUDA events, host-launched back to back (includes launch gaps)"})
+
+    out = {
+        "metric": "quantized_linear_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x int8 -> f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, **{k: v for k, v in wl.items() if k != "kind"},
+                   "weights": "INT8 per-channel, N(0,0.02)", "sharding": f"output channels over {world} GPU(s), all-gather",
+                   "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU) > 2x L2"},
+        "tflops": flops_step * args.steps / (ms_total * 1e-3) / 1e12,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                "d2h_bytes_per_step": y_host.numel() * 2},
+        "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cstep, tokens, sample = cpu_step_factory(wl)
+        cstep()
+        t0 = time.perf_counter()
+        n_cpu = 0
+        while n_cpu < 3 or (time.perf_counter() - t0 < 10 and n_cpu < 20):
+            cstep()
+            n_cpu += 1
+        dt = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": tokens * n_cpu / dt, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                               "kind": "port", "sample": f"{n_cpu} x " + sample}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
