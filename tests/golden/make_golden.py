@@ -5,7 +5,7 @@ vectors, only small fixed inputs with tolerance and metadata assertions
 (crates/shrew/src/quantize.rs:601-789).  This script replays those inputs, plus the edge
 cases the reference's code branches on, through a THIRD restatement of the quantizer that
 shares no code with oracle/: plain Python floats (IEEE binary64, the same arithmetic as
-Rust f64) and math.floor/ceil for the rounding.  The resulting codes and scales are the
+Rust f64) and math.trunc for the rounding.  The resulting codes and scales are the
 committed golden vectors; tests check the C oracle, its numpy twin and the CUDA kernels
 against them, and check the reference's own assertions on them.
 
