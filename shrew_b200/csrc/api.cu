@@ -328,6 +328,33 @@ int shrewq_linear_forward(shrewq_linear *lin, const void *x_dev, int x_dtype, si
     return forward_impl(lin, nullptr, x_dev, x_dtype, M, y_dev, y_dtype, ldy, epilogue, "linear_forward");
 }
 
+int shrewq_linear_forward_noalloc(shrewq_linear *lin, const void *x_dev, size_t M, void *y_dev, int y_dtype,
+                                  size_t ldy, int epilogue) {
+    if (!lin) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: handle is NULL");
+    shrewq_ctx *ctx = lin->ctx;
+    if (y_dtype != SHREWQ_F32 && y_dtype != SHREWQ_BF16)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: y_dtype must be SHREWQ_F32 or SHREWQ_BF16");
+    if (epilogue != SHREWQ_EPILOGUE_NONE && epilogue != SHREWQ_EPILOGUE_RELU)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: unknown epilogue %d", epilogue);
+    if (M == 0) return SHREWQ_OK;
+    if (!x_dev || !y_dev) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: x / y is NULL");
+    if (ldy < lin->n) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: ldy smaller than out_features");
+    if ((reinterpret_cast<uintptr_t>(y_dev) % (y_dtype == SHREWQ_BF16 ? 2 : 4)))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: y not aligned to its element size");
+    int rc = bind(ctx);
+    if (rc != SHREWQ_OK) return rc;
+    ForwardArgs a;
+    a.q = lin->q; a.scales = lin->scales_f32; a.bias = lin->bias;
+    a.x = x_dev; a.x_dtype = SHREWQ_BF16; a.y = y_dev; a.y_dtype = y_dtype;
+    a.M = M; a.N = lin->n; a.K = lin->k; a.ldy = ldy; a.epilogue = epilogue;
+    if (!tcgen05_supported(a) || !lin->tmap_ok)
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
+                       "forward_noalloc: needs bf16 activations, 16-byte aligned x and weights, in_features a multiple of 16");
+    rc = launch_gemm_tcgen05_noalloc(ctx, a, lin->w_tmap);
+    lin->last_kernel = "tcgen05";
+    return rc;
+}
+
 int shrewq_linear_forward_gate_up_silu(shrewq_linear *gate, shrewq_linear *up, const void *x_dev, int x_dtype,
                                        size_t M, void *h_dev, int h_dtype, size_t ldh) {
     if (!up) return set_err(gate ? gate->ctx : nullptr, SHREWQ_ERR_INVALID_ARG, "gate_up_silu: up handle is NULL");

@@ -101,6 +101,7 @@ int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a);
 int launch_gemm_simt(shrewq_ctx *ctx, const ForwardArgs &a);
 bool tcgen05_supported(const ForwardArgs &a);
 int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);
+int launch_gemm_tcgen05_noalloc(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap);
 int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, void *tmap_out);
 
 // bf16 <-> f32 helpers usable on host and device

@@ -648,6 +648,87 @@ int launch_y(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const
     return launch_tuned<256, 1, YT>(ctx, a, tw, tw2);
 }
 
+// ---- forward without any allocation ---------------------------------------------------
+// Split-K scratch for shrewq_linear_forward_noalloc: a fixed array inside the library image
+// instead of a cudaMalloc'd buffer.  Every GPU that loads the library holds these 8 MiB
+// until the process exits.  Layout: [0,4096) tile counters, partial sums from 4096.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+constexpr size_t kStaticCounterBytes = 4096;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device address:
+// the address is looked up once per device (with that device current) and cached.
+constexpr int kMaxDevices = 64;
+static void *g_static_scratch_addr[kMaxDevices] = {nullptr};
+
+int static_scratch_for_device(shrewq_ctx *ctx, void **out) {
+    if (ctx->device < 0 || ctx->device >= kMaxDevices)
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "forward_noalloc: device index %d above %d", ctx->device, kMaxDevices - 1);
+    if (!g_static_scratch_addr[ctx->device]) {
+        void *p = nullptr;
+        SHREWQ_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return set_err(ctx, SHREWQ_ERR_CUDA, "forward_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_static_scratch_addr[ctx->device] = p;
+    }
+    *out = g_static_scratch_addr[ctx->device];
+    return SHREWQ_OK;
+}
+
+template <int TOK, typename YT>
+int launch_noalloc_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw) {
+    constexpr int G = 3;
+    using C = Cfg<TOK, 1>;
+    CUtensorMap tx;
+    int rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, a.K, a.M, kBlockK, TOK,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != SHREWQ_OK) return rc;
+    auto kern = linear_i8_tcgen05_kernel<TOK, 1, G, YT>;
+    SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemRequest));
+    const int n_tiles = (int)((a.N + kTileN - 1) / kTileN), m_tiles = (int)((a.M + TOK - 1) / TOK);
+    const int num_kb = (int)((a.K + kBlockK - 1) / kBlockK);
+    const size_t tiles = (size_t)n_tiles * m_tiles;
+    int splits = 1;
+    if (tiles <= kStaticCounterBytes / 4) {
+        int want = (int)(ctx->sm_count / tiles);
+        if (want > num_kb / 4) want = num_kb / 4;
+        if (want > 1) splits = want;
+    }
+    int kb_per_split = (num_kb + splits - 1) / splits;
+    splits = (num_kb + kb_per_split - 1) / kb_per_split;
+    SplitK sk{nullptr, nullptr, kb_per_split};
+    if (splits > 1) {
+        const size_t need = kStaticCounterBytes + tiles * splits * TOK * kTileN * sizeof(float);
+        if (need > kStaticScratchBytes)
+            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
+                           "forward_noalloc: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu "
+                           "(use shrewq_linear_forward, which allocates)", need, kStaticScratchBytes);
+        void *base = nullptr;
+        if ((rc = static_scratch_for_device(ctx, &base)) != SHREWQ_OK) return rc;
+        // the array keeps whatever the previous call left: the counters must start at zero
+        SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(base, 0, kStaticCounterBytes, ctx->stream));
+        sk.counters = static_cast<unsigned int *>(base);
+        sk.partials = reinterpret_cast<float *>(static_cast<unsigned char *>(base) + kStaticCounterBytes);
+    }
+    dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits);
+    kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw, tx, a.scales, a.bias, nullptr, nullptr,
+                                                                static_cast<YT *>(a.y), (int)a.M, (int)a.N, (int)a.K,
+                                                                a.ldy, a.epilogue, sk, ctx->dev_status);
+    ctx->launches += 1;
+    SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+    return SHREWQ_OK;
+}
+
+template <typename YT>
+int launch_noalloc_y(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw) {
+    if (a.M <= 16) return launch_noalloc_cfg<16, YT>(ctx, a, tw);
+    if (a.M <= 32) return launch_noalloc_cfg<32, YT>(ctx, a, tw);
+    if (a.M <= 64) return launch_noalloc_cfg<64, YT>(ctx, a, tw);
+    if (a.M <= 128) return launch_noalloc_cfg<128, YT>(ctx, a, tw);
+    return launch_noalloc_cfg<256, YT>(ctx, a, tw);
+}
+
 }  // namespace
 
 #ifdef SHREWQ_TRACE
@@ -666,6 +747,12 @@ bool tcgen05_supported(const ForwardArgs &a) {
 int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, void *tmap_out) {
     return encode_2d(ctx, static_cast<CUtensorMap *>(tmap_out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, k, n, kBlockK,
                      kTileN, CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
+int launch_gemm_tcgen05_noalloc(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap) {
+    const CUtensorMap &tw = *static_cast<const CUtensorMap *>(w_tmap);
+    if (a.y_dtype == SHREWQ_BF16) return launch_noalloc_y<__nv_bfloat16>(ctx, a, tw);
+    return launch_noalloc_y<float>(ctx, a, tw);
 }
 
 int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap) {

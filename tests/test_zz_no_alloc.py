@@ -1,0 +1,78 @@
+"""GPU: shrewq_linear_forward_noalloc, the forward for callers that cannot allocate device
+memory (a process whose HBM is fully reserved by its own pools, or a loop that cannot take
+the device-wide synchronisation an allocation implies).  It keeps its split-K partial sums
+in an array inside the library image.  The test calls it through the C ABI twice in a row
+— the second call meets the first call's leftovers in the shared array — and compares each
+result with the allocating entry point on the same inputs.  Collected last on purpose."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 1e-2  # max|y - y_ref| / max|y_ref|, the bf16-path tolerance of the other GPU tests
+
+
+def _rel_err(y, ref):
+    y, ref = y.double(), ref.double()
+    return float((y - ref).abs().max() / ref.abs().max())
+
+
+def _make(N, K, seed):
+    from shrew_b200 import Linear, QuantConfig, QuantizedLinear
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    b = torch.randn(N, device="cuda", generator=g) * 0.1
+    return QuantizedLinear.from_linear(Linear(w, b), QuantConfig.int8_per_channel())
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 1024, 4096), (48, 512, 2048), (300, 384, 1024)])
+def test_noalloc_matches_allocating_forward_twice(M, N, K):
+    from shrew_b200 import _lib
+    from shrew_b200.quantize import Device
+    L = _lib.lib()
+    dev = Device.get("cuda:0")
+    ql = _make(N, K, seed=M + N)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    try:
+        for call in range(2):
+            x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+            L.shrewq_force_kernel(b"tcgen05")
+            ref = ql.forward(x)                       # existing entry point (may allocate scratch)
+            dev.synchronize()
+            y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            dev.bind_stream()
+            rc = L.shrewq_linear_forward_noalloc(ql._h, ctypes.c_void_p(x.data_ptr()), M, ctypes.c_void_p(y.data_ptr()),
+                                                 _lib.BF16, N, _lib.EPILOGUE_NONE)
+            _lib.check(rc, dev.handle)
+            dev.synchronize()
+            assert not torch.isnan(y.float()).any(), f"call {call}: output not fully written"
+            err = _rel_err(y, ref)
+            assert err <= TOL_BF16, f"call {call}: rel err {err:.3e}"
+    finally:
+        L.shrewq_force_kernel(b"auto")
+
+
+def test_noalloc_refuses_shapes_beyond_its_scratch_and_wrong_inputs():
+    from shrew_b200 import _lib
+    from shrew_b200.quantize import Device
+    L = _lib.lib()
+    dev = Device.get("cuda:0")
+    # 64 tokens x 2 channel tiles x 2 splits... pick a shape whose partial sums exceed 8 MiB:
+    # N = 128*36 (36 tiles) -> 4 splits of TOK = 128 tokens: 36*4*128*128*4 B = 9.4 MB
+    ql = _make(128 * 36, 2048, seed=1)
+    x = torch.zeros(128, 2048, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(128, 128 * 36, dtype=torch.bfloat16, device="cuda")
+    dev.bind_stream()
+    rc = L.shrewq_linear_forward_noalloc(ql._h, ctypes.c_void_p(x.data_ptr()), 128, ctypes.c_void_p(y.data_ptr()),
+                                         _lib.BF16, 128 * 36, 0)
+    assert rc == _lib.ERR_UNSUPPORTED
+    msg = L.shrewq_last_error(dev.handle).decode()
+    assert "built-in array" in msg and "8388608" in msg
+    assert L.shrewq_linear_forward_noalloc(None, None, 1, None, 1, 1, 0) == _lib.ERR_INVALID_ARG
+    odd = _make(64, 72, seed=2)  # in_features not a multiple of 16
+    rc = L.shrewq_linear_forward_noalloc(odd._h, ctypes.c_void_p(x.data_ptr()), 4, ctypes.c_void_p(y.data_ptr()),
+                                         _lib.BF16, 64, 0)
+    assert rc == _lib.ERR_UNSUPPORTED
