@@ -139,16 +139,17 @@ SHREWQ_API int shrewq_linear_forward_host(shrewq_linear *lin, const void *x_host
  * cannot afford the device-wide synchronisation a cudaMalloc / cudaFree implies; a host
  * that runs under an allocator it must account every byte to.  shrewq_linear_forward may
  * grow the context's scratch buffer (cudaMalloc) the first time a small batch makes it
- * split the K dimension; this entry point instead keeps the split-K partial sums in an
- * 8 MiB array that is part of the library image, and calls no cudaMalloc, cudaFree or
+ * split the K dimension; this entry point instead keeps the split-K partial sums in a
+ * 4 MiB array that is part of the library image, and calls no cudaMalloc, cudaFree or
  * allocating library routine.
  *  - bf16 activations only (x_dev is [M, in_features] bf16), tensor-core kernel only; the
  *    same requirements as that kernel: in_features a multiple of 16, 16-byte aligned x_dev
  *    and weights.  Anything else returns SHREWQ_ERR_UNSUPPORTED.
- *  - Limit: a shape whose split-K scratch (4096 B + tiles * splits * TOK * 128 * 4 B) exceeds
- *    8 MiB is refused with SHREWQ_ERR_UNSUPPORTED and a message giving both sizes; batches
- *    large enough not to need a K split never touch the array.
- *  - Every GPU that loads the library holds the 8 MiB until the process exits.
+ *  - Limit: a shape whose split-K scratch (4096 B + tiles * splits * TOK * 128 * 4 B, with
+ *    TOK the token tile of 16, 32 or 64) exceeds 4 MiB is refused with
+ *    SHREWQ_ERR_UNSUPPORTED and a message giving both sizes; batches above 64 tokens are
+ *    never split along K and never touch the array.
+ *  - Every GPU that loads the library holds the 4 MiB until the process exits.
  *  - The first call on each device looks up the array's device address (a host-side
  *    query, done once and cached); make that first call before any stream capture begins.
  *  - All calls on a device share the one array, which keeps the previous call's contents

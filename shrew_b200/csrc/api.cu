@@ -243,7 +243,9 @@ int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const double *sca
     }
     rc = launch_scales_to_f32(ctx, scales_dev, granularity, out_features, lin->scales_f32);
     if (rc == SHREWQ_OK && (in_features % 16) == 0 && (reinterpret_cast<uintptr_t>(q_dev) & 15) == 0) {
-        if (encode_weight_tmap(ctx, q_dev, out_features, in_features, lin->w_tmap) == SHREWQ_OK) lin->tmap_ok = true;
+        if (encode_weight_tmap(ctx, q_dev, out_features, in_features, 128, lin->w_tmap) == SHREWQ_OK &&
+            encode_weight_tmap(ctx, q_dev, out_features, in_features, 64, lin->w_tmap64) == SHREWQ_OK)
+            lin->tmap_ok = true;
     }
     if (rc != SHREWQ_OK) {
         cudaFree(lin->scales_f32);
@@ -317,7 +319,8 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
     }
     const char *name;
     if (choice == kForceGemv) { rc = launch_gemv(ctx, a); name = "gemv"; }
-    else if (choice == kForceTc) { rc = launch_gemm_tcgen05(ctx, a, lin->w_tmap, up ? up->w_tmap : nullptr); name = "tcgen05"; }
+    else if (choice == kForceTc) { rc = up ? launch_gemm_tcgen05(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
+        name = "tcgen05"; }
     else { rc = launch_gemm_simt(ctx, a); name = "simt"; }
     lin->last_kernel = name;
     return rc;

@@ -54,9 +54,10 @@ struct shrewq_linear {
     size_t n = 0, k = 0;
     int granularity = 0;
     const char *last_kernel = "none";
-    // TMA descriptor for the INT8 weight matrix (128 B, opaque CUtensorMap), valid when
-    // tmap_ok: 64-byte k boxes over 128 weight rows.
+    // TMA descriptors for the INT8 weight matrix (128 B each, opaque CUtensorMap), valid when
+    // tmap_ok: 64-byte k boxes over 128 weight rows, and over 64 rows (gate / up halves).
     alignas(64) unsigned char w_tmap[128];
+    alignas(64) unsigned char w_tmap64[128];
     bool tmap_ok = false;
 };
 
@@ -102,7 +103,7 @@ int launch_gemm_simt(shrewq_ctx *ctx, const ForwardArgs &a);
 bool tcgen05_supported(const ForwardArgs &a);
 int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);
 int launch_gemm_tcgen05_noalloc(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap);
-int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, void *tmap_out);
+int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, int box_rows, void *tmap_out);
 
 // bf16 <-> f32 helpers usable on host and device
 __host__ __device__ inline float bf16_bits_to_float(uint16_t h) {

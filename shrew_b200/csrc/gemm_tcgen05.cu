@@ -16,15 +16,19 @@
 // scale, bias and the elementwise op, and stores; for a fixed token the 32 lanes of a warp
 // write 32 consecutive channels.
 //
-// With NW == 2 the CTA carries two weight matrices (gate and up) over the same
-// activations and two accumulators, and the epilogue writes silu(gate)*up.
+// GATED: the 128 lanes carry 64 rows of a gate matrix and the same 64 rows of an up matrix
+// (two 64-row TMA boxes per sub-block); the epilogue pairs lane r with lane r+64 and
+// writes silu(gate)*up for 64 channels.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer,
-// warps 2..5 = converters (one TMEM lane quadrant each), which then run the epilogue.
-// Pipeline per k-block of 64: full[s] (TMA bytes landed) -> converters -> aready[s] ->
-// MMA -> tcgen05.commit -> empty[s] -> producer.  Every wait is bounded: after the limit
-// the waiter records where it gave up in a status block, raises a CTA-wide abort flag and
-// all roles fall through to the common teardown, which frees TMEM.
+// Warp roles: warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer, then G groups of
+// 4 converter warps (one TMEM lane quadrant each) which also run the epilogue.  A pipeline
+// stage holds KSUB sub-blocks of 64 k: full[s] (TMA bytes landed) -> converters (group g
+// takes stages g, g+G, ...) -> aready[s] -> MMA (4*KSUB instructions, one commit) ->
+// empty[s] -> producer.  One barrier round trip per stage costs the single MMA-issuing
+// thread ~400 cycles, so small token tiles (short MMAs) use more sub-blocks per stage.
+// Every wait is bounded: after the limit the waiter records where it gave up in a status
+// block, raises a CTA-wide abort flag and all roles fall through to the common teardown,
+// which frees TMEM.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -34,31 +38,31 @@
 namespace shrewq {
 namespace {
 
-constexpr int kTileN = 128;  // weight rows per CTA (MMA M, TMEM lanes)
-constexpr int kBlockK = 64;  // k per pipeline stage
+constexpr int kTileN = 128;  // TMEM lanes = weight rows per CTA (64 + 64 when GATED)
+constexpr int kBlockK = 64;  // k per sub-block (one 64-byte-swizzled INT8 box)
 constexpr int kUmmaK = 16;
 constexpr uint32_t kSpinFast = 1u << 14;
 constexpr uint32_t kSpinSlow = 1u << 21;  // x ~100 ns sleeps: a fraction of a second
 
-template <int TOK, int NW>
+template <int TOK, int KSUB>
 struct Cfg {
-    static constexpr int kWBytes = kTileN * kBlockK;                 // 8192 per matrix
-    static constexpr int kXBytes = TOK * kBlockK * 2;                // bf16
-    static constexpr int kStageBytes = NW * kWBytes + kXBytes;
-    static constexpr int kAColsPerStage = NW * (kBlockK / 2);        // 32-bit TMEM columns
-    static constexpr int kDCols = NW * TOK;
-    static constexpr int kABase = (kDCols + 31) / 32 * 32;
+    static constexpr int kWSub = kTileN * kBlockK;                   // 8192 B of codes per sub-block
+    static constexpr int kXSub = TOK * kBlockK * 2;                  // bf16 activations per sub-block
+    static constexpr int kStageBytes = KSUB * (kWSub + kXSub);
+    static constexpr int kXOff = KSUB * kWSub;                       // activations follow the codes
+    static constexpr int kAColsPerStage = KSUB * (kBlockK / 2);      // 32-bit TMEM columns
+    static constexpr int kABase = (TOK + 31) / 32 * 32;
     static constexpr int kMaxStagesSmem = (200 * 1024) / kStageBytes;
     static constexpr int kMaxStagesTmem = (512 - kABase) / kAColsPerStage;
     static constexpr int kStagesRaw = kMaxStagesSmem < kMaxStagesTmem ? kMaxStagesSmem : kMaxStagesTmem;
     static constexpr int kStages = kStagesRaw > 12 ? 12 : kStagesRaw;
-    static constexpr int kBarBytes = 1024;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + align slack
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*barriers*/ + 1024 /*alignment slack*/;
     // one CTA per SM is required (the CTA allocates all 512 TMEM columns)
     static constexpr int kSmemRequest = kSmemBytes > 120 * 1024 ? kSmemBytes : 120 * 1024;
     static_assert(kStages >= 2, "pipeline needs at least two stages");
     static_assert(kABase + kStages * kAColsPerStage <= 512, "TMEM columns");
     static_assert(kSmemRequest <= 227 * 1024, "shared memory");
+    static_assert(kStageBytes % 1024 == 0, "stage bases must keep the 1024-byte swizzle alignment");
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------
@@ -124,7 +128,11 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, Ct
                                                uint32_t role, uint32_t stage) {
     int ok = 1;
     if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, st, role, stage) ? 1 : 0;
-    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+    // every lane observes the completed phase itself (one try_wait that succeeds at once), so
+    // each has its own acquire on the data the barrier guards
+    if (ok) ok = mbar_try(bar, parity) ? 1 : 0;
+    return __all_sync(0xFFFFFFFFu, ok) != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int c0, int c1, uint32_t bar) {
@@ -149,27 +157,6 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// Predicated forms for warp-converged loops: every lane computes the (uniform) operands, one
-// lane (leader != 0) issues.
-__device__ __forceinline__ void tc_mma_ts_if(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                             uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "setp.ne.b32 q, %5, 0;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
-        : "memory");
-}
-__device__ __forceinline__ void tc_commit_if(uint32_t leader, uint32_t bar) {
-    asm volatile(
-        "{\n\t.reg .pred q;\n\t"
-        "setp.ne.b32 q, %1, 0;\n\t"
-        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
-        ::"r"(bar), "r"(leader)
         : "memory");
 }
 
@@ -236,7 +223,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 
 #ifdef SHREWQ_TRACE
-__device__ long long *g_trace = nullptr;  // [role 0..3][kb 0..255][tag 0..3]
+__device__ long long *g_trace = nullptr;  // [role 0..3][stage index 0..255][tag 0..3]
 __device__ __forceinline__ void trace_rec(long long *tr, int role, int kb, int tag) {
     if (tr && kb < 256) tr[(role * 256 + kb) * 4 + tag] = clock64();
 }
@@ -250,47 +237,52 @@ __device__ __forceinline__ void trace_rec(long long *tr, int role, int kb, int t
 struct SplitK {
     float *partials;         // [tile][split][TOK][128] f32, only when gridDim.z > 1
     unsigned int *counters;  // one per (n tile, token tile), zero between launches
-    int kb_per_split;
+    int rounds_per_split;    // pipeline rounds (KSUB sub-blocks each) per split
 };
 
-// G = number of converter groups (4 warps each); group g converts k-blocks g, g+G, ...
-template <int TOK, int NW, int G, typename YT>
+struct Operands {
+    const float *scales;   // per output channel
+    const float *bias;     // or null
+    const float *scales2;  // up matrix (GATED)
+    const float *bias2;
+};
+
+template <int TOK, int KSUB, int G, bool GATED, typename YT>
 __global__ void __launch_bounds__(64 + 128 * G, 1)
 linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
-                         const __grid_constant__ CUtensorMap tmap_x, const float *__restrict__ scales,
-                         const float *__restrict__ bias, const float *__restrict__ scales2,
-                         const float *__restrict__ bias2, YT *__restrict__ y, int M, int N, int K, size_t ldy,
-                         int epilogue, SplitK sk, DeviceStatus *status) {
-    using C = Cfg<TOK, NW>;
+                         const __grid_constant__ CUtensorMap tmap_x, Operands ops, YT *__restrict__ y, int M, int N,
+                         int K, size_t ldy, int epilogue, SplitK sk, DeviceStatus *status) {
+    using C = Cfg<TOK, KSUB>;
+    constexpr int kChan = GATED ? 64 : 128;  // output channels per CTA
     TRACE_INIT
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle with base_offset 0
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *bar_area = smem + C::kStages * C::kStageBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(bar_area);
-    // barrier indices: full[s]=s, aready[s]=S+s, empty[s]=2S+s, accfull=3S
     Ctl *ctl = reinterpret_cast<Ctl *>(bar_area + 512);
     int *s_is_last = reinterpret_cast<int *>(bar_area + 640);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kTileN;
+    const int n0 = blockIdx.x * kChan;
     const int m0 = blockIdx.y * TOK;
-    const int num_kb_total = (K + kBlockK - 1) / kBlockK;
-    const int kb_begin = blockIdx.z * sk.kb_per_split;
-    const int nkb = min(num_kb_total - kb_begin, sk.kb_per_split);  // >= 1 by construction of the grid
-    auto bar = [&](int i) { return smem_u32(bars + i); };
-    auto stage_w = [&](int s, int w) { return smem + s * C::kStageBytes + w * C::kWBytes; };
-    auto stage_x = [&](int s) { return smem + s * C::kStageBytes + NW * C::kWBytes; };
+    const int rounds_total = (K + kBlockK * KSUB - 1) / (kBlockK * KSUB);
+    const int r_begin = blockIdx.z * sk.rounds_per_split;
+    const int nr = min(rounds_total - r_begin, sk.rounds_per_split);  // >= 1 by construction of the grid
+    // barrier byte offsets: full[s], aready[s], empty[s], accfull
+    constexpr uint32_t kFullBar = 0, kAreadyBar = C::kStages * 8, kEmptyBar = 2 * C::kStages * 8, kAccBar = 3 * C::kStages * 8;
+    const uint32_t bars_u32 = smem_u32(bars);
+    const uint32_t smem_base = smem_u32(smem);
 
     if (threadIdx.x == 0) {
         ctl->abort_flag = 0;
         ctl->tmem_base = 0;
         for (int s = 0; s < C::kStages; ++s) {
-            mbar_init(bar(s), 1);
-            mbar_init(bar(C::kStages + s), 4);
-            mbar_init(bar(2 * C::kStages + s), 1);
+            mbar_init(bars_u32 + kFullBar + s * 8, 1);
+            mbar_init(bars_u32 + kAreadyBar + s * 8, 4);
+            mbar_init(bars_u32 + kEmptyBar + s * 8, 1);
         }
-        mbar_init(bar(3 * C::kStages), 1);
+        mbar_init(bars_u32 + kAccBar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -303,68 +295,69 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    // Producer and MMA issuer are single threads whose loop time bounds the whole pipeline
-    // (every k-block passes through them), so their loops carry incrementally updated
-    // addresses instead of recomputing stage indices, and exactly one barrier wait each.
-    constexpr uint32_t kFullBar = 0, kAreadyBar = C::kStages * 8, kEmptyBar = 2 * C::kStages * 8;
-    const uint32_t bars_u32 = smem_u32(bars);
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer (one thread) ----------------
         if (lane == 0) {
             uint32_t s = 0, ph = 1;  // waiting on parity 1 of a fresh barrier returns at once
-            uint32_t dst = smem_u32(smem);
-            int kc = kb_begin * kBlockK;
-            for (int i = 0; i < nkb; ++i) {
+            uint32_t dst = smem_base;
+            int kc = r_begin * KSUB * kBlockK;
+            for (int i = 0; i < nr; ++i) {
                 TRACE(0, i, 0);
                 if (!mbar_wait(bars_u32 + kEmptyBar + s * 8, ph, ctl, status, 0, s)) break;
                 TRACE(0, i, 1);
                 const uint32_t fb = bars_u32 + kFullBar + s * 8;
                 mbar_expect_tx(fb, C::kStageBytes);
-                tma_load_2d(dst, &tmap_w, kc, n0, fb);
-                if constexpr (NW == 2) tma_load_2d(dst + C::kWBytes, &tmap_w2, kc, n0, fb);
-                tma_load_2d(dst + NW * C::kWBytes, &tmap_x, kc, m0, fb);
+#pragma unroll
+                for (int j = 0; j < KSUB; ++j) {
+                    if constexpr (GATED) {
+                        tma_load_2d(dst + j * C::kWSub, &tmap_w, kc + j * kBlockK, n0, fb);
+                        tma_load_2d(dst + j * C::kWSub + 64 * kBlockK, &tmap_w2, kc + j * kBlockK, n0, fb);
+                    } else {
+                        tma_load_2d(dst + j * C::kWSub, &tmap_w, kc + j * kBlockK, n0, fb);
+                    }
+                    tma_load_2d(dst + C::kXOff + j * C::kXSub, &tmap_x, kc + j * kBlockK, m0, fb);
+                }
                 TRACE(0, i, 2);
-                kc += kBlockK;
+                kc += KSUB * kBlockK;
                 dst += C::kStageBytes;
-                if (++s == C::kStages) { s = 0; ph ^= 1; dst = smem_u32(smem); }
+                if (++s == C::kStages) { s = 0; ph ^= 1; dst = smem_base; }
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        // All 32 lanes run the loop converged and compute the (warp-uniform) operands; only
-        // the leader lane's tcgen05 instructions are issued.
-        {
-            const uint32_t leader = lane == 0 ? 1u : 0u;
+        // ---------------- MMA issuer (one thread) ----------------
+        if (lane == 0) {
             // instruction descriptor: D=f32, A=bf16 (K-major, from TMEM), B=bf16 (K-major), M=128, N=TOK
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                                        ((uint32_t)(TOK >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
-            const uint64_t bdesc0 = make_b_desc(smem_u32(stage_x(0)));
+            const uint64_t bdesc0 = make_b_desc(smem_base + C::kXOff);
             const uint32_t a0 = tmem_base + C::kABase;
             uint32_t s = 0, ph = 0, a_tmem = a0;
             uint64_t bdesc = bdesc0;
             bool ok = true;
-            for (int i = 0; i < nkb; ++i) {
+            for (int i = 0; i < nr; ++i) {
                 TRACE(1, i, 0);
-                // aready[s] implies full[s]: the converters waited for the stage's TMA bytes
-                // (weights and activations share one transaction barrier) before arriving here
-                ok = mbar_wait(bars_u32 + kAreadyBar + s * 8, ph, ctl, status, 2, s);
-                if (!__all_sync(0xFFFFFFFFu, ok)) { ok = false; break; }
+                // aready[s] implies full[s] (the converters waited for it), so the second wait
+                // returns at once; it gives this thread its own acquire on the activation tile
+                ok = mbar_wait(bars_u32 + kAreadyBar + s * 8, ph, ctl, status, 2, s) &&
+                     mbar_wait(bars_u32 + kFullBar + s * 8, ph, ctl, status, 1, s);
+                if (!ok) break;
                 TRACE(1, i, 2);
                 tc_fence_after();
 #pragma unroll
-                for (int w = 0; w < NW; ++w) {
+                for (int j = 0; j < KSUB; ++j) {
 #pragma unroll
-                    for (int j = 0; j < kBlockK / kUmmaK; ++j)
-                        tc_mma_ts_if(leader, tmem_base + w * TOK, a_tmem + w * (kBlockK / 2) + j * (kUmmaK / 2),
-                                     bdesc + (uint64_t)((j * kUmmaK * 2) >> 4), idesc, (i > 0 || j > 0) ? 1u : 0u);
+                    for (int jj = 0; jj < kBlockK / kUmmaK; ++jj)
+                        tc_mma_ts(tmem_base, a_tmem + j * (kBlockK / 2) + jj * (kUmmaK / 2),
+                                  bdesc + (uint64_t)((j * C::kXSub + jj * kUmmaK * 2) >> 4), idesc,
+                                  (i > 0 || j > 0 || jj > 0) ? 1u : 0u);
                 }
-                tc_commit_if(leader, bars_u32 + kEmptyBar + s * 8);  // frees smem stage s and TMEM A stage s
+                tc_commit(bars_u32 + kEmptyBar + s * 8);  // frees smem stage s and TMEM A stage s
                 TRACE(1, i, 3);
                 a_tmem += C::kAColsPerStage;
                 bdesc += (uint64_t)(C::kStageBytes >> 4);
                 if (++s == C::kStages) { s = 0; ph ^= 1; a_tmem = a0; bdesc = bdesc0; }
             }
-            if (ok) tc_commit_if(leader, bar(3 * C::kStages));  // accumulators complete
+            if (ok) tc_commit(bars_u32 + kAccBar);  // accumulators complete
         }
         __syncwarp();
     } else {
@@ -375,19 +368,19 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const int swz = (row >> 1) & 3;
         bool ok = true;
-        for (int i = group; i < nkb && ok; i += G) {
+        for (int i = group; i < nr && ok; i += G) {
             const int s = i % C::kStages;
             const uint32_t ph = (i / C::kStages) & 1;
             if (((warp - 2) & 3) == 0) TRACE(2, i, 0);
-            ok = mbar_wait_warp(bar(s), ph, ctl, status, 3, s);
+            ok = mbar_wait_warp(bars_u32 + kFullBar + s * 8, ph, ctl, status, 3, s);
             if (!ok) break;
             tc_fence_after();
             if (((warp - 2) & 3) == 0) TRACE(2, i, 1);
 #pragma unroll
-            for (int w = 0; w < NW; ++w) {
+            for (int j = 0; j < KSUB; ++j) {
                 // 64 codes of this row; TMA wrote them with the 64-byte swizzle: the 16-byte
                 // chunk c of row r sits at chunk position c ^ ((r >> 1) & 3)
-                const uint8_t *rowp = stage_w(s, w) + row * kBlockK;
+                const uint8_t *rowp = smem + s * C::kStageBytes + j * C::kWSub + row * kBlockK;
                 uint32_t packed[32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -397,46 +390,61 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                     cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
                     cvt_i8x4_bf16(v.w, packed[8 * c + 6], packed[8 * c + 7]);
                 }
-                tc_st32(tmem_base + lane_addr + C::kABase + s * C::kAColsPerStage + w * (kBlockK / 2), packed);
+                tc_st32(tmem_base + lane_addr + C::kABase + s * C::kAColsPerStage + j * (kBlockK / 2), packed);
             }
             if (((warp - 2) & 3) == 0) TRACE(2, i, 2);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(C::kStages + s));
+            if (lane == 0) mbar_arrive(bars_u32 + kAreadyBar + s * 8);
             if (((warp - 2) & 3) == 0) TRACE(2, i, 3);
         }
         // ---------------- epilogue: 16-column chunks dealt round-robin to the groups ----------------
-        if (ok) ok = mbar_wait_warp(bar(3 * C::kStages), 0, ctl, status, 4, 0);
-        const int n = n0 + row;
+        if (ok) ok = mbar_wait_warp(bars_u32 + kAccBar, 0, ctl, status, 4, 0);
+        // this lane's channel: plain tiles map lane -> n0 + lane; gated tiles map lanes 0..63 to
+        // the gate rows and lanes 64..127 to the up rows of channels n0 .. n0+63
+        const bool is_up = GATED && row >= 64;
+        const int n = n0 + (GATED ? (row & 63) : row);
         const bool n_ok = n < N;
-        const float sc = n_ok ? scales[n] : 0.0f;
-        const float bs = (n_ok && bias) ? bias[n] : 0.0f;
-        float sc2 = 0.0f, bs2 = 0.0f;
-        if constexpr (NW == 2) {
-            sc2 = n_ok ? scales2[n] : 0.0f;
-            bs2 = (n_ok && bias2) ? bias2[n] : 0.0f;
-        }
+        const float *sc_p = is_up ? ops.scales2 : ops.scales;
+        const float *bs_p = is_up ? ops.bias2 : ops.bias;
+        const float sc = n_ok ? sc_p[n] : 0.0f;
+        const float bs = (n_ok && bs_p) ? bs_p[n] : 0.0f;
         const int splits = gridDim.z;
         if (splits == 1) {
-            if (ok) {
-                tc_fence_after();
+            if (ok) tc_fence_after();
+            // gated tiles: the up half hands its values to the gate half through shared memory
+            // (the pipeline stages are idle once the accumulators are complete)
+            float *xch = reinterpret_cast<float *>(smem) + group * (16 * 64);
 #pragma unroll 1
-                for (int c = group; c < TOK / 16; c += G) {
-                    uint32_t r[16], r2[16];
+            for (int c = group; c < TOK / 16; c += G) {
+                uint32_t r[16];
+                if (ok) {
                     tc_ld16(tmem_base + lane_addr + c * 16, r);
-                    if constexpr (NW == 2) tc_ld16(tmem_base + lane_addr + TOK + c * 16, r2);
                     tc_wait_ld();
+                }
+                if constexpr (GATED) {
+                    if (is_up && ok) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) xch[i * 64 + (row - 64)] = __uint_as_float(r[i]) * sc + bs;
+                    }
+                    named_bar_sync(2 + group, 128);
+                    if (!is_up && ok) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int m = m0 + c * 16 + i;
+                            const float g = __uint_as_float(r[i]) * sc + bs;
+                            const float o = silu_f(g) * xch[i * 64 + row];
+                            if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
+                        }
+                    }
+                    named_bar_sync(2 + group, 128);  // xch is rewritten by the next chunk
+                } else if (ok) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int m = m0 + c * 16 + i;
                         float o = __uint_as_float(r[i]) * sc + bs;
-                        if constexpr (NW == 2) {
-                            const float u = __uint_as_float(r2[i]) * sc2 + bs2;
-                            o = silu_f(o) * u;
-                        } else if (epilogue == SHREWQ_EPILOGUE_RELU) {
-                            o = fmaxf(o, 0.0f);
-                        }
+                        if (epilogue == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
                         if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
                     }
                 }
@@ -468,16 +476,25 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             if (*s_is_last) {
                 __threadfence();
                 const float *base = sk.partials + tile * splits * (size_t)(TOK * kTileN);
-                if (ok) {
+                if (ok && !is_up) {
 #pragma unroll 1
                     for (int c = group; c < TOK / 16; c += G) {
 #pragma unroll 4
                         for (int i = 0; i < 16; ++i) {
                             const int ml = c * 16 + i, m = m0 + ml;
-                            float acc = 0.0f;
-                            for (int z = 0; z < splits; ++z) acc += __ldcg(base + (size_t)z * (TOK * kTileN) + ml * kTileN + row);
+                            float acc = 0.0f, acc2 = 0.0f;
+                            for (int z = 0; z < splits; ++z) {
+                                const float *p = base + (size_t)z * (TOK * kTileN) + ml * kTileN + row;
+                                acc += __ldcg(p);
+                                if constexpr (GATED) acc2 += __ldcg(p + 64);
+                            }
                             float o = acc * sc + bs;
-                            if (epilogue == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
+                            if constexpr (GATED) {
+                                const float u = acc2 * (n_ok ? ops.scales2[n] : 0.0f) + ((n_ok && ops.bias2) ? ops.bias2[n] : 0.0f);
+                                o = silu_f(o) * u;
+                            } else if (epilogue == SHREWQ_EPILOGUE_RELU) {
+                                o = fmaxf(o, 0.0f);
+                            }
                             if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
                         }
                     }
@@ -491,29 +508,6 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     // ---------------- teardown ----------------
     tc_fence_before();
     __syncthreads();
-#ifdef SHREWQ_TRACE
-    if (trace_buf && threadIdx.x == 32) {
-        // microbenchmarks on an idle CTA: cost of clock reads, of a try_wait on a completed
-        // phase, of the trace store
-        long long t0 = clock64();
-        long long t1 = clock64();
-        bool r = true;
-        for (int i = 0; i < 16; ++i) r &= mbar_try(bar(3 * C::kStages), 0);
-        long long t2 = clock64();
-        for (int i = 0; i < 16; ++i) r &= mbar_wait(bar(3 * C::kStages), 0, ctl, status, 9, 0);
-        long long t3 = clock64();
-        for (int i = 0; i < 16; ++i) trace_rec(trace_buf, 3, 250, 0);
-        long long t4 = clock64();
-        for (int i = 0; i < 16; ++i) tc_fence_after();
-        long long t5 = clock64();
-        trace_buf[(3 * 256 + 255) * 4 + 0] = t1 - t0;
-        trace_buf[(3 * 256 + 255) * 4 + 1] = (t2 - t1) + (r ? 0 : 1000000);
-        trace_buf[(3 * 256 + 255) * 4 + 2] = t3 - t2;
-        trace_buf[(3 * 256 + 255) * 4 + 3] = t4 - t3;
-        trace_buf[(3 * 256 + 254) * 4 + 0] = t5 - t4;
-    }
-    __syncthreads();
-#endif
     if (warp == 1) {
         if (ctl->abort_flag) {
             // give in-flight copies / MMAs a bounded moment to land before TMEM is released
@@ -558,102 +552,148 @@ int encode_2d(shrewq_ctx *ctx, CUtensorMap *out, CUtensorMapDataType dt, int ele
     return SHREWQ_OK;
 }
 
+// ---- launch ---------------------------------------------------------------------------
 struct Tuning {
     int groups;   // converter groups (1..3)
     bool splitk;  // allow split-K when the grid would leave SMs idle
+    int tok;      // 0 = choose; else force the token tile
 };
 
 Tuning read_tuning() {
-    Tuning t{3, true};
+    Tuning t{3, true, 0};
     if (const char *e = getenv("SHREWQ_TC_GROUPS")) t.groups = atoi(e);
     if (const char *e = getenv("SHREWQ_TC_SPLITK")) t.splitk = atoi(e) != 0;
+    if (const char *e = getenv("SHREWQ_TC_TOK")) t.tok = atoi(e);
     if (t.groups < 1) t.groups = 1;
     if (t.groups > 3) t.groups = 3;
     return t;
 }
 
-template <int TOK, int NW, int G, typename YT>
-int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, bool allow_split) {
-    using C = Cfg<TOK, NW>;
+constexpr size_t kScratchCounterOff = 4096, kScratchPartialOff = 8192;
+
+struct LaunchPlan {
+    int n_tiles, m_tiles, splits, rounds_per_split;
+};
+
+template <int TOK, int KSUB>
+LaunchPlan plan_launch(const ForwardArgs &a, int chan_per_tile, int sm_count, bool allow_split) {
+    LaunchPlan p;
+    p.n_tiles = (int)((a.N + chan_per_tile - 1) / chan_per_tile);
+    p.m_tiles = (int)((a.M + TOK - 1) / TOK);
+    const int rounds = (int)((a.K + kBlockK * KSUB - 1) / (kBlockK * KSUB));
+    // split-K only for small token tiles (their partial sums are small) when the output
+    // tiles alone leave most SMs idle: as many splits as fit in one wave, >= 2 rounds each
+    int splits = 1;
+    const long tiles = (long)p.n_tiles * p.m_tiles;
+    if (allow_split && TOK <= 64 && tiles <= 1024) {
+        int want = (int)(sm_count / tiles);
+        if (want > rounds / 2) want = rounds / 2;
+        if (want > 1) splits = want;
+    }
+    p.rounds_per_split = (rounds + splits - 1) / splits;
+    p.splits = (rounds + p.rounds_per_split - 1) / p.rounds_per_split;  // no empty split
+    return p;
+}
+
+// scratch == nullptr: use (and grow) the context's scratch; otherwise a caller-provided
+// region of scratch_bytes laid out as [0,4096) counters, partial sums from 4096.
+template <int TOK, int KSUB, int G, bool GATED, typename YT>
+int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, bool allow_split,
+               void *fixed_scratch, size_t fixed_scratch_bytes) {
+    using C = Cfg<TOK, KSUB>;
     CUtensorMap tx;
     int rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, a.K, a.M, kBlockK, TOK,
                        CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SHREWQ_OK) return rc;
-    auto kern = linear_i8_tcgen05_kernel<TOK, NW, G, YT>;
+    auto kern = linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT>;
     static bool attr_set = false;  // per instantiation
     if (!attr_set) {
         SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemRequest));
         attr_set = true;
     }
-    const int n_tiles = (int)((a.N + kTileN - 1) / kTileN), m_tiles = (int)((a.M + TOK - 1) / TOK);
-    const int num_kb = (int)((a.K + kBlockK - 1) / kBlockK);
-    // split-K when the output tiles alone leave most SMs idle: as many splits as fit in one
-    // wave, each with at least 4 k-blocks
-    int splits = 1;
-    if (allow_split && NW == 1) {
-        const int tiles = n_tiles * m_tiles;
-        int want = tiles <= 1024 ? ctx->sm_count / tiles : 1;
-        if (want > num_kb / 4) want = num_kb / 4;
-        if (want > 1) splits = want;
-    }
-    int kb_per_split = (num_kb + splits - 1) / splits;
-    splits = (num_kb + kb_per_split - 1) / kb_per_split;  // no empty split
-    SplitK sk{nullptr, nullptr, kb_per_split};
-    if (splits > 1) {
-        // scratch layout: [0,4096) quantizer words, [4096,8192) tile counters (at most one per
-        // SM is ever in use), partial sums from 8192
-        const size_t tiles = (size_t)n_tiles * m_tiles;
-        const size_t part_bytes = tiles * splits * TOK * kTileN * sizeof(float);
-        const size_t ctr_off = 4096, part_off = 8192;
-        if ((rc = ensure_scratch(ctx, part_off + part_bytes)) != SHREWQ_OK) return rc;
-        if (!ctx->counters_zeroed) {
-            // fresh scratch: counters must start at zero (the kernels reset them after use)
-            SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(static_cast<char *>(ctx->scratch) + ctr_off, 0, part_off - ctr_off, ctx->stream));
-            ctx->counters_zeroed = true;
+    const LaunchPlan p = plan_launch<TOK, KSUB>(a, GATED ? 64 : 128, ctx->sm_count, allow_split);
+    SplitK sk{nullptr, nullptr, p.rounds_per_split};
+    if (p.splits > 1) {
+        const size_t tiles = (size_t)p.n_tiles * p.m_tiles;
+        const size_t part_bytes = tiles * p.splits * TOK * kTileN * sizeof(float);
+        if (fixed_scratch) {
+            const size_t need = 4096 + part_bytes;
+            if (need > fixed_scratch_bytes)
+                return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
+                               "forward_noalloc: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu "
+                               "(use shrewq_linear_forward, which allocates)", need, fixed_scratch_bytes);
+            // the array keeps whatever the previous call left: the counters must start at zero
+            SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(fixed_scratch, 0, 4096, ctx->stream));
+            sk.counters = static_cast<unsigned int *>(fixed_scratch);
+            sk.partials = reinterpret_cast<float *>(static_cast<unsigned char *>(fixed_scratch) + 4096);
+        } else {
+            // context scratch: [0,4096) quantizer words, [4096,8192) tile counters (at most one
+            // per SM is ever in use), partial sums from 8192
+            if ((rc = ensure_scratch(ctx, kScratchPartialOff + part_bytes)) != SHREWQ_OK) return rc;
+            if (!ctx->counters_zeroed) {
+                // fresh scratch: counters must start at zero (the kernels reset them after use)
+                SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(static_cast<char *>(ctx->scratch) + kScratchCounterOff, 0,
+                                                     kScratchPartialOff - kScratchCounterOff, ctx->stream));
+                ctx->counters_zeroed = true;
+            }
+            sk.counters = reinterpret_cast<unsigned int *>(static_cast<char *>(ctx->scratch) + kScratchCounterOff);
+            sk.partials = reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + kScratchPartialOff);
         }
-        sk.counters = reinterpret_cast<unsigned int *>(static_cast<char *>(ctx->scratch) + ctr_off);
-        sk.partials = reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + part_off);
     }
-    dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits);
-    kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw2, tx, a.scales, a.bias, a.scales_up, a.bias_up,
-                                                                static_cast<YT *>(a.y), (int)a.M, (int)a.N, (int)a.K,
-                                                                a.ldy, a.epilogue, sk, ctx->dev_status);
+    Operands ops{a.scales, a.bias, a.scales_up, a.bias_up};
+    dim3 grid((unsigned)p.n_tiles, (unsigned)p.m_tiles, (unsigned)p.splits);
+    kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), (int)a.M,
+                                                                (int)a.N, (int)a.K, a.ldy, a.epilogue, sk,
+                                                                ctx->dev_status);
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;
 }
 
-template <int TOK, int NW, typename YT>
-int launch_tuned(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2) {
-    const Tuning t = read_tuning();
-#define SHREWQ_TC_CASE(G) return launch_cfg<TOK, NW, G, YT>(ctx, a, tw, tw2, t.splitk)
-    if (t.groups == 1) SHREWQ_TC_CASE(1);
-    if (t.groups == 2) SHREWQ_TC_CASE(2);
-    SHREWQ_TC_CASE(3);
-#undef SHREWQ_TC_CASE
+template <int TOK, int KSUB, bool GATED, typename YT>
+int launch_groups(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, const Tuning &t,
+                  void *fs, size_t fsb) {
+    if (t.groups == 1) return launch_cfg<TOK, KSUB, 1, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);
+    if (t.groups == 2) return launch_cfg<TOK, KSUB, 2, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);
+    return launch_cfg<TOK, KSUB, 3, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);
 }
 
-template <typename YT>
-int launch_y(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2) {
-    if (a.q_up) {
-        if (a.M <= 16) return launch_tuned<16, 2, YT>(ctx, a, tw, tw2);
-        if (a.M <= 32) return launch_tuned<32, 2, YT>(ctx, a, tw, tw2);
-        if (a.M <= 64) return launch_tuned<64, 2, YT>(ctx, a, tw, tw2);
-        return launch_tuned<128, 2, YT>(ctx, a, tw, tw2);
+// Token tile: the smallest tile that covers M up to 256; above that 256 tokens, unless
+// 128-token tiles fill the SMs markedly better (few channel tiles, e.g. N = 4096 at M = 512).
+int choose_tok(const ForwardArgs &a, int chan_per_tile, int sm_count) {
+    if (a.M <= 16) return 16;
+    if (a.M <= 32) return 32;
+    if (a.M <= 64) return 64;
+    if (a.M <= 128) return 128;
+    const long n_tiles = (long)((a.N + chan_per_tile - 1) / chan_per_tile);
+    auto fill = [&](int tok) {
+        const long tiles = n_tiles * (long)((a.M + tok - 1) / tok);
+        const long waves = (tiles + sm_count - 1) / sm_count;
+        return (double)tiles / (double)(waves * sm_count);
+    };
+    return fill(128) * 0.85 > fill(256) ? 128 : 256;
+}
+
+template <bool GATED, typename YT>
+int launch_y(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, void *fs, size_t fsb) {
+    const Tuning t = read_tuning();
+    const int tok = t.tok ? t.tok : choose_tok(a, GATED ? 64 : 128, ctx->sm_count);
+    switch (tok) {
+        // small token tiles are HBM-bound: 2 sub-blocks per stage keeps the pipeline 6-7 stages
+        // deep (TMEM columns limit the depth), i.e. ~100 KB of codes in flight per SM
+        case 16: return launch_groups<16, 2, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
+        case 32: return launch_groups<32, 2, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
+        case 64: return launch_groups<64, 2, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
+        case 128: return launch_groups<128, 2, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
+        default: return launch_groups<256, 1, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
     }
-    if (a.M <= 16) return launch_tuned<16, 1, YT>(ctx, a, tw, tw2);
-    if (a.M <= 32) return launch_tuned<32, 1, YT>(ctx, a, tw, tw2);
-    if (a.M <= 64) return launch_tuned<64, 1, YT>(ctx, a, tw, tw2);
-    if (a.M <= 128) return launch_tuned<128, 1, YT>(ctx, a, tw, tw2);
-    return launch_tuned<256, 1, YT>(ctx, a, tw, tw2);
 }
 
 // ---- forward without any allocation ---------------------------------------------------
 // Split-K scratch for shrewq_linear_forward_noalloc: a fixed array inside the library image
-// instead of a cudaMalloc'd buffer.  Every GPU that loads the library holds these 8 MiB
+// instead of a cudaMalloc'd buffer.  Every GPU that loads the library holds these 4 MiB
 // until the process exits.  Layout: [0,4096) tile counters, partial sums from 4096.
-constexpr size_t kStaticScratchBytes = 8u << 20;
-constexpr size_t kStaticCounterBytes = 4096;
+constexpr size_t kStaticScratchBytes = 4u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // In host code the array's name is only a handle for the runtime, not a device address:
@@ -676,59 +716,6 @@ int static_scratch_for_device(shrewq_ctx *ctx, void **out) {
     return SHREWQ_OK;
 }
 
-template <int TOK, typename YT>
-int launch_noalloc_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw) {
-    constexpr int G = 3;
-    using C = Cfg<TOK, 1>;
-    CUtensorMap tx;
-    int rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, a.K, a.M, kBlockK, TOK,
-                       CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != SHREWQ_OK) return rc;
-    auto kern = linear_i8_tcgen05_kernel<TOK, 1, G, YT>;
-    SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemRequest));
-    const int n_tiles = (int)((a.N + kTileN - 1) / kTileN), m_tiles = (int)((a.M + TOK - 1) / TOK);
-    const int num_kb = (int)((a.K + kBlockK - 1) / kBlockK);
-    const size_t tiles = (size_t)n_tiles * m_tiles;
-    int splits = 1;
-    if (tiles <= kStaticCounterBytes / 4) {
-        int want = (int)(ctx->sm_count / tiles);
-        if (want > num_kb / 4) want = num_kb / 4;
-        if (want > 1) splits = want;
-    }
-    int kb_per_split = (num_kb + splits - 1) / splits;
-    splits = (num_kb + kb_per_split - 1) / kb_per_split;
-    SplitK sk{nullptr, nullptr, kb_per_split};
-    if (splits > 1) {
-        const size_t need = kStaticCounterBytes + tiles * splits * TOK * kTileN * sizeof(float);
-        if (need > kStaticScratchBytes)
-            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
-                           "forward_noalloc: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu "
-                           "(use shrewq_linear_forward, which allocates)", need, kStaticScratchBytes);
-        void *base = nullptr;
-        if ((rc = static_scratch_for_device(ctx, &base)) != SHREWQ_OK) return rc;
-        // the array keeps whatever the previous call left: the counters must start at zero
-        SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(base, 0, kStaticCounterBytes, ctx->stream));
-        sk.counters = static_cast<unsigned int *>(base);
-        sk.partials = reinterpret_cast<float *>(static_cast<unsigned char *>(base) + kStaticCounterBytes);
-    }
-    dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits);
-    kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw, tx, a.scales, a.bias, nullptr, nullptr,
-                                                                static_cast<YT *>(a.y), (int)a.M, (int)a.N, (int)a.K,
-                                                                a.ldy, a.epilogue, sk, ctx->dev_status);
-    ctx->launches += 1;
-    SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
-    return SHREWQ_OK;
-}
-
-template <typename YT>
-int launch_noalloc_y(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw) {
-    if (a.M <= 16) return launch_noalloc_cfg<16, YT>(ctx, a, tw);
-    if (a.M <= 32) return launch_noalloc_cfg<32, YT>(ctx, a, tw);
-    if (a.M <= 64) return launch_noalloc_cfg<64, YT>(ctx, a, tw);
-    if (a.M <= 128) return launch_noalloc_cfg<128, YT>(ctx, a, tw);
-    return launch_noalloc_cfg<256, YT>(ctx, a, tw);
-}
-
 }  // namespace
 
 #ifdef SHREWQ_TRACE
@@ -744,22 +731,32 @@ bool tcgen05_supported(const ForwardArgs &a) {
            a.M < (1u << 31) && (a.M + 15) / 16 <= 65535 * 16;
 }
 
-int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, void *tmap_out) {
+// box_rows = 128 for plain tiles, 64 for the gate / up halves of a gated tile
+int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, int box_rows, void *tmap_out) {
     return encode_2d(ctx, static_cast<CUtensorMap *>(tmap_out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, k, n, kBlockK,
-                     kTileN, CU_TENSOR_MAP_SWIZZLE_64B);
+                     box_rows, CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
 int launch_gemm_tcgen05_noalloc(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap) {
     const CUtensorMap &tw = *static_cast<const CUtensorMap *>(w_tmap);
-    if (a.y_dtype == SHREWQ_BF16) return launch_noalloc_y<__nv_bfloat16>(ctx, a, tw);
-    return launch_noalloc_y<float>(ctx, a, tw);
+    void *base = nullptr;
+    int rc = static_scratch_for_device(ctx, &base);
+    if (rc != SHREWQ_OK) return rc;
+    if (a.y_dtype == SHREWQ_BF16) return launch_y<false, __nv_bfloat16>(ctx, a, tw, tw, base, kStaticScratchBytes);
+    return launch_y<false, float>(ctx, a, tw, tw, base, kStaticScratchBytes);
 }
 
+// w_tmap: 128-row boxes of the weight (plain) or 64-row boxes of the gate matrix (gated, with
+// w_up_tmap the 64-row boxes of the up matrix)
 int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap) {
     const CUtensorMap &tw = *static_cast<const CUtensorMap *>(w_tmap);
-    const CUtensorMap &tw2 = *static_cast<const CUtensorMap *>(w_up_tmap ? w_up_tmap : w_tmap);
-    if (a.y_dtype == SHREWQ_BF16) return launch_y<__nv_bfloat16>(ctx, a, tw, tw2);
-    return launch_y<float>(ctx, a, tw, tw2);
+    if (a.q_up) {
+        const CUtensorMap &tw2 = *static_cast<const CUtensorMap *>(w_up_tmap);
+        if (a.y_dtype == SHREWQ_BF16) return launch_y<true, __nv_bfloat16>(ctx, a, tw, tw2, nullptr, 0);
+        return launch_y<true, float>(ctx, a, tw, tw2, nullptr, 0);
+    }
+    if (a.y_dtype == SHREWQ_BF16) return launch_y<false, __nv_bfloat16>(ctx, a, tw, tw, nullptr, 0);
+    return launch_y<false, float>(ctx, a, tw, tw, nullptr, 0);
 }
 
 }  // namespace shrewq

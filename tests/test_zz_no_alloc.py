@@ -28,7 +28,7 @@ def _make(N, K, seed):
     return QuantizedLinear.from_linear(Linear(w, b), QuantConfig.int8_per_channel())
 
 
-@pytest.mark.parametrize("M,N,K", [(16, 1024, 4096), (48, 512, 2048), (300, 384, 1024)])
+@pytest.mark.parametrize("M,N,K", [(16, 1024, 4096), (48, 512, 2048), (32, 2048, 4096), (300, 384, 1024)])
 def test_noalloc_matches_allocating_forward_twice(M, N, K):
     from shrew_b200 import _lib
     from shrew_b200.quantize import Device
@@ -60,17 +60,17 @@ def test_noalloc_refuses_shapes_beyond_its_scratch_and_wrong_inputs():
     from shrew_b200.quantize import Device
     L = _lib.lib()
     dev = Device.get("cuda:0")
-    # 64 tokens x 2 channel tiles x 2 splits... pick a shape whose partial sums exceed 8 MiB:
-    # N = 128*36 (36 tiles) -> 4 splits of TOK = 128 tokens: 36*4*128*128*4 B = 9.4 MB
-    ql = _make(128 * 36, 2048, seed=1)
-    x = torch.zeros(128, 2048, dtype=torch.bfloat16, device="cuda")
-    y = torch.zeros(128, 128 * 36, dtype=torch.bfloat16, device="cuda")
+    # a shape whose partial sums exceed the 4 MiB array: 64 tokens, N = 1024 (8 channel
+    # tiles), K = 8192 -> 16 splits: 8*16 slices of 64*128 f32 = 4.19 MB (+ counters)
+    ql = _make(1024, 8192, seed=1)
+    x = torch.zeros(64, 8192, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(64, 1024, dtype=torch.bfloat16, device="cuda")
     dev.bind_stream()
-    rc = L.shrewq_linear_forward_noalloc(ql._h, ctypes.c_void_p(x.data_ptr()), 128, ctypes.c_void_p(y.data_ptr()),
-                                         _lib.BF16, 128 * 36, 0)
+    rc = L.shrewq_linear_forward_noalloc(ql._h, ctypes.c_void_p(x.data_ptr()), 64, ctypes.c_void_p(y.data_ptr()),
+                                         _lib.BF16, 1024, 0)
     assert rc == _lib.ERR_UNSUPPORTED
     msg = L.shrewq_last_error(dev.handle).decode()
-    assert "built-in array" in msg and "8388608" in msg
+    assert "built-in array" in msg and "4194304" in msg
     assert L.shrewq_linear_forward_noalloc(None, None, 1, None, 1, 1, 0) == _lib.ERR_INVALID_ARG
     odd = _make(64, 72, seed=2)  # in_features not a multiple of 16
     rc = L.shrewq_linear_forward_noalloc(odd._h, ctypes.c_void_p(x.data_ptr()), 4, ctypes.c_void_p(y.data_ptr()),
