@@ -193,6 +193,9 @@ def main():
     ap.add_argument("--workload", default="llama_mlp_m512", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="multi-GPU exchange: 'fused' = peer stores from the kernel epilogue, 'nccl' = all-gather")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = WORKLOADS[args.workload]
@@ -202,7 +205,7 @@ def main():
     import torch.distributed as dist
     from shrew_b200 import Linear, QuantConfig, QuantizedLinear, _lib
     from shrew_b200.quantize import Device
-    from shrew_b200.sharded import ShardedGatedMLP, ShardedLinear, plan_shards
+    from shrew_b200.sharded import FusedShardedGatedMLP, FusedShardedLinear, ShardedGatedMLP, ShardedLinear, plan_shards
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -233,14 +236,21 @@ def main():
         in_features = wl["K"]
         flops_step = 2 * M * wl["N"] * wl["K"]
     ring = max(2, -(-2 * L2_BYTES // shard_bytes) + 1)
+    fused = world > 1 and args.gather == "fused"
     models = []
     for c in range(ring):
         if wl["kind"] == "mlp":
             g, u, d = make_shard(dff, dm, 0), make_shard(dff, dm, 1), make_shard(dm, dff, 2)
-            models.append(ShardedGatedMLP(g, u, d, dff, dm))
+            if fused:
+                models.append(FusedShardedGatedMLP(g, u, d, dff, dm, M, share=models[0] if models else None))
+            else:
+                models.append(ShardedGatedMLP(g, u, d, dff, dm))
         else:
             q = make_shard(wl["N"], wl["K"], 0)
-            models.append(ShardedLinear(wl["N"], lambda x, out, _q=q: _q.forward(x, out=out)))
+            if fused:
+                models.append(FusedShardedLinear(wl["N"], q, None, M, torch.bfloat16, out=models[0].out if models else None))
+            else:
+                models.append(ShardedLinear(wl["N"], lambda x, out, _q=q: _q.forward(x, out=out)))
             models[-1].shard = q
     torch.cuda.synchronize()
 
@@ -255,12 +265,49 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step(i, x):
+    def eager_step(i, x):
         return models[i % ring].forward(x)
+
+    # One CUDA graph per ring entry: a step is a handful of short kernels (and, on several
+    # GPUs, device-side barriers), so replaying a captured graph removes the host launch
+    # path from the measurement.  x_static is the graph's input buffer, outs[i] its result.
+    x_static = x_dev.clone()
+    graphs, outs = [], []
+    # NCCL collectives captured in a graph left the processes hanging at exit on this software
+    # stack (results were printed, the ranks never ended): the NCCL variant is launched eagerly
+    use_graphs = not args.no_graph and not (world > 1 and not fused)
+    if use_graphs:
+        try:
+            for i in range(ring):
+                eager_step(i, x_static)  # first use of a kernel sets its attributes: outside capture
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(ring):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        outs.append(eager_step(i, x_static))
+                    graphs.append(g)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+        except Exception as e:  # capture unsupported for some collective: measure eagerly
+            sys.stderr.write(f"bench: graph capture failed ({e!r}); running eagerly\n")
+            graphs, outs, use_graphs = [], [], False
+
+    launches_per_step = 2 if wl["kind"] == "mlp" else 1
+
+    def step(i, x):
+        if use_graphs:
+            if x is not x_static:
+                x_static.copy_(x, non_blocking=True)
+            graphs[i % ring].replay()
+            return outs[i % ring]
+        return eager_step(i, x)
 
     # ---- device-resident metric ----
     for i in range(args.warmup):
-        step(i, x_dev)
+        step(i, x_static)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -270,7 +317,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        step(i, x_dev)
+        step(i, x_static)
     e1.record()
     barrier()
     sdev.synchronize()  # also surfaces a kernel that gave up a bounded wait
@@ -278,20 +325,26 @@ def main():
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_total = float(ms.item())
-    launches = sdev.launch_count() - launches0
+    launches = launches_per_step * args.steps if use_graphs else sdev.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     value = M * args.steps / (ms_total * 1e-3)
 
     # ---- end to end: pinned host input in, host output back, every step ----
+    def e2e_step(i):
+        if use_graphs:
+            x_static.copy_(x_host, non_blocking=True)   # pinned host -> the graph's input buffer
+            y = step(i, x_static)
+        else:
+            y = step(i, x_host.to(dev, non_blocking=True))
+        y_host.copy_(y, non_blocking=True)              # result back to pinned host memory
+        torch.cuda.current_stream().synchronize()
+
     for i in range(3):
-        y_host.copy_(step(i, x_host.to(dev, non_blocking=True)))
+        e2e_step(i)
     barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        xd = x_host.to(dev, non_blocking=True)
-        y = step(i, xd)
-        y_host.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        e2e_step(i)
     t_e2e = torch.tensor([time.perf_counter() - t0], device=dev)
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
@@ -339,12 +392,12 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x int8 -> f32 accumulate", "data": "synthetic",
         "config": {"workload": args.workload, **{k: v for k, v in wl.items() if k != "kind"},
-                   "weights": "INT8 per-channel, N(0,0.02)", "sharding": f"output channels over {world} GPU(s), all-gather",
+                   "weights": "INT8 per-channel, N(0,0.02)", "sharding": "none (single GPU)" if world == 1 else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
                    "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU) > 2x L2"},
         "tflops": flops_step * args.steps / (ms_total * 1e-3) / 1e12,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": y_host.numel() * 2},
-        "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+        "gpu_launches": int(launches), "launch_mode": "cuda graph replay (one graph per ring entry)" if use_graphs else "host launches", "clocks": clocks, "roofline": roof,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cstep, tokens, sample = cpu_step_factory(wl)

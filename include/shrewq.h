@@ -170,6 +170,21 @@ SHREWQ_API int shrewq_linear_forward_noalloc(shrewq_linear *lin, const void *x_d
 SHREWQ_API int shrewq_linear_forward_gate_up_silu(shrewq_linear *gate, shrewq_linear *up, const void *x_dev,
                                        int x_dtype, size_t M, void *h_dev, int h_dtype, size_t ldh);
 
+/*
+ * Forward of a row shard with the all-gather fused into the epilogue (no counterpart in the
+ * reference, whose `distributed.rs` is single-process).  The slice y[:, n0:n1] this shard
+ * computes is stored into y_dev and, with the same element offsets, into each of the
+ * n_peers (<= 7) buffers peer_y_dev[i]: the other GPUs' copies of the full [M, N] output,
+ * mapped into this process (CUDA peer access / IPC / symmetric memory), each pointer already
+ * advanced to column n0.  Plain stores over NVLink; the caller synchronises the GPUs
+ * afterwards (a cross-device barrier) before anyone reads.  `up` != NULL selects the gated
+ * form silu(lin(x)) * up(x) (epilogue is then ignored).  Only the gemv and tcgen05 kernels
+ * take peer destinations.
+ */
+SHREWQ_API int shrewq_linear_forward_peers(shrewq_linear *lin, shrewq_linear *up, const void *x_dev, int x_dtype,
+                                           size_t M, void *y_dev, void *const *peer_y_dev, int n_peers, int y_dtype,
+                                           size_t ldy, int epilogue);
+
 /* Accessors mirroring QuantizedLinear's public fields / methods (quantize.rs:392-394,
  * :455-459). */
 SHREWQ_API size_t shrewq_linear_in_features(const shrewq_linear *lin);

@@ -271,7 +271,8 @@ size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin) { return lin
 const char *shrewq_linear_last_kernel(const shrewq_linear *lin) { return lin ? lin->last_kernel : "none"; }
 
 static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev, int x_dtype, size_t M, void *y_dev,
-                        int y_dtype, size_t ldy, int epilogue, const char *who) {
+                        int y_dtype, size_t ldy, int epilogue, const char *who, void *const *peers = nullptr,
+                        int n_peers = 0) {
     if (!lin) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "%s: handle is NULL", who);
     shrewq_ctx *ctx = lin->ctx;
     if (up && (up->ctx != ctx || up->n != lin->n || up->k != lin->k))
@@ -295,6 +296,14 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
     a.x = x_dev; a.x_dtype = x_dtype; a.y = y_dev; a.y_dtype = y_dtype;
     a.M = M; a.N = lin->n; a.K = lin->k; a.ldy = ldy; a.epilogue = epilogue;
     if (up) { a.q_up = up->q; a.scales_up = up->scales_f32; a.bias_up = up->bias; }
+    if (n_peers < 0 || n_peers > kMaxPeers || (n_peers > 0 && !peers))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: between 0 and %d peer destinations", who, kMaxPeers);
+    for (int i = 0; i < n_peers; ++i) {
+        if (!peers[i] || (reinterpret_cast<uintptr_t>(peers[i]) % yal))
+            return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: peer destination %d is NULL or misaligned", who, i);
+        a.extra.p[i] = peers[i];
+    }
+    a.extra.n = n_peers;
 
     const bool vec16 = (lin->k % 16) == 0 && (reinterpret_cast<uintptr_t>(lin->q) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 &&
@@ -321,7 +330,10 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
     if (choice == kForceGemv) { rc = launch_gemv(ctx, a); name = "gemv"; }
     else if (choice == kForceTc) { rc = up ? launch_gemm_tcgen05(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
         name = "tcgen05"; }
-    else { rc = launch_gemm_simt(ctx, a); name = "simt"; }
+    else {
+        if (n_peers > 0) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: peer destinations need the gemv or tcgen05 kernel", who);
+        rc = launch_gemm_simt(ctx, a); name = "simt";
+    }
     lin->last_kernel = name;
     return rc;
 }
@@ -362,6 +374,13 @@ int shrewq_linear_forward_gate_up_silu(shrewq_linear *gate, shrewq_linear *up, c
                                        size_t M, void *h_dev, int h_dtype, size_t ldh) {
     if (!up) return set_err(gate ? gate->ctx : nullptr, SHREWQ_ERR_INVALID_ARG, "gate_up_silu: up handle is NULL");
     return forward_impl(gate, up, x_dev, x_dtype, M, h_dev, h_dtype, ldh, SHREWQ_EPILOGUE_NONE, "gate_up_silu");
+}
+
+int shrewq_linear_forward_peers(shrewq_linear *lin, shrewq_linear *up, const void *x_dev, int x_dtype, size_t M,
+                                void *y_dev, void *const *peer_y_dev, int n_peers, int y_dtype, size_t ldy,
+                                int epilogue) {
+    return forward_impl(lin, up, x_dev, x_dtype, M, y_dev, y_dtype, ldy, up ? SHREWQ_EPILOGUE_NONE : epilogue,
+                        "linear_forward_peers", peer_y_dev, n_peers);
 }
 
 int shrewq_linear_forward_host(shrewq_linear *lin, const void *x_host, int x_dtype, size_t M, void *y_host,

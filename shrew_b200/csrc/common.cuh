@@ -82,6 +82,14 @@ int launch_dequantize(shrewq_ctx *ctx, const int8_t *q, const double *scales, si
                       size_t cols, int granularity, int out_dtype, void *out);
 int launch_scales_to_f32(shrewq_ctx *ctx, const double *scales, int granularity, size_t n, float *out);
 
+// Extra destinations of a forward: the same output slice is also stored into these buffers
+// (peer GPUs' memory, mapped into this process) — the all-gather fused into the epilogue.
+constexpr int kMaxPeers = 7;
+struct Dests {
+    void *p[kMaxPeers];
+    int n;
+};
+
 struct ForwardArgs {
     const int8_t *q;       // [N,K]
     const float *scales;   // [N] f32
@@ -96,6 +104,7 @@ struct ForwardArgs {
     const int8_t *q_up = nullptr;
     const float *scales_up = nullptr;
     const float *bias_up = nullptr;
+    Dests extra = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0};
 };
 
 int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a);

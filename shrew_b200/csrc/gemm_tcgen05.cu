@@ -211,10 +211,19 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
 
 template <typename YT>
 __device__ __forceinline__ void store_out(YT *p, float v);
+// the local store plus one store per peer destination (same element offset in each buffer)
+template <typename YT>
+__device__ __forceinline__ void store_all(YT *y, const Dests &extra, size_t off, float v);
 template <>
 __device__ __forceinline__ void store_out<float>(float *p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename YT>
+__device__ __forceinline__ void store_all(YT *y, const Dests &extra, size_t off, float v) {
+    store_out<YT>(y + off, v);
+    for (int d = 0; d < extra.n; ++d) store_out<YT>(static_cast<YT *>(extra.p[d]) + off, v);
+}
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
@@ -250,7 +259,7 @@ struct Operands {
 template <int TOK, int KSUB, int G, bool GATED, typename YT>
 __global__ void __launch_bounds__(64 + 128 * G, 1)
 linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
-                         const __grid_constant__ CUtensorMap tmap_x, Operands ops, YT *__restrict__ y, int M, int N,
+                         const __grid_constant__ CUtensorMap tmap_x, Operands ops, YT *__restrict__ y, Dests extra, int M, int N,
                          int K, size_t ldy, int epilogue, SplitK sk, DeviceStatus *status) {
     using C = Cfg<TOK, KSUB>;
     constexpr int kChan = GATED ? 64 : 128;  // output channels per CTA
@@ -435,7 +444,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                             const int m = m0 + c * 16 + i;
                             const float g = __uint_as_float(r[i]) * sc + bs;
                             const float o = silu_f(g) * xch[i * 64 + row];
-                            if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
+                            if (n_ok && m < M) store_all<YT>(y, extra, (size_t)m * ldy + n, o);
                         }
                     }
                     named_bar_sync(2 + group, 128);  // xch is rewritten by the next chunk
@@ -445,7 +454,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                         const int m = m0 + c * 16 + i;
                         float o = __uint_as_float(r[i]) * sc + bs;
                         if (epilogue == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
-                        if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
+                        if (n_ok && m < M) store_all<YT>(y, extra, (size_t)m * ldy + n, o);
                     }
                 }
             }
@@ -495,7 +504,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                             } else if (epilogue == SHREWQ_EPILOGUE_RELU) {
                                 o = fmaxf(o, 0.0f);
                             }
-                            if (n_ok && m < M) store_out<YT>(y + (size_t)m * ldy + n, o);
+                            if (n_ok && m < M) store_all<YT>(y, extra, (size_t)m * ldy + n, o);
                         }
                     }
                 }
@@ -642,7 +651,7 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
     }
     Operands ops{a.scales, a.bias, a.scales_up, a.bias_up};
     dim3 grid((unsigned)p.n_tiles, (unsigned)p.m_tiles, (unsigned)p.splits);
-    kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), (int)a.M,
+    kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M,
                                                                 (int)a.N, (int)a.K, a.ldy, a.epilogue, sk,
                                                                 ctx->dev_status);
     ctx->launches += 1;

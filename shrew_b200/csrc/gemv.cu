@@ -79,8 +79,8 @@ __global__ void __launch_bounds__(kThreads)
 gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                const float *__restrict__ bias, const int8_t *__restrict__ q_up,
                const float *__restrict__ scales_up, const float *__restrict__ bias_up,
-               const XT *__restrict__ x, YT *__restrict__ y, int M, int N, int K, size_t ldy,
-               int epilogue) {
+               const XT *__restrict__ x, YT *__restrict__ y, Dests extra, int M, int N, int K,
+               size_t ldy, int epilogue) {
     constexpr int NR = GATED ? R / 2 : R;  // distinct output columns per CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * NR;
@@ -180,6 +180,7 @@ gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
             if (epilogue == SHREWQ_EPILOGUE_RELU) out = fmaxf(out, 0.0f);
         }
         store_y<YT>(y + (size_t)m * ldy + n, out);
+        for (int d = 0; d < extra.n; ++d) store_y<YT>(static_cast<YT *>(extra.p[d]) + (size_t)m * ldy + n, out);
     }
 }
 
@@ -189,7 +190,7 @@ void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     const unsigned grid = (unsigned)((a.N + NR - 1) / NR);
     gemv_i8_kernel<MT, R, XT, YT, GATED><<<grid, kThreads, 0, ctx->stream>>>(
         a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const XT *>(a.x),
-        static_cast<YT *>(a.y), (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
+        static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
 }
 
 template <typename XT, typename YT, bool GATED>

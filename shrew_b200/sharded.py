@@ -119,3 +119,81 @@ class ShardedGatedMLP:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.out.forward(self.hidden.forward(x))
+
+
+# ---- all-gather fused into the kernel epilogue (peer stores over NVLink) ------------------
+class PeerOutput:
+    """The full [m_max, n] output of a sharded layer, allocated as symmetric memory so that
+    every rank holds a mapping of every other rank's copy.  A shard's kernel stores its
+    column slice into all copies itself; `barrier()` (a device-side signal exchange on the
+    current stream) then makes the whole matrix readable everywhere."""
+
+    def __init__(self, m_max: int, n: int, dtype: torch.dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.buf = symm.empty((m_max, n), dtype=dtype, device=device)
+        self.hdl = symm.rendezvous(self.buf, self.group)
+        self.rank, self.world = self.hdl.rank, self.hdl.world_size
+        self.n = n
+        self.esize = self.buf.element_size()
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+
+    def slice_ptrs(self, n0: int):
+        """(own pointer, [peer pointers]) of element [0, n0] in every copy."""
+        off = n0 * self.esize
+        own = self.ptrs[self.rank] + off
+        return own, [p + off for r, p in enumerate(self.ptrs) if r != self.rank]
+
+    def barrier(self):
+        self.hdl.barrier()
+
+
+class FusedShardedLinear:
+    """Row shard of a quantized Linear whose forward writes y[:, n0:n1] into every rank's
+    output buffer from the kernel epilogue (shrewq_linear_forward_peers)."""
+
+    def __init__(self, n: int, shard, up_shard, m_max: int, dtype: torch.dtype, group=None, out=None):
+        import ctypes
+        self.plan = plan_shards(n, dist.get_world_size(group))
+        self.rank = dist.get_rank(group)
+        self.n0, self.n1 = self.plan.rows(self.rank)
+        self.shard, self.up = shard, up_shard
+        # `out` lets several layers of the same shape share one symmetric buffer
+        self.out = out if out is not None else PeerOutput(m_max, n, dtype, shard.weight_q.data.device, group)
+        own, peers = self.out.slice_ptrs(self.n0)
+        self._own = ctypes.c_void_p(own)
+        self._peers = (ctypes.c_void_p * max(1, len(peers)))(*peers)
+        self._n_peers = len(peers)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from . import _lib
+        from .quantize import _DTYPE_CODE, _ptr
+        m = x.shape[0]
+        if m > self.out.buf.shape[0]:
+            raise ValueError("FusedShardedLinear: batch larger than the symmetric output buffer")
+        x = x.contiguous()
+        dev = self.shard.device
+        dev.bind_stream()
+        if self.n1 > self.n0:
+            rc = _lib.lib().shrewq_linear_forward_peers(
+                self.shard._h, self.up._h if self.up is not None else None, _ptr(x), _DTYPE_CODE[x.dtype], m,
+                self._own, self._peers, self._n_peers, _DTYPE_CODE[self.out.buf.dtype], self.out.n, _lib.EPILOGUE_NONE)
+            _lib.check(rc, dev.handle)
+        self.out.barrier()
+        return self.out.buf[:m]
+
+
+class FusedShardedGatedMLP:
+    """The gated MLP block with both all-gathers fused into the kernels: gate/up shard ->
+    peer stores of h -> barrier -> down shard -> peer stores of y -> barrier."""
+
+    def __init__(self, gate, up, down, n_hidden: int, n_out: int, m_max: int, dtype=torch.bfloat16, group=None,
+                 share=None):
+        self.hidden = FusedShardedLinear(n_hidden, gate, up, m_max, dtype, group,
+                                         out=None if share is None else share.hidden.out)
+        self.out = FusedShardedLinear(n_out, down, None, m_max, dtype, group,
+                                      out=None if share is None else share.out.out)
+        self.gate, self.up, self.down = gate, up, down
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.out.forward(self.hidden.forward(x))
