@@ -101,19 +101,10 @@ gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
 #pragma unroll
         for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
 
-    // software pipeline: the next step's weight loads are issued before this step's math, so
-    // every lane keeps 2*R independent 16-byte loads in flight
-    int c = warp * 32 + lane;
-    bool have = c < chunks;
-    uint4 wv[R];
+    for (int c = warp * 32 + lane; c < chunks; c += kWarps * 32) {
+        uint4 wv[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) wv[r] = have ? ld_stream_16(rowp[r] + ((size_t)c << 4)) : make_uint4(0, 0, 0, 0);
-    while (have) {
-        const int cn = c + kWarps * 32;
-        const bool have_n = cn < chunks;
-        uint4 wn[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) wn[r] = have_n ? ld_stream_16(rowp[r] + ((size_t)cn << 4)) : make_uint4(0, 0, 0, 0);
+        for (int r = 0; r < R; ++r) wv[r] = ld_stream_16(rowp[r] + ((size_t)c << 4));
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             float xf[16];
@@ -139,10 +130,6 @@ gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                 acc[r][m] = s;
             }
         }
-#pragma unroll
-        for (int r = 0; r < R; ++r) wv[r] = wn[r];
-        c = cn;
-        have = have_n;
     }
 
     __shared__ float s_red[kWarps][R][MT];

@@ -1,0 +1,120 @@
+"""Kernel-level timings of libshrewq on one GPU (CUDA events around CUDA-graph replays, so
+host launch cost is excluded; the weights rotate through a ring larger than twice L2).
+
+    python -m shrew_b200.kernel_bench quant      # quantize / dequantize bandwidth sweep
+    python -m shrew_b200.kernel_bench lin        # forward kernels over a batch sweep
+    python -m shrew_b200.kernel_bench lin 4096 4096 1,16,256   # one layer shape, chosen batches
+
+Prints one JSON object per measurement: microseconds per launch, algorithmic GB/s and
+TFLOP/s.  Algorithmic bytes: quantize 5 B/element + 8 B/row; forward N*K + 4*N +
+M*K*2 + M*N*2 (bf16 activations and outputs)."""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from . import QuantConfig, QuantizedLinear, QuantizedTensor, _lib, dequantize_tensor, quantize_tensor
+from .quantize import Device
+
+L2_BYTES = 126 << 20
+
+
+def _time_graph(fn, iters=10, warm=3):
+    """Seconds per call of fn, replayed from a CUDA graph."""
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    for _ in range(warm):
+        g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e-3 / iters
+
+
+def bench_quant():
+    for (R, C) in [(1024, 1024), (2048, 2048), (4096, 4096), (8192, 8192), (16384, 8192), (16384, 16384), (32768, 16384)]:
+        nbuf = max(1, int(2 * L2_BYTES // (R * C * 4)) + 1) if R * C * 4 < 2 * L2_BYTES else 1
+        ws = []
+        for i in range(nbuf):
+            w = torch.randn(R, C, device="cuda")
+            w[torch.rand(R, C, device="cuda") < 0.01] *= 50.0   # 1 % outliers x50
+            ws.append(w)
+        q = torch.empty(R * C, dtype=torch.int8, device="cuda")
+        out = {}
+        for name, cfg in (("per_channel", QuantConfig.int8_per_channel()), ("per_tensor", QuantConfig.int8())):
+            def f():
+                for w in ws:
+                    quantize_tensor(w, cfg)
+            t = _time_graph(f) / nbuf
+            print(json.dumps(dict(kernel="quantize", granularity=name, rows=R, cols=C, us=t * 1e6,
+                                  GBs=(5 * R * C + 8 * R) / t / 1e9)), flush=True)
+        qt = quantize_tensor(ws[0], QuantConfig.int8_per_channel())
+        t = _time_graph(lambda: dequantize_tensor(qt))
+        print(json.dumps(dict(kernel="dequantize", rows=R, cols=C, us=t * 1e6, GBs=5 * R * C / t / 1e9)), flush=True)
+        del ws, q, qt
+
+
+def _layers(N, K, nbuf):
+    out = []
+    for _ in range(nbuf):
+        q = torch.randint(-127, 128, (N * K,), dtype=torch.int8, device="cuda")
+        qt = QuantizedTensor(q, torch.rand(N, dtype=torch.float64, device="cuda") * 1e-3 + 1e-4, [N, K], torch.float32,
+                             QuantConfig.int8_per_channel())
+        out.append(QuantizedLinear.new(qt, None))
+    return out
+
+
+def bench_lin(shapes, batches):
+    L = _lib.lib()
+    for (N, K) in shapes:
+        nbuf = max(2, int(2 * L2_BYTES // (N * K)) + 1)
+        lins = _layers(N, K, nbuf)
+        for M in batches:
+            x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            for force in ("gemv", "tcgen05"):
+                if force == "gemv" and M > 16:
+                    continue
+                L.shrewq_force_kernel(force.encode())
+
+                def f():
+                    for lin in lins:
+                        lin.forward(x, out=y)
+                try:
+                    t = _time_graph(f, iters=5, warm=2) / nbuf
+                    Device.get("cuda:0").synchronize()
+                except Exception as e:  # noqa: BLE001
+                    print(json.dumps(dict(kernel=force, M=M, N=N, K=K, error=str(e))), flush=True)
+                    continue
+                by = N * K + 4 * N + M * K * 2 + M * N * 2
+                print(json.dumps(dict(kernel=force, M=M, N=N, K=K, us=t * 1e6, GBs=by / t / 1e9,
+                                      TFs=2 * M * N * K / t / 1e12)), flush=True)
+        L.shrewq_force_kernel(b"auto")
+        del lins
+
+
+def main(argv):
+    which = argv[1] if len(argv) > 1 else "lin"
+    if which == "quant":
+        bench_quant()
+    else:
+        shapes = [(4096, 4096), (11008, 4096), (4096, 11008)]
+        batches = [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 4096]
+        if len(argv) >= 4:
+            shapes = [(int(argv[2]), int(argv[3]))]
+        if len(argv) >= 5:
+            batches = [int(b) for b in argv[4].split(",")]
+        bench_lin(shapes, batches)
+
+
+if __name__ == "__main__":
+    main(sys.argv)
