@@ -58,7 +58,7 @@ static int bind(shrewq_ctx *ctx) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt };
+enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma };
 
 }  // namespace shrewq
 
@@ -147,6 +147,7 @@ int shrewq_force_kernel(const char *name) {
     else if (!strcmp(name, "gemv")) g_forced_kernel = kForceGemv;
     else if (!strcmp(name, "tcgen05")) g_forced_kernel = kForceTc;
     else if (!strcmp(name, "simt")) g_forced_kernel = kForceSimt;
+    else if (!strcmp(name, "mma")) g_forced_kernel = kForceMma;
     else return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "force_kernel: unknown kernel '%s'", name);
     return SHREWQ_OK;
 }
@@ -319,6 +320,9 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             if (!tc_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05 cannot take this shape/dtype", who);
             choice = kForceTc; break;
         case kForceSimt: choice = kForceSimt; break;
+        case kForceMma:
+            if (!gemv_mma_supported(a)) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced mma kernel cannot take this shape/dtype", who);
+            choice = kForceMma; break;
         default:
             // CUDA-core GEMV keeps up with HBM only for a few tokens; beyond that the tensor
             // cores take over (bf16 activations), else the general f32 kernel.
@@ -328,6 +332,7 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
     }
     const char *name;
     if (choice == kForceGemv) { rc = launch_gemv(ctx, a); name = "gemv"; }
+    else if (choice == kForceMma) { rc = launch_gemv_mma(ctx, a); name = "mma"; }
     else if (choice == kForceTc) { rc = up ? launch_gemm_tcgen05(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
         name = "tcgen05"; }
     else {

@@ -11,6 +11,8 @@
 // L1 (read once); the activations are tiny, read through L1 and reused by every row.
 // Codes are widened to f32 in registers and fed to FFMA; partial sums are combined with
 // warp shuffles, then across the 4 warps through shared memory.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace shrewq {
@@ -80,8 +82,11 @@ gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                const float *__restrict__ bias, const int8_t *__restrict__ q_up,
                const float *__restrict__ scales_up, const float *__restrict__ bias_up,
                const XT *__restrict__ x, YT *__restrict__ y, Dests extra, int M, int N, int K,
-               size_t ldy, int epilogue) {
+               size_t ldy, int epilogue, int pdl) {
     constexpr int NR = GATED ? R / 2 : R;  // distinct output columns per CTA
+    // Programmatic dependent launch (opt-in): let the next kernel of the stream start its
+    // prologue while this one runs ...
+    if (pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * NR;
     const int chunks = K >> 4;
@@ -100,6 +105,10 @@ gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
     for (int r = 0; r < R; ++r)
 #pragma unroll
         for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
+
+    // ... and do not touch the activations (or write the output) before the previous kernel
+    // of the stream, which may have produced them, has completed
+    if (pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     for (int c = warp * 32 + lane; c < chunks; c += kWarps * 32) {
         uint4 wv[R];
@@ -175,9 +184,29 @@ template <int MT, int R, typename XT, typename YT, bool GATED>
 void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     constexpr int NR = GATED ? R / 2 : R;
     const unsigned grid = (unsigned)((a.N + NR - 1) / NR);
+    // SHREWQ_GEMV_PDL=1 launches with programmatic stream serialization so that back-to-back
+    // GEMVs overlap launch latency and prologue.  Built, compiled, NOT yet run on a GPU: off
+    // unless the variable is set.
+    static const bool pdl = getenv("SHREWQ_GEMV_PDL") && atoi(getenv("SHREWQ_GEMV_PDL")) != 0;
+    if (pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, gemv_i8_kernel<MT, R, XT, YT, GATED>, a.q, a.scales, a.bias, a.q_up, a.scales_up,
+                           a.bias_up, static_cast<const XT *>(a.x), static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N,
+                           (int)a.K, a.ldy, a.epilogue, 1);
+        return;
+    }
     gemv_i8_kernel<MT, R, XT, YT, GATED><<<grid, kThreads, 0, ctx->stream>>>(
         a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const XT *>(a.x),
-        static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
+        static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, 0);
 }
 
 template <typename XT, typename YT, bool GATED>

@@ -1,0 +1,228 @@
+// Weight-only INT8 forward for small batches (M <= 64) on warp-level MMA, sm_100a.
+//
+// STATUS: built and compiled, its index arithmetic is checked on the CPU
+// (tests/test_mma_layout.py emulates the fragment layouts), but it has NOT yet run on a GPU.
+// It is never chosen automatically; shrewq_force_kernel("mma") selects it.
+//
+// Why it exists: for 4 < M <= 64 the layer is HBM-bound, but the tcgen05 kernel feeds the
+// tensor core from ONE issuing thread per CTA (about 80 cycles per instruction, each covering
+// 2 KB of codes), which caps an SM's stream rate below what HBM delivers, and the CUDA-core
+// GEMV needs M FMAs per code.  Here every warp loads its own codes straight from global
+// memory into registers (no shared-memory staging, no barrier hand-offs), widens them, and
+// issues mma.sync.m16n8k16 (bf16): 64 warps per SM issue in parallel and an MMA costs the
+// same for 1 or 16 tokens.
+//
+// Mapping (per warp, per 64-wide k-block): lane (g = lane/4, t = lane%4) loads the 16 codes
+// W[n0 + 8*nb + g][kb*64 + 16t .. +15] for each of its NB channel blocks, and the 16
+// activations x[m][kb*64 + 16t .. +15] for token rows m = 16*mt + g and m + 8.  MMA step j
+// (0..3) uses codes 4j..4j+3 and activations 4j..4j+3 of those runs: operand slot 2t+e holds
+// k = 16t + 4j + e and slot 2t+8+e holds k = 16t + 4j + 2 + e, for A and B alike, so the 16
+// slots of one instruction cover 16 distinct k of the block and four instructions cover all
+// 64 (a dot product does not care about the order of k).
+// A CTA of 8 warps owns 16 channels (8 when gated: a gate block and an up block); the warps
+// split K in 64-wide blocks and their accumulators are summed through shared memory.
+#include <cstdlib>
+
+#include "common.cuh"
+
+namespace shrewq {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int NB = 2;  // channel blocks of 8 per warp
+
+__device__ __forceinline__ uint4 ld_stream_16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// 4 INT8 codes -> two packed bf16x2 words, exactly (see gemm_tcgen05.cu for the trick)
+__device__ __forceinline__ void cvt_i8x4_bf16(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    const uint32_t u = w ^ 0x80808080u;
+    const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440)) - 8388736.0f;
+    const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7441)) - 8388736.0f;
+    const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7442)) - 8388736.0f;
+    const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)) - 8388736.0f;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(f1), "f"(f0));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(f3), "f"(f2));
+}
+
+// D[16x8] += A[16x16] * B[16x8], bf16 operands, f32 accumulate
+__device__ __forceinline__ void mma_bf16_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+
+template <typename YT>
+__device__ __forceinline__ void put(YT *p, float v);
+template <>
+__device__ __forceinline__ void put<float>(float *p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void put<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+// MT16: token tiles of 16 (M <= 16*MT16).  K must be a multiple of 64.
+template <int MT16, typename YT, bool GATED>
+__global__ void __launch_bounds__(kThreads)
+gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, const float *__restrict__ bias,
+                const int8_t *__restrict__ q_up, const float *__restrict__ scales_up,
+                const float *__restrict__ bias_up, const __nv_bfloat16 *__restrict__ x, YT *__restrict__ y,
+                Dests extra, int M, int N, int K, size_t ldy, int epilogue) {
+    constexpr int kChan = GATED ? 8 : 8 * NB;  // output channels per CTA
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * kChan;
+    const int kblocks = K >> 6;
+
+    // the row of codes this lane reads for each channel block
+    const int8_t *wrow[NB];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        int n = n0 + (GATED ? 0 : nb * 8) + g;
+        n = n < N ? n : N - 1;  // clamp: duplicates are computed and dropped
+        wrow[nb] = ((GATED && nb == 1) ? q_up : q) + (size_t)n * K + 16 * t;
+    }
+    // the activation rows this lane reads for each token tile (null = padding row)
+    const __nv_bfloat16 *xlo[MT16], *xhi[MT16];
+#pragma unroll
+    for (int mt = 0; mt < MT16; ++mt) {
+        const int m = mt * 16 + g;
+        xlo[mt] = m < M ? x + (size_t)m * K + 16 * t : nullptr;
+        xhi[mt] = m + 8 < M ? x + (size_t)(m + 8) * K + 16 * t : nullptr;
+    }
+
+    float acc[MT16][NB][4];
+#pragma unroll
+    for (int mt = 0; mt < MT16; ++mt)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[mt][nb][r] = 0.0f;
+
+#pragma unroll 2
+    for (int kb = warp; kb < kblocks; kb += kWarps) {
+        const size_t koff = (size_t)kb << 6;
+        uint4 wv[NB];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) wv[nb] = ld_stream_16(wrow[nb] + koff);
+        // 16 activations = 8 bf16x2 words per row
+        uint32_t al[MT16][8], ah[MT16][8];
+#pragma unroll
+        for (int mt = 0; mt < MT16; ++mt) {
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            const uint4 l0 = xlo[mt] ? __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff)) : z;
+            const uint4 l1 = xlo[mt] ? __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff) + 1) : z;
+            const uint4 h0 = xhi[mt] ? __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff)) : z;
+            const uint4 h1 = xhi[mt] ? __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff) + 1) : z;
+            al[mt][0] = l0.x; al[mt][1] = l0.y; al[mt][2] = l0.z; al[mt][3] = l0.w;
+            al[mt][4] = l1.x; al[mt][5] = l1.y; al[mt][6] = l1.z; al[mt][7] = l1.w;
+            ah[mt][0] = h0.x; ah[mt][1] = h0.y; ah[mt][2] = h0.z; ah[mt][3] = h0.w;
+            ah[mt][4] = h1.x; ah[mt][5] = h1.y; ah[mt][6] = h1.z; ah[mt][7] = h1.w;
+        }
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const uint32_t w4[4] = {wv[nb].x, wv[nb].y, wv[nb].z, wv[nb].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t b0, b1;  // codes 4j,4j+1 | 4j+2,4j+3 of this lane's run
+                cvt_i8x4_bf16(w4[j], b0, b1);
+#pragma unroll
+                for (int mt = 0; mt < MT16; ++mt)
+                    mma_bf16_16816(acc[mt][nb], al[mt][2 * j], ah[mt][2 * j], al[mt][2 * j + 1], ah[mt][2 * j + 1], b0, b1);
+            }
+        }
+    }
+
+    // sum the 8 warps' accumulators through shared memory
+    __shared__ float s_red[kWarps][MT16 * NB * 4][32];
+#pragma unroll
+    for (int mt = 0; mt < MT16; ++mt)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) s_red[warp][(mt * NB + nb) * 4 + r][lane] = acc[mt][nb][r];
+    __syncthreads();
+
+    // accumulator element (mt, nb, lane, r) is token 16*mt + lane/4 + (r >= 2 ? 8 : 0),
+    // channel 8*nb + 2*(lane%4) + (r & 1) of the block
+    constexpr int kOutBlocks = GATED ? 1 : NB;
+    for (int i = threadIdx.x; i < MT16 * kOutBlocks * 4 * 32; i += kThreads) {
+        const int ln = i & 31, r = (i >> 5) & 3, rest = i >> 7;
+        const int nb = rest % kOutBlocks, mt = rest / kOutBlocks;
+        const int m = mt * 16 + (ln >> 2) + ((r & 2) ? 8 : 0);
+        const int n = n0 + nb * 8 + 2 * (ln & 3) + (r & 1);
+        if (m >= M || n >= N) continue;
+        float out;
+        if constexpr (GATED) {
+            float gs = 0.0f, us = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                gs += s_red[w][(mt * NB + 0) * 4 + r][ln];
+                us += s_red[w][(mt * NB + 1) * 4 + r][ln];
+            }
+            gs = gs * scales[n] + (bias ? bias[n] : 0.0f);
+            us = us * scales_up[n] + (bias_up ? bias_up[n] : 0.0f);
+            out = silu(gs) * us;
+        } else {
+            float s = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) s += s_red[w][(mt * NB + nb) * 4 + r][ln];
+            out = s * scales[n] + (bias ? bias[n] : 0.0f);
+            if (epilogue == SHREWQ_EPILOGUE_RELU) out = fmaxf(out, 0.0f);
+        }
+        const size_t off = (size_t)m * ldy + n;
+        put<YT>(y + off, out);
+        for (int d = 0; d < extra.n; ++d) put<YT>(static_cast<YT *>(extra.p[d]) + off, out);
+    }
+}
+
+template <int MT16, typename YT, bool GATED>
+void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
+    constexpr int kChan = GATED ? 8 : 8 * NB;
+    const unsigned grid = (unsigned)((a.N + kChan - 1) / kChan);
+    gemv_mma_kernel<MT16, YT, GATED><<<grid, kThreads, 0, ctx->stream>>>(
+        a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const __nv_bfloat16 *>(a.x),
+        static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
+}
+
+template <typename YT, bool GATED>
+void dispatch_m(shrewq_ctx *ctx, const ForwardArgs &a) {
+    if (a.M <= 16) launch_one<1, YT, GATED>(ctx, a);
+    else if (a.M <= 32) launch_one<2, YT, GATED>(ctx, a);
+    else launch_one<4, YT, GATED>(ctx, a);
+}
+
+}  // namespace
+
+bool gemv_mma_supported(const ForwardArgs &a) {
+    return a.x_dtype == SHREWQ_BF16 && a.M >= 1 && a.M <= 64 && a.K >= 64 && (a.K % 64) == 0 &&
+           (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0 &&
+           (!a.q_up || (reinterpret_cast<uintptr_t>(a.q_up) & 15) == 0) && a.N <= 0x7FFFFFFF && a.K <= 0x7FFFFFFF;
+}
+
+int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a) {
+    if (a.M == 0 || a.N == 0) return SHREWQ_OK;
+    if (!gemv_mma_supported(a))
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "mma gemv: needs bf16 activations, M<=64, K a multiple of 64, 16-byte alignment");
+    const bool gated = a.q_up != nullptr;
+    if (a.y_dtype == SHREWQ_BF16) {
+        if (gated) dispatch_m<__nv_bfloat16, true>(ctx, a);
+        else dispatch_m<__nv_bfloat16, false>(ctx, a);
+    } else {
+        if (gated) dispatch_m<float, true>(ctx, a);
+        else dispatch_m<float, false>(ctx, a);
+    }
+    ctx->launches += 1;
+    SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+    return SHREWQ_OK;
+}
+
+}  // namespace shrewq

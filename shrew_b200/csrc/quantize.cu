@@ -322,7 +322,10 @@ int launch_quantize(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, i
         else if (vec && cols <= 2048) launch_rows_reg<256, 2>(ctx, w, rows, cols, q, scales);
         else if (vec && cols <= 4096) launch_rows_reg<256, 4>(ctx, w, rows, cols, q, scales);
         else if (vec && cols <= 8192) launch_rows_reg<256, 8>(ctx, w, rows, cols, q, scales);
-        else if (vec && cols <= 16384) launch_rows_reg<256, 16>(ctx, w, rows, cols, q, scales);
+        // 512 threads x 8 float4 rather than 256 x 16: 48 registers per thread instead of 80 keeps
+        // more rows resident per SM (the 256 x 16 tile measured 4.4 TB/s against 5.1-5.5 TB/s for
+        // the 8-float4 tiles)
+        else if (vec && cols <= 16384) launch_rows_reg<512, 8>(ctx, w, rows, cols, q, scales);
         else if (vec && cols <= 32768) launch_rows_reg<1024, 8>(ctx, w, rows, cols, q, scales);
         else {
             const unsigned grid = (unsigned)(rows < (size_t)ctx->sm_count * 32 ? rows : (size_t)ctx->sm_count * 32);
