@@ -247,6 +247,11 @@ struct SplitK {
     float *partials;         // [tile][split][TOK][128] f32, only when gridDim.z > 1
     unsigned int *counters;  // one per (n tile, token tile), zero between launches
     int rounds_per_split;    // pipeline rounds (KSUB sub-blocks each) per split
+    // Tile-list mode (n_tiles_total > 0): the grid is a 1-D list of output tiles starting at
+    // tile_begin in channel-major order, instead of the (channel tile, token tile) grid.
+    // Lets one forward be issued as two launches with different split counts.
+    int tile_begin;
+    int n_tiles_total;
 };
 
 struct Operands {
@@ -273,8 +278,14 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     int *s_is_last = reinterpret_cast<int *>(bar_area + 640);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kChan;
-    const int m0 = blockIdx.y * TOK;
+    int tile_x = blockIdx.x, tile_y = blockIdx.y;
+    if (sk.n_tiles_total > 0) {
+        const int tl = sk.tile_begin + (int)blockIdx.x;
+        tile_x = tl % sk.n_tiles_total;
+        tile_y = tl / sk.n_tiles_total;
+    }
+    const int n0 = tile_x * kChan;
+    const int m0 = tile_y * TOK;
     const int rounds_total = (K + kBlockK * KSUB - 1) / (kBlockK * KSUB);
     const int r_begin = blockIdx.z * sk.rounds_per_split;
     const int nr = min(rounds_total - r_begin, sk.rounds_per_split);  // >= 1 by construction of the grid
@@ -621,7 +632,43 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
         attr_set = true;
     }
     const LaunchPlan p = plan_launch<TOK, KSUB>(a, GATED ? 64 : 128, ctx->sm_count, allow_split);
-    SplitK sk{nullptr, nullptr, p.rounds_per_split};
+    SplitK sk{nullptr, nullptr, p.rounds_per_split, 0, 0};
+    Operands ops{a.scales, a.bias, a.scales_up, a.bias_up};
+    // SHREWQ_TC_TAILSPLIT=1 (built, NOT yet run on a GPU, off by default): when large tiles
+    // leave a short last wave, issue the full waves as one launch and the tiles of the last
+    // wave as a second launch split along K so that it also fills the SMs.
+    static const bool tail_split = getenv("SHREWQ_TC_TAILSPLIT") && atoi(getenv("SHREWQ_TC_TAILSPLIT")) != 0;
+    if (tail_split && !fixed_scratch && TOK >= 128 && p.splits == 1) {
+        const int tiles = p.n_tiles * p.m_tiles, rem = tiles % ctx->sm_count;
+        const int rounds = p.rounds_per_split;
+        int s_tail = rem > 0 ? ctx->sm_count / rem : 0;
+        if (s_tail > 4) s_tail = 4;
+        if (s_tail > rounds / 8) s_tail = rounds / 8;
+        if (tiles > ctx->sm_count && rem > 0 && s_tail >= 2) {
+            const size_t part_bytes = (size_t)rem * s_tail * TOK * kTileN * sizeof(float);
+            if ((rc = ensure_scratch(ctx, kScratchPartialOff + part_bytes)) != SHREWQ_OK) return rc;
+            if (!ctx->counters_zeroed) {
+                SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(static_cast<char *>(ctx->scratch) + kScratchCounterOff, 0,
+                                                     kScratchPartialOff - kScratchCounterOff, ctx->stream));
+                ctx->counters_zeroed = true;
+            }
+            SplitK head{nullptr, nullptr, rounds, 0, p.n_tiles};
+            kern<<<dim3((unsigned)(tiles - rem), 1, 1), 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(
+                tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, head,
+                ctx->dev_status);
+            const int rps = (rounds + s_tail - 1) / s_tail;
+            const int splits = (rounds + rps - 1) / rps;
+            SplitK tail{reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + kScratchPartialOff),
+                        reinterpret_cast<unsigned int *>(static_cast<char *>(ctx->scratch) + kScratchCounterOff), rps,
+                        tiles - rem, p.n_tiles};
+            kern<<<dim3((unsigned)rem, 1, (unsigned)splits), 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(
+                tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, tail,
+                ctx->dev_status);
+            ctx->launches += 2;
+            SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+            return SHREWQ_OK;
+        }
+    }
     if (p.splits > 1) {
         const size_t tiles = (size_t)p.n_tiles * p.m_tiles;
         const size_t part_bytes = tiles * p.splits * TOK * kTileN * sizeof(float);
@@ -649,7 +696,6 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
             sk.partials = reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + kScratchPartialOff);
         }
     }
-    Operands ops{a.scales, a.bias, a.scales_up, a.bias_up};
     dim3 grid((unsigned)p.n_tiles, (unsigned)p.m_tiles, (unsigned)p.splits);
     kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M,
                                                                 (int)a.N, (int)a.K, a.ldy, a.epilogue, sk,
