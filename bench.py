@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 A "step" is one pass of the hot path over one batch of synthetic input.  The default
-workload is the Llama-7B-shaped MLP block of BASELINE.json (4096 -> 11008 gate/up with
+workload is the Llama-7B-shaped MLP block of the benchmark configs (4096 -> 11008 gate/up with
 SiLU, 11008 -> 4096 down, INT8 per-channel weights ~N(0,0.02), bf16 activations ~N(0,1),
 batch 512), output channels sharded over the N GPUs with an all-gather after each of the
 two sharded layers.  Metric: tokens/s (rows of the batch per second) for the whole job.

@@ -84,7 +84,7 @@ def shard_quantized_linear(weight: torch.Tensor, bias: Optional[torch.Tensor], c
     """Quantizes this rank's rows of `weight` [N,K] on its GPU and wraps the shard.
     Per-tensor granularity needs the whole tensor's amax, so every rank first takes the
     max over ranks of its local amax (one scalar all-reduce) — equivalently, quantize
-    before sharding; here the per-channel case (all BASELINE multi-GPU configs) is direct."""
+    before sharding; here the per-channel case (what the sharded benchmark configs use) is direct."""
     from .quantize import Linear, QuantGranularity, QuantizedLinear
     if config.granularity is not QuantGranularity.PerChannel and dist.is_initialized() and dist.get_world_size(group) > 1:
         raise NotImplementedError("sharded per-tensor quantization: quantize the full tensor first, then shard the codes")

@@ -154,7 +154,7 @@ def test_simt_parity(oracle, M, N, K, dtype):
     _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16 if dtype == "bf16" else TOL_F32, relu=(N == 256), force="simt")
 
 
-# ---- BASELINE configs at reduced or full size -------------------------------------------------------------
+# ---- the benchmark configurations at reduced or full size -------------------------------------------------------------
 def test_config1_mlp_784_256_10(oracle):
     # INT8 per-channel MLP 784 -> 256 -> 10 (ReLU), weights N(0,0.05) seed 0, batch 64 U(0,1)
     from shrew_b200 import _lib
