@@ -44,6 +44,8 @@ int ensure_scratch(shrewq_ctx *ctx, size_t bytes) {
     return rc;
 }
 
+int ensure_xsplit(shrewq_ctx *ctx, size_t bytes) { return grow(ctx, &ctx->xsplit, &ctx->xsplit_bytes, bytes, false); }
+
 int ensure_stage(shrewq_ctx *ctx, size_t dev_bytes, size_t pinned_bytes) {
     int rc = grow(ctx, &ctx->stage_dev, &ctx->stage_dev_bytes, dev_bytes, false);
     if (rc != SHREWQ_OK) return rc;
@@ -58,7 +60,7 @@ static int bind(shrewq_ctx *ctx) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma };
+enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceTcF32 };
 
 }  // namespace shrewq
 
@@ -133,6 +135,7 @@ void shrewq_ctx_destroy(shrewq_ctx *ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage_dev) cudaFree(ctx->stage_dev);
+    if (ctx->xsplit) cudaFree(ctx->xsplit);
     if (ctx->stage_pinned) cudaFreeHost(ctx->stage_pinned);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     delete ctx;
@@ -148,6 +151,7 @@ int shrewq_force_kernel(const char *name) {
     else if (!strcmp(name, "tcgen05")) g_forced_kernel = kForceTc;
     else if (!strcmp(name, "simt")) g_forced_kernel = kForceSimt;
     else if (!strcmp(name, "mma")) g_forced_kernel = kForceMma;
+    else if (!strcmp(name, "tcgen05-f32")) g_forced_kernel = kForceTcF32;
     else return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "force_kernel: unknown kernel '%s'", name);
     return SHREWQ_OK;
 }
@@ -271,6 +275,36 @@ size_t shrewq_linear_out_features(const shrewq_linear *lin) { return lin ? lin->
 size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin) { return lin ? lin->n * lin->k * 4 - lin->n * lin->k : 0; }
 const char *shrewq_linear_last_kernel(const shrewq_linear *lin) { return lin ? lin->last_kernel : "none"; }
 
+// f32 activations on the tensor cores: x is split into bf16 hi + lo (exact to ~2^-17), the
+// hi pass writes scale*acc to the f32 output, the lo pass adds its own scale*acc, the bias and
+// the elementwise op on top.  Two passes over the codes instead of one, but on the tensor
+// pipe instead of f32 FMAs.  Built and compiled, NOT yet run on a GPU: reachable only with
+// shrewq_force_kernel("tcgen05-f32"); the automatic choice for f32 stays the general f32 kernel.
+static int forward_f32_on_tensor_cores(shrewq_linear *lin, const ForwardArgs &orig, const char *who) {
+    shrewq_ctx *ctx = lin->ctx;
+    const size_t n = orig.M * orig.K, half = align_up(n * 2, 256);
+    int rc = ensure_xsplit(ctx, 2 * half);
+    if (rc != SHREWQ_OK) return rc;
+    char *hi = static_cast<char *>(ctx->xsplit), *lo = hi + half;
+    if ((rc = launch_split_f32(ctx, static_cast<const float *>(orig.x), n, hi, lo)) != SHREWQ_OK) return rc;
+    ForwardArgs a = orig;
+    a.x_dtype = SHREWQ_BF16;
+    a.x = hi;
+    a.bias = nullptr;
+    a.epilogue = SHREWQ_EPILOGUE_NONE;
+    Dests none = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0};
+    a.extra = none;  // peers receive the final values from the second pass only
+    if (!tcgen05_supported(a)) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05 cannot take this shape", who);
+    if ((rc = launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr)) != SHREWQ_OK) return rc;
+    a.x = lo;
+    a.bias = orig.bias;
+    a.epilogue = orig.epilogue | kEpilogueAccumulate;
+    a.extra = orig.extra;
+    rc = launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
+    lin->last_kernel = "tcgen05";
+    return rc;
+}
+
 static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev, int x_dtype, size_t M, void *y_dev,
                         int y_dtype, size_t ldy, int epilogue, const char *who, void *const *peers = nullptr,
                         int n_peers = 0) {
@@ -316,6 +350,10 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
         case kForceGemv:
             if (!gemv_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced gemv cannot take this shape", who);
             choice = kForceGemv; break;
+        case kForceTcF32:
+            if (x_dtype == SHREWQ_F32 && y_dtype == SHREWQ_F32 && !up && lin->tmap_ok)
+                return forward_f32_on_tensor_cores(lin, a, who);
+            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05-f32 needs f32 activations and output, no gate/up pair", who);
         case kForceTc:
             if (!tc_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05 cannot take this shape/dtype", who);
             choice = kForceTc; break;

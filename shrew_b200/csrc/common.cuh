@@ -42,6 +42,9 @@ struct shrewq_ctx {
     size_t stage_dev_bytes = 0;
     void *stage_pinned = nullptr;
     size_t stage_pinned_bytes = 0;
+    // bf16 hi/lo split of f32 activations (tensor-core route for f32 inputs)
+    void *xsplit = nullptr;
+    size_t xsplit_bytes = 0;
     // device status block + pinned mirror
     shrewq::DeviceStatus *dev_status = nullptr;
 };
@@ -81,6 +84,12 @@ int launch_quantize(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, i
 int launch_dequantize(shrewq_ctx *ctx, const int8_t *q, const double *scales, size_t rows,
                       size_t cols, int granularity, int out_dtype, void *out);
 int launch_scales_to_f32(shrewq_ctx *ctx, const double *scales, int granularity, size_t n, float *out);
+int launch_split_f32(shrewq_ctx *ctx, const float *x, size_t n, void *hi_bf16, void *lo_bf16);
+int ensure_xsplit(shrewq_ctx *ctx, size_t bytes);
+
+// internal epilogue flag (above the public SHREWQ_EPILOGUE_* values): add the f32 value already
+// stored at the output position before the elementwise op
+constexpr int kEpilogueAccumulate = 0x100;
 
 // Extra destinations of a forward: the same output slice is also stored into these buffers
 // (peer GPUs' memory, mapped into this process) — the all-gather fused into the epilogue.

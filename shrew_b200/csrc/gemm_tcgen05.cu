@@ -219,6 +219,9 @@ __device__ __forceinline__ void store_out<float>(float *p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
+__device__ __forceinline__ float load_prev(const float *p) { return *p; }
+__device__ __forceinline__ float load_prev(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+
 template <typename YT>
 __device__ __forceinline__ void store_all(YT *y, const Dests &extra, size_t off, float v) {
     store_out<YT>(y + off, v);
@@ -464,7 +467,8 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                     for (int i = 0; i < 16; ++i) {
                         const int m = m0 + c * 16 + i;
                         float o = __uint_as_float(r[i]) * sc + bs;
-                        if (epilogue == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
+                        if ((epilogue & kEpilogueAccumulate) && n_ok && m < M) o += load_prev(y + (size_t)m * ldy + n);
+                        if ((epilogue & 0xFF) == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
                         if (n_ok && m < M) store_all<YT>(y, extra, (size_t)m * ldy + n, o);
                     }
                 }
@@ -512,8 +516,9 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                             if constexpr (GATED) {
                                 const float u = acc2 * (n_ok ? ops.scales2[n] : 0.0f) + ((n_ok && ops.bias2) ? ops.bias2[n] : 0.0f);
                                 o = silu_f(o) * u;
-                            } else if (epilogue == SHREWQ_EPILOGUE_RELU) {
-                                o = fmaxf(o, 0.0f);
+                            } else {
+                                if ((epilogue & kEpilogueAccumulate) && n_ok && m < M) o += load_prev(y + (size_t)m * ldy + n);
+                                if ((epilogue & 0xFF) == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
                             }
                             if (n_ok && m < M) store_all<YT>(y, extra, (size_t)m * ldy + n, o);
                         }
@@ -626,10 +631,10 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
                        CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SHREWQ_OK) return rc;
     auto kern = linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT>;
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
+    static bool attr_set[64] = {false};  // per instantiation and per device (the attribute is per device)
+    if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
         SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemRequest));
-        attr_set = true;
+        if (ctx->device >= 0 && ctx->device < 64) attr_set[ctx->device] = true;
     }
     const LaunchPlan p = plan_launch<TOK, KSUB>(a, GATED ? 64 : 128, ctx->sm_count, allow_split);
     SplitK sk{nullptr, nullptr, p.rounds_per_split, 0, 0};

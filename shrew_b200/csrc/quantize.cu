@@ -297,6 +297,20 @@ __global__ void scales_to_f32_kernel(const double *__restrict__ scales, int per_
     if (i < n) out[i] = (float)(per_channel ? scales[i] : scales[0]);
 }
 
+// x = hi + lo with hi = bf16(x), lo = bf16(x - hi): two bf16 matrices whose sum carries ~16
+// significand bits of the f32 activations (relative error ~2^-17), so two tensor-core passes
+// over exact bf16 x int8 products stay inside the 1e-4 tolerance of the f32 path.
+__global__ void __launch_bounds__(256)
+split_f32_kernel(const float *__restrict__ x, size_t n, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = x[i];
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        hi[i] = h;
+        lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+    }
+}
+
 template <int GROUP, int NV>
 void launch_rows_reg(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, int8_t *q, double *scales) {
     constexpr int THREADS = GROUP >= 256 ? GROUP : 256;
@@ -373,6 +387,17 @@ int launch_dequantize(shrewq_ctx *ctx, const int8_t *q, const double *scales, si
     else
         dequantize_kernel<uint16_t><<<grid, 256, 0, ctx->stream>>>(q, scales, rows, cols, per_channel,
                                                                     static_cast<uint16_t *>(out), vec_ok);
+    ctx->launches += 1;
+    SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+    return SHREWQ_OK;
+}
+
+int launch_split_f32(shrewq_ctx *ctx, const float *x, size_t n, void *hi_bf16, void *lo_bf16) {
+    if (n == 0) return SHREWQ_OK;
+    size_t want = (n + 255) / 256;
+    const size_t cap = (size_t)ctx->sm_count * 32;
+    split_f32_kernel<<<(unsigned)(want > cap ? cap : want), 256, 0, ctx->stream>>>(
+        x, n, static_cast<__nv_bfloat16 *>(hi_bf16), static_cast<__nv_bfloat16 *>(lo_bf16));
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;

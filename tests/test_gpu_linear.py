@@ -46,7 +46,7 @@ def _check(oracle, ql, x_t, x_np, b, gran, tol, relu=False, force=None):
     y = ql.forward(x_t, epilogue=_lib.EPILOGUE_RELU if relu else _lib.EPILOGUE_NONE)
     Device.get(x_t.device).synchronize()
     if force:
-        assert ql.last_kernel() == force
+        assert ql.last_kernel() == force.split("-")[0]
     q = ql.weight_q.data.cpu().numpy().reshape(ql.out_features, ql.in_features)
     s = ql.weight_q.scales.cpu().numpy()
     small = x_np.shape[0] * q.size <= 1 << 22
@@ -278,3 +278,12 @@ def test_mma_gated_parity(oracle):
     g_ref, u_ref = fwd(gate), fwd(up)
     h_ref = (g_ref / (1.0 + np.exp(-g_ref.astype(np.float64)))).astype(np.float32) * u_ref
     assert oracle.rel_err(h.float().cpu().numpy(), h_ref) < TOL_BF16
+
+
+@_UNVALIDATED
+@pytest.mark.parametrize("M,N,K", [(64, 256, 784), (300, 1000, 1024), (4096, 1024, 256)])
+def test_f32_activations_on_tensor_cores(oracle, M, N, K):
+    # f32 path tolerance (1e-4) through the bf16 hi/lo split
+    ql, w, b = _make(N, K, 1, seed=N + K)
+    x_t, x_np = _x(M, K, "f32", uniform=True)
+    _check(oracle, ql, x_t, x_np, b, 1, TOL_F32, relu=True, force="tcgen05-f32")
