@@ -123,3 +123,46 @@ def test_forward_c_loop_equals_blas_twin(oracle):
         y_c = oracle.linear_forward_f32(q, s, gran, b, x, relu=True)
         y_np = oracle.np_linear_forward(q, s, gran, b, x, relu=True)
         assert oracle.rel_err(y_c, y_np) < 1e-6
+
+
+def test_committed_golden_file_matches_its_generator(tmp_path, monkeypatch):
+    # the fixture is exactly what tests/golden/make_golden.py produces
+    import importlib.util
+    import json
+    import os
+    from tests.conftest import ROOT
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(ROOT, "tests", "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = tmp_path / "quantize_golden.json"
+    monkeypatch.setattr(mod.os.path, "dirname", lambda p: str(tmp_path))
+    mod.main()
+    fresh = json.load(open(out))
+    committed = json.load(open(os.path.join(ROOT, "tests", "golden", "quantize_golden.json")))
+    assert fresh == committed
+
+
+def test_oracle_property_random_shapes_and_specials(oracle):
+    # C oracle == numpy twin over random shapes, scales and injected special values
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=60, deadline=None)
+    @given(rows=st.integers(1, 9), cols=st.integers(0, 40), gran=st.integers(0, 1),
+           log_scale=st.floats(-35, 35), seed=st.integers(0, 2 ** 31 - 1),
+           special=st.sampled_from([None, np.nan, np.inf, -np.inf, 0.0, -0.0]))
+    def check(rows, cols, gran, log_scale, seed, special):
+        rng = np.random.default_rng(seed)
+        with np.errstate(over="ignore"):
+            w = (rng.standard_normal((rows, cols)) * 10.0 ** log_scale).astype(np.float32)
+        if special is not None and w.size:
+            w.reshape(-1)[rng.integers(0, w.size)] = special
+        qc, sc = oracle.quantize_f32(w, gran)
+        qn, sn = oracle.np_quantize_f32(w, gran)
+        np.testing.assert_array_equal(qc, qn)
+        assert sc.tobytes() == sn.tobytes()
+        assert np.abs(qc.astype(np.int32)).max(initial=0) <= 127
+        d32 = oracle.dequantize(qc, sc, gran, "f32")
+        with np.errstate(over="ignore", invalid="ignore"):
+            np.testing.assert_array_equal(d32, oracle.np_dequantize_f64(qc, sc, gran).astype(np.float32))
+
+    check()
