@@ -15,7 +15,8 @@ PER_TENSOR, PER_CHANNEL = 0, 1
 F32, BF16 = 0, 1
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libshrewq.so")
+# SHREWQ_LIB points at another build of the same library (e.g. the tracing build)
+LIB_PATH = os.environ.get("SHREWQ_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libshrewq.so")
 
 # every symbol include/shrewq.h declares, with (restype, argtypes)
 _vp, _sz, _ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int

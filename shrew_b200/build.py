@@ -1,6 +1,6 @@
 """Builds libshrewq.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-    python -m shrew_b200.build [--force] [--verbose]
+    python -m shrew_b200.build [--force] [--verbose] [--trace]
 
 nvcc cross-compiles without a GPU.  The shared object lands beside this file so that it
 travels with the source tree; nothing is written outside the package directory.
@@ -29,15 +29,23 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    objdir = os.path.join(CSRC, "build")
+def build_library(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """trace=True builds libshrewq_trace.so: the same library with -DSHREWQ_TRACE, whose
+    tcgen05 kernel stamps clock64() per pipeline role and stage (see kernel_bench trace)."""
+    if trace:
+        return _build(os.path.join(CSRC, "build_trace"), os.path.join(HERE, "libshrewq_trace.so"),
+                      FLAGS + ["-DSHREWQ_TRACE"], force, verbose)
+    return _build(os.path.join(CSRC, "build"), LIB, FLAGS, force, verbose)
+
+
+def _build(objdir: str, lib: str, flags: list[str], force: bool, verbose: bool) -> str:
     os.makedirs(objdir, exist_ok=True)
     jobs = []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
         o = os.path.join(objdir, src.replace(".cu", ".o"))
         if force or _stale(o, [s] + HEADERS):
-            cmd = [NVCC, *FLAGS, "-c", s, "-o", o]
+            cmd = [NVCC, *flags, "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)
@@ -52,10 +60,10 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 1) or 1) as ex:
         list(ex.map(run, jobs))
     objs = [os.path.join(objdir, s.replace(".cu", ".o")) for s in SOURCES]
-    if force or jobs or _stale(LIB, objs):
-        run([NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs, "-cudart", "static"])
-    return LIB
+    if force or jobs or _stale(lib, objs):
+        run([NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib, *objs, "-cudart", "static"])
+    return lib
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

@@ -4,6 +4,8 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     python -m shrew_b200.kernel_bench quant      # quantize / dequantize bandwidth sweep
     python -m shrew_b200.kernel_bench lin        # forward kernels over a batch sweep
     python -m shrew_b200.kernel_bench lin 4096 4096 1,16,256   # one layer shape, chosen batches
+    python -m shrew_b200.build --trace && SHREWQ_LIB=shrew_b200/libshrewq_trace.so \
+        python -m shrew_b200.kernel_bench trace 4096 4096 16,1024  # in-kernel cycle trace of CTA 0
 
 Prints one JSON object per measurement: microseconds per launch, algorithmic GB/s and
 TFLOP/s.  Algorithmic bytes: quantize 5 B/element + 8 B/row; forward N*K + 4*N +
@@ -102,10 +104,42 @@ def bench_lin(shapes, batches):
         del lins
 
 
+def bench_trace(N, K, batches):
+    """clock64() stamps of CTA (0,0,0) of the tcgen05 kernel, per role and pipeline stage:
+    producer [wait empty, got it, TMA issued], converter [wait full, got it, converted,
+    arrived], MMA issuer [loop top, -, barrier passed, committed].  Needs the tracing build
+    of the library (SHREWQ_LIB).  Prints cycles relative to the producer's first stamp."""
+    import ctypes
+    L = _lib.lib()
+    if not hasattr(L, "shrewq_debug_set_trace"):
+        raise SystemExit("trace: load the tracing build (python -m shrew_b200.build --trace; SHREWQ_LIB=...)")
+    L.shrewq_debug_set_trace.argtypes = [ctypes.c_void_p]
+    lin = _layers(N, K, 1)[0]
+    L.shrewq_force_kernel(b"tcgen05")
+    for M in batches:
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        buf = torch.zeros(4 * 256 * 4, dtype=torch.int64, device="cuda")
+        lin.forward(x)
+        torch.cuda.synchronize()
+        L.shrewq_debug_set_trace(ctypes.c_void_p(buf.data_ptr()))
+        lin.forward(x)
+        Device.get("cuda:0").synchronize()
+        L.shrewq_debug_set_trace(None)
+        t = buf.cpu().numpy().reshape(4, 256, 4)
+        t0 = t[0, 0, 0]
+        stages = int((t[1, :, 3] != 0).sum())
+        for i in range(stages):
+            print(json.dumps(dict(M=M, stage=i, producer=(t[0, i, :3] - t0).tolist(), converter=(t[2, i] - t0).tolist(),
+                                  mma=(t[1, i, [0, 2, 3]] - t0).tolist())), flush=True)
+    L.shrewq_force_kernel(b"auto")
+
+
 def main(argv):
     which = argv[1] if len(argv) > 1 else "lin"
     if which == "quant":
         bench_quant()
+    elif which == "trace":
+        bench_trace(int(argv[2]), int(argv[3]), [int(b) for b in argv[4].split(",")])
     else:
         shapes = [(4096, 4096), (11008, 4096), (4096, 11008)]
         batches = [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 4096]
