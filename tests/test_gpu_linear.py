@@ -287,3 +287,14 @@ def test_f32_activations_on_tensor_cores(oracle, M, N, K):
     ql, w, b = _make(N, K, 1, seed=N + K)
     x_t, x_np = _x(M, K, "f32", uniform=True)
     _check(oracle, ql, x_t, x_np, b, 1, TOL_F32, relu=True, force="tcgen05-f32")
+
+
+@_UNVALIDATED
+@pytest.mark.parametrize("N,K,dtype", [(256, 256, "f32"), (1024, 256, "f32"), (256, 1024, "f32"), (50257, 256, "f32"),
+                                       (50257, 256, "bf16"), (1024, 256, "bf16")])
+def test_config2_tinygpt_shaped_linears(oracle, N, K, dtype):
+    # the Linear shapes of the TinyGPT-shaped stack (d_model 256, d_ff 1024, vocab 50257) at
+    # 512 of its 4096 token rows; the vocabulary head has a ragged last channel tile
+    ql, w, b = _make(N, K, 1, seed=N + K, bias=(N != 50257))
+    x_t, x_np = _x(512, K, dtype, seed=7)
+    _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16 if dtype == "bf16" else TOL_F32)

@@ -52,6 +52,28 @@ def _worker(rank, world, port, q):
                 yf = fl.forward(x)
                 torch.cuda.synchronize()
                 res[f"fused_{M}_{it}"] = oracle.rel_err(yf.float().cpu().numpy(), ref)
+        if os.environ.get("SHREWQ_TEST_UNVALIDATED", "0") == "1":
+            # the gated MLP block with both exchanges fused (not yet validated against the oracle)
+            from shrew_b200.sharded import FusedShardedGatedMLP
+            dm, dff, M = 512, 1408, 96
+            ws = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in ((dff, dm), (dff, dm), (dm, dff))]
+            x = torch.from_numpy(rng.standard_normal((M, dm)).astype(np.float32)).to(dev).to(torch.bfloat16)
+            shards = []
+            for wfull in ws:
+                n0, n1 = plan_shards(wfull.shape[0], world).rows(rank)
+                shards.append(QuantizedLinear.from_linear(Linear(torch.from_numpy(wfull[n0:n1].copy()).to(dev), None),
+                                                          QuantConfig.int8_per_channel()))
+            mlp = FusedShardedGatedMLP(shards[0], shards[1], shards[2], dff, dm, 128)
+            y = mlp.forward(x)
+            torch.cuda.synchronize()
+            qs = [oracle.quantize_f32(wfull, oracle.PER_CHANNEL) for wfull in ws]
+            xn = x.float().cpu().numpy()
+            g = oracle.np_linear_forward(qs[0][0], qs[0][1], 1, None, xn)
+            u = oracle.np_linear_forward(qs[1][0], qs[1][1], 1, None, xn)
+            h = ((g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u)
+            h16 = torch.from_numpy(h).to(torch.bfloat16).float().numpy()
+            ref = oracle.np_linear_forward(qs[2][0], qs[2][1], 1, None, h16)
+            res["fused_mlp"] = oracle.rel_err(y.float().cpu().numpy(), ref)
         q.put((rank, res))
         dist.barrier()
     finally:
