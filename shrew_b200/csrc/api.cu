@@ -60,7 +60,7 @@ static int bind(shrewq_ctx *ctx) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceTcF32 };
+enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceTcF32, kForceTc2Cta };
 
 }  // namespace shrewq
 
@@ -152,6 +152,7 @@ int shrewq_force_kernel(const char *name) {
     else if (!strcmp(name, "simt")) g_forced_kernel = kForceSimt;
     else if (!strcmp(name, "mma")) g_forced_kernel = kForceMma;
     else if (!strcmp(name, "tcgen05-f32")) g_forced_kernel = kForceTcF32;
+    else if (!strcmp(name, "tcgen05-2cta")) g_forced_kernel = kForceTc2Cta;
     else return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "force_kernel: unknown kernel '%s'", name);
     return SHREWQ_OK;
 }
@@ -350,6 +351,11 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
         case kForceGemv:
             if (!gemv_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced gemv cannot take this shape", who);
             choice = kForceGemv; break;
+        case kForceTc2Cta:
+            if (!tc_ok || up) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05-2cta cannot take this shape/dtype", who);
+            rc = launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap);
+            lin->last_kernel = "tcgen05";
+            return rc;
         case kForceTcF32:
             if (x_dtype == SHREWQ_F32 && y_dtype == SHREWQ_F32 && !up && lin->tmap_ok)
                 return forward_f32_on_tensor_cores(lin, a, who);

@@ -298,3 +298,11 @@ def test_config2_tinygpt_shaped_linears(oracle, N, K, dtype):
     ql, w, b = _make(N, K, 1, seed=N + K, bias=(N != 50257))
     x_t, x_np = _x(512, K, dtype, seed=7)
     _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16 if dtype == "bf16" else TOL_F32)
+
+
+@_UNVALIDATED
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (256, 512, 1024), (300, 1000, 1040), (1024, 4096, 4096)])
+def test_cta_pair_kernel_parity(oracle, M, N, K):
+    ql, w, b = _make(N, K, 1, seed=N + K)
+    x_t, x_np = _x(M, K, "bf16", seed=M)
+    _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, force="tcgen05-2cta")
