@@ -23,7 +23,7 @@
 // Warp roles: warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer, then G groups of
 // 4 converter warps (one TMEM lane quadrant each) which also run the epilogue.  A pipeline
 // stage holds KSUB sub-blocks of 64 k: full[s] (TMA bytes landed) -> converters (group g
-// takes stages g, g+G, ...) -> aready[s] -> MMA (4*KSUB instructions, one commit) ->
+// owns the stages s with s % G == g) -> aready[s] -> MMA (4*KSUB instructions, one commit) ->
 // empty[s] -> producer.  One barrier round trip per stage costs the single MMA-issuing
 // thread ~400 cycles, so small token tiles (short MMAs) use more sub-blocks per stage.
 // Every wait is bounded: after the limit the waiter records where it gave up in a status
@@ -391,8 +391,12 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const int swz = (row >> 1) & 3;
         bool ok = true;
-        for (int i = group; i < nr && ok; i += G) {
+        // A group owns pipeline STAGES (stage s belongs to group s % G), not every G-th round: its
+        // warps then pass through every phase of the barriers they poll, so a parity wait can never
+        // mistake phase k-2 for phase k, whatever order the TMA loads complete in.
+        for (int i = 0; i < nr && ok; ++i) {
             const int s = i % C::kStages;
+            if (s % G != group) continue;
             const uint32_t ph = (i / C::kStages) & 1;
             if (((warp - 2) & 3) == 0) TRACE(2, i, 0);
             ok = mbar_wait_warp(bars_u32 + kFullBar + s * 8, ph, ctl, status, 3, s);

@@ -337,8 +337,11 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
         const int swz = (row >> 1) & 3;
         const uint32_t aready_leader = map_to_cta(bars_u32 + kAready, 0);
         bool ok = true;
-        for (int i = group; i < rounds && ok; i += kGroups) {
+        // a group owns pipeline stages (s % kGroups), so that it passes through every phase of the
+        // barriers it polls and a parity wait stays unambiguous under any TMA completion order
+        for (int i = 0; i < rounds && ok; ++i) {
             const int s = i % kStages;
+            if (s % kGroups != group) continue;
             const uint32_t ph = (i / kStages) & 1;
             ok = mbar_wait_warp(bars_u32 + kWFull + s * 8, ph, ctl, status, 3, s);
             if (!ok) break;
