@@ -197,8 +197,10 @@ SHREWQ_API const char *shrewq_linear_last_kernel(const shrewq_linear *lin);
 /* Forces the kernel family used by forwards issued from the calling thread: "gemv",
  * "tcgen05", "simt", or "auto"/NULL to restore the built-in choice.  Two further names select
  * kernels that are built but not yet validated on a GPU and are never chosen automatically:
- * "mma" (warp-level MMA for M <= 64), "tcgen05-f32" (f32 activations split into bf16 hi + lo
- * and run as two tensor-core passes) and "tcgen05-2cta" (CTA pairs, tcgen05.mma.cta_group::2).  A forced kernel that
+ * "mma" (warp-level MMA for M <= 64), "mma-f16" (the same with f16 operands: activations
+ * rescaled per token row by a power of two, codes widened in one instruction each),
+ * "tcgen05-f32" (f32 activations split into bf16 hi + lo and run as two tensor-core passes)
+ * and "tcgen05-2cta" (CTA pairs, tcgen05.mma.cta_group::2).  A forced kernel that
  * cannot take a shape makes the forward fail with SHREWQ_ERR_UNSUPPORTED (it never falls
  * back silently).  For tests and benchmarks; no counterpart in the reference. */
 SHREWQ_API int shrewq_force_kernel(const char *name);

@@ -60,7 +60,7 @@ static int bind(shrewq_ctx *ctx) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceTcF32, kForceTc2Cta };
+enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceMmaF16, kForceTcF32, kForceTc2Cta };
 
 }  // namespace shrewq
 
@@ -151,6 +151,7 @@ int shrewq_force_kernel(const char *name) {
     else if (!strcmp(name, "tcgen05")) g_forced_kernel = kForceTc;
     else if (!strcmp(name, "simt")) g_forced_kernel = kForceSimt;
     else if (!strcmp(name, "mma")) g_forced_kernel = kForceMma;
+    else if (!strcmp(name, "mma-f16")) g_forced_kernel = kForceMmaF16;
     else if (!strcmp(name, "tcgen05-f32")) g_forced_kernel = kForceTcF32;
     else if (!strcmp(name, "tcgen05-2cta")) g_forced_kernel = kForceTc2Cta;
     else return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "force_kernel: unknown kernel '%s'", name);
@@ -365,8 +366,9 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             choice = kForceTc; break;
         case kForceSimt: choice = kForceSimt; break;
         case kForceMma:
+        case kForceMmaF16:
             if (!gemv_mma_supported(a)) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced mma kernel cannot take this shape/dtype", who);
-            choice = kForceMma; break;
+            choice = g_forced_kernel; break;
         default:
             // CUDA-core GEMV keeps up with HBM only for a few tokens; beyond that the tensor
             // cores take over (bf16 activations), else the general f32 kernel.
@@ -376,7 +378,8 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
     }
     const char *name;
     if (choice == kForceGemv) { rc = launch_gemv(ctx, a); name = "gemv"; }
-    else if (choice == kForceMma) { rc = launch_gemv_mma(ctx, a); name = "mma"; }
+    else if (choice == kForceMma) { rc = launch_gemv_mma(ctx, a, false); name = "mma"; }
+    else if (choice == kForceMmaF16) { rc = launch_gemv_mma(ctx, a, true); name = "mma-f16"; }
     else if (choice == kForceTc) { rc = up ? launch_gemm_tcgen05(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
         name = "tcgen05"; }
     else {

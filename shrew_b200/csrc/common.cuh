@@ -119,7 +119,7 @@ struct ForwardArgs {
 int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a);
 int launch_gemm_simt(shrewq_ctx *ctx, const ForwardArgs &a);
 bool gemv_mma_supported(const ForwardArgs &a);
-int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a);
+int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a, bool f16);
 bool tcgen05_supported(const ForwardArgs &a);
 int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);
 int launch_gemm_tcgen05_2cta(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap);

@@ -21,6 +21,22 @@
 // 64 (a dot product does not care about the order of k).
 // A CTA of 8 warps owns 16 channels (8 when gated: a gate block and an up block); the warps
 // split K in 64-wide blocks and their accumulators are summed through shared memory.
+//
+// F16 variant ("mma-f16").  Widening a code to bf16 costs 2.5 instructions (byte-permute into
+// an f32 magic number, subtract, pack two f32 into bf16x2), which at batch 1-4 makes the
+// kernel issue-bound like the CUDA-core GEMV.  To f16 it costs 1: a byte-permute builds the
+// halves 0x6400 | u (= 1024 + u exactly, u = code + 128), one packed subtract of 1152 leaves
+// the code.  The MMA then needs f16 activations, and f16 has 5 exponent bits where bf16 has
+// 8, so a small kernel first rescales each token row by a power of two chosen from the row's
+// largest magnitude (2^14 <= amax * 2^s < 2^15) and converts it to f16.  A bf16 value has 8
+// significant bits and f16 keeps 11 down to 2^-14 (fewer below, none under 2^-24), so every
+// element within 2^-31 of the row's amax converts exactly; a smaller one is rounded with an
+// error of at most amax * 2^-39 (half an f16 subnormal step), so a dot product over K codes is
+// off by at most K * 127 * amax * 2^-39 in the rescaled row's units: for K = 16384 that is
+// 2^-18 * amax, below the f32 rounding of a sum whose terms reach 127 * amax.  The epilogue
+// multiplies the sum by 2^-s (ldexp).
+#include <cuda_fp16.h>
+
 #include <cstdlib>
 
 #include "common.cuh"
@@ -51,6 +67,53 @@ __device__ __forceinline__ void cvt_i8x4_bf16(uint32_t w, uint32_t &lo, uint32_t
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(f3), "f"(f2));
 }
 
+// 4 INT8 codes -> two packed f16x2 words, exactly: (1024 + (code + 128)) - 1152
+__device__ __forceinline__ void cvt_i8x4_f16(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    const uint32_t u = w ^ 0x80808080u;
+    const uint32_t h01 = __byte_perm(u, 0x64646464u, 0x4140);  // halves 0x64:u0, 0x64:u1
+    const uint32_t h23 = __byte_perm(u, 0x64646464u, 0x4342);
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(h01), "r"(0x64806480u));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(h23), "r"(0x64806480u));
+}
+
+// D[16x8] += A[16x16] * B[16x8], f16 operands, f32 accumulate
+__device__ __forceinline__ void mma_f16_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Token row m of bf16 activations -> f16 of x * 2^shift[m], shift[m] = 14 - floor(log2(amax of
+// the row)) (0 for an all-zero row; a row holding Inf uses the largest finite exponent; NaN
+// elements stay NaN and do not take part in amax).  One CTA per token row.
+__global__ void __launch_bounds__(256)
+x_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ x16, int *__restrict__ shift, int K) {
+    const __nv_bfloat16 *row = x + (size_t)blockIdx.x * K;
+    __half *out = x16 + (size_t)blockIdx.x * K;
+    float amax = 0.0f;
+    for (int k = threadIdx.x; k < K; k += 256) amax = fmaxf(amax, fabsf(__bfloat162float(row[k])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    __shared__ float s_max[8];
+    __shared__ int s_shift;
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = s_max[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) a = fmaxf(a, s_max[w]);
+        int e = 0;
+        if (a > 0.0f) e = isinf(a) ? 127 : ilogbf(a);
+        s_shift = 14 - e;
+        shift[blockIdx.x] = 14 - e;
+    }
+    __syncthreads();
+    const int sh = s_shift;
+    for (int k = threadIdx.x; k < K; k += 256) out[k] = __float2half_rn(ldexpf(__bfloat162float(row[k]), sh));
+}
+
 // D[16x8] += A[16x16] * B[16x8], bf16 operands, f32 accumulate
 __device__ __forceinline__ void mma_bf16_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -70,12 +133,13 @@ template <>
 __device__ __forceinline__ void put<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
 // MT16: token tiles of 16 (M <= 16*MT16).  K must be a multiple of 64.
-template <int MT16, typename YT, bool GATED>
+// F16: x holds f16 activations rescaled per token row by 2^xshift[m] (x_to_f16_kernel), else bf16.
+template <int MT16, typename YT, bool GATED, bool F16>
 __global__ void __launch_bounds__(kThreads)
 gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, const float *__restrict__ bias,
                 const int8_t *__restrict__ q_up, const float *__restrict__ scales_up,
-                const float *__restrict__ bias_up, const __nv_bfloat16 *__restrict__ x, YT *__restrict__ y,
-                Dests extra, int M, int N, int K, size_t ldy, int epilogue) {
+                const float *__restrict__ bias_up, const uint16_t *__restrict__ x, const int *__restrict__ xshift,
+                YT *__restrict__ y, Dests extra, int M, int N, int K, size_t ldy, int epilogue) {
     constexpr int kChan = GATED ? 8 : 8 * NB;  // output channels per CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -91,7 +155,7 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
         wrow[nb] = ((GATED && nb == 1) ? q_up : q) + (size_t)n * K + 16 * t;
     }
     // the activation rows this lane reads for each token tile (null = padding row)
-    const __nv_bfloat16 *xlo[MT16], *xhi[MT16];
+    const uint16_t *xlo[MT16], *xhi[MT16];
 #pragma unroll
     for (int mt = 0; mt < MT16; ++mt) {
         const int m = mt * 16 + g;
@@ -133,10 +197,15 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 uint32_t b0, b1;  // codes 4j,4j+1 | 4j+2,4j+3 of this lane's run
-                cvt_i8x4_bf16(w4[j], b0, b1);
+                if constexpr (F16) cvt_i8x4_f16(w4[j], b0, b1);
+                else cvt_i8x4_bf16(w4[j], b0, b1);
 #pragma unroll
-                for (int mt = 0; mt < MT16; ++mt)
-                    mma_bf16_16816(acc[mt][nb], al[mt][2 * j], ah[mt][2 * j], al[mt][2 * j + 1], ah[mt][2 * j + 1], b0, b1);
+                for (int mt = 0; mt < MT16; ++mt) {
+                    if constexpr (F16)
+                        mma_f16_16816(acc[mt][nb], al[mt][2 * j], ah[mt][2 * j], al[mt][2 * j + 1], ah[mt][2 * j + 1], b0, b1);
+                    else
+                        mma_bf16_16816(acc[mt][nb], al[mt][2 * j], ah[mt][2 * j], al[mt][2 * j + 1], ah[mt][2 * j + 1], b0, b1);
+                }
             }
         }
     }
@@ -161,6 +230,7 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
         const int n = n0 + nb * 8 + 2 * (ln & 3) + (r & 1);
         if (m >= M || n >= N) continue;
         float out;
+        const int back = F16 ? -xshift[m] : 0;  // undo the row's power-of-two rescale
         if constexpr (GATED) {
             float gs = 0.0f, us = 0.0f;
 #pragma unroll
@@ -168,6 +238,7 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
                 gs += s_red[w][(mt * NB + 0) * 4 + r][ln];
                 us += s_red[w][(mt * NB + 1) * 4 + r][ln];
             }
+            if constexpr (F16) { gs = ldexpf(gs, back); us = ldexpf(us, back); }
             gs = gs * scales[n] + (bias ? bias[n] : 0.0f);
             us = us * scales_up[n] + (bias_up ? bias_up[n] : 0.0f);
             out = silu(gs) * us;
@@ -175,6 +246,7 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
             float s = 0.0f;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) s += s_red[w][(mt * NB + nb) * 4 + r][ln];
+            if constexpr (F16) s = ldexpf(s, back);
             out = s * scales[n] + (bias ? bias[n] : 0.0f);
             if (epilogue == SHREWQ_EPILOGUE_RELU) out = fmaxf(out, 0.0f);
         }
@@ -184,20 +256,32 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
     }
 }
 
-template <int MT16, typename YT, bool GATED>
-void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
+template <int MT16, typename YT, bool GATED, bool F16>
+void launch_one(shrewq_ctx *ctx, const ForwardArgs &a, const void *x, const int *xshift) {
     constexpr int kChan = GATED ? 8 : 8 * NB;
     const unsigned grid = (unsigned)((a.N + kChan - 1) / kChan);
-    gemv_mma_kernel<MT16, YT, GATED><<<grid, kThreads, 0, ctx->stream>>>(
-        a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const __nv_bfloat16 *>(a.x),
+    gemv_mma_kernel<MT16, YT, GATED, F16><<<grid, kThreads, 0, ctx->stream>>>(
+        a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const uint16_t *>(x), xshift,
         static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
 }
 
-template <typename YT, bool GATED>
-void dispatch_m(shrewq_ctx *ctx, const ForwardArgs &a) {
-    if (a.M <= 16) launch_one<1, YT, GATED>(ctx, a);
-    else if (a.M <= 32) launch_one<2, YT, GATED>(ctx, a);
-    else launch_one<4, YT, GATED>(ctx, a);
+template <typename YT, bool GATED, bool F16>
+void dispatch_m(shrewq_ctx *ctx, const ForwardArgs &a, const void *x, const int *xshift) {
+    if (a.M <= 16) launch_one<1, YT, GATED, F16>(ctx, a, x, xshift);
+    else if (a.M <= 32) launch_one<2, YT, GATED, F16>(ctx, a, x, xshift);
+    else launch_one<4, YT, GATED, F16>(ctx, a, x, xshift);
+}
+
+template <bool F16>
+void dispatch_y(shrewq_ctx *ctx, const ForwardArgs &a, const void *x, const int *xshift) {
+    const bool gated = a.q_up != nullptr;
+    if (a.y_dtype == SHREWQ_BF16) {
+        if (gated) dispatch_m<__nv_bfloat16, true, F16>(ctx, a, x, xshift);
+        else dispatch_m<__nv_bfloat16, false, F16>(ctx, a, x, xshift);
+    } else {
+        if (gated) dispatch_m<float, true, F16>(ctx, a, x, xshift);
+        else dispatch_m<float, false, F16>(ctx, a, x, xshift);
+    }
 }
 
 }  // namespace
@@ -208,19 +292,25 @@ bool gemv_mma_supported(const ForwardArgs &a) {
            (!a.q_up || (reinterpret_cast<uintptr_t>(a.q_up) & 15) == 0) && a.N <= 0x7FFFFFFF && a.K <= 0x7FFFFFFF;
 }
 
-int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a) {
+int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a, bool f16) {
     if (a.M == 0 || a.N == 0) return SHREWQ_OK;
     if (!gemv_mma_supported(a))
         return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "mma gemv: needs bf16 activations, M<=64, K a multiple of 64, 16-byte alignment");
-    const bool gated = a.q_up != nullptr;
-    if (a.y_dtype == SHREWQ_BF16) {
-        if (gated) dispatch_m<__nv_bfloat16, true>(ctx, a);
-        else dispatch_m<__nv_bfloat16, false>(ctx, a);
+    if (f16) {
+        // [M,K] f16 activations, then M shift words (K % 64 == 0 keeps the words aligned)
+        const size_t xbytes = a.M * a.K * sizeof(__half);
+        int rc = ensure_xsplit(ctx, xbytes + a.M * sizeof(int));
+        if (rc != SHREWQ_OK) return rc;
+        __half *x16 = static_cast<__half *>(ctx->xsplit);
+        int *xshift = reinterpret_cast<int *>(static_cast<char *>(ctx->xsplit) + xbytes);
+        x_to_f16_kernel<<<(unsigned)a.M, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16 *>(a.x), x16, xshift,
+                                                                (int)a.K);
+        dispatch_y<true>(ctx, a, x16, xshift);
+        ctx->launches += 2;
     } else {
-        if (gated) dispatch_m<float, true>(ctx, a);
-        else dispatch_m<float, false>(ctx, a);
+        dispatch_y<false>(ctx, a, a.x, nullptr);
+        ctx->launches += 1;
     }
-    ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;
 }

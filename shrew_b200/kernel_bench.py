@@ -4,6 +4,7 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     python -m shrew_b200.kernel_bench quant      # quantize / dequantize bandwidth sweep
     python -m shrew_b200.kernel_bench lin        # forward kernels over a batch sweep
     python -m shrew_b200.kernel_bench lin 4096 4096 1,16,256   # one layer shape, chosen batches
+    SHREWQ_BENCH_KERNELS=gemv,mma,mma-f16,tcgen05 python -m shrew_b200.kernel_bench lin   # other kernel families
     python -m shrew_b200.build --trace && SHREWQ_LIB=shrew_b200/libshrewq_trace.so \
         python -m shrew_b200.kernel_bench trace 4096 4096 16,1024  # in-kernel cycle trace of CTA 0
 
@@ -13,6 +14,7 @@ M*K*2 + M*N*2 (bf16 activations and outputs)."""
 from __future__ import annotations
 
 import json
+import os
 import sys
 
 import torch
@@ -83,8 +85,8 @@ def bench_lin(shapes, batches):
         for M in batches:
             x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
             y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-            for force in ("gemv", "tcgen05"):
-                if force == "gemv" and M > 16:
+            for force in os.environ.get("SHREWQ_BENCH_KERNELS", "gemv,tcgen05").split(","):
+                if (force == "gemv" and M > 16) or (force.startswith("mma") and M > 64):
                     continue
                 L.shrewq_force_kernel(force.encode())
 
