@@ -614,9 +614,19 @@ LaunchPlan plan_launch(const ForwardArgs &a, int chan_per_tile, int sm_count, bo
     // tiles alone leave most SMs idle: as many splits as fit in one wave, >= 2 rounds each
     int splits = 1;
     const long tiles = (long)p.n_tiles * p.m_tiles;
-    if (allow_split && TOK <= 64 && tiles <= 1024) {
+    // SHREWQ_TC_SPLITK_MAXTOK=128|256 (NOT yet run on a GPU, default 64) extends the rule to the
+    // large token tiles, with at least 8 rounds per split: batches 65..256 on layers with few
+    // channel tiles (N = 4096: 32 tiles) otherwise run on a fraction of the SMs.  The kernel's
+    // split path is the same code for every tile width.
+    static const int max_tok = [] {
+        const char *e = getenv("SHREWQ_TC_SPLITK_MAXTOK");
+        const int v = e ? atoi(e) : 64;
+        return v < 64 ? 64 : v;
+    }();
+    const int min_rounds = TOK <= 64 ? 2 : 8;
+    if (allow_split && TOK <= max_tok && tiles <= 1024) {
         int want = (int)(sm_count / tiles);
-        if (want > rounds / 2) want = rounds / 2;
+        if (want > rounds / min_rounds) want = rounds / min_rounds;
         if (want > 1) splits = want;
     }
     p.rounds_per_split = (rounds + splits - 1) / splits;
