@@ -19,6 +19,10 @@
  *     here accumulates in f64 and rounds once, the centre of every valid f32 ordering;
  *     kernels are compared to it under a stated tolerance, never bit-exactly.
  *
+ *   - The *_ex functions restate the reference's other modes (asymmetric INT8, INT4 symmetric
+ *     and asymmetric, quantize.rs:124-139, :339-366) the same way; tests/test_oracle_modes.py
+ *     pins them.  They are ahead of the CUDA library, which implements INT8 symmetric only.
+ *
  * The reference cannot be compiled here (Rust, sibling crates absent), so there is no
  * oracle/_ref build of it.
  *
@@ -33,6 +37,8 @@
 
 #define SHREW_PER_TENSOR 0
 #define SHREW_PER_CHANNEL 1
+#define SHREW_SYMMETRIC 0
+#define SHREW_ASYMMETRIC 1
 
 /* Rust f64::round: round half away from zero (pinned by
  * crates/shrew/tests/nn_tests.rs:2413-2420).  C99 round() has the same definition. */
@@ -117,6 +123,78 @@ int shrew_oracle_quantize_f32(const float *w, size_t rows, size_t cols, int gran
         quantize_per_tensor_f64(data, n, q, scales);
     free(data);
     return 0;
+}
+
+/* ---- every mode: INT8 / INT4 codes (one per byte, as the reference stores them), symmetric or
+ * asymmetric.  qmax / qmin — quantize.rs:124-139. */
+static double qmax_of(int bits) { return bits == 4 ? 7.0 : 127.0; }
+static double qmin_of(int bits, int mode) {
+    if (bits == 4) return mode == SHREW_ASYMMETRIC ? -8.0 : -7.0;
+    return mode == SHREW_ASYMMETRIC ? -128.0 : -127.0;
+}
+
+/* compute_scale_zp, both branches — quantize.rs:339-366.  f64::min / f64::max return the other
+ * operand when one is NaN, which is fmin / fmax. */
+static void scale_zp_of(const double *data, size_t n, int bits, int mode, double *scale, double *zp) {
+    if (n == 0) { *scale = 1.0; *zp = 0.0; return; }
+    const double qmin = qmin_of(bits, mode), qmax = qmax_of(bits);
+    if (mode != SHREW_ASYMMETRIC) {
+        double amax = 0.0;
+        for (size_t i = 0; i < n; ++i) amax = max_ignore_nan(amax, fabs(data[i]));
+        *scale = amax < 1e-30 ? 1.0 : amax / qmax;
+        *zp = 0.0;
+        return;
+    }
+    double min_val = INFINITY, max_val = -INFINITY;
+    for (size_t i = 0; i < n; ++i) {
+        min_val = fmin(min_val, data[i]);
+        max_val = fmax(max_val, data[i]);
+    }
+    const double range = max_val - min_val;
+    *scale = range < 1e-30 ? 1.0 : range / (qmax - qmin);
+    *zp = round_half_away(qmin - min_val / *scale);
+}
+
+/* The element map with a zero point and the mode's clamp range — quantize.rs:244-250, :301-304.
+ * f64::clamp keeps a NaN, and NaN as i8 is 0. */
+static inline int8_t quantize_one_ex(double v, double inv_scale, double zp, double qmin, double qmax) {
+    double t = round_half_away(v * inv_scale + zp);
+    if (t != t) return 0;
+    return f64_as_i8(clamp_f64(t, qmin, qmax));
+}
+
+/* quantize_tensor for an F32 tensor in any mode — quantize.rs:194-205, :229-260, :270-318.
+ * scales and zero_points receive 1 (per-tensor) or `rows` (per-channel) values. */
+int shrew_oracle_quantize_f32_ex(const float *w, size_t rows, size_t cols, int granularity, int bits, int mode,
+                                 int8_t *q, double *scales, double *zero_points) {
+    size_t n = rows * cols;
+    double *data = (double *)malloc((n ? n : 1) * sizeof(double));
+    if (!data) return -1;
+    for (size_t i = 0; i < n; ++i) data[i] = (double)w[i];
+    const double qmin = qmin_of(bits, mode), qmax = qmax_of(bits);
+    const size_t groups = granularity == SHREW_PER_CHANNEL ? rows : 1;
+    const size_t len = granularity == SHREW_PER_CHANNEL ? cols : n;
+    for (size_t g = 0; g < groups; ++g) {
+        const double *src = data + g * len;
+        double scale, zp;
+        scale_zp_of(src, len, bits, mode, &scale, &zp);
+        const double inv = inv_scale_of(scale);
+        for (size_t i = 0; i < len; ++i) q[g * len + i] = quantize_one_ex(src[i], inv, zp, qmin, qmax);
+        scales[g] = scale;
+        zero_points[g] = zp;
+    }
+    free(data);
+    return 0;
+}
+
+/* dequantize with zero points — quantize.rs:262-266, :320-335: (q as f64 - zp) * scale. */
+void shrew_oracle_dequantize_f64_ex(const int8_t *q, const double *scales, const double *zero_points, size_t rows,
+                                    size_t cols, int granularity, double *out) {
+    for (size_t r = 0; r < rows; ++r) {
+        const double s = granularity == SHREW_PER_CHANNEL ? scales[r] : scales[0];
+        const double zp = granularity == SHREW_PER_CHANNEL ? zero_points[r] : zero_points[0];
+        for (size_t c = 0; c < cols; ++c) out[r * cols + c] = ((double)q[r * cols + c] - zp) * s;
+    }
 }
 
 /* dequantize_per_tensor / dequantize_per_channel — quantize.rs:262-266, :320-335:

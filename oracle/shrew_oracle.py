@@ -48,6 +48,10 @@ def lib() -> ctypes.CDLL:
         sz, vp, ci = ctypes.c_size_t, ctypes.c_void_p, ctypes.c_int
         L.shrew_oracle_quantize_f32.argtypes = [vp, sz, sz, ci, vp, vp]
         L.shrew_oracle_quantize_f32.restype = ci
+        L.shrew_oracle_quantize_f32_ex.argtypes = [vp, sz, sz, ci, ci, ci, vp, vp, vp]
+        L.shrew_oracle_quantize_f32_ex.restype = ci
+        L.shrew_oracle_dequantize_f64_ex.argtypes = [vp, vp, vp, sz, sz, ci, vp]
+        L.shrew_oracle_dequantize_f64_ex.restype = None
         for name in ("f64", "f32", "bf16"):
             fn = getattr(L, f"shrew_oracle_dequantize_{name}")
             fn.argtypes = [vp, vp, sz, sz, ci, vp]
@@ -94,6 +98,36 @@ def quantize_f32(w: np.ndarray, granularity: int) -> tuple[np.ndarray, np.ndarra
     if rc != 0:
         raise MemoryError("oracle: f64 widening copy failed")
     return q, scales
+
+
+SYMMETRIC, ASYMMETRIC = 0, 1
+
+
+def quantize_f32_ex(w: np.ndarray, granularity: int, bits: int = 8, mode: int = SYMMETRIC):
+    """quantize_tensor in any of the reference's modes (quantize.rs:124-139, :339-366): INT8 or
+    INT4 codes (one per byte), symmetric or asymmetric.  Returns (codes, scales, zero_points)."""
+    w = np.require(w, dtype=np.float32, requirements="C")
+    rows, cols = _rows_cols(w.shape)
+    if w.ndim == 0:
+        granularity = PER_TENSOR
+    q = np.empty(w.shape, dtype=np.int8)
+    n = rows if granularity == PER_CHANNEL else 1
+    scales, zps = np.empty(n, dtype=np.float64), np.empty(n, dtype=np.float64)
+    rc = lib().shrew_oracle_quantize_f32_ex(_p(w), rows, cols, granularity, bits, mode, _p(q), _p(scales), _p(zps))
+    if rc != 0:
+        raise MemoryError("oracle: f64 widening copy failed")
+    return q, scales, zps
+
+
+def dequantize_f64_ex(q: np.ndarray, scales: np.ndarray, zero_points: np.ndarray, granularity: int) -> np.ndarray:
+    """(q as f64 - zp) * scale (quantize.rs:262-266, :320-335), the intermediate Vec<f64>."""
+    q = np.ascontiguousarray(q, dtype=np.int8)
+    rows, cols = _rows_cols(q.shape)
+    out = np.empty(q.shape, dtype=np.float64)
+    lib().shrew_oracle_dequantize_f64_ex(_p(q), _p(np.ascontiguousarray(scales, dtype=np.float64)),
+                                         _p(np.ascontiguousarray(zero_points, dtype=np.float64)), rows, cols,
+                                         granularity if q.ndim else PER_TENSOR, _p(out))
+    return out
 
 
 def dequantize(q: np.ndarray, scales: np.ndarray, granularity: int, dtype: str = "f32") -> np.ndarray:
@@ -161,6 +195,35 @@ def np_quantize_f32(w: np.ndarray, granularity: int) -> tuple[np.ndarray, np.nda
         t = np_round_half_away(data * inv[:, None] + 0.0)
         t = np.where(np.isnan(t), 0.0, np.clip(t, -127.0, 127.0))  # NaN as i8 == 0
     return t.astype(np.int8).reshape(w.shape), scale.astype(np.float64)
+
+
+def np_quantize_f32_ex(w: np.ndarray, granularity: int, bits: int = 8, mode: int = SYMMETRIC):
+    """numpy twin of quantize_f32_ex."""
+    w = np.require(w, dtype=np.float32, requirements="C")
+    rows, cols = _rows_cols(w.shape)
+    data = w.astype(np.float64).reshape(rows, cols)
+    if granularity == PER_TENSOR or w.ndim == 0:
+        data = data.reshape(1, -1)
+    qmax = 7.0 if bits == 4 else 127.0
+    qmin = (-8.0 if mode == ASYMMETRIC else -7.0) if bits == 4 else (-128.0 if mode == ASYMMETRIC else -127.0)
+    g = data.shape[0]
+    with np.errstate(all="ignore"):
+        if data.shape[1] == 0:
+            scale, zp = np.ones(g), np.zeros(g)
+        elif mode == ASYMMETRIC:
+            lo = np.fmin.reduce(data, axis=1, initial=np.inf)     # fmin / fmax skip NaN like f64::min / max
+            hi = np.fmax.reduce(data, axis=1, initial=-np.inf)
+            rng = hi - lo
+            scale = np.where(rng < 1e-30, 1.0, rng / (qmax - qmin))
+            zp = np_round_half_away(qmin - lo / scale)
+        else:
+            amax = np.fmax.reduce(np.abs(data), axis=1, initial=0.0)
+            scale = np.where(amax < 1e-30, 1.0, amax / qmax)
+            zp = np.zeros(g)
+        inv = np.where(np.abs(scale) < 1e-30, 0.0, 1.0 / scale)
+        t = np_round_half_away(data * inv[:, None] + zp[:, None])
+        t = np.where(np.isnan(t), 0.0, np.clip(t, qmin, qmax))
+    return t.astype(np.int8).reshape(w.shape), scale.astype(np.float64), zp.astype(np.float64)
 
 
 def np_dequantize_f64(q: np.ndarray, scales: np.ndarray, granularity: int) -> np.ndarray:

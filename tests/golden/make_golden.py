@@ -83,6 +83,101 @@ def case(name, shape, data, granularity, note):
     }
 
 
+# ---- the other modes: asymmetric INT8, INT4 symmetric / asymmetric (quantize.rs:124-139, :339-366) ----
+def qrange(bits, mode):
+    qmax = 7.0 if bits == 4 else 127.0
+    if bits == 4:
+        return (-8.0 if mode == "asymmetric" else -7.0), qmax
+    return (-128.0 if mode == "asymmetric" else -127.0), qmax
+
+
+def scale_zp_of(vals, bits, mode):
+    if not vals:
+        return 1.0, 0.0
+    qmin, qmax = qrange(bits, mode)
+    if mode == "symmetric":
+        amax = 0.0
+        for v in vals:
+            a = abs(v)
+            if a == a and a > amax:
+                amax = a
+        return (1.0 if amax < 1e-30 else amax / qmax), 0.0
+    lo, hi = float("inf"), float("-inf")
+    for v in vals:  # f64::min / f64::max keep the other operand when one is NaN
+        if v == v:
+            lo = v if v < lo else lo
+            hi = v if v > hi else hi
+    rng = hi - lo
+    scale = 1.0 if rng < 1e-30 else rng / (qmax - qmin)
+    return scale, exact_round_half_away(qmin - div(lo, scale))
+
+
+def div(a, b):
+    """IEEE division (Python raises on a zero divisor; not reachable here, scale is never 0)."""
+    return a / b
+
+
+def quantize_mode(vals, scale, zp, bits, mode):
+    qmin, qmax = qrange(bits, mode)
+    inv = 0.0 if abs(scale) < 1e-30 else 1.0 / scale
+    out = []
+    for v in vals:
+        t = exact_round_half_away(v * inv + zp)
+        if t != t:
+            out.append(0)
+            continue
+        out.append(int(min(max(t, qmin), qmax)))
+    return out
+
+
+def mode_case(name, shape, data, granularity, bits, mode, note):
+    data = [f32(v) for v in data]
+    rows = shape[0] if shape else 1
+    cols = 1
+    for s in shape[1:]:
+        cols *= s
+    groups = [data[r * cols:(r + 1) * cols] for r in range(rows)] if (granularity == "per_channel" and shape) else [data]
+    scales, zps, codes = [], [], []
+    for g in groups:
+        s, z = scale_zp_of(g, bits, mode)
+        scales.append(s)
+        zps.append(z)
+        codes += quantize_mode(g, s, z, bits, mode)
+    bits64 = lambda v: struct.unpack("<Q", struct.pack("<d", v))[0]  # noqa: E731
+    return {"name": name, "note": note, "shape": shape, "granularity": granularity, "bits": bits, "mode": mode,
+            "data_f32_bits": [struct.unpack("<I", struct.pack("<f", v))[0] for v in data], "codes": codes,
+            "scales_f64_bits": [bits64(s) for s in scales], "zero_points_f64_bits": [bits64(z) for z in zps]}
+
+
+def mode_cases():
+    inf, nan = float("inf"), float("nan")
+    ramp = [(i - 6.0) * 0.1 for i in range(12)]
+    out = []
+    for bits in (8, 4):
+        for mode in ("symmetric", "asymmetric"):
+            tag = f"int{bits}_{mode}"
+            out += [
+                mode_case(f"{tag}_ref_asymmetric_input", [1, 5], [-1.0, -0.5, 0.0, 0.5, 1.0], "per_tensor", bits, mode,
+                          "input of quantize.rs:676-699 (the reference asserts round-trip < 0.02 in INT8 asymmetric)"),
+                mode_case(f"{tag}_ref_int4_input", [2, 2], [1.0, -0.5, 0.25, -1.0], "per_tensor",
+                          bits, mode, "input of quantize.rs:626-650 (the reference asserts round-trip < 0.2 in INT4 symmetric)"),
+                mode_case(f"{tag}_ramp_per_channel", [3, 4], ramp, "per_channel", bits, mode, "three rows, own scale and zero point each"),
+                mode_case(f"{tag}_constant_rows", [2, 3], [3.0, 3.0, 3.0, -2.0, -2.0, -2.0], "per_channel", bits, mode,
+                          "range < 1e-30 -> scale 1.0, zero point qmin - min"),
+                mode_case(f"{tag}_positive_only", [1, 6], [0.1, 0.2, 0.4, 0.8, 1.6, 3.2], "per_tensor", bits, mode,
+                          "one-sided data: the asymmetric range starts at the minimum"),
+                mode_case(f"{tag}_zeros", [2, 2], [0.0] * 4, "per_tensor", bits, mode, "all zero"),
+                mode_case(f"{tag}_nan_inf", [2, 3], [nan, 1.0, -2.0, inf, -1.0, 0.5], "per_channel", bits, mode,
+                          "NaN skipped by min/max, code 0; a row holding Inf: scale Inf, inverse 0"),
+                mode_case(f"{tag}_all_nan", [1, 3], [nan, nan, nan], "per_tensor", bits, mode, "min=+Inf, max=-Inf, range=-Inf < 1e-30"),
+                mode_case(f"{tag}_empty", [0, 3], [], "per_channel", bits, mode, "no channels"),
+                mode_case(f"{tag}_empty_cols", [2, 0], [], "per_channel", bits, mode, "empty channels -> (1.0, 0.0)"),
+                mode_case(f"{tag}_rank0", [], [2.5], "per_channel", bits, mode, "rank 0 falls back to per-tensor"),
+                mode_case(f"{tag}_ties", [1, 6], [7.0, 3.5, -3.5, 0.5, -0.5, 1.5], "per_tensor", bits, mode, "products on .5"),
+            ]
+    return out
+
+
 def main():
     inf, nan = float("inf"), float("nan")
     cases = [
@@ -121,6 +216,11 @@ def main():
     with open(out, "w") as f:
         json.dump({"generator": "tests/golden/make_golden.py", "cases": cases}, f, indent=1)
     print("wrote", out, len(cases), "cases")
+    out2 = os.path.join(os.path.dirname(os.path.abspath(__file__)), "quantize_modes_golden.json")
+    mc = mode_cases()
+    with open(out2, "w") as f:
+        json.dump({"generator": "tests/golden/make_golden.py", "cases": mc}, f, indent=1)
+    print("wrote", out2, len(mc), "cases")
 
 
 if __name__ == "__main__":
