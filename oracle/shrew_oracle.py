@@ -176,7 +176,7 @@ def np_round_half_away(t: np.ndarray) -> np.ndarray:
     """f64::round.  trunc(t) plus one step when the exact fractional part is >= 0.5
     (t - trunc(t) is exact in binary floating point)."""
     r = np.trunc(t)
-    return r + np.where(np.abs(t - r) >= 0.5, np.sign(t), 0.0)
+    return np.copysign(r + np.where(np.abs(t - r) >= 0.5, np.sign(t), 0.0), t)  # round(-0.3) is -0.0
 
 
 def np_quantize_f32(w: np.ndarray, granularity: int) -> tuple[np.ndarray, np.ndarray]:

@@ -30,7 +30,7 @@ def exact_round_half_away(t: float) -> float:
     r = float(math.trunc(t))
     if abs(t - r) >= 0.5:
         r += 1.0 if t > 0 else -1.0
-    return r
+    return math.copysign(r, t)  # f64::round keeps the sign: round(-0.3) is -0.0
 
 
 def scale_of(vals):
@@ -173,6 +173,8 @@ def mode_cases():
                 mode_case(f"{tag}_empty", [0, 3], [], "per_channel", bits, mode, "no channels"),
                 mode_case(f"{tag}_empty_cols", [2, 0], [], "per_channel", bits, mode, "empty channels -> (1.0, 0.0)"),
                 mode_case(f"{tag}_rank0", [], [2.5], "per_channel", bits, mode, "rank 0 falls back to per-tensor"),
+                mode_case(f"{tag}_negative_zero_point", [1, 2], [0.12573022, -0.13210486], "per_tensor", bits, mode,
+                          "INT4 asymmetric: qmin - min/scale = -0.31 rounds to -0.0, sign kept in the zero point"),
                 mode_case(f"{tag}_ties", [1, 6], [7.0, 3.5, -3.5, 0.5, -0.5, 1.5], "per_tensor", bits, mode, "products on .5"),
             ]
     return out
