@@ -57,6 +57,10 @@ extern "C" {
 #define SHREWQ_F32 0
 #define SHREWQ_BF16 1
 /* elementwise op fused after the bias add (the tensor op a caller applies next) */
+/* QuantMode (quantize.rs:51-58) */
+#define SHREWQ_SYMMETRIC 0
+#define SHREWQ_ASYMMETRIC 1
+
 #define SHREWQ_EPILOGUE_NONE 0
 #define SHREWQ_EPILOGUE_RELU 1
 
@@ -99,6 +103,23 @@ SHREWQ_API int shrewq_quantize_f32_host(shrewq_ctx *ctx, const float *w_host, si
 SHREWQ_API int shrewq_dequantize(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
                       size_t rows, size_t cols, int granularity, int out_dtype, void *out_dev);
 
+/*
+ * The same two calls for every mode of QuantConfig (quantize.rs:64-139): bits = 8 or 4 (INT4
+ * codes are stored one per byte, as the reference's Vec<i8> does, within [-8, 7]), mode =
+ * SHREWQ_SYMMETRIC or SHREWQ_ASYMMETRIC (compute_scale_zp, :353-364: scale from max - min, zero
+ * point round(qmin - min / scale)).  zero_points_dev receives 1 or `rows` f64 values (0.0 in
+ * symmetric mode).  bits = 8 with SHREWQ_SYMMETRIC runs the kernels of shrewq_quantize_f32.  The
+ * kernels of the other modes are built but have not run on a GPU yet: they answer
+ * SHREWQ_ERR_UNSUPPORTED unless the environment sets SHREWQ_EXPERIMENTAL_MODES=1.
+ * shrewq_dequantize_ex with zero_points_dev = NULL is shrewq_dequantize.
+ */
+SHREWQ_API int shrewq_quantize_f32_ex(shrewq_ctx *ctx, const float *w_dev, size_t rows, size_t cols,
+                           int granularity, int bits, int mode, int8_t *q_dev, double *scales_dev,
+                           double *zero_points_dev);
+SHREWQ_API int shrewq_dequantize_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
+                         const double *zero_points_dev, size_t rows, size_t cols, int granularity,
+                         int out_dtype, void *out_dev);
+
 /* ---- quantized Linear --------------------------------------------------------------- */
 /*
  * QuantizedLinear::new — quantize.rs:437-447 (from_linear, :413-434, is
@@ -113,6 +134,14 @@ SHREWQ_API int shrewq_dequantize(shrewq_ctx *ctx, const int8_t *q_dev, const dou
 SHREWQ_API int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
                          const float *bias_dev, size_t out_features, size_t in_features,
                          int granularity, shrewq_linear **out);
+/* QuantizedLinear::new for a weight quantized with zero points (asymmetric mode): the forward
+ * computes scale * sum(q x) + bias - (scale * zero_point) * sum(x), which equals the reference's
+ * x . dequant(W)^T + bias up to f32 rounding.  zero_points_dev = NULL is shrewq_linear_create.
+ * Same experimental status and environment switch as shrewq_quantize_f32_ex; such a handle is
+ * not accepted by the gate/up, peer-destination and no-allocation forwards. */
+SHREWQ_API int shrewq_linear_create_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
+                            const double *zero_points_dev, const float *bias_dev, size_t out_features,
+                            size_t in_features, int granularity, shrewq_linear **out);
 SHREWQ_API void shrewq_linear_destroy(shrewq_linear *lin);
 
 /*

@@ -12,6 +12,7 @@ import os
 OK = 0
 ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_TIMEOUT, ERR_ALLOC = -1, -2, -3, -4, -5, -6
 PER_TENSOR, PER_CHANNEL = 0, 1
+SYMMETRIC, ASYMMETRIC = 0, 1
 F32, BF16 = 0, 1
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
 
@@ -31,7 +32,10 @@ SIGNATURES = {
     "shrewq_quantize_f32": (_ci, [_vp, _vp, _sz, _sz, _ci, _vp, _vp]),
     "shrewq_quantize_f32_host": (_ci, [_vp, _vp, _sz, _sz, _ci, _vp, _vp]),
     "shrewq_dequantize": (_ci, [_vp, _vp, _vp, _sz, _sz, _ci, _ci, _vp]),
+    "shrewq_quantize_f32_ex": (_ci, [_vp, _vp, _sz, _sz, _ci, _ci, _ci, _vp, _vp, _vp]),
+    "shrewq_dequantize_ex": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _ci, _vp]),
     "shrewq_linear_create": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _pp]),
+    "shrewq_linear_create_ex": (_ci, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _ci, _pp]),
     "shrewq_linear_destroy": (None, [_vp]),
     "shrewq_linear_forward": (_ci, [_vp, _vp, _ci, _sz, _vp, _ci, _sz, _ci]),
     "shrewq_linear_forward_host": (_ci, [_vp, _vp, _ci, _sz, _vp, _ci, _ci]),

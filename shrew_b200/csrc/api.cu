@@ -136,6 +136,7 @@ void shrewq_ctx_destroy(shrewq_ctx *ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->stage_dev) cudaFree(ctx->stage_dev);
     if (ctx->xsplit) cudaFree(ctx->xsplit);
+    if (ctx->ytmp) cudaFree(ctx->ytmp);
     if (ctx->stage_pinned) cudaFreeHost(ctx->stage_pinned);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     delete ctx;
@@ -220,6 +221,65 @@ int shrewq_dequantize(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales
     return launch_dequantize(ctx, q_dev, scales_dev, rows, cols, granularity, out_dtype, out_dev);
 }
 
+// ---- the reference's other modes (asymmetric INT8, INT4) ------------------------------------
+// Built and checked against the CPU restatement by reading only: until they have run on a GPU
+// they answer SHREWQ_ERR_UNSUPPORTED unless the environment sets SHREWQ_EXPERIMENTAL_MODES=1.
+static bool experimental_modes() {
+    const char *e = getenv("SHREWQ_EXPERIMENTAL_MODES");
+    return e && atoi(e) != 0;
+}
+
+static int check_mode(shrewq_ctx *ctx, int bits, int mode, const char *who) {
+    if ((bits != 8 && bits != 4) || (mode != SHREWQ_SYMMETRIC && mode != SHREWQ_ASYMMETRIC))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: bits must be 8 or 4, mode SHREWQ_SYMMETRIC or SHREWQ_ASYMMETRIC", who);
+    if (!(bits == 8 && mode == SHREWQ_SYMMETRIC) && !experimental_modes())
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
+                       "%s: only INT8 symmetric is validated; INT4 and asymmetric kernels are built but have not run on a "
+                       "GPU yet (SHREWQ_EXPERIMENTAL_MODES=1 enables them)", who);
+    return SHREWQ_OK;
+}
+
+int shrewq_quantize_f32_ex(shrewq_ctx *ctx, const float *w_dev, size_t rows, size_t cols, int granularity, int bits,
+                           int mode, int8_t *q_dev, double *scales_dev, double *zero_points_dev) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "quantize_ex: ctx is NULL");
+    int rc = check_gran(ctx, granularity, "quantize_ex");
+    if (rc != SHREWQ_OK) return rc;
+    if ((rc = check_mode(ctx, bits, mode, "quantize_ex")) != SHREWQ_OK) return rc;
+    const size_t n = rows * cols;
+    if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_ex: rows*cols overflows");
+    const size_t ns = granularity == SHREWQ_PER_CHANNEL ? rows : 1;
+    if (ns > 0 && (!scales_dev || !zero_points_dev))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_ex: scales_dev / zero_points_dev is NULL");
+    if (n > 0 && (!w_dev || !q_dev)) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_ex: w_dev / q_dev is NULL");
+    if ((reinterpret_cast<uintptr_t>(w_dev) & 3) || (reinterpret_cast<uintptr_t>(scales_dev) & 7) ||
+        (reinterpret_cast<uintptr_t>(zero_points_dev) & 7))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_ex: w_dev must be 4-byte, scales / zero points 8-byte aligned");
+    if ((rc = bind(ctx)) != SHREWQ_OK) return rc;
+    if (bits == 8 && mode == SHREWQ_SYMMETRIC) {
+        if ((rc = launch_quantize(ctx, w_dev, rows, cols, granularity, q_dev, scales_dev)) != SHREWQ_OK) return rc;
+        if (ns) SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(zero_points_dev, 0, ns * sizeof(double), ctx->stream));  // 0.0
+        return SHREWQ_OK;
+    }
+    return launch_quantize_ex(ctx, w_dev, rows, cols, granularity, bits, mode, q_dev, scales_dev, zero_points_dev);
+}
+
+int shrewq_dequantize_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev, const double *zero_points_dev,
+                         size_t rows, size_t cols, int granularity, int out_dtype, void *out_dev) {
+    if (!zero_points_dev) return shrewq_dequantize(ctx, q_dev, scales_dev, rows, cols, granularity, out_dtype, out_dev);
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: ctx is NULL");
+    int rc = check_gran(ctx, granularity, "dequantize_ex");
+    if (rc != SHREWQ_OK) return rc;
+    if (!experimental_modes())
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "dequantize_ex: zero points need SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
+    if (out_dtype != SHREWQ_F32 && out_dtype != SHREWQ_BF16)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: out_dtype must be SHREWQ_F32 or SHREWQ_BF16");
+    const size_t n = rows * cols;
+    if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: rows*cols overflows");
+    if (n > 0 && (!q_dev || !scales_dev || !out_dev)) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: NULL buffer");
+    if ((rc = bind(ctx)) != SHREWQ_OK) return rc;
+    return launch_dequantize_ex(ctx, q_dev, scales_dev, zero_points_dev, rows, cols, granularity, out_dtype, out_dev);
+}
+
 // ---- quantized Linear ---------------------------------------------------------------------
 int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev, const float *bias_dev,
                          size_t out_features, size_t in_features, int granularity, shrewq_linear **out) {
@@ -263,11 +323,40 @@ int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const double *sca
     return SHREWQ_OK;
 }
 
+int shrewq_linear_create_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
+                            const double *zero_points_dev, const float *bias_dev, size_t out_features,
+                            size_t in_features, int granularity, shrewq_linear **out) {
+    if (!zero_points_dev)
+        return shrewq_linear_create(ctx, q_dev, scales_dev, bias_dev, out_features, in_features, granularity, out);
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "linear_create_ex: ctx is NULL");
+    if (!experimental_modes()) {
+        if (out) *out = nullptr;
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "linear_create_ex: zero points need SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
+    }
+    int rc = shrewq_linear_create(ctx, q_dev, scales_dev, bias_dev, out_features, in_features, granularity, out);
+    if (rc != SHREWQ_OK) return rc;
+    shrewq_linear *lin = *out;
+    cudaError_t e = cudaMalloc(&lin->czp, out_features * sizeof(float));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        shrewq_linear_destroy(lin);
+        *out = nullptr;
+        return set_err(ctx, SHREWQ_ERR_ALLOC, "linear_create_ex: cudaMalloc failed: %s", cudaGetErrorString(e));
+    }
+    rc = launch_scale_zp_to_f32(ctx, scales_dev, zero_points_dev, granularity, out_features, lin->czp);
+    if (rc != SHREWQ_OK) {
+        shrewq_linear_destroy(lin);
+        *out = nullptr;
+    }
+    return rc;
+}
+
 void shrewq_linear_destroy(shrewq_linear *lin) {
     if (!lin) return;
     cudaSetDevice(lin->ctx->device);
     cudaStreamSynchronize(lin->ctx->stream);
     if (lin->scales_f32) cudaFree(lin->scales_f32);
+    if (lin->czp) cudaFree(lin->czp);
     delete lin;
 }
 
@@ -342,6 +431,23 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
     }
     a.extra.n = n_peers;
 
+    // Zero points: y = scale * (sum_k q x) + bias - (scale * zp) * sum_k x.  The kernels below
+    // compute the first part into an f32 buffer; a last pass subtracts the second, applies the
+    // elementwise op and narrows to the caller's type.
+    const bool zp_route = lin->czp != nullptr || (up && up->czp != nullptr);
+    float *zp_acc = nullptr, *zp_xsum = nullptr;
+    if (zp_route) {
+        if (up || n_peers > 0 || g_forced_kernel == kForceTc2Cta || g_forced_kernel == kForceTcF32)
+            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
+                           "%s: zero points are not supported with a gate/up pair, peer destinations or this forced kernel", who);
+        const size_t acc_bytes = align_up(M * lin->n * sizeof(float), 256);
+        if ((rc = grow(ctx, &ctx->ytmp, &ctx->ytmp_bytes, acc_bytes + M * sizeof(float), false)) != SHREWQ_OK) return rc;
+        zp_acc = static_cast<float *>(ctx->ytmp);
+        zp_xsum = reinterpret_cast<float *>(static_cast<char *>(ctx->ytmp) + acc_bytes);
+        if ((rc = launch_row_sums(ctx, x_dev, x_dtype, M, lin->k, zp_xsum)) != SHREWQ_OK) return rc;
+        a.y = zp_acc; a.y_dtype = SHREWQ_F32; a.ldy = lin->n; a.epilogue = SHREWQ_EPILOGUE_NONE;
+    }
+
     const bool vec16 = (lin->k % 16) == 0 && (reinterpret_cast<uintptr_t>(lin->q) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 &&
                        (!up || (reinterpret_cast<uintptr_t>(up->q) & 15) == 0);
@@ -387,6 +493,8 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
         rc = launch_gemm_simt(ctx, a); name = "simt";
     }
     lin->last_kernel = name;
+    if (zp_route && rc == SHREWQ_OK)
+        rc = launch_zero_point_fix(ctx, zp_acc, lin->czp, zp_xsum, M, lin->n, ldy, epilogue == SHREWQ_EPILOGUE_RELU, y_dtype, y_dev);
     return rc;
 }
 
@@ -403,6 +511,7 @@ int shrewq_linear_forward_noalloc(shrewq_linear *lin, const void *x_dev, size_t 
         return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: y_dtype must be SHREWQ_F32 or SHREWQ_BF16");
     if (epilogue != SHREWQ_EPILOGUE_NONE && epilogue != SHREWQ_EPILOGUE_RELU)
         return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: unknown epilogue %d", epilogue);
+    if (lin->czp) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "forward_noalloc: handles with zero points need shrewq_linear_forward");
     if (M == 0) return SHREWQ_OK;
     if (!x_dev || !y_dev) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: x / y is NULL");
     if (ldy < lin->n) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: ldy smaller than out_features");

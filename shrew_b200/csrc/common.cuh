@@ -45,6 +45,9 @@ struct shrewq_ctx {
     // bf16 hi/lo split of f32 activations (tensor-core route for f32 inputs)
     void *xsplit = nullptr;
     size_t xsplit_bytes = 0;
+    // f32 [M,N] accumulators + per-token activation sums of a forward through zero points
+    void *ytmp = nullptr;
+    size_t ytmp_bytes = 0;
     // device status block + pinned mirror
     shrewq::DeviceStatus *dev_status = nullptr;
 };
@@ -54,6 +57,7 @@ struct shrewq_linear {
     const int8_t *q = nullptr;
     const float *bias = nullptr;
     float *scales_f32 = nullptr;  // owned, out_features entries (per-tensor scale broadcast)
+    float *czp = nullptr;         // owned, scale * zero_point per output channel; null = symmetric
     size_t n = 0, k = 0;
     int granularity = 0;
     const char *last_kernel = "none";
@@ -86,6 +90,14 @@ int launch_dequantize(shrewq_ctx *ctx, const int8_t *q, const double *scales, si
 int launch_scales_to_f32(shrewq_ctx *ctx, const double *scales, int granularity, size_t n, float *out);
 int launch_split_f32(shrewq_ctx *ctx, const float *x, size_t n, void *hi_bf16, void *lo_bf16);
 int ensure_xsplit(shrewq_ctx *ctx, size_t bytes);
+int launch_quantize_ex(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, int granularity, int bits, int mode,
+                       int8_t *q, double *scales, double *zps);
+int launch_dequantize_ex(shrewq_ctx *ctx, const int8_t *q, const double *scales, const double *zps, size_t rows,
+                         size_t cols, int granularity, int out_dtype, void *out);
+int launch_scale_zp_to_f32(shrewq_ctx *ctx, const double *scales, const double *zps, int granularity, size_t n, float *out);
+int launch_row_sums(shrewq_ctx *ctx, const void *x, int x_dtype, size_t M, size_t K, float *sums);
+int launch_zero_point_fix(shrewq_ctx *ctx, const float *acc, const float *czp, const float *xsum, size_t M, size_t N,
+                          size_t ldy, int relu, int y_dtype, void *y);
 
 // internal epilogue flag (above the public SHREWQ_EPILOGUE_* values): add the f32 value already
 // stored at the output position before the elementwise op

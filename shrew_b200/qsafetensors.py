@@ -191,8 +191,8 @@ def pack_records(named: Sequence[Tuple[str, Union[HostQuantized, Entry]]]):
         if s != want or int(t.zero_points.size) != s:
             raise FormatError(f"'{name}': {s} scales / {int(t.zero_points.size)} zero points for granularity "
                               f"{t.granularity} and shape {list(t.codes.shape)}")
-        if t.bits != 8:
-            raise FormatError(f"'{name}': only 8-bit records are defined")
+        if t.bits not in (4, 8):
+            raise FormatError(f"'{name}': records hold 8-bit or 4-bit codes (one per byte)")
         entries.append((name + ".qweight", Entry("I8", list(t.codes.shape), np.asarray(t.codes, dtype=np.int8))))
         entries.append((name + ".scales", Entry("F64", [s], np.asarray(t.scales, dtype=np.float64).reshape(s))))
         entries.append((name + ".zero_points", Entry("F64", [s], np.asarray(t.zero_points, dtype=np.float64).reshape(s))))
@@ -220,7 +220,7 @@ def unpack_records(metadata: Dict[str, str], entries: Dict[str, Entry]):
                 raise FormatError(f"quantized record '{name}': '{name + suf}' has dtype {e.dtype}, expected {dt}")
             parts.append(e)
             used.add(name + suf)
-        if not isinstance(d, dict) or d.get("bits") != 8 or d.get("mode") not in ("symmetric", "asymmetric") \
+        if not isinstance(d, dict) or d.get("bits") not in (4, 8) or d.get("mode") not in ("symmetric", "asymmetric") \
                 or d.get("granularity") not in ("per_tensor", "per_channel") or d.get("original_dtype") not in _NP:
             raise FormatError(f"quantized record '{name}': bad description {d!r}")
         q, sc, zp = parts
@@ -229,7 +229,7 @@ def unpack_records(metadata: Dict[str, str], entries: Dict[str, Entry]):
         if sc.shape != [want] or zp.shape != [want]:
             raise FormatError(f"quantized record '{name}': {sc.shape} scales for granularity {d['granularity']} "
                               f"and shape {q.shape}")
-        out[name] = HostQuantized(q.data, sc.data, zp.data, 8, d["mode"], d["granularity"], d["original_dtype"])
+        out[name] = HostQuantized(q.data, sc.data, zp.data, d["bits"], d["mode"], d["granularity"], d["original_dtype"])
     for name, e in entries.items():
         if name not in used:
             out[name] = e
@@ -248,12 +248,12 @@ def save(path: str, named) -> None:
     host = []
     for name, t in named:
         if isinstance(t, QuantizedTensor):
-            t.config._require_int8_symmetric()
             gran = "per_channel" if (t.config.granularity is QuantGranularity.PerChannel and len(t.shape)) else "per_tensor"
             mode = "symmetric" if t.config.mode is QuantMode.Symmetric else "asymmetric"
             codes = t.data.detach().cpu().numpy().reshape(t.shape)
             scales = t.scales.detach().cpu().numpy()
-            host.append((name, HostQuantized(codes, scales, np.zeros_like(scales), 8, mode, gran, st[t.original_dtype])))
+            zps = np.zeros_like(scales) if t.zero_points_t is None else t.zero_points_t.detach().cpu().numpy()
+            host.append((name, HostQuantized(codes, scales, zps, t.config.bits.value, mode, gran, st[t.original_dtype])))
         else:
             if t.dtype not in st:
                 raise FormatError(f"'{name}': dtype {t.dtype} cannot be stored")
@@ -276,13 +276,13 @@ def load(path: str, device):
     out = []
     for name, t in unpack_records(metadata, entries).items():
         if isinstance(t, HostQuantized):
-            if t.mode != "symmetric":
-                raise FormatError(f"'{name}': asymmetric records have no device kernels")
-            cfg = QuantConfig(QuantBits.Int8, QuantMode.Symmetric,
+            cfg = QuantConfig(QuantBits.Int8 if t.bits == 8 else QuantBits.Int4,
+                              QuantMode.Symmetric if t.mode == "symmetric" else QuantMode.Asymmetric,
                               QuantGranularity.PerChannel if t.granularity == "per_channel" else QuantGranularity.PerTensor)
             q = torch.from_numpy(np.array(t.codes, copy=True).reshape(-1)).to(device)
             s = torch.from_numpy(np.array(t.scales, copy=True)).to(device)
-            out.append((name, QuantizedTensor(q, s, [int(d) for d in t.codes.shape], ts[t.original_dtype], cfg)))
+            z = None if t.mode == "symmetric" else torch.from_numpy(np.array(t.zero_points, copy=True)).to(device)
+            out.append((name, QuantizedTensor(q, s, [int(d) for d in t.codes.shape], ts[t.original_dtype], cfg, z)))
         else:
             if t.dtype not in ts:
                 raise FormatError(f"'{name}': dtype {t.dtype} has no device tensor type here")

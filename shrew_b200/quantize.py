@@ -75,10 +75,17 @@ class QuantConfig:
             return -127.0 if self.mode is QuantMode.Symmetric else -128.0
         return -7.0 if self.mode is QuantMode.Symmetric else -8.0
 
+    def _is_int8_symmetric(self) -> bool:
+        return self.bits is QuantBits.Int8 and self.mode is QuantMode.Symmetric
+
     def _require_int8_symmetric(self) -> None:
-        if self.bits is not QuantBits.Int8 or self.mode is not QuantMode.Symmetric:
+        if not self._is_int8_symmetric():
             raise ShrewError(_lib.ERR_UNSUPPORTED,
-                             "only INT8 symmetric quantization has device kernels (INT4 and asymmetric are not built)")
+                             "only INT8 symmetric quantization is validated on the device (INT4 and asymmetric kernels are "
+                             "experimental: SHREWQ_EXPERIMENTAL_MODES=1)")
+
+    def _abi_mode(self) -> Tuple[int, int]:
+        return (8 if self.bits is QuantBits.Int8 else 4, _lib.SYMMETRIC if self.mode is QuantMode.Symmetric else _lib.ASYMMETRIC)
 
 
 # ---- device / context ------------------------------------------------------------------------
@@ -144,10 +151,13 @@ class QuantizedTensor:
     shape: List[int]
     original_dtype: torch.dtype
     config: QuantConfig = field(default_factory=QuantConfig)
+    zero_points_t: Optional[torch.Tensor] = None   # float64 on the device; None = all 0.0 (symmetric)
 
     @property
     def zero_points(self) -> List[float]:
-        """All 0.0 in symmetric mode (quantize.rs:351)."""
+        """All 0.0 in symmetric mode (quantize.rs:351); round(qmin - min/scale) per group otherwise."""
+        if self.zero_points_t is not None:
+            return [float(v) for v in self.zero_points_t.cpu().tolist()]
         return [0.0] * int(self.scales.numel())
 
     def numel(self) -> int:
@@ -164,8 +174,9 @@ class QuantizedTensor:
 
 
 def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTensor:
-    """quantize.rs:194-205 on the GPU.  `tensor` is an f32 CUDA tensor."""
-    config._require_int8_symmetric()
+    """quantize.rs:194-205 on the GPU.  `tensor` is an f32 CUDA tensor.  INT8 symmetric runs the
+    validated kernels; the other modes go through shrewq_quantize_f32_ex, which refuses them
+    unless SHREWQ_EXPERIMENTAL_MODES=1 is set."""
     dev = Device.get(tensor.device)
     if tensor.dtype != torch.float32:
         raise ShrewError(_lib.ERR_UNSUPPORTED, f"quantize_tensor: dtype {tensor.dtype} not supported (f32 only)")
@@ -179,9 +190,16 @@ def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTenso
     q = torch.empty(w.numel(), dtype=torch.int8, device=w.device)
     scales = torch.empty(n_scales, dtype=torch.float64, device=w.device)
     dev.bind_stream()
-    rc = _lib.lib().shrewq_quantize_f32(dev.handle, _ptr(w), rows, cols, gran.value, _ptr(q), _ptr(scales))
+    if config._is_int8_symmetric():
+        rc = _lib.lib().shrewq_quantize_f32(dev.handle, _ptr(w), rows, cols, gran.value, _ptr(q), _ptr(scales))
+        _lib.check(rc, dev.handle)
+        return QuantizedTensor(q, scales, shape, tensor.dtype, config)
+    bits, mode = config._abi_mode()
+    zps = torch.empty(n_scales, dtype=torch.float64, device=w.device)
+    rc = _lib.lib().shrewq_quantize_f32_ex(dev.handle, _ptr(w), rows, cols, gran.value, bits, mode, _ptr(q), _ptr(scales),
+                                           _ptr(zps))
     _lib.check(rc, dev.handle)
-    return QuantizedTensor(q, scales, shape, tensor.dtype, config)
+    return QuantizedTensor(q, scales, shape, tensor.dtype, config, zps)
 
 
 def dequantize_tensor(qtensor: QuantizedTensor, device=None) -> torch.Tensor:
@@ -195,8 +213,12 @@ def dequantize_tensor(qtensor: QuantizedTensor, device=None) -> torch.Tensor:
     gran = qtensor.config.granularity if len(qtensor.shape) else QuantGranularity.PerTensor
     out = torch.empty(qtensor.shape, dtype=out_dtype, device=qtensor.data.device)
     dev.bind_stream()
-    rc = _lib.lib().shrewq_dequantize(dev.handle, _ptr(qtensor.data), _ptr(qtensor.scales), rows, cols, gran.value,
-                                      _DTYPE_CODE[out_dtype], _ptr(out))
+    if qtensor.zero_points_t is not None:
+        rc = _lib.lib().shrewq_dequantize_ex(dev.handle, _ptr(qtensor.data), _ptr(qtensor.scales), _ptr(qtensor.zero_points_t),
+                                             rows, cols, gran.value, _DTYPE_CODE[out_dtype], _ptr(out))
+    else:
+        rc = _lib.lib().shrewq_dequantize(dev.handle, _ptr(qtensor.data), _ptr(qtensor.scales), rows, cols, gran.value,
+                                          _DTYPE_CODE[out_dtype], _ptr(out))
     _lib.check(rc, dev.handle)
     return out
 
@@ -226,8 +248,10 @@ class Linear:
 # ---- QuantizedLinear (quantize.rs:384-482) --------------------------------------------------------
 class QuantizedLinear:
     def __init__(self, weight_q: QuantizedTensor, bias: Optional[torch.Tensor], device=None):
-        """QuantizedLinear::new (quantize.rs:437-447)."""
-        weight_q.config._require_int8_symmetric()
+        """QuantizedLinear::new (quantize.rs:437-447).  A weight carrying zero points (asymmetric
+        mode) goes through shrewq_linear_create_ex; INT4 codes are ordinary i8 codes within [-8, 7]."""
+        if weight_q.config.mode is QuantMode.Asymmetric and weight_q.zero_points_t is None:
+            raise ShrewError(_lib.ERR_INVALID_ARG, "QuantizedLinear: an asymmetric weight needs its zero points")
         if len(weight_q.shape) != 2:
             raise ShrewError(_lib.ERR_INVALID_ARG, "QuantizedLinear needs a rank-2 weight [out,in]")
         self.weight_q = weight_q
@@ -241,9 +265,14 @@ class QuantizedLinear:
             self._bias_flat = bias.reshape(-1).to(torch.float32).contiguous()
         h = ctypes.c_void_p()
         self.device.bind_stream()
-        rc = _lib.lib().shrewq_linear_create(self.device.handle, _ptr(weight_q.data), _ptr(weight_q.scales),
-                                             _ptr(self._bias_flat), self.out_features, self.in_features,
-                                             weight_q.config.granularity.value, ctypes.byref(h))
+        if weight_q.zero_points_t is not None and weight_q.config.mode is QuantMode.Asymmetric:
+            rc = _lib.lib().shrewq_linear_create_ex(self.device.handle, _ptr(weight_q.data), _ptr(weight_q.scales),
+                                                    _ptr(weight_q.zero_points_t), _ptr(self._bias_flat), self.out_features,
+                                                    self.in_features, weight_q.config.granularity.value, ctypes.byref(h))
+        else:
+            rc = _lib.lib().shrewq_linear_create(self.device.handle, _ptr(weight_q.data), _ptr(weight_q.scales),
+                                                 _ptr(self._bias_flat), self.out_features, self.in_features,
+                                                 weight_q.config.granularity.value, ctypes.byref(h))
         _lib.check(rc, self.device.handle)
         self._h = h
 

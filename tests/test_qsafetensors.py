@@ -130,7 +130,7 @@ def test_broken_quantized_records_are_rejected(tmp_path):
     with pytest.raises(qs.FormatError, match="scales"):
         qs.pack_records([("w", bad)])
     # a description that is not what this format defines
-    qs.write_file(p, entries, {"shrew.quantized": json.dumps({"w": {"bits": 4, "mode": "symmetric",
+    qs.write_file(p, entries, {"shrew.quantized": json.dumps({"w": {"bits": 2, "mode": "symmetric",
                                                                       "granularity": "per_channel", "original_dtype": "F32"}})})
     with pytest.raises(qs.FormatError, match="bad description"):
         qs.unpack_records(*qs.read_file(p))
