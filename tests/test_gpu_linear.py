@@ -296,16 +296,17 @@ def test_mma_f16_activation_range(oracle, scale):
 
 
 @_UNVALIDATED
-def test_mma_gated_parity(oracle):
+@pytest.mark.parametrize("kind", ["mma", "mma-f16"])
+def test_mma_gated_parity(oracle, kind):
     from shrew_b200 import _lib
     from shrew_b200.quantize import Device
     gate, wg, _ = _make(1000, 1024, 1, seed=0, bias=False)
     up, wu, _ = _make(1000, 1024, 1, seed=1, bias=False)
     x_t, x_np = _x(12, 1024, "bf16")
-    _lib.lib().shrewq_force_kernel(b"mma")
+    _lib.lib().shrewq_force_kernel(kind.encode())
     h = gate.forward_gate_up_silu(up, x_t)
     Device.get("cuda:0").synchronize()
-    assert gate.last_kernel() == "mma"
+    assert gate.last_kernel() == kind
 
     def fwd(ql):
         q = ql.weight_q.data.cpu().numpy().reshape(ql.out_features, ql.in_features)
