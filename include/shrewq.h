@@ -104,6 +104,20 @@ SHREWQ_API int shrewq_dequantize(shrewq_ctx *ctx, const int8_t *q_dev, const dou
                       size_t rows, size_t cols, int granularity, int out_dtype, void *out_dev);
 
 /*
+ * Per-tensor quantization of a ROW SHARD of a tensor that is split over several GPUs.  The one
+ * per-tensor scale is amax / 127 of the WHOLE tensor (quantize.rs:349-351), so: every rank calls
+ * shrewq_absmax_f32 on its shard (max |w|, NaN ignored, +0.0 for n = 0, written as one f32), the
+ * ranks reduce those with MAX (one float through ncclAllReduce / torch.distributed, the caller's
+ * job), then every rank calls shrewq_quantize_f32_given_amax with the reduced value.  Codes and
+ * scale are then bit-identical to quantizing the unsplit tensor.  Per-channel shards need none of
+ * this: shrewq_quantize_f32 on the shard is already identical.  No counterpart in the reference
+ * (which is single-device); not yet run on a GPU (the kernels are those of the per-tensor path).
+ */
+SHREWQ_API int shrewq_absmax_f32(shrewq_ctx *ctx, const float *w_dev, size_t n, float *amax_dev);
+SHREWQ_API int shrewq_quantize_f32_given_amax(shrewq_ctx *ctx, const float *w_dev, size_t n,
+                                   const float *amax_dev, int8_t *q_dev, double *scale_dev);
+
+/*
  * The same two calls for every mode of QuantConfig (quantize.rs:64-139): bits = 8 or 4 (INT4
  * codes are stored one per byte, as the reference's Vec<i8> does, within [-8, 7]), mode =
  * SHREWQ_SYMMETRIC or SHREWQ_ASYMMETRIC (compute_scale_zp, :353-364: scale from max - min, zero

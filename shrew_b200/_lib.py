@@ -32,6 +32,8 @@ SIGNATURES = {
     "shrewq_quantize_f32": (_ci, [_vp, _vp, _sz, _sz, _ci, _vp, _vp]),
     "shrewq_quantize_f32_host": (_ci, [_vp, _vp, _sz, _sz, _ci, _vp, _vp]),
     "shrewq_dequantize": (_ci, [_vp, _vp, _vp, _sz, _sz, _ci, _ci, _vp]),
+    "shrewq_absmax_f32": (_ci, [_vp, _vp, _sz, _vp]),
+    "shrewq_quantize_f32_given_amax": (_ci, [_vp, _vp, _sz, _vp, _vp, _vp]),
     "shrewq_quantize_f32_ex": (_ci, [_vp, _vp, _sz, _sz, _ci, _ci, _ci, _vp, _vp, _vp]),
     "shrewq_dequantize_ex": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _ci, _vp]),
     "shrewq_linear_create": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _pp]),

@@ -221,6 +221,30 @@ int shrewq_dequantize(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales
     return launch_dequantize(ctx, q_dev, scales_dev, rows, cols, granularity, out_dtype, out_dev);
 }
 
+// ---- per-tensor quantization of a shard: amax, (caller's all-reduce), quantize -------------------
+int shrewq_absmax_f32(shrewq_ctx *ctx, const float *w_dev, size_t n, float *amax_dev) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "absmax: ctx is NULL");
+    if (!amax_dev || (n > 0 && !w_dev)) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "absmax: NULL buffer");
+    if ((reinterpret_cast<uintptr_t>(w_dev) & 3) || (reinterpret_cast<uintptr_t>(amax_dev) & 3))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "absmax: buffers must be 4-byte aligned");
+    int rc = bind(ctx);
+    if (rc != SHREWQ_OK) return rc;
+    return launch_absmax(ctx, w_dev, n, amax_dev);
+}
+
+int shrewq_quantize_f32_given_amax(shrewq_ctx *ctx, const float *w_dev, size_t n, const float *amax_dev, int8_t *q_dev,
+                                   double *scale_dev) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "quantize_given_amax: ctx is NULL");
+    if (!amax_dev || !scale_dev || (n > 0 && (!w_dev || !q_dev)))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_given_amax: NULL buffer");
+    if ((reinterpret_cast<uintptr_t>(w_dev) & 3) || (reinterpret_cast<uintptr_t>(amax_dev) & 3) ||
+        (reinterpret_cast<uintptr_t>(scale_dev) & 7))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_given_amax: w / amax must be 4-byte, scale 8-byte aligned");
+    int rc = bind(ctx);
+    if (rc != SHREWQ_OK) return rc;
+    return launch_quantize_given_amax(ctx, w_dev, n, amax_dev, q_dev, scale_dev);
+}
+
 // ---- the reference's other modes (asymmetric INT8, INT4) ------------------------------------
 // Built and checked against the CPU restatement by reading only: until they have run on a GPU
 // they answer SHREWQ_ERR_UNSUPPORTED unless the environment sets SHREWQ_EXPERIMENTAL_MODES=1.

@@ -85,6 +85,8 @@ int ensure_stage(shrewq_ctx *ctx, size_t dev_bytes, size_t pinned_bytes);
 // ---- launchers implemented in the kernel translation units -------------------------
 int launch_quantize(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, int granularity,
                     int8_t *q, double *scales);
+int launch_absmax(shrewq_ctx *ctx, const float *w, size_t n, float *amax_dev);
+int launch_quantize_given_amax(shrewq_ctx *ctx, const float *w, size_t n, const float *amax_dev, int8_t *q, double *scale);
 int launch_dequantize(shrewq_ctx *ctx, const int8_t *q, const double *scales, size_t rows,
                       size_t cols, int granularity, int out_dtype, void *out);
 int launch_scales_to_f32(shrewq_ctx *ctx, const double *scales, int granularity, size_t n, float *out);

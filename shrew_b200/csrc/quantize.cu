@@ -371,6 +371,44 @@ int launch_quantize(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, i
     return SHREWQ_OK;
 }
 
+// ---- per-tensor quantization of a row shard ---------------------------------------------------
+// A tensor split over several GPUs has ONE per-tensor scale, defined by the amax of the whole
+// tensor (quantize.rs:349-351).  Each rank takes the amax of its shard, the ranks take the max of
+// those (one float through an all-reduce, done by the caller), and every rank quantizes its shard
+// with the global value.  Same kernels as the single-GPU per-tensor path.
+int launch_absmax(shrewq_ctx *ctx, const float *w, size_t n, float *amax_dev) {
+    SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(amax_dev, 0, sizeof(float), ctx->stream));  // +0.0f
+    if (n > 0) {
+        size_t want = (n / 4 + 255) / 256;
+        const size_t cap = (size_t)ctx->sm_count * 16;
+        const unsigned grid = (unsigned)(want < 1 ? 1 : (want > cap ? cap : want));
+        absmax_flat_kernel<<<grid, 256, 0, ctx->stream>>>(w, n, reinterpret_cast<unsigned int *>(amax_dev));
+        ctx->launches += 1;
+    }
+    SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+    return SHREWQ_OK;
+}
+
+int launch_quantize_given_amax(shrewq_ctx *ctx, const float *w, size_t n, const float *amax_dev, int8_t *q,
+                               double *scale) {
+    int rc = ensure_scratch(ctx, 256);
+    if (rc != SHREWQ_OK) return rc;
+    TensorParams *tp = reinterpret_cast<TensorParams *>(reinterpret_cast<char *>(ctx->scratch) + 64);
+    // n = 1 here: the scale always derives from the supplied amax, also for an empty shard (an
+    // all-empty tensor has amax 0, which gives the same scale 1.0 as the reference's empty case)
+    finalize_tensor_scale_kernel<<<1, 1, 0, ctx->stream>>>(reinterpret_cast<const unsigned int *>(amax_dev), 1, scale, tp);
+    ctx->launches += 1;
+    if (n > 0) {
+        size_t want = (n / 4 + 255) / 256;
+        const size_t cap = (size_t)ctx->sm_count * 16;
+        const unsigned grid = (unsigned)(want < 1 ? 1 : (want > cap ? cap : want));
+        quantize_flat_kernel<<<grid, 256, 0, ctx->stream>>>(w, n, tp, q);
+        ctx->launches += 1;
+    }
+    SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+    return SHREWQ_OK;
+}
+
 int launch_dequantize(shrewq_ctx *ctx, const int8_t *q, const double *scales, size_t rows,
                       size_t cols, int granularity, int out_dtype, void *out) {
     const size_t n = rows * cols;

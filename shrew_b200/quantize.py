@@ -20,7 +20,7 @@ from ._lib import ShrewError
 
 __all__ = [
     "QuantBits", "QuantMode", "QuantGranularity", "QuantConfig", "QuantizedTensor", "quantize_tensor",
-    "dequantize_tensor", "QuantizedLinear", "quantize_named_parameters", "QuantStats", "quantization_stats",
+    "dequantize_tensor", "absmax", "quantize_tensor_given_amax", "QuantizedLinear", "quantize_named_parameters", "QuantStats", "quantization_stats",
     "Linear", "ShrewError", "Device",
 ]
 
@@ -200,6 +200,35 @@ def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTenso
                                            _ptr(zps))
     _lib.check(rc, dev.handle)
     return QuantizedTensor(q, scales, shape, tensor.dtype, config, zps)
+
+
+def absmax(tensor: torch.Tensor) -> torch.Tensor:
+    """max |w| of an f32 CUDA tensor (NaN ignored) as a 1-element f32 tensor on its device: the value
+    a per-tensor scale derives from (quantize.rs:349-351).  For shards: reduce it over the ranks with
+    MAX, then `quantize_tensor_given_amax`."""
+    dev = Device.get(tensor.device)
+    if tensor.dtype != torch.float32:
+        raise ShrewError(_lib.ERR_UNSUPPORTED, f"absmax: dtype {tensor.dtype} not supported (f32 only)")
+    w = tensor.contiguous()
+    out = torch.empty(1, dtype=torch.float32, device=w.device)
+    dev.bind_stream()
+    _lib.check(_lib.lib().shrewq_absmax_f32(dev.handle, _ptr(w), w.numel(), _ptr(out)), dev.handle)
+    return out
+
+
+def quantize_tensor_given_amax(tensor: torch.Tensor, amax: torch.Tensor) -> QuantizedTensor:
+    """INT8 symmetric per-tensor quantization of a shard with the whole tensor's amax supplied
+    (a 1-element f32 tensor on the same device)."""
+    dev = Device.get(tensor.device)
+    if tensor.dtype != torch.float32 or amax.dtype != torch.float32 or amax.numel() != 1 or amax.device != tensor.device:
+        raise ShrewError(_lib.ERR_INVALID_ARG, "quantize_tensor_given_amax: f32 tensor and a 1-element f32 amax on its device")
+    w = tensor.contiguous()
+    q = torch.empty(w.numel(), dtype=torch.int8, device=w.device)
+    scale = torch.empty(1, dtype=torch.float64, device=w.device)
+    dev.bind_stream()
+    rc = _lib.lib().shrewq_quantize_f32_given_amax(dev.handle, _ptr(w), w.numel(), _ptr(amax.contiguous()), _ptr(q), _ptr(scale))
+    _lib.check(rc, dev.handle)
+    return QuantizedTensor(q, scale, list(w.shape), tensor.dtype, QuantConfig.int8())
 
 
 def dequantize_tensor(qtensor: QuantizedTensor, device=None) -> torch.Tensor:

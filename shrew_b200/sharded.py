@@ -80,20 +80,34 @@ class ShardedLinear:
         return all_gather_columns(local, self.plan, self.group)
 
 
+def quantize_row_shard(w_shard: torch.Tensor, config, group=None, *, quantize=None, absmax=None, quantize_given_amax=None):
+    """Quantizes this rank's row shard so that the result equals the matching rows of the
+    unsplit tensor's quantization, bit for bit.  Per-channel: the shard alone decides
+    (crates/shrew/src/quantize.rs:289-308).  Per-tensor: the scale is amax / 127 of the WHOLE tensor
+    (quantize.rs:349-351), so the ranks first reduce their local amax with MAX — one f32 through an
+    all-reduce, the only collective of the quantize path — and then quantize with the global value.
+    The three callables default to the library's kernels; the CPU tests pass stand-ins."""
+    from . import quantize as qz
+    quantize = quantize or qz.quantize_tensor
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if config.granularity is qz.QuantGranularity.PerChannel or world == 1 or w_shard.dim() == 0:
+        return quantize(w_shard, config)
+    if not config._is_int8_symmetric():
+        raise qz.ShrewError(qz._lib.ERR_UNSUPPORTED, "sharded per-tensor quantization is built for INT8 symmetric only")
+    amax = (absmax or qz.absmax)(w_shard)
+    dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+    return (quantize_given_amax or qz.quantize_tensor_given_amax)(w_shard, amax)
+
+
 def shard_quantized_linear(weight: torch.Tensor, bias: Optional[torch.Tensor], config, group=None) -> ShardedLinear:
-    """Quantizes this rank's rows of `weight` [N,K] on its GPU and wraps the shard.
-    Per-tensor granularity needs the whole tensor's amax, so every rank first takes the
-    max over ranks of its local amax (one scalar all-reduce) — equivalently, quantize
-    before sharding; here the per-channel case (what the sharded benchmark configs use) is direct."""
-    from .quantize import Linear, QuantGranularity, QuantizedLinear
-    if config.granularity is not QuantGranularity.PerChannel and dist.is_initialized() and dist.get_world_size(group) > 1:
-        raise NotImplementedError("sharded per-tensor quantization: quantize the full tensor first, then shard the codes")
+    """Quantizes this rank's rows of `weight` [N,K] on its GPU (`quantize_row_shard`) and wraps the shard."""
+    from .quantize import QuantizedLinear
     n = weight.shape[0]
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     n0, n1 = plan_shards(n, world).rows(rank)
-    b = None if bias is None else bias.reshape(-1)[n0:n1].contiguous()
-    ql = QuantizedLinear.from_linear(Linear(weight[n0:n1].contiguous(), b), config)
+    b = None if bias is None else bias.reshape(1, -1)[:, n0:n1].contiguous()
+    ql = QuantizedLinear.new(quantize_row_shard(weight[n0:n1].contiguous().detach(), config, group), b)
 
     def local_forward(x, out, _ql=ql):
         _ql.forward(x, out=out)

@@ -151,3 +151,24 @@ def test_bad_arguments_return_errors():
     assert L.shrewq_quantize_f32(dev.handle, None, 4, 4, 1, None, t.data_ptr()) == _lib.ERR_INVALID_ARG
     assert b"NULL" in L.shrewq_last_error(dev.handle)
     assert L.shrewq_dequantize(dev.handle, t.data_ptr(), t.data_ptr(), 4, 4, 1, 9, t.data_ptr()) == _lib.ERR_INVALID_ARG
+
+
+@pytest.mark.skipif(__import__("os").environ.get("SHREWQ_TEST_UNVALIDATED", "0") != "1",
+                    reason="entry points built from validated kernels but not yet run on a GPU; set SHREWQ_TEST_UNVALIDATED=1")
+@pytest.mark.parametrize("rows,cols,split", [(64, 128, 40), (1000, 333, 1), (7, 5, 7), (2048, 4096, 1024)])
+def test_per_tensor_quantization_of_row_shards(oracle, rows, cols, split):
+    # two "ranks" on one GPU: amax per shard, max of the two on the host (the all-reduce), then each
+    # shard quantized with the global amax == the rows of the unsplit per-tensor quantization
+    from shrew_b200.quantize import absmax, quantize_tensor_given_amax
+    w = _outlier_matrix(rows, cols, seed=rows + cols, std=0.05)
+    w[0, 0] = np.nan
+    q_ref, s_ref = oracle.np_quantize_f32(w, oracle.PER_TENSOR)
+    shards = [torch.from_numpy(w[:split].copy()).cuda(), torch.from_numpy(w[split:].copy()).cuda()]
+    amax = torch.maximum(absmax(shards[0]), absmax(shards[1]))
+    assert float(amax) == float(np.fmax.reduce(np.abs(w).reshape(-1)))
+    got = [quantize_tensor_given_amax(s, amax) for s in shards]
+    torch.cuda.synchronize()
+    q = np.concatenate([g.data.cpu().numpy().reshape(s.shape) for g, s in zip(got, shards)], axis=0)
+    np.testing.assert_array_equal(q, q_ref)
+    for g in got:
+        assert g.scales.cpu().numpy().tobytes() == s_ref.tobytes()

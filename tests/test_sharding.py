@@ -89,3 +89,67 @@ def test_sharded_forward_gloo_world2(n):
     for rank, ok, shape in res:
         assert ok, f"rank {rank}: gathered output differs from the unsharded oracle"
         assert shape == [5, n]
+
+
+# ---- per-tensor quantization of row shards: one f32 through an all-reduce(MAX) ----------------------
+def _pt_worker(rank, world, port, n, k, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import shrew_oracle as oracle
+        from shrew_b200.quantize import QuantConfig
+        from shrew_b200.sharded import quantize_row_shard
+        rng = np.random.default_rng(3)
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        w[n - 1, 0] = 0.9 if n > 1 else w[0, 0]      # the global amax sits in the LAST rank's shard
+        w[0, 1] = np.nan                             # NaN is ignored by the amax on every rank
+        n0, n1 = plan_shards(n, world).rows(rank)
+        calls = []
+
+        # stand-ins for the three kernels, from the oracle
+        def quantize(t, cfg):
+            calls.append("quantize")
+            q, s = oracle.quantize_f32(t.numpy(), 1 if cfg.granularity.value == 1 else 0)
+            return q, s
+
+        def absmax(t):
+            calls.append("absmax")
+            a = t.numpy()
+            return torch.tensor([np.fmax.reduce(np.abs(a).reshape(-1), initial=0.0)], dtype=torch.float32)
+
+        def quantize_given_amax(t, amax):
+            calls.append("given")
+            # a per-tensor quantization whose amax is the supplied one: append it to the data
+            aug = np.concatenate([t.numpy().reshape(-1), amax.numpy()]).astype(np.float32)
+            q, s = oracle.quantize_f32(aug, oracle.PER_TENSOR)
+            return q[:-1].reshape(t.shape), s
+
+        shard = torch.from_numpy(w[n0:n1].copy())
+        q_full, s_full = oracle.quantize_f32(w, oracle.PER_TENSOR)
+        q, s = quantize_row_shard(shard, QuantConfig.int8(), quantize=quantize, absmax=absmax, quantize_given_amax=quantize_given_amax)
+        ok_pt = bool(np.array_equal(q, q_full[n0:n1]) and s.tobytes() == s_full.tobytes()) and calls == ["absmax", "given"]
+        calls.clear()
+        qc_full, sc_full = oracle.quantize_f32(w, oracle.PER_CHANNEL)
+        q, s = quantize_row_shard(shard, QuantConfig.int8_per_channel(), quantize=quantize, absmax=absmax,
+                                  quantize_given_amax=quantize_given_amax)
+        ok_pc = bool(np.array_equal(q, qc_full[n0:n1]) and s.tobytes() == sc_full[n0:n1].tobytes()) and calls == ["quantize"]
+        out_q.put((rank, ok_pt, ok_pc))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n", [64, 5, 1])  # even shards, ragged shards, an empty shard on rank 1
+def test_sharded_per_tensor_quantization_gloo_world2(n):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pt_worker, args=(r, 2, port, n, 24, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok_pt, ok_pc in res:
+        assert ok_pt, f"rank {rank}: per-tensor shard differs from the rows of the unsplit quantization"
+        assert ok_pc, f"rank {rank}: per-channel shard differs"
