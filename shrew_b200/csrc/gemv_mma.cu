@@ -238,16 +238,20 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
                 gs += s_red[w][(mt * NB + 0) * 4 + r][ln];
                 us += s_red[w][(mt * NB + 1) * 4 + r][ln];
             }
+            // scale first, then undo the row's rescale: the raw sum times 2^-s alone could overflow
+            gs = gs * scales[n];
+            us = us * scales_up[n];
             if constexpr (F16) { gs = ldexpf(gs, back); us = ldexpf(us, back); }
-            gs = gs * scales[n] + (bias ? bias[n] : 0.0f);
-            us = us * scales_up[n] + (bias_up ? bias_up[n] : 0.0f);
+            gs += bias ? bias[n] : 0.0f;
+            us += bias_up ? bias_up[n] : 0.0f;
             out = silu(gs) * us;
         } else {
             float s = 0.0f;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) s += s_red[w][(mt * NB + nb) * 4 + r][ln];
+            s = s * scales[n];
             if constexpr (F16) s = ldexpf(s, back);
-            out = s * scales[n] + (bias ? bias[n] : 0.0f);
+            out = s + (bias ? bias[n] : 0.0f);
             if (epilogue == SHREWQ_EPILOGUE_RELU) out = fmaxf(out, 0.0f);
         }
         const size_t off = (size_t)m * ldy + n;
