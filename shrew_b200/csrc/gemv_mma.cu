@@ -85,6 +85,13 @@ __device__ __forceinline__ void mma_f16_16816(float *d, uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// amax exponent -> shift, the one rule of the staging kernel and of the in-CTA staging
+__device__ __forceinline__ int shift_of_amax(float a) {
+    int e = 0;
+    if (a > 0.0f) e = isinf(a) ? 127 : ilogbf(a);
+    return 14 - e;
+}
+
 // Token row m of bf16 activations -> f16 of x * 2^shift[m], shift[m] = 14 - floor(log2(amax of
 // the row)) (0 for an all-zero row; a row holding Inf uses the largest finite exponent; NaN
 // elements stay NaN and do not take part in amax).  One CTA per token row.
@@ -104,10 +111,8 @@ x_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ x16, i
         float a = s_max[0];
 #pragma unroll
         for (int w = 1; w < 8; ++w) a = fmaxf(a, s_max[w]);
-        int e = 0;
-        if (a > 0.0f) e = isinf(a) ? 127 : ilogbf(a);
-        s_shift = 14 - e;
-        shift[blockIdx.x] = 14 - e;
+        s_shift = shift_of_amax(a);
+        shift[blockIdx.x] = s_shift;
     }
     __syncthreads();
     const int sh = s_shift;
@@ -132,9 +137,15 @@ __device__ __forceinline__ void put<float>(float *p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void put<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
+constexpr int kStageMaxTokens = 4;            // in-CTA staging (XS) covers M <= 4 ...
+constexpr int kStageMaxBytes = 40 * 1024;     // ... when the f16 copy of x fits this much shared memory
+
 // MT16: token tiles of 16 (M <= 16*MT16).  K must be a multiple of 64.
-// F16: x holds f16 activations rescaled per token row by 2^xshift[m] (x_to_f16_kernel), else bf16.
-template <int MT16, typename YT, bool GATED, bool F16>
+// F16: the activations are f16, rescaled per token row by 2^shift[m]; else bf16 as given.
+// XS (with F16, MT16 == 1, M <= 4): x is the caller's bf16 tensor and every CTA converts it into its
+// own shared memory first (x_to_f16_kernel's arithmetic), so that a batch-1..4 forward is one launch
+// with no kernel-to-kernel dependency; otherwise x / xshift come from x_to_f16_kernel.
+template <int MT16, typename YT, bool GATED, bool F16, bool XS>
 __global__ void __launch_bounds__(kThreads)
 gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, const float *__restrict__ bias,
                 const int8_t *__restrict__ q_up, const float *__restrict__ scales_up,
@@ -156,11 +167,60 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
     }
     // the activation rows this lane reads for each token tile (null = padding row)
     const uint16_t *xlo[MT16], *xhi[MT16];
+    __shared__ int s_shift[kStageMaxTokens];
+    if constexpr (XS) {
+        static_assert(F16 && MT16 == 1, "in-CTA staging is the f16, single token tile case");
+        extern __shared__ __align__(16) uint16_t xs[];  // [M][K] f16 bits
+        __shared__ float s_amax[kStageMaxTokens][kWarps];
+        const int chunks = K >> 3;  // 8 values = 16 bytes
+        for (int m = 0; m < M; ++m) {
+            float a = 0.0f;
+            for (int c = threadIdx.x; c < chunks; c += kThreads) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)m * K) + c);
+                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int mt = 0; mt < MT16; ++mt) {
-        const int m = mt * 16 + g;
-        xlo[mt] = m < M ? x + (size_t)m * K + 16 * t : nullptr;
-        xhi[mt] = m + 8 < M ? x + (size_t)(m + 8) * K + 16 * t : nullptr;
+                for (int i = 0; i < 4; ++i) {
+                    a = fmaxf(a, fabsf(__uint_as_float(w4[i] << 16)));          // fmaxf drops NaN
+                    a = fmaxf(a, fabsf(__uint_as_float(w4[i] & 0xFFFF0000u)));
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+            if (lane == 0) s_amax[m][warp] = a;
+        }
+        __syncthreads();
+        if (threadIdx.x < M) {
+            float a = s_amax[threadIdx.x][0];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) a = fmaxf(a, s_amax[threadIdx.x][w]);
+            s_shift[threadIdx.x] = shift_of_amax(a);
+        }
+        __syncthreads();
+        for (int m = 0; m < M; ++m) {
+            const int sh = s_shift[m];
+            for (int c = threadIdx.x; c < chunks; c += kThreads) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)m * K) + c);
+                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+                uint32_t o4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __half lo = __float2half_rn(ldexpf(__uint_as_float(w4[i] << 16), sh));
+                    const __half hi = __float2half_rn(ldexpf(__uint_as_float(w4[i] & 0xFFFF0000u), sh));
+                    o4[i] = (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+                }
+                reinterpret_cast<uint4 *>(xs + (size_t)m * K)[c] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+        }
+        __syncthreads();
+        xlo[0] = g < M ? xs + (size_t)g * K + 16 * t : nullptr;
+        xhi[0] = nullptr;
+    } else {
+#pragma unroll
+        for (int mt = 0; mt < MT16; ++mt) {
+            const int m = mt * 16 + g;
+            xlo[mt] = m < M ? x + (size_t)m * K + 16 * t : nullptr;
+            xhi[mt] = m + 8 < M ? x + (size_t)(m + 8) * K + 16 * t : nullptr;
+        }
     }
 
     float acc[MT16][NB][4];
@@ -182,10 +242,22 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
 #pragma unroll
         for (int mt = 0; mt < MT16; ++mt) {
             const uint4 z = make_uint4(0, 0, 0, 0);
-            const uint4 l0 = xlo[mt] ? __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff)) : z;
-            const uint4 l1 = xlo[mt] ? __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff) + 1) : z;
-            const uint4 h0 = xhi[mt] ? __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff)) : z;
-            const uint4 h1 = xhi[mt] ? __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff) + 1) : z;
+            uint4 l0 = z, l1 = z, h0 = z, h1 = z;
+            if constexpr (XS) {  // shared memory: plain loads (the read-only global path does not apply)
+                if (xlo[mt]) {
+                    l0 = *reinterpret_cast<const uint4 *>(xlo[mt] + koff);
+                    l1 = *(reinterpret_cast<const uint4 *>(xlo[mt] + koff) + 1);
+                }
+            } else {
+                if (xlo[mt]) {
+                    l0 = __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff));
+                    l1 = __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff) + 1);
+                }
+                if (xhi[mt]) {
+                    h0 = __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff));
+                    h1 = __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff) + 1);
+                }
+            }
             al[mt][0] = l0.x; al[mt][1] = l0.y; al[mt][2] = l0.z; al[mt][3] = l0.w;
             al[mt][4] = l1.x; al[mt][5] = l1.y; al[mt][6] = l1.z; al[mt][7] = l1.w;
             ah[mt][0] = h0.x; ah[mt][1] = h0.y; ah[mt][2] = h0.z; ah[mt][3] = h0.w;
@@ -230,7 +302,7 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
         const int n = n0 + nb * 8 + 2 * (ln & 3) + (r & 1);
         if (m >= M || n >= N) continue;
         float out;
-        const int back = F16 ? -xshift[m] : 0;  // undo the row's power-of-two rescale
+        const int back = F16 ? -(XS ? s_shift[m] : xshift[m]) : 0;  // undo the row's power-of-two rescale
         if constexpr (GATED) {
             float gs = 0.0f, us = 0.0f;
 #pragma unroll
@@ -264,8 +336,19 @@ template <int MT16, typename YT, bool GATED, bool F16>
 void launch_one(shrewq_ctx *ctx, const ForwardArgs &a, const void *x, const int *xshift) {
     constexpr int kChan = GATED ? 8 : 8 * NB;
     const unsigned grid = (unsigned)((a.N + kChan - 1) / kChan);
-    gemv_mma_kernel<MT16, YT, GATED, F16><<<grid, kThreads, 0, ctx->stream>>>(
+    gemv_mma_kernel<MT16, YT, GATED, F16, false><<<grid, kThreads, 0, ctx->stream>>>(
         a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const uint16_t *>(x), xshift,
+        static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
+}
+
+// batch 1..4, f16: one launch, every CTA stages its own f16 copy of x in shared memory
+template <typename YT, bool GATED>
+void launch_staged(shrewq_ctx *ctx, const ForwardArgs &a) {
+    constexpr int kChan = GATED ? 8 : 8 * NB;
+    const unsigned grid = (unsigned)((a.N + kChan - 1) / kChan);
+    const size_t smem = a.M * a.K * sizeof(uint16_t);  // <= kStageMaxBytes: below the 48 KB that need no opt-in
+    gemv_mma_kernel<1, YT, GATED, true, true><<<grid, kThreads, smem, ctx->stream>>>(
+        a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const uint16_t *>(a.x), nullptr,
         static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
 }
 
@@ -300,7 +383,17 @@ int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a, bool f16) {
     if (a.M == 0 || a.N == 0) return SHREWQ_OK;
     if (!gemv_mma_supported(a))
         return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "mma gemv: needs bf16 activations, M<=64, K a multiple of 64, 16-byte alignment");
-    if (f16) {
+    if (f16 && a.M <= (size_t)kStageMaxTokens && a.M * a.K * sizeof(uint16_t) <= (size_t)kStageMaxBytes) {
+        const bool gated = a.q_up != nullptr;
+        if (a.y_dtype == SHREWQ_BF16) {
+            if (gated) launch_staged<__nv_bfloat16, true>(ctx, a);
+            else launch_staged<__nv_bfloat16, false>(ctx, a);
+        } else {
+            if (gated) launch_staged<float, true>(ctx, a);
+            else launch_staged<float, false>(ctx, a);
+        }
+        ctx->launches += 1;
+    } else if (f16) {
         // [M,K] f16 activations, then M shift words (K % 64 == 0 keeps the words aligned)
         const size_t xbytes = a.M * a.K * sizeof(__half);
         int rc = ensure_xsplit(ctx, xbytes + a.M * sizeof(int));
