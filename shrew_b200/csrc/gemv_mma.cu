@@ -40,6 +40,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "activation_f16.cuh"
 
 namespace shrewq {
 namespace {
@@ -83,40 +84,6 @@ __device__ __forceinline__ void mma_f16_16816(float *d, uint32_t a0, uint32_t a1
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// amax exponent -> shift, the one rule of the staging kernel and of the in-CTA staging
-__device__ __forceinline__ int shift_of_amax(float a) {
-    int e = 0;
-    if (a > 0.0f) e = isinf(a) ? 127 : ilogbf(a);
-    return 14 - e;
-}
-
-// Token row m of bf16 activations -> f16 of x * 2^shift[m], shift[m] = 14 - floor(log2(amax of
-// the row)) (0 for an all-zero row; a row holding Inf uses the largest finite exponent; NaN
-// elements stay NaN and do not take part in amax).  One CTA per token row.
-__global__ void __launch_bounds__(256)
-x_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ x16, int *__restrict__ shift, int K) {
-    const __nv_bfloat16 *row = x + (size_t)blockIdx.x * K;
-    __half *out = x16 + (size_t)blockIdx.x * K;
-    float amax = 0.0f;
-    for (int k = threadIdx.x; k < K; k += 256) amax = fmaxf(amax, fabsf(__bfloat162float(row[k])));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    __shared__ float s_max[8];
-    __shared__ int s_shift;
-    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float a = s_max[0];
-#pragma unroll
-        for (int w = 1; w < 8; ++w) a = fmaxf(a, s_max[w]);
-        s_shift = shift_of_amax(a);
-        shift[blockIdx.x] = s_shift;
-    }
-    __syncthreads();
-    const int sh = s_shift;
-    for (int k = threadIdx.x; k < K; k += 256) out[k] = __float2half_rn(ldexpf(__bfloat162float(row[k]), sh));
 }
 
 // D[16x8] += A[16x16] * B[16x8], bf16 operands, f32 accumulate

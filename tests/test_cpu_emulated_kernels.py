@@ -1,0 +1,278 @@
+"""CPU: the library's scalar CUDA kernels, executed thread by thread under a small stand-in for the
+CUDA execution model (tests/cpu_emu/cuda_shim.h), against the golden vectors and the oracle.
+
+The device code of the quantize / dequantize families lives in headers without launch syntax
+(shrew_b200/csrc/quantize_kernels.cuh, quantize_modes_kernels.cuh, activation_f16.cuh); g++ compiles
+them here as plain C++.  This is a check of kernel LOGIC (indexing, block and warp reductions, the
+f32 shortcut and its f64 replay, special values); it says nothing about speed and is no substitute
+for the GPU parity tests.  The INT8 symmetric kernels have run on B200s and pass the same golden
+vectors there, which is what validates the stand-in itself; the kernels of the other modes have not
+run on a GPU yet, so this is their first execution of any kind."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from tests.conftest import GOLDEN, ROOT
+from tests.test_oracle_modes import MODES
+
+EMU_DIR = os.path.join(ROOT, "tests", "cpu_emu")
+BUILD_DIR = os.path.join(EMU_DIR, "_build")
+_vp, _sz, _ci, _cu = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_uint
+
+
+def _build(name):
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    src = os.path.join(EMU_DIR, name + ".cpp")
+    out = os.path.join(BUILD_DIR, "lib" + name + ".so")
+    deps = [src, os.path.join(EMU_DIR, "cuda_shim.h")] + [
+        os.path.join(ROOT, "shrew_b200", "csrc", h) for h in ("quantize_kernels.cuh", "quantize_modes_kernels.cuh", "activation_f16.cuh")]
+    if not os.path.exists(out) or any(os.path.getmtime(d) > os.path.getmtime(out) for d in deps):
+        subprocess.run(["g++", "-std=c++20", "-O1", "-pthread", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math",
+                        "-Wno-unknown-pragmas", "-o", out, src], check=True, cwd=EMU_DIR)
+    return ctypes.CDLL(out)
+
+
+@pytest.fixture(scope="module")
+def emu():
+    L = _build("emu_quantize")
+    L.emu_quantize_rows.argtypes = [_vp, _sz, _sz, _ci, _vp, _vp]
+    L.emu_quantize_tensor.argtypes = [_vp, _sz, _cu, _vp, _vp]
+    L.emu_quantize_given_amax.argtypes = [_vp, _sz, _vp, _cu, _vp, _vp]
+    L.emu_absmax.argtypes = [_vp, _sz, _cu, _vp]
+    L.emu_dequantize.argtypes = [_vp, _vp, _sz, _sz, _ci, _ci, _ci, _cu, _vp]
+    return L
+
+
+@pytest.fixture(scope="module")
+def emu_modes():
+    L = _build("emu_quantize_modes")
+    L.emu_quantize_ex.argtypes = [_vp, _sz, _sz, _ci, _ci, _ci, _cu, _vp, _vp, _vp]
+    L.emu_dequantize_ex.argtypes = [_vp, _vp, _vp, _sz, _sz, _ci, _ci, _cu, _vp]
+    L.emu_scale_zp_to_f32.argtypes = [_vp, _vp, _ci, _sz, _vp]
+    L.emu_row_sums.argtypes = [_vp, _ci, _sz, _sz, _vp]
+    L.emu_zero_point_fix.argtypes = [_vp, _vp, _vp, _sz, _sz, _sz, _ci, _ci, _cu, _vp]
+    L.emu_x_to_f16.argtypes = [_vp, _sz, _ci, _vp, _vp]
+    return L
+
+
+def _p(a):
+    return ctypes.c_void_p(a.ctypes.data)
+
+
+def _aligned(shape, dtype, align=64):
+    """numpy array whose data pointer is `align`-byte aligned (the launcher's vector paths check it)."""
+    n = int(np.prod(shape)) if len(shape) else 1
+    raw = np.empty(n * np.dtype(dtype).itemsize + align, dtype=np.uint8)
+    off = (-raw.ctypes.data) % align
+    return raw[off:off + n * np.dtype(dtype).itemsize].view(dtype).reshape(shape)
+
+
+def _rows_cols(shape):
+    if len(shape) == 0:
+        return 1, 1
+    return int(shape[0]), int(np.prod(shape[1:], dtype=np.int64))
+
+
+def _quantize_rows(emu, w, variant):
+    rows, cols = _rows_cols(w.shape)
+    wa = _aligned(w.shape, np.float32)
+    wa[...] = w
+    q = _aligned(w.shape, np.int8)
+    q[...] = 99
+    s = np.full(rows, -1.0)
+    rc = emu.emu_quantize_rows(_p(wa), rows, cols, variant, _p(q), _p(s))
+    return rc, q, s
+
+
+# ---- INT8 symmetric (GPU-validated kernels: this validates the stand-in) ----------------------------
+@pytest.mark.parametrize("case", [c for c in GOLDEN if c["granularity"] == 1 and len(c["shape"]) >= 1],
+                         ids=lambda c: c["name"])
+def test_golden_per_channel_generic_kernel(emu, case):
+    rc, q, s = _quantize_rows(emu, case["data"], 0)
+    assert rc == 0
+    np.testing.assert_array_equal(q, case["codes"])
+    assert s.tobytes() == case["scales"].tobytes()
+
+
+@pytest.mark.parametrize("case", [c for c in GOLDEN if c["granularity"] == 0 or len(c["shape"]) == 0], ids=lambda c: c["name"])
+@pytest.mark.parametrize("grid", [1, 3])
+def test_golden_per_tensor_chain(emu, case, grid):
+    w = _aligned(case["data"].shape, np.float32)
+    w[...] = case["data"]
+    q = _aligned(w.shape, np.int8)
+    s = np.full(1, -1.0)
+    emu.emu_quantize_tensor(_p(w), w.size, grid, _p(q), _p(s))
+    np.testing.assert_array_equal(q, case["codes"])
+    assert s.tobytes() == case["scales"].tobytes()
+
+
+def _special_matrix(rows, cols, seed, scale=1.0):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((rows, cols)) * scale).astype(np.float32)
+    flat = w.reshape(-1)
+    if flat.size > 8:
+        flat[rng.integers(0, flat.size, 4)] = [np.nan, np.inf, -0.0, 0.0][: 4]
+        flat[1] = flat[0] * 0.5           # an exact .5 product when flat[0] is the row's amax? not guaranteed; ties are in the goldens
+    return w
+
+
+@pytest.mark.parametrize("variant,rows,cols", [
+    (1, 9, 32), (1, 20, 128), (2, 11, 200), (3, 9, 512), (4, 17, 1000), (5, 3, 1028), (5, 2, 2048), (6, 2, 4096),
+    (7, 2, 6000), (8, 2, 16384), (8, 1, 9000), (9, 1, 20000), (0, 7, 33), (0, 3, 5000), (0, 12, 1)])
+def test_register_tile_kernels_match_oracle(oracle, emu, variant, rows, cols):
+    for seed, scale in ((0, 1.0), (1, 1e-35), (2, 3e37)):
+        w = _special_matrix(rows, cols, seed + variant, scale)
+        if seed == 0:
+            w[rows - 1] = 0.0                      # an all-zero row: amax < 1e-30 -> scale 1.0
+        rc, q, s = _quantize_rows(emu, w, variant)
+        assert rc == 0
+        q_ref, s_ref = oracle.np_quantize_f32(w, oracle.PER_CHANNEL)
+        np.testing.assert_array_equal(q, q_ref)
+        assert s.tobytes() == s_ref.tobytes()
+
+
+def test_variant_rejects_what_the_launcher_would_not_choose(emu):
+    assert _quantize_rows(emu, np.zeros((2, 130), np.float32), 1)[0] == -1    # cols not a multiple of 4
+    assert _quantize_rows(emu, np.zeros((2, 256), np.float32), 1)[0] == -1    # too wide for 32 x 1 float4
+
+
+@pytest.mark.parametrize("n,grid", [(1, 1), (1023, 2), (4096 + 3, 3), (100000, 4)])
+def test_per_tensor_chain_and_shard_entry_points(oracle, emu, n, grid):
+    w = _special_matrix(1, n, n).reshape(-1)
+    wa = _aligned((n,), np.float32)
+    wa[...] = w
+    q = _aligned((n,), np.int8)
+    s = np.zeros(1)
+    emu.emu_quantize_tensor(_p(wa), n, grid, _p(q), _p(s))
+    q_ref, s_ref = oracle.np_quantize_f32(w, oracle.PER_TENSOR)
+    np.testing.assert_array_equal(q, q_ref)
+    assert s.tobytes() == s_ref.tobytes()
+    # two shards, each with the global amax
+    cut = n // 3
+    am = np.zeros(2, np.float32)
+    for i, part in enumerate((wa[:cut], wa[cut:])):
+        pa = _aligned(part.shape, np.float32)
+        pa[...] = part
+        emu.emu_absmax(_p(pa), pa.size, grid, ctypes.c_void_p(am.ctypes.data + 4 * i))
+    g = np.array([max(am)], np.float32)
+    assert float(g[0]) == float(np.fmax.reduce(np.abs(w), initial=0.0))
+    off = 0
+    for part in (wa[:cut], wa[cut:]):
+        pa = _aligned(part.shape, np.float32)
+        pa[...] = part
+        qs, ss = _aligned(part.shape, np.int8), np.zeros(1)
+        emu.emu_quantize_given_amax(_p(pa), pa.size, _p(g), grid, _p(qs), _p(ss))
+        np.testing.assert_array_equal(qs, q_ref[off:off + part.size])
+        assert ss.tobytes() == s_ref.tobytes()
+        off += part.size
+
+
+@pytest.mark.parametrize("rows,cols,gran", [(5, 64, 1), (7, 33, 1), (3, 100, 0), (1, 4, 0)])
+@pytest.mark.parametrize("bf16", [0, 1])
+def test_dequantize_kernels_match_oracle(oracle, emu, rows, cols, gran, bf16):
+    rng = np.random.default_rng(rows * cols)
+    q = _aligned((rows, cols), np.int8)
+    q[...] = rng.integers(-127, 128, size=(rows, cols))
+    s = (rng.random(rows if gran else 1) * 10.0 ** rng.integers(-30, 30)).astype(np.float64)
+    ref = oracle.dequantize(q, s, gran, "bf16" if bf16 else "f32")
+    for vec in ((1, 0) if cols % 4 == 0 else (0,)):
+        out = _aligned((rows, cols), np.uint16 if bf16 else np.float32)
+        assert emu.emu_dequantize(_p(q), _p(s), rows, cols, gran, bf16, vec, 2, _p(out)) == 0
+        np.testing.assert_array_equal(out, ref)
+
+
+# ---- the other modes: first execution of these kernels ---------------------------------------------------
+@pytest.mark.parametrize("case", MODES, ids=lambda c: c["name"])
+def test_modes_golden(emu_modes, case):
+    w = _aligned(case["data"].shape, np.float32)
+    w[...] = case["data"]
+    rows, cols = _rows_cols(w.shape)
+    gran = case["granularity"] if len(w.shape) else 0
+    n = rows if gran else 1
+    q = _aligned(w.shape, np.int8)
+    s, z = np.full(n, -1.0), np.full(n, -1.0)
+    emu_modes.emu_quantize_ex(_p(w), rows, cols, gran, case["bits"], case["mode"], 3, _p(q), _p(s), _p(z))
+    np.testing.assert_array_equal(q, case["codes"])
+    assert s.tobytes() == case["scales"].tobytes()
+    assert z.tobytes() == case["zps"].tobytes()
+
+
+@pytest.mark.parametrize("bits,mode", [(8, 1), (4, 0), (4, 1), (8, 0)])
+@pytest.mark.parametrize("rows,cols,gran", [(9, 300, 1), (4, 1000, 1), (3, 777, 0), (1, 5000, 0), (600, 3, 1)])
+def test_modes_match_oracle_and_round_trip(oracle, emu_modes, bits, mode, rows, cols, gran):
+    for seed, scale, shift in ((0, 1.0, 0.3), (1, 1e-33, 0.0), (2, 1e36, -2.0)):
+        w = _special_matrix(rows, cols, seed + bits + mode, 1.0)
+        w = ((w + shift) * scale).astype(np.float32)
+        wa = _aligned(w.shape, np.float32)
+        wa[...] = w
+        n = rows if gran else 1
+        q = _aligned(w.shape, np.int8)
+        s, z = np.zeros(n), np.zeros(n)
+        emu_modes.emu_quantize_ex(_p(wa), rows, cols, gran, bits, mode, 4, _p(q), _p(s), _p(z))
+        q_ref, s_ref, z_ref = oracle.np_quantize_f32_ex(w, gran, bits, mode)
+        np.testing.assert_array_equal(q, q_ref)
+        assert s.tobytes() == s_ref.tobytes() and z.tobytes() == z_ref.tobytes()
+        with np.errstate(all="ignore"):
+            ref64 = oracle.dequantize_f64_ex(q_ref, s_ref, z_ref, gran)
+            out = _aligned(w.shape, np.float32)
+            emu_modes.emu_dequantize_ex(_p(q), _p(s), _p(z), rows, cols, gran, 0, 3, _p(out))
+            np.testing.assert_array_equal(out, ref64.astype(np.float32))
+            out16 = _aligned(w.shape, np.uint16)
+            emu_modes.emu_dequantize_ex(_p(q), _p(s), _p(z), rows, cols, gran, 1, 3, _p(out16))
+            want16 = np.array([oracle.f64_to_bf16_bits(v) for v in ref64.reshape(-1)[:200]], dtype=np.uint16)
+            np.testing.assert_array_equal(out16.reshape(-1)[:200], want16)
+
+
+def test_zero_point_forward_pieces(emu_modes):
+    rng = np.random.default_rng(5)
+    M, N, K = 5, 37, 300
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    sums = np.zeros(M, np.float32)
+    emu_modes.emu_row_sums(_p(x), 0, M, K, _p(sums))
+    np.testing.assert_array_equal(sums, x.astype(np.float64).sum(axis=1).astype(np.float32))
+    xb = (x.view(np.uint32) >> 16).astype(np.uint16)          # truncated bf16 copies of x
+    emu_modes.emu_row_sums(_p(xb), 1, M, K, _p(sums))
+    xb_f = (xb.astype(np.uint32) << 16).view(np.float32)
+    np.testing.assert_allclose(sums, xb_f.astype(np.float64).sum(axis=1), rtol=1e-6)
+    scales, zps = rng.random(N) * 1e-2, np.round(rng.standard_normal(N) * 50)
+    czp = np.zeros(N, np.float32)
+    emu_modes.emu_scale_zp_to_f32(_p(scales), _p(zps), 1, N, _p(czp))
+    np.testing.assert_array_equal(czp, (scales * zps).astype(np.float32))
+    emu_modes.emu_scale_zp_to_f32(_p(scales), _p(zps), 0, N, _p(czp))
+    np.testing.assert_array_equal(czp, np.full(N, np.float32(scales[0] * zps[0])))
+    acc = rng.standard_normal((M, N)).astype(np.float32)
+    ldy = N + 3
+    for relu in (0, 1):
+        y = np.full((M, ldy), 7.0, np.float32)
+        emu_modes.emu_zero_point_fix(_p(acc), _p(czp), _p(sums), M, N, ldy, relu, 0, 2, _p(y))
+        want = acc - czp[None, :] * sums[:, None]
+        if relu:
+            want = np.maximum(want, 0.0)
+        np.testing.assert_array_equal(y[:, :N], want.astype(np.float32))
+        assert np.all(y[:, N:] == 7.0)                          # the row stride's padding is untouched
+
+
+@pytest.mark.parametrize("scale", [1e-37, 1e-12, 1.0, 6e4, 1e20, 3e38])
+def test_activation_rescale_kernel_matches_its_model(emu_modes, scale):
+    from tests.test_mma_f16_numerics import rescale_row, to_bf16
+    rng = np.random.default_rng(9)
+    M, K = 4, 1088
+    x = to_bf16((rng.standard_normal((M, K)) * scale / 4).astype(np.float32))
+    x[1] *= np.float32(1e-6)
+    x[2] = 0.0
+    x[3, 5] = np.nan
+    x = to_bf16(np.where(np.isinf(x), np.float32(1e38), x))
+    bits = (x.view(np.uint32) >> 16).astype(np.uint16)
+    x16 = np.zeros((M, K), np.uint16)
+    shift = np.zeros(M, np.int32)
+    emu_modes.emu_x_to_f16(_p(bits), M, K, _p(x16), _p(shift))
+    for m in range(M):
+        ref16, s, _ = rescale_row(x[m])
+        assert int(shift[m]) == s
+        got = x16[m].view(np.float16)
+        np.testing.assert_array_equal(np.isnan(got), np.isnan(ref16))
+        ok = ~np.isnan(ref16)
+        np.testing.assert_array_equal(got[ok], ref16[ok])
