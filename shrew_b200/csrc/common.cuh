@@ -10,6 +10,7 @@
 #include <cstring>
 
 #include "../../include/shrewq.h"
+#include "dests.cuh"
 
 namespace shrewq {
 
@@ -105,13 +106,6 @@ int launch_zero_point_fix(shrewq_ctx *ctx, const float *acc, const float *czp, c
 // stored at the output position before the elementwise op
 constexpr int kEpilogueAccumulate = 0x100;
 
-// Extra destinations of a forward: the same output slice is also stored into these buffers
-// (peer GPUs' memory, mapped into this process) — the all-gather fused into the epilogue.
-constexpr int kMaxPeers = 7;
-struct Dests {
-    void *p[kMaxPeers];
-    int n;
-};
 
 struct ForwardArgs {
     const int8_t *q;       // [N,K]

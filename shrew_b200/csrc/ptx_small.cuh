@@ -1,0 +1,58 @@
+// The few PTX instructions the warp-MMA kernels use, each behind a small function, and the
+// declaration of dynamic shared memory.  The CPU tests (tests/cpu_emu/) provide stand-ins with the
+// same names and semantics, so the kernels that call them also compile as plain C++.
+#pragma once
+
+#ifndef SHREWQ_CPU_EMU
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace shrewq {
+namespace {
+
+// 16 bytes through the read-only path, not kept in L1 (weights are read once)
+__device__ __forceinline__ uint4 ld_stream_16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// two f32 -> packed bf16x2, round to nearest even; `hi` lands in the upper half
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float hi, float lo) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+// per-half f16 subtraction a - b
+__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// D[16x8] += A[16x16] * B[16x8], bf16 operands, f32 accumulate
+__device__ __forceinline__ void mma_bf16_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D[16x8] += A[16x16] * B[16x8], f16 operands, f32 accumulate
+__device__ __forceinline__ void mma_f16_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+}  // namespace
+}  // namespace shrewq
+
+#define SHREWQ_DYNAMIC_SMEM(T, name) extern __shared__ __align__(16) T name[]
+#endif  // SHREWQ_CPU_EMU

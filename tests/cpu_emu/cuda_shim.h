@@ -1,5 +1,5 @@
-// A small stand-in for the CUDA execution model, enough to run the library's scalar kernels
-// (quantize / dequantize families) on the CPU, thread by thread.
+// A small stand-in for the CUDA execution model, enough to run the library's scalar and warp-MMA
+// kernels (quantize / dequantize families, the small-batch forward) on the CPU, thread by thread.
 //
 // TEST INFRASTRUCTURE ONLY.  Nothing in the shipped library includes this file; the product has
 // no CPU path.  The CPU tests compile the device-code headers (shrew_b200/csrc/*_kernels.cuh)
@@ -10,8 +10,10 @@
 // (std::thread) that share the kernel's `__shared__` variables (function-local statics) and meet at
 // __syncthreads() (a std::barrier).  Warp shuffles exchange through a per-warp slot array between
 // two warp barriers; every lane of a warp must take part, as with a full mask on the GPU.
+// mma.sync.m16n8k16 is computed from its documented fragment layout; the other PTX pieces the
+// warp-MMA kernels use (shrew_b200/csrc/ptx_small.cuh) have plain C++ stand-ins of the same name.
 // Not modelled: memory ordering weaker than sequential, divergence inside a warp at a shuffle,
-// dynamic shared memory, tensor-core and TMA instructions.
+// tcgen05 / TMEM / TMA instructions.
 #pragma once
 #define SHREWQ_CPU_EMU 1
 
@@ -46,7 +48,9 @@ struct Block {
     std::barrier<> all;
     std::vector<std::unique_ptr<std::barrier<>>> warp;
     std::vector<uint64_t> slots;  // one 8-byte exchange slot per thread
-    explicit Block(unsigned t) : threads(t), all(t), slots(t) {
+    std::vector<uint32_t> frag;   // eight 32-bit registers per thread: MMA operand fragments
+    std::vector<unsigned char> dyn;  // dynamic shared memory of the block
+    explicit Block(unsigned t, size_t dyn_bytes = 0) : threads(t), all(t), slots(t), frag(8 * (size_t)t), dyn(dyn_bytes + 16) {
         for (unsigned w = 0; w < (t + 31) / 32; ++w) {
             const unsigned lanes = std::min(32u, t - w * 32);
             warp.emplace_back(std::make_unique<std::barrier<>>(lanes));
@@ -60,9 +64,10 @@ inline thread_local emu_uint3 threadIdx{0, 0, 0}, blockIdx{0, 0, 0};
 inline thread_local emu_uint3 blockDim{1, 1, 1}, gridDim{1, 1, 1};
 
 namespace emu {
-// Runs `body` as a kernel of `grid` blocks of `block` threads (1-D).
-inline void launch(unsigned grid, unsigned block, const std::function<void()> &body) {
-    Block blk(block);
+// Runs `body` as a kernel of `grid` blocks of `block` threads (1-D) with `dyn_bytes` of dynamic
+// shared memory per block.
+inline void launch(unsigned grid, unsigned block, size_t dyn_bytes, const std::function<void()> &body) {
+    Block blk(block, dyn_bytes);
     std::vector<std::thread> pool;
     for (unsigned t = 0; t < block; ++t) {
         pool.emplace_back([&, t] {
@@ -80,6 +85,15 @@ inline void launch(unsigned grid, unsigned block, const std::function<void()> &b
     for (auto &th : pool) th.join();
 }
 }  // namespace emu
+
+namespace emu {
+inline void launch(unsigned grid, unsigned block, const std::function<void()> &body) { launch(grid, block, 0, body); }
+inline void *dynamic_smem() {
+    unsigned char *p = g_block->dyn.data();
+    return p + ((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15);
+}
+}  // namespace emu
+#define SHREWQ_DYNAMIC_SMEM(T, name) T *name = static_cast<T *>(emu::dynamic_smem())
 
 static inline void __syncthreads() { emu::g_block->all.arrive_and_wait(); }
 static inline void __syncwarp(unsigned = 0xFFFFFFFFu) { emu::g_block->warp[threadIdx.x >> 5]->arrive_and_wait(); }
@@ -160,3 +174,57 @@ static inline unsigned short __half_as_ushort(__half h) { unsigned short u; memc
 
 using std::max;
 using std::min;
+
+// ---- the PTX pieces of shrew_b200/csrc/ptx_small.cuh -----------------------------------------------
+static inline unsigned __byte_perm(unsigned x, unsigned y, unsigned sel) {
+    const uint64_t both = ((uint64_t)y << 32) | x;
+    unsigned out = 0;
+    for (int i = 0; i < 4; ++i) out |= (unsigned)((both >> (8 * ((sel >> (4 * i)) & 7))) & 0xFF) << (8 * i);
+    return out;
+}
+#define __expf expf
+static inline uint4 ld_stream_16(const void *p) { uint4 v; memcpy(&v, p, 16); return v; }
+static inline uint32_t pack_bf16x2_rn(float hi, float lo) {
+    return ((uint32_t)__float2bfloat16_rn(hi).bits << 16) | __float2bfloat16_rn(lo).bits;
+}
+static inline _Float16 emu_f16_of(uint32_t bits16) { uint16_t u = (uint16_t)bits16; _Float16 h; memcpy(&h, &u, 2); return h; }
+static inline uint32_t emu_bits_of(_Float16 h) { uint16_t u; memcpy(&u, &h, 2); return u; }
+static inline uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+    const _Float16 lo = emu_f16_of(a & 0xFFFF) - emu_f16_of(b & 0xFFFF), hi = emu_f16_of(a >> 16) - emu_f16_of(b >> 16);
+    return emu_bits_of(lo) | (emu_bits_of(hi) << 16);
+}
+
+// mma.sync.aligned.m16n8k16.row.col.f32.{bf16|f16}.{bf16|f16}.f32: D[16x8] += A[16x16] * B[16x8].
+// Lane (g = lane / 4, t = lane % 4) holds  a0: A[g][2t,2t+1]  a1: A[g+8][2t,2t+1]  a2: A[g][2t+8,2t+9]
+// a3: A[g+8][2t+8,2t+9];  b0: B[2t,2t+1][g]  b1: B[2t+8,2t+9][g];  d0,d1: D[g][2t,2t+1]  d2,d3: D[g+8][2t,2t+1];
+// the lower half of a register is the element with the even k.
+template <bool F16>
+static inline void emu_mma_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    emu::Block *blk = emu::g_block;
+    const unsigned me = threadIdx.x, w0 = me & ~31u, lane = me & 31u, g = lane >> 2, t = lane & 3u;
+    uint32_t *mine = &blk->frag[8 * (size_t)me];
+    mine[0] = a0; mine[1] = a1; mine[2] = a2; mine[3] = a3; mine[4] = b0; mine[5] = b1;
+    blk->warp[me >> 5]->arrive_and_wait();
+    auto val = [](uint32_t reg, unsigned odd) -> double {
+        const uint32_t h = odd ? (reg >> 16) : (reg & 0xFFFF);
+        return F16 ? (double)emu_f16_of(h) : (double)__uint_as_float(h << 16);
+    };
+    auto A = [&](unsigned row, unsigned k) { return val(blk->frag[8 * (size_t)(w0 + (row & 7) * 4 + ((k & 7) >> 1)) + (row >> 3) + 2 * (k >> 3)], k & 1); };
+    auto B = [&](unsigned k, unsigned n) { return val(blk->frag[8 * (size_t)(w0 + n * 4 + ((k & 7) >> 1)) + 4 + (k >> 3)], k & 1); };
+    float out[4];
+    for (unsigned r = 0; r < 4; ++r) {
+        const unsigned row = g + ((r & 2) ? 8 : 0), col = 2 * t + (r & 1);
+        double acc = d[r];
+        for (unsigned k = 0; k < 16; ++k) acc += A(row, k) * B(k, col);
+        out[r] = (float)acc;
+    }
+    blk->warp[me >> 5]->arrive_and_wait();  // everybody has read the fragments before they are overwritten
+    for (unsigned r = 0; r < 4; ++r) d[r] = out[r];
+}
+static inline void mma_bf16_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    emu_mma_16816<false>(d, a0, a1, a2, a3, b0, b1);
+}
+static inline void mma_f16_16816(float *d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    emu_mma_16816<true>(d, a0, a1, a2, a3, b0, b1);
+}
+

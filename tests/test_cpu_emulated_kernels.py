@@ -1,9 +1,10 @@
 """CPU: the library's scalar CUDA kernels, executed thread by thread under a small stand-in for the
 CUDA execution model (tests/cpu_emu/cuda_shim.h), against the golden vectors and the oracle.
 
-The device code of the quantize / dequantize families lives in headers without launch syntax
-(shrew_b200/csrc/quantize_kernels.cuh, quantize_modes_kernels.cuh, activation_f16.cuh); g++ compiles
-them here as plain C++.  This is a check of kernel LOGIC (indexing, block and warp reductions, the
+The device code of the quantize / dequantize families and of the warp-MMA small-batch forward lives
+in headers without launch syntax (shrew_b200/csrc/quantize_kernels.cuh, quantize_modes_kernels.cuh,
+activation_f16.cuh, gemv_mma_kernels.cuh; their few PTX instructions sit behind ptx_small.cuh); g++
+compiles them here as plain C++, with mma.sync computed from its documented fragment layout.  This is a check of kernel LOGIC (indexing, block and warp reductions, the
 f32 shortcut and its f64 replay, special values); it says nothing about speed and is no substitute
 for the GPU parity tests.  The INT8 symmetric kernels have run on B200s and pass the same golden
 vectors there, which is what validates the stand-in itself; the kernels of the other modes have not
@@ -28,7 +29,8 @@ def _build(name):
     src = os.path.join(EMU_DIR, name + ".cpp")
     out = os.path.join(BUILD_DIR, "lib" + name + ".so")
     deps = [src, os.path.join(EMU_DIR, "cuda_shim.h")] + [
-        os.path.join(ROOT, "shrew_b200", "csrc", h) for h in ("quantize_kernels.cuh", "quantize_modes_kernels.cuh", "activation_f16.cuh")]
+        os.path.join(ROOT, "shrew_b200", "csrc", h) for h in ("quantize_kernels.cuh", "quantize_modes_kernels.cuh", "activation_f16.cuh",
+                                                              "gemv_mma_kernels.cuh", "ptx_small.cuh", "dests.cuh")]
     if not os.path.exists(out) or any(os.path.getmtime(d) > os.path.getmtime(out) for d in deps):
         subprocess.run(["g++", "-std=c++20", "-O1", "-pthread", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math",
                         "-Wno-unknown-pragmas", "-o", out, src], check=True, cwd=EMU_DIR)
@@ -276,3 +278,102 @@ def test_activation_rescale_kernel_matches_its_model(emu_modes, scale):
         np.testing.assert_array_equal(np.isnan(got), np.isnan(ref16))
         ok = ~np.isnan(ref16)
         np.testing.assert_array_equal(got[ok], ref16[ok])
+
+
+# ---- the warp-MMA small-batch forward (never run on a GPU): whole kernels, mma.sync emulated --------
+@pytest.fixture(scope="module")
+def emu_mma():
+    L = _build("emu_gemv_mma")
+    L.emu_gemv_mma.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci, _vp]
+    return L
+
+
+def _bf16_bits(x32):
+    """f32 -> (bf16 bits, the bf16 values as f32), round to nearest even"""
+    b = np.ascontiguousarray(x32, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    b = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+    return b, (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def _mma_forward(emu_mma, q, scales, bias, x_bits, f16, y_bf16, relu=False, up=None, ldy=None):
+    N, K = q.shape
+    M = x_bits.shape[0]
+    ldy = ldy or N
+    qa = _aligned(q.shape, np.int8)
+    qa[...] = q
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    y = np.full((M, ldy), 7.0, np.float32) if not y_bf16 else np.full((M, ldy), 0x4100, np.uint16)
+    s32 = scales.astype(np.float32)
+    staged = ctypes.c_int(-1)
+    if up is None:
+        args = (_p(qa), _p(s32), None if bias is None else _p(bias), None, None, None)
+    else:
+        qu = _aligned(q.shape, np.int8)
+        qu[...] = up[0]
+        su = up[1].astype(np.float32)
+        args = (_p(qa), _p(s32), None if bias is None else _p(bias), _p(qu), _p(su), None if up[2] is None else _p(up[2]))
+    rc = emu_mma.emu_gemv_mma(*args, _p(xa), _p(y), M, N, K, ldy, 1 if relu else 0, int(f16), int(y_bf16), ctypes.byref(staged))
+    assert rc == 0
+    return y, staged.value
+
+
+@pytest.mark.parametrize("f16", [0, 1], ids=["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K", [(1, 16, 64), (1, 40, 512), (3, 21, 128), (4, 16, 5120), (5, 16, 64), (16, 32, 192),
+                                   (17, 24, 128), (33, 16, 128), (64, 17, 64)])
+def test_warp_mma_forward_matches_oracle(oracle, emu_mma, f16, M, N, K):
+    rng = np.random.default_rng(M * 1000 + N + K)
+    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    scales = rng.random(N) * 1e-2 + 1e-4
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
+    y, staged = _mma_forward(emu_mma, q, scales, bias, x_bits, f16, y_bf16=False, relu=True, ldy=N + 5)
+    assert staged == int(bool(f16) and M <= 4 and M * K * 2 <= 40960)
+    assert oracle.rel_err(y[:, :N], ref) < 2e-6        # exact products, f32-level accumulation
+    assert np.all(y[:, N:] == 7.0)                     # nothing written outside [M, N]
+    y16, _ = _mma_forward(emu_mma, q, scales, None, x_bits, f16, y_bf16=True)
+    ref_nb = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, None, x)
+    got = (y16.astype(np.uint32) << 16).view(np.float32)
+    assert oracle.rel_err(got, ref_nb) < 1e-2          # the bf16 output rounding
+
+
+@pytest.mark.parametrize("f16", [0, 1], ids=["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K", [(2, 24, 128), (12, 9, 192)])
+def test_warp_mma_gate_up_matches_oracle(oracle, emu_mma, f16, M, N, K):
+    rng = np.random.default_rng(N + K)
+    qg, qu = (rng.integers(-127, 128, size=(N, K)).astype(np.int8) for _ in range(2))
+    sg, su = rng.random(N) * 1e-2 + 1e-4, rng.random(N) * 1e-2 + 1e-4
+    bg = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    g = oracle.np_linear_forward(qg, sg, 1, bg, x).astype(np.float64)
+    u = oracle.np_linear_forward(qu, su, 1, None, x).astype(np.float64)
+    ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    y, _ = _mma_forward(emu_mma, qg, sg, bg, x_bits, f16, y_bf16=False, up=(qu, su, None))
+    assert oracle.rel_err(y, ref) < 1e-5
+
+
+@pytest.mark.parametrize("rows", [3, 7], ids=["staged_in_kernel", "staging_kernel"])
+def test_warp_mma_f16_activation_range(oracle, emu_mma, rows):
+    # rows of very different magnitude, far outside f16's range, each rescaled by its own power of two
+    rng = np.random.default_rng(2)
+    N, K = 16, 256
+    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    scales = rng.random(N) * 1e-3 + 1e-5
+    x = rng.standard_normal((7, K)).astype(np.float32)
+    x *= np.array([1e-25, 1e30, 0.0, 3e4, 1e-12, 1.0, 1e20], np.float32)[:, None]
+    x_bits, xb = _bf16_bits(x[:rows])
+    y, staged = _mma_forward(emu_mma, q, scales, None, x_bits, 1, y_bf16=False)
+    assert staged == int(rows <= 4)
+    ref = oracle.np_linear_forward(q, scales, 1, None, xb)
+    for m in range(rows):
+        assert oracle.rel_err(y[m:m + 1], ref[m:m + 1]) < 2e-6, m
+
+
+def test_warp_mma_refuses_unsupported_shapes(emu_mma):
+    q = _aligned((16, 96), np.int8)
+    x = _aligned((2, 96), np.uint16)
+    y = np.zeros((2, 16), np.float32)
+    s = np.ones(16, np.float32)
+    st = ctypes.c_int(0)
+    assert emu_mma.emu_gemv_mma(_p(q), _p(s), None, None, None, None, _p(x), _p(y), 2, 16, 96, 16, 0, 0, 0, ctypes.byref(st)) == -1
