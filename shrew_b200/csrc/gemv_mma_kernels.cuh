@@ -38,7 +38,7 @@
 //
 // Device code only (no launch syntax, no runtime calls, PTX behind ptx_small.cuh): it also compiles
 // as plain C++ against the CUDA stand-in of the CPU tests (tests/cpu_emu/), which run these
-// kernels with an emulated mma.sync and compare them with the oracle.
+// kernels with an emulated mma.sync and compare their results with the reference arithmetic.
 #pragma once
 
 #include "../../include/shrewq.h"
