@@ -16,14 +16,6 @@ namespace shrewq {
 
 constexpr int kErrLen = 512;
 
-// Device-visible record a kernel writes when one of its bounded waits runs out.
-struct DeviceStatus {
-    unsigned int timeout_flag;  // 0 = fine; otherwise a code naming the wait that gave up
-    unsigned int where;         // (blockIdx.x << 8) | role
-    unsigned int stage;
-    unsigned int parity;
-};
-
 }  // namespace shrewq
 
 // Opaque in the ABI.
@@ -101,10 +93,6 @@ int launch_scale_zp_to_f32(shrewq_ctx *ctx, const double *scales, const double *
 int launch_row_sums(shrewq_ctx *ctx, const void *x, int x_dtype, size_t M, size_t K, float *sums);
 int launch_zero_point_fix(shrewq_ctx *ctx, const float *acc, const float *czp, const float *xsum, size_t M, size_t N,
                           size_t ldy, int relu, int y_dtype, void *y);
-
-// internal epilogue flag (above the public SHREWQ_EPILOGUE_* values): add the f32 value already
-// stored at the output position before the elementwise op
-constexpr int kEpilogueAccumulate = 0x100;
 
 
 struct ForwardArgs {
