@@ -200,7 +200,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     using C = Cfg<TOK, KSUB>;
     constexpr int kChan = GATED ? 64 : 128;  // output channels per CTA
     TRACE_INIT
-    extern __shared__ uint8_t smem_raw[];
+    SHREWQ_DYNAMIC_SMEM(uint8_t, smem_raw);
     // 1024-byte alignment: required by the 128-byte swizzle with base_offset 0
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *bar_area = smem + C::kStages * C::kStageBytes;

@@ -19,12 +19,15 @@
 
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
 #include <barrier>
 #include <functional>
+#include <map>
 #include <memory>
+#include <mutex>
 #include <thread>
 #include <vector>
 
@@ -49,13 +52,21 @@ struct Block {
     std::vector<std::unique_ptr<std::barrier<>>> warp;
     std::vector<uint64_t> slots;  // one 8-byte exchange slot per thread
     std::vector<uint32_t> frag;   // eight 32-bit registers per thread: MMA operand fragments
-    std::vector<unsigned char> dyn;  // dynamic shared memory of the block
-    explicit Block(unsigned t, size_t dyn_bytes = 0) : threads(t), all(t), slots(t), frag(8 * (size_t)t), dyn(dyn_bytes + 16) {
+    unsigned char *dyn = nullptr;    // dynamic shared memory of the block, 256 KiB aligned: like real shared
+    size_t dyn_bytes = 0;            // addresses, its offsets fit the 18 address bits a matrix descriptor keeps
+    std::mutex mu;                   // serialises the modelled mbarrier / named-barrier bookkeeping
+    std::vector<uint32_t> tmem;      // tensor memory: 128 lanes x 512 columns of 32 bits (allocated on first use)
+    std::map<int, std::unique_ptr<std::barrier<>>> named;  // bar.sync id -> barrier
+    explicit Block(unsigned t, size_t dyn_b = 0) : threads(t), all(t), slots(t), frag(8 * (size_t)t), dyn_bytes(dyn_b) {
         for (unsigned w = 0; w < (t + 31) / 32; ++w) {
             const unsigned lanes = std::min(32u, t - w * 32);
             warp.emplace_back(std::make_unique<std::barrier<>>(lanes));
         }
+        dyn = static_cast<unsigned char *>(std::aligned_alloc(size_t(1) << 18, size_t(1) << 18));
+        memset(dyn, 0xA5, size_t(1) << 18);  // shared memory starts with whatever was there
     }
+    ~Block() { std::free(dyn); }
+    Block(const Block &) = delete;
 };
 inline thread_local Block *g_block = nullptr;
 }  // namespace emu
@@ -66,7 +77,7 @@ inline thread_local emu_uint3 blockDim{1, 1, 1}, gridDim{1, 1, 1};
 namespace emu {
 // Runs `body` as a kernel of `grid` blocks of `block` threads (1-D) with `dyn_bytes` of dynamic
 // shared memory per block.
-inline void launch(unsigned grid, unsigned block, size_t dyn_bytes, const std::function<void()> &body) {
+inline void launch3(unsigned gx, unsigned gy, unsigned gz, unsigned block, size_t dyn_bytes, const std::function<void()> &body) {
     Block blk(block, dyn_bytes);
     std::vector<std::thread> pool;
     for (unsigned t = 0; t < block; ++t) {
@@ -74,24 +85,26 @@ inline void launch(unsigned grid, unsigned block, size_t dyn_bytes, const std::f
             g_block = &blk;
             threadIdx = emu_uint3{t, 0, 0};
             blockDim = emu_uint3{block, 1, 1};
-            gridDim = emu_uint3{grid, 1, 1};
-            for (unsigned b = 0; b < grid; ++b) {
-                blockIdx = emu_uint3{b, 0, 0};
-                body();
-                blk.all.arrive_and_wait();  // the next block reuses the shared variables
-            }
+            gridDim = emu_uint3{gx, gy, gz};
+            for (unsigned z = 0; z < gz; ++z)
+                for (unsigned y = 0; y < gy; ++y)
+                    for (unsigned x = 0; x < gx; ++x) {
+                        blockIdx = emu_uint3{x, y, z};
+                        body();
+                        blk.all.arrive_and_wait();  // the next block reuses the shared variables
+                    }
         });
     }
     for (auto &th : pool) th.join();
+}
+inline void launch(unsigned grid, unsigned block, size_t dyn_bytes, const std::function<void()> &body) {
+    launch3(grid, 1, 1, block, dyn_bytes, body);
 }
 }  // namespace emu
 
 namespace emu {
 inline void launch(unsigned grid, unsigned block, const std::function<void()> &body) { launch(grid, block, 0, body); }
-inline void *dynamic_smem() {
-    unsigned char *p = g_block->dyn.data();
-    return p + ((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15);
-}
+inline void *dynamic_smem() { return g_block->dyn; }
 }  // namespace emu
 #define SHREWQ_DYNAMIC_SMEM(T, name) T *name = static_cast<T *>(emu::dynamic_smem())
 

@@ -377,3 +377,112 @@ def test_warp_mma_refuses_unsupported_shapes(emu_mma):
     s = np.ones(16, np.float32)
     st = ctypes.c_int(0)
     assert emu_mma.emu_gemv_mma(_p(q), _p(s), None, None, None, None, _p(x), _p(y), 2, 16, 96, 16, 0, 0, 0, ctypes.byref(st)) == -1
+
+
+# ---- the tcgen05 forward kernel: mbarriers, TMA, tensor memory and tcgen05.mma modelled ---------------
+# (tests/cpu_emu/cuda_shim_tcgen05.h).  This kernel has passed its parity tests on B200s; that it
+# also produces the oracle's results on top of the model is what ties the model to the hardware.  The
+# variants below that have NOT run on a GPU yet are marked.
+@pytest.fixture(scope="module")
+def emu_tc():
+    L = _build("emu_gemm_tcgen05")
+    L.emu_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci, _ci, _ci, _ci]
+    return L
+
+
+def _tc_forward(emu_tc, q, scales, bias, x_bits, tok, groups, splits=1, y_bf16=False, epilogue=0, up=None, ldy=None,
+                tile_list=0, y_init=None):
+    N, K = q.shape
+    M = x_bits.shape[0]
+    ldy = ldy or N
+    qa = _aligned(q.shape, np.int8)
+    qa[...] = q
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    if y_init is not None:
+        y = y_init.copy()
+    else:
+        y = np.full((M, ldy), 0x4100, np.uint16) if y_bf16 else np.full((M, ldy), 7.0, np.float32)
+    s32 = scales.astype(np.float32)
+    if up is None:
+        args = (_p(qa), _p(s32), None if bias is None else _p(bias), None, None, None)
+    else:
+        qu = _aligned(q.shape, np.int8)
+        qu[...] = up[0]
+        su = up[1].astype(np.float32)
+        args = (_p(qa), _p(s32), None if bias is None else _p(bias), _p(qu), _p(su), None if up[2] is None else _p(up[2]))
+    rc = emu_tc.emu_gemm_tcgen05(*args, _p(xa), _p(y), M, N, K, ldy, epilogue, int(y_bf16), tok, groups, splits, tile_list)
+    assert rc == 0, f"emulated kernel returned {rc} (-2: a bounded wait gave up, -3: a tile counter was left set)"
+    return y
+
+
+def _tc_case(M, N, K, seed):
+    rng = np.random.default_rng(seed)
+    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    scales = rng.random(N) * 1e-2 + 1e-4
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    return q, scales, bias, x_bits, x
+
+
+# every (token tile, converter groups) pair the launcher can choose: 7 pipeline stages at 16 and 32
+# tokens, 6 at 64, 4 at 128, 5 at 256; converter groups own stages (stage s -> group s % G)
+@pytest.mark.parametrize("groups", [1, 2, 3])
+@pytest.mark.parametrize("tok,M,N,K", [(16, 5, 130, 1088), (32, 30, 128, 960), (64, 64, 200, 1024), (128, 100, 129, 1280),
+                                       (256, 300, 140, 704)])
+def test_tcgen05_forward_matches_oracle(oracle, emu_tc, tok, groups, M, N, K):
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, tok + groups)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
+    y = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, groups, epilogue=1, ldy=N + 3)
+    assert oracle.rel_err(y[:, :N], ref) < 2e-6
+    assert np.all(y[:, N:] == 7.0)
+
+
+@pytest.mark.parametrize("tok,M,N,K,splits", [(16, 3, 128, 1024, 4), (64, 40, 130, 768, 3), (32, 20, 64, 1100 // 4 * 4, 2),
+                                              (128, 100, 200, 2048, 3),      # large-tile split-K: not yet run on a GPU
+                                              (256, 260, 128, 1024, 2)])     # large-tile split-K: not yet run on a GPU
+def test_tcgen05_split_k(oracle, emu_tc, tok, M, N, K, splits):
+    K = K // 16 * 16
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, splits)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
+    y = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, 3, splits=splits)
+    assert oracle.rel_err(y, ref) < 2e-6
+    y2 = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, 3, splits=splits)
+    np.testing.assert_array_equal(y, y2)               # slices are summed in split order: same bits every run
+
+
+@pytest.mark.parametrize("tok,M,N,K,splits", [(16, 8, 100, 512, 1), (64, 50, 64, 640, 2), (128, 128, 130, 256, 1), (256, 257, 70, 320, 1)])
+def test_tcgen05_gate_up_tile(oracle, emu_tc, tok, M, N, K, splits):
+    rng = np.random.default_rng(tok)
+    qg, qu = (rng.integers(-127, 128, size=(N, K)).astype(np.int8) for _ in range(2))
+    sg, su = rng.random(N) * 1e-2 + 1e-4, rng.random(N) * 1e-2 + 1e-4
+    bg, bu = ((rng.standard_normal(N) * 0.1).astype(np.float32) for _ in range(2))
+    x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    g = oracle.np_linear_forward(qg, sg, 1, bg, x).astype(np.float64)
+    u = oracle.np_linear_forward(qu, su, 1, bu, x).astype(np.float64)
+    ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    y = _tc_forward(emu_tc, qg, sg, bg, x_bits, tok, 3, splits=splits, up=(qu, su, bu))
+    assert oracle.rel_err(y, ref) < 1e-5
+
+
+def test_tcgen05_bf16_output_and_accumulate_epilogue(oracle, emu_tc):
+    q, scales, bias, x_bits, x = _tc_case(70, 130, 384, 11)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
+    y16 = _tc_forward(emu_tc, q, scales, bias, x_bits, 128, 3, y_bf16=True)
+    assert oracle.rel_err((y16.astype(np.uint32) << 16).view(np.float32), ref) < 1e-2
+    # internal accumulate flag (0x100): adds what the output already holds before the elementwise op;
+    # used by the two-pass f32-activation route, which has not run on a GPU yet
+    prev = np.random.default_rng(1).standard_normal((70, 130)).astype(np.float32)
+    y = _tc_forward(emu_tc, q, scales, bias, x_bits, 128, 3, epilogue=0x100 | 1, y_init=prev)
+    assert oracle.rel_err(y, np.maximum(ref + prev, 0.0)) < 2e-6
+    y = _tc_forward(emu_tc, q, scales, bias, x_bits, 64, 3, splits=2, epilogue=0x100, y_init=prev)
+    assert oracle.rel_err(y, ref + prev) < 2e-6
+
+
+def test_tcgen05_tile_list_grid(oracle, emu_tc):
+    # the 1-D tile list of the two-launch tail-split scheme (not yet run on a GPU)
+    q, scales, bias, x_bits, x = _tc_case(300, 260, 512, 5)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
+    for splits in (1, 2):
+        y = _tc_forward(emu_tc, q, scales, bias, x_bits, 128, 3, splits=splits, tile_list=1)
+        assert oracle.rel_err(y, ref) < 2e-6
