@@ -79,3 +79,9 @@ extern "C" int emu_dequantize(const int8_t *q, const double *scales, size_t rows
         emu::launch(grid, 256, [&] { dequantize_kernel<float>(q, scales, rows, cols, per_channel, static_cast<float *>(out), vec_ok); });
     return 0;
 }
+
+// f32 activations -> bf16 hi + bf16 lo (the tensor-core route for f32 inputs)
+extern "C" int emu_split_f32(const float *x, size_t n, unsigned grid, void *hi, void *lo) {
+    if (n) emu::launch(grid, 256, [&] { split_f32_kernel(x, n, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo)); });
+    return 0;
+}

@@ -486,3 +486,23 @@ def test_tcgen05_tile_list_grid(oracle, emu_tc):
     for splits in (1, 2):
         y = _tc_forward(emu_tc, q, scales, bias, x_bits, 128, 3, splits=splits, tile_list=1)
         assert oracle.rel_err(y, ref) < 2e-6
+
+
+def test_f32_activations_through_two_tensor_core_passes(oracle, emu, emu_tc):
+    # forward_f32_on_tensor_cores (not yet run on a GPU): x = hi + lo in bf16, the hi pass writes
+    # scale * acc, the lo pass adds its own on top together with bias and the elementwise op
+    emu.emu_split_f32.argtypes = [_vp, _sz, _cu, _vp, _vp]
+    rng = np.random.default_rng(3)
+    M, N, K = 90, 140, 784 // 16 * 16
+    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    scales = rng.random(N) * 1e-2 + 1e-4
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    x = rng.random((M, K)).astype(np.float32)                 # U(0,1) like the MLP config's inputs
+    hi, lo = np.zeros((M, K), np.uint16), np.zeros((M, K), np.uint16)
+    emu.emu_split_f32(_p(x), x.size, 3, _p(hi), _p(lo))
+    hi_f, lo_f = (hi.astype(np.uint32) << 16).view(np.float32), (lo.astype(np.uint32) << 16).view(np.float32)
+    assert np.max(np.abs((hi_f.astype(np.float64) + lo_f) - x)) <= 2.0 ** -16 * np.max(np.abs(x))
+    y1 = _tc_forward(emu_tc, q, scales, None, hi, 128, 3, epilogue=0)
+    y2 = _tc_forward(emu_tc, q, scales, bias, lo, 128, 3, epilogue=0x100 | 1, y_init=y1)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
+    assert oracle.rel_err(y2, ref) < 1e-4                      # the f32 path's tolerance
