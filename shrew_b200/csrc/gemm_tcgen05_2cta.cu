@@ -1,412 +1,13 @@
-// Quantized Linear forward on CTA PAIRS (tcgen05.mma.cta_group::2), sm_100a only.
-//
-// STATUS: built and compiled, NOT yet run on a GPU.  Never chosen automatically;
-// shrewq_force_kernel("tcgen05-2cta") selects it (bf16 activations, M >= 1).
-//
-// Why: in the single-CTA kernel (gemm_tcgen05.cu) one thread issues every MMA; at ~80 cycles
-// per issue plus ~380 cycles of wait / fence / commit per pipeline stage it needs ~700 cycles
-// for a 128x256x64 block whose tensor work is 512 cycles.  A CTA pair doubles the work of each
-// issued instruction (256 channels x 256 tokens x 16 k), and because each CTA of the pair
-// holds only HALF of the activation tile (128 tokens), a 128-wide k stage fits four times in
-// shared memory, which halves the per-stage overhead as well: ~1020 issue cycles for 1024
-// cycles of tensor work per stage.
-//
-// Mapping (cluster of 2 CTAs along the channel dimension, rank r = 0 leader, 1 peer):
-//   A  = 256 channels: CTA r converts rows n0 + 128 r .. +127 into ITS tensor memory.
-//   B  = 256 tokens:   CTA r TMA-loads tokens m0 + 128 r .. +127 into ITS shared memory; the
-//        pair MMA reads both halves through the same descriptor offset.
-//   D  = 256 x 256 f32: CTA r's tensor memory holds its 128 channels x all 256 tokens.
-// Barriers (mbarriers in each CTA's shared memory, same offsets in both):
-//   wfull[s]  local : the CTA's own INT8 sub-blocks landed (plain TMA)          -> converters
-//   xfull[s]  leader: the activation halves of BOTH CTAs landed (TMA .cta_group::2 completing
-//                     on the leader's barrier; the leader expects the bytes of both)
-//   aready[s] leader: 8 converter warps (4 per CTA) wrote and fenced their A stage (remote
-//                     arrive from the peer)                                        -> MMA issuer
-//   empty[s]  both  : tcgen05.commit.cta_group::2, one commit per CTA's barrier    -> producers
-//   accfull   both  : the same pair of commits after the last stage              -> epilogues
-// Tensor memory is allocated and freed by both CTAs with the cta_group::2 forms, with a
-// cluster barrier before the free.  Every mbarrier wait is bounded as in the single-CTA
-// kernel; the cluster barriers are reached by every thread on every path.
+// Host side of the CTA-pair forward (device code and its description: gemm_tcgen05_2cta_kernels.cuh).
 #include <cuda.h>
 
 #include <cstdlib>
 
 #include "common.cuh"
+#include "gemm_tcgen05_2cta_kernels.cuh"
 
 namespace shrewq {
 namespace {
-
-constexpr int kLanes = 128;     // TMEM lanes = weight rows per CTA
-constexpr int kTokHalf = 128;   // tokens per CTA (half of the pair's tile)
-constexpr int kTokPair = 256;   // MMA N
-constexpr int kBlockK = 64;     // k per sub-block
-constexpr int kSub = 2;         // sub-blocks per stage (128 k)
-constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
-constexpr int kGroups = 3;      // converter groups of 4 warps
-constexpr int kThreads = 64 + 128 * kGroups;
-constexpr int kWSub = kLanes * kBlockK;          // 8192 B of codes
-constexpr int kXSub = kTokHalf * kBlockK * 2;    // 16384 B of bf16 activations
-constexpr int kStageBytes = kSub * (kWSub + kXSub);  // 49152
-constexpr int kXOff = kSub * kWSub;
-constexpr int kAColsPerStage = kSub * (kBlockK / 2);  // 64
-constexpr int kABase = kTokPair;                      // D occupies columns [0,256)
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
-constexpr uint32_t kSpinFast = 1u << 14;
-constexpr uint32_t kSpinSlow = 1u << 21;
-static_assert(kABase + kStages * kAColsPerStage <= 512, "TMEM columns");
-static_assert(kSmemBytes <= 227 * 1024, "shared memory");
-
-struct Ctl {
-    volatile int abort_flag;
-    uint32_t tmem_base;
-};
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
-// address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
-    return r;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// arrive on a barrier of any CTA of the cluster (address from map_to_cta)
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role,
-                                            uint32_t stage) {
-    for (uint32_t i = 0; i < kSpinFast; ++i)
-        if (mbar_try(bar, parity)) return true;
-    for (uint32_t i = 0; i < kSpinSlow; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if (ctl->abort_flag) return false;
-        __nanosleep(100);
-    }
-    ctl->abort_flag = 1;
-    if (atomicCAS(&st->timeout_flag, 0u, 2u) == 0u) {
-        st->where = (blockIdx.x << 8) | role;
-        st->stage = stage;
-        st->parity = parity;
-    }
-    return false;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role,
-                                          uint32_t stage) {
-    if (mbar_try(bar, parity)) return true;
-    if (mbar_try(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, ctl, st, role, stage);
-}
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role,
-                                               uint32_t stage) {
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, st, role, stage) ? 1 : 0;
-    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-    if (ok) ok = mbar_try(bar, parity) ? 1 : 0;  // every lane acquires the phase itself
-    return __all_sync(0xFFFFFFFFu, ok) != 0;
-}
-
-// plain TMA load completing on a barrier of this CTA
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-// pair TMA load: the data lands in THIS CTA's shared memory, the bytes complete on the LEADER
-// CTA's barrier (same offset in CTA 0 of the cluster)
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void *tmap, int c0, int c1, uint32_t bar_local) {
-    const uint32_t bar_leader = map_to_cta(bar_local, 0);
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(tmap), "r"(bar_leader), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// completion of all prior MMAs of this thread arrives on the barrier at this offset in BOTH CTAs:
-// two commits, one per CTA's copy of the barrier (each commit arrives once on its barrier when
-// every MMA issued so far has completed)
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-    const uint32_t b0 = map_to_cta(bar, 0), b1 = map_to_cta(bar, 1);
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(b0) : "memory");
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(b1) : "memory");
-}
-
-// D[256 x 256] (+)= A[256 x 16, TMEM of both CTAs] * B[256 x 16, shared memory of both CTAs]^T
-__device__ __forceinline__ void tc_mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                               uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t *r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t *r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void cvt_i8x4_bf16(uint32_t w, uint32_t &lo, uint32_t &hi) {
-    const uint32_t u = w ^ 0x80808080u;
-    const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440)) - 8388736.0f;
-    const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7441)) - 8388736.0f;
-    const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7442)) - 8388736.0f;
-    const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)) - 8388736.0f;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(f1), "f"(f0));
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(f3), "f"(f2));
-}
-
-// K-major, 128-byte swizzle, 8-row groups 1024 B apart, descriptor version 1
-__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-template <typename YT>
-__device__ __forceinline__ void store_out(YT *p, float v);
-template <>
-__device__ __forceinline__ void store_out<float>(float *p, float v) { *p = v; }
-template <>
-__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
-
-struct Operands2 {
-    const float *scales;
-    const float *bias;
-};
-
-template <typename YT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                              Operands2 ops, YT *__restrict__ y, Dests extra, int M, int N, int K, size_t ldy,
-                              int epilogue, DeviceStatus *status) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *bar_area = smem + kStages * kStageBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(bar_area);
-    Ctl *ctl = reinterpret_cast<Ctl *>(bar_area + 512);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();          // 0 = leader
-    const int pair = blockIdx.x >> 1;
-    const int n0 = pair * 2 * kLanes + (int)rank * kLanes;       // this CTA's first channel
-    const int m0 = blockIdx.y * kTokPair + (int)rank * kTokHalf;  // this CTA's first token (B half)
-    const int m0_pair = blockIdx.y * kTokPair;
-    const int rounds = (K + kBlockK * kSub - 1) / (kBlockK * kSub);
-    // barrier byte offsets
-    constexpr uint32_t kWFull = 0, kXFull = kStages * 8, kAready = 2 * kStages * 8, kEmpty = 3 * kStages * 8,
-                       kAcc = 4 * kStages * 8;
-    const uint32_t bars_u32 = smem_u32(bars);
-    const uint32_t smem_base = smem_u32(smem);
-
-    if (threadIdx.x == 0) {
-        ctl->abort_flag = 0;
-        ctl->tmem_base = 0;
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(bars_u32 + kWFull + s * 8, 1);
-            mbar_init(bars_u32 + kXFull + s * 8, 1);    // used in the leader only
-            mbar_init(bars_u32 + kAready + s * 8, 8);   // used in the leader only: 4 warps x 2 CTAs
-            mbar_init(bars_u32 + kEmpty + s * 8, 1);
-        }
-        mbar_init(bars_u32 + kAcc, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&ctl->tmem_base))
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    // both CTAs' barriers exist before anyone signals across the pair
-    cluster_arrive();
-    cluster_wait();
-    tc_fence_after();
-    const uint32_t tmem_base = ctl->tmem_base;
-
-    if (warp == 0) {
-        // ---------------- TMA producer (one thread per CTA) ----------------
-        if (lane == 0) {
-            uint32_t s = 0, ph = 1;
-            uint32_t dst = smem_base;
-            int kc = 0;
-            for (int i = 0; i < rounds; ++i) {
-                if (!mbar_wait(bars_u32 + kEmpty + s * 8, ph, ctl, status, 0, s)) break;
-                const uint32_t wb = bars_u32 + kWFull + s * 8, xb = bars_u32 + kXFull + s * 8;
-                mbar_expect_tx(wb, kSub * kWSub);
-                if (rank == 0) mbar_expect_tx(xb, 2 * kSub * kXSub);  // the halves of both CTAs
-#pragma unroll
-                for (int j = 0; j < kSub; ++j) {
-                    tma_load_2d(dst + j * kWSub, &tmap_w, kc + j * kBlockK, n0, wb);
-                    tma_load_2d_pair(dst + kXOff + j * kXSub, &tmap_x, kc + j * kBlockK, m0, xb);
-                }
-                kc += kSub * kBlockK;
-                dst += kStageBytes;
-                if (++s == kStages) { s = 0; ph ^= 1; dst = smem_base; }
-            }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer (one thread of the leader CTA) ----------------
-        if (lane == 0 && rank == 0) {
-            // D=f32, A=bf16 (K-major, TMEM), B=bf16 (K-major), M=256 (two CTAs), N=256
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTokPair >> 3) << 17) |
-                                       ((uint32_t)((2 * kLanes) >> 4) << 24);
-            const uint64_t bdesc0 = make_b_desc(smem_base + kXOff);
-            const uint32_t a0 = tmem_base + kABase;
-            uint32_t s = 0, ph = 0, a_tmem = a0;
-            uint64_t bdesc = bdesc0;
-            bool ok = true;
-            for (int i = 0; i < rounds; ++i) {
-                ok = mbar_wait(bars_u32 + kAready + s * 8, ph, ctl, status, 2, s) &&
-                     mbar_wait(bars_u32 + kXFull + s * 8, ph, ctl, status, 1, s);
-                if (!ok) break;
-                tc_fence_after();
-#pragma unroll
-                for (int j = 0; j < kSub; ++j) {
-#pragma unroll
-                    for (int jj = 0; jj < kBlockK / kUmmaK; ++jj)
-                        tc_mma_ts_pair(tmem_base, a_tmem + j * (kBlockK / 2) + jj * (kUmmaK / 2),
-                                       bdesc + (uint64_t)((j * kXSub + jj * kUmmaK * 2) >> 4), idesc,
-                                       (i > 0 || j > 0 || jj > 0) ? 1u : 0u);
-                }
-                tc_commit_pair(bars_u32 + kEmpty + s * 8);  // frees stage s in both CTAs
-                a_tmem += kAColsPerStage;
-                bdesc += (uint64_t)(kStageBytes >> 4);
-                if (++s == kStages) { s = 0; ph ^= 1; a_tmem = a0; bdesc = bdesc0; }
-            }
-            if (ok) tc_commit_pair(bars_u32 + kAcc);  // accumulators complete, both CTAs
-        }
-        __syncwarp();
-    } else {
-        // ---------------- converters, then epilogue (both CTAs) ----------------
-        const int group = (warp - 2) >> 2;
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;
-        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        const int swz = (row >> 1) & 3;
-        const uint32_t aready_leader = map_to_cta(bars_u32 + kAready, 0);
-        bool ok = true;
-        // a group owns pipeline stages (s % kGroups), so that it passes through every phase of the
-        // barriers it polls and a parity wait stays unambiguous under any TMA completion order
-        for (int i = 0; i < rounds && ok; ++i) {
-            const int s = i % kStages;
-            if (s % kGroups != group) continue;
-            const uint32_t ph = (i / kStages) & 1;
-            ok = mbar_wait_warp(bars_u32 + kWFull + s * 8, ph, ctl, status, 3, s);
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int j = 0; j < kSub; ++j) {
-                const uint8_t *rowp = smem + s * kStageBytes + j * kWSub + row * kBlockK;
-                uint32_t packed[32];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(rowp + ((c ^ swz) << 4));
-                    cvt_i8x4_bf16(v.x, packed[8 * c + 0], packed[8 * c + 1]);
-                    cvt_i8x4_bf16(v.y, packed[8 * c + 2], packed[8 * c + 3]);
-                    cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
-                    cvt_i8x4_bf16(v.w, packed[8 * c + 6], packed[8 * c + 7]);
-                }
-                tc_st32(tmem_base + lane_addr + kABase + s * kAColsPerStage + j * (kBlockK / 2), packed);
-            }
-            tc_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(aready_leader + s * 8);
-        }
-        // epilogue: this CTA's 128 channels x the pair's 256 tokens
-        if (ok) ok = mbar_wait_warp(bars_u32 + kAcc, 0, ctl, status, 4, 0);
-        if (ok) {
-            tc_fence_after();
-            const int n = n0 + row;
-            const bool n_ok = n < N;
-            const float sc = n_ok ? ops.scales[n] : 0.0f;
-            const float bs = (n_ok && ops.bias) ? ops.bias[n] : 0.0f;
-#pragma unroll 1
-            for (int c = group; c < kTokPair / 16; c += kGroups) {
-                uint32_t r[16];
-                tc_ld16(tmem_base + lane_addr + c * 16, r);
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int m = m0_pair + c * 16 + i;
-                    float o = __uint_as_float(r[i]) * sc + bs;
-                    if ((epilogue & 0xFF) == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
-                    if (n_ok && m < M) {
-                        const size_t off = (size_t)m * ldy + n;
-                        store_out<YT>(y + off, o);
-                        for (int d = 0; d < extra.n; ++d) store_out<YT>(static_cast<YT *>(extra.p[d]) + off, o);
-                    }
-                }
-            }
-        }
-    }
-
-    // ---------------- teardown: both CTAs are done with tensor memory before it is freed ----------------
-    tc_fence_before();
-    __syncthreads();
-    cluster_arrive();
-    cluster_wait();
-    if (warp == 1) {
-        if (ctl->abort_flag) {
-            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-        }
-        tc_fence_after();
-        __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
-    }
-}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,

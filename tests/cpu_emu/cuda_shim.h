@@ -57,15 +57,33 @@ struct Block {
     std::mutex mu;                   // serialises the modelled mbarrier / named-barrier bookkeeping
     std::vector<uint32_t> tmem;      // tensor memory: 128 lanes x 512 columns of 32 bits (allocated on first use)
     std::map<int, std::unique_ptr<std::barrier<>>> named;  // bar.sync id -> barrier
-    explicit Block(unsigned t, size_t dyn_b = 0) : threads(t), all(t), slots(t), frag(8 * (size_t)t), dyn_bytes(dyn_b) {
+    // thread-block cluster (pairs): rank in the cluster, the member blocks, the cluster-wide barrier, and
+    // the region that holds every member's shared memory back to back (256 KiB each)
+    unsigned rank = 0;
+    Block *cluster[2] = {nullptr, nullptr};
+    std::barrier<> *cluster_bar = nullptr;
+    unsigned char *region = nullptr;
+    size_t region_bytes = 0;
+    bool owns_region = false;
+    // `shared`: this block's 256 KiB window inside a cluster region; null = allocate an own window
+    explicit Block(unsigned t, size_t dyn_b = 0, unsigned char *shared = nullptr)
+        : threads(t), all(t), slots(t), frag(8 * (size_t)t), dyn_bytes(dyn_b) {
         for (unsigned w = 0; w < (t + 31) / 32; ++w) {
             const unsigned lanes = std::min(32u, t - w * 32);
             warp.emplace_back(std::make_unique<std::barrier<>>(lanes));
         }
-        dyn = static_cast<unsigned char *>(std::aligned_alloc(size_t(1) << 18, size_t(1) << 18));
+        cluster[0] = this;
+        if (shared) {
+            dyn = shared;
+        } else {
+            dyn = static_cast<unsigned char *>(std::aligned_alloc(size_t(1) << 18, size_t(1) << 18));
+            region = dyn;
+            region_bytes = size_t(1) << 18;
+            owns_region = true;
+        }
         memset(dyn, 0xA5, size_t(1) << 18);  // shared memory starts with whatever was there
     }
-    ~Block() { std::free(dyn); }
+    ~Block() { if (owns_region) std::free(dyn); }
     Block(const Block &) = delete;
 };
 inline thread_local Block *g_block = nullptr;
@@ -99,6 +117,42 @@ inline void launch3(unsigned gx, unsigned gy, unsigned gz, unsigned block, size_
 }
 inline void launch(unsigned grid, unsigned block, size_t dyn_bytes, const std::function<void()> &body) {
     launch3(grid, 1, 1, block, dyn_bytes, body);
+}
+// Clusters of 2 blocks along x: the two blocks of a cluster run at the same time (2 * block threads),
+// clusters one after the other.  gx must be even.
+inline void launch_cluster2(unsigned gx, unsigned gy, unsigned block, size_t dyn_bytes, const std::function<void()> &body) {
+    unsigned char *region = static_cast<unsigned char *>(std::aligned_alloc(size_t(1) << 19, size_t(1) << 19));
+    {
+        Block b0(block, dyn_bytes, region), b1(block, dyn_bytes, region + (size_t(1) << 18));
+        std::barrier<> cluster_bar(2 * block);
+        Block *both[2] = {&b0, &b1};
+        for (unsigned r = 0; r < 2; ++r) {
+            both[r]->rank = r;
+            both[r]->cluster[0] = &b0;
+            both[r]->cluster[1] = &b1;
+            both[r]->cluster_bar = &cluster_bar;
+            both[r]->region = region;
+            both[r]->region_bytes = size_t(1) << 19;
+        }
+        std::vector<std::thread> pool;
+        for (unsigned r = 0; r < 2; ++r)
+            for (unsigned t = 0; t < block; ++t) {
+                pool.emplace_back([&, r, t] {
+                    g_block = both[r];
+                    threadIdx = emu_uint3{t, 0, 0};
+                    blockDim = emu_uint3{block, 1, 1};
+                    gridDim = emu_uint3{gx, gy, 1};
+                    for (unsigned y = 0; y < gy; ++y)
+                        for (unsigned c = 0; c < gx / 2; ++c) {
+                            blockIdx = emu_uint3{2 * c + r, y, 0};
+                            body();
+                            cluster_bar.arrive_and_wait();  // the next cluster reuses the blocks' memories
+                        }
+                });
+            }
+        for (auto &th : pool) th.join();
+    }
+    std::free(region);
 }
 }  // namespace emu
 

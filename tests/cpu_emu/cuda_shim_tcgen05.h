@@ -30,12 +30,14 @@ struct CUtensorMap {
 };
 
 namespace emu {
+// a shared-memory address of this block or, in a cluster, of any member (shared::cluster window)
 inline uint8_t *smem_ptr(uint32_t addr) {
-    const uintptr_t base = reinterpret_cast<uintptr_t>(g_block->dyn);
+    const uintptr_t base = reinterpret_cast<uintptr_t>(g_block->region);
     const uintptr_t p = (base & ~uintptr_t(0xFFFFFFFFu)) | addr;
-    assert(p >= base && p < base + (size_t(1) << 18) && "shared-memory address outside the block's shared memory");
+    assert(p >= base && p < base + g_block->region_bytes && "shared-memory address outside the cluster's shared memory");
     return reinterpret_cast<uint8_t *>(p);
 }
+inline std::mutex g_mbar_mu;  // one lock for every modelled mbarrier (a barrier may be touched from the peer block)
 // the XOR the TMA applies when it writes, and tcgen05.mma when it reads: 16-byte chunk index bits
 // [4,7) ^= address bits [7,10) (128-byte mode) or bits [4,6) ^= bits [7,9) (64-byte mode)
 inline uint32_t swizzle(uint32_t addr, int mode) {
@@ -59,20 +61,20 @@ inline void mbar_settle(MBar *b) {
 static inline uint32_t smem_u32(const void *p) { return (uint32_t)reinterpret_cast<uintptr_t>(p); }
 
 static inline void mbar_init(uint32_t bar, uint32_t count) {
-    std::lock_guard<std::mutex> g(emu::g_block->mu);
+    std::lock_guard<std::mutex> g(emu::g_mbar_mu);
     auto *b = reinterpret_cast<emu::MBar *>(emu::smem_ptr(bar));
     b->phase = 0; b->pending = count; b->init = count; b->tx = 0;
 }
 static inline void mbar_fence_init() {}
 static inline void mbar_arrive(uint32_t bar) {
-    std::lock_guard<std::mutex> g(emu::g_block->mu);
+    std::lock_guard<std::mutex> g(emu::g_mbar_mu);
     auto *b = reinterpret_cast<emu::MBar *>(emu::smem_ptr(bar));
     assert(b->pending > 0 && "more arrivals than the barrier was initialised for");
     b->pending -= 1;
     emu::mbar_settle(b);
 }
 static inline void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    std::lock_guard<std::mutex> g(emu::g_block->mu);
+    std::lock_guard<std::mutex> g(emu::g_mbar_mu);
     auto *b = reinterpret_cast<emu::MBar *>(emu::smem_ptr(bar));
     assert(b->pending > 0);
     b->tx += (int32_t)bytes;
@@ -82,7 +84,7 @@ static inline void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 static inline bool mbar_try(uint32_t bar, uint32_t parity) {
     bool done;
     {
-        std::lock_guard<std::mutex> g(emu::g_block->mu);
+        std::lock_guard<std::mutex> g(emu::g_mbar_mu);
         done = reinterpret_cast<emu::MBar *>(emu::smem_ptr(bar))->phase != (parity & 1u);  // that phase has completed
     }
     if (!done) std::this_thread::yield();
@@ -109,7 +111,7 @@ static inline void tma_load_2d(uint32_t dst, const void *tmap_v, int c0, int c1,
             }
         }
     }
-    std::lock_guard<std::mutex> g(emu::g_block->mu);
+    std::lock_guard<std::mutex> g(emu::g_mbar_mu);
     auto *b = reinterpret_cast<emu::MBar *>(emu::smem_ptr(bar));
     b->tx -= (int32_t)(tm.box_outer * row_bytes);
     emu::mbar_settle(b);

@@ -1,10 +1,11 @@
 """CPU: the library's scalar CUDA kernels, executed thread by thread under a small stand-in for the
 CUDA execution model (tests/cpu_emu/cuda_shim.h), against the golden vectors and the oracle.
 
-The device code of the quantize / dequantize families and of the warp-MMA small-batch forward lives
-in headers without launch syntax (shrew_b200/csrc/quantize_kernels.cuh, quantize_modes_kernels.cuh,
-activation_f16.cuh, gemv_mma_kernels.cuh; their few PTX instructions sit behind ptx_small.cuh); g++
-compiles them here as plain C++, with mma.sync computed from its documented fragment layout.  This is a check of kernel LOGIC (indexing, block and warp reductions, the
+The device code of the quantize / dequantize families, of the warp-MMA small-batch forward and of the
+tcgen05 kernels lives in headers without launch syntax (shrew_b200/csrc/*_kernels.cuh,
+activation_f16.cuh; their PTX instructions sit behind ptx_small.cuh, ptx_tcgen05.cuh and
+ptx_tcgen05_pair.cuh); g++ compiles them here as plain C++, with mma.sync, mbarriers, TMA, tensor memory
+and tcgen05.mma modelled from their documented behaviour.  This is a check of kernel LOGIC (indexing, block and warp reductions, the
 f32 shortcut and its f64 replay, special values); it says nothing about speed and is no substitute
 for the GPU parity tests.  The INT8 symmetric kernels have run on B200s and pass the same golden
 vectors there, which is what validates the stand-in itself; the kernels of the other modes have not
@@ -29,8 +30,8 @@ def _build(name):
     src = os.path.join(EMU_DIR, name + ".cpp")
     out = os.path.join(BUILD_DIR, "lib" + name + ".so")
     deps = [src, os.path.join(EMU_DIR, "cuda_shim.h")] + [
-        os.path.join(ROOT, "shrew_b200", "csrc", h) for h in ("quantize_kernels.cuh", "quantize_modes_kernels.cuh", "activation_f16.cuh",
-                                                              "gemv_mma_kernels.cuh", "ptx_small.cuh", "dests.cuh")]
+        os.path.join(ROOT, "shrew_b200", "csrc", h) for h in os.listdir(os.path.join(ROOT, "shrew_b200", "csrc")) if h.endswith(".cuh")] + [
+        os.path.join(EMU_DIR, h) for h in os.listdir(EMU_DIR) if h.endswith(".h")]
     if not os.path.exists(out) or any(os.path.getmtime(d) > os.path.getmtime(out) for d in deps):
         subprocess.run(["g++", "-std=c++20", "-O1", "-pthread", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math",
                         "-Wno-unknown-pragmas", "-o", out, src], check=True, cwd=EMU_DIR)
@@ -506,3 +507,34 @@ def test_f32_activations_through_two_tensor_core_passes(oracle, emu, emu_tc):
     y2 = _tc_forward(emu_tc, q, scales, bias, lo, 128, 3, epilogue=0x100 | 1, y_init=y1)
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
     assert oracle.rel_err(y2, ref) < 1e-4                      # the f32 path's tolerance
+
+
+# ---- the CTA-pair kernel (cta_group::2), never run on a GPU: two blocks of a cluster run concurrently --
+# over modelled cluster shared memory.  The single-CTA parts of the model are tied to the hardware by the
+# kernel above; the cta_group::2 parts (tests/cpu_emu/cuda_shim_tcgen05_pair.h) state how the documentation
+# is read here, and are what the first GPU run of this kernel has to confirm.
+@pytest.fixture(scope="module")
+def emu_pair():
+    L = _build("emu_gemm_tcgen05_pair")
+    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci]
+    return L
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (300, 300, 320), (100, 130, 128), (513, 512, 1088), (1, 256, 1024), (260, 1000, 64)])
+def test_cta_pair_forward_matches_oracle(oracle, emu_pair, M, N, K):
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, M + N)
+    qa = _aligned(q.shape, np.int8)
+    qa[...] = q
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    s32 = scales.astype(np.float32)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
+    ldy = N + 2
+    y = np.full((M, ldy), 7.0, np.float32)
+    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(xa), _p(y), M, N, K, ldy, 1, 0) == 0
+    assert oracle.rel_err(y[:, :N], ref) < 2e-6
+    assert np.all(y[:, N:] == 7.0)
+    y16 = np.full((M, N), 0x4100, np.uint16)
+    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), None, _p(xa), _p(y16), M, N, K, N, 0, 1) == 0
+    ref_nb = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, None, x)
+    assert oracle.rel_err((y16.astype(np.uint32) << 16).view(np.float32), ref_nb) < 1e-2
