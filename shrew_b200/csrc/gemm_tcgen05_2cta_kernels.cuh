@@ -57,8 +57,14 @@ constexpr int kXOff = kSub * kWSub;
 constexpr int kAColsPerStage = kSub * (kBlockK / 2);  // 64
 constexpr int kABase = kTokPair;                      // D occupies columns [0,256)
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
-constexpr uint32_t kSpinFast = 1u << 14;
-constexpr uint32_t kSpinSlow = 1u << 21;
+#ifndef SHREWQ_SPIN_FAST_LIMIT
+#define SHREWQ_SPIN_FAST_LIMIT (1u << 14)
+#endif
+#ifndef SHREWQ_SPIN_SLOW_LIMIT
+#define SHREWQ_SPIN_SLOW_LIMIT (1u << 21)
+#endif
+constexpr uint32_t kSpinFast = SHREWQ_SPIN_FAST_LIMIT;  // polls, then polls with ~100 ns sleeps
+constexpr uint32_t kSpinSlow = SHREWQ_SPIN_SLOW_LIMIT;
 static_assert(kABase + kStages * kAColsPerStage <= 512, "TMEM columns");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 

@@ -46,8 +46,16 @@ namespace {
 constexpr int kTileN = 128;  // TMEM lanes = weight rows per CTA (64 + 64 when GATED)
 constexpr int kBlockK = 64;  // k per sub-block (one 64-byte-swizzled INT8 box)
 constexpr int kUmmaK = 16;
-constexpr uint32_t kSpinFast = 1u << 14;
-constexpr uint32_t kSpinSlow = 1u << 21;  // x ~100 ns sleeps: a fraction of a second
+// limits of a bounded wait: polls, then polls with ~100 ns sleeps (a fraction of a second in all);
+// the CPU tests that make a wait run out on purpose compile with smaller limits
+#ifndef SHREWQ_SPIN_FAST_LIMIT
+#define SHREWQ_SPIN_FAST_LIMIT (1u << 14)
+#endif
+#ifndef SHREWQ_SPIN_SLOW_LIMIT
+#define SHREWQ_SPIN_SLOW_LIMIT (1u << 21)
+#endif
+constexpr uint32_t kSpinFast = SHREWQ_SPIN_FAST_LIMIT;
+constexpr uint32_t kSpinSlow = SHREWQ_SPIN_SLOW_LIMIT;
 
 template <int TOK, int KSUB>
 struct Cfg {

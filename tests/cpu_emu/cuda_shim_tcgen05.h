@@ -37,6 +37,10 @@ inline uint8_t *smem_ptr(uint32_t addr) {
     assert(p >= base && p < base + g_block->region_bytes && "shared-memory address outside the cluster's shared memory");
     return reinterpret_cast<uint8_t *>(p);
 }
+// Fault injection for the tests of the bounded waits: the load with this running number (counted over
+// the whole launch, first load = 0) is dropped: no data, no bytes counted on its barrier.  -1 = none.
+inline std::atomic<int> g_drop_tma{-1};
+inline std::atomic<int> g_tma_count{0};
 inline std::mutex g_mbar_mu;  // one lock for every modelled mbarrier (a barrier may be touched from the peer block)
 // the XOR the TMA applies when it writes, and tcgen05.mma when it reads: 16-byte chunk index bits
 // [4,7) ^= address bits [7,10) (128-byte mode) or bits [4,6) ^= bits [7,9) (64-byte mode)
@@ -96,6 +100,7 @@ static inline bool mbar_try(uint32_t bar, uint32_t parity) {
 static inline void tma_load_2d(uint32_t dst, const void *tmap_v, int c0, int c1, uint32_t bar) {
     const CUtensorMap &tm = *static_cast<const CUtensorMap *>(tmap_v);
     const uint32_t row_bytes = tm.box_inner * tm.elem_bytes;
+    if (emu::g_tma_count.fetch_add(1) == emu::g_drop_tma.load()) return;  // injected fault: this load never lands
     assert((dst & 15u) == 0 && ((uint32_t)c0 * tm.elem_bytes) % 16 == 0 && "TMA alignment rules");
     assert(tm.swizzle_bytes == 0 || row_bytes == (uint32_t)tm.swizzle_bytes);
     for (uint32_t r = 0; r < tm.box_outer; ++r) {

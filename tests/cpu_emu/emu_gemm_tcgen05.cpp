@@ -97,3 +97,10 @@ extern "C" int emu_gemm_tcgen05(const int8_t *q, const float *scales, const floa
     if (st.timeout_flag) return -2;
     return rc;
 }
+
+// fault injection: drop the n-th TMA load of the next launches (-1 = none); resets the running count
+extern "C" void emu_drop_tma(int n) {
+    emu::g_drop_tma = n;
+    emu::g_tma_count = 0;
+}
+

@@ -33,3 +33,10 @@ extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const
     else run<float>(q, scales, bias, static_cast<const uint16_t *>(x), y, M, N, K, ldy, epilogue, &st);
     return st.timeout_flag ? -2 : 0;
 }
+
+// fault injection: drop the n-th TMA load of the next launches (-1 = none); resets the running count
+extern "C" void emu_drop_tma(int n) {
+    emu::g_drop_tma = n;
+    emu::g_tma_count = 0;
+}
+

@@ -538,3 +538,67 @@ def test_cta_pair_forward_matches_oracle(oracle, emu_pair, M, N, K):
     assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), None, _p(xa), _p(y16), M, N, K, N, 0, 1) == 0
     ref_nb = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, None, x)
     assert oracle.rel_err((y16.astype(np.uint32) << 16).view(np.float32), ref_nb) < 1e-2
+
+
+# ---- bounded waits: a wait that runs out must end the kernel, not hang it -------------------------------
+# On the GPU no wait has ever expired, so the give-up path (record where, raise the CTA-wide abort flag,
+# every role falls through to the teardown that frees tensor memory) had only been read, never run.  Here a
+# TMA load is dropped on purpose (host-side injection, nothing faults) and the kernel, compiled with small
+# wait limits (so small that other roles give up at about the same time, wherever they happen to be), has
+# to return with the status set while its 448 threads sit in barriers of every kind.
+def _build_short_waits(name):
+    src = os.path.join(EMU_DIR, name + ".cpp")
+    out = os.path.join(BUILD_DIR, "lib" + name + "_short_waits.so")
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    deps = [src] + [os.path.join(ROOT, "shrew_b200", "csrc", h) for h in os.listdir(os.path.join(ROOT, "shrew_b200", "csrc")) if h.endswith(".cuh")] + [
+        os.path.join(EMU_DIR, h) for h in os.listdir(EMU_DIR) if h.endswith(".h")]
+    if not os.path.exists(out) or any(os.path.getmtime(d) > os.path.getmtime(out) for d in deps):
+        subprocess.run(["g++", "-std=c++20", "-O1", "-pthread", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math",
+                        "-Wno-unknown-pragmas", "-DSHREWQ_SPIN_FAST_LIMIT=64", "-DSHREWQ_SPIN_SLOW_LIMIT=40", "-o", out, src],
+                       check=True, cwd=EMU_DIR)
+    return ctypes.CDLL(out)
+
+
+@pytest.mark.parametrize("tok,M,N,K,splits,gated,drop", [
+    (64, 40, 128, 1024, 1, False, 0), (64, 40, 128, 1024, 1, False, 7), (256, 300, 128, 512, 1, False, 3),
+    (128, 100, 64, 768, 1, True, 4), (32, 20, 128, 1024, 2, False, 5), (16, 8, 128, 2048, 1, False, 31)])
+@pytest.mark.timeout(300)   # a deadlock in the give-up path would otherwise hang the suite
+def test_tcgen05_wait_that_runs_out_ends_the_kernel(tok, M, N, K, splits, gated, drop):
+    L = _build_short_waits("emu_gemm_tcgen05")
+    L.emu_gemm_tcgen05.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci, _ci, _ci, _ci]
+    L.emu_drop_tma.argtypes = [_ci]
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, drop)
+    qa = _aligned(q.shape, np.int8)
+    qa[...] = q
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    s32 = scales.astype(np.float32)
+    y = np.zeros((M, N), np.float32)
+    up = (_p(qa), _p(s32), None) if gated else (None, None, None)
+    L.emu_drop_tma(drop)
+    try:
+        rc = L.emu_gemm_tcgen05(_p(qa), _p(s32), _p(bias), *up, _p(xa), _p(y), M, N, K, N, 0, 0, tok, 3, splits, 0)
+    finally:
+        L.emu_drop_tma(-1)
+    assert rc in (-2, -3)   # a bounded wait gave up and was reported (a split-K tile counter may stay set)
+
+
+@pytest.mark.timeout(300)
+def test_cta_pair_wait_that_runs_out_ends_both_blocks():
+    L = _build_short_waits("emu_gemm_tcgen05_pair")
+    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci]
+    L.emu_drop_tma.argtypes = [_ci]
+    q, scales, bias, x_bits, x = _tc_case(256, 256, 1024, 1)
+    qa = _aligned(q.shape, np.int8)
+    qa[...] = q
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    s32 = scales.astype(np.float32)
+    y = np.zeros((256, 256), np.float32)
+    for drop in (0, 1, 9, 14):   # a code load or an activation load, of the leader or of the peer
+        L.emu_drop_tma(drop)
+        try:
+            rc = L.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(xa), _p(y), 256, 256, 1024, 256, 0, 0)
+        finally:
+            L.emu_drop_tma(-1)
+        assert rc == -2, drop
