@@ -10,6 +10,8 @@
 using namespace shrewq;
 
 namespace {
+Dests g_peers{};  // extra destinations of the next launches (the fused all-gather's peer buffers)
+
 struct Args {
     const int8_t *q, *q_up;
     const float *scales, *bias, *scales_up, *bias_up;
@@ -45,12 +47,26 @@ int run(const Args &a, DeviceStatus *status) {
         sk.counters = counters.data();
     }
     Operands ops{a.scales, a.bias, a.scales_up, a.bias_up};
-    Dests none{};
     auto body = [&] {
-        linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT>(tw, tw2, tx, ops, static_cast<YT *>(a.y), none, a.M, a.N, a.K, a.ldy,
+        linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT>(tw, tw2, tx, ops, static_cast<YT *>(a.y), g_peers, a.M, a.N, a.K, a.ldy,
                                                           a.epilogue, sk, status);
     };
-    if (a.tile_list) {  // the 1-D tile list of the two-launch scheme, here as one launch over all tiles
+    if (a.tile_list >= 2) {
+        // the two-launch scheme of launch_cfg for a short last wave, with `tile_list` standing for the SM
+        // count: full waves as one launch of whole-K tiles, the remaining tiles as a second launch split
+        // along K (a.splits ways); both launches use the 1-D tile list
+        const int tiles = n_tiles * m_tiles, rem = tiles % a.tile_list;
+        if (tiles <= a.tile_list || rem == 0) return -1;
+        sk = SplitK{nullptr, nullptr, rounds, 0, n_tiles};
+        emu::launch3((unsigned)(tiles - rem), 1, 1, 64 + 128 * G, C::kSmemRequest, body);
+        sk = SplitK{partials.data(), counters.data(), rps, tiles - rem, n_tiles};
+        if (splits == 1) sk.partials = nullptr, sk.counters = nullptr;
+        emu::launch3((unsigned)rem, 1, (unsigned)splits, 64 + 128 * G, C::kSmemRequest, body);
+        for (unsigned int c : counters)
+            if (c != 0) return -3;
+        return 0;
+    }
+    if (a.tile_list == 1) {  // the 1-D tile list of the two-launch scheme, here as one launch over all tiles
         sk.tile_begin = 0;
         sk.n_tiles_total = n_tiles;
         emu::launch3((unsigned)(n_tiles * m_tiles), 1, (unsigned)splits, 64 + 128 * G, C::kSmemRequest, body);
@@ -96,6 +112,13 @@ extern "C" int emu_gemm_tcgen05(const int8_t *q, const float *scales, const floa
     else rc = y_bf16 ? run_tok<false, __nv_bfloat16>(a, tok, groups, &st) : run_tok<false, float>(a, tok, groups, &st);
     if (st.timeout_flag) return -2;
     return rc;
+}
+
+// peer destinations of the next launches: every output value is also stored at the same offset there
+extern "C" void emu_set_peers(void **p, int n) {
+    g_peers = Dests{};
+    for (int i = 0; i < n && i < kMaxPeers; ++i) g_peers.p[i] = p[i];
+    g_peers.n = n;
 }
 
 // fault injection: drop the n-th TMA load of the next launches (-1 = none); resets the running count

@@ -602,3 +602,32 @@ def test_cta_pair_wait_that_runs_out_ends_both_blocks():
         finally:
             L.emu_drop_tma(-1)
         assert rc == -2, drop
+
+
+def test_tcgen05_two_launch_tail_split(oracle, emu_tc):
+    # SHREWQ_TC_TAILSPLIT (not yet run on a GPU): with "5 SMs", 12 tiles = two full waves as whole-K tiles
+    # plus 2 tiles split along K in a second launch; both launches index tiles through the 1-D list
+    q, scales, bias, x_bits, x = _tc_case(260, 500, 1024, 21)       # 4 channel tiles x 3 token tiles
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
+    for splits in (2, 3):
+        y = _tc_forward(emu_tc, q, scales, bias, x_bits, 128, 3, splits=splits, epilogue=1, tile_list=5)
+        assert oracle.rel_err(y, ref) < 2e-6
+
+
+def test_tcgen05_peer_destinations(oracle, emu_tc):
+    # the all-gather fused into the epilogue: every value also lands at the same offset of each peer buffer
+    emu_tc.emu_set_peers.argtypes = [_vp, _ci]
+    q, scales, bias, x_bits, x = _tc_case(70, 140, 256, 8)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
+    ldy = 300                                                           # the shard writes columns [0, 140) of a wider row
+    peers = [np.full((70, ldy), 5.0, np.float32) for _ in range(3)]
+    arr = (ctypes.c_void_p * 3)(*[p.ctypes.data for p in peers])
+    for tok, splits in ((128, 1), (64, 2)):
+        emu_tc.emu_set_peers(arr, 3)
+        try:
+            y = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, 3, splits=splits, ldy=ldy)
+        finally:
+            emu_tc.emu_set_peers(None, 0)
+        for buf in [y] + peers:
+            assert oracle.rel_err(buf[:, :140], ref) < 2e-6
+            assert np.all(buf[:, 140:] == (7.0 if buf is y else 5.0))
