@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libshrewq.so")
 SOURCES = ["api.cu", "quantize.cu", "quantize_modes.cu", "gemv.cu", "gemv_mma.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "quantize_kernels.cuh"), os.path.join(CSRC, "quantize_modes_kernels.cuh"), os.path.join(CSRC, "activation_f16.cuh"), os.path.join(CSRC, "gemv_mma_kernels.cuh"), os.path.join(CSRC, "ptx_small.cuh"), os.path.join(CSRC, "dests.cuh"), os.path.join(CSRC, "gemm_tcgen05_kernels.cuh"), os.path.join(CSRC, "ptx_tcgen05.cuh"), os.path.join(CSRC, "ptx_tcgen05_pair.cuh"), os.path.join(CSRC, "gemm_tcgen05_2cta_kernels.cuh"), os.path.join(HERE, "..", "include", "shrewq.h")]
+HEADERS = sorted(os.path.join(CSRC, h) for h in os.listdir(CSRC) if h.endswith(".cuh")) + [os.path.join(HERE, "..", "include", "shrewq.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

@@ -1,0 +1,181 @@
+// Weight-only INT8 GEMV for small batches (M <= 16), sm_100a.
+//
+//   y[m,n] = scale[n] * sum_k q[n,k] * x[m,k] + bias[n]        (quantize.rs:463-476 with
+// the per-channel scale moved behind the dot product: codes are exact small integers, so
+// the f32 accumulator holds sum_k q*x and one multiply applies the scale).
+//
+// HBM-bound: the only large stream is the INT8 matrix, N*K bytes, read exactly once.
+// A CTA of 4 warps owns R consecutive output rows; the K range is dealt to the 4 warps in
+// 512-byte pieces (32 lanes x 16 B), so every warp-level load is one fully used 512 B
+// segment and each lane keeps R independent 16 B loads in flight per step.  Weights bypass
+// L1 (read once); the activations are tiny, read through L1 and reused by every row.
+// Codes are widened to f32 in registers and fed to FFMA; partial sums are combined with
+// warp shuffles, then across the 4 warps through shared memory.
+//
+// Device code only (no launch syntax, no runtime calls, PTX behind ptx_small.cuh): it also compiles as
+// plain C++ against the CUDA stand-in of the CPU tests (tests/cpu_emu/).
+#pragma once
+
+#include "../../include/shrewq.h"
+#include "dests.cuh"
+#include "ptx_small.cuh"
+
+namespace shrewq {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+
+__device__ __forceinline__ void i8x4_to_f32(uint32_t w, float *o) {
+    o[0] = (float)(int)(int8_t)(w & 0xFF);
+    o[1] = (float)(int)(int8_t)((w >> 8) & 0xFF);
+    o[2] = (float)(int)(int8_t)((w >> 16) & 0xFF);
+    o[3] = (float)(int)(int8_t)(w >> 24);
+}
+
+// 16 consecutive activations of one token as f32
+template <typename XT>
+__device__ __forceinline__ void load_x16(const XT *p, float *o);
+
+template <>
+__device__ __forceinline__ void load_x16<float>(const float *p, float *o) {
+    const float4 *p4 = reinterpret_cast<const float4 *>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 v = __ldg(p4 + i);
+        o[4 * i] = v.x; o[4 * i + 1] = v.y; o[4 * i + 2] = v.z; o[4 * i + 3] = v.w;
+    }
+}
+
+template <>
+__device__ __forceinline__ void load_x16<__nv_bfloat16>(const __nv_bfloat16 *p, float *o) {
+    const uint4 *p4 = reinterpret_cast<const uint4 *>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint4 v = __ldg(p4 + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            o[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+            o[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+    }
+}
+
+template <typename YT>
+__device__ __forceinline__ void store_y(YT *p, float v);
+template <>
+__device__ __forceinline__ void store_y<float>(float *p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_y<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
+
+// MT: tokens handled (M padded up to MT, extra tokens masked); R: output rows per CTA.
+// GATED: rows come in pairs (gate row n from q, up row n from q_up); R counts pairs * 2.
+template <int MT, int R, typename XT, typename YT, bool GATED>
+__global__ void __launch_bounds__(kThreads)
+gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
+               const float *__restrict__ bias, const int8_t *__restrict__ q_up,
+               const float *__restrict__ scales_up, const float *__restrict__ bias_up,
+               const XT *__restrict__ x, YT *__restrict__ y, Dests extra, int M, int N, int K,
+               size_t ldy, int epilogue, int pdl) {
+    constexpr int NR = GATED ? R / 2 : R;  // distinct output columns per CTA
+    // Programmatic dependent launch (opt-in): let the next kernel of the stream start its
+    // prologue while this one runs ...
+    if (pdl) pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * NR;
+    const int chunks = K >> 4;
+
+    const int8_t *rowp[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        int n = n0 + (GATED ? (r >> 1) : r);
+        n = n < N ? n : N - 1;  // clamp: duplicates are computed and dropped
+        const int8_t *base = (GATED && (r & 1)) ? q_up : q;
+        rowp[r] = base + (size_t)n * K;
+    }
+
+    float acc[R][MT];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
+
+    // ... and do not touch the activations (or write the output) before the previous kernel
+    // of the stream, which may have produced them, has completed
+    if (pdl) pdl_wait();
+
+    for (int c = warp * 32 + lane; c < chunks; c += kWarps * 32) {
+        uint4 wv[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) wv[r] = ld_stream_16(rowp[r] + ((size_t)c << 4));
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float xf[16];
+            if (m < M) {
+                load_x16<XT>(x + (size_t)m * K + ((size_t)c << 4), xf);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) xf[i] = 0.0f;
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint32_t w4[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+                float s = acc[r][m];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float wf[4];
+                    i8x4_to_f32(w4[j], wf);
+                    s = fmaf(wf[0], xf[4 * j], s);
+                    s = fmaf(wf[1], xf[4 * j + 1], s);
+                    s = fmaf(wf[2], xf[4 * j + 2], s);
+                    s = fmaf(wf[3], xf[4 * j + 3], s);
+                }
+                acc[r][m] = s;
+            }
+        }
+    }
+
+    __shared__ float s_red[kWarps][R][MT];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float v = acc[r][m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+            if (lane == 0) s_red[warp][r][m] = v;
+        }
+    __syncthreads();
+
+    for (int i = threadIdx.x; i < NR * MT; i += kThreads) {
+        const int nr = i / MT, m = i % MT;
+        const int n = n0 + nr;
+        if (n >= N || m >= M) continue;
+        float out;
+        if constexpr (GATED) {
+            float g = 0.0f, u = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                g += s_red[w][2 * nr][m];
+                u += s_red[w][2 * nr + 1][m];
+            }
+            g = g * scales[n] + (bias ? bias[n] : 0.0f);
+            u = u * scales_up[n] + (bias_up ? bias_up[n] : 0.0f);
+            out = silu(g) * u;
+        } else {
+            float s = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) s += s_red[w][nr][m];
+            out = s * scales[n] + (bias ? bias[n] : 0.0f);
+            if (epilogue == SHREWQ_EPILOGUE_RELU) out = fmaxf(out, 0.0f);
+        }
+        store_y<YT>(y + (size_t)m * ldy + n, out);
+        for (int d = 0; d < extra.n; ++d) store_y<YT>(static_cast<YT *>(extra.p[d]) + (size_t)m * ldy + n, out);
+    }
+}
+
+}  // namespace
+}  // namespace shrewq

@@ -251,6 +251,8 @@ static inline unsigned __byte_perm(unsigned x, unsigned y, unsigned sel) {
 }
 #define __expf expf
 static inline uint4 ld_stream_16(const void *p) { uint4 v; memcpy(&v, p, 16); return v; }
+static inline void pdl_launch_dependents() {}   // launches are sequential here
+static inline void pdl_wait() {}
 static inline uint32_t pack_bf16x2_rn(float hi, float lo) {
     return ((uint32_t)__float2bfloat16_rn(hi).bits << 16) | __float2bfloat16_rn(lo).bits;
 }

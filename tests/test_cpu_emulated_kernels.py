@@ -631,3 +631,88 @@ def test_tcgen05_peer_destinations(oracle, emu_tc):
         for buf in [y] + peers:
             assert oracle.rel_err(buf[:, :140], ref) < 2e-6
             assert np.all(buf[:, 140:] == (7.0 if buf is y else 5.0))
+
+
+# ---- the CUDA-core forward kernels (GPU-validated; here for the stand-in's sake and for the paths the GPU
+# tests reach only on several GPUs: peer destinations) ---------------------------------------------------
+@pytest.fixture(scope="module")
+def emu_cc():
+    L = _build("emu_forward_cuda_cores")
+    L.emu_forward_cuda_cores.argtypes = [_ci, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci, _ci]
+    L.emu_set_peers.argtypes = [_vp, _ci]
+    return L
+
+
+def _cc_forward(emu_cc, kernel, q, scales, bias, x, x_bf16, y_bf16, relu=False, up=None, ldy=None, pdl=0, unaligned=False):
+    N, K = q.shape
+    M = x.shape[0]
+    ldy = ldy or N
+    pad = 1 if unaligned else 0
+    qbuf = _aligned((N * K + pad,), np.int8)
+    qa = qbuf[pad:].reshape(N, K)
+    qa[...] = q
+    xa = _aligned(x.shape, x.dtype)
+    xa[...] = x
+    y = np.full((M, ldy), 0x4100, np.uint16) if y_bf16 else np.full((M, ldy), 7.0, np.float32)
+    s32 = scales.astype(np.float32)
+    if up is None:
+        args = (_p(qa), _p(s32), None if bias is None else _p(bias), None, None, None)
+    else:
+        qub = _aligned((N * K + pad,), np.int8)
+        qu = qub[pad:].reshape(N, K)
+        qu[...] = up[0]
+        su = up[1].astype(np.float32)
+        args = (_p(qa), _p(s32), None if bias is None else _p(bias), _p(qu), _p(su), None if up[2] is None else _p(up[2]))
+    rc = emu_cc.emu_forward_cuda_cores(kernel, *args, _p(xa), _p(y), M, N, K, ldy, 1 if relu else 0, int(x_bf16), int(y_bf16), pdl)
+    assert rc == 0
+    return y
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 16])
+@pytest.mark.parametrize("x_bf16", [0, 1], ids=["f32", "bf16"])
+def test_gemv_matches_oracle(oracle, emu_cc, M, x_bf16):
+    rng = np.random.default_rng(M)
+    N, K = 37, 528
+    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    scales = rng.random(N) * 1e-2 + 1e-4
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    x32 = rng.standard_normal((M, K)).astype(np.float32)
+    bits, xb = _bf16_bits(x32)
+    x_in, x_ref = (bits, xb) if x_bf16 else (x32, x32)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x_ref, relu=True)
+    y = _cc_forward(emu_cc, 0, q, scales, bias, x_in, x_bf16, 0, relu=True, ldy=N + 1, pdl=M & 1)
+    assert oracle.rel_err(y[:, :N], ref) < 2e-6 and np.all(y[:, N:] == 7.0)
+
+
+def test_gemv_gate_up_and_peer_destinations(oracle, emu_cc):
+    rng = np.random.default_rng(4)
+    M, N, K = 3, 50, 256
+    qg, qu = (rng.integers(-127, 128, size=(N, K)).astype(np.int8) for _ in range(2))
+    sg, su = rng.random(N) * 1e-2 + 1e-4, rng.random(N) * 1e-2 + 1e-4
+    bits, xb = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    g = oracle.np_linear_forward(qg, sg, 1, None, xb).astype(np.float64)
+    u = oracle.np_linear_forward(qu, su, 1, None, xb).astype(np.float64)
+    ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    peers = [np.full((M, N), 5.0, np.float32) for _ in range(7)]      # the most a launch takes
+    arr = (ctypes.c_void_p * 7)(*[p.ctypes.data for p in peers])
+    emu_cc.emu_set_peers(arr, 7)
+    try:
+        y = _cc_forward(emu_cc, 0, qg, sg, None, bits, 1, 0, up=(qu, su, None))
+    finally:
+        emu_cc.emu_set_peers(None, 0)
+    for buf in [y] + peers:
+        assert oracle.rel_err(buf, ref) < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K,x_bf16,unaligned", [(64, 256, 784, 0, False), (5, 3, 37, 0, True), (130, 70, 100, 1, True), (257, 65, 16, 0, False)])
+def test_general_f32_kernel_matches_oracle(oracle, emu_cc, M, N, K, x_bf16, unaligned):
+    rng = np.random.default_rng(N)
+    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    scales = rng.random(N) * 1e-2 + 1e-4
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    x32 = rng.random((M, K)).astype(np.float32)
+    bits, xb = _bf16_bits(x32)
+    x_in, x_ref = (bits, xb) if x_bf16 else (x32, x32)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x_ref, relu=True)
+    y = _cc_forward(emu_cc, 1, q, scales, bias, x_in, x_bf16, 0, relu=True, unaligned=unaligned)
+    assert oracle.rel_err(y, ref) < 1e-5
