@@ -41,7 +41,8 @@ inline uint8_t *smem_ptr(uint32_t addr) {
 // the whole launch, first load = 0) is dropped: no data, no bytes counted on its barrier.  -1 = none.
 inline std::atomic<int> g_drop_tma{-1};
 inline std::atomic<int> g_tma_count{0};
-inline std::mutex g_mbar_mu;  // one lock for every modelled mbarrier (a barrier may be touched from the peer block)
+inline std::mutex g_mbar_mu;
+inline void tma_progress();  // deferred-TMA mode: whoever polls a barrier may perform a queued load  // one lock for every modelled mbarrier (a barrier may be touched from the peer block)
 // the XOR the TMA applies when it writes, and tcgen05.mma when it reads: 16-byte chunk index bits
 // [4,7) ^= address bits [7,10) (128-byte mode) or bits [4,6) ^= bits [7,9) (64-byte mode)
 inline uint32_t swizzle(uint32_t addr, int mode) {
@@ -86,6 +87,7 @@ static inline void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     emu::mbar_settle(b);
 }
 static inline bool mbar_try(uint32_t bar, uint32_t parity) {
+    emu::tma_progress();
     bool done;
     {
         std::lock_guard<std::mutex> g(emu::g_mbar_mu);
@@ -97,10 +99,53 @@ static inline bool mbar_try(uint32_t bar, uint32_t parity) {
 
 // cp.async.bulk.tensor.2d ... mbarrier::complete_tx::bytes: box at element coordinates (c0 inner,
 // c1 outer), out-of-range elements read as zero, the full box is counted on the barrier
+namespace emu {
+struct PendingTma {
+    uint32_t dst;
+    CUtensorMap tm;
+    int c0, c1;
+    uint32_t bar;
+};
+// Deferred mode (tests of ordering assumptions): a load is queued at issue and performed later, in RANDOM
+// order, by whichever thread polls an mbarrier next.  0 = loads complete at issue.
+inline std::atomic<unsigned> g_tma_async_seed{0};
+inline std::atomic<unsigned> g_tma_one_in{8};  // a poll performs a queued load once in this many polls
+inline std::mutex g_tma_mu;
+inline std::vector<PendingTma> g_tma_pending;
+inline void tma_perform(uint32_t dst, const CUtensorMap &tm, int c0, int c1, uint32_t bar);
+inline void tma_progress() {
+    if (g_tma_async_seed.load() == 0) return;
+    PendingTma job;
+    {
+        std::lock_guard<std::mutex> g(g_tma_mu);
+        if (g_tma_pending.empty()) return;
+        static thread_local unsigned rng = 0;
+        if (rng == 0) rng = g_tma_async_seed.load() * 2654435761u + (unsigned)(uintptr_t)&rng;
+        rng = rng * 1664525u + 1013904223u;
+        if ((rng >> 12) % g_tma_one_in.load() != 0) return;  // mostly: not yet (loads stay in flight for many polls)
+        // usually the most recently issued load lands first (the worst order for a consumer that assumes
+        // issue order), otherwise a random one
+        const size_t pick = ((rng >> 20) & 3) ? g_tma_pending.size() - 1 : (rng >> 8) % g_tma_pending.size();
+        job = g_tma_pending[pick];
+        g_tma_pending.erase(g_tma_pending.begin() + pick);
+    }
+    tma_perform(job.dst, job.tm, job.c0, job.c1, job.bar);
+}
+}  // namespace emu
+
 static inline void tma_load_2d(uint32_t dst, const void *tmap_v, int c0, int c1, uint32_t bar) {
     const CUtensorMap &tm = *static_cast<const CUtensorMap *>(tmap_v);
-    const uint32_t row_bytes = tm.box_inner * tm.elem_bytes;
     if (emu::g_tma_count.fetch_add(1) == emu::g_drop_tma.load()) return;  // injected fault: this load never lands
+    if (emu::g_tma_async_seed.load() != 0) {
+        std::lock_guard<std::mutex> g(emu::g_tma_mu);
+        emu::g_tma_pending.push_back(emu::PendingTma{dst, tm, c0, c1, bar});
+        return;
+    }
+    emu::tma_perform(dst, tm, c0, c1, bar);
+}
+
+inline void emu::tma_perform(uint32_t dst, const CUtensorMap &tm, int c0, int c1, uint32_t bar) {
+    const uint32_t row_bytes = tm.box_inner * tm.elem_bytes;
     assert((dst & 15u) == 0 && ((uint32_t)c0 * tm.elem_bytes) % 16 == 0 && "TMA alignment rules");
     assert(tm.swizzle_bytes == 0 || row_bytes == (uint32_t)tm.swizzle_bytes);
     for (uint32_t r = 0; r < tm.box_outer; ++r) {

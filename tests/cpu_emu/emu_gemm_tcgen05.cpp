@@ -127,3 +127,10 @@ extern "C" void emu_drop_tma(int n) {
     emu::g_tma_count = 0;
 }
 
+// deferred TMA: loads complete later, mostly newest first (seed != 0; a poll performs one queued load
+// once in `one_in` polls), or at issue (seed 0)
+extern "C" void emu_tma_async(unsigned seed, unsigned one_in) {
+    emu::g_tma_async_seed = seed;
+    emu::g_tma_one_in = one_in ? one_in : 8;
+}
+

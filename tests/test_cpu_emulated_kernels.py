@@ -716,3 +716,55 @@ def test_general_f32_kernel_matches_oracle(oracle, emu_cc, M, N, K, x_bf16, unal
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x_ref, relu=True)
     y = _cc_forward(emu_cc, 1, q, scales, bias, x_in, x_bf16, 0, relu=True, unaligned=unaligned)
     assert oracle.rel_err(y, ref) < 1e-5
+
+
+@pytest.mark.parametrize("seed,one_in", [(1, 8), (2, 300), (3, 3000), (4, 3000)])
+@pytest.mark.parametrize("tok,groups,M,N,K,splits,gated", [
+    (256, 3, 300, 130, 1536, 1, False),    # 5 stages, 3 groups: a group meets a stage every few phases
+    (128, 3, 100, 200, 2048, 1, False),    # 4 stages, 3 groups
+    (16, 3, 8, 128, 4096, 1, False),       # 7 stages
+    (32, 2, 20, 128, 2048, 2, False),
+    (128, 3, 128, 64, 1024, 1, True)])
+def test_tcgen05_with_loads_landing_late_and_out_of_order(oracle, emu_tc, seed, one_in, tok, groups, M, N, K, splits, gated):
+    # TMA loads are queued at issue and land later, mostly NEWEST FIRST, one per `one_in` barrier polls: the
+    # kernel may not rely on loads completing in the order they were issued.  With rounds dealt round-robin
+    # to the converter groups (the mapping this kernel had when it was measured) the slow settings of this
+    # test fail, with wrong results or a wait that runs out: a group polled a stage barrier whose previous
+    # phase was still open and the parity bit answered for the phase two back.  Groups own stages now.
+    emu_tc.emu_tma_async.argtypes = [_cu, _cu]
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, seed)
+    emu_tc.emu_tma_async(seed, one_in)
+    try:
+        if gated:
+            rng = np.random.default_rng(seed)
+            qu = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+            su = rng.random(N) * 1e-2 + 1e-4
+            y = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, groups, splits=splits, up=(qu, su, None))
+            g = oracle.np_linear_forward(q, scales, 1, bias, x).astype(np.float64)
+            u = oracle.np_linear_forward(qu, su, 1, None, x).astype(np.float64)
+            ref, tol = (g / (1.0 + np.exp(-g)) * u).astype(np.float32), 1e-5
+        else:
+            y = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, groups, splits=splits)
+            ref, tol = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x), 2e-6
+    finally:
+        emu_tc.emu_tma_async(0, 0)
+    assert oracle.rel_err(y, ref) < tol
+
+
+def test_cta_pair_with_loads_landing_late_and_out_of_order(oracle, emu_pair):
+    emu_pair.emu_tma_async.argtypes = [_cu, _cu]
+    q, scales, bias, x_bits, x = _tc_case(300, 260, 2048, 3)
+    qa = _aligned(q.shape, np.int8)
+    qa[...] = q
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    s32 = scales.astype(np.float32)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
+    for seed, one_in in ((1, 8), (2, 3000)):
+        y = np.zeros((300, 260), np.float32)
+        emu_pair.emu_tma_async(seed, one_in)
+        try:
+            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(xa), _p(y), 300, 260, 2048, 260, 0, 0) == 0
+        finally:
+            emu_pair.emu_tma_async(0, 0)
+        assert oracle.rel_err(y, ref) < 2e-6
