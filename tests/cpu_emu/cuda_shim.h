@@ -23,6 +23,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <barrier>
 #include <functional>
 #include <map>
@@ -46,6 +47,16 @@ static inline float4 make_float4(float x, float y, float z, float w) { return fl
 static inline uint4 make_uint4(unsigned x, unsigned y, unsigned z, unsigned w) { return uint4{x, y, z, w}; }
 
 namespace emu {
+// A violated rule of the model (more arrivals than a barrier expects, a tensor-memory access outside the
+// warp's quadrant, ...) is recorded, not fatal: the harness reports it as a failed run.
+inline std::atomic<bool> g_failed{false};
+inline char g_fail_msg[256] = {0};
+inline void fail(const char *what) {
+    bool expected = false;
+    if (g_failed.compare_exchange_strong(expected, true)) strncpy(g_fail_msg, what, sizeof(g_fail_msg) - 1);
+}
+#define EMU_CHECK(cond, what) do { if (!(cond)) emu::fail(what); } while (0)
+
 struct Block {
     unsigned threads;
     std::barrier<> all;

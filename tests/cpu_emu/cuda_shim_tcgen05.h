@@ -7,11 +7,11 @@
 // which is what ties the model to the hardware (a model that read the swizzle, the descriptor or the
 // tensor-memory layout differently would not reproduce that kernel's results).
 //
-// Simplifications: asynchronous operations (TMA, MMA, commit) complete at issue; shared-memory
-// addresses are the low 32 bits of host addresses inside the block's dynamic shared memory.
+// Asynchronous operations (TMA loads, MMAs, commits) complete at issue by default; in the deferred mode
+// they are queued and performed later by polling threads (loads in an adversarial order, tensor-core
+// work in issue order).  Shared-memory addresses are the low 32 bits of host addresses inside the
+// block's dynamic shared memory.
 #pragma once
-
-#include <assert.h>
 
 #include <atomic>
 #include <chrono>
@@ -34,7 +34,11 @@ namespace emu {
 inline uint8_t *smem_ptr(uint32_t addr) {
     const uintptr_t base = reinterpret_cast<uintptr_t>(g_block->region);
     const uintptr_t p = (base & ~uintptr_t(0xFFFFFFFFu)) | addr;
-    assert(p >= base && p < base + g_block->region_bytes && "shared-memory address outside the cluster's shared memory");
+    if (!(p >= base && p + 16 <= base + g_block->region_bytes)) {
+        static uint8_t sink[64];  // keep the run alive; it is reported as failed
+        fail("shared-memory address outside the cluster's shared memory");
+        return sink;
+    }
     return reinterpret_cast<uint8_t *>(p);
 }
 // Fault injection for the tests of the bounded waits: the load with this running number (counted over
@@ -42,7 +46,8 @@ inline uint8_t *smem_ptr(uint32_t addr) {
 inline std::atomic<int> g_drop_tma{-1};
 inline std::atomic<int> g_tma_count{0};
 inline std::mutex g_mbar_mu;
-inline void tma_progress();  // deferred-TMA mode: whoever polls a barrier may perform a queued load  // one lock for every modelled mbarrier (a barrier may be touched from the peer block)
+inline void tma_progress();  // deferred modes: whoever polls a barrier may perform a queued load ...
+inline void tc_progress();   // ... or the next queued tensor-core job  // one lock for every modelled mbarrier (a barrier may be touched from the peer block)
 // the XOR the TMA applies when it writes, and tcgen05.mma when it reads: 16-byte chunk index bits
 // [4,7) ^= address bits [7,10) (128-byte mode) or bits [4,6) ^= bits [7,9) (64-byte mode)
 inline uint32_t swizzle(uint32_t addr, int mode) {
@@ -74,20 +79,21 @@ static inline void mbar_fence_init() {}
 static inline void mbar_arrive(uint32_t bar) {
     std::lock_guard<std::mutex> g(emu::g_mbar_mu);
     auto *b = reinterpret_cast<emu::MBar *>(emu::smem_ptr(bar));
-    assert(b->pending > 0 && "more arrivals than the barrier was initialised for");
+    if (b->pending == 0) { emu::fail("more arrivals than the barrier was initialised for"); return; }
     b->pending -= 1;
     emu::mbar_settle(b);
 }
 static inline void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     std::lock_guard<std::mutex> g(emu::g_mbar_mu);
     auto *b = reinterpret_cast<emu::MBar *>(emu::smem_ptr(bar));
-    assert(b->pending > 0);
+    if (b->pending == 0) { emu::fail("expect_tx: more arrivals than the barrier was initialised for"); return; }
     b->tx += (int32_t)bytes;
     b->pending -= 1;
     emu::mbar_settle(b);
 }
 static inline bool mbar_try(uint32_t bar, uint32_t parity) {
     emu::tma_progress();
+    emu::tc_progress();
     bool done;
     {
         std::lock_guard<std::mutex> g(emu::g_mbar_mu);
@@ -146,8 +152,8 @@ static inline void tma_load_2d(uint32_t dst, const void *tmap_v, int c0, int c1,
 
 inline void emu::tma_perform(uint32_t dst, const CUtensorMap &tm, int c0, int c1, uint32_t bar) {
     const uint32_t row_bytes = tm.box_inner * tm.elem_bytes;
-    assert((dst & 15u) == 0 && ((uint32_t)c0 * tm.elem_bytes) % 16 == 0 && "TMA alignment rules");
-    assert(tm.swizzle_bytes == 0 || row_bytes == (uint32_t)tm.swizzle_bytes);
+    EMU_CHECK((dst & 15u) == 0 && ((uint32_t)c0 * tm.elem_bytes) % 16 == 0, "TMA alignment rules");
+    EMU_CHECK(tm.swizzle_bytes == 0 || row_bytes == (uint32_t)tm.swizzle_bytes, "tm.swizzle_bytes == 0 || row_bytes == (uint32_t)tm.swizzle_bytes");
     for (uint32_t r = 0; r < tm.box_outer; ++r) {
         const int64_t row = (int64_t)c1 + r;
         for (uint32_t e = 0; e < tm.box_inner; ++e) {
@@ -167,11 +173,46 @@ inline void emu::tma_perform(uint32_t dst, const CUtensorMap &tm, int c0, int c1
     emu::mbar_settle(b);
 }
 
+namespace emu {
+// Deferred mode for tensor-core work (same switch and pace as the deferred TMA): tcgen05.mma and
+// tcgen05.commit are queued at issue and executed later, IN ORDER, by whichever thread polls an mbarrier.
+// An operand overwritten before its MMA has run (a missing wait on `empty`) then shows as a wrong result.
+struct TcJob {
+    Block *blk;                       // the issuing block (its shared and tensor memory)
+    std::function<void()> run;
+};
+inline std::mutex g_tc_mu;
+inline std::vector<TcJob> g_tc_queue;
+inline bool tc_deferred() { return g_tma_async_seed.load() != 0; }
+inline void tc_push(std::function<void()> fn) {
+    std::lock_guard<std::mutex> g(g_tc_mu);
+    g_tc_queue.push_back(TcJob{g_block, std::move(fn)});
+}
+inline void tc_progress() {
+    if (!tc_deferred()) return;
+    static thread_local unsigned rng = 12345u + (unsigned)(uintptr_t)&rng;
+    rng = rng * 1664525u + 1013904223u;
+    if ((rng >> 12) % g_tma_one_in.load() != 0) return;
+    std::lock_guard<std::mutex> g(g_tc_mu);  // held while the job runs: jobs execute one at a time, in order
+    if (g_tc_queue.empty()) return;
+    TcJob job = std::move(g_tc_queue.front());
+    g_tc_queue.erase(g_tc_queue.begin());
+    Block *mine = g_block;
+    g_block = job.blk;
+    job.run();
+    g_block = mine;
+}
+}  // namespace emu
+
 static inline void tc_fence_before() {}
 static inline void tc_fence_after() {}
 static inline void tc_wait_st() {}
 static inline void tc_wait_ld() {}
-static inline void tc_commit(uint32_t bar) { mbar_arrive(bar); }  // the MMAs issued so far have completed (synchronous model)
+// the barrier is arrived on once the MMAs issued so far have completed
+static inline void tc_commit(uint32_t bar) {
+    if (emu::tc_deferred()) emu::tc_push([bar] { mbar_arrive(bar); });
+    else mbar_arrive(bar);
+}
 
 static inline void tc_alloc_512(uint32_t result_smem) {
     emu::Block *blk = emu::g_block;
@@ -188,30 +229,38 @@ static inline void tc_dealloc_512(uint32_t) {}
 // tcgen05.st / ld .32x32b: lane i of the warp accesses tensor-memory lane (taddr.lane + i), consecutive columns
 static inline void tc_st32(uint32_t taddr, const uint32_t *r) {
     const uint32_t lane = (taddr >> 16) + (threadIdx.x & 31), col = taddr & 0xFFFF;
-    assert(lane < 128 && col + 32 <= 512);
-    assert((taddr >> 16) == 32 * ((threadIdx.x >> 5) & 3) && "a warp may only touch the lane quadrant warp % 4");
+    if (!(lane < 128 && col + 32 <= 512)) { emu::fail("tcgen05.st outside tensor memory"); return; }
+    EMU_CHECK((taddr >> 16) == 32 * ((threadIdx.x >> 5) & 3), "a warp may only touch the lane quadrant warp % 4");
     for (int i = 0; i < 32; ++i) emu::g_block->tmem[lane * 512 + col + i] = r[i];
 }
 static inline void tc_ld16(uint32_t taddr, uint32_t *r) {
     const uint32_t lane = (taddr >> 16) + (threadIdx.x & 31), col = taddr & 0xFFFF;
-    assert(lane < 128 && col + 16 <= 512);
-    assert((taddr >> 16) == 32 * ((threadIdx.x >> 5) & 3) && "a warp may only touch the lane quadrant warp % 4");
+    if (!(lane < 128 && col + 16 <= 512)) { emu::fail("tcgen05.ld outside tensor memory"); return; }
+    EMU_CHECK((taddr >> 16) == 32 * ((threadIdx.x >> 5) & 3), "a warp may only touch the lane quadrant warp % 4");
     for (int i = 0; i < 16; ++i) r[i] = emu::g_block->tmem[lane * 512 + col + i];
 }
 
 // tcgen05.mma.cta_group::1.kind::f16 [d], [a], b_desc, idesc, p:  D[128 x N] (+)= A[128 x 16] * B[N x 16]^T,
 // bf16 operands, f32 accumulators.  A: tensor-memory lane m, 8 columns of two bf16 (even k in the lower
 // half).  B: shared memory, K-major rows of 128 bytes, 8-row groups `stride byte offset` apart, 128-byte swizzle.
+static inline void tc_mma_ts_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate);
 static inline void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if (emu::tc_deferred()) emu::tc_push([=] { tc_mma_ts_now(d_tmem, a_tmem, b_desc, idesc, accumulate); });
+    else tc_mma_ts_now(d_tmem, a_tmem, b_desc, idesc, accumulate);
+}
+static inline void tc_mma_ts_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     emu::Block *blk = emu::g_block;
     const uint32_t N = ((idesc >> 17) & 0x3Fu) << 3, Mrows = ((idesc >> 24) & 0x1Fu) << 4;
-    assert(Mrows == 128 && N >= 8 && N <= 256 && N % 8 == 0);
-    assert(((idesc >> 4) & 3u) == 1 && ((idesc >> 7) & 7u) == 1 && ((idesc >> 10) & 7u) == 1 && "D f32, A bf16, B bf16");
-    assert(((b_desc >> 61) & 7u) == 2 && ((b_desc >> 46) & 1u) == 1 && "128-byte swizzle, descriptor version 1");
+    EMU_CHECK(Mrows == 128 && N >= 8 && N <= 256 && N % 8 == 0, "Mrows == 128 && N >= 8 && N <= 256 && N % 8 == 0");
+    EMU_CHECK(((idesc >> 4) & 3u) == 1 && ((idesc >> 7) & 7u) == 1 && ((idesc >> 10) & 7u) == 1, "D f32, A bf16, B bf16");
+    EMU_CHECK(((b_desc >> 61) & 7u) == 2 && ((b_desc >> 46) & 1u) == 1, "128-byte swizzle, descriptor version 1");
     const uint32_t start = (uint32_t)(b_desc & 0x3FFFu) << 4, sbo = (uint32_t)((b_desc >> 32) & 0x3FFFu) << 4;
     const uint32_t smem_hi = smem_u32(blk->dyn);  // 256 KiB aligned; the descriptor keeps the 18 low address bits
     const uint32_t dcol = d_tmem & 0xFFFF, acol = a_tmem & 0xFFFF;
-    assert((d_tmem >> 16) == 0 && (a_tmem >> 16) == 0 && dcol + N <= 512 && acol + 8 <= 512);
+    if (!((d_tmem >> 16) == 0 && (a_tmem >> 16) == 0 && dcol + N <= 512 && acol + 8 <= 512 && N >= 8 && N <= 256)) {
+        emu::fail("tcgen05.mma operands outside tensor memory");
+        return;
+    }
     std::vector<float> b((size_t)N * 16);
     for (uint32_t n = 0; n < N; ++n)
         for (uint32_t k = 0; k < 16; ++k) {

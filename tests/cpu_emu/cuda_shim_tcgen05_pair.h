@@ -22,8 +22,9 @@ static inline void tma_load_2d_pair(uint32_t dst, const void *tmap, int c0, int 
     tma_load_2d(dst, tmap, c0, c1, map_to_cta(bar_local, 0));  // data here, bytes counted on the leader's barrier
 }
 static inline void tc_commit_pair(uint32_t bar) {
-    mbar_arrive(map_to_cta(bar, 0));
-    mbar_arrive(map_to_cta(bar, 1));
+    const uint32_t b0 = map_to_cta(bar, 0), b1 = map_to_cta(bar, 1);
+    if (emu::tc_deferred()) emu::tc_push([=] { mbar_arrive(b0); mbar_arrive(b1); });
+    else { mbar_arrive(b0); mbar_arrive(b1); }
 }
 static inline void tc_alloc_512_pair(uint32_t result_smem) { tc_alloc_512(result_smem); }  // each block: its own tensor memory
 static inline void tc_relinquish_pair() {}
@@ -32,16 +33,24 @@ static inline void tc_dealloc_512_pair(uint32_t) {}
 // tcgen05.mma.cta_group::2.kind::f16: D[256 x N] (+)= A[256 x 16] * B[N x 16]^T issued by one thread of the
 // leader.  Rows 128 r .. 128 r + 127 of A and D live in block r's tensor memory (same columns in both);
 // rows 128 r .. of B live in block r's shared memory at the descriptor's offset.
+static inline void tc_mma_ts_pair_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate);
 static inline void tc_mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if (emu::tc_deferred()) emu::tc_push([=] { tc_mma_ts_pair_now(d_tmem, a_tmem, b_desc, idesc, accumulate); });
+    else tc_mma_ts_pair_now(d_tmem, a_tmem, b_desc, idesc, accumulate);
+}
+static inline void tc_mma_ts_pair_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     emu::Block *me = emu::g_block;
-    assert(me->rank == 0 && "the leader CTA issues the pair MMA");
+    EMU_CHECK(me->rank == 0, "the leader CTA issues the pair MMA");
     const uint32_t N = ((idesc >> 17) & 0x3Fu) << 3, Mrows = ((idesc >> 24) & 0x1Fu) << 4;
-    assert(Mrows == 256 && N == 256);
-    assert(((idesc >> 4) & 3u) == 1 && ((idesc >> 7) & 7u) == 1 && ((idesc >> 10) & 7u) == 1 && "D f32, A bf16, B bf16");
-    assert(((b_desc >> 61) & 7u) == 2 && ((b_desc >> 46) & 1u) == 1 && "128-byte swizzle, descriptor version 1");
+    EMU_CHECK(Mrows == 256 && N == 256, "Mrows == 256 && N == 256");
+    EMU_CHECK(((idesc >> 4) & 3u) == 1 && ((idesc >> 7) & 7u) == 1 && ((idesc >> 10) & 7u) == 1, "D f32, A bf16, B bf16");
+    EMU_CHECK(((b_desc >> 61) & 7u) == 2 && ((b_desc >> 46) & 1u) == 1, "128-byte swizzle, descriptor version 1");
     const uint32_t start = (uint32_t)(b_desc & 0x3FFFu) << 4, sbo = (uint32_t)((b_desc >> 32) & 0x3FFFu) << 4;
     const uint32_t dcol = d_tmem & 0xFFFF, acol = a_tmem & 0xFFFF;
-    assert((d_tmem >> 16) == 0 && (a_tmem >> 16) == 0 && dcol + N <= 512 && acol + 8 <= 512);
+    if (!((d_tmem >> 16) == 0 && (a_tmem >> 16) == 0 && dcol + N <= 512 && acol + 8 <= 512 && N == 256 && Mrows == 256)) {
+        emu::fail("pair tcgen05.mma operands outside tensor memory or not 256 x 256");
+        return;
+    }
     std::vector<float> b((size_t)N * 16);
     for (uint32_t n = 0; n < N; ++n) {
         const uint32_t owner = n >> 7, row = n & 127;

@@ -107,9 +107,11 @@ extern "C" int emu_gemm_tcgen05(const int8_t *q, const float *scales, const floa
     if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || M < 1) return -1;
     Args a{q, q_up, scales, bias, scales_up, bias_up, static_cast<const uint16_t *>(x), y, M, N, K, ldy, epilogue, splits, tile_list};
     DeviceStatus st{0, 0, 0, 0};
+    emu::g_failed = false;
     int rc;
     if (q_up) rc = y_bf16 ? run_tok<true, __nv_bfloat16>(a, tok, groups, &st) : run_tok<true, float>(a, tok, groups, &st);
     else rc = y_bf16 ? run_tok<false, __nv_bfloat16>(a, tok, groups, &st) : run_tok<false, float>(a, tok, groups, &st);
+    if (emu::g_failed) return -4;  // a rule of the model was violated (emu_fail_message)
     if (st.timeout_flag) return -2;
     return rc;
 }
@@ -133,4 +135,7 @@ extern "C" void emu_tma_async(unsigned seed, unsigned one_in) {
     emu::g_tma_async_seed = seed;
     emu::g_tma_one_in = one_in ? one_in : 8;
 }
+
+// the first violated rule of the model during the last run ("" if none)
+extern "C" const char *emu_fail_message() { return emu::g_failed ? emu::g_fail_msg : ""; }
 

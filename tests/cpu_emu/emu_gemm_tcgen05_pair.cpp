@@ -29,8 +29,10 @@ extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const
                                      int N, int K, size_t ldy, int epilogue, int y_bf16) {
     if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || M < 1) return -1;
     DeviceStatus st{0, 0, 0, 0};
+    emu::g_failed = false;
     if (y_bf16) run<__nv_bfloat16>(q, scales, bias, static_cast<const uint16_t *>(x), y, M, N, K, ldy, epilogue, &st);
     else run<float>(q, scales, bias, static_cast<const uint16_t *>(x), y, M, N, K, ldy, epilogue, &st);
+    if (emu::g_failed) return -4;  // a rule of the model was violated (emu_fail_message)
     return st.timeout_flag ? -2 : 0;
 }
 
@@ -46,4 +48,7 @@ extern "C" void emu_tma_async(unsigned seed, unsigned one_in) {
     emu::g_tma_async_seed = seed;
     emu::g_tma_one_in = one_in ? one_in : 8;
 }
+
+// the first violated rule of the model during the last run ("" if none)
+extern "C" const char *emu_fail_message() { return emu::g_failed ? emu::g_fail_msg : ""; }
 
