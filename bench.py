@@ -196,6 +196,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU exchange: 'fused' = peer stores from the kernel epilogue, 'nccl' = all-gather")
+    ap.add_argument("--force-kernel", default="auto",
+                    help="kernel family for every forward of the run (see shrewq_force_kernel); experiments only")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = WORKLOADS[args.workload]
@@ -217,6 +219,8 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     sdev = Device.get(dev)
+    if args.force_kernel != "auto":
+        _lib.check(_lib.lib().shrewq_force_kernel(args.force_kernel.encode()), None)
     cfg = QuantConfig.int8_per_channel()
     M = wl["M"]
 
@@ -451,7 +455,7 @@ def main():
         "metric": "quantized_linear_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x int8 -> f32 accumulate", "data": "synthetic",
-        "config": {"workload": args.workload, **{k: v for k, v in wl.items() if k != "kind"},
+        "config": {"workload": args.workload, **({"forced_kernel": args.force_kernel} if args.force_kernel != "auto" else {}), **{k: v for k, v in wl.items() if k != "kind"},
                    "weights": "INT8 per-channel, N(0,0.02)", "sharding": "none (single GPU)" if world == 1 else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
                    "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU) > 2x L2"},
         "tflops": flops_step * args.steps / (ms_total * 1e-3) / 1e12,

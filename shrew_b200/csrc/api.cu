@@ -483,8 +483,8 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             if (!gemv_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced gemv cannot take this shape", who);
             choice = kForceGemv; break;
         case kForceTc2Cta:
-            if (!tc_ok || up) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05-2cta cannot take this shape/dtype", who);
-            rc = launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap);
+            if (!tc_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05-2cta cannot take this shape/dtype", who);
+            rc = up ? launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap, nullptr);
             lin->last_kernel = "tcgen05";
             return rc;
         case kForceTcF32:

@@ -34,21 +34,22 @@ int encode_x_half(shrewq_ctx *ctx, CUtensorMap *out, const void *x, size_t K, si
     return SHREWQ_OK;
 }
 
-template <typename YT>
-int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw) {
+template <typename YT, bool GATED>
+int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2) {
     CUtensorMap tx;
     int rc = encode_x_half(ctx, &tx, a.x, a.K, a.M);
     if (rc != SHREWQ_OK) return rc;
-    auto kern = linear_i8_tcgen05_pair_kernel<YT>;
+    auto kern = linear_i8_tcgen05_pair_kernel<YT, GATED>;
     static bool attr_set[64] = {false};
     if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
         SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         if (ctx->device >= 0 && ctx->device < 64) attr_set[ctx->device] = true;
     }
-    const unsigned pairs = (unsigned)((a.N + 2 * kLanes - 1) / (2 * kLanes));
+    constexpr int kChanPair = GATED ? kLanes : 2 * kLanes;  // output channels per CTA pair
+    const unsigned pairs = (unsigned)((a.N + kChanPair - 1) / kChanPair);
     dim3 grid(2 * pairs, (unsigned)((a.M + kTokPair - 1) / kTokPair), 1);
-    Operands2 ops{a.scales, a.bias};
-    kern<<<grid, kThreads, kSmemBytes, ctx->stream>>>(tw, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N,
+    Operands2 ops{a.scales, a.bias, a.scales_up, a.bias_up};
+    kern<<<grid, kThreads, kSmemBytes, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N,
                                                       (int)a.K, a.ldy, a.epilogue, ctx->dev_status);
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
@@ -57,12 +58,18 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw) {
 
 }  // namespace
 
-// w_tmap: the handle's 128-row INT8 boxes (the same descriptor the single-CTA kernel uses)
-int launch_gemm_tcgen05_2cta(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap) {
-    if (a.q_up) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "tcgen05-2cta: the gate/up form is not built for CTA pairs");
+// Plain forward: w_tmap = the handle's 128-row INT8 boxes, w_up_tmap = nullptr.  Gate/up pair: the
+// 64-row boxes of the gate and of the up handle (the descriptors the single-CTA kernel uses).
+int launch_gemm_tcgen05_2cta(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap) {
     const CUtensorMap &tw = *static_cast<const CUtensorMap *>(w_tmap);
-    if (a.y_dtype == SHREWQ_BF16) return launch_pair<__nv_bfloat16>(ctx, a, tw);
-    return launch_pair<float>(ctx, a, tw);
+    if (a.q_up) {
+        if (!w_up_tmap) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "tcgen05-2cta: the up matrix has no tensor map");
+        const CUtensorMap &tw2 = *static_cast<const CUtensorMap *>(w_up_tmap);
+        if (a.y_dtype == SHREWQ_BF16) return launch_pair<__nv_bfloat16, true>(ctx, a, tw, tw2);
+        return launch_pair<float, true>(ctx, a, tw, tw2);
+    }
+    if (a.y_dtype == SHREWQ_BF16) return launch_pair<__nv_bfloat16, false>(ctx, a, tw, tw);
+    return launch_pair<float, false>(ctx, a, tw, tw);
 }
 
 }  // namespace shrewq

@@ -136,13 +136,21 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16 *p, float
 struct Operands2 {
     const float *scales;
     const float *bias;
+    const float *scales2;  // up matrix (GATED)
+    const float *bias2;
 };
 
-template <typename YT>
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
+
+// GATED: as in the single-CTA kernel, the 128 lanes of a CTA carry 64 rows of a gate matrix (tmap_w,
+// 64-row boxes) and the same 64 rows of an up matrix (tmap_w2); the epilogue pairs lane r with lane
+// r + 64 and writes silu(gate) * up for 64 channels per CTA, 128 per pair.
+template <typename YT, bool GATED>
 __global__ void SHREWQ_CLUSTER_OF_2 __launch_bounds__(kThreads, 1)
-linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                              Operands2 ops, YT *__restrict__ y, Dests extra, int M, int N, int K, size_t ldy,
-                              int epilogue, DeviceStatus *status) {
+linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
+                              const __grid_constant__ CUtensorMap tmap_x, Operands2 ops, YT *__restrict__ y, Dests extra,
+                              int M, int N, int K, size_t ldy, int epilogue, DeviceStatus *status) {
+    constexpr int kChan = GATED ? kLanes / 2 : kLanes;  // output channels per CTA
     SHREWQ_DYNAMIC_SMEM(uint8_t, smem_raw);
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *bar_area = smem + kStages * kStageBytes;
@@ -152,7 +160,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const int pair = blockIdx.x >> 1;
-    const int n0 = pair * 2 * kLanes + (int)rank * kLanes;       // this CTA's first channel
+    const int n0 = pair * 2 * kChan + (int)rank * kChan;         // this CTA's first channel
     const int m0 = blockIdx.y * kTokPair + (int)rank * kTokHalf;  // this CTA's first token (B half)
     const int m0_pair = blockIdx.y * kTokPair;
     const int rounds = (K + kBlockK * kSub - 1) / (kBlockK * kSub);
@@ -199,7 +207,12 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                 if (rank == 0) mbar_expect_tx(xb, 2 * kSub * kXSub);  // the halves of both CTAs
 #pragma unroll
                 for (int j = 0; j < kSub; ++j) {
-                    tma_load_2d(dst + j * kWSub, &tmap_w, kc + j * kBlockK, n0, wb);
+                    if constexpr (GATED) {
+                        tma_load_2d(dst + j * kWSub, &tmap_w, kc + j * kBlockK, n0, wb);
+                        tma_load_2d(dst + j * kWSub + (kLanes / 2) * kBlockK, &tmap_w2, kc + j * kBlockK, n0, wb);
+                    } else {
+                        tma_load_2d(dst + j * kWSub, &tmap_w, kc + j * kBlockK, n0, wb);
+                    }
                     tma_load_2d_pair(dst + kXOff + j * kXSub, &tmap_x, kc + j * kBlockK, m0, xb);
                 }
                 kc += kSub * kBlockK;
@@ -276,19 +289,47 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(aready_leader + s * 8);
         }
-        // epilogue: this CTA's 128 channels x the pair's 256 tokens
+        // epilogue: this CTA's channels x the pair's 256 tokens; 16-column chunks dealt to the groups
         if (ok) ok = mbar_wait_warp(bars_u32 + kAcc, 0, ctl, status, 4, 0);
-        if (ok) {
-            tc_fence_after();
-            const int n = n0 + row;
-            const bool n_ok = n < N;
-            const float sc = n_ok ? ops.scales[n] : 0.0f;
-            const float bs = (n_ok && ops.bias) ? ops.bias[n] : 0.0f;
+        if (ok) tc_fence_after();
+        const bool is_up = GATED && row >= kLanes / 2;
+        const int n = n0 + (GATED ? (row & (kLanes / 2 - 1)) : row);
+        const bool n_ok = n < N;
+        const float *sc_p = is_up ? ops.scales2 : ops.scales;
+        const float *bs_p = is_up ? ops.bias2 : ops.bias;
+        const float sc = n_ok ? sc_p[n] : 0.0f;
+        const float bs = (n_ok && bs_p) ? bs_p[n] : 0.0f;
+        // gate/up: the up half hands its values to the gate half through shared memory (the pipeline
+        // stages are idle once the accumulators are complete); the named barriers are reached by every
+        // thread of the group whether or not its waits succeeded
+        float *xch = reinterpret_cast<float *>(smem) + group * (16 * 64);
 #pragma unroll 1
-            for (int c = group; c < kTokPair / 16; c += kGroups) {
-                uint32_t r[16];
+        for (int c = group; c < kTokPair / 16; c += kGroups) {
+            uint32_t r[16];
+            if (ok) {
                 tc_ld16(tmem_base + lane_addr + c * 16, r);
                 tc_wait_ld();
+            }
+            if constexpr (GATED) {
+                if (is_up && ok) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) xch[i * 64 + (row - 64)] = __uint_as_float(r[i]) * sc + bs;
+                }
+                named_bar_sync(2 + group, 128);
+                if (!is_up && ok) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int m = m0_pair + c * 16 + i;
+                        const float o = silu_f(__uint_as_float(r[i]) * sc + bs) * xch[i * 64 + row];
+                        if (n_ok && m < M) {
+                            const size_t off = (size_t)m * ldy + n;
+                            store_out<YT>(y + off, o);
+                            for (int d = 0; d < extra.n; ++d) store_out<YT>(static_cast<YT *>(extra.p[d]) + off, o);
+                        }
+                    }
+                }
+                named_bar_sync(2 + group, 128);  // xch is rewritten by the next chunk
+            } else if (ok) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int m = m0_pair + c * 16 + i;

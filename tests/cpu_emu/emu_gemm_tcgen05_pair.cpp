@@ -9,29 +9,40 @@
 using namespace shrewq;
 
 namespace {
-template <typename YT>
-int run(const int8_t *q, const float *scales, const float *bias, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
+template <typename YT, bool GATED>
+int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
         int epilogue, DeviceStatus *st) {
-    const CUtensorMap tw{q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, 128, 64};
+    const uint32_t box_rows = GATED ? 64 : 128;
+    const CUtensorMap tw{q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
+    const CUtensorMap tw2{GATED ? q_up : q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
     const CUtensorMap tx{x, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, kBlockK, kTokHalf, 128};
-    const unsigned pairs = (unsigned)((N + 2 * kLanes - 1) / (2 * kLanes));
-    Operands2 ops{scales, bias};
+    const int chan_pair = GATED ? kLanes : 2 * kLanes;
+    const unsigned pairs = (unsigned)((N + chan_pair - 1) / chan_pair);
     Dests none{};
     emu::launch_cluster2(2 * pairs, (unsigned)((M + kTokPair - 1) / kTokPair), kThreads, kSmemBytes, [&] {
-        linear_i8_tcgen05_pair_kernel<YT>(tw, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, st);
+        linear_i8_tcgen05_pair_kernel<YT, GATED>(tw, tw2, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, st);
     });
     return 0;
 }
 }  // namespace
 
-// Returns 0; -1 for a shape the launcher refuses; -2 when a bounded wait of the kernel gave up.
-extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const float *bias, const void *x, void *y, int M,
-                                     int N, int K, size_t ldy, int epilogue, int y_bf16) {
+// q_up == NULL: plain forward; else silu(gate) * up.  Returns 0; -1 for a shape the launcher refuses; -2 when
+// a bounded wait of the kernel gave up; -4 when a rule of the model was violated.
+extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const float *bias, const int8_t *q_up,
+                                     const float *scales_up, const float *bias_up, const void *x, void *y, int M, int N, int K,
+                                     size_t ldy, int epilogue, int y_bf16) {
     if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || M < 1) return -1;
     DeviceStatus st{0, 0, 0, 0};
     emu::g_failed = false;
-    if (y_bf16) run<__nv_bfloat16>(q, scales, bias, static_cast<const uint16_t *>(x), y, M, N, K, ldy, epilogue, &st);
-    else run<float>(q, scales, bias, static_cast<const uint16_t *>(x), y, M, N, K, ldy, epilogue, &st);
+    const Operands2 ops{scales, bias, scales_up, bias_up};
+    const uint16_t *xs = static_cast<const uint16_t *>(x);
+    if (q_up) {
+        if (y_bf16) run<__nv_bfloat16, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, &st);
+        else run<float, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, &st);
+    } else {
+        if (y_bf16) run<__nv_bfloat16, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, &st);
+        else run<float, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, &st);
+    }
     if (emu::g_failed) return -4;  // a rule of the model was violated (emu_fail_message)
     return st.timeout_flag ? -2 : 0;
 }

@@ -519,7 +519,7 @@ def test_f32_activations_through_two_tensor_core_passes(oracle, emu, emu_tc):
 @pytest.fixture(scope="module")
 def emu_pair():
     L = _build("emu_gemm_tcgen05_pair")
-    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci]
+    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci]
     return L
 
 
@@ -534,11 +534,11 @@ def test_cta_pair_forward_matches_oracle(oracle, emu_pair, M, N, K):
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
     ldy = N + 2
     y = np.full((M, ldy), 7.0, np.float32)
-    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(xa), _p(y), M, N, K, ldy, 1, 0) == 0
+    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, ldy, 1, 0) == 0
     assert oracle.rel_err(y[:, :N], ref) < 2e-6
     assert np.all(y[:, N:] == 7.0)
     y16 = np.full((M, N), 0x4100, np.uint16)
-    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), None, _p(xa), _p(y16), M, N, K, N, 0, 1) == 0
+    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), None, None, None, None, _p(xa), _p(y16), M, N, K, N, 0, 1) == 0
     ref_nb = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, None, x)
     assert oracle.rel_err((y16.astype(np.uint32) << 16).view(np.float32), ref_nb) < 1e-2
 
@@ -590,7 +590,7 @@ def test_tcgen05_wait_that_runs_out_ends_the_kernel(tok, M, N, K, splits, gated,
 @pytest.mark.timeout(300)
 def test_cta_pair_wait_that_runs_out_ends_both_blocks():
     L = _build_short_waits("emu_gemm_tcgen05_pair")
-    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci]
+    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci]
     L.emu_drop_tma.argtypes = [_ci]
     q, scales, bias, x_bits, x = _tc_case(256, 256, 1024, 1)
     qa = _aligned(q.shape, np.int8)
@@ -602,7 +602,7 @@ def test_cta_pair_wait_that_runs_out_ends_both_blocks():
     for drop in (0, 1, 9, 14):   # a code load or an activation load, of the leader or of the peer
         L.emu_drop_tma(drop)
         try:
-            rc = L.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(xa), _p(y), 256, 256, 1024, 256, 0, 0)
+            rc = L.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 256, 256, 1024, 256, 0, 0)
         finally:
             L.emu_drop_tma(-1)
         assert rc == -2, drop
@@ -768,7 +768,31 @@ def test_cta_pair_with_loads_landing_late_and_out_of_order(oracle, emu_pair):
         y = np.zeros((300, 260), np.float32)
         emu_pair.emu_tma_async(seed, one_in)
         try:
-            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(xa), _p(y), 300, 260, 2048, 260, 0, 0) == 0
+            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 300, 260, 2048, 260, 0, 0) == 0
         finally:
             emu_pair.emu_tma_async(0, 0)
         assert oracle.rel_err(y, ref) < 2e-6
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 128, 256), (300, 200, 384), (40, 70, 1024), (513, 300, 128)])
+def test_cta_pair_gate_up_tile(oracle, emu_pair, M, N, K):
+    # gate/up on CTA pairs: each block carries 64 gate + 64 up rows, the pair 128 channels x 256 tokens
+    rng = np.random.default_rng(M + K)
+    qg, qu = (rng.integers(-127, 128, size=(N, K)).astype(np.int8) for _ in range(2))
+    sg, su = rng.random(N) * 1e-2 + 1e-4, rng.random(N) * 1e-2 + 1e-4
+    bg, bu = ((rng.standard_normal(N) * 0.1).astype(np.float32) for _ in range(2))
+    x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    g = oracle.np_linear_forward(qg, sg, 1, bg, x).astype(np.float64)
+    u = oracle.np_linear_forward(qu, su, 1, bu, x).astype(np.float64)
+    ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    qga, qua = _aligned(qg.shape, np.int8), _aligned(qu.shape, np.int8)
+    qga[...] = qg
+    qua[...] = qu
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    sg32, su32 = sg.astype(np.float32), su.astype(np.float32)
+    y = np.full((M, N), 7.0, np.float32)
+    rc = emu_pair.emu_gemm_tcgen05_pair(_p(qga), _p(sg32), _p(bg), _p(qua), _p(su32), _p(bu), _p(xa), _p(y), M, N, K, N, 0, 0)
+    assert rc == 0
+    assert oracle.rel_err(y, ref) < 1e-5
+

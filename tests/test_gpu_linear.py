@@ -347,3 +347,27 @@ def test_cta_pair_kernel_parity(oracle, M, N, K):
     ql, w, b = _make(N, K, 1, seed=N + K)
     x_t, x_np = _x(M, K, "bf16", seed=M)
     _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, force="tcgen05-2cta")
+
+
+@_UNVALIDATED
+def test_cta_pair_gate_up_parity(oracle):
+    from shrew_b200 import _lib
+    from shrew_b200.quantize import Device
+    gate, wg, _ = _make(1000, 1024, 1, seed=0, bias=False)
+    up, wu, _ = _make(1000, 1024, 1, seed=1, bias=False)
+    x_t, x_np = _x(300, 1024, "bf16")
+    _lib.lib().shrewq_force_kernel(b"tcgen05-2cta")
+    try:
+        h = gate.forward_gate_up_silu(up, x_t)
+        Device.get("cuda:0").synchronize()
+    finally:
+        _lib.lib().shrewq_force_kernel(b"auto")
+
+    def fwd(ql):
+        q = ql.weight_q.data.cpu().numpy().reshape(ql.out_features, ql.in_features)
+        return oracle.np_linear_forward(q, ql.weight_q.scales.cpu().numpy(), 1, None, x_np)
+
+    g_ref, u_ref = fwd(gate), fwd(up)
+    h_ref = (g_ref / (1.0 + np.exp(-g_ref.astype(np.float64)))).astype(np.float32) * u_ref
+    assert oracle.rel_err(h.float().cpu().numpy(), h_ref) < TOL_BF16
+
