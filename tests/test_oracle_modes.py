@@ -74,7 +74,7 @@ def test_ref_int4_symmetric_round_trip(oracle):
 def test_modes_property_c_equals_numpy(oracle):
     from hypothesis import given, settings, strategies as st
 
-    @settings(max_examples=80, deadline=None)
+    @settings(max_examples=150, deadline=None, derandomize=True)
     @given(rows=st.integers(1, 7), cols=st.integers(0, 30), gran=st.integers(0, 1), bits=st.sampled_from([4, 8]),
            mode=st.integers(0, 1), log_scale=st.floats(-33, 33), shift=st.floats(-3, 3), seed=st.integers(0, 2 ** 31 - 1),
            special=st.sampled_from([None, np.nan, np.inf, -np.inf, -0.0]))
@@ -91,8 +91,9 @@ def test_modes_property_c_equals_numpy(oracle):
         qmax = 7 if bits == 4 else 127
         qmin = -(qmax + 1) if mode else -qmax
         assert qc.min(initial=0) >= qmin and qc.max(initial=0) <= qmax
-        if np.isfinite(w).all() and w.size:
-            # round trip within one quantization step of every element (finite inputs)
+        if np.isfinite(w).all() and w.size and np.all(np.abs(sc) >= 1e-30):
+            # round trip within one quantization step of every element (finite inputs; a scale under
+            # 1e-30 makes the reference use an inverse of 0, i.e. every code 0: quantize.rs:236-240)
             rec = oracle.dequantize_f64_ex(qc, sc, zc, gran)
             step = (sc.reshape(-1, 1) if gran else sc.reshape(1, 1)) * np.ones((rows, 1))
             with np.errstate(invalid="ignore", over="ignore"):
