@@ -47,10 +47,34 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
     }
     constexpr int kChanPair = GATED ? kLanes : 2 * kLanes;  // output channels per CTA pair
     const unsigned pairs = (unsigned)((a.N + kChanPair - 1) / kChanPair);
-    dim3 grid(2 * pairs, (unsigned)((a.M + kTokPair - 1) / kTokPair), 1);
+    const unsigned m_tiles = (unsigned)((a.M + kTokPair - 1) / kTokPair);
+    // split-K when the CTA grid leaves SMs idle: as many splits as fit in one wave, >= 8 rounds each
+    const int rounds = (int)((a.K + kBlockK * kSub - 1) / (kBlockK * kSub));
+    const long ctas = 2L * pairs * m_tiles;
+    int splits = 1;
+    if (ctas <= 1024) {
+        int want = (int)(ctx->sm_count / ctas);
+        if (want > rounds / 8) want = rounds / 8;
+        if (want > 1) splits = want;
+    }
+    const int rps = (rounds + splits - 1) / splits;
+    splits = (rounds + rps - 1) / rps;  // no empty split
+    SplitK2 sk{nullptr, nullptr, rps};
+    if (splits > 1) {
+        // context scratch as in the single-CTA launcher: tile counters at 4096, partial sums from 8192
+        const size_t part_bytes = (size_t)ctas * splits * kTokPair * kLanes * sizeof(float);
+        if ((rc = ensure_scratch(ctx, 8192 + part_bytes)) != SHREWQ_OK) return rc;
+        if (!ctx->counters_zeroed) {
+            SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(static_cast<char *>(ctx->scratch) + 4096, 0, 4096, ctx->stream));
+            ctx->counters_zeroed = true;
+        }
+        sk.counters = reinterpret_cast<unsigned int *>(static_cast<char *>(ctx->scratch) + 4096);
+        sk.partials = reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + 8192);
+    }
+    dim3 grid(2 * pairs, m_tiles, (unsigned)splits);
     Operands2 ops{a.scales, a.bias, a.scales_up, a.bias_up};
     kern<<<grid, kThreads, kSmemBytes, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N,
-                                                      (int)a.K, a.ldy, a.epilogue, ctx->dev_status);
+                                                      (int)a.K, a.ldy, a.epilogue, sk, ctx->dev_status);
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;

@@ -142,6 +142,16 @@ struct Operands2 {
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
+// Split-K (gridDim.z > 1): CTA (x, y, z) walks pipeline rounds [z * rounds_per_split, ...) of its tile
+// and parks its raw accumulators in `partials`; the CTA arriving last at the tile's counter adds the
+// slices in split order, applies the epilogue and resets the counter.  Every CTA of a pair is a tile
+// of its own here (128 lanes x 256 tokens), so nothing crosses the pair in the reduction.
+struct SplitK2 {
+    float *partials;         // [tile][split][256 tokens][128 lanes] f32
+    unsigned int *counters;  // one per CTA tile, zero between launches
+    int rounds_per_split;
+};
+
 // GATED: as in the single-CTA kernel, the 128 lanes of a CTA carry 64 rows of a gate matrix (tmap_w,
 // 64-row boxes) and the same 64 rows of an up matrix (tmap_w2); the epilogue pairs lane r with lane
 // r + 64 and writes silu(gate) * up for 64 channels per CTA, 128 per pair.
@@ -149,7 +159,7 @@ template <typename YT, bool GATED>
 __global__ void SHREWQ_CLUSTER_OF_2 __launch_bounds__(kThreads, 1)
 linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
                               const __grid_constant__ CUtensorMap tmap_x, Operands2 ops, YT *__restrict__ y, Dests extra,
-                              int M, int N, int K, size_t ldy, int epilogue, DeviceStatus *status) {
+                              int M, int N, int K, size_t ldy, int epilogue, SplitK2 sk, DeviceStatus *status) {
     constexpr int kChan = GATED ? kLanes / 2 : kLanes;  // output channels per CTA
     SHREWQ_DYNAMIC_SMEM(uint8_t, smem_raw);
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -163,7 +173,10 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
     const int n0 = pair * 2 * kChan + (int)rank * kChan;         // this CTA's first channel
     const int m0 = blockIdx.y * kTokPair + (int)rank * kTokHalf;  // this CTA's first token (B half)
     const int m0_pair = blockIdx.y * kTokPair;
-    const int rounds = (K + kBlockK * kSub - 1) / (kBlockK * kSub);
+    const int rounds_total = (K + kBlockK * kSub - 1) / (kBlockK * kSub);
+    const int r_begin = (int)blockIdx.z * sk.rounds_per_split;
+    const int rounds = min(rounds_total - r_begin, sk.rounds_per_split);  // >= 1 by construction of the grid
+    int *s_is_last = reinterpret_cast<int *>(bar_area + 640);
     // barrier byte offsets
     constexpr uint32_t kWFull = 0, kXFull = kStages * 8, kAready = 2 * kStages * 8, kEmpty = 3 * kStages * 8,
                        kAcc = 4 * kStages * 8;
@@ -199,7 +212,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
         if (lane == 0) {
             uint32_t s = 0, ph = 1;
             uint32_t dst = smem_base;
-            int kc = 0;
+            int kc = r_begin * kSub * kBlockK;
             for (int i = 0; i < rounds; ++i) {
                 if (!mbar_wait(bars_u32 + kEmpty + s * 8, ph, ctl, status, 0, s)) break;
                 const uint32_t wb = bars_u32 + kWFull + s * 8, xb = bars_u32 + kXFull + s * 8;
@@ -303,6 +316,61 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
         // stages are idle once the accumulators are complete); the named barriers are reached by every
         // thread of the group whether or not its waits succeeded
         float *xch = reinterpret_cast<float *>(smem) + group * (16 * 64);
+        const int splits = (int)gridDim.z;
+        if (splits > 1) {
+            const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+            float *mine = sk.partials + (tile * splits + blockIdx.z) * (size_t)(kTokPair * kLanes);
+            if (ok) {
+#pragma unroll 1
+                for (int c = group; c < kTokPair / 16; c += kGroups) {
+                    uint32_t r[16];
+                    tc_ld16(tmem_base + lane_addr + c * 16, r);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) __stcg(mine + (c * 16 + i) * kLanes + row, __uint_as_float(r[i]));
+                }
+            }
+            __threadfence();
+            named_bar_sync(1, 128 * kGroups);
+            if (threadIdx.x == 64) {
+                const unsigned int old = atomicAdd(sk.counters + tile, 1u);
+                *s_is_last = (old == (unsigned int)(splits - 1));
+            }
+            named_bar_sync(1, 128 * kGroups);
+            if (*s_is_last) {
+                __threadfence();
+                const float *base = sk.partials + tile * splits * (size_t)(kTokPair * kLanes);
+                if (ok && !is_up) {
+#pragma unroll 1
+                    for (int c = group; c < kTokPair / 16; c += kGroups) {
+#pragma unroll 4
+                        for (int i = 0; i < 16; ++i) {
+                            const int ml = c * 16 + i, m = m0_pair + ml;
+                            float acc = 0.0f, acc2 = 0.0f;
+                            for (int z = 0; z < splits; ++z) {
+                                const float *p = base + (size_t)z * (kTokPair * kLanes) + ml * kLanes + row;
+                                acc += __ldcg(p);
+                                if constexpr (GATED) acc2 += __ldcg(p + kLanes / 2);
+                            }
+                            float o = acc * sc + bs;
+                            if constexpr (GATED) {
+                                const float u = acc2 * (n_ok ? ops.scales2[n] : 0.0f) + ((n_ok && ops.bias2) ? ops.bias2[n] : 0.0f);
+                                o = silu_f(o) * u;
+                            } else if ((epilogue & 0xFF) == SHREWQ_EPILOGUE_RELU) {
+                                o = fmaxf(o, 0.0f);
+                            }
+                            if (n_ok && m < M) {
+                                const size_t off = (size_t)m * ldy + n;
+                                store_out<YT>(y + off, o);
+                                for (int d = 0; d < extra.n; ++d) store_out<YT>(static_cast<YT *>(extra.p[d]) + off, o);
+                            }
+                        }
+                    }
+                }
+                named_bar_sync(1, 128 * kGroups);
+                if (threadIdx.x == 64) sk.counters[tile] = 0;  // ready for the next launch
+            }
+        } else {
 #pragma unroll 1
         for (int c = group; c < kTokPair / 16; c += kGroups) {
             uint32_t r[16];
@@ -343,6 +411,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                 }
             }
         }
+        }  // splits == 1
     }
 
     // ---------------- teardown: both CTAs are done with tensor memory before it is freed ----------------

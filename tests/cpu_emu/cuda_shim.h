@@ -131,7 +131,7 @@ inline void launch(unsigned grid, unsigned block, size_t dyn_bytes, const std::f
 }
 // Clusters of 2 blocks along x: the two blocks of a cluster run at the same time (2 * block threads),
 // clusters one after the other.  gx must be even.
-inline void launch_cluster2(unsigned gx, unsigned gy, unsigned block, size_t dyn_bytes, const std::function<void()> &body) {
+inline void launch_cluster2(unsigned gx, unsigned gy, unsigned gz, unsigned block, size_t dyn_bytes, const std::function<void()> &body) {
     unsigned char *region = static_cast<unsigned char *>(std::aligned_alloc(size_t(1) << 19, size_t(1) << 19));
     {
         Block b0(block, dyn_bytes, region), b1(block, dyn_bytes, region + (size_t(1) << 18));
@@ -152,13 +152,14 @@ inline void launch_cluster2(unsigned gx, unsigned gy, unsigned block, size_t dyn
                     g_block = both[r];
                     threadIdx = emu_uint3{t, 0, 0};
                     blockDim = emu_uint3{block, 1, 1};
-                    gridDim = emu_uint3{gx, gy, 1};
-                    for (unsigned y = 0; y < gy; ++y)
-                        for (unsigned c = 0; c < gx / 2; ++c) {
-                            blockIdx = emu_uint3{2 * c + r, y, 0};
-                            body();
-                            cluster_bar.arrive_and_wait();  // the next cluster reuses the blocks' memories
-                        }
+                    gridDim = emu_uint3{gx, gy, gz};
+                    for (unsigned z = 0; z < gz; ++z)
+                        for (unsigned y = 0; y < gy; ++y)
+                            for (unsigned c = 0; c < gx / 2; ++c) {
+                                blockIdx = emu_uint3{2 * c + r, y, z};
+                                body();
+                                cluster_bar.arrive_and_wait();  // the next cluster reuses the blocks' memories
+                            }
                 });
             }
         for (auto &th : pool) th.join();

@@ -11,7 +11,7 @@ using namespace shrewq;
 namespace {
 template <typename YT, bool GATED>
 int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
-        int epilogue, DeviceStatus *st) {
+        int epilogue, int splits, DeviceStatus *st) {
     const uint32_t box_rows = GATED ? 64 : 128;
     const CUtensorMap tw{q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
     const CUtensorMap tw2{GATED ? q_up : q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
@@ -19,32 +19,46 @@ int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_
     const int chan_pair = GATED ? kLanes : 2 * kLanes;
     const unsigned pairs = (unsigned)((N + chan_pair - 1) / chan_pair);
     Dests none{};
-    emu::launch_cluster2(2 * pairs, (unsigned)((M + kTokPair - 1) / kTokPair), kThreads, kSmemBytes, [&] {
-        linear_i8_tcgen05_pair_kernel<YT, GATED>(tw, tw2, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, st);
+    const unsigned m_tiles = (unsigned)((M + kTokPair - 1) / kTokPair);
+    const int rounds = (K + kBlockK * kSub - 1) / (kBlockK * kSub);
+    if (splits < 1) splits = 1;
+    const int rps = (rounds + splits - 1) / splits;
+    splits = (rounds + rps - 1) / rps;  // no empty split
+    const size_t ctas = (size_t)2 * pairs * m_tiles;
+    std::vector<float> partials(splits > 1 ? ctas * splits * kTokPair * kLanes : 0, -12345.0f);
+    std::vector<unsigned int> counters(ctas, 0u);
+    SplitK2 sk{splits > 1 ? partials.data() : nullptr, splits > 1 ? counters.data() : nullptr, rps};
+    emu::launch_cluster2(2 * pairs, m_tiles, (unsigned)splits, kThreads, kSmemBytes, [&] {
+        linear_i8_tcgen05_pair_kernel<YT, GATED>(tw, tw2, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, sk, st);
     });
+    for (unsigned int c : counters)
+        if (c != 0) return -3;  // the kernel leaves the tile counters at zero for the next launch
     return 0;
 }
 }  // namespace
 
-// q_up == NULL: plain forward; else silu(gate) * up.  Returns 0; -1 for a shape the launcher refuses; -2 when
-// a bounded wait of the kernel gave up; -4 when a rule of the model was violated.
+// q_up == NULL: plain forward; else silu(gate) * up.  splits: K splits (blockIdx.z).  Returns 0; -1 for a shape
+// the launcher refuses; -2 when a bounded wait of the kernel gave up; -3 when a tile counter was left set;
+// -4 when a rule of the model was violated.
 extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const float *bias, const int8_t *q_up,
                                      const float *scales_up, const float *bias_up, const void *x, void *y, int M, int N, int K,
-                                     size_t ldy, int epilogue, int y_bf16) {
+                                     size_t ldy, int epilogue, int y_bf16, int splits) {
     if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || M < 1) return -1;
     DeviceStatus st{0, 0, 0, 0};
     emu::g_failed = false;
     const Operands2 ops{scales, bias, scales_up, bias_up};
     const uint16_t *xs = static_cast<const uint16_t *>(x);
+    int rc;
     if (q_up) {
-        if (y_bf16) run<__nv_bfloat16, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, &st);
-        else run<float, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, &st);
+        if (y_bf16) rc = run<__nv_bfloat16, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, &st);
+        else rc = run<float, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, &st);
     } else {
-        if (y_bf16) run<__nv_bfloat16, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, &st);
-        else run<float, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, &st);
+        if (y_bf16) rc = run<__nv_bfloat16, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, &st);
+        else rc = run<float, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, &st);
     }
     if (emu::g_failed) return -4;  // a rule of the model was violated (emu_fail_message)
-    return st.timeout_flag ? -2 : 0;
+    if (st.timeout_flag) return -2;
+    return rc;
 }
 
 // fault injection: drop the n-th TMA load of the next launches (-1 = none); resets the running count

@@ -519,7 +519,7 @@ def test_f32_activations_through_two_tensor_core_passes(oracle, emu, emu_tc):
 @pytest.fixture(scope="module")
 def emu_pair():
     L = _build("emu_gemm_tcgen05_pair")
-    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci]
+    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci]
     return L
 
 
@@ -534,11 +534,11 @@ def test_cta_pair_forward_matches_oracle(oracle, emu_pair, M, N, K):
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
     ldy = N + 2
     y = np.full((M, ldy), 7.0, np.float32)
-    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, ldy, 1, 0) == 0
+    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, ldy, 1, 0, 1) == 0
     assert oracle.rel_err(y[:, :N], ref) < 2e-6
     assert np.all(y[:, N:] == 7.0)
     y16 = np.full((M, N), 0x4100, np.uint16)
-    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), None, None, None, None, _p(xa), _p(y16), M, N, K, N, 0, 1) == 0
+    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), None, None, None, None, _p(xa), _p(y16), M, N, K, N, 0, 1, 1) == 0
     ref_nb = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, None, x)
     assert oracle.rel_err((y16.astype(np.uint32) << 16).view(np.float32), ref_nb) < 1e-2
 
@@ -590,7 +590,7 @@ def test_tcgen05_wait_that_runs_out_ends_the_kernel(tok, M, N, K, splits, gated,
 @pytest.mark.timeout(300)
 def test_cta_pair_wait_that_runs_out_ends_both_blocks():
     L = _build_short_waits("emu_gemm_tcgen05_pair")
-    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci]
+    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci]
     L.emu_drop_tma.argtypes = [_ci]
     q, scales, bias, x_bits, x = _tc_case(256, 256, 1024, 1)
     qa = _aligned(q.shape, np.int8)
@@ -602,7 +602,7 @@ def test_cta_pair_wait_that_runs_out_ends_both_blocks():
     for drop in (0, 1, 9, 14):   # a code load or an activation load, of the leader or of the peer
         L.emu_drop_tma(drop)
         try:
-            rc = L.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 256, 256, 1024, 256, 0, 0)
+            rc = L.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 256, 256, 1024, 256, 0, 0, 1)
         finally:
             L.emu_drop_tma(-1)
         assert rc == -2, drop
@@ -768,7 +768,7 @@ def test_cta_pair_with_loads_landing_late_and_out_of_order(oracle, emu_pair):
         y = np.zeros((300, 260), np.float32)
         emu_pair.emu_tma_async(seed, one_in)
         try:
-            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 300, 260, 2048, 260, 0, 0) == 0
+            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 300, 260, 2048, 260, 0, 0, 1) == 0
         finally:
             emu_pair.emu_tma_async(0, 0)
         assert oracle.rel_err(y, ref) < 2e-6
@@ -792,7 +792,34 @@ def test_cta_pair_gate_up_tile(oracle, emu_pair, M, N, K):
     xa[...] = x_bits
     sg32, su32 = sg.astype(np.float32), su.astype(np.float32)
     y = np.full((M, N), 7.0, np.float32)
-    rc = emu_pair.emu_gemm_tcgen05_pair(_p(qga), _p(sg32), _p(bg), _p(qua), _p(su32), _p(bu), _p(xa), _p(y), M, N, K, N, 0, 0)
+    rc = emu_pair.emu_gemm_tcgen05_pair(_p(qga), _p(sg32), _p(bg), _p(qua), _p(su32), _p(bu), _p(xa), _p(y), M, N, K, N, 0, 0, 1)
     assert rc == 0
     assert oracle.rel_err(y, ref) < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K,splits,gated", [(300, 256, 2048, 2, False), (256, 130, 3072, 3, False), (100, 128, 2048, 4, True)])
+def test_cta_pair_split_k(oracle, emu_pair, M, N, K, splits, gated):
+    # K split over blockIdx.z; every CTA of a pair reduces its own 128 lanes x 256 tokens
+    rng = np.random.default_rng(K + splits)
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, splits)
+    qa = _aligned(q.shape, np.int8)
+    qa[...] = q
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    s32 = scales.astype(np.float32)
+    y = np.full((M, N), 7.0, np.float32)
+    if gated:
+        qu = _aligned(q.shape, np.int8)
+        qu[...] = rng.integers(-127, 128, size=q.shape)
+        su = rng.random(N) * 1e-2 + 1e-4
+        su32 = su.astype(np.float32)
+        rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(qu), _p(su32), None, _p(xa), _p(y), M, N, K, N, 0, 0, splits)
+        g = oracle.np_linear_forward(q, scales, 1, bias, x).astype(np.float64)
+        u = oracle.np_linear_forward(np.array(qu), su, 1, None, x).astype(np.float64)
+        ref, tol = (g / (1.0 + np.exp(-g)) * u).astype(np.float32), 1e-5
+    else:
+        rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, N, 1, 0, splits)
+        ref, tol = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True), 2e-6
+    assert rc == 0
+    assert oracle.rel_err(y, ref) < tol
 
