@@ -248,6 +248,11 @@ int shrewq_quantize_f32_given_amax(shrewq_ctx *ctx, const float *w_dev, size_t n
 // ---- the reference's other modes (asymmetric INT8, INT4) ------------------------------------
 // Built and checked against the CPU restatement by reading only: until they have run on a GPU
 // they answer SHREWQ_ERR_UNSUPPORTED unless the environment sets SHREWQ_EXPERIMENTAL_MODES=1.
+static bool env_flag(const char *name) {
+    const char *e = getenv(name);
+    return e && atoi(e) != 0;
+}
+
 static bool experimental_modes() {
     const char *e = getenv("SHREWQ_EXPERIMENTAL_MODES");
     return e && atoi(e) != 0;
@@ -500,6 +505,16 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             if (!gemv_mma_supported(a)) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced mma kernel cannot take this shape/dtype", who);
             choice = g_forced_kernel; break;
         default:
+            // Candidate rules, off unless the environment asks (kernels not yet run on a GPU): the f16
+            // warp-MMA kernel for batches up to 64 (SHREWQ_AUTO_MMA_F16=1), CTA pairs for batches above
+            // 128 (SHREWQ_AUTO_PAIR=1).  They let the whole test-suite and the benchmark run on those
+            // kernels before the rule below is changed.
+            if (env_flag("SHREWQ_AUTO_MMA_F16") && M <= 64 && gemv_mma_supported(a)) { choice = kForceMmaF16; break; }
+            if (env_flag("SHREWQ_AUTO_PAIR") && M > 128 && tc_ok && !zp_route) {
+                rc = up ? launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap, nullptr);
+                lin->last_kernel = "tcgen05-2cta";
+                return rc;
+            }
             // CUDA-core GEMV keeps up with HBM only for a few tokens; beyond that the tensor
             // cores take over (bf16 activations), else the general f32 kernel.
             if (gemv_ok && (M <= 4 || !tc_ok)) choice = kForceGemv;
