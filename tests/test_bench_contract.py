@@ -1,0 +1,35 @@
+"""CPU: the benchmark's reference arm prints the contract's JSON line, and the GPU arm refuses to run
+without a CUDA device instead of falling back to anything."""
+import json
+import os
+import subprocess
+import sys
+
+from tests.conftest import ROOT
+
+
+def _run(*args):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], capture_output=True, text=True, cwd=ROOT,
+                          env=env, timeout=600)
+
+
+def test_reference_arm_prints_the_contract_line():
+    r = _run("--impl", "reference", "--steps", "1", "--warmup", "1", "--workload", "linear4096_m1")
+    assert r.returncode == 0, r.stderr
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference"
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
+        assert key in line, key
+    assert line["metric"] == "quantized_linear_tokens_per_s" and line["unit"] == "tokens/s"
+    assert line["config"]["workload"] == "linear4096_m1"
+    assert line["cpu_baseline"]["kind"] in ("port", "reference") and line["cpu_baseline"]["value"] == line["value"]
+    assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert line["warmup"] >= 3 and line["value"] > 0
+
+
+def test_gpu_arm_has_no_cpu_fallback():
+    r = _run("--steps", "1", "--warmup", "1")
+    assert r.returncode != 0
+    assert "no CUDA device" in (r.stderr + r.stdout)
