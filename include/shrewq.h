@@ -56,6 +56,9 @@ extern "C" {
 /* element types of activations / outputs (shrew_core DType F32 and BF16) */
 #define SHREWQ_F32 0
 #define SHREWQ_BF16 1
+/* storage types accepted only by shrewq_quantize_any / shrewq_dequantize_ex */
+#define SHREWQ_F16 2
+#define SHREWQ_F64 3
 /* elementwise op fused after the bias add (the tensor op a caller applies next) */
 /* QuantMode (quantize.rs:51-58) */
 #define SHREWQ_SYMMETRIC 0
@@ -130,6 +133,14 @@ SHREWQ_API int shrewq_quantize_f32_given_amax(shrewq_ctx *ctx, const float *w_de
 SHREWQ_API int shrewq_quantize_f32_ex(shrewq_ctx *ctx, const float *w_dev, size_t rows, size_t cols,
                            int granularity, int bits, int mode, int8_t *q_dev, double *scales_dev,
                            double *zero_points_dev);
+/* quantize_tensor for a tensor of any float storage type (quantize.rs:194-205 widens every dtype with
+ * to_f64_vec): w_dtype = SHREWQ_F32, SHREWQ_BF16, SHREWQ_F16 or SHREWQ_F64, any bits / mode.  All
+ * arithmetic in f64 as in the reference.  Experimental like the other modes (f32 INT8 symmetric input
+ * should use shrewq_quantize_f32, the tuned path).  shrewq_dequantize_ex likewise narrows to any of the
+ * four types when given SHREWQ_F16 / SHREWQ_F64 (dequantize_tensor, quantize.rs:210-225). */
+SHREWQ_API int shrewq_quantize_any(shrewq_ctx *ctx, const void *w_dev, int w_dtype, size_t rows, size_t cols,
+                        int granularity, int bits, int mode, int8_t *q_dev, double *scales_dev,
+                        double *zero_points_dev);
 SHREWQ_API int shrewq_dequantize_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
                          const double *zero_points_dev, size_t rows, size_t cols, int granularity,
                          int out_dtype, void *out_dev);

@@ -13,7 +13,7 @@ OK = 0
 ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_TIMEOUT, ERR_ALLOC = -1, -2, -3, -4, -5, -6
 PER_TENSOR, PER_CHANNEL = 0, 1
 SYMMETRIC, ASYMMETRIC = 0, 1
-F32, BF16 = 0, 1
+F32, BF16, F16, F64 = 0, 1, 2, 3
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
 
 # SHREWQ_LIB points at another build of the same library (e.g. the tracing build)
@@ -35,6 +35,7 @@ SIGNATURES = {
     "shrewq_absmax_f32": (_ci, [_vp, _vp, _sz, _vp]),
     "shrewq_quantize_f32_given_amax": (_ci, [_vp, _vp, _sz, _vp, _vp, _vp]),
     "shrewq_quantize_f32_ex": (_ci, [_vp, _vp, _sz, _sz, _ci, _ci, _ci, _vp, _vp, _vp]),
+    "shrewq_quantize_any": (_ci, [_vp, _vp, _ci, _sz, _sz, _ci, _ci, _ci, _vp, _vp, _vp]),
     "shrewq_dequantize_ex": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _ci, _vp]),
     "shrewq_linear_create": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _pp]),
     "shrewq_linear_create_ex": (_ci, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _ci, _pp]),

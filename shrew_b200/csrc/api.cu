@@ -292,16 +292,43 @@ int shrewq_quantize_f32_ex(shrewq_ctx *ctx, const float *w_dev, size_t rows, siz
     return launch_quantize_ex(ctx, w_dev, rows, cols, granularity, bits, mode, q_dev, scales_dev, zero_points_dev);
 }
 
+int shrewq_quantize_any(shrewq_ctx *ctx, const void *w_dev, int w_dtype, size_t rows, size_t cols, int granularity, int bits,
+                        int mode, int8_t *q_dev, double *scales_dev, double *zero_points_dev) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "quantize_any: ctx is NULL");
+    int rc = check_gran(ctx, granularity, "quantize_any");
+    if (rc != SHREWQ_OK) return rc;
+    if (w_dtype != SHREWQ_F32 && w_dtype != SHREWQ_BF16 && w_dtype != SHREWQ_F16 && w_dtype != SHREWQ_F64)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_any: w_dtype must be SHREWQ_F32, _BF16, _F16 or _F64");
+    if ((bits != 8 && bits != 4) || (mode != SHREWQ_SYMMETRIC && mode != SHREWQ_ASYMMETRIC))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_any: bits must be 8 or 4, mode SHREWQ_SYMMETRIC or SHREWQ_ASYMMETRIC");
+    if (!experimental_modes())
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
+                       "quantize_any: the any-dtype kernels are built but have not run on a GPU yet (SHREWQ_EXPERIMENTAL_MODES=1 "
+                       "enables them; f32 INT8 symmetric has shrewq_quantize_f32)");
+    const size_t n = rows * cols;
+    if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_any: rows*cols overflows");
+    const size_t ns = granularity == SHREWQ_PER_CHANNEL ? rows : 1;
+    if ((ns > 0 && (!scales_dev || !zero_points_dev)) || (n > 0 && (!w_dev || !q_dev)))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_any: NULL buffer");
+    const size_t wal = w_dtype == SHREWQ_F64 ? 8 : (w_dtype == SHREWQ_F32 ? 4 : 2);
+    if ((reinterpret_cast<uintptr_t>(w_dev) % wal) || (reinterpret_cast<uintptr_t>(scales_dev) & 7) ||
+        (reinterpret_cast<uintptr_t>(zero_points_dev) & 7))
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_any: buffers not aligned to their element size");
+    if ((rc = bind(ctx)) != SHREWQ_OK) return rc;
+    return launch_quantize_any(ctx, w_dev, w_dtype, rows, cols, granularity, bits, mode, q_dev, scales_dev, zero_points_dev);
+}
+
 int shrewq_dequantize_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev, const double *zero_points_dev,
                          size_t rows, size_t cols, int granularity, int out_dtype, void *out_dev) {
-    if (!zero_points_dev) return shrewq_dequantize(ctx, q_dev, scales_dev, rows, cols, granularity, out_dtype, out_dev);
+    if (!zero_points_dev && (out_dtype == SHREWQ_F32 || out_dtype == SHREWQ_BF16))
+        return shrewq_dequantize(ctx, q_dev, scales_dev, rows, cols, granularity, out_dtype, out_dev);
     if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: ctx is NULL");
     int rc = check_gran(ctx, granularity, "dequantize_ex");
     if (rc != SHREWQ_OK) return rc;
     if (!experimental_modes())
-        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "dequantize_ex: zero points need SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
-    if (out_dtype != SHREWQ_F32 && out_dtype != SHREWQ_BF16)
-        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: out_dtype must be SHREWQ_F32 or SHREWQ_BF16");
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "dequantize_ex: zero points and f16 / f64 outputs need SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
+    if (out_dtype != SHREWQ_F32 && out_dtype != SHREWQ_BF16 && out_dtype != SHREWQ_F16 && out_dtype != SHREWQ_F64)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: out_dtype must be SHREWQ_F32, _BF16, _F16 or _F64");
     const size_t n = rows * cols;
     if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: rows*cols overflows");
     if (n > 0 && (!q_dev || !scales_dev || !out_dev)) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: NULL buffer");

@@ -87,6 +87,8 @@ int launch_split_f32(shrewq_ctx *ctx, const float *x, size_t n, void *hi_bf16, v
 int ensure_xsplit(shrewq_ctx *ctx, size_t bytes);
 int launch_quantize_ex(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, int granularity, int bits, int mode,
                        int8_t *q, double *scales, double *zps);
+int launch_quantize_any(shrewq_ctx *ctx, const void *w, int w_dtype, size_t rows, size_t cols, int granularity, int bits,
+                        int mode, int8_t *q, double *scales, double *zps);
 int launch_dequantize_ex(shrewq_ctx *ctx, const int8_t *q, const double *scales, const double *zps, size_t rows,
                          size_t cols, int granularity, int out_dtype, void *out);
 int launch_scale_zp_to_f32(shrewq_ctx *ctx, const double *scales, const double *zps, int granularity, size_t n, float *out);

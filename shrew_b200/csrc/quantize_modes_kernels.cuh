@@ -26,6 +26,7 @@
 #include "../../include/shrewq.h"
 #ifndef SHREWQ_CPU_EMU
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #endif
@@ -50,8 +51,15 @@ __device__ __forceinline__ double round_half_away(double t) {
     return copysign(r, t);                          // round(-0.3) is -0.0, as f64::round
 }
 
-// compute_scale_zp for a group of n elements whose extrema are lo / hi / amax
-__device__ __forceinline__ GroupParams make_group(float lo, float hi, float amax, size_t n, int bits, int mode) {
+// Tensor element -> f64, exactly (Tensor::to_f64_vec, quantize.rs:198): f32, f64, bf16 or f16 storage.
+__device__ __forceinline__ double widen(float v) { return (double)v; }
+__device__ __forceinline__ double widen(double v) { return v; }
+__device__ __forceinline__ double widen(__nv_bfloat16 v) { return (double)__bfloat162float(v); }
+__device__ __forceinline__ double widen(__half v) { return (double)__half2float(v); }
+
+// compute_scale_zp for a group of n elements whose extrema are lo / hi / amax (f64: exact for every
+// storage type)
+__device__ __forceinline__ GroupParams make_group(double lo, double hi, double amax, size_t n, int bits, int mode) {
     GroupParams p;
     p.qmin = qmin_of(bits, mode);
     p.qmax = qmax_of(bits);
@@ -59,39 +67,37 @@ __device__ __forceinline__ GroupParams make_group(float lo, float hi, float amax
         p.scale = 1.0;
         p.zp = 0.0;
     } else if (mode != SHREWQ_ASYMMETRIC) {
-        const double a = (double)amax;
-        p.scale = a < 1e-30 ? 1.0 : a / p.qmax;
+        p.scale = amax < 1e-30 ? 1.0 : amax / p.qmax;
         p.zp = 0.0;
     } else {
-        const double mn = (double)lo, mx = (double)hi;
-        const double range = mx - mn;
+        const double range = hi - lo;
         p.scale = range < 1e-30 ? 1.0 : range / (p.qmax - p.qmin);
-        p.zp = round_half_away(p.qmin - mn / p.scale);
+        p.zp = round_half_away(p.qmin - lo / p.scale);
     }
     p.inv = fabs(p.scale) < 1e-30 ? 0.0 : 1.0 / p.scale;
     return p;
 }
 
-__device__ __forceinline__ int quant_ex(float v, const GroupParams &p) {
-    const double t = round_half_away(__dadd_rn(__dmul_rn((double)v, p.inv), p.zp));
+__device__ __forceinline__ int quant_ex(double v, const GroupParams &p) {
+    const double t = round_half_away(__dadd_rn(__dmul_rn(v, p.inv), p.zp));
     if (t != t) return 0;  // NaN as i8 == 0
     return (int)fmin(fmax(t, p.qmin), p.qmax);
 }
 
-__device__ __forceinline__ float warp_min(float v) {
+__device__ __forceinline__ double warp_min(double v) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    for (int o = 16; o > 0; o >>= 1) v = fmin(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
     return v;
 }
-__device__ __forceinline__ float warp_max(float v) {
+__device__ __forceinline__ double warp_max(double v) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    for (int o = 16; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
     return v;
 }
 
 // Block-wide extrema of (lo, hi, amax); every thread of the 256-thread CTA gets the result.
-__device__ __forceinline__ void block_extrema(float &lo, float &hi, float &amax) {
-    __shared__ float s_lo[8], s_hi[8], s_am[8];
+__device__ __forceinline__ void block_extrema(double &lo, double &hi, double &amax) {
+    __shared__ double s_lo[8], s_hi[8], s_am[8];
     lo = warp_min(lo);
     hi = warp_max(hi);
     amax = warp_max(amax);
@@ -107,24 +113,25 @@ __device__ __forceinline__ void block_extrema(float &lo, float &hi, float &amax)
     amax = s_am[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) {
-        lo = fminf(lo, s_lo[i]);      // fminf / fmaxf drop a NaN operand, as f64::min / f64::max do
-        hi = fmaxf(hi, s_hi[i]);
-        amax = fmaxf(amax, s_am[i]);
+        lo = fmin(lo, s_lo[i]);      // fmin / fmax drop a NaN operand, as f64::min / f64::max do
+        hi = fmax(hi, s_hi[i]);
+        amax = fmax(amax, s_am[i]);
     }
 }
 
 // ---- per-channel: one CTA per row, two passes ---------------------------------------------------
+template <typename T>
 __global__ void __launch_bounds__(256)
-quantize_rows_ex_kernel(const float *__restrict__ w, size_t rows, size_t cols, int bits, int mode,
+quantize_rows_ex_kernel(const T *__restrict__ w, size_t rows, size_t cols, int bits, int mode,
                         int8_t *__restrict__ q, double *__restrict__ scales, double *__restrict__ zps) {
     for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const float *src = w + row * cols;
-        float lo = INFINITY, hi = -INFINITY, amax = 0.0f;
+        const T *src = w + row * cols;
+        double lo = INFINITY, hi = -INFINITY, amax = 0.0;
         for (size_t c = threadIdx.x; c < cols; c += 256) {
-            const float v = src[c];
-            lo = fminf(lo, v);
-            hi = fmaxf(hi, v);
-            amax = fmaxf(amax, fabsf(v));
+            const double v = widen(src[c]);
+            lo = fmin(lo, v);
+            hi = fmax(hi, v);
+            amax = fmax(amax, fabs(v));
         }
         block_extrema(lo, hi, amax);
         const GroupParams p = make_group(lo, hi, amax, cols, bits, mode);  // every thread: same inputs, same result
@@ -133,65 +140,68 @@ quantize_rows_ex_kernel(const float *__restrict__ w, size_t rows, size_t cols, i
             zps[row] = p.zp;
         }
         int8_t *dst = q + row * cols;
-        for (size_t c = threadIdx.x; c < cols; c += 256) dst[c] = (int8_t)quant_ex(src[c], p);
+        for (size_t c = threadIdx.x; c < cols; c += 256) dst[c] = (int8_t)quant_ex(widen(src[c]), p);
     }
 }
 
 // ---- per-tensor ---------------------------------------------------------------------------------
-// Floats order like these integer keys (negative floats reversed below the positive ones), so
-// atomicMin / atomicMax on the keys are a float min / max.  NaN never reaches a key.
-__device__ __forceinline__ unsigned int key_of(float f) {
-    const unsigned int b = __float_as_uint(f);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+// Doubles order like these integer keys (negative values reversed below the positive ones), so
+// atomicMin / atomicMax on the keys are a min / max of the values.  NaN never reaches a key.
+__device__ __forceinline__ unsigned long long key_of(double f) {
+    const unsigned long long b = (unsigned long long)__double_as_longlong(f);
+    return (b >> 63) ? ~b : (b | 0x8000000000000000ull);
 }
-__device__ __forceinline__ float float_of(unsigned int k) {
-    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+__device__ __forceinline__ double double_of(unsigned long long k) {
+    return __longlong_as_double((long long)((k >> 63) ? (k & 0x7FFFFFFFFFFFFFFFull) : ~k));
 }
 
 struct TensorWords {
-    unsigned int lo_key, hi_key, amax_bits, pad;
+    unsigned long long lo_key, hi_key, amax_key;
     GroupParams p;
 };
 
 __global__ void init_words_kernel(TensorWords *t) {
     t->lo_key = key_of(INFINITY);
     t->hi_key = key_of(-INFINITY);
-    t->amax_bits = 0u;
+    t->amax_key = key_of(0.0);
 }
 
+template <typename T>
 __global__ void __launch_bounds__(256)
-extrema_flat_kernel(const float *__restrict__ w, size_t n, TensorWords *t) {
-    float lo = INFINITY, hi = -INFINITY, amax = 0.0f;
+extrema_flat_kernel(const T *__restrict__ w, size_t n, TensorWords *t) {
+    double lo = INFINITY, hi = -INFINITY, amax = 0.0;
     const size_t stride = (size_t)gridDim.x * 256;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
-        const float v = w[i];
-        lo = fminf(lo, v);
-        hi = fmaxf(hi, v);
-        amax = fmaxf(amax, fabsf(v));
+        const double v = widen(w[i]);
+        lo = fmin(lo, v);
+        hi = fmax(hi, v);
+        amax = fmax(amax, fabs(v));
     }
     block_extrema(lo, hi, amax);
     if (threadIdx.x == 0) {
         atomicMin(&t->lo_key, key_of(lo));
         atomicMax(&t->hi_key, key_of(hi));
-        atomicMax(&t->amax_bits, __float_as_uint(amax));  // non-negative floats order like their bits
+        atomicMax(&t->amax_key, key_of(amax));
     }
 }
 
 __global__ void finalize_ex_kernel(TensorWords *t, size_t n, int bits, int mode, double *scales, double *zps) {
-    const GroupParams p = make_group(float_of(t->lo_key), float_of(t->hi_key), __uint_as_float(t->amax_bits), n, bits, mode);
+    const GroupParams p = make_group(double_of(t->lo_key), double_of(t->hi_key), double_of(t->amax_key), n, bits, mode);
     t->p = p;
     scales[0] = p.scale;
     zps[0] = p.zp;
 }
 
+template <typename T>
 __global__ void __launch_bounds__(256)
-quantize_flat_ex_kernel(const float *__restrict__ w, size_t n, const TensorWords *__restrict__ t, int8_t *__restrict__ q) {
+quantize_flat_ex_kernel(const T *__restrict__ w, size_t n, const TensorWords *__restrict__ t, int8_t *__restrict__ q) {
     const GroupParams p = t->p;
     const size_t stride = (size_t)gridDim.x * 256;
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) q[i] = (int8_t)quant_ex(w[i], p);
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) q[i] = (int8_t)quant_ex(widen(w[i]), p);
 }
 
 // ---- dequantize with zero points ------------------------------------------------------------------
+// f64 -> the tensor's storage type with one rounding (Tensor::from_f64_slice, quantize.rs:219-224)
 __device__ __forceinline__ uint16_t f64_to_bf16_rne(double v) {
     if (v != v) return 0x7FC0;
     float f = __double2float_rz(v);
@@ -200,7 +210,12 @@ __device__ __forceinline__ uint16_t f64_to_bf16_rne(double v) {
     if (isinf(v)) return (uint16_t)(b >> 16);
     return (uint16_t)((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
 }
+__device__ __forceinline__ void narrow(double v, float *o) { *o = (float)v; }
+__device__ __forceinline__ void narrow(double v, double *o) { *o = v; }
+__device__ __forceinline__ void narrow(double v, uint16_t *o) { *o = f64_to_bf16_rne(v); }
+__device__ __forceinline__ void narrow(double v, __half *o) { *o = __double2half(v); }
 
+// OutT: float, double, uint16_t (bf16 bits) or __half; zps == nullptr means zero points of 0.0
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 dequantize_ex_kernel(const int8_t *__restrict__ q, const double *__restrict__ scales, const double *__restrict__ zps,
@@ -209,9 +224,8 @@ dequantize_ex_kernel(const int8_t *__restrict__ q, const double *__restrict__ sc
     const size_t stride = (size_t)gridDim.x * 256;
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) {
         const size_t g = per_channel ? i / cols : 0;
-        const double v = __dmul_rn(__dsub_rn((double)q[i], zps[g]), scales[g]);
-        if constexpr (sizeof(OutT) == 4) out[i] = (float)v;
-        else out[i] = f64_to_bf16_rne(v);
+        const double v = __dmul_rn(__dsub_rn((double)q[i], zps ? zps[g] : 0.0), scales[g]);
+        narrow(v, out + i);
     }
 }
 

@@ -141,6 +141,8 @@ def _rows_cols(shape: Sequence[int]) -> Tuple[int, int]:
 
 
 _DTYPE_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+# storage types of quantize_tensor / dequantize_tensor (the forward takes f32 and bf16 only)
+_STORAGE_CODE = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float64: _lib.F64}
 
 
 # ---- QuantizedTensor (quantize.rs:150-185) -----------------------------------------------------
@@ -178,8 +180,8 @@ def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTenso
     validated kernels; the other modes go through shrewq_quantize_f32_ex, which refuses them
     unless SHREWQ_EXPERIMENTAL_MODES=1 is set."""
     dev = Device.get(tensor.device)
-    if tensor.dtype != torch.float32:
-        raise ShrewError(_lib.ERR_UNSUPPORTED, f"quantize_tensor: dtype {tensor.dtype} not supported (f32 only)")
+    if tensor.dtype not in _STORAGE_CODE:
+        raise ShrewError(_lib.ERR_UNSUPPORTED, f"quantize_tensor: dtype {tensor.dtype} is not a float storage type")
     w = tensor.contiguous()
     shape = list(w.shape)
     rows, cols = _rows_cols(shape)
@@ -190,16 +192,20 @@ def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTenso
     q = torch.empty(w.numel(), dtype=torch.int8, device=w.device)
     scales = torch.empty(n_scales, dtype=torch.float64, device=w.device)
     dev.bind_stream()
-    if config._is_int8_symmetric():
+    if config._is_int8_symmetric() and w.dtype is torch.float32:
         rc = _lib.lib().shrewq_quantize_f32(dev.handle, _ptr(w), rows, cols, gran.value, _ptr(q), _ptr(scales))
         _lib.check(rc, dev.handle)
         return QuantizedTensor(q, scales, shape, tensor.dtype, config)
     bits, mode = config._abi_mode()
     zps = torch.empty(n_scales, dtype=torch.float64, device=w.device)
-    rc = _lib.lib().shrewq_quantize_f32_ex(dev.handle, _ptr(w), rows, cols, gran.value, bits, mode, _ptr(q), _ptr(scales),
-                                           _ptr(zps))
+    if w.dtype is torch.float32:
+        rc = _lib.lib().shrewq_quantize_f32_ex(dev.handle, _ptr(w), rows, cols, gran.value, bits, mode, _ptr(q), _ptr(scales),
+                                               _ptr(zps))
+    else:  # bf16 / f16 / f64 storage: every element is widened to f64 like the reference's to_f64_vec
+        rc = _lib.lib().shrewq_quantize_any(dev.handle, _ptr(w), _STORAGE_CODE[w.dtype], rows, cols, gran.value, bits, mode,
+                                            _ptr(q), _ptr(scales), _ptr(zps))
     _lib.check(rc, dev.handle)
-    return QuantizedTensor(q, scales, shape, tensor.dtype, config, zps)
+    return QuantizedTensor(q, scales, shape, tensor.dtype, config, zps if config.mode is QuantMode.Asymmetric else None)
 
 
 def absmax(tensor: torch.Tensor) -> torch.Tensor:
@@ -236,15 +242,15 @@ def dequantize_tensor(qtensor: QuantizedTensor, device=None) -> torch.Tensor:
     dev_t = qtensor.data.device if device is None else torch.device(device)
     dev = Device.get(dev_t)
     out_dtype = qtensor.original_dtype
-    if out_dtype not in _DTYPE_CODE:
+    if out_dtype not in _STORAGE_CODE:
         raise ShrewError(_lib.ERR_UNSUPPORTED, f"dequantize_tensor: target dtype {out_dtype} not supported")
     rows, cols = _rows_cols(qtensor.shape)
     gran = qtensor.config.granularity if len(qtensor.shape) else QuantGranularity.PerTensor
     out = torch.empty(qtensor.shape, dtype=out_dtype, device=qtensor.data.device)
     dev.bind_stream()
-    if qtensor.zero_points_t is not None:
+    if qtensor.zero_points_t is not None or out_dtype not in _DTYPE_CODE:
         rc = _lib.lib().shrewq_dequantize_ex(dev.handle, _ptr(qtensor.data), _ptr(qtensor.scales), _ptr(qtensor.zero_points_t),
-                                             rows, cols, gran.value, _DTYPE_CODE[out_dtype], _ptr(out))
+                                             rows, cols, gran.value, _STORAGE_CODE[out_dtype], _ptr(out))
     else:
         rc = _lib.lib().shrewq_dequantize(dev.handle, _ptr(qtensor.data), _ptr(qtensor.scales), rows, cols, gran.value,
                                           _DTYPE_CODE[out_dtype], _ptr(out))

@@ -250,6 +250,20 @@ static inline __nv_bfloat16 __float2bfloat16_rn(float f) {
 struct __half { _Float16 v; };
 static inline __half __float2half_rn(float f) { return __half{(_Float16)f}; }
 static inline unsigned short __half_as_ushort(__half h) { unsigned short u; memcpy(&u, &h.v, 2); return u; }
+static inline float __half2float(__half h) { return (float)h.v; }
+static inline __half __double2half(double v) { return __half{(_Float16)v}; }  // one rounding, to nearest even
+static inline long long __double_as_longlong(double v) { long long b; memcpy(&b, &v, 8); return b; }
+static inline double __longlong_as_double(long long b) { double v; memcpy(&v, &b, 8); return v; }
+static inline unsigned long long atomicMax(unsigned long long *p, unsigned long long v) {
+    unsigned long long old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
+    while (old < v && !__atomic_compare_exchange_n(p, &old, v, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST)) {}
+    return old;
+}
+static inline unsigned long long atomicMin(unsigned long long *p, unsigned long long v) {
+    unsigned long long old = __atomic_load_n(p, __ATOMIC_SEQ_CST);
+    while (old > v && !__atomic_compare_exchange_n(p, &old, v, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST)) {}
+    return old;
+}
 
 using std::max;
 using std::min;

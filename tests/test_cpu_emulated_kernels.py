@@ -823,3 +823,70 @@ def test_cta_pair_split_k(oracle, emu_pair, M, N, K, splits, gated):
     assert rc == 0
     assert oracle.rel_err(y, ref) < tol
 
+
+
+# ---- any float storage type (quantize_tensor widens every dtype with to_f64_vec, quantize.rs:198) ------
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16", "f64"])
+@pytest.mark.parametrize("bits,mode", [(8, 0), (8, 1), (4, 0)])
+@pytest.mark.parametrize("gran", [0, 1])
+def test_quantize_any_storage_type(oracle, emu_modes, dtype, bits, mode, gran):
+    emu_modes.emu_quantize_any.argtypes = [_vp, _ci, _sz, _sz, _ci, _ci, _ci, _cu, _vp, _vp, _vp]
+    emu_modes.emu_dequantize_any.argtypes = [_vp, _vp, _vp, _sz, _sz, _ci, _ci, _cu, _vp]
+    rng = np.random.default_rng(bits + mode + gran)
+    rows, cols = 5, 333
+    w64 = rng.standard_normal((rows, cols)) * 0.3 + (0.1 if mode else 0.0)
+    w64[0, 0], w64[1, 1], w64[2, 2] = np.nan, -0.0, 0.0
+    if dtype == "f32":
+        stored, code = w64.astype(np.float32), 0
+        exact = stored.astype(np.float64)
+    elif dtype == "bf16":
+        bits16, f = _bf16_bits(w64.astype(np.float32))
+        stored, code, exact = bits16, 1, f.astype(np.float64)
+    elif dtype == "f16":
+        h = w64.astype(np.float16)
+        stored, code, exact = h.view(np.uint16).copy(), 2, h.astype(np.float64)
+    else:
+        w64[3, 3] = 0.1 + 2.0 ** -40          # not representable in f32: the f64 path must not narrow
+        stored, code, exact = w64.copy(), 3, w64
+    # the oracle restates the arithmetic on f64 data; feed it the exactly widened values (f32 inputs of the
+    # oracle are widened the same way, so for the narrower types go through its f64 twin directly)
+    n = rows if gran else 1
+    q = _aligned((rows, cols), np.int8)
+    s, z = np.zeros(n), np.zeros(n)
+    sa = _aligned(stored.shape, stored.dtype)
+    sa[...] = stored
+    assert emu_modes.emu_quantize_any(_p(sa), code, rows, cols, gran, bits, mode, 3, _p(q), _p(s), _p(z)) == 0
+    q_ref, s_ref, z_ref = _np_quantize_f64(oracle, exact, gran, bits, mode)
+    np.testing.assert_array_equal(q, q_ref)
+    assert s.tobytes() == s_ref.tobytes() and z.tobytes() == z_ref.tobytes()
+    # dequantize_tensor narrows to the original dtype with one rounding
+    back64 = (q_ref.astype(np.float64) - (z_ref.reshape(-1, 1) if gran else z_ref[0])) * (s_ref.reshape(-1, 1) if gran else s_ref[0])
+    for out_code, np_dt in ((2, np.float16), (3, np.float64), (0, np.float32)):
+        out = _aligned((rows, cols), np_dt)
+        zp_arg = _p(z) if mode else None       # symmetric: no zero-point array
+        assert emu_modes.emu_dequantize_any(_p(q), _p(s), zp_arg, rows, cols, gran, out_code, 2, _p(out)) == 0
+        with np.errstate(over="ignore"):
+            np.testing.assert_array_equal(out, back64.astype(np_dt))
+
+
+def _np_quantize_f64(oracle, data64, gran, bits, mode):
+    """the oracle's numpy twin on f64 data (it widens f32 itself; here the data are already f64)"""
+    rows, cols = data64.shape
+    data = data64 if gran else data64.reshape(1, -1)
+    qmax = 7.0 if bits == 4 else 127.0
+    qmin = (-8.0 if mode else -7.0) if bits == 4 else (-128.0 if mode else -127.0)
+    with np.errstate(all="ignore"):
+        if mode:
+            lo = np.fmin.reduce(data, axis=1, initial=np.inf)
+            hi = np.fmax.reduce(data, axis=1, initial=-np.inf)
+            rng_ = hi - lo
+            scale = np.where(rng_ < 1e-30, 1.0, rng_ / (qmax - qmin))
+            zp = oracle.np_round_half_away(qmin - lo / scale)
+        else:
+            amax = np.fmax.reduce(np.abs(data), axis=1, initial=0.0)
+            scale = np.where(amax < 1e-30, 1.0, amax / qmax)
+            zp = np.zeros(data.shape[0])
+        inv = np.where(np.abs(scale) < 1e-30, 0.0, 1.0 / scale)
+        t = oracle.np_round_half_away(data * inv[:, None] + zp[:, None])
+        t = np.where(np.isnan(t), 0.0, np.clip(t, qmin, qmax))
+    return t.astype(np.int8).reshape(rows, cols), scale.astype(np.float64), zp.astype(np.float64)

@@ -63,7 +63,8 @@ def test_quantize_dequantize_modes_match_oracle(oracle, monkeypatch, bits, mode,
     q_ref, s_ref, z_ref = oracle.np_quantize_f32_ex(w, gran, bits, mode)
     np.testing.assert_array_equal(qt.data.cpu().numpy().reshape(shape), q_ref)
     assert qt.scales.cpu().numpy().tobytes() == s_ref.tobytes()
-    assert qt.zero_points_t.cpu().numpy().tobytes() == z_ref.tobytes()
+    zps = np.zeros_like(s_ref) if qt.zero_points_t is None else qt.zero_points_t.cpu().numpy()
+    assert zps.tobytes() == z_ref.tobytes()
     back = dequantize_tensor(qt).cpu().numpy()
     g = gran if len(shape) > 1 else 0
     ref = oracle.dequantize_f64_ex(q_ref, s_ref, z_ref, g).astype(np.float32)
@@ -94,3 +95,31 @@ def test_forward_with_zero_points(oracle, monkeypatch, M, dtype):
     ref = (x.astype(np.float64) @ wd.astype(np.float32).astype(np.float64).T).astype(np.float32) + b.reshape(1, -1)
     ref = np.maximum(ref, 0.0)
     assert oracle.rel_err(y.float().cpu().numpy(), ref) < (1e-2 if dtype == "bf16" else 1e-4)
+
+
+@_UNVALIDATED
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float64])
+@pytest.mark.parametrize("gran", [0, 1])
+def test_quantize_any_storage_type(oracle, monkeypatch, dtype, gran):
+    # quantize_tensor widens every storage type to f64 (quantize.rs:198); dequantize_tensor narrows back
+    from shrew_b200 import dequantize_tensor, quantize_tensor
+    monkeypatch.setenv("SHREWQ_EXPERIMENTAL_MODES", "1")
+    rng = np.random.default_rng(gran)
+    w64 = rng.standard_normal((40, 700)) * 0.2
+    t = torch.from_numpy(w64).to(dtype).cuda()
+    exact = t.double().cpu().numpy()
+    qt = quantize_tensor(t, _cfg(8, 0, gran))
+    torch.cuda.synchronize()
+    # reference arithmetic on the exactly widened values
+    data = exact if gran else exact.reshape(1, -1)
+    amax = np.abs(data).max(axis=1)
+    scale = np.where(amax < 1e-30, 1.0, amax / 127.0)
+    tq = oracle.np_round_half_away(data * (1.0 / scale)[:, None])
+    q_ref = np.clip(tq, -127, 127).astype(np.int8).reshape(40, 700)
+    np.testing.assert_array_equal(qt.data.cpu().numpy().reshape(40, 700), q_ref)
+    assert qt.scales.cpu().numpy().tobytes() == scale.tobytes()
+    back = dequantize_tensor(qt)
+    assert back.dtype == dtype
+    ref = torch.from_numpy(q_ref.astype(np.float64) * (scale[:, None] if gran else scale[0])).to(dtype)
+    assert torch.equal(back.cpu(), ref)
+
