@@ -61,6 +61,17 @@ def test_null_handles_are_rejected_not_crashed(shrewq):
     assert L.shrewq_linear_in_features(None) == 0
     L.shrewq_linear_destroy(None)
     L.shrewq_ctx_destroy(None)
+    # the later entry points too
+    out = ctypes.c_void_p()
+    assert L.shrewq_quantize_f32_ex(None, None, 1, 1, 0, 8, 0, None, None, None) == shrewq.ERR_INVALID_ARG
+    assert L.shrewq_quantize_any(None, None, 0, 1, 1, 0, 8, 0, None, None, None) == shrewq.ERR_INVALID_ARG
+    assert L.shrewq_dequantize_ex(None, None, None, None, 1, 1, 0, 0, None) == shrewq.ERR_INVALID_ARG
+    assert L.shrewq_absmax_f32(None, None, 1, None) == shrewq.ERR_INVALID_ARG
+    assert L.shrewq_quantize_f32_given_amax(None, None, 1, None, None, None) == shrewq.ERR_INVALID_ARG
+    assert L.shrewq_linear_create_ex(None, None, None, None, None, 1, 1, 0, ctypes.byref(out)) == shrewq.ERR_INVALID_ARG
+    assert L.shrewq_linear_forward_noalloc(None, None, 1, None, 0, 1, 0) == shrewq.ERR_INVALID_ARG
+    for kind in (b"gemv", b"tcgen05", b"simt", b"mma", b"mma-f16", b"tcgen05-f32", b"tcgen05-2cta", b"auto"):
+        assert L.shrewq_force_kernel(kind) == shrewq.OK
 
 
 def test_quant_config_mirror():
