@@ -167,6 +167,19 @@ SHREWQ_API int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const 
 SHREWQ_API int shrewq_linear_create_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
                             const double *zero_points_dev, const float *bias_dev, size_t out_features,
                             size_t in_features, int granularity, shrewq_linear **out);
+/*
+ * INT4 codes two per byte, beyond the reference (whose INT4 tensors keep one code per i8 and only
+ * report the packed size, quantize.rs:176): shrewq_pack_int4 turns rows*cols INT4 codes (from
+ * shrewq_quantize_f32_ex with bits = 4, values in [-8, 7]) into rows*cols/2 bytes, byte j of a row =
+ * code 2j + 8 in the low and code 2j+1 + 8 in the high nibble; shrewq_linear_create_int4 builds a
+ * QuantizedLinear over such rows (symmetric scales).  Its forward streams half the bytes of INT8; it
+ * is served by the warp-MMA kernel only: bf16 activations, M <= 32, in_features a multiple of 128.
+ * Experimental (SHREWQ_EXPERIMENTAL_MODES=1), not yet run on a GPU.
+ */
+SHREWQ_API int shrewq_pack_int4(shrewq_ctx *ctx, const int8_t *q_dev, size_t rows, size_t cols, uint8_t *packed_dev);
+SHREWQ_API int shrewq_linear_create_int4(shrewq_ctx *ctx, const uint8_t *packed_dev, const double *scales_dev,
+                              const float *bias_dev, size_t out_features, size_t in_features,
+                              int granularity, shrewq_linear **out);
 SHREWQ_API void shrewq_linear_destroy(shrewq_linear *lin);
 
 /*

@@ -38,6 +38,8 @@ SIGNATURES = {
     "shrewq_quantize_any": (_ci, [_vp, _vp, _ci, _sz, _sz, _ci, _ci, _ci, _vp, _vp, _vp]),
     "shrewq_dequantize_ex": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _ci, _vp]),
     "shrewq_linear_create": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _pp]),
+    "shrewq_pack_int4": (_ci, [_vp, _vp, _sz, _sz, _vp]),
+    "shrewq_linear_create_int4": (_ci, [_vp, _vp, _vp, _vp, _sz, _sz, _ci, _pp]),
     "shrewq_linear_create_ex": (_ci, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _ci, _pp]),
     "shrewq_linear_destroy": (None, [_vp]),
     "shrewq_linear_forward": (_ci, [_vp, _vp, _ci, _sz, _vp, _ci, _sz, _ci]),

@@ -25,7 +25,8 @@ __device__ __forceinline__ int shift_of_amax(float a) {
 // the row)) (0 for an all-zero row; a row holding Inf uses the largest finite exponent; NaN
 // elements stay NaN and do not take part in amax).  One CTA per token row.
 __global__ void __launch_bounds__(256)
-x_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ x16, int *__restrict__ shift, int K) {
+x_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ x16, int *__restrict__ shift, int K,
+                int perm = 0) {
     const __nv_bfloat16 *row = x + (size_t)blockIdx.x * K;
     __half *out = x16 + (size_t)blockIdx.x * K;
     float amax = 0.0f;
@@ -45,7 +46,12 @@ x_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ x16, i
     }
     __syncthreads();
     const int sh = s_shift;
-    for (int k = threadIdx.x; k < K; k += 256) out[k] = __float2half_rn(ldexpf(__bfloat162float(row[k]), sh));
+    // perm: within every group of 8 the values are stored in the order 0 4 1 5 2 6 3 7 (what the
+    // packed-INT4 forward pairs its codes with)
+    for (int k = threadIdx.x; k < K; k += 256) {
+        const int pos = perm ? ((k & ~7) | (((k & 3) << 1) | ((k >> 2) & 1))) : k;
+        out[pos] = __float2half_rn(ldexpf(__bfloat162float(row[k]), sh));
+    }
 }
 
 }  // namespace

@@ -336,6 +336,19 @@ int shrewq_dequantize_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *sca
     return launch_dequantize_ex(ctx, q_dev, scales_dev, zero_points_dev, rows, cols, granularity, out_dtype, out_dev);
 }
 
+int shrewq_pack_int4(shrewq_ctx *ctx, const int8_t *q_dev, size_t rows, size_t cols, uint8_t *packed_dev) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "pack_int4: ctx is NULL");
+    if (!experimental_modes())
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "pack_int4: needs SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
+    if (cols % 2 != 0) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "pack_int4: cols must be even (two codes per byte)");
+    const size_t n = rows * cols;
+    if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "pack_int4: rows*cols overflows");
+    if (n > 0 && (!q_dev || !packed_dev)) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "pack_int4: NULL buffer");
+    int rc = bind(ctx);
+    if (rc != SHREWQ_OK) return rc;
+    return launch_pack_int4(ctx, q_dev, n / 2, packed_dev);
+}
+
 // ---- quantized Linear ---------------------------------------------------------------------
 int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev, const float *bias_dev,
                          size_t out_features, size_t in_features, int granularity, shrewq_linear **out) {
@@ -407,6 +420,24 @@ int shrewq_linear_create_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *
     return rc;
 }
 
+int shrewq_linear_create_int4(shrewq_ctx *ctx, const uint8_t *packed_dev, const double *scales_dev, const float *bias_dev,
+                              size_t out_features, size_t in_features, int granularity, shrewq_linear **out) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "linear_create_int4: ctx is NULL");
+    if (!out) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_create_int4: out is NULL");
+    *out = nullptr;
+    if (!experimental_modes())
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "linear_create_int4: needs SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
+    if (in_features % 2 != 0) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_create_int4: in_features must be even");
+    // the plain constructor does everything but the TMA descriptors, which describe an INT8 [N,K] matrix
+    // and must not be used with packed rows: build the handle, then mark it
+    int rc = shrewq_linear_create(ctx, reinterpret_cast<const int8_t *>(packed_dev), scales_dev, bias_dev, out_features,
+                                  in_features, granularity, out);
+    if (rc != SHREWQ_OK) return rc;
+    (*out)->int4_packed = true;
+    (*out)->tmap_ok = false;
+    return SHREWQ_OK;
+}
+
 void shrewq_linear_destroy(shrewq_linear *lin) {
     if (!lin) return;
     cudaSetDevice(lin->ctx->device);
@@ -419,7 +450,10 @@ void shrewq_linear_destroy(shrewq_linear *lin) {
 size_t shrewq_linear_in_features(const shrewq_linear *lin) { return lin ? lin->k : 0; }
 size_t shrewq_linear_out_features(const shrewq_linear *lin) { return lin ? lin->n : 0; }
 /* fp32 size minus INT8 size — quantize.rs:455-459 */
-size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin) { return lin ? lin->n * lin->k * 4 - lin->n * lin->k : 0; }
+size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin) {
+    if (!lin) return 0;
+    return lin->n * lin->k * 4 - (lin->int4_packed ? lin->n * lin->k / 2 : lin->n * lin->k);
+}
 const char *shrewq_linear_last_kernel(const shrewq_linear *lin) { return lin ? lin->last_kernel : "none"; }
 
 // f32 activations on the tensor cores: x is split into bf16 hi + lo (exact to ~2^-17), the
@@ -486,6 +520,20 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
         a.extra.p[i] = peers[i];
     }
     a.extra.n = n_peers;
+
+    // Packed INT4 rows: only the warp-MMA forward reads them (batch <= 32 for now)
+    if (lin->int4_packed || (up && up->int4_packed)) {
+        if (up && !(lin->int4_packed && up->int4_packed))
+            return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: gate and up must both be packed INT4 or both INT8", who);
+        if (lin->czp || (up && up->czp))
+            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: packed INT4 with zero points is not built", who);
+        if (!gemv_mma_w4_supported(a))
+            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
+                           "%s: packed INT4 weights need bf16 activations, M <= 32, in_features a multiple of 128", who);
+        rc = launch_gemv_mma_w4(ctx, a);
+        lin->last_kernel = "mma-w4";
+        return rc;
+    }
 
     // Zero points: y = scale * (sum_k q x) + bias - (scale * zp) * sum_k x.  The kernels below
     // compute the first part into an f32 buffer; a last pass subtracts the second, applies the
@@ -577,7 +625,8 @@ int shrewq_linear_forward_noalloc(shrewq_linear *lin, const void *x_dev, size_t 
         return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: y_dtype must be SHREWQ_F32 or SHREWQ_BF16");
     if (epilogue != SHREWQ_EPILOGUE_NONE && epilogue != SHREWQ_EPILOGUE_RELU)
         return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: unknown epilogue %d", epilogue);
-    if (lin->czp) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "forward_noalloc: handles with zero points need shrewq_linear_forward");
+    if (lin->czp || lin->int4_packed)
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "forward_noalloc: handles with zero points or packed INT4 rows need shrewq_linear_forward");
     if (M == 0) return SHREWQ_OK;
     if (!x_dev || !y_dev) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: x / y is NULL");
     if (ldy < lin->n) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "forward_noalloc: ldy smaller than out_features");

@@ -51,6 +51,7 @@ struct shrewq_linear {
     const float *bias = nullptr;
     float *scales_f32 = nullptr;  // owned, out_features entries (per-tensor scale broadcast)
     float *czp = nullptr;         // owned, scale * zero_point per output channel; null = symmetric
+    bool int4_packed = false;     // q points at packed INT4 rows (in_features / 2 bytes each)
     size_t n = 0, k = 0;
     int granularity = 0;
     const char *last_kernel = "none";
@@ -118,6 +119,9 @@ int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a);
 int launch_gemm_simt(shrewq_ctx *ctx, const ForwardArgs &a);
 bool gemv_mma_supported(const ForwardArgs &a);
 int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a, bool f16);
+bool gemv_mma_w4_supported(const ForwardArgs &a);
+int launch_gemv_mma_w4(shrewq_ctx *ctx, const ForwardArgs &a);
+int launch_pack_int4(shrewq_ctx *ctx, const int8_t *q, size_t n_pairs, uint8_t *packed);
 bool tcgen05_supported(const ForwardArgs &a);
 int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);
 int launch_gemm_tcgen05_2cta(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);

@@ -73,6 +73,19 @@ __device__ __forceinline__ void cvt_i8x4_f16(uint32_t w, uint32_t &lo, uint32_t 
     hi = sub_f16x2(h23, 0x64806480u);
 }
 
+// 8 packed INT4 codes (one 32-bit word; nibble i = code i + 8) -> four f16x2 words, exactly:
+// (1024 + nibble) - 1032.  Word j of the result holds codes (j, j + 4): a mask and an OR place two
+// nibbles that sit 16 bits apart into the two halves at once.
+__device__ __forceinline__ void cvt_i4x8_f16(uint32_t w, uint32_t *p) {
+    p[0] = sub_f16x2((w & 0x000F000Fu) | 0x64006400u, 0x64086408u);
+    p[1] = sub_f16x2(((w >> 4) & 0x000F000Fu) | 0x64006400u, 0x64086408u);
+    p[2] = sub_f16x2(((w >> 8) & 0x000F000Fu) | 0x64006400u, 0x64086408u);
+    p[3] = sub_f16x2(((w >> 12) & 0x000F000Fu) | 0x64006400u, 0x64086408u);
+}
+
+// The unpacking above pairs codes (j, j + 4), so with packed INT4 weights the activations are stored in
+// the order 0 4 1 5 2 6 3 7 inside every group of 8 and a contiguous load yields the matching pairs.
+
 __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g)); }
 
 template <typename YT>
@@ -90,7 +103,10 @@ constexpr int kStageMaxBytes = 40 * 1024;     // ... when the f16 copy of x fits
 // XS (with F16, MT16 == 1, M <= 4): x is the caller's bf16 tensor and every CTA converts it into its
 // own shared memory first (x_to_f16_kernel's arithmetic), so that a batch-1..4 forward is one launch
 // with no kernel-to-kernel dependency; otherwise x / xshift come from x_to_f16_kernel.
-template <int MT16, typename YT, bool GATED, bool F16, bool XS>
+// W4 (with F16): q / q_up hold packed INT4 codes, K/2 bytes per row (byte j = codes 2j in the low and
+// 2j+1 in the high nibble, each stored as code + 8); a lane then reads 32 codes per 16-byte load, a
+// k-block is 128 wide, and x must be in that permuted order (x_to_f16_kernel with perm = 1, or staged here).
+template <int MT16, typename YT, bool GATED, bool F16, bool XS, bool W4 = false>
 __global__ void __launch_bounds__(kThreads)
 gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, const float *__restrict__ bias,
                 const int8_t *__restrict__ q_up, const float *__restrict__ scales_up,
@@ -99,8 +115,12 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
     constexpr int kChan = GATED ? 8 : 8 * NB;  // output channels per CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    static_assert(!W4 || F16, "packed INT4 weights go with f16 operands");
+    constexpr int kRun = W4 ? 32 : 16;        // codes (and activations) per lane per k-block
+    constexpr int kXWords = kRun / 2;         // 32-bit words of activations per lane, row and k-block
     const int n0 = blockIdx.x * kChan;
-    const int kblocks = K >> 6;
+    const int kblocks = K / (4 * kRun);
+    const size_t wrow_bytes = W4 ? (size_t)K / 2 : (size_t)K;
 
     // the row of codes this lane reads for each channel block
     const int8_t *wrow[NB];
@@ -108,7 +128,7 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
     for (int nb = 0; nb < NB; ++nb) {
         int n = n0 + (GATED ? 0 : nb * 8) + g;
         n = n < N ? n : N - 1;  // clamp: duplicates are computed and dropped
-        wrow[nb] = ((GATED && nb == 1) ? q_up : q) + (size_t)n * K + 16 * t;
+        wrow[nb] = ((GATED && nb == 1) ? q_up : q) + (size_t)n * wrow_bytes + 16 * t;
     }
     // the activation rows this lane reads for each token tile (null = padding row)
     const uint16_t *xlo[MT16], *xhi[MT16];
@@ -153,18 +173,26 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
                     const __half hi = __float2half_rn(ldexpf(__uint_as_float(w4[i] & 0xFFFF0000u), sh));
                     o4[i] = (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
                 }
+                if constexpr (W4) {  // the chunk is one group of 8: store it as 0 4 1 5 2 6 3 7
+                    const uint32_t e[8] = {o4[0] & 0xFFFF, o4[0] >> 16, o4[1] & 0xFFFF, o4[1] >> 16,
+                                           o4[2] & 0xFFFF, o4[2] >> 16, o4[3] & 0xFFFF, o4[3] >> 16};
+                    o4[0] = e[0] | (e[4] << 16);
+                    o4[1] = e[1] | (e[5] << 16);
+                    o4[2] = e[2] | (e[6] << 16);
+                    o4[3] = e[3] | (e[7] << 16);
+                }
                 reinterpret_cast<uint4 *>(xs + (size_t)m * K)[c] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
             }
         }
         __syncthreads();
-        xlo[0] = g < M ? xs + (size_t)g * K + 16 * t : nullptr;
+        xlo[0] = g < M ? xs + (size_t)g * K + kRun * t : nullptr;
         xhi[0] = nullptr;
     } else {
 #pragma unroll
         for (int mt = 0; mt < MT16; ++mt) {
             const int m = mt * 16 + g;
-            xlo[mt] = m < M ? x + (size_t)m * K + 16 * t : nullptr;
-            xhi[mt] = m + 8 < M ? x + (size_t)(m + 8) * K + 16 * t : nullptr;
+            xlo[mt] = m < M ? x + (size_t)m * K + kRun * t : nullptr;
+            xhi[mt] = m + 8 < M ? x + (size_t)(m + 8) * K + kRun * t : nullptr;
         }
     }
 
@@ -178,50 +206,53 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
 
 #pragma unroll 2
     for (int kb = warp; kb < kblocks; kb += kWarps) {
-        const size_t koff = (size_t)kb << 6;
+        const size_t koff = (size_t)kb * (4 * kRun);              // activations: elements
+        const size_t woff = W4 ? (size_t)kb << 6 : koff;            // codes: bytes (64 per k-block either way)
         uint4 wv[NB];
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) wv[nb] = ld_stream_16(wrow[nb] + koff);
-        // 16 activations = 8 bf16x2 words per row
-        uint32_t al[MT16][8], ah[MT16][8];
+        for (int nb = 0; nb < NB; ++nb) wv[nb] = ld_stream_16(wrow[nb] + woff);
+        // kRun activations = kXWords packed words per row
+        uint32_t al[MT16][kXWords], ah[MT16][kXWords];
 #pragma unroll
         for (int mt = 0; mt < MT16; ++mt) {
-            const uint4 z = make_uint4(0, 0, 0, 0);
-            uint4 l0 = z, l1 = z, h0 = z, h1 = z;
-            if constexpr (XS) {  // shared memory: plain loads (the read-only global path does not apply)
-                if (xlo[mt]) {
-                    l0 = *reinterpret_cast<const uint4 *>(xlo[mt] + koff);
-                    l1 = *(reinterpret_cast<const uint4 *>(xlo[mt] + koff) + 1);
+#pragma unroll
+            for (int v4 = 0; v4 < kXWords / 4; ++v4) {
+                const uint4 z = make_uint4(0, 0, 0, 0);
+                uint4 l = z, h = z;
+                if constexpr (XS) {  // shared memory: plain loads (the read-only global path does not apply)
+                    if (xlo[mt]) l = *(reinterpret_cast<const uint4 *>(xlo[mt] + koff) + v4);
+                } else {
+                    if (xlo[mt]) l = __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff) + v4);
+                    if (xhi[mt]) h = __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff) + v4);
                 }
-            } else {
-                if (xlo[mt]) {
-                    l0 = __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff));
-                    l1 = __ldg(reinterpret_cast<const uint4 *>(xlo[mt] + koff) + 1);
-                }
-                if (xhi[mt]) {
-                    h0 = __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff));
-                    h1 = __ldg(reinterpret_cast<const uint4 *>(xhi[mt] + koff) + 1);
-                }
+                al[mt][4 * v4 + 0] = l.x; al[mt][4 * v4 + 1] = l.y; al[mt][4 * v4 + 2] = l.z; al[mt][4 * v4 + 3] = l.w;
+                ah[mt][4 * v4 + 0] = h.x; ah[mt][4 * v4 + 1] = h.y; ah[mt][4 * v4 + 2] = h.z; ah[mt][4 * v4 + 3] = h.w;
             }
-            al[mt][0] = l0.x; al[mt][1] = l0.y; al[mt][2] = l0.z; al[mt][3] = l0.w;
-            al[mt][4] = l1.x; al[mt][5] = l1.y; al[mt][6] = l1.z; al[mt][7] = l1.w;
-            ah[mt][0] = h0.x; ah[mt][1] = h0.y; ah[mt][2] = h0.z; ah[mt][3] = h0.w;
-            ah[mt][4] = h1.x; ah[mt][5] = h1.y; ah[mt][6] = h1.z; ah[mt][7] = h1.w;
         }
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             const uint32_t w4[4] = {wv[nb].x, wv[nb].y, wv[nb].z, wv[nb].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                uint32_t b0, b1;  // codes 4j,4j+1 | 4j+2,4j+3 of this lane's run
-                if constexpr (F16) cvt_i8x4_f16(w4[j], b0, b1);
-                else cvt_i8x4_bf16(w4[j], b0, b1);
+                if constexpr (W4) {
+                    uint32_t p[4];  // codes (0,4) (1,5) (2,6) (3,7) of word j; activation words 4j..4j+3 pair the same k
+                    cvt_i4x8_f16(w4[j], p);
 #pragma unroll
-                for (int mt = 0; mt < MT16; ++mt) {
-                    if constexpr (F16)
-                        mma_f16_16816(acc[mt][nb], al[mt][2 * j], ah[mt][2 * j], al[mt][2 * j + 1], ah[mt][2 * j + 1], b0, b1);
-                    else
-                        mma_bf16_16816(acc[mt][nb], al[mt][2 * j], ah[mt][2 * j], al[mt][2 * j + 1], ah[mt][2 * j + 1], b0, b1);
+                    for (int mt = 0; mt < MT16; ++mt) {
+                        mma_f16_16816(acc[mt][nb], al[mt][4 * j], ah[mt][4 * j], al[mt][4 * j + 1], ah[mt][4 * j + 1], p[0], p[1]);
+                        mma_f16_16816(acc[mt][nb], al[mt][4 * j + 2], ah[mt][4 * j + 2], al[mt][4 * j + 3], ah[mt][4 * j + 3], p[2], p[3]);
+                    }
+                } else {
+                    uint32_t b0, b1;  // codes 4j,4j+1 | 4j+2,4j+3 of this lane's run
+                    if constexpr (F16) cvt_i8x4_f16(w4[j], b0, b1);
+                    else cvt_i8x4_bf16(w4[j], b0, b1);
+#pragma unroll
+                    for (int mt = 0; mt < MT16; ++mt) {
+                        if constexpr (F16)
+                            mma_f16_16816(acc[mt][nb], al[mt][2 * j], ah[mt][2 * j], al[mt][2 * j + 1], ah[mt][2 * j + 1], b0, b1);
+                        else
+                            mma_bf16_16816(acc[mt][nb], al[mt][2 * j], ah[mt][2 * j], al[mt][2 * j + 1], ah[mt][2 * j + 1], b0, b1);
+                    }
                 }
             }
         }

@@ -78,6 +78,14 @@ int launch_dequantize_ex(shrewq_ctx *ctx, const int8_t *q, const double *scales,
     return SHREWQ_OK;
 }
 
+int launch_pack_int4(shrewq_ctx *ctx, const int8_t *q, size_t n_pairs, uint8_t *packed) {
+    if (n_pairs == 0) return SHREWQ_OK;
+    pack_int4_kernel<<<grid_for(ctx, n_pairs), 256, 0, ctx->stream>>>(q, n_pairs, packed);
+    ctx->launches += 1;
+    SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+    return SHREWQ_OK;
+}
+
 int launch_scale_zp_to_f32(shrewq_ctx *ctx, const double *scales, const double *zps, int granularity, size_t n, float *out) {
     if (n == 0) return SHREWQ_OK;
     scale_zp_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(scales, zps, granularity == SHREWQ_PER_CHANNEL,

@@ -229,6 +229,19 @@ dequantize_ex_kernel(const int8_t *__restrict__ q, const double *__restrict__ sc
     }
 }
 
+// ---- INT4 codes, two per byte --------------------------------------------------------------------
+// The reference keeps INT4 codes one per i8 (its size_bytes only pretends to pack, quantize.rs:176).
+// Packed form used by the small-batch forward: byte j of a row = codes 2j (low nibble) and 2j+1 (high
+// nibble), each stored as code + 8 (0..15), so unpacking needs no sign extension.
+__global__ void __launch_bounds__(256)
+pack_int4_kernel(const int8_t *__restrict__ q, size_t n_pairs, uint8_t *__restrict__ out) {
+    const size_t stride = (size_t)gridDim.x * 256;
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n_pairs; i += stride) {
+        const unsigned lo = (unsigned)(q[2 * i] + 8) & 0xFu, hi = (unsigned)(q[2 * i + 1] + 8) & 0xFu;
+        out[i] = (uint8_t)(lo | (hi << 4));
+    }
+}
+
 // ---- forward support: y -= (scale * zp)[n] * sum_k x[m,k] ----------------------------------------
 __global__ void scale_zp_to_f32_kernel(const double *__restrict__ scales, const double *__restrict__ zps,
                                        int per_channel, size_t n, float *__restrict__ out) {

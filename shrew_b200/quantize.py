@@ -237,6 +237,17 @@ def quantize_tensor_given_amax(tensor: torch.Tensor, amax: torch.Tensor) -> Quan
     return QuantizedTensor(q, scale, list(w.shape), tensor.dtype, QuantConfig.int8())
 
 
+def pack_int4(qtensor: QuantizedTensor) -> torch.Tensor:
+    """INT4 codes (one per i8, as quantize_tensor returns them) -> two per byte: a uint8 tensor
+    [shape[0], cols / 2], byte j of a row = code 2j + 8 in the low and code 2j+1 + 8 in the high nibble."""
+    dev = Device.get(qtensor.data.device)
+    rows, cols = _rows_cols(qtensor.shape)
+    out = torch.empty((rows, cols // 2), dtype=torch.uint8, device=qtensor.data.device)
+    dev.bind_stream()
+    _lib.check(_lib.lib().shrewq_pack_int4(dev.handle, _ptr(qtensor.data), rows, cols, _ptr(out)), dev.handle)
+    return out
+
+
 def dequantize_tensor(qtensor: QuantizedTensor, device=None) -> torch.Tensor:
     """quantize.rs:210-225 on the GPU: a tensor of the original dtype and shape."""
     dev_t = qtensor.data.device if device is None else torch.device(device)
@@ -314,6 +325,28 @@ class QuantizedLinear:
     @classmethod
     def new(cls, weight_q: QuantizedTensor, bias: Optional[torch.Tensor], device=None) -> "QuantizedLinear":
         return cls(weight_q, bias, device)
+
+    @classmethod
+    def new_int4_packed(cls, weight_q: QuantizedTensor, bias: Optional[torch.Tensor] = None) -> "QuantizedLinear":
+        """A layer over INT4 codes packed two per byte (beyond the reference, whose INT4 tensors keep one
+        code per i8): half the weight bytes of INT8 for the small-batch forward (bf16 activations, M <= 32,
+        in_features a multiple of 128).  `weight_q` is an INT4 symmetric QuantizedTensor."""
+        if weight_q.config.bits is not QuantBits.Int4 or weight_q.config.mode is not QuantMode.Symmetric:
+            raise ShrewError(_lib.ERR_INVALID_ARG, "new_int4_packed: needs an INT4 symmetric weight")
+        self = cls.__new__(cls)
+        self.weight_q, self.bias = weight_q, bias
+        self.out_features, self.in_features = int(weight_q.shape[0]), int(weight_q.shape[1])
+        self.device = Device.get(weight_q.data.device)
+        self.packed = pack_int4(weight_q)
+        self._bias_flat = None if bias is None else bias.reshape(-1).to(torch.float32).contiguous()
+        h = ctypes.c_void_p()
+        self.device.bind_stream()
+        rc = _lib.lib().shrewq_linear_create_int4(self.device.handle, _ptr(self.packed), _ptr(weight_q.scales), _ptr(self._bias_flat),
+                                                  self.out_features, self.in_features, weight_q.config.granularity.value,
+                                                  ctypes.byref(h))
+        _lib.check(rc, self.device.handle)
+        self._h = h
+        return self
 
     @classmethod
     def from_linear(cls, linear, config: QuantConfig) -> "QuantizedLinear":

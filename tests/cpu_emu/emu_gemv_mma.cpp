@@ -80,3 +80,50 @@ extern "C" int emu_gemv_mma(const int8_t *q, const float *scales, const float *b
     const Args a{q, q_up, scales, bias, scales_up, bias_up, x, y, M, N, K, ldy, epilogue};
     return y_bf16 ? run_y<__nv_bfloat16>(a, f16, staged) : run_y<float>(a, f16, staged);
 }
+
+namespace {
+template <int MT16, typename YT, bool GATED, bool XS>
+void run_w4(const Args &a, const void *x, const int *xshift, size_t smem) {
+    constexpr int kChan = GATED ? 8 : 8 * NB;
+    const unsigned grid = (unsigned)((a.N + kChan - 1) / kChan);
+    Dests none{};
+    emu::launch(grid, kThreads, smem, [&] {
+        gemv_mma_kernel<MT16, YT, GATED, true, XS, true>(a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up,
+                                                         static_cast<const uint16_t *>(x), xshift, static_cast<YT *>(a.y), none,
+                                                         a.M, a.N, a.K, a.ldy, a.epilogue);
+    });
+}
+
+template <typename YT, bool GATED>
+int forward_w4(const Args &a, int *staged_out) {
+    *staged_out = 0;
+    if (a.M <= kStageMaxTokens && (size_t)a.M * a.K * sizeof(uint16_t) <= (size_t)kStageMaxBytes) {
+        *staged_out = 1;
+        run_w4<1, YT, GATED, true>(a, a.x, nullptr, (size_t)a.M * a.K * sizeof(uint16_t));
+        return 0;
+    }
+    std::vector<uint16_t> x16((size_t)a.M * a.K);
+    std::vector<int> shift(a.M);
+    emu::launch((unsigned)a.M, 256, [&] {
+        x_to_f16_kernel(static_cast<const __nv_bfloat16 *>(a.x), reinterpret_cast<__half *>(x16.data()), shift.data(), a.K, 1);
+    });
+    if (a.M <= 16) run_w4<1, YT, GATED, false>(a, x16.data(), shift.data(), 0);
+    else run_w4<2, YT, GATED, false>(a, x16.data(), shift.data(), 0);
+    return 0;
+}
+}  // namespace
+
+// packed INT4 weights: q / q_up are [N][K/2] bytes (code 2j + 8 in the low, code 2j+1 + 8 in the high nibble)
+extern "C" int emu_gemv_mma_w4(const uint8_t *q, const float *scales, const float *bias, const uint8_t *q_up,
+                               const float *scales_up, const float *bias_up, const void *x, void *y, int M, int N, int K,
+                               size_t ldy, int epilogue, int y_bf16, int *staged) {
+    if (M < 1 || M > 32 || K < 128 || (K % 128) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) ||
+        (q_up && (reinterpret_cast<uintptr_t>(q_up) & 15)))
+        return -1;
+    const Args a{reinterpret_cast<const int8_t *>(q), reinterpret_cast<const int8_t *>(q_up), scales, bias, scales_up, bias_up, x, y,
+                 M, N, K, ldy, epilogue};
+    const bool gated = q_up != nullptr;
+    if (y_bf16) return gated ? forward_w4<__nv_bfloat16, true>(a, staged) : forward_w4<__nv_bfloat16, false>(a, staged);
+    return gated ? forward_w4<float, true>(a, staged) : forward_w4<float, false>(a, staged);
+}
+

@@ -94,3 +94,9 @@ extern "C" int emu_x_to_f16(const void *x_bf16, size_t M, int K, void *x16, int 
     });
     return 0;
 }
+
+extern "C" int emu_pack_int4(const int8_t *q, size_t n_pairs, unsigned grid, uint8_t *out) {
+    if (n_pairs) emu::launch(grid, 256, [&] { pack_int4_kernel(q, n_pairs, out); });
+    return 0;
+}
+

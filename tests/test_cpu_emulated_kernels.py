@@ -890,3 +890,63 @@ def _np_quantize_f64(oracle, data64, gran, bits, mode):
         t = oracle.np_round_half_away(data * inv[:, None] + zp[:, None])
         t = np.where(np.isnan(t), 0.0, np.clip(t, qmin, qmax))
     return t.astype(np.int8).reshape(rows, cols), scale.astype(np.float64), zp.astype(np.float64)
+
+
+# ---- INT4 codes packed two per byte and their small-batch forward (beyond the reference, never run on a GPU)
+def _pack_int4(codes):
+    u = (codes.astype(np.int16) + 8).astype(np.uint8) & 0xF
+    return (u[:, 0::2] | (u[:, 1::2] << 4)).astype(np.uint8)
+
+
+def test_pack_int4_kernel(emu_modes):
+    emu_modes.emu_pack_int4.argtypes = [_vp, _sz, _cu, _vp]
+    rng = np.random.default_rng(0)
+    codes = rng.integers(-8, 8, size=(7, 130)).astype(np.int8)
+    out = np.zeros((7, 65), np.uint8)
+    emu_modes.emu_pack_int4(_p(codes), codes.size // 2, 3, _p(out))
+    np.testing.assert_array_equal(out, _pack_int4(codes))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16, 128), (1, 40, 1024), (3, 21, 256), (4, 16, 5120), (5, 16, 128), (16, 24, 384), (17, 17, 256),
+                                   (32, 16, 128)])
+def test_packed_int4_forward_matches_oracle(oracle, emu_mma, M, N, K):
+    emu_mma.emu_gemv_mma_w4.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _vp]
+    rng = np.random.default_rng(M * 100 + N + K)
+    codes = rng.integers(-8, 8, size=(N, K)).astype(np.int8)       # the asymmetric range too: -8 is representable
+    scales = rng.random(N) * 1e-1 + 1e-3
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    ref = oracle.np_linear_forward(codes, scales, oracle.PER_CHANNEL, bias, x, relu=True)
+    packed = _aligned((N, K // 2), np.uint8)
+    packed[...] = _pack_int4(codes)
+    xa = _aligned(x_bits.shape, np.uint16)
+    xa[...] = x_bits
+    s32 = scales.astype(np.float32)
+    y = np.full((M, N + 2), 7.0, np.float32)
+    staged = ctypes.c_int(-1)
+    rc = emu_mma.emu_gemv_mma_w4(_p(packed), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, N + 2, 1, 0, ctypes.byref(staged))
+    assert rc == 0
+    assert staged.value == int(M <= 4 and M * K * 2 <= 40960)
+    assert oracle.rel_err(y[:, :N], ref) < 2e-6 and np.all(y[:, N:] == 7.0)
+
+
+def test_packed_int4_gate_up(oracle, emu_mma):
+    emu_mma.emu_gemv_mma_w4.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _vp]
+    rng = np.random.default_rng(9)
+    for M, N, K in ((2, 24, 256), (12, 9, 384)):
+        cg, cu = (rng.integers(-7, 8, size=(N, K)).astype(np.int8) for _ in range(2))
+        sg, su = rng.random(N) * 1e-1 + 1e-3, rng.random(N) * 1e-1 + 1e-3
+        x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+        g = oracle.np_linear_forward(cg, sg, 1, None, x).astype(np.float64)
+        u = oracle.np_linear_forward(cu, su, 1, None, x).astype(np.float64)
+        ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+        pg, pu = _aligned((N, K // 2), np.uint8), _aligned((N, K // 2), np.uint8)
+        pg[...] = _pack_int4(cg)
+        pu[...] = _pack_int4(cu)
+        xa = _aligned(x_bits.shape, np.uint16)
+        xa[...] = x_bits
+        sg32, su32 = sg.astype(np.float32), su.astype(np.float32)
+        y = np.zeros((M, N), np.float32)
+        staged = ctypes.c_int(-1)
+        assert emu_mma.emu_gemv_mma_w4(_p(pg), _p(sg32), None, _p(pu), _p(su32), None, _p(xa), _p(y), M, N, K, N, 0, 0, ctypes.byref(staged)) == 0
+        assert oracle.rel_err(y, ref) < 1e-5

@@ -123,3 +123,25 @@ def test_quantize_any_storage_type(oracle, monkeypatch, dtype, gran):
     ref = torch.from_numpy(q_ref.astype(np.float64) * (scale[:, None] if gran else scale[0])).to(dtype)
     assert torch.equal(back.cpu(), ref)
 
+
+@_UNVALIDATED
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (3, 300, 1024), (16, 523, 2048), (32, 1000, 1152)])
+def test_packed_int4_forward(oracle, monkeypatch, M, N, K):
+    # INT4 symmetric per-channel codes packed two per byte, small-batch forward on the warp-MMA kernel
+    from shrew_b200 import quantize_tensor
+    from shrew_b200.quantize import Device, QuantizedLinear
+    monkeypatch.setenv("SHREWQ_EXPERIMENTAL_MODES", "1")
+    rng = np.random.default_rng(M + N)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    qt = quantize_tensor(torch.from_numpy(w).cuda(), _cfg(4, 0, 1))
+    ql = QuantizedLinear.new_int4_packed(qt, torch.from_numpy(b).cuda())
+    x_t = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).cuda().to(torch.bfloat16)
+    y = ql.forward(x_t, out_dtype=torch.float32)
+    Device.get("cuda:0").synchronize()
+    assert ql.last_kernel() == "mma-w4"
+    q_ref, s_ref, _ = oracle.np_quantize_f32_ex(w, 1, 4, 0)
+    np.testing.assert_array_equal(qt.data.cpu().numpy().reshape(N, K), q_ref)
+    ref = oracle.np_linear_forward(q_ref, s_ref, 1, b, x_t.float().cpu().numpy())
+    assert oracle.rel_err(y.cpu().numpy(), ref) < 1e-4
+
