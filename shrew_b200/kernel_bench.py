@@ -4,7 +4,8 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     python -m shrew_b200.kernel_bench quant      # quantize / dequantize bandwidth sweep
     python -m shrew_b200.kernel_bench lin        # forward kernels over a batch sweep
     python -m shrew_b200.kernel_bench lin 4096 4096 1,16,256   # one layer shape, chosen batches
-    SHREWQ_BENCH_KERNELS=gemv,mma,mma-f16,tcgen05 python -m shrew_b200.kernel_bench lin   # other kernel families
+    SHREWQ_BENCH_KERNELS=gemv,mma,mma-f16,mma-w4,tcgen05,tcgen05-2cta python -m shrew_b200.kernel_bench lin   # other kernel families
+    (mma-w4 = packed INT4 weights, also needs SHREWQ_EXPERIMENTAL_MODES=1)
     python -m shrew_b200.build --trace && SHREWQ_LIB=shrew_b200/libshrewq_trace.so \
         python -m shrew_b200.kernel_bench trace 4096 4096 16,1024  # in-kernel cycle trace of CTA 0
 
@@ -77,29 +78,47 @@ def _layers(N, K, nbuf):
     return out
 
 
+def _layers_int4(N, K, nbuf):
+    """packed INT4 layers (experimental: needs SHREWQ_EXPERIMENTAL_MODES=1)"""
+    from .quantize import QuantBits, QuantGranularity, QuantMode
+    cfg = QuantConfig(QuantBits.Int4, QuantMode.Symmetric, QuantGranularity.PerChannel)
+    out = []
+    for _ in range(nbuf):
+        q = torch.randint(-7, 8, (N * K,), dtype=torch.int8, device="cuda")
+        qt = QuantizedTensor(q, torch.rand(N, dtype=torch.float64, device="cuda") * 1e-2 + 1e-3, [N, K], torch.float32, cfg)
+        out.append(QuantizedLinear.new_int4_packed(qt, None))
+    return out
+
+
 def bench_lin(shapes, batches):
     L = _lib.lib()
+    kernels = os.environ.get("SHREWQ_BENCH_KERNELS", "gemv,tcgen05").split(",")
     for (N, K) in shapes:
         nbuf = max(2, int(2 * L2_BYTES // (N * K)) + 1)
         lins = _layers(N, K, nbuf)
+        lins4 = _layers_int4(N, K, 2 * nbuf) if "mma-w4" in kernels and K % 128 == 0 else None
         for M in batches:
             x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
             y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-            for force in os.environ.get("SHREWQ_BENCH_KERNELS", "gemv,tcgen05").split(","):
+            for force in kernels:
                 if (force == "gemv" and M > 16) or (force.startswith("mma") and M > 64):
                     continue
-                L.shrewq_force_kernel(force.encode())
+                w4 = force == "mma-w4"
+                if w4 and (lins4 is None or M > 32):
+                    continue
+                L.shrewq_force_kernel(b"auto" if w4 else force.encode())
+                use = lins4 if w4 else lins
 
                 def f():
-                    for lin in lins:
+                    for lin in use:
                         lin.forward(x, out=y)
                 try:
-                    t = _time_graph(f, iters=5, warm=2) / nbuf
+                    t = _time_graph(f, iters=5, warm=2) / len(use)
                     Device.get("cuda:0").synchronize()
                 except Exception as e:  # noqa: BLE001
                     print(json.dumps(dict(kernel=force, M=M, N=N, K=K, error=str(e))), flush=True)
                     continue
-                by = N * K + 4 * N + M * K * 2 + M * N * 2
+                by = (N * K // 2 if w4 else N * K) + 4 * N + M * K * 2 + M * N * 2
                 print(json.dumps(dict(kernel=force, M=M, N=N, K=K, us=t * 1e6, GBs=by / t / 1e9,
                                       TFs=2 * M * N * K / t / 1e12)), flush=True)
         L.shrewq_force_kernel(b"auto")
