@@ -477,7 +477,15 @@ def main():
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Every rank has its result; leave together and at once.  Collectives and symmetric-memory
+        # buffers captured in CUDA graphs have kept ranks from ending in interpreter teardown on this
+        # software stack (results printed, processes never exited), so after a last barrier the ranks
+        # skip that teardown; the driver reclaims the context with the process.
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 
