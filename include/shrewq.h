@@ -271,6 +271,14 @@ SHREWQ_API const char *shrewq_linear_last_kernel(const shrewq_linear *lin);
  * cannot take a shape makes the forward fail with SHREWQ_ERR_UNSUPPORTED (it never falls
  * back silently).  For tests and benchmarks; no counterpart in the reference. */
 SHREWQ_API int shrewq_force_kernel(const char *name);
+/* Which kernel family and launch plan a forward of this shape would get on a GPU with `sm_count` SMs
+ * (16-byte aligned buffers, no forced kernel): writes the family name into `kernel` (at least 16 bytes)
+ * and, for "tcgen05", the token tile, the tile grid, the K splits and the pipeline rounds per split
+ * (zeros otherwise).  Pure host arithmetic: needs no GPU and no context.  For tests, benchmarks and
+ * capacity planning; no counterpart in the reference. */
+SHREWQ_API int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, int sm_count, char *kernel,
+                        size_t kernel_len, int *tok, int *n_tiles, int *m_tiles, int *splits,
+                        int *rounds_per_split);
 /* Number of kernels this context has launched since creation (for benchmark accounting). */
 SHREWQ_API uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx);
 

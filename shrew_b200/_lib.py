@@ -53,6 +53,8 @@ SIGNATURES = {
     "shrewq_linear_last_kernel": (ctypes.c_char_p, [_vp]),
     "shrewq_force_kernel": (_ci, [ctypes.c_char_p]),
     "shrewq_ctx_launch_count": (ctypes.c_uint64, [_vp]),
+    "shrewq_plan_forward": (_ci, [_sz, _sz, _sz, _ci, _ci, _ci, ctypes.c_char_p, _sz, ctypes.POINTER(_ci), ctypes.POINTER(_ci),
+                                 ctypes.POINTER(_ci), ctypes.POINTER(_ci), ctypes.POINTER(_ci)]),
 }
 
 _lib = None

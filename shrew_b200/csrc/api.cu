@@ -146,6 +146,30 @@ const char *shrewq_last_error(const shrewq_ctx *ctx) { return ctx ? ctx->err : g
 
 uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx) { return ctx ? ctx->launches : 0; }
 
+// The default kernel family of a forward: the one rule, shared by forward_impl and shrewq_plan_forward.
+static int default_family(size_t M, bool gemv_ok, bool tc_ok) {
+    if (gemv_ok && (M <= 4 || !tc_ok)) return kForceGemv;
+    return tc_ok ? kForceTc : kForceSimt;
+}
+
+int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, int sm_count, char *kernel, size_t kernel_len,
+                        int *tok, int *n_tiles, int *m_tiles, int *splits, int *rounds_per_split) {
+    if (!kernel || kernel_len < 16 || !tok || !n_tiles || !m_tiles || !splits || !rounds_per_split || sm_count < 1 || N == 0 ||
+        K == 0)
+        return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "plan_forward: bad argument");
+    *tok = *n_tiles = *m_tiles = *splits = *rounds_per_split = 0;
+    // the rule of forward_impl for aligned buffers and no forced kernel
+    const bool vec16 = (K % 16) == 0;
+    const bool small = M < (1u << 31) && N < (1u << 31) && K < (1u << 31);
+    const bool tc_ok = x_is_bf16 && vec16 && M >= 1 && small;
+    const int fam = default_family(M, vec16 && M <= 16, tc_ok);
+    const char *name = fam == kForceGemv ? "gemv" : fam == kForceTc ? "tcgen05" : "simt";
+    snprintf(kernel, kernel_len, "%s", name);
+    if (!strcmp(name, "tcgen05"))
+        return plan_gemm_tcgen05(M, N, K, gated != 0, sm_count, tok, n_tiles, m_tiles, splits, rounds_per_split);
+    return SHREWQ_OK;
+}
+
 int shrewq_force_kernel(const char *name) {
     if (!name || !*name || !strcmp(name, "auto")) g_forced_kernel = kAuto;
     else if (!strcmp(name, "gemv")) g_forced_kernel = kForceGemv;
@@ -592,9 +616,7 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             }
             // CUDA-core GEMV keeps up with HBM only for a few tokens; beyond that the tensor
             // cores take over (bf16 activations), else the general f32 kernel.
-            if (gemv_ok && (M <= 4 || !tc_ok)) choice = kForceGemv;
-            else if (tc_ok) choice = kForceTc;
-            else choice = kForceSimt;
+            choice = default_family(M, gemv_ok, tc_ok);
     }
     const char *name;
     if (choice == kForceGemv) { rc = launch_gemv(ctx, a); name = "gemv"; }

@@ -124,6 +124,8 @@ int launch_gemv_mma_w4(shrewq_ctx *ctx, const ForwardArgs &a);
 int launch_pack_int4(shrewq_ctx *ctx, const int8_t *q, size_t n_pairs, uint8_t *packed);
 bool tcgen05_supported(const ForwardArgs &a);
 int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);
+int plan_gemm_tcgen05(size_t M, size_t N, size_t K, bool gated, int sm_count, int *tok, int *n_tiles, int *m_tiles,
+                      int *splits, int *rounds_per_split);
 int launch_gemm_tcgen05_2cta(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);
 int launch_gemm_tcgen05_noalloc(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap);
 int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, int box_rows, void *tmap_out);

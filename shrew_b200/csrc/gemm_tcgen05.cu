@@ -284,6 +284,28 @@ int launch_gemm_tcgen05_noalloc(shrewq_ctx *ctx, const ForwardArgs &a, const voi
 
 // w_tmap: 128-row boxes of the weight (plain) or 64-row boxes of the gate matrix (gated, with
 // w_up_tmap the 64-row boxes of the up matrix)
+// The launch plan of the tcgen05 forward for a shape, without launching anything (pure host arithmetic:
+// token tile, tile grid, K splits, pipeline rounds per split).
+int plan_gemm_tcgen05(size_t M, size_t N, size_t K, bool gated, int sm_count, int *tok, int *n_tiles, int *m_tiles,
+                      int *splits, int *rounds_per_split) {
+    ForwardArgs a{};
+    a.M = M; a.N = N; a.K = K;
+    const Tuning t = read_tuning();
+    const int chan = gated ? 64 : 128;
+    const int tk = t.tok ? t.tok : choose_tok(a, chan, sm_count);
+    LaunchPlan p;
+    switch (tk) {
+        case 16: p = plan_launch<16, 2>(a, chan, sm_count, t.splitk); break;
+        case 32: p = plan_launch<32, 2>(a, chan, sm_count, t.splitk); break;
+        case 64: p = plan_launch<64, 2>(a, chan, sm_count, t.splitk); break;
+        case 128: p = plan_launch<128, 2>(a, chan, sm_count, t.splitk); break;
+        case 256: p = plan_launch<256, 1>(a, chan, sm_count, t.splitk); break;
+        default: return SHREWQ_ERR_INVALID_ARG;
+    }
+    *tok = tk; *n_tiles = p.n_tiles; *m_tiles = p.m_tiles; *splits = p.splits; *rounds_per_split = p.rounds_per_split;
+    return SHREWQ_OK;
+}
+
 int launch_gemm_tcgen05(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap) {
     const CUtensorMap &tw = *static_cast<const CUtensorMap *>(w_tmap);
     if (a.q_up) {

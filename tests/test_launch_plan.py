@@ -1,0 +1,109 @@
+"""Host-side launch planning of the QuantizedLinear forward (kernel family, token tile, tile grid, K splits).
+
+`shrewq_plan_forward` is pure host arithmetic, so the choice the library would make on a 148-SM GPU is
+checked here without one.  The forward it plans replaces QuantizedLinear::forward
+(crates/shrew/src/quantize.rs:208-223 of the reference), which has one code path for every shape.
+"""
+import ctypes
+import itertools
+
+import pytest
+
+from shrew_b200 import _lib
+
+SMS = 148
+
+
+def plan(M, N, K, bf16=1, gated=0, sms=SMS):
+    name = ctypes.create_string_buffer(32)
+    out = [ctypes.c_int(-1) for _ in range(5)]
+    rc = _lib.lib().shrewq_plan_forward(M, N, K, bf16, gated, sms, name, 32, *[ctypes.byref(v) for v in out])
+    return rc, name.value.decode(), dict(zip(("tok", "n_tiles", "m_tiles", "splits", "rounds"), (v.value for v in out)))
+
+
+def test_a_few_tokens_go_to_the_cuda_core_gemv():
+    for M in (1, 2, 4):
+        rc, name, p = plan(M, 4096, 4096)
+        assert (rc, name) == (0, "gemv") and not any(p.values())
+
+
+def test_f32_activations_never_reach_the_tensor_cores():
+    assert plan(8, 4096, 4096, bf16=0)[1] == "gemv"
+    assert plan(16, 4096, 4096, bf16=0)[1] == "gemv"
+    assert plan(17, 4096, 4096, bf16=0)[1] == "simt"
+    assert plan(512, 4096, 4096, bf16=0)[1] == "simt"
+
+
+def test_ragged_in_features_fall_back_to_the_general_kernel():
+    for K in (4100, 17, 1):
+        assert plan(8, 4096, K)[1] == "simt"
+        assert plan(1, 4096, K)[1] == "simt"
+
+
+@pytest.mark.parametrize("gated", [0, 1])
+@pytest.mark.parametrize("M,N,K", list(itertools.product(
+    (5, 16, 17, 33, 64, 100, 128, 129, 256, 512, 1000, 2048, 8192),
+    (128, 1000, 4096, 11008, 32000),
+    (16, 64, 128, 4096, 11008))))
+def test_the_plan_covers_the_problem(M, N, K, gated):
+    rc, name, p = plan(M, N, K, gated=gated)
+    assert (rc, name) == (0, "tcgen05")
+    chan = 64 if gated else 128
+    assert p["tok"] in (16, 32, 64, 128, 256)
+    assert p["n_tiles"] == -(-N // chan)
+    assert p["m_tiles"] == -(-M // p["tok"])
+    # the token tile is not a size larger than the batch needs
+    assert p["tok"] == 16 or p["tok"] // 2 < M
+    # every 64-wide block of in_features belongs to exactly one split
+    kblk = 64 if p["tok"] == 256 else 128
+    rounds_total = -(-K // kblk)
+    assert p["splits"] >= 1 and p["rounds"] >= 1
+    assert p["splits"] * p["rounds"] >= rounds_total
+    assert (p["splits"] - 1) * p["rounds"] < rounds_total
+    # K is split only to fill SMs that the tile grid leaves idle, and never below a useful pipeline length
+    tiles = p["n_tiles"] * p["m_tiles"]
+    if p["splits"] > 1:
+        assert p["tok"] <= 64                      # partial sums of large tiles are not worth their traffic
+        assert tiles * p["splits"] <= SMS          # all splits of all tiles run in one wave
+        assert p["rounds"] >= 2
+
+
+def test_headline_shapes():
+    # decode-sized batches of a 4096x4096 projection: 32 channel tiles cannot fill 148 SMs, so K is split
+    assert plan(16, 4096, 4096)[2] == dict(tok=16, n_tiles=32, m_tiles=1, splits=4, rounds=8)
+    # wide projections fill the GPU by themselves
+    assert plan(16, 11008, 4096)[2] == dict(tok=16, n_tiles=86, m_tiles=1, splits=1, rounds=32)
+    # prefill: 128-token tiles until the grid is several waves deep, then 256
+    assert plan(512, 4096, 4096)[2]["tok"] == 128
+    assert plan(2048, 4096, 4096)[2] == dict(tok=256, n_tiles=32, m_tiles=8, splits=1, rounds=64)
+    # gate and up halves share a tile: twice the channel tiles
+    assert plan(512, 11008, 4096, gated=1)[2]["n_tiles"] == 172
+
+
+def test_fewer_sms_split_less():
+    full = plan(16, 4096, 4096, sms=148)[2]["splits"]
+    small = plan(16, 4096, 4096, sms=40)[2]["splits"]
+    assert small <= full and small == 1
+
+
+def test_forced_token_tile(monkeypatch):
+    monkeypatch.setenv("SHREWQ_TC_TOK", "256")
+    assert plan(512, 4096, 4096)[2]["tok"] == 256
+    monkeypatch.setenv("SHREWQ_TC_TOK", "48")
+    assert plan(512, 4096, 4096)[0] != 0
+    monkeypatch.setenv("SHREWQ_TC_TOK", "0")
+    monkeypatch.setenv("SHREWQ_TC_SPLITK", "0")
+    assert plan(16, 4096, 4096)[2]["splits"] == 1
+
+
+def test_bad_arguments_are_refused():
+    L = _lib.lib()
+    name = ctypes.create_string_buffer(32)
+    v = [ctypes.c_int() for _ in range(5)]
+    refs = [ctypes.byref(x) for x in v]
+    assert L.shrewq_plan_forward(8, 4096, 4096, 1, 0, 148, None, 32, *refs) != 0
+    assert L.shrewq_plan_forward(8, 4096, 4096, 1, 0, 148, name, 4, *refs) != 0
+    assert L.shrewq_plan_forward(8, 4096, 4096, 1, 0, 0, name, 32, *refs) != 0
+    assert L.shrewq_plan_forward(8, 0, 4096, 1, 0, 148, name, 32, *refs) != 0
+    assert L.shrewq_plan_forward(8, 4096, 0, 1, 0, 148, name, 32, *refs) != 0
+    assert L.shrewq_plan_forward(8, 4096, 4096, 1, 0, 148, name, 32, None, *refs[1:]) != 0
