@@ -5,7 +5,8 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     python -m shrew_b200.kernel_bench lin        # forward kernels over a batch sweep
     python -m shrew_b200.kernel_bench lin 4096 4096 1,16,256   # one layer shape, chosen batches
     SHREWQ_BENCH_KERNELS=gemv,mma,mma-f16,mma-w4,tcgen05,tcgen05-2cta python -m shrew_b200.kernel_bench lin   # other kernel families
-    (mma-w4 = packed INT4 weights, also needs SHREWQ_EXPERIMENTAL_MODES=1)
+    (mma-w4 = packed INT4 weights, also needs SHREWQ_EXPERIMENTAL_MODES=1; a "+af16" suffix on a tcgen05
+    family, e.g. tcgen05+af16, runs it with f16 weights in tensor memory, SHREWQ_TC_A_F16=1)
     python -m shrew_b200.build --trace && SHREWQ_LIB=shrew_b200/libshrewq_trace.so \
         python -m shrew_b200.kernel_bench trace 4096 4096 16,1024  # in-kernel cycle trace of CTA 0
 
@@ -106,7 +107,9 @@ def bench_lin(shapes, batches):
                 w4 = force == "mma-w4"
                 if w4 and (lins4 is None or M > 32):
                     continue
-                L.shrewq_force_kernel(b"auto" if w4 else force.encode())
+                family, _, variant = force.partition("+")
+                os.environ["SHREWQ_TC_A_F16"] = "1" if variant == "af16" else "0"   # read by the library at every launch
+                L.shrewq_force_kernel(b"auto" if w4 else family.encode())
                 use = lins4 if w4 else lins
 
                 def f():
@@ -122,6 +125,7 @@ def bench_lin(shapes, batches):
                 print(json.dumps(dict(kernel=force, M=M, N=N, K=K, us=t * 1e6, GBs=by / t / 1e9,
                                       TFs=2 * M * N * K / t / 1e12)), flush=True)
         L.shrewq_force_kernel(b"auto")
+        os.environ.pop("SHREWQ_TC_A_F16", None)
         del lins
 
 

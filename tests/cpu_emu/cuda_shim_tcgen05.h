@@ -241,8 +241,9 @@ static inline void tc_ld16(uint32_t taddr, uint32_t *r) {
 }
 
 // tcgen05.mma.cta_group::1.kind::f16 [d], [a], b_desc, idesc, p:  D[128 x N] (+)= A[128 x 16] * B[N x 16]^T,
-// bf16 operands, f32 accumulators.  A: tensor-memory lane m, 8 columns of two bf16 (even k in the lower
-// half).  B: shared memory, K-major rows of 128 bytes, 8-row groups `stride byte offset` apart, 128-byte swizzle.
+// bf16 B, bf16 or f16 A (the descriptor's format fields), f32 accumulators.  A: tensor-memory lane m, 8 columns
+// of two 16-bit values (even k in the lower half).  B: shared memory, K-major rows of 128 bytes, 8-row groups `stride byte offset` apart, 128-byte swizzle.
+namespace emu { inline std::atomic<int> g_last_a_format{-1}; }  // A operand format of the latest MMA (for the tests)
 static inline void tc_mma_ts_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate);
 static inline void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     if (emu::tc_deferred()) emu::tc_push([=] { tc_mma_ts_now(d_tmem, a_tmem, b_desc, idesc, accumulate); });
@@ -252,7 +253,10 @@ static inline void tc_mma_ts_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_de
     emu::Block *blk = emu::g_block;
     const uint32_t N = ((idesc >> 17) & 0x3Fu) << 3, Mrows = ((idesc >> 24) & 0x1Fu) << 4;
     EMU_CHECK(Mrows == 128 && N >= 8 && N <= 256 && N % 8 == 0, "Mrows == 128 && N >= 8 && N <= 256 && N % 8 == 0");
-    EMU_CHECK(((idesc >> 4) & 3u) == 1 && ((idesc >> 7) & 7u) == 1 && ((idesc >> 10) & 7u) == 1, "D f32, A bf16, B bf16");
+    // operand formats of kind::f16: 0 = f16, 1 = bf16, named separately for A [7,10) and B [10,13)
+    const uint32_t a_fmt = (idesc >> 7) & 7u;
+    emu::g_last_a_format = (int)a_fmt;
+    EMU_CHECK(((idesc >> 4) & 3u) == 1 && a_fmt <= 1 && ((idesc >> 10) & 7u) == 1, "D f32, A f16 or bf16, B bf16");
     EMU_CHECK(((b_desc >> 61) & 7u) == 2 && ((b_desc >> 46) & 1u) == 1, "128-byte swizzle, descriptor version 1");
     const uint32_t start = (uint32_t)(b_desc & 0x3FFFu) << 4, sbo = (uint32_t)((b_desc >> 32) & 0x3FFFu) << 4;
     const uint32_t smem_hi = smem_u32(blk->dyn);  // 256 KiB aligned; the descriptor keeps the 18 low address bits
@@ -273,7 +277,8 @@ static inline void tc_mma_ts_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_de
         float a[16];
         for (uint32_t k = 0; k < 16; ++k) {
             const uint32_t w = blk->tmem[m * 512 + acol + (k >> 1)];
-            a[k] = __uint_as_float(((k & 1) ? (w >> 16) : (w & 0xFFFF)) << 16);
+            const uint32_t h = (k & 1) ? (w >> 16) : (w & 0xFFFF);
+            a[k] = a_fmt == 1 ? __uint_as_float(h << 16) : (float)emu_f16_of(h);
         }
         for (uint32_t n = 0; n < N; ++n) {
             double acc = accumulate ? (double)__uint_as_float(blk->tmem[m * 512 + dcol + n]) : 0.0;

@@ -43,7 +43,9 @@ static inline void tc_mma_ts_pair_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t
     EMU_CHECK(me->rank == 0, "the leader CTA issues the pair MMA");
     const uint32_t N = ((idesc >> 17) & 0x3Fu) << 3, Mrows = ((idesc >> 24) & 0x1Fu) << 4;
     EMU_CHECK(Mrows == 256 && N == 256, "Mrows == 256 && N == 256");
-    EMU_CHECK(((idesc >> 4) & 3u) == 1 && ((idesc >> 7) & 7u) == 1 && ((idesc >> 10) & 7u) == 1, "D f32, A bf16, B bf16");
+    const uint32_t a_fmt = (idesc >> 7) & 7u;  // 0 = f16, 1 = bf16
+    emu::g_last_a_format = (int)a_fmt;
+    EMU_CHECK(((idesc >> 4) & 3u) == 1 && a_fmt <= 1 && ((idesc >> 10) & 7u) == 1, "D f32, A f16 or bf16, B bf16");
     EMU_CHECK(((b_desc >> 61) & 7u) == 2 && ((b_desc >> 46) & 1u) == 1, "128-byte swizzle, descriptor version 1");
     const uint32_t start = (uint32_t)(b_desc & 0x3FFFu) << 4, sbo = (uint32_t)((b_desc >> 32) & 0x3FFFu) << 4;
     const uint32_t dcol = d_tmem & 0xFFFF, acol = a_tmem & 0xFFFF;
@@ -68,7 +70,8 @@ static inline void tc_mma_ts_pair_now(uint32_t d_tmem, uint32_t a_tmem, uint64_t
             float a[16];
             for (uint32_t k = 0; k < 16; ++k) {
                 const uint32_t w = tm[m * 512 + acol + (k >> 1)];
-                a[k] = __uint_as_float(((k & 1) ? (w >> 16) : (w & 0xFFFF)) << 16);
+                const uint32_t h = (k & 1) ? (w >> 16) : (w & 0xFFFF);
+                a[k] = a_fmt == 1 ? __uint_as_float(h << 16) : (float)emu_f16_of(h);
             }
             for (uint32_t n = 0; n < N; ++n) {
                 double acc = accumulate ? (double)__uint_as_float(tm[m * 512 + dcol + n]) : 0.0;

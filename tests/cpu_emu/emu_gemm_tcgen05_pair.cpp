@@ -9,8 +9,14 @@
 using namespace shrewq;
 
 namespace {
+bool g_a_f16 = false;  // next launches use the variant with f16 weights in tensor memory
+
 template <typename YT, bool GATED>
 int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
+        int epilogue, int splits, DeviceStatus *st);
+
+template <typename YT, bool GATED, bool AF16>
+int run_as(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
         int epilogue, int splits, DeviceStatus *st) {
     const uint32_t box_rows = GATED ? 64 : 128;
     const CUtensorMap tw{q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
@@ -29,13 +35,22 @@ int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_
     std::vector<unsigned int> counters(ctas, 0u);
     SplitK2 sk{splits > 1 ? partials.data() : nullptr, splits > 1 ? counters.data() : nullptr, rps};
     emu::launch_cluster2(2 * pairs, m_tiles, (unsigned)splits, kThreads, kSmemBytes, [&] {
-        linear_i8_tcgen05_pair_kernel<YT, GATED>(tw, tw2, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, sk, st);
+        linear_i8_tcgen05_pair_kernel<YT, GATED, AF16>(tw, tw2, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, sk, st);
     });
     for (unsigned int c : counters)
         if (c != 0) return -3;  // the kernel leaves the tile counters at zero for the next launch
     return 0;
 }
+template <typename YT, bool GATED>
+int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
+        int epilogue, int splits, DeviceStatus *st) {
+    return g_a_f16 ? run_as<YT, GATED, true>(q, q_up, ops, x, y, M, N, K, ldy, epilogue, splits, st)
+                   : run_as<YT, GATED, false>(q, q_up, ops, x, y, M, N, K, ldy, epilogue, splits, st);
+}
 }  // namespace
+
+extern "C" void emu_set_a_f16(int on) { g_a_f16 = on != 0; }
+extern "C" int emu_last_a_format() { return emu::g_last_a_format.load(); }  // 0 = f16, 1 = bf16
 
 // q_up == NULL: plain forward; else silu(gate) * up.  splits: K splits (blockIdx.z).  Returns 0; -1 for a shape
 // the launcher refuses; -2 when a bounded wait of the kernel gave up; -3 when a tile counter was left set;

@@ -371,3 +371,25 @@ def test_cta_pair_gate_up_parity(oracle):
     h_ref = (g_ref / (1.0 + np.exp(-g_ref.astype(np.float64)))).astype(np.float32) * u_ref
     assert oracle.rel_err(h.float().cpu().numpy(), h_ref) < TOL_BF16
 
+
+
+@_UNVALIDATED
+@pytest.mark.parametrize("M,N,K", [(8, 523, 1024), (64, 4096, 4096), (128, 1000, 1040), (512, 4096, 4096), (1024, 1000, 2048)])
+def test_f16_weights_in_tensor_memory_give_the_same_bits(oracle, monkeypatch, M, N, K):
+    # SHREWQ_TC_A_F16=1: the converters write f16 instead of bf16 weights (every code exact in both), the
+    # activations stay bf16: same products, same accumulation order, so the very same output bits
+    from shrew_b200 import _lib
+    from shrew_b200.quantize import Device
+    ql, w, b = _make(N, K, 1, seed=N + K)
+    x_t, x_np = _x(M, K, "bf16", seed=M)
+    monkeypatch.setenv("SHREWQ_TC_A_F16", "1")
+    _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, force="tcgen05")
+    _lib.lib().shrewq_force_kernel(b"tcgen05")
+    try:
+        y_h = ql.forward(x_t)
+        monkeypatch.setenv("SHREWQ_TC_A_F16", "0")
+        y_b = ql.forward(x_t)
+        Device.get("cuda:0").synchronize()
+    finally:
+        _lib.lib().shrewq_force_kernel(b"auto")
+    assert torch.equal(y_h, y_b)
