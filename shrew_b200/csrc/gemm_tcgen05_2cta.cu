@@ -59,7 +59,42 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
     }
     const int rps = (rounds + splits - 1) / splits;
     splits = (rounds + rps - 1) / rps;  // no empty split
-    SplitK2 sk{nullptr, nullptr, rps};
+    SplitK2 sk{nullptr, nullptr, rps, 0, 0};
+    Operands2 ops{a.scales, a.bias, a.scales_up, a.bias_up};
+    // SHREWQ_TC_TAILSPLIT=1 (as for the single-CTA kernel; NOT yet run on a GPU, off by default): when
+    // the pair tiles leave a short last wave, the full waves go out as one launch of whole-K tiles and
+    // the tiles of the last wave as a second launch split along K, so that it fills the SMs too.
+    const char *ts = getenv("SHREWQ_TC_TAILSPLIT");
+    if (ts && atoi(ts) != 0 && splits == 1) {
+        const int per_wave = ctx->sm_count / 2;  // pair tiles resident at once, one CTA per SM
+        const int tiles = (int)(pairs * m_tiles), rem = per_wave > 0 ? tiles % per_wave : 0;
+        int s_tail = rem > 0 ? per_wave / rem : 0;
+        if (s_tail > 4) s_tail = 4;
+        if (s_tail > rounds / 8) s_tail = rounds / 8;
+        if (tiles > per_wave && rem > 0 && s_tail >= 2) {
+            const int rps_t = (rounds + s_tail - 1) / s_tail;
+            const int splits_t = (rounds + rps_t - 1) / rps_t;
+            const size_t part_bytes = (size_t)2 * rem * splits_t * kTokPair * kLanes * sizeof(float);
+            if ((rc = ensure_scratch(ctx, 8192 + part_bytes)) != SHREWQ_OK) return rc;
+            if (!ctx->counters_zeroed) {
+                SHREWQ_CUDA_TRY(ctx, cudaMemsetAsync(static_cast<char *>(ctx->scratch) + 4096, 0, 4096, ctx->stream));
+                ctx->counters_zeroed = true;
+            }
+            SplitK2 head{nullptr, nullptr, rounds, 0, (int)pairs};
+            kern<<<dim3(2u * (unsigned)(tiles - rem), 1, 1), kThreads, kSmemBytes, ctx->stream>>>(
+                tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, head,
+                ctx->dev_status);
+            SplitK2 tail{reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + 8192),
+                         reinterpret_cast<unsigned int *>(static_cast<char *>(ctx->scratch) + 4096), rps_t, tiles - rem,
+                         (int)pairs};
+            kern<<<dim3(2u * (unsigned)rem, 1, (unsigned)splits_t), kThreads, kSmemBytes, ctx->stream>>>(
+                tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, tail,
+                ctx->dev_status);
+            ctx->launches += 2;
+            SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+            return SHREWQ_OK;
+        }
+    }
     if (splits > 1) {
         // context scratch as in the single-CTA launcher: tile counters at 4096, partial sums from 8192
         const size_t part_bytes = (size_t)ctas * splits * kTokPair * kLanes * sizeof(float);
@@ -72,7 +107,6 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
         sk.partials = reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + 8192);
     }
     dim3 grid(2 * pairs, m_tiles, (unsigned)splits);
-    Operands2 ops{a.scales, a.bias, a.scales_up, a.bias_up};
     kern<<<grid, kThreads, kSmemBytes, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N,
                                                       (int)a.K, a.ldy, a.epilogue, sk, ctx->dev_status);
     ctx->launches += 1;

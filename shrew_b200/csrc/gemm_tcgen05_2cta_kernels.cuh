@@ -157,6 +157,11 @@ struct SplitK2 {
     float *partials;         // [tile][split][256 tokens][128 lanes] f32
     unsigned int *counters;  // one per CTA tile, zero between launches
     int rounds_per_split;
+    // Tile-list mode (pairs_total > 0): the grid is a 1-D list of pair tiles (blockIdx.x / 2) starting at
+    // tile_begin, channel pairs fastest, instead of the (channel pair, token tile) grid.  Lets one forward
+    // be issued as two launches with different split counts (full waves whole, the short last wave split).
+    int tile_begin;
+    int pairs_total;
 };
 
 // GATED: as in the single-CTA kernel, the 128 lanes of a CTA carry 64 rows of a gate matrix (tmap_w,
@@ -178,10 +183,15 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
-    const int pair = blockIdx.x >> 1;
-    const int n0 = pair * 2 * kChan + (int)rank * kChan;         // this CTA's first channel
-    const int m0 = blockIdx.y * kTokPair + (int)rank * kTokHalf;  // this CTA's first token (B half)
-    const int m0_pair = blockIdx.y * kTokPair;
+    int pair = blockIdx.x >> 1, m_tile = blockIdx.y;
+    if (sk.pairs_total > 0) {
+        const int t = sk.tile_begin + pair;
+        pair = t % sk.pairs_total;
+        m_tile = t / sk.pairs_total;
+    }
+    const int n0 = pair * 2 * kChan + (int)rank * kChan;      // this CTA's first channel
+    const int m0 = m_tile * kTokPair + (int)rank * kTokHalf;  // this CTA's first token (B half)
+    const int m0_pair = m_tile * kTokPair;
     const int rounds_total = (K + kBlockK * kSub - 1) / (kBlockK * kSub);
     const int r_begin = (int)blockIdx.z * sk.rounds_per_split;
     const int rounds = min(rounds_total - r_begin, sk.rounds_per_split);  // >= 1 by construction of the grid

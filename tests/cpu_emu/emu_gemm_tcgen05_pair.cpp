@@ -13,11 +13,11 @@ bool g_a_f16 = false;  // next launches use the variant with f16 weights in tens
 
 template <typename YT, bool GATED>
 int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
-        int epilogue, int splits, DeviceStatus *st);
+        int epilogue, int splits, int tile_list, DeviceStatus *st);
 
 template <typename YT, bool GATED, bool AF16>
 int run_as(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
-        int epilogue, int splits, DeviceStatus *st) {
+        int epilogue, int splits, int tile_list, DeviceStatus *st) {
     const uint32_t box_rows = GATED ? 64 : 128;
     const CUtensorMap tw{q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
     const CUtensorMap tw2{GATED ? q_up : q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
@@ -33,19 +33,34 @@ int run_as(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint
     const size_t ctas = (size_t)2 * pairs * m_tiles;
     std::vector<float> partials(splits > 1 ? ctas * splits * kTokPair * kLanes : 0, -12345.0f);
     std::vector<unsigned int> counters(ctas, 0u);
-    SplitK2 sk{splits > 1 ? partials.data() : nullptr, splits > 1 ? counters.data() : nullptr, rps};
-    emu::launch_cluster2(2 * pairs, m_tiles, (unsigned)splits, kThreads, kSmemBytes, [&] {
+    SplitK2 sk{splits > 1 ? partials.data() : nullptr, splits > 1 ? counters.data() : nullptr, rps, 0, 0};
+    auto body = [&] {
         linear_i8_tcgen05_pair_kernel<YT, GATED, AF16>(tw, tw2, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, sk, st);
-    });
+    };
+    if (tile_list >= 2) {
+        // the two-launch scheme of launch_pair for a short last wave, `tile_list` standing for the pair tiles
+        // that are resident at once: full waves as one launch of whole-K tiles, the rest split along K
+        const int tiles = (int)(pairs * m_tiles), rem = tiles % tile_list;
+        if (tiles <= tile_list || rem == 0) return -1;
+        sk = SplitK2{nullptr, nullptr, rounds, 0, (int)pairs};
+        emu::launch_cluster2(2u * (unsigned)(tiles - rem), 1, 1, kThreads, kSmemBytes, body);
+        sk = SplitK2{splits > 1 ? partials.data() : nullptr, splits > 1 ? counters.data() : nullptr, rps, tiles - rem, (int)pairs};
+        emu::launch_cluster2(2u * (unsigned)rem, 1, (unsigned)splits, kThreads, kSmemBytes, body);
+    } else if (tile_list == 1) {  // the 1-D tile list as one launch over all pair tiles
+        sk.pairs_total = (int)pairs;
+        emu::launch_cluster2(2 * pairs * m_tiles, 1, (unsigned)splits, kThreads, kSmemBytes, body);
+    } else {
+        emu::launch_cluster2(2 * pairs, m_tiles, (unsigned)splits, kThreads, kSmemBytes, body);
+    }
     for (unsigned int c : counters)
         if (c != 0) return -3;  // the kernel leaves the tile counters at zero for the next launch
     return 0;
 }
 template <typename YT, bool GATED>
 int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
-        int epilogue, int splits, DeviceStatus *st) {
-    return g_a_f16 ? run_as<YT, GATED, true>(q, q_up, ops, x, y, M, N, K, ldy, epilogue, splits, st)
-                   : run_as<YT, GATED, false>(q, q_up, ops, x, y, M, N, K, ldy, epilogue, splits, st);
+        int epilogue, int splits, int tile_list, DeviceStatus *st) {
+    return g_a_f16 ? run_as<YT, GATED, true>(q, q_up, ops, x, y, M, N, K, ldy, epilogue, splits, tile_list, st)
+                   : run_as<YT, GATED, false>(q, q_up, ops, x, y, M, N, K, ldy, epilogue, splits, tile_list, st);
 }
 }  // namespace
 
@@ -54,10 +69,11 @@ extern "C" int emu_last_a_format() { return emu::g_last_a_format.load(); }  // 0
 
 // q_up == NULL: plain forward; else silu(gate) * up.  splits: K splits (blockIdx.z).  Returns 0; -1 for a shape
 // the launcher refuses; -2 when a bounded wait of the kernel gave up; -3 when a tile counter was left set;
-// -4 when a rule of the model was violated.
+// -4 when a rule of the model was violated.  tile_list: 0 = (channel pair, token tile) grid; 1 = 1-D list of
+// pair tiles; >= 2 = two launches (see run_as).
 extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const float *bias, const int8_t *q_up,
                                      const float *scales_up, const float *bias_up, const void *x, void *y, int M, int N, int K,
-                                     size_t ldy, int epilogue, int y_bf16, int splits) {
+                                     size_t ldy, int epilogue, int y_bf16, int splits, int tile_list) {
     if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || M < 1) return -1;
     DeviceStatus st{0, 0, 0, 0};
     emu::g_failed = false;
@@ -65,11 +81,11 @@ extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const
     const uint16_t *xs = static_cast<const uint16_t *>(x);
     int rc;
     if (q_up) {
-        if (y_bf16) rc = run<__nv_bfloat16, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, &st);
-        else rc = run<float, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, &st);
+        if (y_bf16) rc = run<__nv_bfloat16, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, tile_list, &st);
+        else rc = run<float, true>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, tile_list, &st);
     } else {
-        if (y_bf16) rc = run<__nv_bfloat16, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, &st);
-        else rc = run<float, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, &st);
+        if (y_bf16) rc = run<__nv_bfloat16, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, tile_list, &st);
+        else rc = run<float, false>(q, q_up, ops, xs, y, M, N, K, ldy, epilogue, splits, tile_list, &st);
     }
     if (emu::g_failed) return -4;  // a rule of the model was violated (emu_fail_message)
     if (st.timeout_flag) return -2;

@@ -547,7 +547,7 @@ def test_f32_activations_through_two_tensor_core_passes(oracle, emu, emu_tc):
 @pytest.fixture(scope="module")
 def emu_pair():
     L = _build("emu_gemm_tcgen05_pair")
-    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci]
+    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci, _ci]
     return L
 
 
@@ -562,11 +562,11 @@ def test_cta_pair_forward_matches_oracle(oracle, emu_pair, M, N, K):
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
     ldy = N + 2
     y = np.full((M, ldy), 7.0, np.float32)
-    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, ldy, 1, 0, 1) == 0
+    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, ldy, 1, 0, 1, 0) == 0
     assert oracle.rel_err(y[:, :N], ref) < 2e-6
     assert np.all(y[:, N:] == 7.0)
     y16 = np.full((M, N), 0x4100, np.uint16)
-    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), None, None, None, None, _p(xa), _p(y16), M, N, K, N, 0, 1, 1) == 0
+    assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), None, None, None, None, _p(xa), _p(y16), M, N, K, N, 0, 1, 1, 0) == 0
     ref_nb = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, None, x)
     assert oracle.rel_err((y16.astype(np.uint32) << 16).view(np.float32), ref_nb) < 1e-2
 
@@ -592,12 +592,45 @@ def test_cta_pair_f16_weights_give_the_same_bits(emu_pair, M, N, K, splits, gate
         emu_pair.emu_set_a_f16(on)
         try:
             y = np.full((M, N), 7.0, np.float32)
-            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), *up, _p(xa), _p(y), M, N, K, N, 0, 0, splits) == 0
+            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), *up, _p(xa), _p(y), M, N, K, N, 0, 0, splits, 0) == 0
             assert emu_pair.emu_last_a_format() == fmt
         finally:
             emu_pair.emu_set_a_f16(0)
         ys.append(y)
     np.testing.assert_array_equal(ys[0], ys[1])
+
+
+@pytest.mark.parametrize("gated", [False, True])
+def test_cta_pair_tile_list_and_tail_split(oracle, emu_pair, gated):
+    # SHREWQ_TC_TAILSPLIT on the pair kernel (not yet run on a GPU): the 1-D list of pair tiles as one launch,
+    # then the two-launch scheme with 4 (5) pair tiles "resident at once": 4 (5) whole-K tiles in the first
+    # launch, the remaining 2 (1) split 2 (3) ways along K in the second
+    M, N, K = 300, (300 if gated else 600), 2048           # 3 channel pairs x 2 token tiles = 6 pair tiles
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, 77)
+    qa, xa = _aligned(q.shape, np.int8), _aligned(x_bits.shape, np.uint16)
+    qa[...] = q
+    xa[...] = x_bits
+    s32 = scales.astype(np.float32)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
+    up = (None, None, None)
+    if gated:
+        rng = np.random.default_rng(5)
+        qu = _aligned(q.shape, np.int8)
+        qu[...] = rng.integers(-127, 128, size=q.shape).astype(np.int8)
+        su = rng.random(N) * 1e-2 + 1e-4
+        su32 = su.astype(np.float32)
+        up = (_p(qu), _p(su32), None)
+        u = oracle.np_linear_forward(qu, su, oracle.PER_CHANNEL, None, x).astype(np.float64)
+        g = ref.astype(np.float64)
+        ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    for tile_list, splits in ((1, 1), (1, 2), (4, 2), (5, 3)):
+        y = np.full((M, N), 7.0, np.float32)
+        rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), *up, _p(xa), _p(y), M, N, K, N, 0, 0, splits, tile_list)
+        if rc == -4:
+            emu_pair.emu_fail_message.restype = ctypes.c_char_p
+            raise AssertionError(emu_pair.emu_fail_message().decode())
+        assert rc == 0
+        assert oracle.rel_err(y, ref) < (1e-5 if gated else 2e-6), (tile_list, splits)
 
 
 # ---- bounded waits: a wait that runs out must end the kernel, not hang it -------------------------------
@@ -647,7 +680,7 @@ def test_tcgen05_wait_that_runs_out_ends_the_kernel(tok, M, N, K, splits, gated,
 @pytest.mark.timeout(300)
 def test_cta_pair_wait_that_runs_out_ends_both_blocks():
     L = _build_short_waits("emu_gemm_tcgen05_pair")
-    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci]
+    L.emu_gemm_tcgen05_pair.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci, _ci]
     L.emu_drop_tma.argtypes = [_ci]
     q, scales, bias, x_bits, x = _tc_case(256, 256, 1024, 1)
     qa = _aligned(q.shape, np.int8)
@@ -659,7 +692,7 @@ def test_cta_pair_wait_that_runs_out_ends_both_blocks():
     for drop in (0, 1, 9, 14):   # a code load or an activation load, of the leader or of the peer
         L.emu_drop_tma(drop)
         try:
-            rc = L.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 256, 256, 1024, 256, 0, 0, 1)
+            rc = L.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 256, 256, 1024, 256, 0, 0, 1, 0)
         finally:
             L.emu_drop_tma(-1)
         assert rc == -2, drop
@@ -825,7 +858,7 @@ def test_cta_pair_with_loads_landing_late_and_out_of_order(oracle, emu_pair):
         y = np.zeros((300, 260), np.float32)
         emu_pair.emu_tma_async(seed, one_in)
         try:
-            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 300, 260, 2048, 260, 0, 0, 1) == 0
+            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), 300, 260, 2048, 260, 0, 0, 1, 0) == 0
         finally:
             emu_pair.emu_tma_async(0, 0)
         assert oracle.rel_err(y, ref) < 2e-6
@@ -849,7 +882,7 @@ def test_cta_pair_gate_up_tile(oracle, emu_pair, M, N, K):
     xa[...] = x_bits
     sg32, su32 = sg.astype(np.float32), su.astype(np.float32)
     y = np.full((M, N), 7.0, np.float32)
-    rc = emu_pair.emu_gemm_tcgen05_pair(_p(qga), _p(sg32), _p(bg), _p(qua), _p(su32), _p(bu), _p(xa), _p(y), M, N, K, N, 0, 0, 1)
+    rc = emu_pair.emu_gemm_tcgen05_pair(_p(qga), _p(sg32), _p(bg), _p(qua), _p(su32), _p(bu), _p(xa), _p(y), M, N, K, N, 0, 0, 1, 0)
     assert rc == 0
     assert oracle.rel_err(y, ref) < 1e-5
 
@@ -870,12 +903,12 @@ def test_cta_pair_split_k(oracle, emu_pair, M, N, K, splits, gated):
         qu[...] = rng.integers(-127, 128, size=q.shape)
         su = rng.random(N) * 1e-2 + 1e-4
         su32 = su.astype(np.float32)
-        rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(qu), _p(su32), None, _p(xa), _p(y), M, N, K, N, 0, 0, splits)
+        rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), _p(qu), _p(su32), None, _p(xa), _p(y), M, N, K, N, 0, 0, splits, 0)
         g = oracle.np_linear_forward(q, scales, 1, bias, x).astype(np.float64)
         u = oracle.np_linear_forward(np.array(qu), su, 1, None, x).astype(np.float64)
         ref, tol = (g / (1.0 + np.exp(-g)) * u).astype(np.float32), 1e-5
     else:
-        rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, N, 1, 0, splits)
+        rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, N, 1, 0, splits, 0)
         ref, tol = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True), 2e-6
     assert rc == 0
     assert oracle.rel_err(y, ref) < tol
