@@ -11,9 +11,10 @@ template <int MT, int R, typename XT, typename YT, bool GATED>
 void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     constexpr int NR = GATED ? R / 2 : R;
     const unsigned grid = (unsigned)((a.N + NR - 1) / NR);
-    // SHREWQ_GEMV_PDL=1 launches with programmatic stream serialization so that back-to-back
-    // GEMVs overlap launch latency and prologue.  Built, compiled, NOT yet run on a GPU: off
-    // unless the variable is set.
+    // SHREWQ_GEMV_PDL=1 launches the PDL variant of the kernel with programmatic stream
+    // serialization: back-to-back GEMVs overlap launch latency, prologue and the first weight
+    // loads with the tail of the kernel before.  Built, compiled, NOT yet run on a GPU: off unless
+    // the variable is set (the default instantiations are the validated kernel, unchanged).
     static const bool pdl = getenv("SHREWQ_GEMV_PDL") && atoi(getenv("SHREWQ_GEMV_PDL")) != 0;
     if (pdl) {
         cudaLaunchConfig_t cfg = {};
@@ -26,14 +27,14 @@ void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaLaunchKernelEx(&cfg, gemv_i8_kernel<MT, R, XT, YT, GATED>, a.q, a.scales, a.bias, a.q_up, a.scales_up,
+        cudaLaunchKernelEx(&cfg, gemv_i8_kernel<MT, R, XT, YT, GATED, true>, a.q, a.scales, a.bias, a.q_up, a.scales_up,
                            a.bias_up, static_cast<const XT *>(a.x), static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N,
-                           (int)a.K, a.ldy, a.epilogue, 1);
+                           (int)a.K, a.ldy, a.epilogue);
         return;
     }
     gemv_i8_kernel<MT, R, XT, YT, GATED><<<grid, kThreads, 0, ctx->stream>>>(
         a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const XT *>(a.x),
-        static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, 0);
+        static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
 }
 
 template <typename XT, typename YT, bool GATED>

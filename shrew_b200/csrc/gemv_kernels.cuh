@@ -73,17 +73,19 @@ __device__ __forceinline__ float silu(float g) { return g / (1.0f + __expf(-g));
 
 // MT: tokens handled (M padded up to MT, extra tokens masked); R: output rows per CTA.
 // GATED: rows come in pairs (gate row n from q, up row n from q_up); R counts pairs * 2.
-template <int MT, int R, typename XT, typename YT, bool GATED>
+// PDL (programmatic dependent launch, opt-in): the kernel lets the next kernel of the stream start at
+// once, fetches its first weights, and only then waits for the previous kernel, whose output its
+// activations may be; the weights never depend on an earlier kernel.  Back-to-back GEMVs thus keep
+// the weight stream going across the kernel boundary.
+template <int MT, int R, typename XT, typename YT, bool GATED, bool PDL = false>
 __global__ void __launch_bounds__(kThreads)
 gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                const float *__restrict__ bias, const int8_t *__restrict__ q_up,
                const float *__restrict__ scales_up, const float *__restrict__ bias_up,
                const XT *__restrict__ x, YT *__restrict__ y, Dests extra, int M, int N, int K,
-               size_t ldy, int epilogue, int pdl) {
+               size_t ldy, int epilogue) {
     constexpr int NR = GATED ? R / 2 : R;  // distinct output columns per CTA
-    // Programmatic dependent launch (opt-in): let the next kernel of the stream start its
-    // prologue while this one runs ...
-    if (pdl) pdl_launch_dependents();
+    if constexpr (PDL) pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * NR;
     const int chunks = K >> 4;
@@ -103,14 +105,26 @@ gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
 #pragma unroll
         for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
 
-    // ... and do not touch the activations (or write the output) before the previous kernel
-    // of the stream, which may have produced them, has completed
-    if (pdl) pdl_wait();
-
-    for (int c = warp * 32 + lane; c < chunks; c += kWarps * 32) {
-        uint4 wv[R];
+    int c = warp * 32 + lane;
+    uint4 wv[R];
+    bool have = false;  // wv already holds the weights of chunk c
+    if constexpr (PDL) {
+        have = c < chunks;
+        if (have) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) wv[r] = ld_stream_16(rowp[r] + ((size_t)c << 4));
+            for (int r = 0; r < R; ++r) wv[r] = ld_stream_16(rowp[r] + ((size_t)c << 4));
+        }
+        // neither read the activations nor write the output before the previous kernel of the
+        // stream, which may have produced or may still read them, has completed
+        pdl_wait();
+    }
+
+    for (; c < chunks; c += kWarps * 32) {
+        if (!have) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) wv[r] = ld_stream_16(rowp[r] + ((size_t)c << 4));
+        }
+        have = false;
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             float xf[16];

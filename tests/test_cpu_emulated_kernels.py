@@ -778,6 +778,23 @@ def test_gemv_matches_oracle(oracle, emu_cc, M, x_bf16):
     assert oracle.rel_err(y[:, :N], ref) < 2e-6 and np.all(y[:, N:] == 7.0)
 
 
+@pytest.mark.parametrize("M,K", [(1, 16 * 296), (4, 16 * 130), (8, 16 * 128), (2, 16 * 5)])
+def test_gemv_pdl_variant_gives_the_same_bits(oracle, emu_cc, M, K):
+    # SHREWQ_GEMV_PDL (not yet run on a GPU): the first weights are fetched before the wait for the
+    # previous kernel, the remaining chunks in the usual loop; same operations in the same order
+    rng = np.random.default_rng(K)
+    N = 9
+    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    scales = rng.random(N) * 1e-2 + 1e-4
+    bits, xb = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    ys = [_cc_forward(emu_cc, 0, q, scales, None, bits, 1, 0, pdl=p) for p in (0, 1)]
+    np.testing.assert_array_equal(ys[0], ys[1])
+    assert oracle.rel_err(ys[1], oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, None, xb)) < 2e-6
+    qu = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    yg = [_cc_forward(emu_cc, 0, q, scales, None, bits, 1, 0, up=(qu, scales, None), pdl=p) for p in (0, 1)]
+    np.testing.assert_array_equal(yg[0], yg[1])
+
+
 def test_gemv_gate_up_and_peer_destinations(oracle, emu_cc):
     rng = np.random.default_rng(4)
     M, N, K = 3, 50, 256
