@@ -93,6 +93,24 @@ SHREWQ_API const char *shrewq_version(void);
  */
 SHREWQ_API int shrewq_quantize_f32(shrewq_ctx *ctx, const float *w_dev, size_t rows, size_t cols,
                         int granularity, int8_t *q_dev, double *scales_dev);
+/*
+ * quantize_named_parameters (quantize.rs:500-516: every parameter of rank >= 2, one after the other) as
+ * ONE call for many F32 tensors: `items` is a HOST array of n_items descriptors with the arguments of
+ * shrewq_quantize_f32; all tensors take the same granularity.  The tensors are covered by a few launches
+ * in all (one per 64 tensors per-channel, three per-tensor) instead of one to three each, which is what
+ * a model of many small matrices needs; results are the same bits as shrewq_quantize_f32 gives.  Tuned
+ * for small tensors (a warp per row): tensors of many MB are better quantized one by one.  No device
+ * memory is allocated beyond the context's scratch.  Built and checked on the CPU model; not yet run on
+ * a GPU.
+ */
+typedef struct shrewq_quant_item {
+    const float *w_dev;
+    size_t rows, cols;
+    int8_t *q_dev;
+    double *scales_dev;
+} shrewq_quant_item;
+SHREWQ_API int shrewq_quantize_f32_batch(shrewq_ctx *ctx, const shrewq_quant_item *items, size_t n_items,
+                              int granularity);
 /* Same with host buffers: what `quantize_tensor(&tensor, &cfg)` does for a caller whose
  * tensor lives on the host (upload, quantize on the GPU, download codes and scales). */
 SHREWQ_API int shrewq_quantize_f32_host(shrewq_ctx *ctx, const float *w_host, size_t rows, size_t cols,

@@ -17,4 +17,5 @@ from .quantize import (  # noqa: F401
     quantization_stats,
     quantize_named_parameters,
     quantize_tensor,
+    quantize_tensors,
 )

@@ -30,6 +30,7 @@ SIGNATURES = {
     "shrewq_last_error": (ctypes.c_char_p, [_vp]),
     "shrewq_version": (ctypes.c_char_p, []),
     "shrewq_quantize_f32": (_ci, [_vp, _vp, _sz, _sz, _ci, _vp, _vp]),
+    "shrewq_quantize_f32_batch": (_ci, [_vp, _vp, _sz, _ci]),
     "shrewq_quantize_f32_host": (_ci, [_vp, _vp, _sz, _sz, _ci, _vp, _vp]),
     "shrewq_dequantize": (_ci, [_vp, _vp, _vp, _sz, _sz, _ci, _ci, _vp]),
     "shrewq_absmax_f32": (_ci, [_vp, _vp, _sz, _vp]),
@@ -56,6 +57,12 @@ SIGNATURES = {
     "shrewq_plan_forward": (_ci, [_sz, _sz, _sz, _ci, _ci, _ci, ctypes.c_char_p, _sz, ctypes.POINTER(_ci), ctypes.POINTER(_ci),
                                  ctypes.POINTER(_ci), ctypes.POINTER(_ci), ctypes.POINTER(_ci)]),
 }
+
+class QuantItem(ctypes.Structure):
+    """shrewq_quant_item: one tensor of shrewq_quantize_f32_batch."""
+    _fields_ = [("w_dev", ctypes.c_void_p), ("rows", ctypes.c_size_t), ("cols", ctypes.c_size_t),
+                ("q_dev", ctypes.c_void_p), ("scales_dev", ctypes.c_void_p)]
+
 
 _lib = None
 

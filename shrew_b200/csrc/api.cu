@@ -206,6 +206,29 @@ int shrewq_quantize_f32(shrewq_ctx *ctx, const float *w_dev, size_t rows, size_t
     return launch_quantize(ctx, w_dev, rows, cols, granularity, q_dev, scales_dev);
 }
 
+int shrewq_quantize_f32_batch(shrewq_ctx *ctx, const shrewq_quant_item *items, size_t n_items, int granularity) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "quantize_batch: ctx is NULL");
+    int rc = check_gran(ctx, granularity, "quantize_batch");
+    if (rc != SHREWQ_OK) return rc;
+    if (n_items == 0) return SHREWQ_OK;
+    if (!items) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_batch: items is NULL");
+    for (size_t i = 0; i < n_items; ++i) {
+        const shrewq_quant_item &t = items[i];
+        const size_t n = t.rows * t.cols;
+        if (t.cols != 0 && n / t.cols != t.rows)
+            return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_batch: item %zu: rows*cols overflows", i);
+        if (!t.scales_dev && (granularity == SHREWQ_PER_TENSOR || t.rows > 0))
+            return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_batch: item %zu: scales_dev is NULL", i);
+        if (n > 0 && (!t.w_dev || !t.q_dev))
+            return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_batch: item %zu: w_dev / q_dev is NULL", i);
+        if ((reinterpret_cast<uintptr_t>(t.w_dev) & 3) || (reinterpret_cast<uintptr_t>(t.scales_dev) & 7))
+            return set_err(ctx, SHREWQ_ERR_INVALID_ARG,
+                           "quantize_batch: item %zu: w_dev must be 4-byte and scales_dev 8-byte aligned", i);
+    }
+    if ((rc = bind(ctx)) != SHREWQ_OK) return rc;
+    return launch_quantize_batch(ctx, items, n_items, granularity);
+}
+
 int shrewq_quantize_f32_host(shrewq_ctx *ctx, const float *w_host, size_t rows, size_t cols, int granularity,
                              int8_t *q_host, double *scales_host) {
     if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "quantize_host: ctx is NULL");

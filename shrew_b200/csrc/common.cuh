@@ -77,6 +77,7 @@ int ensure_stage(shrewq_ctx *ctx, size_t dev_bytes, size_t pinned_bytes);
     } while (0)
 
 // ---- launchers implemented in the kernel translation units -------------------------
+int launch_quantize_batch(shrewq_ctx *ctx, const shrewq_quant_item *items, size_t n_items, int granularity);
 int launch_quantize(shrewq_ctx *ctx, const float *w, size_t rows, size_t cols, int granularity,
                     int8_t *q, double *scales);
 int launch_absmax(shrewq_ctx *ctx, const float *w, size_t n, float *amax_dev);

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import enum
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
@@ -206,6 +207,42 @@ def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTenso
                                             _ptr(q), _ptr(scales), _ptr(zps))
     _lib.check(rc, dev.handle)
     return QuantizedTensor(q, scales, shape, tensor.dtype, config, zps if config.mode is QuantMode.Asymmetric else None)
+
+
+def quantize_tensors(tensors: Sequence[torch.Tensor], config: QuantConfig) -> List[QuantizedTensor]:
+    """`quantize_tensor` for many tensors in a few launches in all (shrewq_quantize_f32_batch): what a model
+    of many small matrices needs, where a launch per tensor costs more than the data.  F32 CUDA tensors on
+    one device, INT8 symmetric; same codes and scales as `quantize_tensor`.  Not yet run on a GPU."""
+    if not tensors:
+        return []
+    if not config._is_int8_symmetric():
+        raise ShrewError(_lib.ERR_UNSUPPORTED, "quantize_tensors: INT8 symmetric only")
+    dev = Device.get(tensors[0].device)
+    items = (_lib.QuantItem * len(tensors))()
+    out, keep = [], []
+    per_tensor_group: List[int] = []     # rank-0 tensors fall back to per-tensor (quantize.rs:276-278)
+    for i, t in enumerate(tensors):
+        if t.dtype is not torch.float32 or t.device != tensors[0].device:
+            raise ShrewError(_lib.ERR_UNSUPPORTED, "quantize_tensors: f32 tensors on one CUDA device")
+        w = t.contiguous()
+        shape = list(w.shape)
+        rows, cols = _rows_cols(shape)
+        gran = config.granularity if shape else QuantGranularity.PerTensor
+        if gran is not config.granularity:
+            per_tensor_group.append(i)
+        q = torch.empty(w.numel(), dtype=torch.int8, device=w.device)
+        scales = torch.empty(rows if gran is QuantGranularity.PerChannel else 1, dtype=torch.float64, device=w.device)
+        items[i] = _lib.QuantItem(_ptr(w), rows, cols, _ptr(q), _ptr(scales))
+        keep.append(w)
+        out.append(QuantizedTensor(q, scales, shape, t.dtype, config))
+    dev.bind_stream()
+    main = [i for i in range(len(tensors)) if i not in per_tensor_group]
+    for idx, gran in ((main, config.granularity), (per_tensor_group, QuantGranularity.PerTensor)):
+        if idx:
+            sub = (_lib.QuantItem * len(idx))(*[items[i] for i in idx])
+            _lib.check(_lib.lib().shrewq_quantize_f32_batch(dev.handle, ctypes.cast(sub, ctypes.c_void_p), len(idx), gran.value),
+                       dev.handle)
+    return out
 
 
 def absmax(tensor: torch.Tensor) -> torch.Tensor:
@@ -427,11 +464,12 @@ class QuantizedLinear:
 def quantize_named_parameters(module, config: QuantConfig) -> List[Tuple[str, QuantizedTensor]]:
     """Every parameter of rank >= 2 is quantized — including a Linear's [1,out] bias, which
     is rank 2 in Shrew (quantize.rs:507-513, :760-766)."""
-    out = []
-    for name, t in module.named_parameters():
-        if t.dim() >= 2:
-            out.append((name, quantize_tensor(t.detach(), config)))
-    return out
+    params = [(name, t.detach()) for name, t in module.named_parameters() if t.dim() >= 2]
+    # SHREWQ_BATCH_QUANTIZE=1: all tensors in a few launches (quantize_tensors; not yet run on a GPU)
+    if (os.environ.get("SHREWQ_BATCH_QUANTIZE", "0") == "1" and config._is_int8_symmetric() and params
+            and all(t.dtype is torch.float32 for _, t in params)):
+        return list(zip([n for n, _ in params], quantize_tensors([t for _, t in params], config)))
+    return [(name, quantize_tensor(t, config)) for name, t in params]
 
 
 @dataclass

@@ -3,6 +3,7 @@
 #include "cuda_shim.h"
 struct uint2 { unsigned x, y; };
 #include "../../shrew_b200/csrc/quantize_kernels.cuh"
+#include "../../shrew_b200/csrc/quantize_batch_kernels.cuh"
 
 using namespace shrewq;
 
@@ -83,5 +84,40 @@ extern "C" int emu_dequantize(const int8_t *q, const double *scales, size_t rows
 // f32 activations -> bf16 hi + bf16 lo (the tensor-core route for f32 inputs)
 extern "C" int emu_split_f32(const float *x, size_t n, unsigned grid, void *hi, void *lo) {
     if (n) emu::launch(grid, 256, [&] { split_f32_kernel(x, n, static_cast<__nv_bfloat16 *>(hi), static_cast<__nv_bfloat16 *>(lo)); });
+    return 0;
+}
+
+// Many tensors per launch (launch_quantize_batch in shrew_b200/csrc/quantize_batch.cu): the same table,
+// chunking and kernel sequence; `grid` stands for the launcher's block count (fewer blocks than work
+// units makes the unit loop run).  items: n x {w, rows, cols, q, scales} as the C ABI's shrewq_quant_item.
+struct EmuQuantItem {
+    const float *w;
+    size_t rows, cols;
+    int8_t *q;
+    double *scales;
+};
+extern "C" int emu_quantize_batch(const EmuQuantItem *items, size_t n_items, int per_channel, unsigned grid) {
+    for (size_t first = 0; first < n_items; first += kBatchMax) {
+        BatchTable t{};
+        t.n = (int)std::min<size_t>(n_items - first, kBatchMax);
+        unsigned long long units = 0;
+        for (int i = 0; i < t.n; ++i) {
+            const EmuQuantItem &s = items[first + i];
+            t.it[i] = BatchItem{s.w, s.q, s.scales, s.rows, s.cols, (unsigned int)units, 0};
+            const unsigned long long n = (unsigned long long)s.rows * s.cols;
+            units += per_channel ? (unsigned long long)s.rows : (n + kBatchSegment - 1) / kBatchSegment;
+        }
+        t.total_units = (unsigned int)units;
+        if (per_channel) {
+            if (units > 0) emu::launch(grid, kBatchWarps * 32, [&] { quantize_batch_rows_kernel(t); });
+        } else {
+            alignas(16) unsigned char scratch[4096] = {0};
+            unsigned int *amax_bits = reinterpret_cast<unsigned int *>(scratch);
+            TensorParams *tp = reinterpret_cast<TensorParams *>(scratch + 256);
+            if (units > 0) emu::launch(grid, kBatchWarps * 32, [&] { absmax_batch_kernel(t, amax_bits); });
+            emu::launch(1, kBatchMax, [&] { finalize_batch_kernel(t, amax_bits, tp); });
+            if (units > 0) emu::launch(grid, kBatchWarps * 32, [&] { quantize_batch_flat_kernel(t, tp); });
+        }
+    }
     return 0;
 }

@@ -112,6 +112,57 @@ def test_golden_per_tensor_chain(emu, case, grid):
     assert s.tobytes() == case["scales"].tobytes()
 
 
+class _EmuQuantItem(ctypes.Structure):
+    _fields_ = [("w", ctypes.c_void_p), ("rows", ctypes.c_size_t), ("cols", ctypes.c_size_t), ("q", ctypes.c_void_p),
+                ("scales", ctypes.c_void_p)]
+
+
+def _quantize_batch(emu, tensors, per_channel, grid, misalign=False):
+    emu.emu_quantize_batch.argtypes = [_vp, _sz, _ci, _cu]
+    items = (_EmuQuantItem * len(tensors))()
+    bufs = []
+    for i, w in enumerate(tensors):
+        rows, cols = _rows_cols(w.shape)
+        pad = 1 if misalign and i % 2 else 0              # every other tensor off the 16-byte boundary: scalar path
+        wa = _aligned((w.size + pad,), np.float32)[pad:]
+        wa[...] = w.reshape(-1)
+        q = _aligned((w.size + pad,), np.int8)[pad:]
+        q[...] = 99
+        s = np.full(rows if per_channel else 1, -1.0)
+        items[i] = _EmuQuantItem(wa.ctypes.data, rows, cols, q.ctypes.data, s.ctypes.data)
+        bufs.append((wa, q, s))
+    assert emu.emu_quantize_batch(ctypes.cast(items, ctypes.c_void_p), len(tensors), int(per_channel), grid) == 0
+    return [(q.reshape(w.shape), s) for (wa, q, s), w in zip(bufs, tensors)]
+
+
+@pytest.mark.parametrize("per_channel", [1, 0], ids=["per_channel", "per_tensor"])
+def test_batched_quantizer_on_the_golden_vectors(emu, per_channel):
+    # every golden tensor of the granularity, all in one table (not yet run on a GPU)
+    cases = [c for c in GOLDEN if len(c["shape"]) >= 1 and c["granularity"] == per_channel]
+    assert len(cases) >= 5
+    for grid in (1, 7):
+        got = _quantize_batch(emu, [c["data"] for c in cases], per_channel, grid)
+        for c, (q, s) in zip(cases, got):
+            np.testing.assert_array_equal(q, c["codes"], err_msg=c["name"])
+            assert s.tobytes() == c["scales"].tobytes(), c["name"]
+
+
+@pytest.mark.parametrize("per_channel", [1, 0], ids=["per_channel", "per_tensor"])
+def test_batched_quantizer_matches_oracle_on_a_model(oracle, emu, per_channel):
+    # a small GPT's parameter list (scaled down), empty and ragged tensors, special values, more tensors
+    # than one table holds (64), odd alignments
+    rng = np.random.default_rng(3)
+    shapes = [(64, 64)] * 4 + [(256, 64), (64, 256), (1, 64), (0, 5), (3, 0), (1, 1), (5, 3), (2, 4100), (50, 33)]
+    tensors = [_special_matrix(r, c, i) if r * c else np.zeros((r, c), np.float32) for i, (r, c) in enumerate(shapes)]
+    tensors += [(rng.standard_normal((3, 20)) * 10.0 ** rng.integers(-38, 38)).astype(np.float32) for _ in range(70)]
+    for misalign in (False, True):
+        got = _quantize_batch(emu, tensors, per_channel, 5, misalign=misalign)
+        for i, (w, (q, s)) in enumerate(zip(tensors, got)):
+            rq, rs = oracle.quantize_f32(w, oracle.PER_CHANNEL if per_channel else oracle.PER_TENSOR)
+            np.testing.assert_array_equal(q, rq, err_msg=f"tensor {i} shape {w.shape}")
+            assert s.tobytes() == rs.tobytes(), f"tensor {i} shape {w.shape}"
+
+
 def _special_matrix(rows, cols, seed, scale=1.0):
     rng = np.random.default_rng(seed)
     w = (rng.standard_normal((rows, cols)) * scale).astype(np.float32)

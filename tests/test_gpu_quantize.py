@@ -172,3 +172,35 @@ def test_per_tensor_quantization_of_row_shards(oracle, rows, cols, split):
     np.testing.assert_array_equal(q, q_ref)
     for g in got:
         assert g.scales.cpu().numpy().tobytes() == s_ref.tobytes()
+
+
+@pytest.mark.skipif(__import__("os").environ.get("SHREWQ_TEST_UNVALIDATED", "0") != "1",
+                    reason="kernels built and checked on the CPU model but not yet run on a GPU; set SHREWQ_TEST_UNVALIDATED=1")
+@pytest.mark.parametrize("gran", [0, 1])
+def test_many_tensors_per_launch_match_one_by_one(oracle, gran, monkeypatch):
+    # the parameter list of config 2's model shape (4 blocks of 256-wide layers, scaled-down head), plus
+    # ragged, empty and rank-0 tensors, and more tensors than one table holds
+    from shrew_b200 import Linear, QuantConfig, quantize_named_parameters, quantize_tensor, quantize_tensors
+    cfg = QuantConfig.int8_per_channel() if gran == 1 else QuantConfig.int8()
+    rng = np.random.default_rng(gran)
+    shapes = ([(256, 256)] * 4 + [(1024, 256), (1, 1024), (256, 1024), (1, 256)]) * 4 + [(5025, 256), (7, 5), (0, 4), (3, 0), (), (2, 3, 4)]
+    shapes += [(3, 20)] * 70
+    ws = [torch.from_numpy(np.asarray(rng.standard_normal(s) * 0.02, dtype=np.float32)).cuda() for s in shapes]
+    ws[0][0, 0] = float("nan")
+    got = quantize_tensors(ws, cfg)
+    torch.cuda.synchronize()
+    for w, g in zip(ws, got):
+        one = quantize_tensor(w, cfg)
+        assert torch.equal(g.data, one.data) and g.shape == one.shape, tuple(w.shape)
+        assert g.scales.cpu().numpy().tobytes() == one.scales.cpu().numpy().tobytes(), tuple(w.shape)
+    q_ref, s_ref = oracle.np_quantize_f32(ws[4].cpu().numpy(), gran)
+    np.testing.assert_array_equal(got[4].data.cpu().numpy().reshape(1024, 256), q_ref)
+    assert got[4].scales.cpu().numpy().tobytes() == s_ref.tobytes()
+    # and through the model-level helper
+    lin = Linear(ws[1], torch.randn(256, device="cuda"))
+    monkeypatch.setenv("SHREWQ_BATCH_QUANTIZE", "1")
+    a = quantize_named_parameters(lin, cfg)
+    monkeypatch.setenv("SHREWQ_BATCH_QUANTIZE", "0")
+    b = quantize_named_parameters(lin, cfg)
+    assert [n for n, _ in a] == [n for n, _ in b] and all(torch.equal(x.data, y.data) and torch.equal(x.scales, y.scales)
+                                                          for (_, x), (_, y) in zip(a, b))
