@@ -130,6 +130,22 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
         n = n < N ? n : N - 1;  // clamp: duplicates are computed and dropped
         wrow[nb] = ((GATED && nb == 1) ? q_up : q) + (size_t)n * wrow_bytes + 16 * t;
     }
+    // XS: the first kPrefetch k-blocks of this warp's codes are requested BEFORE the activations are
+    // staged: the weights do not depend on them, and the staging (two dependent passes over x with
+    // block-wide barriers, ~2 us) would otherwise delay the start of the weight stream, which is the
+    // whole kernel at batch 1-4.
+    constexpr int kPrefetch = XS ? 4 : 0;
+    uint4 pre[kPrefetch > 0 ? kPrefetch : 1][NB];
+    if constexpr (XS) {
+#pragma unroll
+        for (int p = 0; p < kPrefetch; ++p) {
+            const int kb = warp + p * kWarps;
+            if (kb < kblocks) {
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) pre[p][nb] = ld_stream_16(wrow[nb] + ((size_t)kb << 6));
+            }
+        }
+    }
     // the activation rows this lane reads for each token tile (null = padding row)
     const uint16_t *xlo[MT16], *xhi[MT16];
     __shared__ int s_shift[kStageMaxTokens];
@@ -204,13 +220,10 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
 #pragma unroll
             for (int r = 0; r < 4; ++r) acc[mt][nb][r] = 0.0f;
 
-#pragma unroll 2
-    for (int kb = warp; kb < kblocks; kb += kWarps) {
+    // one k-block: wv = this lane's 16 bytes of codes per channel block (64 bytes per row and k-block,
+    // INT8 or packed INT4 alike)
+    auto k_block = [&](int kb, const uint4 (&wv)[NB]) {
         const size_t koff = (size_t)kb * (4 * kRun);              // activations: elements
-        const size_t woff = W4 ? (size_t)kb << 6 : koff;            // codes: bytes (64 per k-block either way)
-        uint4 wv[NB];
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) wv[nb] = ld_stream_16(wrow[nb] + woff);
         // kRun activations = kXWords packed words per row
         uint32_t al[MT16][kXWords], ah[MT16][kXWords];
 #pragma unroll
@@ -256,6 +269,21 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
                 }
             }
         }
+    };
+
+    if constexpr (XS) {
+#pragma unroll
+        for (int p = 0; p < kPrefetch; ++p) {
+            const int kb = warp + p * kWarps;
+            if (kb < kblocks) k_block(kb, pre[p]);
+        }
+    }
+#pragma unroll 2
+    for (int kb = warp + kPrefetch * kWarps; kb < kblocks; kb += kWarps) {
+        uint4 wv[NB];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) wv[nb] = ld_stream_16(wrow[nb] + ((size_t)kb << 6));
+        k_block(kb, wv);
     }
 
     // sum the 8 warps' accumulators through shared memory
