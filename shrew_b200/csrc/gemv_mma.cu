@@ -23,6 +23,25 @@ void launch_staged(shrewq_ctx *ctx, const ForwardArgs &a) {
     constexpr int kChan = GATED ? 8 : 8 * NB;
     const unsigned grid = (unsigned)((a.N + kChan - 1) / kChan);
     const size_t smem = a.M * a.K * sizeof(uint16_t);  // <= kStageMaxBytes: below the 48 KB that need no opt-in
+    // SHREWQ_GEMV_PDL=1 (as for the CUDA-core GEMV): programmatic stream serialization, so that a chain
+    // of batch-1 forwards keeps the weight stream going across kernel boundaries
+    const char *e = getenv("SHREWQ_GEMV_PDL");
+    if (e && atoi(e) != 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, gemv_mma_kernel<1, YT, GATED, true, true>, a.q, a.scales, a.bias, a.q_up, a.scales_up,
+                           a.bias_up, static_cast<const uint16_t *>(a.x), static_cast<const int *>(nullptr),
+                           static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
+        return;
+    }
     gemv_mma_kernel<1, YT, GATED, true, true><<<grid, kThreads, smem, ctx->stream>>>(
         a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const uint16_t *>(a.x), nullptr,
         static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);

@@ -137,6 +137,8 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
     constexpr int kPrefetch = XS ? 4 : 0;
     uint4 pre[kPrefetch > 0 ? kPrefetch : 1][NB];
     if constexpr (XS) {
+        // (both calls do nothing unless the launch asked for programmatic stream serialization)
+        pdl_launch_dependents();  // the next kernel of the stream may start its own prologue
 #pragma unroll
         for (int p = 0; p < kPrefetch; ++p) {
             const int kb = warp + p * kWarps;
@@ -145,6 +147,9 @@ gemv_mma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, 
                 for (int nb = 0; nb < NB; ++nb) pre[p][nb] = ld_stream_16(wrow[nb] + ((size_t)kb << 6));
             }
         }
+        // the activations may be the previous kernel's output, and the output buffer may still be
+        // read by it: wait for it here, with this kernel's first weights already on their way
+        pdl_wait();
     }
     // the activation rows this lane reads for each token tile (null = padding row)
     const uint16_t *xlo[MT16], *xhi[MT16];
