@@ -632,6 +632,11 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             // 128 (SHREWQ_AUTO_PAIR=1).  They let the whole test-suite and the benchmark run on those
             // kernels before the rule below is changed.
             if (env_flag("SHREWQ_AUTO_MMA_F16") && M <= 64 && gemv_mma_supported(a)) { choice = kForceMmaF16; break; }
+            // SHREWQ_AUTO_TC_F32=1: f32 activations of batches above 16 through the two bf16 passes on the
+            // tensor cores instead of the f32 FMA kernel (same status: not yet run on a GPU)
+            if (env_flag("SHREWQ_AUTO_TC_F32") && x_dtype == SHREWQ_F32 && y_dtype == SHREWQ_F32 && !up && !zp_route &&
+                lin->tmap_ok && M > 16 && (a.K % 16) == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0)
+                return forward_f32_on_tensor_cores(lin, a, who);
             if (env_flag("SHREWQ_AUTO_PAIR") && M > 128 && tc_ok && !zp_route) {
                 rc = up ? launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap, nullptr);
                 lin->last_kernel = "tcgen05-2cta";
