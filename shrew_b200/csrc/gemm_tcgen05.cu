@@ -82,7 +82,7 @@ LaunchPlan plan_launch(const ForwardArgs &a, int chan_per_tile, int sm_count, bo
     // large token tiles, with at least 8 rounds per split: batches 65..256 on layers with few
     // channel tiles (N = 4096: 32 tiles) otherwise run on a fraction of the SMs.  The kernel's
     // split path is the same code for every tile width.
-    static const int max_tok = [] {
+    const int max_tok = [] {  // read at every launch, so that one process can compare settings
         const char *e = getenv("SHREWQ_TC_SPLITK_MAXTOK");
         const int v = e ? atoi(e) : 64;
         return v < 64 ? 64 : v;
@@ -120,7 +120,8 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
     // SHREWQ_TC_TAILSPLIT=1 (built, NOT yet run on a GPU, off by default): when large tiles
     // leave a short last wave, issue the full waves as one launch and the tiles of the last
     // wave as a second launch split along K so that it also fills the SMs.
-    static const bool tail_split = getenv("SHREWQ_TC_TAILSPLIT") && atoi(getenv("SHREWQ_TC_TAILSPLIT")) != 0;
+    const char *ts = getenv("SHREWQ_TC_TAILSPLIT");
+    const bool tail_split = ts && atoi(ts) != 0;
     if (tail_split && !fixed_scratch && TOK >= 128 && p.splits == 1) {
         const int tiles = p.n_tiles * p.m_tiles, rem = tiles % ctx->sm_count;
         const int rounds = p.rounds_per_split;

@@ -15,7 +15,8 @@ void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     // serialization: back-to-back GEMVs overlap launch latency, prologue and the first weight
     // loads with the tail of the kernel before.  Built, compiled, NOT yet run on a GPU: off unless
     // the variable is set (the default instantiations are the validated kernel, unchanged).
-    static const bool pdl = getenv("SHREWQ_GEMV_PDL") && atoi(getenv("SHREWQ_GEMV_PDL")) != 0;
+    const char *pe = getenv("SHREWQ_GEMV_PDL");
+    const bool pdl = pe && atoi(pe) != 0;
     if (pdl) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);

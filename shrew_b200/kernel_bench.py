@@ -7,6 +7,7 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     SHREWQ_BENCH_KERNELS=gemv,mma,mma-f16,mma-w4,tcgen05,tcgen05-2cta python -m shrew_b200.kernel_bench lin   # other kernel families
     (mma-w4 = packed INT4 weights, also needs SHREWQ_EXPERIMENTAL_MODES=1; a "+af16" suffix on a tcgen05
     family, e.g. tcgen05+af16, runs it with f16 weights in tensor memory, SHREWQ_TC_A_F16=1)
+    python -m shrew_b200.kernel_bench mlp 512    # the Llama MLP block (gate/up + down) under every prepared tuning setting
     python -m shrew_b200.build --trace && SHREWQ_LIB=shrew_b200/libshrewq_trace.so \
         python -m shrew_b200.kernel_bench trace 4096 4096 16,1024  # in-kernel cycle trace of CTA 0
 
@@ -159,10 +160,71 @@ def bench_trace(N, K, batches):
     L.shrewq_force_kernel(b"auto")
 
 
+# Tuning settings of the forward kernels (environment variables the library reads at every launch),
+# compared in ONE process: a fresh process costs more GPU time than the measurement.
+MLP_SETTINGS = [
+    ("default", {}),
+    ("tok256", {"SHREWQ_TC_TOK": "256"}),
+    ("tok256+tail", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1"}),
+    ("tok256+tail+split", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}),
+    ("af16", {"SHREWQ_TC_A_F16": "1"}),
+    ("tok256+tail+split+af16", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256",
+                                "SHREWQ_TC_A_F16": "1"}),
+    ("pair", {"SHREWQ_AUTO_PAIR": "1"}),
+    ("pair+tail", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1"}),
+    ("pair+tail+af16", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_A_F16": "1"}),
+    ("mma-f16", {"SHREWQ_AUTO_MMA_F16": "1"}),
+    ("mma-f16+pdl", {"SHREWQ_AUTO_MMA_F16": "1", "SHREWQ_GEMV_PDL": "1"}),
+    ("pdl", {"SHREWQ_GEMV_PDL": "1"}),
+]
+_TUNING_VARS = sorted({k for _, env in MLP_SETTINGS for k in env})
+
+
+def bench_mlp(batches, d_model=4096, d_ff=11008, only=None):
+    """gate/up (one fused launch) + down of the Llama MLP block, per setting: microseconds per block, tokens/s and
+    TFLOP/s, and whether the result equals the default setting's (same bits expected unless the accumulation order
+    changes: split-K, another kernel family)."""
+    nbuf = max(2, int(2 * L2_BYTES // (3 * d_ff * d_model)) + 1)
+    gates, ups, downs = _layers(d_ff, d_model, nbuf), _layers(d_ff, d_model, nbuf), _layers(d_model, d_ff, nbuf)
+    for M in batches:
+        x = torch.randn(M, d_model, device="cuda").to(torch.bfloat16)
+        h = torch.empty(M, d_ff, device="cuda", dtype=torch.bfloat16)
+        y = torch.empty(M, d_model, device="cuda", dtype=torch.bfloat16)
+        ref = None
+        for name, env in MLP_SETTINGS:
+            if only and name not in only:
+                continue
+            for k in _TUNING_VARS:
+                os.environ.pop(k, None)
+            os.environ.update(env)
+
+            def f():
+                for g, u, d in zip(gates, ups, downs):
+                    g.forward_gate_up_silu(u, x, out=h)
+                    d.forward(h, out=y)
+            try:
+                t = _time_graph(f, iters=5, warm=2) / nbuf
+                Device.get("cuda:0").synchronize()
+            except Exception as e:  # noqa: BLE001
+                print(json.dumps(dict(setting=name, M=M, error=str(e))), flush=True)
+                continue
+            out = y.float()
+            if ref is None:
+                ref = out
+            err = float((out - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+            print(json.dumps(dict(setting=name, M=M, us=t * 1e6, tokens_per_s=M / t, TFs=6 * M * d_ff * d_model / t / 1e12,
+                                  kernels=[gates[0].last_kernel(), downs[0].last_kernel()], rel_diff_vs_first=err)), flush=True)
+    for k in _TUNING_VARS:
+        os.environ.pop(k, None)
+
+
 def main(argv):
     which = argv[1] if len(argv) > 1 else "lin"
     if which == "quant":
         bench_quant()
+    elif which == "mlp":
+        bench_mlp([int(b) for b in argv[2].split(",")] if len(argv) > 2 else [512, 1],
+                  only=set(argv[3].split(",")) if len(argv) > 3 else None)
     elif which == "trace":
         bench_trace(int(argv[2]), int(argv[3]), [int(b) for b in argv[4].split(",")])
     else:
