@@ -167,15 +167,16 @@ MLP_SETTINGS = [
     ("tok256", {"SHREWQ_TC_TOK": "256"}),
     ("tok256+tail", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1"}),
     ("tok256+tail+split", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}),
+    ("pdl", {"SHREWQ_GEMV_PDL": "1"}),
+    ("mma-f16", {"SHREWQ_AUTO_MMA_F16": "1"}),
+    ("mma-f16+pdl", {"SHREWQ_AUTO_MMA_F16": "1", "SHREWQ_GEMV_PDL": "1"}),
+    ("pair", {"SHREWQ_AUTO_PAIR": "1"}),
+    ("pair+tail", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1"}),
+    # f16 weights beside bf16 activations: last (the one setting whose instruction form has not run here)
     ("af16", {"SHREWQ_TC_A_F16": "1"}),
     ("tok256+tail+split+af16", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256",
                                 "SHREWQ_TC_A_F16": "1"}),
-    ("pair", {"SHREWQ_AUTO_PAIR": "1"}),
-    ("pair+tail", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1"}),
     ("pair+tail+af16", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_A_F16": "1"}),
-    ("mma-f16", {"SHREWQ_AUTO_MMA_F16": "1"}),
-    ("mma-f16+pdl", {"SHREWQ_AUTO_MMA_F16": "1", "SHREWQ_GEMV_PDL": "1"}),
-    ("pdl", {"SHREWQ_GEMV_PDL": "1"}),
 ]
 _TUNING_VARS = sorted({k for _, env in MLP_SETTINGS for k in env})
 
