@@ -562,6 +562,59 @@ def test_tcgen05_f16_weights_give_the_same_bits(oracle, emu_tc, tok, M, N, K, sp
         assert oracle.rel_err(y_h, oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)) < 2e-6
 
 
+def _gated_ref(oracle, qg, sg, bg, qu, su, bu, x):
+    g = oracle.np_linear_forward(qg, sg, 1, bg, x).astype(np.float64)
+    u = oracle.np_linear_forward(qu, su, 1, bu, x).astype(np.float64)
+    return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+
+
+@pytest.mark.parametrize("seed", range(36))
+def test_tcgen05_random_configurations(oracle, emu_tc, seed):
+    # a seeded sweep over what the launcher can combine: token tile, converter groups, K splits, plain or
+    # gate/up tile, output type, elementwise op, f16 or bf16 weights in tensor memory, grid or tile list,
+    # ragged M / N / K (K a multiple of 16 only)
+    rng = np.random.default_rng(1000 + seed)
+    tok = int(rng.choice([16, 32, 64, 128, 256]))
+    M = int(rng.integers(1, tok + tok // 2 + 2))
+    N = int(rng.integers(1, 280))
+    K = 16 * int(rng.integers(1, 72))
+    groups = int(rng.integers(1, 4))
+    gated = bool(rng.integers(0, 2))
+    y_bf16 = bool(rng.integers(0, 2))
+    relu = (not gated) and bool(rng.integers(0, 2))
+    kblk = 64 if tok == 256 else 128
+    rounds = -(-K // kblk)
+    splits = int(rng.integers(1, min(4, rounds) + 1))
+    af16 = groups == 3 and bool(rng.integers(0, 2))
+    tile_list = int(rng.integers(0, 2))
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, seed)
+    up = None
+    if gated:
+        qu = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+        su = rng.random(N) * 1e-2 + 1e-4
+        bu = (rng.standard_normal(N) * 0.1).astype(np.float32)
+        up = (qu, su, bu)
+        ref = _gated_ref(oracle, q, scales, bias, qu, su, bu, x)
+    else:
+        ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=relu)
+    what = dict(tok=tok, M=M, N=N, K=K, groups=groups, gated=gated, y_bf16=y_bf16, relu=relu, splits=splits, af16=af16,
+                tile_list=tile_list)
+    emu_tc.emu_set_a_f16(int(af16))
+    emu_tc.emu_tma_async.argtypes = [_cu, _cu]
+    if seed % 3 == 0:                                  # loads land late and newest first
+        emu_tc.emu_tma_async(seed + 1, int(rng.choice([8, 200, 1500])))
+        what["late_loads"] = True
+    try:
+        y = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, groups, splits=splits, y_bf16=y_bf16, epilogue=int(relu), up=up,
+                        tile_list=tile_list)
+    finally:
+        emu_tc.emu_set_a_f16(0)
+        emu_tc.emu_tma_async(0, 0)
+    if y_bf16:
+        y = (y.astype(np.uint32) << 16).view(np.float32)
+    assert oracle.rel_err(y, ref) < (1e-2 if y_bf16 else 1e-5), what
+
+
 def test_tcgen05_tile_list_grid(oracle, emu_tc):
     # the 1-D tile list of the two-launch tail-split scheme (not yet run on a GPU)
     q, scales, bias, x_bits, x = _tc_case(300, 260, 512, 5)
@@ -649,6 +702,57 @@ def test_cta_pair_f16_weights_give_the_same_bits(emu_pair, M, N, K, splits, gate
             emu_pair.emu_set_a_f16(0)
         ys.append(y)
     np.testing.assert_array_equal(ys[0], ys[1])
+
+
+@pytest.mark.parametrize("seed", range(15))
+def test_cta_pair_random_configurations(oracle, emu_pair, seed):
+    rng = np.random.default_rng(2000 + seed)
+    M = int(rng.integers(1, 560))
+    N = int(rng.integers(1, 560))
+    K = 16 * int(rng.integers(1, 60))
+    gated = bool(rng.integers(0, 2))
+    y_bf16 = bool(rng.integers(0, 2))
+    relu = (not gated) and bool(rng.integers(0, 2))
+    rounds = -(-K // 128)
+    splits = int(rng.integers(1, min(3, rounds) + 1))
+    af16 = bool(rng.integers(0, 2))
+    tile_list = int(rng.integers(0, 2))
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, seed)
+    qa, xa = _aligned(q.shape, np.int8), _aligned(x_bits.shape, np.uint16)
+    qa[...] = q
+    xa[...] = x_bits
+    s32 = scales.astype(np.float32)
+    up = (None, None, None)
+    if gated:
+        qu = _aligned(q.shape, np.int8)
+        qu[...] = rng.integers(-127, 128, size=q.shape).astype(np.int8)
+        su = rng.random(N) * 1e-2 + 1e-4
+        bu = (rng.standard_normal(N) * 0.1).astype(np.float32)
+        su32 = su.astype(np.float32)
+        up = (_p(qu), _p(su32), _p(bu))
+        ref = _gated_ref(oracle, q, scales, bias, qu, su, bu, x)
+    else:
+        ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=relu)
+    what = dict(M=M, N=N, K=K, gated=gated, y_bf16=y_bf16, relu=relu, splits=splits, af16=af16, tile_list=tile_list)
+    y = np.full((M, N), 0x4100, np.uint16) if y_bf16 else np.full((M, N), 7.0, np.float32)
+    emu_pair.emu_set_a_f16(int(af16))
+    emu_pair.emu_tma_async.argtypes = [_cu, _cu]
+    if seed % 3 == 0:                                  # loads land late and newest first
+        emu_pair.emu_tma_async(seed + 1, int(rng.choice([8, 200, 1500])))
+        what["late_loads"] = True
+    try:
+        rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), *up, _p(xa), _p(y), M, N, K, N, int(relu), int(y_bf16), splits,
+                                            tile_list)
+    finally:
+        emu_pair.emu_set_a_f16(0)
+        emu_pair.emu_tma_async(0, 0)
+    if rc == -4:
+        emu_pair.emu_fail_message.restype = ctypes.c_char_p
+        raise AssertionError(emu_pair.emu_fail_message().decode() + f" {what}")
+    assert rc == 0, what
+    if y_bf16:
+        y = (y.astype(np.uint32) << 16).view(np.float32)
+    assert oracle.rel_err(y, ref) < (1e-2 if y_bf16 else 1e-5), what
 
 
 @pytest.mark.parametrize("gated", [False, True])
