@@ -347,6 +347,13 @@ def _bf16_bits(x32):
     return b, (b.astype(np.uint32) << 16).view(np.float32)
 
 
+def _gated_ref(oracle, qg, sg, bg, qu, su, bu, x):
+    g = oracle.np_linear_forward(qg, sg, 1, bg, x).astype(np.float64)
+    u = oracle.np_linear_forward(qu, su, 1, bu, x).astype(np.float64)
+    with np.errstate(over="ignore"):
+        return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+
+
 def _mma_forward(emu_mma, q, scales, bias, x_bits, f16, y_bf16, relu=False, up=None, ldy=None):
     N, K = q.shape
     M = x_bits.shape[0]
@@ -368,6 +375,41 @@ def _mma_forward(emu_mma, q, scales, bias, x_bits, f16, y_bf16, relu=False, up=N
     rc = emu_mma.emu_gemv_mma(*args, _p(xa), _p(y), M, N, K, ldy, 1 if relu else 0, int(f16), int(y_bf16), ctypes.byref(staged))
     assert rc == 0
     return y, staged.value
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_warp_mma_random_configurations(oracle, emu_mma, seed):
+    # seeded sweep: batch 1..64 (staged in the CTA up to 4, else the separate conversion kernel), ragged N,
+    # K a multiple of 64, bf16 or f16 operands, plain or gate/up, either output type, activations of any scale
+    rng = np.random.default_rng(3000 + seed)
+    M = int(rng.choice([1, 2, 3, 4, 5, 8, 15, 16, 17, 31, 32, 33, 48, 64]))
+    N = int(rng.integers(1, 70))
+    K = 64 * int(rng.integers(1, 40 if M <= 4 else 12))
+    f16 = int(rng.integers(0, 2))
+    gated = bool(rng.integers(0, 2))
+    y_bf16 = bool(rng.integers(0, 2))
+    relu = (not gated) and bool(rng.integers(0, 2))
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, seed)
+    xs = (x * np.float32(2.0) ** rng.integers(-30, 30, size=(M, 1))).astype(np.float32)   # per-row scales: the f16 rescale
+    x_bits, x = _bf16_bits(xs)
+    up = None
+    if gated:
+        qu = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+        su = rng.random(N) * 1e-2 + 1e-4
+        bu = (rng.standard_normal(N) * 0.1).astype(np.float32)
+        up = (qu, su, bu)
+        ref = _gated_ref(oracle, q, scales, bias, qu, su, bu, x)
+    else:
+        ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=relu)
+    y, staged = _mma_forward(emu_mma, q, scales, bias, x_bits, f16, y_bf16, relu=relu, up=up)
+    assert staged == int(bool(f16) and M <= 4 and M * K * 2 <= 40960)
+    if y_bf16:
+        y = (y.astype(np.uint32) << 16).view(np.float32)
+    with np.errstate(invalid="ignore"):
+        ok = np.isfinite(ref)
+    assert np.array_equal(np.isfinite(y), ok)
+    what = dict(M=M, N=N, K=K, f16=f16, gated=gated, y_bf16=y_bf16, relu=relu)
+    assert oracle.rel_err(np.where(ok, y, 0), np.where(ok, ref, 0)) < (1e-2 if y_bf16 else 1e-5), what
 
 
 @pytest.mark.parametrize("f16", [0, 1], ids=["bf16", "f16"])
@@ -560,12 +602,6 @@ def test_tcgen05_f16_weights_give_the_same_bits(oracle, emu_tc, tok, M, N, K, sp
     np.testing.assert_array_equal(y_h, y_bf)
     if not gated:
         assert oracle.rel_err(y_h, oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)) < 2e-6
-
-
-def _gated_ref(oracle, qg, sg, bg, qu, su, bu, x):
-    g = oracle.np_linear_forward(qg, sg, 1, bg, x).astype(np.float64)
-    u = oracle.np_linear_forward(qu, su, 1, bu, x).astype(np.float64)
-    return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
 
 
 @pytest.mark.parametrize("seed", range(36))
