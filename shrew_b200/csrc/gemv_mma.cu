@@ -22,7 +22,7 @@ template <typename YT, bool GATED>
 void launch_staged(shrewq_ctx *ctx, const ForwardArgs &a) {
     constexpr int kChan = GATED ? 8 : 8 * NB;
     const unsigned grid = (unsigned)((a.N + kChan - 1) / kChan);
-    const size_t smem = a.M * a.K * sizeof(uint16_t);  // <= kStageMaxBytes: below the 48 KB that need no opt-in
+    const size_t smem = a.M * a.K * sizeof(uint16_t);  // <= kStageMaxBytes: static + dynamic stay below 48 KB
     // SHREWQ_GEMV_PDL=1 (as for the CUDA-core GEMV): programmatic stream serialization, so that a chain
     // of batch-1 forwards keeps the weight stream going across kernel boundaries
     const char *e = getenv("SHREWQ_GEMV_PDL");

@@ -402,7 +402,7 @@ def test_warp_mma_random_configurations(oracle, emu_mma, seed):
     else:
         ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=relu)
     y, staged = _mma_forward(emu_mma, q, scales, bias, x_bits, f16, y_bf16, relu=relu, up=up)
-    assert staged == int(bool(f16) and M <= 4 and M * K * 2 <= 40960)
+    assert staged == int(bool(f16) and M <= 4 and M * K * 2 <= 36864)
     if y_bf16:
         y = (y.astype(np.uint32) << 16).view(np.float32)
     with np.errstate(invalid="ignore"):
@@ -413,7 +413,7 @@ def test_warp_mma_random_configurations(oracle, emu_mma, seed):
 
 
 @pytest.mark.parametrize("f16", [0, 1], ids=["bf16", "f16"])
-@pytest.mark.parametrize("M,N,K", [(1, 16, 64), (1, 40, 512), (3, 21, 128), (4, 16, 5120), (5, 16, 64), (16, 32, 192),
+@pytest.mark.parametrize("M,N,K", [(1, 16, 64), (1, 40, 512), (3, 21, 128), (4, 16, 4608), (4, 16, 4672), (5, 16, 64), (16, 32, 192),
                                    (17, 24, 128), (33, 16, 128), (64, 17, 64)])
 def test_warp_mma_forward_matches_oracle(oracle, emu_mma, f16, M, N, K):
     rng = np.random.default_rng(M * 1000 + N + K)
@@ -423,7 +423,7 @@ def test_warp_mma_forward_matches_oracle(oracle, emu_mma, f16, M, N, K):
     x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
     y, staged = _mma_forward(emu_mma, q, scales, bias, x_bits, f16, y_bf16=False, relu=True, ldy=N + 5)
-    assert staged == int(bool(f16) and M <= 4 and M * K * 2 <= 40960)
+    assert staged == int(bool(f16) and M <= 4 and M * K * 2 <= 36864)
     assert oracle.rel_err(y[:, :N], ref) < 2e-6        # exact products, f32-level accumulation
     assert np.all(y[:, N:] == 7.0)                     # nothing written outside [M, N]
     y16, _ = _mma_forward(emu_mma, q, scales, None, x_bits, f16, y_bf16=True)
@@ -1224,7 +1224,7 @@ def test_packed_int4_forward_matches_oracle(oracle, emu_mma, M, N, K):
     staged = ctypes.c_int(-1)
     rc = emu_mma.emu_gemv_mma_w4(_p(packed), _p(s32), _p(bias), None, None, None, _p(xa), _p(y), M, N, K, N + 2, 1, 0, ctypes.byref(staged))
     assert rc == 0
-    assert staged.value == int(M <= 4 and M * K * 2 <= 40960)
+    assert staged.value == int(M <= 4 and M * K * 2 <= 36864)
     assert oracle.rel_err(y[:, :N], ref) < 2e-6 and np.all(y[:, N:] == 7.0)
 
 

@@ -261,8 +261,8 @@ def test_mma_small_batch_parity(oracle, M, N, K):
 
 @_UNVALIDATED
 @pytest.mark.parametrize("M,N,K", [(1, 523, 1024), (5, 16, 64), (16, 4096, 4096), (23, 300, 1088), (50, 1000, 2048), (64, 11008, 4096),
-                                   # batch 1..4 stage x inside the kernel while M*K*2 <= 40 KiB, else the staging kernel
-                                   (2, 300, 4096), (3, 523, 1024), (4, 128, 5120), (4, 128, 5184), (1, 4096, 11008), (2, 64, 11008)])
+                                   # batch 1..4 stage x inside the kernel while M*K*2 <= 36 KiB, else the staging kernel
+                                   (2, 300, 4096), (3, 523, 1024), (4, 128, 4608), (4, 128, 4672), (1, 4096, 11008), (2, 64, 11008)])
 def test_mma_f16_small_batch_parity(oracle, M, N, K):
     ql, w, b = _make(N, K, 1, seed=N + K)
     x_t, x_np = _x(M, K, "bf16", seed=M)
