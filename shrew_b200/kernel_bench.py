@@ -2,6 +2,7 @@
 host launch cost is excluded; the weights rotate through a ring larger than twice L2).
 
     python -m shrew_b200.kernel_bench quant      # quantize / dequantize bandwidth sweep
+    python -m shrew_b200.kernel_bench quant 8192 8192   # one shape (a case small enough for a profiler capture)
     python -m shrew_b200.kernel_bench lin        # forward kernels over a batch sweep
     python -m shrew_b200.kernel_bench lin 4096 4096 1,16,256   # one layer shape, chosen batches
     SHREWQ_BENCH_KERNELS=gemv,mma,mma-f16,mma-w4,tcgen05,tcgen05-2cta python -m shrew_b200.kernel_bench lin   # other kernel families
@@ -47,8 +48,8 @@ def _time_graph(fn, iters=10, warm=3):
     return a.elapsed_time(b) * 1e-3 / iters
 
 
-def bench_quant():
-    for (R, C) in [(1024, 1024), (2048, 2048), (4096, 4096), (8192, 8192), (16384, 8192), (16384, 16384), (32768, 16384)]:
+def bench_quant(shapes=None):
+    for (R, C) in shapes or [(1024, 1024), (2048, 2048), (4096, 4096), (8192, 8192), (16384, 8192), (16384, 16384), (32768, 16384)]:
         nbuf = max(1, int(2 * L2_BYTES // (R * C * 4)) + 1) if R * C * 4 < 2 * L2_BYTES else 1
         ws = []
         for i in range(nbuf):
@@ -222,7 +223,7 @@ def bench_mlp(batches, d_model=4096, d_ff=11008, only=None):
 def main(argv):
     which = argv[1] if len(argv) > 1 else "lin"
     if which == "quant":
-        bench_quant()
+        bench_quant([(int(argv[2]), int(argv[3]))] if len(argv) >= 4 else None)
     elif which == "mlp":
         bench_mlp([int(b) for b in argv[2].split(",")] if len(argv) > 2 else [512, 1],
                   only=set(argv[3].split(",")) if len(argv) > 3 else None)
