@@ -116,6 +116,12 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
 
 }  // namespace
 
+#ifdef SHREWQ_TRACE
+extern "C" __attribute__((visibility("default"))) int shrewq_debug_set_trace_pair(long long *dev_buf) {
+    return (int)cudaMemcpyToSymbol(g_trace_pair, &dev_buf, sizeof(dev_buf));
+}
+#endif
+
 // Plain forward: w_tmap = the handle's 128-row INT8 boxes, w_up_tmap = nullptr.  Gate/up pair: the
 // 64-row boxes of the gate and of the up handle (the descriptors the single-CTA kernel uses).
 int launch_gemm_tcgen05_2cta(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap) {

@@ -73,6 +73,20 @@ struct Ctl {
     uint32_t tmem_base;
 };
 
+// In-kernel cycle trace (tracing build only): CTA (0,0,0), the pair's leader, stamps clock64() per role
+// and pipeline round; layout and meaning as in the single-CTA kernel.
+#ifdef SHREWQ_TRACE
+__device__ long long *g_trace_pair = nullptr;  // [role 0..3][round 0..255][tag 0..3]
+__device__ __forceinline__ void trace_rec_pair(long long *tr, int role, int kb, int tag) {
+    if (tr && kb < 256) tr[(role * 256 + kb) * 4 + tag] = clock64();
+}
+#define TRACE2(role, kb, tag) do { if ((threadIdx.x & 31) == 0) trace_rec_pair(trace_buf, role, kb, tag); } while (0)
+#define TRACE2_INIT long long *trace_buf = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? g_trace_pair : nullptr;
+#else
+#define TRACE2(role, kb, tag)
+#define TRACE2_INIT
+#endif
+
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role,
                                             uint32_t stage) {
     for (uint32_t i = 0; i < kSpinFast; ++i)
@@ -175,6 +189,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                               const __grid_constant__ CUtensorMap tmap_x, Operands2 ops, YT *__restrict__ y, Dests extra,
                               int M, int N, int K, size_t ldy, int epilogue, SplitK2 sk, DeviceStatus *status) {
     constexpr int kChan = GATED ? kLanes / 2 : kLanes;  // output channels per CTA
+    TRACE2_INIT
     SHREWQ_DYNAMIC_SMEM(uint8_t, smem_raw);
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *bar_area = smem + kStages * kStageBytes;
@@ -233,7 +248,9 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             uint32_t dst = smem_base;
             int kc = r_begin * kSub * kBlockK;
             for (int i = 0; i < rounds; ++i) {
+                TRACE2(0, i, 0);
                 if (!mbar_wait(bars_u32 + kEmpty + s * 8, ph, ctl, status, 0, s)) break;
+                TRACE2(0, i, 1);
                 const uint32_t wb = bars_u32 + kWFull + s * 8, xb = bars_u32 + kXFull + s * 8;
                 mbar_expect_tx(wb, kSub * kWSub);
                 if (rank == 0) mbar_expect_tx(xb, 2 * kSub * kXSub);  // the halves of both CTAs
@@ -247,6 +264,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                     }
                     tma_load_2d_pair(dst + kXOff + j * kXSub, &tmap_x, kc + j * kBlockK, m0, xb);
                 }
+                TRACE2(0, i, 2);
                 kc += kSub * kBlockK;
                 dst += kStageBytes;
                 if (++s == kStages) { s = 0; ph ^= 1; dst = smem_base; }
@@ -264,9 +282,11 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             uint64_t bdesc = bdesc0;
             bool ok = true;
             for (int i = 0; i < rounds; ++i) {
+                TRACE2(1, i, 0);
                 ok = mbar_wait(bars_u32 + kAready + s * 8, ph, ctl, status, 2, s) &&
                      mbar_wait(bars_u32 + kXFull + s * 8, ph, ctl, status, 1, s);
                 if (!ok) break;
+                TRACE2(1, i, 2);
                 tc_fence_after();
 #pragma unroll
                 for (int j = 0; j < kSub; ++j) {
@@ -277,6 +297,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                                        (i > 0 || j > 0 || jj > 0) ? 1u : 0u);
                 }
                 tc_commit_pair(bars_u32 + kEmpty + s * 8);  // frees stage s in both CTAs
+                TRACE2(1, i, 3);
                 a_tmem += kAColsPerStage;
                 bdesc += (uint64_t)(kStageBytes >> 4);
                 if (++s == kStages) { s = 0; ph ^= 1; a_tmem = a0; bdesc = bdesc0; }
@@ -299,9 +320,11 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             const int s = i % kStages;
             if (s % kGroups != group) continue;
             const uint32_t ph = (i / kStages) & 1;
+            if (quad == 0) TRACE2(2, i, 0);
             ok = mbar_wait_warp(bars_u32 + kWFull + s * 8, ph, ctl, status, 3, s);
             if (!ok) break;
             tc_fence_after();
+            if (quad == 0) TRACE2(2, i, 1);
 #pragma unroll
             for (int j = 0; j < kSub; ++j) {
                 const uint8_t *rowp = smem + s * kStageBytes + j * kWSub + row * kBlockK;
@@ -323,10 +346,12 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                 }
                 tc_st32(tmem_base + lane_addr + kABase + s * kAColsPerStage + j * (kBlockK / 2), packed);
             }
+            if (quad == 0) TRACE2(2, i, 2);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(aready_leader + s * 8);
+            if (quad == 0) TRACE2(2, i, 3);
         }
         // epilogue: this CTA's channels x the pair's 256 tokens; 16-column chunks dealt to the groups
         if (ok) ok = mbar_wait_warp(bars_u32 + kAcc, 0, ctl, status, 4, 0);

@@ -11,6 +11,7 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     python -m shrew_b200.kernel_bench mlp 512    # the Llama MLP block (gate/up + down) under every prepared tuning setting
     python -m shrew_b200.build --trace && SHREWQ_LIB=shrew_b200/libshrewq_trace.so \
         python -m shrew_b200.kernel_bench trace 4096 4096 16,1024  # in-kernel cycle trace of CTA 0
+        (a fifth argument `tcgen05-2cta` traces the leader CTA of the CTA-pair kernel; SHREWQ_TC_A_F16=1 etc. apply)
 
 Prints one JSON object per measurement: microseconds per launch, algorithmic GB/s and
 TFLOP/s.  Algorithmic bytes: quantize 5 B/element + 8 B/row; forward N*K + 4*N +
@@ -131,7 +132,7 @@ def bench_lin(shapes, batches):
         del lins
 
 
-def bench_trace(N, K, batches):
+def bench_trace(N, K, batches, kernel="tcgen05"):
     """clock64() stamps of CTA (0,0,0) of the tcgen05 kernel, per role and pipeline stage:
     producer [wait empty, got it, TMA issued], converter [wait full, got it, converted,
     arrived], MMA issuer [loop top, -, barrier passed, committed].  Needs the tracing build
@@ -140,18 +141,19 @@ def bench_trace(N, K, batches):
     L = _lib.lib()
     if not hasattr(L, "shrewq_debug_set_trace"):
         raise SystemExit("trace: load the tracing build (python -m shrew_b200.build --trace; SHREWQ_LIB=...)")
-    L.shrewq_debug_set_trace.argtypes = [ctypes.c_void_p]
+    set_trace = L.shrewq_debug_set_trace_pair if kernel == "tcgen05-2cta" else L.shrewq_debug_set_trace
+    set_trace.argtypes = [ctypes.c_void_p]
     lin = _layers(N, K, 1)[0]
-    L.shrewq_force_kernel(b"tcgen05")
+    L.shrewq_force_kernel(kernel.encode())
     for M in batches:
         x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         buf = torch.zeros(4 * 256 * 4, dtype=torch.int64, device="cuda")
         lin.forward(x)
         torch.cuda.synchronize()
-        L.shrewq_debug_set_trace(ctypes.c_void_p(buf.data_ptr()))
+        set_trace(ctypes.c_void_p(buf.data_ptr()))
         lin.forward(x)
         Device.get("cuda:0").synchronize()
-        L.shrewq_debug_set_trace(None)
+        set_trace(None)
         t = buf.cpu().numpy().reshape(4, 256, 4)
         t0 = t[0, 0, 0]
         stages = int((t[1, :, 3] != 0).sum())
@@ -228,7 +230,7 @@ def main(argv):
         bench_mlp([int(b) for b in argv[2].split(",")] if len(argv) > 2 else [512, 1],
                   only=set(argv[3].split(",")) if len(argv) > 3 else None)
     elif which == "trace":
-        bench_trace(int(argv[2]), int(argv[3]), [int(b) for b in argv[4].split(",")])
+        bench_trace(int(argv[2]), int(argv[3]), [int(b) for b in argv[4].split(",")], argv[5] if len(argv) > 5 else "tcgen05")
     else:
         shapes = [(4096, 4096), (11008, 4096), (4096, 11008)]
         batches = [1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 4096]
