@@ -6,6 +6,7 @@
 #include <cstdlib>
 
 #include "shrewq.hpp"
+#include "shrewq_checkpoint.hpp"
 
 using namespace shrew;
 
@@ -118,7 +119,30 @@ static void test_quantize_zero_tensor() {
     for (double v : dequantize_tensor(qt, DEV).to_f64_vec()) CHECK(v == 0.0);
 }
 
-int main() {
+// not a reference test: the reference cannot store a QuantizedTensor.  Quantize, save, load, and the
+// loaded layer gives the same output bits.
+static void test_checkpoint_round_trip(const char *path) {
+    std::vector<double> w(24 * 16), b(24), x(5 * 16);
+    for (size_t i = 0; i < w.size(); ++i) w[i] = std::sin(0.37 * double(i)) * 0.4;
+    for (size_t i = 0; i < b.size(); ++i) b[i] = 0.01 * double(i) - 0.1;
+    for (size_t i = 0; i < x.size(); ++i) x[i] = std::cos(0.11 * double(i));
+    Linear linear{Tensor::from_f64_slice(w, {24, 16}, DType::F32, DEV), Tensor::from_f64_slice(b, {1, 24}, DType::F32, DEV), true};
+    QuantizedLinear ql = QuantizedLinear::from_linear(linear, QuantConfig::int8_per_channel());
+    QuantizedTensor pt = quantize_tensor(linear.weight, QuantConfig::int8());
+    save_quantized(path, {{"fc.weight", ql.weight_quantized()}, {"fc_pt.weight", pt}});
+    auto loaded = load_quantized(path, DEV);   // (the file stays for the caller to inspect)
+    CHECK(loaded.size() == 2 && loaded[0].first == "fc.weight" && loaded[1].first == "fc_pt.weight");
+    CHECK(loaded[0].second.data_host() == ql.weight_quantized().data_host());
+    CHECK(loaded[0].second.scales_host() == ql.weight_quantized().scales_host());
+    CHECK(loaded[0].second.shape == std::vector<size_t>({24, 16}) && loaded[0].second.n_scales == 24);
+    CHECK(loaded[1].second.n_scales == 1 && loaded[1].second.scales_host() == pt.scales_host());
+    QuantizedLinear ql2 = QuantizedLinear::create(loaded[0].second, &linear.bias, DEV);
+    Tensor xt = Tensor::from_f64_slice(x, {5, 16}, DType::F32, DEV);
+    CHECK(ql.forward(xt).to_f64_vec() == ql2.forward(xt).to_f64_vec());
+}
+
+// usage: test_quantize_api [file to write the checkpoint round trip to]
+int main(int argc, char **argv) {
     try {
         DEV = Device(0);
         test_int8_symmetric_per_tensor();
@@ -130,11 +154,13 @@ int main() {
         test_quantize_named_parameters();
         test_quantization_stats();
         test_quantize_zero_tensor();
+        if (argc > 1) test_checkpoint_round_trip(argv[1]);
         DEV.synchronize();
     } catch (const Error &e) {
         std::fprintf(stderr, "shrew::Error %d: %s\n", e.code, e.what());
         return 2;
     }
     std::puts("9 reference tests passed");
+    if (argc > 1) std::puts("checkpoint round trip passed");
     return 0;
 }
