@@ -28,13 +28,20 @@ def test_cpp_mirror_compiles():
 
 
 @pytest.mark.gpu
-def test_reference_unit_tests_in_cpp(tmp_path):
+def test_reference_unit_tests_in_cpp():
+    exe = _compile()
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "9 reference tests passed" in r.stdout
+
+
+@pytest.mark.gpu
+def test_cpp_checkpoint_round_trip(tmp_path):
+    # the C++ host's save / load of quantized tensors (include/shrewq_checkpoint.hpp): quantize, save, load,
+    # same forward bits; the Python reader opens the file too
     exe = _compile()
     r = subprocess.run([exe, str(tmp_path / "ckpt.safetensors")], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert "9 reference tests passed" in r.stdout
-    # and the C++ host's save / load of quantized tensors (include/shrewq_checkpoint.hpp), which the Python
-    # reader opens too
     assert "checkpoint round trip passed" in r.stdout
     from shrew_b200 import qsafetensors as qs
     back = qs.unpack_records(*qs.read_file(str(tmp_path / "ckpt.safetensors")))
