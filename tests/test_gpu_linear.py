@@ -97,6 +97,20 @@ def test_known_answer_linear(oracle):
     np.testing.assert_allclose(y, [[127 - 381 + 0.5, 1 + 4 + 381 - 0.5]], rtol=1e-6)
 
 
+def test_linear_from_tensors_known_answer():
+    # nn_tests.rs:68-79 as written: W = identity, b = [0.5, -0.5], x = [3, 7] -> [3.5, 6.5]; the identity's codes
+    # are {127, 0} with scale 1/127, which dequantizes to exactly 1.0f
+    from shrew_b200 import Linear, QuantConfig, QuantizedLinear, dequantize_tensor
+    w = torch.eye(2, device="cuda")
+    b = torch.tensor([0.5, -0.5], device="cuda")
+    x = torch.tensor([[3.0, 7.0]], device="cuda")
+    for cfg in (QuantConfig.int8_per_channel(), QuantConfig.int8()):
+        ql = QuantizedLinear.from_linear(Linear(w, b), cfg)
+        assert ql.weight_q.data.cpu().tolist() == [127, 0, 0, 127]
+        assert torch.equal(dequantize_tensor(ql.weight_q), w)
+        np.testing.assert_allclose(ql.forward(x).cpu().numpy(), [[3.5, 6.5]], rtol=1e-6)
+
+
 # ---- GEMV (M <= 16) --------------------------------------------------------------------------------
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 16])
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])

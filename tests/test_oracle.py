@@ -78,6 +78,43 @@ def test_float_linear_known_answers(oracle):
     np.testing.assert_allclose(y, [[4, 4], [8, 8]], rtol=1e-6)
 
 
+def test_rounding_convention_of_the_reference(oracle):
+    # nn_tests.rs:2413-2420: f64::round rounds half away from zero; the vector and its expected result
+    t = np.array([-1.7, -0.5, 0.0, 0.3, 1.5, 2.9])
+    np.testing.assert_array_equal(oracle.np_round_half_away(t), [-2.0, -1.0, 0.0, 0.0, 2.0, 3.0])
+    # and through the C restatement: values that are exactly these after the multiply by 1/scale (scale 1.0:
+    # amax 127 puts the codes on the values themselves)
+    w = np.array([[127.0, -1.5, -0.5, 0.5, 1.5, 2.5, -2.5, 0.49999997]], dtype=np.float32)
+    q, s = oracle.quantize_f32(w, oracle.PER_TENSOR)
+    assert s[0] == 1.0
+    np.testing.assert_array_equal(q, [[127, -2, -1, 1, 2, 3, -3, 0]])
+
+
+def test_linear_from_tensors_known_answer(oracle):
+    # nn_tests.rs:68-79: W = identity (2 x 2), b = [0.5, -0.5], x = [3, 7] -> [3.5, 6.5]; quantized per channel
+    # the identity's rows have amax 1, codes {127, 0}, and 127 * (1 / 127) narrows to exactly 1.0f
+    w = np.eye(2, dtype=np.float32)
+    b = np.array([[0.5, -0.5]], dtype=np.float32)
+    x = np.array([[3.0, 7.0]], dtype=np.float32)
+    for gran in (oracle.PER_CHANNEL, oracle.PER_TENSOR):
+        q, s = oracle.quantize_f32(w, gran)
+        np.testing.assert_array_equal(q, [[127, 0], [0, 127]])
+        np.testing.assert_array_equal(oracle.dequantize(q, s, gran, "f32"), w)
+        np.testing.assert_allclose(oracle.linear_forward_f32(q, s, gran, b, x), [[3.5, 6.5]], rtol=1e-7)
+
+
+def test_matmul_known_answer_within_quantization_error(oracle):
+    # exec_tests.rs:132-173: a [2,3] = rows of the identity, b [3,2] = [[1,2],[3,4],[5,6]] -> [[1,2],[3,4]].
+    # As a Linear the weight is b^T; its entries are not multiples of amax / 127, so the quantized result
+    # is off by at most half a step per weight: |error| <= 0.5 * amax / 127
+    wt = np.array([[1.0, 3.0, 5.0], [2.0, 4.0, 6.0]], dtype=np.float32)
+    a = np.array([[1.0, 0.0, 0.0], [0.0, 1.0, 0.0]], dtype=np.float32)
+    q, s = oracle.quantize_f32(wt, oracle.PER_CHANNEL)
+    y = oracle.linear_forward_f32(q, s, oracle.PER_CHANNEL, None, a)
+    assert np.all(np.abs(y - np.array([[1.0, 2.0], [3.0, 4.0]])) <= 0.5 * np.array([5.0, 6.0]) / 127 + 1e-6)
+    np.testing.assert_array_equal(q, [[25, 76, 127], [42, 85, 127]])   # round(v * 127 / amax): 25.4, 76.2 | 42.33, 84.67
+
+
 @pytest.mark.parametrize("shape,gran", [((64, 96), 0), ((64, 96), 1), ((7, 33), 1), ((5, 3, 11), 1), ((1, 513), 0)])
 def test_c_oracle_equals_numpy_twin_random(oracle, shape, gran):
     rng = np.random.default_rng(123)
