@@ -177,3 +177,30 @@ def test_device_round_trip(tmp_path):
     y1, y2 = ql.forward(x), ql2.forward(x)
     Device.get("cuda:0").synchronize()
     assert torch.equal(y1, y2)
+
+
+def test_device_layer_round_trip_on_cpu_tensors(tmp_path):
+    # `save` / `load` are plain torch + numpy: with CPU tensors they run without a GPU (the GPU test above
+    # adds the forward through the loaded layer)
+    import torch
+
+    from shrew_b200 import QuantConfig
+    from shrew_b200.quantize import QuantizedTensor
+    rng = np.random.default_rng(1)
+    codes = torch.from_numpy(rng.integers(-127, 128, size=96 * 32).astype(np.int8))
+    pc = QuantizedTensor(codes, torch.from_numpy(rng.random(96) * 1e-2), [96, 32], torch.float32, QuantConfig.int8_per_channel())
+    pt = QuantizedTensor(codes[:64].clone(), torch.tensor([0.125], dtype=torch.float64), [2, 4, 8], torch.bfloat16, QuantConfig.int8())
+    asym = QuantizedTensor(codes[:12].clone(), torch.from_numpy(rng.random(3)), [3, 4], torch.float32,
+                           QuantConfig.int8_per_channel().asymmetric(), torch.tensor([-3.0, 0.0, 17.0], dtype=torch.float64))
+    bias = torch.arange(96, dtype=torch.float32)
+    emb = torch.arange(12, dtype=torch.float32).reshape(3, 4).to(torch.bfloat16)
+    p = str(tmp_path / "m.safetensors")
+    qs.save(p, [("fc.weight", pc), ("fc.bias", bias), ("pt.weight", pt), ("asym.weight", asym), ("emb", emb)])
+    got = dict(qs.load(p, "cpu"))
+    for name, t in (("fc.weight", pc), ("pt.weight", pt), ("asym.weight", asym)):
+        g = got[name]
+        assert torch.equal(g.data, t.data) and torch.equal(g.scales, t.scales) and g.shape == t.shape
+        assert g.original_dtype == t.original_dtype and g.config == t.config
+    assert got["fc.weight"].zero_points_t is None and got["pt.weight"].zero_points_t is None
+    assert torch.equal(got["asym.weight"].zero_points_t, asym.zero_points_t)
+    assert torch.equal(got["fc.bias"], bias) and torch.equal(got["emb"], emb) and got["emb"].dtype == torch.bfloat16
