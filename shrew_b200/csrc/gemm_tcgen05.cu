@@ -88,7 +88,22 @@ LaunchPlan plan_launch(const ForwardArgs &a, int chan_per_tile, int sm_count, bo
         return v < 64 ? 64 : v;
     }();
     const int min_rounds = TOK <= 64 ? 2 : 8;
-    if (allow_split && TOK <= max_tok && tiles <= 1024) {
+    // SHREWQ_TC_SPLIT_WAVES=1 (NOT yet run on a GPU; same kernel path, another launch rule): choose the
+    // split count by waves instead of "as many as fit in one wave".  86 tiles on 148 SMs (N = 11008) take
+    // one wave whole, but 3 splits take 2 waves of a third each (0.67 of the time) and 5 splits 3 waves of
+    // a fifth (0.6): the rule below minimises waves / splits plus a charge per split for the reduction.
+    const char *wv = getenv("SHREWQ_TC_SPLIT_WAVES");
+    if (allow_split && wv && atoi(wv) != 0 && TOK <= max_tok && tiles <= 2L * sm_count) {
+        // (grids of many waves lose little to the last one, and their partial sums would be many: the
+        // two-launch tail split is the tool there)
+        double best = 1e30;
+        for (int sp = 1; sp <= 8 && (sp == 1 || rounds / sp >= min_rounds); ++sp) {
+            const long ctas = tiles * sp;
+            const long waves = (ctas + sm_count - 1) / sm_count;
+            const double cost = (double)waves / sp + (sp > 1 ? 0.03 * sp : 0.0);
+            if (cost < best - 1e-9) { best = cost; splits = sp; }
+        }
+    } else if (allow_split && TOK <= max_tok && tiles <= 1024) {
         int want = (int)(sm_count / tiles);
         if (want > rounds / min_rounds) want = rounds / min_rounds;
         if (want > 1) splits = want;

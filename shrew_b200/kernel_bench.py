@@ -170,6 +170,8 @@ MLP_SETTINGS = [
     ("tok256", {"SHREWQ_TC_TOK": "256"}),
     ("tok256+tail", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1"}),
     ("tok256+tail+split", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}),
+    ("waves", {"SHREWQ_TC_SPLIT_WAVES": "1"}),
+    ("waves+maxtok", {"SHREWQ_TC_SPLIT_WAVES": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}),
     ("pdl", {"SHREWQ_GEMV_PDL": "1"}),
     ("mma-f16", {"SHREWQ_AUTO_MMA_F16": "1"}),
     ("mma-f16+pdl", {"SHREWQ_AUTO_MMA_F16": "1", "SHREWQ_GEMV_PDL": "1"}),

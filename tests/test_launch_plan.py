@@ -107,3 +107,23 @@ def test_bad_arguments_are_refused():
     assert L.shrewq_plan_forward(8, 0, 4096, 1, 0, 148, name, 32, *refs) != 0
     assert L.shrewq_plan_forward(8, 4096, 0, 1, 0, 148, name, 32, *refs) != 0
     assert L.shrewq_plan_forward(8, 4096, 4096, 1, 0, 148, name, 32, None, *refs[1:]) != 0
+
+
+def test_wave_aware_split_rule(monkeypatch):
+    # SHREWQ_TC_SPLIT_WAVES=1 (opt-in): 86 channel tiles on 148 SMs are one wave whole, two waves of a third
+    # each when split 3 ways, three waves of a fifth when split 5 ways
+    assert plan(16, 11008, 4096)[2]["splits"] == 1
+    monkeypatch.setenv("SHREWQ_TC_SPLIT_WAVES", "1")
+    p = plan(16, 11008, 4096)[2]
+    assert (p["splits"], p["rounds"]) == (5, 7)
+    assert plan(16, 4096, 4096)[2]["splits"] == 4                 # 32 tiles: as before, one wave of 128
+    assert plan(128, 11008, 4096)[2]["splits"] == 1               # large tiles stay whole ...
+    assert plan(512, 11008, 4096, gated=1)[2]["splits"] == 1      # ... and so do grids of many waves
+    monkeypatch.setenv("SHREWQ_TC_SPLITK_MAXTOK", "256")
+    assert plan(128, 11008, 4096)[2]["splits"] == 3               # ... unless split-K is extended to them
+    assert plan(512, 11008, 4096, gated=1)[2]["splits"] == 1
+    for M, N, K in [(16, 11008, 4096), (64, 4096, 11008), (128, 11008, 4096), (256, 4096, 4096), (100, 1000, 4096)]:
+        q = plan(M, N, K)[2]
+        kblk = 64 if q["tok"] == 256 else 128
+        total = -(-K // kblk)
+        assert q["splits"] * q["rounds"] >= total and (q["splits"] - 1) * q["rounds"] < total
