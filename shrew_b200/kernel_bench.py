@@ -6,8 +6,8 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     python -m shrew_b200.kernel_bench lin        # forward kernels over a batch sweep
     python -m shrew_b200.kernel_bench lin 4096 4096 1,16,256   # one layer shape, chosen batches
     SHREWQ_BENCH_KERNELS=gemv,mma,mma-f16,mma-w4,tcgen05,tcgen05-2cta python -m shrew_b200.kernel_bench lin   # other kernel families
-    (mma-w4 = packed INT4 weights, also needs SHREWQ_EXPERIMENTAL_MODES=1; a "+af16" suffix on a tcgen05
-    family, e.g. tcgen05+af16, runs it with f16 weights in tensor memory, SHREWQ_TC_A_F16=1)
+    (mma-w4 = packed INT4 weights, also needs SHREWQ_EXPERIMENTAL_MODES=1; "+suffix"es set a tuning variable
+    for that measurement: tcgen05+af16, tcgen05+waves+maxtok, tcgen05-2cta+tail, gemv+pdl, tcgen05+tok256 ...)
     python -m shrew_b200.kernel_bench mlp 512    # the Llama MLP block (gate/up + down) under every prepared tuning setting
     python -m shrew_b200.build --trace && SHREWQ_LIB=shrew_b200/libshrewq_trace.so \
         python -m shrew_b200.kernel_bench trace 4096 4096 16,1024  # in-kernel cycle trace of CTA 0
@@ -94,6 +94,11 @@ def _layers_int4(N, K, nbuf):
     return out
 
 
+# "+suffix" on a kernel family name in SHREWQ_BENCH_KERNELS: the tuning variable it sets for that measurement
+_SUFFIX = {"af16": ("SHREWQ_TC_A_F16", "1"), "waves": ("SHREWQ_TC_SPLIT_WAVES", "1"), "maxtok": ("SHREWQ_TC_SPLITK_MAXTOK", "256"),
+           "tail": ("SHREWQ_TC_TAILSPLIT", "1"), "pdl": ("SHREWQ_GEMV_PDL", "1"), "tok256": ("SHREWQ_TC_TOK", "256")}
+
+
 def bench_lin(shapes, batches):
     L = _lib.lib()
     kernels = os.environ.get("SHREWQ_BENCH_KERNELS", "gemv,tcgen05").split(",")
@@ -110,8 +115,11 @@ def bench_lin(shapes, batches):
                 w4 = force == "mma-w4"
                 if w4 and (lins4 is None or M > 32):
                     continue
-                family, _, variant = force.partition("+")
-                os.environ["SHREWQ_TC_A_F16"] = "1" if variant == "af16" else "0"   # read by the library at every launch
+                family, *variants = force.split("+")
+                for var, _ in _SUFFIX.values():
+                    os.environ.pop(var, None)
+                for v in variants:                       # read by the library at every launch
+                    os.environ[_SUFFIX[v][0]] = _SUFFIX[v][1]
                 L.shrewq_force_kernel(b"auto" if w4 else family.encode())
                 use = lins4 if w4 else lins
 
@@ -128,7 +136,8 @@ def bench_lin(shapes, batches):
                 print(json.dumps(dict(kernel=force, M=M, N=N, K=K, us=t * 1e6, GBs=by / t / 1e9,
                                       TFs=2 * M * N * K / t / 1e12)), flush=True)
         L.shrewq_force_kernel(b"auto")
-        os.environ.pop("SHREWQ_TC_A_F16", None)
+        for var, _ in _SUFFIX.values():
+            os.environ.pop(var, None)
         del lins
 
 
