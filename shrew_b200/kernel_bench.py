@@ -105,17 +105,17 @@ def bench_lin(shapes, batches):
     for (N, K) in shapes:
         nbuf = max(2, int(2 * L2_BYTES // (N * K)) + 1)
         lins = _layers(N, K, nbuf)
-        lins4 = _layers_int4(N, K, 2 * nbuf) if "mma-w4" in kernels and K % 128 == 0 else None
+        lins4 = _layers_int4(N, K, 2 * nbuf) if any(k.split("+")[0] == "mma-w4" for k in kernels) and K % 128 == 0 else None
         for M in batches:
             x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
             y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
             for force in kernels:
-                if (force == "gemv" and M > 16) or (force.startswith("mma") and M > 64):
+                family, *variants = force.split("+")
+                if (family == "gemv" and M > 16) or (family.startswith("mma") and M > 64):
                     continue
-                w4 = force == "mma-w4"
+                w4 = family == "mma-w4"
                 if w4 and (lins4 is None or M > 32):
                     continue
-                family, *variants = force.split("+")
                 for var, _ in _SUFFIX.values():
                     os.environ.pop(var, None)
                 for v in variants:                       # read by the library at every launch
