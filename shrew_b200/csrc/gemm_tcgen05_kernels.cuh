@@ -229,6 +229,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     int *s_is_last = reinterpret_cast<int *>(bar_area + 640);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 2) TRACE(3, 1, 0);  // kernel entry
     int tile_x = blockIdx.x, tile_y = blockIdx.y;
     if (sk.n_tiles_total > 0) {
         const int tl = sk.tile_begin + (int)blockIdx.x;
@@ -264,6 +265,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
+    if (warp == 2) TRACE(3, 1, 1);  // barriers initialised, tensor memory allocated
 
     if (warp == 0) {
         // ---------------- TMA producer (one thread) ----------------
@@ -382,7 +384,9 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             if (((warp - 2) & 3) == 0) TRACE(2, i, 3);
         }
         // ---------------- epilogue: 16-column chunks dealt round-robin to the groups ----------------
+        if (warp == 2) TRACE(3, 0, 0);  // (tracing build: role 3 = the epilogue of the first converter warp)
         if (ok) ok = mbar_wait_warp(bars_u32 + kAccBar, 0, ctl, status, 4, 0);
+        if (warp == 2) TRACE(3, 0, 1);  // accumulators complete
         // this lane's channel: plain tiles map lane -> n0 + lane; gated tiles map lanes 0..63 to
         // the gate rows and lanes 64..127 to the up rows of channels n0 .. n0+63
         const bool is_up = GATED && row >= 64;
@@ -449,6 +453,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                     for (int i = 0; i < 16; ++i) __stcg(mine + (c * 16 + i) * kTileN + row, __uint_as_float(r[i]));
                 }
             }
+            if (warp == 2) TRACE(3, 0, 2);  // partial sums written
             __threadfence();
             named_bar_sync(1, 128 * G);
             if (threadIdx.x == 64) {
@@ -456,6 +461,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                 *s_is_last = (old == (unsigned int)(splits - 1));
             }
             named_bar_sync(1, 128 * G);
+            if (warp == 2) TRACE(3, 0, 3);  // this CTA's arrival counted
             if (*s_is_last) {
                 __threadfence();
                 const float *base = sk.partials + tile * splits * (size_t)(TOK * kTileN);
@@ -490,8 +496,10 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     }
 
     // ---------------- teardown ----------------
+    if (warp == 2) TRACE(3, 1, 2);  // this warp's epilogue done
     tc_fence_before();
     __syncthreads();
+    if (warp == 2) TRACE(3, 1, 3);  // every warp done
     if (warp == 1) {
         if (ctl->abort_flag) {
             // give in-flight copies / MMAs a bounded moment to land before TMEM is released

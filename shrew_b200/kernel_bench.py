@@ -144,7 +144,8 @@ def bench_lin(shapes, batches):
 def bench_trace(N, K, batches, kernel="tcgen05"):
     """clock64() stamps of CTA (0,0,0) of the tcgen05 kernel, per role and pipeline stage:
     producer [wait empty, got it, TMA issued], converter [wait full, got it, converted,
-    arrived], MMA issuer [loop top, -, barrier passed, committed].  Needs the tracing build
+    arrived], MMA issuer [loop top, -, barrier passed, committed]; for the single-CTA kernel also
+    the kernel's set-up / epilogue / teardown stamps.  Needs the tracing build
     of the library (SHREWQ_LIB).  Prints cycles relative to the producer's first stamp."""
     import ctypes
     L = _lib.lib()
@@ -169,6 +170,10 @@ def bench_trace(N, K, batches, kernel="tcgen05"):
         for i in range(stages):
             print(json.dumps(dict(M=M, stage=i, producer=(t[0, i, :3] - t0).tolist(), converter=(t[2, i] - t0).tolist(),
                                   mma=(t[1, i, [0, 2, 3]] - t0).tolist())), flush=True)
+        if t[3, 1, 0]:  # single-CTA kernel: [entry, set-up done, epilogue done, all warps done] and the epilogue's
+            # [start, accumulators complete, partial sums written, arrival counted] (the last two with split-K)
+            print(json.dumps(dict(M=M, kernel=(t[3, 1] - t0).tolist(), epilogue=[int(v - t0) if v else None for v in t[3, 0]])),
+                  flush=True)
     L.shrewq_force_kernel(b"auto")
 
 
