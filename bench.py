@@ -330,7 +330,6 @@ def main():
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_total = float(ms.item())
     launches = launches_per_step * args.steps if use_graphs else sdev.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
     value = M * args.steps / (ms_total * 1e-3)
 
     # ---- end to end: pinned host input in, host output back, every step ----
@@ -440,6 +439,9 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     k_s = e0.elapsed_time(e1) * 1e-3 / iters
+    # the sampler ran from the start of the device-resident timed region through the end-to-end and
+    # kernel-alone timed regions: the device-resident one alone lasts ~10 ms, one nvidia-smi period
+    clocks = sampler.stop() if rank == 0 else None
     kernel_family = kname.last_kernel()
     tensor_bound = M >= 128
     if tensor_bound:
