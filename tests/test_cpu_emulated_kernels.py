@@ -918,6 +918,40 @@ def test_tcgen05_peer_destinations(oracle, emu_tc):
             assert np.all(buf[:, 140:] == (7.0 if buf is y else 5.0))
 
 
+def test_tcgen05_gated_shard_of_eight_ranks_with_seven_peers(oracle, emu_tc):
+    # the benchmark's MLP block over 8 GPUs: each rank owns 11008 / 8 = 1376 = 21 x 64 + 32 hidden channels, so its
+    # gated launch ends in a half-full channel tile, writes bf16 into columns [n0, n0 + n_local) of the full-width
+    # row and into the same columns of seven peer buffers.  Same structure at reduced size: 2 x 64 + 32 channels,
+    # two token tiles (the second ragged), row stride 8 x n_local.
+    emu_tc.emu_set_peers.argtypes = [_vp, _ci]
+    rng = np.random.default_rng(88)
+    M, N, K, world, rank = 130, 160, 256, 8, 3
+    ldy = world * N
+    qg, qu = (rng.integers(-127, 128, size=(N, K)).astype(np.int8) for _ in range(2))
+    sg, su = rng.random(N) * 1e-2 + 1e-4, rng.random(N) * 1e-2 + 1e-4
+    x_bits, x = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    g = oracle.np_linear_forward(qg, sg, 1, None, x).astype(np.float64)
+    u = oracle.np_linear_forward(qu, su, 1, None, x).astype(np.float64)
+    ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    # every buffer is the full [M, ldy] matrix; the kernel is handed the address of column n0 in each
+    full = [np.full((M, ldy), 0x4100, np.uint16) for _ in range(world)]
+    n0 = rank * N
+    views = [f[:, n0:] for f in full]
+    arr = (ctypes.c_void_p * 7)(*[v.ctypes.data for i, v in enumerate(views) if i != rank])
+    own = np.full((M, ldy), 0x4100, np.uint16)
+    emu_tc.emu_set_peers(arr, 7)
+    try:
+        y = _tc_forward(emu_tc, qg, sg, None, x_bits, 128, 3, y_bf16=True, up=(qu, su, None), ldy=ldy, y_init=own)
+    finally:
+        emu_tc.emu_set_peers(None, 0)
+    # _tc_forward's own buffer starts at column 0: compare its first N columns, and columns [n0, n0 + N) of the peers
+    got = [(y[:, :N], y[:, N:])] + [(f[:, n0:n0 + N], np.delete(f, np.s_[n0:n0 + N], axis=1)) for i, f in enumerate(full) if i != rank]
+    for inside, outside in got:
+        assert oracle.rel_err((inside.astype(np.uint32) << 16).view(np.float32), ref) < 1e-2
+        assert np.all(outside == 0x4100)                       # nothing written outside the shard's columns
+    assert all(np.array_equal(inside, got[0][0]) for inside, _ in got)   # every copy holds the same bits
+
+
 # ---- the CUDA-core forward kernels (GPU-validated; here for the stand-in's sake and for the paths the GPU
 # tests reach only on several GPUs: peer destinations) ---------------------------------------------------
 @pytest.fixture(scope="module")
