@@ -8,6 +8,9 @@ workload is the Llama-7B-shaped MLP block of the benchmark configs (4096 -> 1100
 SiLU, 11008 -> 4096 down, INT8 per-channel weights ~N(0,0.02), bf16 activations ~N(0,1),
 batch 512), output channels sharded over the N GPUs with an all-gather after each of the
 two sharded layers.  Metric: tokens/s (rows of the batch per second) for the whole job.
+Other workloads (`--workload`): single Linears of config 3, the block at batch 1, and, on one
+GPU, the f32-activation configs 1 (`mnist_mlp_m64`) and 2 (`tinygpt_stack_m4096`: the 25 Linears of
+the TinyGPT-shaped stack; its vocabulary head is bound by the 823 MB f32 output it writes).
 
 Prints ONE JSON line on rank 0.  Timing: CUDA events on the launching stream, barrier and
 synchronize on both sides, max over ranks.  L2: every step uses a different copy of the
@@ -46,7 +49,30 @@ WORKLOADS = {
     "linear4096_m64": dict(kind="linear", M=64, N=4096, K=4096),
     "linear4096_m256": dict(kind="linear", M=256, N=4096, K=4096),
     "linear4096_m1024": dict(kind="linear", M=1024, N=4096, K=4096),
+    # config 1: MLP 784 -> 256 -> 10 with ReLU, f32 activations ~U(0,1), batch 64 (the layers are chained)
+    "mnist_mlp_m64": dict(kind="stack", M=64, chain=True, uniform=True, std=0.05,
+                          layers=[(256, 784, True, True), (10, 256, False, True)]),
+    # config 2: the Linear layers of a TinyGPT-shaped stack (d_model 256, d_ff 1024, 4 blocks, vocabulary 50257) on
+    # batch 8 x seq 512 = 4096 rows of f32 activations; the glue between the layers (attention, norms, residuals)
+    # is not part of the path, so every layer reads a resident N(0,1) stand-in of its input width
+    "tinygpt_stack_m4096": dict(kind="stack", M=4096, chain=False, uniform=False, std=0.02,
+                                layers=([(256, 256, False, False)] * 4 + [(1024, 256, False, True), (256, 1024, False, True)]) * 4
+                                + [(50257, 256, False, False)]),
 }
+
+
+def config_of(wl):
+    """The workload's entries for the JSON line's `config` (a stack's layer list as one string)."""
+    c = {k: v for k, v in wl.items() if k not in ("kind", "layers")}
+    if wl["kind"] == "stack":
+        c["layers"] = f"{len(wl['layers'])} Linears, " + " ".join(sorted({f"{k}->{n}" for n, k, _, _ in wl["layers"]}))
+        c["activations"] = "f32"
+    return c
+
+
+def stack_layers(wl):
+    """(N, K, relu, bias) per Linear of a "stack" workload."""
+    return [tuple(l) for l in wl["layers"]]
 
 
 def measured_peaks():
@@ -133,13 +159,23 @@ def cpu_step_factory(wl):
     if wl["kind"] == "mlp":
         dm, dff = wl["d_model"], wl["d_ff"]
         shapes = [(dff, dm), (dff, dm), (dm, dff)]
+    elif wl["kind"] == "stack":
+        shapes = [(n, k) for n, k, _, _ in stack_layers(wl)]
     else:
         shapes = [(wl["N"], wl["K"])]
     qs = []
     for i, (n, k) in enumerate(shapes):
-        q, s = oracle.np_quantize_f32(host_weight(n, k, i), oracle.PER_CHANNEL)
+        w = host_weight(n, k, i)
+        if wl["kind"] == "stack":
+            w = w * np.float32(wl["std"] / 0.02)
+        q, s = oracle.np_quantize_f32(w, oracle.PER_CHANNEL)
         qs.append((q, s, np.empty((n, k), dtype=np.float32)))
-    x = torch.from_numpy(rng.standard_normal((M, shapes[0][1]), dtype=np.float32)).to(torch.bfloat16).float()
+    if wl["kind"] == "stack":  # f32 activations: U(0,1) for config 1, N(0,1) stand-ins per input width for config 2
+        draw = (lambda k: rng.random((M, k), dtype=np.float32)) if wl["uniform"] else (lambda k: rng.standard_normal((M, k), dtype=np.float32))
+        xs = {k: torch.from_numpy(draw(k)) for k in sorted({k for _, k in shapes})}
+        x = xs[shapes[0][1]]
+    else:
+        x = torch.from_numpy(rng.standard_normal((M, shapes[0][1]), dtype=np.float32)).to(torch.bfloat16).float()
 
     def lin(i, inp):
         q, s, buf = qs[i]
@@ -151,6 +187,15 @@ def cpu_step_factory(wl):
             g, u = lin(0, x), lin(1, x)
             h = torch.nn.functional.silu(g) * u
             return lin(2, h)
+        if wl["kind"] == "stack":
+            y = x
+            for i, (n, k, relu, bias) in enumerate(stack_layers(wl)):
+                y = lin(i, y if wl["chain"] else xs[k])
+                if bias:
+                    y = y + torch.zeros(1, n)      # quantize.rs:471-472: the broadcast add of the [1,out] bias
+                if relu:
+                    y = torch.relu(y)
+            return y
         return lin(0, x)
 
     return step, M, f"full step: batch {M}, every weight dequantized per call (1 thread) + f32 GEMM on {torch.get_num_threads()} threads"
@@ -172,7 +217,7 @@ def run_reference_arm(args, wl, name):
         "impl": "reference", "metric": "quantized_linear_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, **{k: v for k, v in wl.items() if k != "kind"}},
+        "config": {"workload": name, **config_of(wl)},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "Rust reference (shrew-cpu: gemm 0.18.2 + rayon) cannot be built on this image; this is the CPU port of "
@@ -223,6 +268,8 @@ def main():
         _lib.check(_lib.lib().shrewq_force_kernel(args.force_kernel.encode()), None)
     cfg = QuantConfig.int8_per_channel()
     M = wl["M"]
+    if wl["kind"] == "stack" and world > 1:
+        raise SystemExit("bench.py: the stack workloads (configs 1 and 2) run on one GPU; --gpus N takes the default workload")
 
     # ---- build the rank's shards; a ring of weight copies defeats L2 between steps ----
     def make_shard(n, k, seed):
@@ -235,15 +282,53 @@ def main():
         shard_bytes = (2 * dff * dm + dm * dff) // world
         in_features = dm
         flops_step = 2 * M * (2 * dff * dm + dm * dff)
+    elif wl["kind"] == "stack":
+        layers = stack_layers(wl)
+        shard_bytes = sum(n * k for n, k, _, _ in layers)
+        in_features = layers[0][1]
+        flops_step = sum(2 * M * n * k for n, k, _, _ in layers)
     else:
         shard_bytes = wl["N"] * wl["K"] // world
         in_features = wl["K"]
         flops_step = 2 * M * wl["N"] * wl["K"]
     ring = max(2, -(-2 * L2_BYTES // shard_bytes) + 1)
+    if wl["kind"] == "stack":
+        ring = min(ring, 32)   # config 1 is 0.2 MB of codes: no ring of sensible length exceeds L2, and the line says so
     fused = world > 1 and args.gather == "fused"
+    x_dt = torch.float32 if wl["kind"] == "stack" else torch.bfloat16
+
+    class Stack:
+        """The Linears of a stack workload, one after the other.  Output buffers and the stand-in inputs of
+        the other widths are shared by all ring entries; only the weights differ between entries."""
+        bufs, stand_ins = None, None
+
+        def __init__(self):
+            gb = torch.Generator(device=dev).manual_seed(3)
+            self.layers = []
+            for i, (n, k, relu, bias) in enumerate(layers):
+                w = gpu_weight(n, k, i, dev) * (wl["std"] / 0.02)
+                b = torch.randn(n, device=dev, generator=gb) * 0.1 if bias else None
+                self.layers.append((QuantizedLinear.from_linear(Linear(w, b), cfg), relu))
+            if Stack.bufs is None:
+                Stack.bufs = [torch.empty((M, n), dtype=x_dt, device=dev) for n, _, _, _ in layers]
+                gs = torch.Generator(device=dev).manual_seed(4)
+                Stack.stand_ins = {k: torch.randn(M, k, device=dev, generator=gs) for k in sorted({k for _, k, _, _ in layers})}
+
+        def forward(self, x):
+            y = x
+            for (ql, relu), (n, k, _, _), buf in zip(self.layers, layers, Stack.bufs):
+                if wl["chain"]:
+                    src = y
+                else:
+                    src = x if k == x.shape[1] else Stack.stand_ins[k]
+                y = ql.forward(src, epilogue=_lib.EPILOGUE_RELU if relu else _lib.EPILOGUE_NONE, out=buf)
+            return y
+
     models = []
     for c in range(ring):
-        if wl["kind"] == "mlp":
+        if wl["kind"] == "stack":
+            models.append(Stack())
+        elif wl["kind"] == "mlp":
             g, u, d = make_shard(dff, dm, 0), make_shard(dff, dm, 1), make_shard(dm, dff, 2)
             if fused:
                 models.append(FusedShardedGatedMLP(g, u, d, dff, dm, M, share=models[0] if models else None))
@@ -259,10 +344,13 @@ def main():
     torch.cuda.synchronize()
 
     gx = torch.Generator(device=dev).manual_seed(1)
-    x_dev = torch.randn(M, in_features, device=dev, generator=gx).to(torch.bfloat16)
+    if wl["kind"] == "stack" and wl["uniform"]:
+        x_dev = torch.rand(M, in_features, device=dev, generator=gx)
+    else:
+        x_dev = torch.randn(M, in_features, device=dev, generator=gx).to(x_dt)
     x_host = x_dev.cpu().pin_memory()
-    out_features = wl["d_model"] if wl["kind"] == "mlp" else wl["N"]
-    y_host = torch.empty((M, out_features), dtype=torch.bfloat16).pin_memory()
+    out_features = wl["d_model"] if wl["kind"] == "mlp" else layers[-1][0] if wl["kind"] == "stack" else wl["N"]
+    y_host = torch.empty((M, out_features), dtype=x_dt).pin_memory()
 
     def barrier():
         if world > 1:
@@ -299,7 +387,7 @@ def main():
             sys.stderr.write(f"bench: graph capture failed ({e!r}); running eagerly\n")
             graphs, outs, use_graphs = [], [], False
 
-    launches_per_step = 2 if wl["kind"] == "mlp" else 1
+    launches_per_step = 2 if wl["kind"] == "mlp" else len(layers) if wl["kind"] == "stack" else 1
 
     def step(i, x):
         if use_graphs:
@@ -361,7 +449,7 @@ def main():
     # on three streams (copy-in, compute, copy-out), at most two steps in flight.  One GPU
     # only: on several GPUs the ring entries share one output buffer that peers write into.
     # Any failure, or a result that differs from the sequential one, keeps the sequential figure.
-    if use_graphs and world == 1:
+    if use_graphs and world == 1 and wl["kind"] != "stack":   # (a stack's ring entries share their output buffers)
         try:
             y_ref = y_host.clone()
             ring_of = lambda i: i % ring  # noqa: E731
@@ -423,6 +511,18 @@ def main():
         k_flops = 2 * 2 * M * n_loc * dm
         k_bytes = 2 * n_loc * dm + 2 * 4 * n_loc + M * dm * 2 + M * n_loc * 2
         kname = models[0].gate
+    elif wl["kind"] == "stack":
+        # the layer whose roofline time is the longest (config 2: the vocabulary head, bound by its 823 MB f32 output)
+        def roof_time(l):
+            n, k, _, b = l
+            return max(2 * M * n * k / (peaks["tc_sustained"] * 1e12), (n * k + 4 * n * (1 + b) + 4 * M * k + 4 * M * n) / (peaks["hbm"] * 1e9))
+        li = max(range(len(layers)), key=lambda j: roof_time(layers[j]))
+        n_d, k_d, relu_d, bias_d = layers[li]
+        x_d = x_dev if k_d == x_dev.shape[1] else Stack.stand_ins[k_d]
+        kern = lambda i: models[i % ring].layers[li][0].forward(x_d, out=Stack.bufs[li])  # noqa: E731
+        k_flops = 2 * M * n_d * k_d
+        k_bytes = n_d * k_d + 4 * n_d * (1 + bias_d) + 4 * M * k_d + 4 * M * n_d
+        kname = models[0].layers[li][0]
     else:
         q = models[0].shard
         ybuf = torch.empty((M, q.out_features), dtype=torch.bfloat16, device=dev)
@@ -444,6 +544,8 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     kernel_family = kname.last_kernel()
     tensor_bound = M >= 128
+    if wl["kind"] == "stack":   # decided by the dominant layer's own arithmetic intensity
+        tensor_bound = k_flops / (peaks["tc_sustained"] * 1e12) > k_bytes / (peaks["hbm"] * 1e9)
     if tensor_bound:
         roof = {"bound": "tensor", "achieved": k_flops / k_s / 1e12, "peak": peaks["tc_sustained"], "unit": "TFLOP/s",
                 "peak_burst": peaks["tc_burst"]}
@@ -456,13 +558,13 @@ def main():
     out = {
         "metric": "quantized_linear_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x int8 -> f32 accumulate", "data": "synthetic",
-        "config": {"workload": args.workload, **({"forced_kernel": args.force_kernel} if args.force_kernel != "auto" else {}), **{k: v for k, v in wl.items() if k != "kind"},
+        "scaling": "strong", "vs_baseline": None, "dtype": ("f32" if wl["kind"] == "stack" else "bf16") + " x int8 -> f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, **({"forced_kernel": args.force_kernel} if args.force_kernel != "auto" else {}), **config_of(wl),
                    "weights": "INT8 per-channel, N(0,0.02)", "sharding": "none (single GPU)" if world == 1 else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
-                   "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU) > 2x L2"},
+                   "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU)" + (" > 2x L2" if ring * shard_bytes > 2 * L2_BYTES else "; the whole configuration is smaller than L2, so the weights stay L2-resident as they would in use")},
         "tflops": flops_step * args.steps / (ms_total * 1e-3) / 1e12,
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2,
-                "d2h_bytes_per_step": y_host.numel() * 2, **e2e_info},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
+                "d2h_bytes_per_step": y_host.numel() * y_host.element_size(), **e2e_info},
         "gpu_launches": int(launches), "launch_mode": "cuda graph replay (one graph per ring entry)" if use_graphs else "host launches", "clocks": clocks, "roofline": roof,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -33,3 +33,26 @@ def test_gpu_arm_has_no_cpu_fallback():
     r = _run("--steps", "1", "--warmup", "1")
     assert r.returncode != 0
     assert "no CUDA device" in (r.stderr + r.stdout)
+
+
+def test_reference_arm_runs_the_small_mlp_of_config_1():
+    r = _run("--impl", "reference", "--steps", "2", "--warmup", "1", "--workload", "mnist_mlp_m64")
+    assert r.returncode == 0, r.stderr
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["config"]["workload"] == "mnist_mlp_m64" and line["config"]["activations"] == "f32"
+    assert line["config"]["layers"].startswith("2 Linears") and line["value"] > 0
+
+
+def test_stack_workloads_are_well_formed():
+    sys.path.insert(0, ROOT)
+    import bench
+    for name, wl in bench.WORKLOADS.items():
+        json.dumps(bench.config_of(wl))
+        if wl["kind"] != "stack":
+            continue
+        layers = bench.stack_layers(wl)
+        assert all(n > 0 and k > 0 for n, k, _, _ in layers)
+        if wl["chain"]:   # each layer reads the previous one's output
+            assert all(layers[i][1] == layers[i - 1][0] for i in range(1, len(layers))), name
+    # config 2: 4 blocks of (4 x 256->256, 256->1024, 1024->256) and the 256->50257 head: 16,011,520 codes
+    assert sum(n * k for n, k, _, _ in bench.stack_layers(bench.WORKLOADS["tinygpt_stack_m4096"])) == 16011520
