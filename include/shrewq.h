@@ -15,7 +15,10 @@
  *    the given context (or of the last failed create call on this thread when ctx is NULL).
  *  - Pointers named *_dev are device pointers owned by the caller, valid on the context's
  *    device; pointers named *_host are ordinary host memory.  The library allocates only
- *    its own workspaces, inside contexts and handles.
+ *    its own workspaces, inside contexts and handles.  A workspace grows (synchronize + cudaMalloc)
+ *    the first time a call needs more than it holds; a call that would have to grow one while its
+ *    stream is being captured fails with SHREWQ_ERR_UNSUPPORTED instead of breaking the capture —
+ *    make the same call once outside the capture first.
  *  - Device entry points enqueue work on the context's stream and return without
  *    synchronising.  Host entry points (suffix _host) copy in, run, copy out and
  *    synchronise the stream before returning.

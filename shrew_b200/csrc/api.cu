@@ -19,6 +19,15 @@ int set_err(shrewq_ctx *ctx, int code, const char *fmt, ...) {
 
 static int grow(shrewq_ctx *ctx, void **p, size_t *have, size_t want, bool pinned) {
     if (*have >= want) return SHREWQ_OK;
+    // Growing means a synchronize and an allocation, neither of which a stream capture survives: say so
+    // instead of invalidating the caller's capture (one call of the same shape outside the capture sizes
+    // the buffer for good).
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &cap) != cudaSuccess) cudaGetLastError();
+    else if (cap != cudaStreamCaptureStatusNone)
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
+                       "this call needs %zu bytes of library workspace (have %zu) and cannot allocate while its stream is "
+                       "being captured: make the same call once outside the capture first", want, *have);
     // work already enqueued may still use the old buffer
     SHREWQ_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     if (*p) {
