@@ -48,11 +48,13 @@ struct Tuning {
     int groups;   // converter groups (1..3)
     bool splitk;  // allow split-K when the grid would leave SMs idle
     int tok;      // 0 = choose; else force the token tile
+    int tok_gated;  // 0 = as above; else the token tile of gate/up launches only (NOT yet run on a GPU at 256)
     bool a_f16;   // weights as f16 in tensor memory (cheaper conversion); NOT yet run on a GPU, off by default
 };
 
 Tuning read_tuning() {
-    Tuning t{3, true, 0, false};
+    Tuning t{3, true, 0, 0, false};
+    if (const char *e = getenv("SHREWQ_TC_TOK_GATED")) t.tok_gated = atoi(e);
     if (const char *e = getenv("SHREWQ_TC_A_F16")) t.a_f16 = atoi(e) != 0;
     if (const char *e = getenv("SHREWQ_TC_GROUPS")) t.groups = atoi(e);
     if (const char *e = getenv("SHREWQ_TC_SPLITK")) t.splitk = atoi(e) != 0;
@@ -233,7 +235,7 @@ int choose_tok(const ForwardArgs &a, int chan_per_tile, int sm_count) {
 template <bool GATED, typename YT>
 int launch_y(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, void *fs, size_t fsb) {
     const Tuning t = read_tuning();
-    const int tok = t.tok ? t.tok : choose_tok(a, GATED ? 64 : 128, ctx->sm_count);
+    const int tok = (GATED && t.tok_gated) ? t.tok_gated : t.tok ? t.tok : choose_tok(a, GATED ? 64 : 128, ctx->sm_count);
     switch (tok) {
         // small token tiles are HBM-bound: 2 sub-blocks per stage keeps the pipeline 6-7 stages
         // deep (TMEM columns limit the depth), i.e. ~100 KB of codes in flight per SM
@@ -312,7 +314,7 @@ int plan_gemm_tcgen05(size_t M, size_t N, size_t K, bool gated, int sm_count, in
     a.M = M; a.N = N; a.K = K;
     const Tuning t = read_tuning();
     const int chan = gated ? 64 : 128;
-    const int tk = t.tok ? t.tok : choose_tok(a, chan, sm_count);
+    const int tk = (gated && t.tok_gated) ? t.tok_gated : t.tok ? t.tok : choose_tok(a, chan, sm_count);
     LaunchPlan p;
     switch (tk) {
         case 16: p = plan_launch<16, 2>(a, chan, sm_count, t.splitk); break;

@@ -181,6 +181,8 @@ def bench_trace(N, K, batches, kernel="tcgen05"):
 # compared in ONE process: a fresh process costs more GPU time than the measurement.
 MLP_SETTINGS = [
     ("default", {}),
+    ("gated256", {"SHREWQ_TC_TOK_GATED": "256"}),
+    ("gated256+tail", {"SHREWQ_TC_TOK_GATED": "256", "SHREWQ_TC_TAILSPLIT": "1"}),
     ("tok256", {"SHREWQ_TC_TOK": "256"}),
     ("tok256+tail", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1"}),
     ("tok256+tail+split", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}),

@@ -127,3 +127,13 @@ def test_wave_aware_split_rule(monkeypatch):
         kblk = 64 if q["tok"] == 256 else 128
         total = -(-K // kblk)
         assert q["splits"] * q["rounds"] >= total and (q["splits"] - 1) * q["rounds"] < total
+
+
+def test_token_tile_of_gate_up_launches_can_be_set_on_its_own(monkeypatch):
+    # the benchmark's block at batch 512: 128-token tiles by default for both launches; SHREWQ_TC_TOK_GATED moves the
+    # gate/up launch alone (the down projection has too few channel tiles to afford 256-token tiles)
+    assert plan(512, 11008, 4096, gated=1)[2]["tok"] == 128
+    monkeypatch.setenv("SHREWQ_TC_TOK_GATED", "256")
+    rc, name, p = plan(512, 11008, 4096, gated=1)
+    assert (rc, name) == (0, "tcgen05") and (p["tok"], p["n_tiles"], p["m_tiles"], p["splits"]) == (256, 172, 2, 1)
+    assert plan(512, 4096, 11008, gated=0)[2]["tok"] == 128
