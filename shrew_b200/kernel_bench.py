@@ -30,8 +30,9 @@ from .quantize import Device
 L2_BYTES = 126 << 20
 
 
-def _time_graph(fn, iters=10, warm=3):
-    """Seconds per call of fn, replayed from a CUDA graph."""
+def _time_graph(fn, iters=10, warm=3, repeats=5):
+    """Seconds per call of fn, replayed from a CUDA graph: the median over `repeats` timed runs of `iters`
+    replays each (CUDA events on the replaying stream)."""
     fn()
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
@@ -40,13 +41,17 @@ def _time_graph(fn, iters=10, warm=3):
     for _ in range(warm):
         g.replay()
     torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(iters):
-        g.replay()
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) * 1e-3 / iters
+    times = []
+    for _ in range(repeats):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e-3 / iters)
+    times.sort()
+    return times[len(times) // 2]
 
 
 def bench_quant(shapes=None):
