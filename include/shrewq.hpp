@@ -253,11 +253,19 @@ class QuantizedLinear {
     }
     // inference only — quantize.rs:478-481
     std::vector<Tensor> parameters() const { return {}; }
+    // the rest of the Module surface (trait defaults in the reference; quantize.rs:462-482 overrides only forward
+    // and parameters): nothing to name or count, the mode flag is kept as set and the forward ignores it
+    std::vector<std::pair<std::string, Tensor>> named_parameters() const { return {}; }
+    size_t num_parameters() const { return 0; }
+    size_t trainable_params_count() const { return 0; }
+    void set_training(bool training) { training_ = training; }
+    bool is_training() const { return training_; }
 
   private:
     QuantizedTensor weight_q_;
     Tensor bias_;
     bool has_bias_ = false;
+    bool training_ = true;
     Device device_;
     std::shared_ptr<shrewq_linear> h_;
 };

@@ -403,6 +403,25 @@ class QuantizedLinear:
         """Inference only: no trainable parameters (quantize.rs:478-481)."""
         return []
 
+    # The rest of the Module surface a QuantizedLinear inherits from the trait's defaults (the reference
+    # overrides only forward and parameters, quantize.rs:462-482; containers such as DataParallel forward
+    # these calls to the module they wrap, distributed.rs:203-218).  They follow from parameters() being
+    # empty; the mode flag is kept and returned as set, the forward does not depend on it.
+    def named_parameters(self) -> list:
+        return []
+
+    def num_parameters(self) -> int:
+        return 0
+
+    def trainable_params_count(self) -> int:
+        return 0
+
+    def set_training(self, training: bool) -> None:
+        self._training = bool(training)
+
+    def is_training(self) -> bool:
+        return getattr(self, "_training", True)
+
     def last_kernel(self) -> str:
         return _lib.lib().shrewq_linear_last_kernel(self._h).decode()
 

@@ -85,6 +85,10 @@ static void test_quantized_linear_no_trainable_params() {
     Linear linear{Tensor::zeros({2, 4}, DType::F32, DEV), Tensor::zeros({1, 2}, DType::F32, DEV), true};
     QuantizedLinear ql = QuantizedLinear::from_linear(linear, QuantConfig::int8());
     CHECK(ql.parameters().empty());
+    // (beyond the reference's assertion: the rest of the Module surface follows from that)
+    CHECK(ql.named_parameters().empty() && ql.num_parameters() == 0 && ql.trainable_params_count() == 0);
+    ql.set_training(false);
+    CHECK(!ql.is_training());
 }
 
 // quantize.rs:748-755

@@ -124,3 +124,15 @@ def test_every_mode_of_the_python_mirror_marshals_its_call(monkeypatch):
     assert {"shrewq_quantize_f32", "shrewq_quantize_f32_ex", "shrewq_quantize_any", "shrewq_dequantize", "shrewq_dequantize_ex",
             "shrewq_absmax_f32", "shrewq_quantize_f32_given_amax", "shrewq_linear_create", "shrewq_linear_create_ex",
             "shrewq_pack_int4", "shrewq_linear_create_int4"} <= set(lib.calls)
+
+
+def test_quantized_linear_module_surface_without_a_device():
+    # the Module methods a QuantizedLinear inherits (quantize.rs:462-482 overrides only forward and parameters):
+    # pure host state, checked on an instance that never touched the library
+    ql = object.__new__(Q.QuantizedLinear)
+    ql._h = None
+    assert ql.parameters() == [] and ql.named_parameters() == []
+    assert ql.num_parameters() == 0 and ql.trainable_params_count() == 0
+    assert ql.is_training() is True
+    ql.set_training(False)
+    assert ql.is_training() is False
