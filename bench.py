@@ -262,6 +262,10 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL carries only barriers and one-float reductions here (the exchange is peer stores from the kernels, or
+        # an all-gather of a few MB): in-switch reduction buys nothing, and every multi-GPU run of this benchmark so
+        # far was made with it off
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     sdev = Device.get(dev)
     if args.force_kernel != "auto":
