@@ -16,6 +16,9 @@ Prints ONE JSON line on rank 0.  Timing: CUDA events on the launching stream, ba
 synchronize on both sides, max over ranks.  L2: every step uses a different copy of the
 weights out of a ring larger than twice the 126 MB L2.
 
+`--gpus N --parallel replicas` is the data-parallel alternative (every GPU the whole block on its own
+batch, weak scaling, no collective); the default `shard` is the configured output-channel split.
+
 `--impl reference` times the reference's own CPU algorithm for the same step (the oracle
 port: single-threaded f64 dequantization on every call, as quantize.rs:214-224,465 does,
 then an f32 GEMM on all host cores) — the Rust reference cannot be built on this image.
@@ -241,6 +244,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU exchange: 'fused' = peer stores from the kernel epilogue, 'nccl' = all-gather")
+    ap.add_argument("--parallel", default="shard", choices=["shard", "replicas"],
+                    help="--gpus N: 'shard' = the weights split by output channel (strong scaling, the configured path); "
+                         "'replicas' = every GPU runs the whole block on a batch of its own (weak scaling, no collective)")
     ap.add_argument("--force-kernel", default="auto",
                     help="kernel family for every forward of the run (see shrewq_force_kernel); experiments only")
     args = ap.parse_args()
@@ -272,18 +278,24 @@ def main():
         _lib.check(_lib.lib().shrewq_force_kernel(args.force_kernel.encode()), None)
     cfg = QuantConfig.int8_per_channel()
     M = wl["M"]
+    # replicas: the model is not split; sw/sr are the world size and rank the sharding sees
+    replicas = world > 1 and args.parallel == "replicas"
+    sw, sr = (1, 0) if replicas else (world, rank)
+    own_group = None
+    if replicas:   # every rank's layers live in a group of one (new_group is collective: all ranks create all groups)
+        own_group = [dist.new_group([r]) for r in range(world)][rank]
     if wl["kind"] == "stack" and world > 1:
         raise SystemExit("bench.py: the stack workloads (configs 1 and 2) run on one GPU; --gpus N takes the default workload")
 
     # ---- build the rank's shards; a ring of weight copies defeats L2 between steps ----
     def make_shard(n, k, seed):
-        n0, n1 = plan_shards(n, world).rows(rank)
+        n0, n1 = plan_shards(n, sw).rows(sr)
         w = gpu_weight(n, k, seed, dev)[n0:n1].contiguous()
         return QuantizedLinear.from_linear(Linear(w, None), cfg)
 
     if wl["kind"] == "mlp":
         dm, dff = wl["d_model"], wl["d_ff"]
-        shard_bytes = (2 * dff * dm + dm * dff) // world
+        shard_bytes = (2 * dff * dm + dm * dff) // sw
         in_features = dm
         flops_step = 2 * M * (2 * dff * dm + dm * dff)
     elif wl["kind"] == "stack":
@@ -292,13 +304,13 @@ def main():
         in_features = layers[0][1]
         flops_step = sum(2 * M * n * k for n, k, _, _ in layers)
     else:
-        shard_bytes = wl["N"] * wl["K"] // world
+        shard_bytes = wl["N"] * wl["K"] // sw
         in_features = wl["K"]
         flops_step = 2 * M * wl["N"] * wl["K"]
     ring = max(2, -(-2 * L2_BYTES // shard_bytes) + 1)
     if wl["kind"] == "stack":
         ring = min(ring, 32)   # config 1 is 0.2 MB of codes: no ring of sensible length exceeds L2, and the line says so
-    fused = world > 1 and args.gather == "fused"
+    fused = sw > 1 and args.gather == "fused"
     x_dt = torch.float32 if wl["kind"] == "stack" else torch.bfloat16
 
     class Stack:
@@ -337,13 +349,13 @@ def main():
             if fused:
                 models.append(FusedShardedGatedMLP(g, u, d, dff, dm, M, share=models[0] if models else None))
             else:
-                models.append(ShardedGatedMLP(g, u, d, dff, dm))
+                models.append(ShardedGatedMLP(g, u, d, dff, dm, group=own_group))
         else:
             q = make_shard(wl["N"], wl["K"], 0)
             if fused:
                 models.append(FusedShardedLinear(wl["N"], q, None, M, torch.bfloat16, out=models[0].out if models else None))
             else:
-                models.append(ShardedLinear(wl["N"], lambda x, out, _q=q: _q.forward(x, out=out)))
+                models.append(ShardedLinear(wl["N"], lambda x, out, _q=q: _q.forward(x, out=out), group=own_group))
             models[-1].shard = q
     torch.cuda.synchronize()
 
@@ -371,7 +383,7 @@ def main():
     graphs, outs = [], []
     # NCCL collectives captured in a graph left the processes hanging at exit on this software
     # stack (results were printed, the ranks never ended): the NCCL variant is launched eagerly
-    use_graphs = not args.no_graph and not (world > 1 and not fused)
+    use_graphs = not args.no_graph and not (sw > 1 and not fused)
     if use_graphs:
         try:
             for i in range(ring):
@@ -422,7 +434,8 @@ def main():
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_total = float(ms.item())
     launches = launches_per_step * args.steps if use_graphs else sdev.launch_count() - launches0
-    value = M * args.steps / (ms_total * 1e-3)
+    rows_per_step = M * (world if replicas else 1)   # replicas: every GPU processes a batch of its own
+    value = rows_per_step * args.steps / (ms_total * 1e-3)
 
     # ---- end to end: pinned host input in, host output back, every step ----
     def e2e_step(i):
@@ -443,7 +456,7 @@ def main():
     t_e2e = torch.tensor([time.perf_counter() - t0], device=dev)
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
-    e2e_value = M * args.steps / float(t_e2e.item())
+    e2e_value = rows_per_step * args.steps / float(t_e2e.item())
     e2e_info = {"mode": "sequential: copy in, compute, copy out, synchronize, per step",
                 "sequential_value": e2e_value}
 
@@ -562,13 +575,13 @@ def main():
     out = {
         "metric": "quantized_linear_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": ("f32" if wl["kind"] == "stack" else "bf16") + " x int8 -> f32 accumulate", "data": "synthetic",
+        "scaling": "weak" if replicas else "strong", "vs_baseline": None, "dtype": ("f32" if wl["kind"] == "stack" else "bf16") + " x int8 -> f32 accumulate", "data": "synthetic",
         "config": {"workload": args.workload, **({"forced_kernel": args.force_kernel} if args.force_kernel != "auto" else {}), **config_of(wl),
-                   "weights": "INT8 per-channel, N(0,0.02)", "sharding": "none (single GPU)" if world == 1 else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
+                   "weights": "INT8 per-channel, N(0,0.02)", "sharding": "none (single GPU)" if world == 1 else f"none: {world} independent replicas, each on its own batch of {M} rows, no collective" if replicas else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
                    "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU)" + (" > 2x L2" if ring * shard_bytes > 2 * L2_BYTES else "; the whole configuration is smaller than L2, so the weights stay L2-resident as they would in use")},
-        "tflops": flops_step * args.steps / (ms_total * 1e-3) / 1e12,
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
-                "d2h_bytes_per_step": y_host.numel() * y_host.element_size(), **e2e_info},
+        "tflops": flops_step * (world if replicas else 1) * args.steps / (ms_total * 1e-3) / 1e12,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * (world if replicas else 1),
+                "d2h_bytes_per_step": y_host.numel() * y_host.element_size() * (world if replicas else 1), **e2e_info},
         "gpu_launches": int(launches), "launch_mode": "cuda graph replay (one graph per ring entry)" if use_graphs else "host launches", "clocks": clocks, "roofline": roof,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
