@@ -90,7 +90,7 @@ class ClockSampler:
     """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_power_cap,utilization.gpu")
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
@@ -120,19 +120,27 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smax, reasons = [], None, set()
+        sm, busy, smax, reasons = [], [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             try:
-                sm.append(float(r[1]))
+                mhz = float(r[1])
                 smax = float(r[2])
                 for nm, v in zip(names, r[5:9]):
                     if v.lower().startswith("active"):
                         reasons.add(nm)
             except Exception:
+                continue
+            sm.append(mhz)
+            try:
+                if float(r[9]) >= 10.0:
+                    busy.append(mhz)
+            except Exception:
                 pass
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        # the median is taken over the samples that saw the GPU busy (all samples if none reported a utilisation)
+        use = busy or sm
+        return {"sm_mhz": statistics.median(use) if use else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(use), "samples_all": len(sm)}
 
 
 # ---------------------------------------------------------------------------------------------

@@ -56,3 +56,17 @@ def test_stack_workloads_are_well_formed():
             assert all(layers[i][1] == layers[i - 1][0] for i in range(1, len(layers))), name
     # config 2: 4 blocks of (4 x 256->256, 256->1024, 1024->256) and the 256->50257 head: 16,011,520 codes
     assert sum(n * k for n, k, _, _ in bench.stack_layers(bench.WORKLOADS["tinygpt_stack_m4096"])) == 16011520
+
+
+def test_clock_summary_takes_the_median_of_the_samples_under_load():
+    sys.path.insert(0, ROOT)
+    import bench
+    c = bench.ClockSampler(0)
+    c.proc = type("P", (), {"terminate": lambda s: None, "wait": lambda s, timeout=0: None})()
+    idle = ["0", "1965", "1965", "300.0", "0x0", "Not Active", "Not Active", "Not Active", "Not Active", "0"]
+    busy = lambda mhz: ["0", str(mhz), "1965", "950.0", "0x4", "Not Active", "Not Active", "Not Active", "Active", "98"]  # noqa: E731
+    c.rows = [idle, busy(1500), busy(1400), busy(1300), ["cut off"]]
+    out = c.stop()
+    assert out == {"sm_mhz": 1400.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"], "samples": 3, "samples_all": 4}
+    c.rows = [idle[:9] + ["[N/A]"]]      # no utilisation reported: every sample counts
+    assert c.stop()["sm_mhz"] == 1965.0
