@@ -585,7 +585,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "weak" if replicas else "strong", "vs_baseline": None, "dtype": ("f32" if wl["kind"] == "stack" else "bf16") + " x int8 -> f32 accumulate", "data": "synthetic",
         "config": {"workload": args.workload, **({"forced_kernel": args.force_kernel} if args.force_kernel != "auto" else {}), **config_of(wl),
-                   "weights": "INT8 per-channel, N(0,0.02)", "sharding": "none (single GPU)" if world == 1 else f"none: {world} independent replicas, each on its own batch of {M} rows, no collective" if replicas else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
+                   "weights": f"INT8 per-channel, N(0,{wl.get('std', 0.02)})", "sharding": "none (single GPU)" if world == 1 else f"none: {world} independent replicas, each on its own batch of {M} rows, no collective" if replicas else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
                    "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU)" + (" > 2x L2" if ring * shard_bytes > 2 * L2_BYTES else "; the whole configuration is smaller than L2, so the weights stay L2-resident as they would in use")},
         "tflops": flops_step * (world if replicas else 1) * args.steps / (ms_total * 1e-3) / 1e12,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * (world if replicas else 1),
