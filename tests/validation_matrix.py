@@ -1,0 +1,106 @@
+"""Runs the GPU parity tests once per prepared, opt-in code path, each in a process of its own.
+
+    python tests/validation_matrix.py [--only NAME[,NAME...]] [--list] [--timeout SECONDS] [--json PATH]
+
+The library's default paths are covered by `python -m pytest tests -m gpu`.  The paths that are built and
+checked on the CPU model but switched off until they have passed on a GPU (environment switches, forced
+kernel families, tests behind SHREWQ_TEST_UNVALIDATED=1) are listed below, safest first.  Every entry runs
+as a separate pytest process, so a failure in one leaves the others standing; the run STOPS at the first
+entry whose output shows a CUDA fault or a kernel that gave up a bounded wait, because whatever runs next on
+that GPU would not be trustworthy, and the faulting path has to be read before it runs again.  Prints one
+line per entry and, with --json, writes the same as a list of records.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIN = "tests/test_gpu_linear.py"
+
+# (name, environment, pytest arguments)
+MATRIX = [
+    ("default", {}, ["tests"]),
+    ("gemv-pdl", {"SHREWQ_GEMV_PDL": "1"}, [LIN, "-k", "gemv or config3 or config4"]),
+    ("batch-quantize", {"SHREWQ_TEST_UNVALIDATED": "1", "SHREWQ_BATCH_QUANTIZE": "1"}, ["tests/test_gpu_quantize.py"]),
+    ("shard-per-tensor", {"SHREWQ_TEST_UNVALIDATED": "1"}, ["tests/test_gpu_quantize.py", "-k", "row_shards"]),
+    ("splitk-large-tiles", {"SHREWQ_TC_SPLITK_MAXTOK": "256"}, [LIN]),
+    ("split-by-waves", {"SHREWQ_TC_SPLIT_WAVES": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}, [LIN]),
+    ("gated-tile-256", {"SHREWQ_TC_TOK_GATED": "256"}, [LIN, "-k", "config4 or gate"]),
+    ("tile-256-tail-split", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1"}, [LIN, "-k", "config4 or config3"]),
+    ("mma-bf16", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "mma and not f16"]),
+    ("mma-f16", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "mma_f16 or mma_gated"]),
+    ("mma-f16-auto", {"SHREWQ_AUTO_MMA_F16": "1", "SHREWQ_GEMV_PDL": "1"}, [LIN, "tests/test_zz_no_alloc.py"]),
+    ("f32-on-tensor-cores", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "f32_activations_on_tensor or config2"]),
+    ("f32-on-tensor-cores-auto", {"SHREWQ_AUTO_TC_F32": "1"}, [LIN]),
+    ("other-modes", {"SHREWQ_TEST_UNVALIDATED": "1"}, ["tests/test_gpu_modes.py"]),
+    ("cta-pair", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "cta_pair"]),
+    ("cta-pair-auto", {"SHREWQ_AUTO_PAIR": "1"}, [LIN]),
+    ("cta-pair-auto-tail", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1"}, [LIN, "-k", "config4 or config3"]),
+    # last: mixed operand formats (f16 weights beside bf16 activations) have never run here
+    ("f16-weights", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "f16_weights"]),
+    ("f16-weights-all", {"SHREWQ_TC_A_F16": "1"}, [LIN]),
+]
+
+# what in a test run's output means the GPU, or the context, can no longer be trusted
+FAULT_MARKS = ("illegal memory access", "illegal instruction", "unspecified launch failure", "misaligned address",
+               "device-side assert", "Xid", "gave up a bounded wait", "CUDA error: an illegal", "launch timed out")
+
+
+def run_entry(name, env, args, timeout):
+    cmd = [sys.executable, "-m", "pytest", *args, "-m", "gpu", "-q", "-x", "-p", "no:cacheprovider"]
+    t0 = time.time()
+    try:
+        r = subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, **env), capture_output=True, text=True, timeout=timeout)
+        out, rc = r.stdout + r.stderr, r.returncode
+    except subprocess.TimeoutExpired as e:
+        out = ((e.stdout or b"").decode(errors="replace") if isinstance(e.stdout, bytes) else (e.stdout or "")) + "\n[timed out]"
+        rc = 124
+    lines = [l for l in out.strip().splitlines() if l.strip()]
+    fault = next((m for m in FAULT_MARKS if m in out), None)
+    if rc == 124:
+        fault = fault or "timed out"
+    return {"name": name, "env": env, "args": args, "rc": rc, "seconds": round(time.time() - t0, 1),
+            "summary": lines[-1] if lines else "", "fault": fault,
+            "tail": lines[-25:] if rc not in (0, 5) else []}      # pytest's 5 = nothing selected
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--list", action="store_true")
+    ap.add_argument("--timeout", type=int, default=900, help="seconds per entry")
+    ap.add_argument("--json", default="")
+    a = ap.parse_args()
+    names = [n for n in a.only.split(",") if n]
+    unknown = [n for n in names if n not in {m[0] for m in MATRIX}]
+    if unknown:
+        raise SystemExit(f"unknown entries: {unknown}")
+    todo = [m for m in MATRIX if not names or m[0] in names]
+    if a.list:
+        for name, env, args in todo:
+            print(name, " ".join(f"{k}={v}" for k, v in env.items()), "::", " ".join(args))
+        return 0
+    records = []
+    for name, env, args in todo:
+        rec = run_entry(name, env, args, a.timeout)
+        records.append(rec)
+        print(f"{name:28s} rc={rec['rc']:<3d} {rec['seconds']:7.1f}s  {rec['summary']}", flush=True)
+        for l in rec["tail"]:
+            print("    | " + l, flush=True)
+        if a.json:
+            with open(a.json, "w") as f:
+                json.dump(records, f, indent=1)
+        if rec["fault"]:
+            print(f"stopping: '{rec['fault']}' in the output of {name}; read that path before running anything else on this GPU",
+                  flush=True)
+            return 3
+    return 0 if all(r["rc"] in (0, 5) for r in records) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
