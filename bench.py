@@ -78,6 +78,18 @@ def stack_layers(wl):
     return [tuple(l) for l in wl["layers"]]
 
 
+def stack_forward(x, linears, spec, bufs, stand_ins, chain, relu_code=1, none_code=0):
+    """One pass over the Linears of a stack workload.  `linears[i].forward(src, epilogue=, out=)` writes layer i's
+    output into bufs[i].  chain: every layer reads the previous layer's output (config 1).  Otherwise (config 2, where
+    the glue between the layers is not part of the path) a layer as wide as x reads x and the others read the resident
+    stand-in of their input width.  Returns the last layer's output."""
+    y = x
+    for lin, (n, k, relu, _), buf in zip(linears, spec, bufs):
+        src = y if chain else (x if k == x.shape[1] else stand_ins[k])
+        y = lin.forward(src, epilogue=relu_code if relu else none_code, out=buf)
+    return y
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -339,14 +351,8 @@ def main():
                 Stack.stand_ins = {k: torch.randn(M, k, device=dev, generator=gs) for k in sorted({k for _, k, _, _ in layers})}
 
         def forward(self, x):
-            y = x
-            for (ql, relu), (n, k, _, _), buf in zip(self.layers, layers, Stack.bufs):
-                if wl["chain"]:
-                    src = y
-                else:
-                    src = x if k == x.shape[1] else Stack.stand_ins[k]
-                y = ql.forward(src, epilogue=_lib.EPILOGUE_RELU if relu else _lib.EPILOGUE_NONE, out=buf)
-            return y
+            return stack_forward(x, [ql for ql, _ in self.layers], layers, Stack.bufs, Stack.stand_ins, wl["chain"],
+                                 _lib.EPILOGUE_RELU, _lib.EPILOGUE_NONE)
 
     models = []
     for c in range(ring):

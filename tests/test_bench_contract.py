@@ -70,3 +70,38 @@ def test_clock_summary_takes_the_median_of_the_samples_under_load():
     assert out == {"sm_mhz": 1400.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"], "samples": 3, "samples_all": 4}
     c.rows = [idle[:9] + ["[N/A]"]]      # no utilisation reported: every sample counts
     assert c.stop()["sm_mhz"] == 1965.0
+
+
+def test_stack_forward_routes_inputs_and_buffers():
+    # the routing of the stack workloads' step, with stand-in layers on CPU tensors
+    sys.path.insert(0, ROOT)
+    import torch
+
+    import bench
+
+    class FakeLinear:
+        def __init__(self, n, k, seed):
+            self.w = torch.randn(n, k, generator=torch.Generator().manual_seed(seed))
+
+        def forward(self, src, epilogue=0, out=None):
+            y = src @ self.w.t()
+            out.copy_(torch.relu(y) if epilogue == 1 else y)
+            return out
+
+    M = 5
+    # config 1: chained, ReLU after the first layer
+    spec = bench.stack_layers(bench.WORKLOADS["mnist_mlp_m64"])
+    lins = [FakeLinear(n, k, i) for i, (n, k, _, _) in enumerate(spec)]
+    bufs = [torch.empty(M, n) for n, _, _, _ in spec]
+    x = torch.rand(M, spec[0][1])
+    y = bench.stack_forward(x, lins, spec, bufs, {}, True)
+    want = torch.relu(x @ lins[0].w.t()) @ lins[1].w.t()
+    assert y is bufs[-1] and torch.allclose(y, want, atol=1e-5)
+    # config 2 (one block and a small head): 256-wide layers read x, the 1024-wide one its stand-in
+    spec = [(256, 256, False, False)] * 4 + [(1024, 256, False, True), (256, 1024, False, True), (300, 256, False, False)]
+    lins = [FakeLinear(n, k, i) for i, (n, k, _, _) in enumerate(spec)]
+    bufs = [torch.empty(M, n) for n, _, _, _ in spec]
+    x, s1024 = torch.randn(M, 256), torch.randn(M, 1024)
+    y = bench.stack_forward(x, lins, spec, bufs, {256: torch.zeros(M, 256), 1024: s1024}, False)
+    assert y is bufs[-1] and torch.allclose(y, x @ lins[-1].w.t(), atol=1e-4)
+    assert torch.allclose(bufs[5], s1024 @ lins[5].w.t(), atol=1e-3) and torch.allclose(bufs[4], x @ lins[4].w.t(), atol=1e-4)
