@@ -6,6 +6,7 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     python -m shrew_b200.kernel_bench lin        # forward kernels over a batch sweep
     python -m shrew_b200.kernel_bench lin 4096 4096 1,16,256   # one layer shape, chosen batches
     SHREWQ_BENCH_KERNELS=gemv,mma,mma-f16,mma-w4,tcgen05,tcgen05-2cta python -m shrew_b200.kernel_bench lin   # other kernel families
+    SHREWQ_BENCH_KERNELS=simt,tcgen05-f32 python -m shrew_b200.kernel_bench lin 50257 256 4096   # f32 activations (configs 1, 2)
     (mma-w4 = packed INT4 weights, also needs SHREWQ_EXPERIMENTAL_MODES=1; "+suffix"es set a tuning variable
     for that measurement: tcgen05+af16, tcgen05+waves+maxtok, tcgen05-2cta+tail, gemv+pdl, tcgen05+tok256 ...)
     python -m shrew_b200.kernel_bench mlp 512    # the Llama MLP block (gate/up + down) under every prepared tuning setting
@@ -112,12 +113,17 @@ def bench_lin(shapes, batches):
         lins = _layers(N, K, nbuf)
         lins4 = _layers_int4(N, K, 2 * nbuf) if any(k.split("+")[0] == "mma-w4" for k in kernels) and K % 128 == 0 else None
         for M in batches:
-            x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
-            y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            x16 = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            y16 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            x32, y32 = x16.float(), torch.empty(M, N, device="cuda", dtype=torch.float32)
             for force in kernels:
                 family, *variants = force.split("+")
                 if (family == "gemv" and M > 16) or (family.startswith("mma") and M > 64):
                     continue
+                # "simt" (the general f32 kernel) and "tcgen05-f32" (two bf16 passes on the tensor cores) are the two
+                # routes of f32 activations (configs 1 and 2): timed with f32 input and output
+                f32 = family in ("simt", "tcgen05-f32")
+                x, y, sx = (x32, y32, 4) if f32 else (x16, y16, 2)
                 w4 = family == "mma-w4"
                 if w4 and (lins4 is None or M > 32):
                     continue
@@ -137,8 +143,8 @@ def bench_lin(shapes, batches):
                 except Exception as e:  # noqa: BLE001
                     print(json.dumps(dict(kernel=force, M=M, N=N, K=K, error=str(e))), flush=True)
                     continue
-                by = (N * K // 2 if w4 else N * K) + 4 * N + M * K * 2 + M * N * 2
-                print(json.dumps(dict(kernel=force, M=M, N=N, K=K, us=t * 1e6, GBs=by / t / 1e9,
+                by = (N * K // 2 if w4 else N * K) + 4 * N + M * K * sx + M * N * sx
+                print(json.dumps(dict(kernel=force, M=M, N=N, K=K, x="f32" if f32 else "bf16", us=t * 1e6, GBs=by / t / 1e9,
                                       TFs=2 * M * N * K / t / 1e12)), flush=True)
         L.shrewq_force_kernel(b"auto")
         for var, _ in _SUFFIX.values():
