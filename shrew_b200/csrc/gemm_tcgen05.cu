@@ -3,6 +3,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "gemm_tcgen05_kernels.cuh"
@@ -229,6 +230,19 @@ int choose_tok(const ForwardArgs &a, int chan_per_tile, int sm_count) {
         const long waves = (tiles + sm_count - 1) / sm_count;
         return (double)tiles / (double)(waves * sm_count);
     };
+    // SHREWQ_TC_TILE_RULE=cost (opt-in; a launch rule only, but it sends gate/up launches to the 256-token tile, whose
+    // parity has been checked on the CPU model only): compare waves x cost of a tile's k-loop instead of SM fill.
+    // The issuing thread needs ~1100 cycles per 128 k with 128-token tiles and ~1400 with 256-token tiles that carry
+    // twice the tokens (in-kernel trace), so a 128-token tile is only worth 0.64 of its tokens.
+    if (const char *e = getenv("SHREWQ_TC_TILE_RULE")) {
+        if (!strcmp(e, "cost")) {
+            auto waves = [&](int tok) {
+                const long tiles = n_tiles * (long)((a.M + tok - 1) / tok);
+                return (tiles + sm_count - 1) / sm_count;
+            };
+            return waves(128) * 1100 < waves(256) * 1400 ? 128 : 256;
+        }
+    }
     return fill(128) * 0.85 > fill(256) ? 128 : 256;
 }
 

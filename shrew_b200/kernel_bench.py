@@ -193,6 +193,7 @@ def bench_trace(N, K, batches, kernel="tcgen05"):
 MLP_SETTINGS = [
     ("default", {}),
     ("gated256", {"SHREWQ_TC_TOK_GATED": "256"}),
+    ("cost-rule", {"SHREWQ_TC_TILE_RULE": "cost"}),
     ("gated256+tail", {"SHREWQ_TC_TOK_GATED": "256", "SHREWQ_TC_TAILSPLIT": "1"}),
     ("tok256", {"SHREWQ_TC_TOK": "256"}),
     ("tok256+tail", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1"}),

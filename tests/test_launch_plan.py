@@ -137,3 +137,15 @@ def test_token_tile_of_gate_up_launches_can_be_set_on_its_own(monkeypatch):
     rc, name, p = plan(512, 11008, 4096, gated=1)
     assert (rc, name) == (0, "tcgen05") and (p["tok"], p["n_tiles"], p["m_tiles"], p["splits"]) == (256, 172, 2, 1)
     assert plan(512, 4096, 11008, gated=0)[2]["tok"] == 128
+
+
+def test_cost_rule_for_the_token_tile(monkeypatch):
+    # SHREWQ_TC_TILE_RULE=cost: waves x (1100 | 1400 cycles per 128 k) instead of SM fill.  The benchmark's block at
+    # batch 512: gate/up (172 channel tiles) 5 x 1100 > 3 x 1400 -> 256 tokens; down (32 tiles) 1 x 1100 < 1 x 1400 -> 128
+    assert plan(512, 11008, 4096, gated=1)[2]["tok"] == 128
+    monkeypatch.setenv("SHREWQ_TC_TILE_RULE", "cost")
+    assert plan(512, 11008, 4096, gated=1)[2]["tok"] == 256
+    assert plan(512, 4096, 11008, gated=0)[2]["tok"] == 128
+    assert plan(1024, 4096, 4096)[2]["tok"] == 256        # 2 waves of 128-token tiles against 1 of 256
+    assert plan(512, 4096, 4096)[2]["tok"] == 128
+    assert plan(100, 4096, 4096)[2]["tok"] == 128         # up to 128 tokens the smallest covering tile, as before

@@ -31,6 +31,7 @@ MATRIX = [
     ("splitk-large-tiles", {"SHREWQ_TC_SPLITK_MAXTOK": "256"}, [LIN]),
     ("split-by-waves", {"SHREWQ_TC_SPLIT_WAVES": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}, [LIN]),
     ("gated-tile-256", {"SHREWQ_TC_TOK_GATED": "256"}, [LIN, "-k", "config4 or gate"]),
+    ("tile-cost-rule", {"SHREWQ_TC_TILE_RULE": "cost"}, [LIN]),
     ("tile-256-tail-split", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1"}, [LIN, "-k", "config4 or config3"]),
     ("mma-bf16", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "mma and not f16"]),
     ("mma-f16", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "mma_f16 or mma_gated"]),
