@@ -171,12 +171,13 @@ def host_weight(n, k, seed):
 # ---------------------------------------------------------------------------------------------
 # the CPU arm: reference algorithm on host cores
 # ---------------------------------------------------------------------------------------------
-def cpu_step_factory(wl):
+def cpu_step_factory(wl, per_tensor=False):
     """Returns (step_fn, tokens, description).  Each call performs one forward exactly as the
     reference does: dequantize every weight afresh (single thread, f64 then f32), then f32
     GEMM on all cores (torch CPU as stand-in for the `gemm` crate), then bias / activation."""
     from oracle import shrew_oracle as oracle
     oracle.build()
+    gran = oracle.PER_TENSOR if per_tensor else oracle.PER_CHANNEL
     M = wl["M"]
     rng = np.random.default_rng(1)
     if wl["kind"] == "mlp":
@@ -191,7 +192,7 @@ def cpu_step_factory(wl):
         w = host_weight(n, k, i)
         if wl["kind"] == "stack":
             w = w * np.float32(wl["std"] / 0.02)
-        q, s = oracle.np_quantize_f32(w, oracle.PER_CHANNEL)
+        q, s = oracle.np_quantize_f32(w, gran)
         qs.append((q, s, np.empty((n, k), dtype=np.float32)))
     if wl["kind"] == "stack":  # f32 activations: U(0,1) for config 1, N(0,1) stand-ins per input width for config 2
         draw = (lambda k: rng.random((M, k), dtype=np.float32)) if wl["uniform"] else (lambda k: rng.standard_normal((M, k), dtype=np.float32))
@@ -202,7 +203,7 @@ def cpu_step_factory(wl):
 
     def lin(i, inp):
         q, s, buf = qs[i]
-        oracle.dequantize_like_reference(q, s, oracle.PER_CHANNEL, buf)  # quantize.rs:465, every call
+        oracle.dequantize_like_reference(q, s, gran, buf)  # quantize.rs:465, every call
         return inp @ torch.from_numpy(buf).t()                          # quantize.rs:468-469
 
     def step():
@@ -228,7 +229,7 @@ def run_reference_arm(args, wl, name):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    step, tokens, sample = cpu_step_factory(wl)
+    step, tokens, sample = cpu_step_factory(wl, args.granularity == "per_tensor")
     for _ in range(max(1, min(args.warmup, 2))):
         step()
     t0 = time.perf_counter()
@@ -240,7 +241,7 @@ def run_reference_arm(args, wl, name):
         "impl": "reference", "metric": "quantized_linear_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, **config_of(wl)},
+        "config": {"workload": name, **config_of(wl), "weights": f"INT8 {args.granularity.replace('_', '-')}"},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "Rust reference (shrew-cpu: gemm 0.18.2 + rayon) cannot be built on this image; this is the CPU port of "
@@ -264,6 +265,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU exchange: 'fused' = peer stores from the kernel epilogue, 'nccl' = all-gather")
+    ap.add_argument("--granularity", default="per_channel", choices=["per_channel", "per_tensor"],
+                    help="one scale per output channel (all configs) or one per tensor (the other half of config 3); "
+                         "on several GPUs only per_channel (shards of a per-tensor weight must first agree on amax)")
     ap.add_argument("--parallel", default="shard", choices=["shard", "replicas"],
                     help="--gpus N: 'shard' = the weights split by output channel (strong scaling, the configured path); "
                          "'replicas' = every GPU runs the whole block on a batch of its own (weak scaling, no collective)")
@@ -296,7 +300,10 @@ def main():
     sdev = Device.get(dev)
     if args.force_kernel != "auto":
         _lib.check(_lib.lib().shrewq_force_kernel(args.force_kernel.encode()), None)
-    cfg = QuantConfig.int8_per_channel()
+    cfg = QuantConfig.int8() if args.granularity == "per_tensor" else QuantConfig.int8_per_channel()
+    if args.granularity == "per_tensor" and world > 1 and args.parallel == "shard":
+        raise SystemExit("bench.py: --granularity per_tensor with sharded weights is not a benchmark workload "
+                         "(use sharded.quantize_row_shard for it); run it on one GPU or with --parallel replicas")
     M = wl["M"]
     # replicas: the model is not split; sw/sr are the world size and rank the sharding sees
     replicas = world > 1 and args.parallel == "replicas"
@@ -591,7 +598,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "weak" if replicas else "strong", "vs_baseline": None, "dtype": ("f32" if wl["kind"] == "stack" else "bf16") + " x int8 -> f32 accumulate", "data": "synthetic",
         "config": {"workload": args.workload, **({"forced_kernel": args.force_kernel} if args.force_kernel != "auto" else {}), **config_of(wl),
-                   "weights": f"INT8 per-channel, N(0,{wl.get('std', 0.02)})", "sharding": "none (single GPU)" if world == 1 else f"none: {world} independent replicas, each on its own batch of {M} rows, no collective" if replicas else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
+                   "weights": f"INT8 {args.granularity.replace('_', '-')}, N(0,{wl.get('std', 0.02)})", "sharding": "none (single GPU)" if world == 1 else f"none: {world} independent replicas, each on its own batch of {M} rows, no collective" if replicas else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
                    "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU)" + (" > 2x L2" if ring * shard_bytes > 2 * L2_BYTES else "; the whole configuration is smaller than L2, so the weights stay L2-resident as they would in use")},
         "tflops": flops_step * (world if replicas else 1) * args.steps / (ms_total * 1e-3) / 1e12,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * (world if replicas else 1),
@@ -599,7 +606,7 @@ def main():
         "gpu_launches": int(launches), "launch_mode": "cuda graph replay (one graph per ring entry)" if use_graphs else "host launches", "clocks": clocks, "roofline": roof,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cstep, tokens, sample = cpu_step_factory(wl)
+        cstep, tokens, sample = cpu_step_factory(wl, args.granularity == "per_tensor")
         cstep()
         t0 = time.perf_counter()
         n_cpu = 0
