@@ -11,6 +11,8 @@ two sharded layers.  Metric: tokens/s (rows of the batch per second) for the who
 Other workloads (`--workload`): single Linears of config 3, the block at batch 1, and, on one
 GPU, the f32-activation configs 1 (`mnist_mlp_m64`) and 2 (`tinygpt_stack_m4096`: the 25 Linears of
 the TinyGPT-shaped stack; its vocabulary head is bound by the 823 MB f32 output it writes).
+`--workload quantize_RxC` (config 5) times the per-channel quantizer instead and reports GB/s at
+5 B/element + 8 B/row, with the single-threaded CPU restatement beside it.
 
 Prints ONE JSON line on rank 0.  Timing: CUDA events on the launching stream, barrier and
 synchronize on both sides, max over ranks.  L2: every step uses a different copy of the
@@ -62,6 +64,135 @@ WORKLOADS = {
                                 layers=([(256, 256, False, False)] * 4 + [(1024, 256, False, True), (256, 1024, False, True)]) * 4
                                 + [(50257, 256, False, False)]),
 }
+
+
+# config 5: the quantizer's bandwidth sweep (f32 ~N(0,1) with 1 % of the entries x50, per-channel absmax INT8).  These
+# workloads report GB/s at 5 B/element + 8 B/row instead of tokens/s (there are no tokens in a weight matrix).
+for _r, _c in ((1024, 1024), (4096, 4096), (8192, 8192), (16384, 8192), (16384, 16384), (32768, 16384)):
+    WORKLOADS[f"quantize_{_r}x{_c}"] = dict(kind="quantize", rows=_r, cols=_c)
+
+
+def outlier_matrix_host(rows, cols, seed=0):
+    rng = np.random.default_rng(seed)
+    w = rng.standard_normal((rows, cols), dtype=np.float32)
+    w[rng.random((rows, cols), dtype=np.float32) < 0.01] *= np.float32(50.0)
+    return w
+
+
+def quantize_cpu_sample(wl, target_elements=32 << 20):
+    """(step_fn, bytes per step, description): the oracle's quantize_tensor (quantize.rs:194-205, one thread, the f64
+    widening copy included) on the first rows of the matrix, about 32 M elements of them."""
+    from oracle import shrew_oracle as oracle
+    oracle.build()
+    rows = max(1, min(wl["rows"], target_elements // wl["cols"]))
+    w = outlier_matrix_host(rows, wl["cols"])
+    return (lambda: oracle.quantize_f32(w, oracle.PER_CHANNEL)), 5 * rows * wl["cols"] + 8 * rows, \
+        f"first {rows} of {wl['rows']} rows per step, oracle C restatement on 1 thread"
+
+
+def run_quantize_reference(args, wl, name):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0
+    step, nbytes, sample = quantize_cpu_sample(wl)
+    step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    val = nbytes * args.steps / dt / 1e9
+    print(json.dumps({
+        "impl": "reference", "metric": "quantize_gb_per_s", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 -> int8 (f64 arithmetic)", "data": "synthetic",
+        "config": {"workload": name, **config_of(wl)},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+    return 0
+
+
+def run_quantize_gpu(args, wl, name):
+    """Config 5 on one GPU: quantize_tensor (per-channel) over a ring of matrices larger than twice L2."""
+    import ctypes
+
+    from shrew_b200 import QuantConfig, _lib, quantize_tensor
+    from shrew_b200.quantize import Device
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        raise SystemExit("bench.py: the quantize workloads run on one GPU (rows are independent: N GPUs are N replicas)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device — this path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    sdev = Device.get(dev)
+    R, C = wl["rows"], wl["cols"]
+    cfg = QuantConfig.int8_per_channel()
+    nbytes = 5 * R * C + 8 * R
+    ring = max(1, -(-2 * L2_BYTES // (4 * R * C)))
+    g = torch.Generator(device=dev).manual_seed(0)
+    ws = []
+    for _ in range(ring):
+        w = torch.randn(R, C, device=dev, generator=g)
+        w[torch.rand(R, C, device=dev, generator=g) < 0.01] *= 50.0
+        ws.append(w)
+    for i in range(args.warmup):
+        quantize_tensor(ws[i % ring], cfg)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = sdev.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        quantize_tensor(ws[i % ring], cfg)
+    e1.record()
+    torch.cuda.synchronize()
+    sdev.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = sdev.launch_count() - launches0
+    value = nbytes * args.steps / (ms * 1e-3) / 1e9
+    # end to end: host matrix in, host codes and scales out, through the host-buffer entry point
+    w_host = ws[0].cpu().pin_memory()
+    q_host = torch.empty((R, C), dtype=torch.int8).pin_memory()
+    s_host = torch.empty(R, dtype=torch.float64).pin_memory()
+
+    def e2e_step():
+        sdev.bind_stream()
+        _lib.check(_lib.lib().shrewq_quantize_f32_host(sdev.handle, ctypes.c_void_p(w_host.data_ptr()), R, C, 1,
+                                                       ctypes.c_void_p(q_host.data_ptr()), ctypes.c_void_p(s_host.data_ptr())),
+                   sdev.handle)
+    e2e_step()
+    n_e2e = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    e2e_value = nbytes * n_e2e / (time.perf_counter() - t0) / 1e9
+    clocks = sampler.stop()
+    peaks = measured_peaks()
+    out = {
+        "metric": "quantize_gb_per_s", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 -> int8 (f32 with an exact f64 path for near-ties)", "data": "synthetic",
+        "config": {"workload": name, **config_of(wl), "granularity": "per-channel",
+                   "l2": f"ring of {ring} matrices ({ring * 4 * R * C / 1e6:.0f} MB of f32)"
+                         + (" > 2x L2" if ring * 4 * R * C > 2 * L2_BYTES else "")},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * R * C, "d2h_bytes_per_step": R * C + 8 * R,
+                "steps": n_e2e},
+        "gpu_launches": int(launches), "launch_mode": "host launches", "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm"], "unit": "GB/s", "frac": value / peaks["hbm"],
+                     "traffic": None, "kernel": "quantize_rows_reg" if C % 4 == 0 and C <= 32768 else "quantize_rows_generic",
+                     "kernel_us": ms / args.steps * 1e3, "peaks": peaks["source"],
+                     "timing": "CUDA events around the timed steps (one launch per step)"},
+    }
+    if not args.no_cpu_baseline:
+        step, cbytes, sample = quantize_cpu_sample(wl)
+        step()
+        t0, n = time.perf_counter(), 0
+        while n < 2 or (time.perf_counter() - t0 < 10 and n < 20):
+            step()
+            n += 1
+        out["cpu_baseline"] = {"value": cbytes * n / (time.perf_counter() - t0) / 1e9, "unit": "GB/s", "cores": 1,
+                               "kind": "port", "sample": f"{n} x " + sample}
+    print(json.dumps(out), flush=True)
+    return 0
 
 
 def config_of(wl):
@@ -276,6 +407,8 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     wl = WORKLOADS[args.workload]
+    if wl["kind"] == "quantize":
+        return (run_quantize_reference if args.impl == "reference" else run_quantize_gpu)(args, wl, args.workload)
     if args.impl == "reference":
         return run_reference_arm(args, wl, args.workload)
 

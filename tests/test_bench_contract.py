@@ -105,3 +105,11 @@ def test_stack_forward_routes_inputs_and_buffers():
     y = bench.stack_forward(x, lins, spec, bufs, {256: torch.zeros(M, 256), 1024: s1024}, False)
     assert y is bufs[-1] and torch.allclose(y, x @ lins[-1].w.t(), atol=1e-4)
     assert torch.allclose(bufs[5], s1024 @ lins[5].w.t(), atol=1e-3) and torch.allclose(bufs[4], x @ lins[4].w.t(), atol=1e-4)
+
+
+def test_reference_arm_of_a_quantize_workload_reports_bandwidth():
+    r = _run("--impl", "reference", "--steps", "1", "--warmup", "1", "--workload", "quantize_1024x1024")
+    assert r.returncode == 0, r.stderr
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["metric"] == "quantize_gb_per_s" and line["unit"] == "GB/s" and line["value"] > 0
+    assert line["cpu_baseline"]["cores"] == 1 and line["config"]["rows"] == 1024
