@@ -452,6 +452,25 @@ class QuantizedLinear:
 
     __call__ = forward
 
+    def forward_host(self, x: torch.Tensor, epilogue: int = _lib.EPILOGUE_NONE,
+                     out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """The same forward for a caller whose activations live in HOST memory (shrewq_linear_forward_host):
+        x is a CPU tensor [M, in_features] of f32 or bf16; the library copies it in, runs the kernel, copies the
+        result out and synchronises.  Returns a CPU tensor [M, out_features]."""
+        if x.device.type != "cpu" or x.dim() != 2 or x.shape[1] != self.in_features:
+            raise ShrewError(_lib.ERR_INVALID_ARG, f"forward_host: expected a CPU tensor [M,{self.in_features}], got {list(x.shape)} on {x.device}")
+        if x.dtype not in _DTYPE_CODE:
+            raise ShrewError(_lib.ERR_UNSUPPORTED, f"forward_host: activation dtype {x.dtype} not supported")
+        x = x.contiguous()
+        out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype)
+        if out.dtype not in _DTYPE_CODE:
+            raise ShrewError(_lib.ERR_UNSUPPORTED, f"forward_host: output dtype {out.dtype} not supported")
+        self.device.bind_stream()
+        rc = _lib.lib().shrewq_linear_forward_host(self._h, ctypes.c_void_p(x.data_ptr()), _DTYPE_CODE[x.dtype], x.shape[0],
+                                                   ctypes.c_void_p(out.data_ptr()), _DTYPE_CODE[out.dtype], epilogue)
+        _lib.check(rc, self.device.handle)
+        return out
+
     def forward_gate_up_silu(self, up: "QuantizedLinear", x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """silu(self.forward(x)) * up.forward(x) in one pass over x (self is the gate)."""
         x = x.contiguous()

@@ -407,3 +407,19 @@ def test_f16_weights_in_tensor_memory_give_the_same_bits(oracle, monkeypatch, M,
     finally:
         _lib.lib().shrewq_force_kernel(b"auto")
     assert torch.equal(y_h, y_b)
+
+
+@_UNVALIDATED
+@pytest.mark.parametrize("M,N,K,dtype", [(1, 300, 512, "bf16"), (40, 256, 784, "f32"), (200, 1000, 1024, "bf16")])
+def test_forward_from_host_buffers(oracle, M, N, K, dtype):
+    # shrewq_linear_forward_host: host activations in, host result out, the copies inside the call; the same kernels as
+    # the device entry point, so the same bits
+    ql, w, b = _make(N, K, 1, seed=N + K)
+    x_t, x_np = _x(M, K, dtype, seed=M)
+    y_host = ql.forward_host(x_t.cpu(), epilogue=1)
+    y_dev = ql.forward(x_t, epilogue=1)
+    torch.cuda.synchronize()
+    assert y_host.device.type == "cpu" and torch.equal(y_host, y_dev.cpu())
+    q = ql.weight_q.data.cpu().numpy().reshape(N, K)
+    ref = oracle.np_linear_forward(q, ql.weight_q.scales.cpu().numpy(), 1, b, x_np, relu=True)
+    assert oracle.rel_err(y_host.float().numpy(), ref) < (TOL_BF16 if dtype == "bf16" else TOL_F32)

@@ -136,3 +136,26 @@ def test_quantized_linear_module_surface_without_a_device():
     assert ql.is_training() is True
     ql.set_training(False)
     assert ql.is_training() is False
+
+
+def test_forward_host_marshals_host_pointers_and_checks_its_input(monkeypatch):
+    calls = []
+
+    class Lib:
+        def shrewq_linear_forward_host(self, h, x, x_dtype, M, y, y_dtype, epilogue):
+            calls.append((h, x.value, x_dtype, M, y.value, y_dtype, epilogue))
+            return 0
+
+    monkeypatch.setattr(_lib, "lib", lambda: Lib())
+    ql = object.__new__(Q.QuantizedLinear)
+    ql._h, ql.in_features, ql.out_features, ql.device = 0x77, 8, 3, _FakeDevice()
+    x = torch.zeros(5, 8, dtype=torch.bfloat16)
+    y = ql.forward_host(x, epilogue=1, out_dtype=torch.float32)
+    assert y.shape == (5, 3) and y.dtype == torch.float32 and y.device.type == "cpu"
+    (h, xp, xd, M, yp, yd, ep), = calls
+    assert (h, xp, xd, M, yp, yd, ep) == (0x77, x.data_ptr(), _lib.BF16, 5, y.data_ptr(), _lib.F32, 1)
+    with pytest.raises(Q.ShrewError):
+        ql.forward_host(torch.zeros(5, 7))                       # wrong in_features
+    with pytest.raises(Q.ShrewError):
+        ql.forward_host(torch.zeros(5, 8, dtype=torch.float64))  # unsupported dtype
+    ql._h = None

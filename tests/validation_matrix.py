@@ -26,6 +26,7 @@ LIN = "tests/test_gpu_linear.py"
 MATRIX = [
     ("default", {}, ["tests"]),
     ("gemv-pdl", {"SHREWQ_GEMV_PDL": "1"}, [LIN, "-k", "gemv or config3 or config4"]),
+    ("host-forward", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "host_buffers"]),
     ("batch-quantize", {"SHREWQ_TEST_UNVALIDATED": "1", "SHREWQ_BATCH_QUANTIZE": "1"}, ["tests/test_gpu_quantize.py"]),
     ("shard-per-tensor", {"SHREWQ_TEST_UNVALIDATED": "1"}, ["tests/test_gpu_quantize.py", "-k", "row_shards"]),
     ("splitk-large-tiles", {"SHREWQ_TC_SPLITK_MAXTOK": "256"}, [LIN]),
