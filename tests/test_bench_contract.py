@@ -113,3 +113,16 @@ def test_reference_arm_of_a_quantize_workload_reports_bandwidth():
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["metric"] == "quantize_gb_per_s" and line["unit"] == "GB/s" and line["value"] > 0
     assert line["cpu_baseline"]["cores"] == 1 and line["config"]["rows"] == 1024
+
+
+def test_reference_arm_under_torchrun_prints_one_line_from_rank_0():
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29917", os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
+                        "--steps", "1", "--warmup", "1", "--workload", "mnist_mlp_m64"], capture_output=True, text=True, cwd=ROOT,
+                       env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2
