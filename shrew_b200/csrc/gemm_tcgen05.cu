@@ -50,7 +50,8 @@ struct Tuning {
     bool splitk;  // allow split-K when the grid would leave SMs idle
     int tok;      // 0 = choose; else force the token tile
     int tok_gated;  // 0 = as above; else the token tile of gate/up launches only (NOT yet run on a GPU at 256)
-    bool a_f16;   // weights as f16 in tensor memory (cheaper conversion); NOT yet run on a GPU, off by default
+    bool a_f16;   // weights as f16 in tensor memory (cheaper conversion); off by default and held off the GPU: an
+                  // earlier form of this f16 / bf16 operand mix failed on every launch, cause not established
 };
 
 Tuning read_tuning() {

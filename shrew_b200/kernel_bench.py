@@ -205,12 +205,17 @@ MLP_SETTINGS = [
     ("mma-f16+pdl", {"SHREWQ_AUTO_MMA_F16": "1", "SHREWQ_GEMV_PDL": "1"}),
     ("pair", {"SHREWQ_AUTO_PAIR": "1"}),
     ("pair+tail", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1"}),
-    # f16 weights beside bf16 activations: last (the one setting whose instruction form has not run here)
-    ("af16", {"SHREWQ_TC_A_F16": "1"}),
-    ("tok256+tail+split+af16", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256",
-                                "SHREWQ_TC_A_F16": "1"}),
-    ("pair+tail+af16", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_A_F16": "1"}),
 ]
+# f16 weights beside bf16 activations: an earlier implementation of that operand mix failed on every launch and the
+# cause was never established, so these settings are measured only on request (SHREWQ_BENCH_AF16=1), last
+if os.environ.get("SHREWQ_BENCH_AF16", "0") == "1":
+    MLP_SETTINGS += [
+        ("af16", {"SHREWQ_TC_A_F16": "1"}),
+        ("tok256+tail+split+af16", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256",
+                                    "SHREWQ_TC_A_F16": "1"}),
+        ("pair+tail+af16", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_A_F16": "1"}),
+    ]
+
 _TUNING_VARS = sorted({k for _, env in MLP_SETTINGS for k in env})
 
 

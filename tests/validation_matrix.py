@@ -9,6 +9,10 @@ as a separate pytest process, so a failure in one leaves the others standing; th
 entry whose output shows a CUDA fault or a kernel that gave up a bounded wait, because whatever runs next on
 that GPU would not be trustworthy, and the faulting path has to be read before it runs again.  Prints one
 line per entry and, with --json, writes the same as a list of records.
+
+Not in the list on purpose: f16 weights beside bf16 activations in tensor memory (SHREWQ_TC_A_F16=1).  An earlier
+implementation of that operand mix failed with a CUDA error on every launch, in three runs; the cause was never
+established, so the path stays off the GPU until it is (its parity test has a switch of its own, SHREWQ_TEST_AF16=1).
 """
 from __future__ import annotations
 
@@ -43,9 +47,6 @@ MATRIX = [
     ("cta-pair", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "cta_pair"]),
     ("cta-pair-auto", {"SHREWQ_AUTO_PAIR": "1"}, [LIN]),
     ("cta-pair-auto-tail", {"SHREWQ_AUTO_PAIR": "1", "SHREWQ_TC_TAILSPLIT": "1"}, [LIN, "-k", "config4 or config3"]),
-    # last: mixed operand formats (f16 weights beside bf16 activations) have never run here
-    ("f16-weights", {"SHREWQ_TEST_UNVALIDATED": "1"}, [LIN, "-k", "f16_weights"]),
-    ("f16-weights-all", {"SHREWQ_TC_A_F16": "1"}, [LIN]),
 ]
 
 # what in a test run's output means the GPU, or the context, can no longer be trusted
