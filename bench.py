@@ -710,6 +710,27 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     k_s = e0.elapsed_time(e1) * 1e-3 / iters
+    k_timing = "CUDA events, host-launched back to back (includes launch gaps)"
+    # The same launches replayed from one CUDA graph: no host launch path between them, which matters for the
+    # kernels of a few microseconds (batch 1).  Kept only if it ran; the shorter of the two is reported.
+    if not args.no_graph:
+        try:
+            kg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(kg):
+                for i in range(iters):
+                    kern(i)
+            kg.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            kg.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            k_graph = e0.elapsed_time(e1) * 1e-3 / iters
+            if k_graph < k_s:
+                k_s, k_timing = k_graph, f"CUDA events around one graph replay of {iters} launches over the ring"
+        except Exception as e:  # noqa: BLE001
+            sys.stderr.write(f"bench: graph timing of the dominant kernel failed ({e!r}); keeping the host-launched figure\n")
+            torch.cuda.synchronize()
     # the sampler ran from the start of the device-resident timed region through the end-to-end and
     # kernel-alone timed regions: the device-resident one alone lasts ~10 ms, one nvidia-smi period
     clocks = sampler.stop() if rank == 0 else None
@@ -724,7 +745,7 @@ def main():
         roof = {"bound": "hbm", "achieved": k_bytes / k_s / 1e9, "peak": peaks["hbm"], "unit": "GB/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
     roof.update({"traffic": None, "kernel": kernel_family, "kernel_us": k_s * 1e6, "peaks": peaks["source"],
-                 "timing": "CUDA events, host-launched back to back (includes launch gaps)"})
+                 "timing": k_timing})
 
     out = {
         "metric": "quantized_linear_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
