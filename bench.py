@@ -643,19 +643,24 @@ def main():
         k_flops = 2 * M * q.out_features * q.in_features
         k_bytes = q.out_features * q.in_features + 4 * q.out_features + M * q.in_features * 2 + M * q.out_features * 2
         kname = q
-    for i in range(3):
-        kern(i)
-    torch.cuda.synchronize()
-    e0.record()
-    for i in range(iters):
-        kern(i)
-    e1.record()
-    torch.cuda.synchronize()
-    k_s = e0.elapsed_time(e1) * 1e-3 / iters
-    k_timing = "CUDA events, host-launched back to back (includes launch gaps)"
+    k_s, k_timing, k_error = None, None, None
+    try:
+        for i in range(3):
+            kern(i)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(iters):
+            kern(i)
+        e1.record()
+        torch.cuda.synchronize()
+        k_s = e0.elapsed_time(e1) * 1e-3 / iters
+        k_timing = "CUDA events, host-launched back to back (includes launch gaps)"
+    except Exception as e:  # noqa: BLE001  (the step figures measured above are still reported)
+        k_error = repr(e)
+        sys.stderr.write(f"bench: timing the dominant kernel alone failed ({e!r})\n")
     # The same launches replayed from one CUDA graph: no host launch path between them, which matters for the
     # kernels of a few microseconds (batch 1).  Kept only if it ran; the shorter of the two is reported.
-    if not args.no_graph:
+    if not args.no_graph and k_s is not None:
         try:
             kg = torch.cuda.CUDAGraph()
             with torch.cuda.graph(kg):
@@ -747,13 +752,15 @@ def main():
     if wl["kind"] == "stack":   # decided by the dominant layer's own arithmetic intensity
         tensor_bound = k_flops / (peaks["tc_sustained"] * 1e12) > k_bytes / (peaks["hbm"] * 1e9)
     if tensor_bound:
-        roof = {"bound": "tensor", "achieved": k_flops / k_s / 1e12, "peak": peaks["tc_sustained"], "unit": "TFLOP/s",
-                "peak_burst": peaks["tc_burst"]}
+        roof = {"bound": "tensor", "achieved": k_flops / k_s / 1e12 if k_s else None, "peak": peaks["tc_sustained"],
+                "unit": "TFLOP/s", "peak_burst": peaks["tc_burst"]}
     else:
-        roof = {"bound": "hbm", "achieved": k_bytes / k_s / 1e9, "peak": peaks["hbm"], "unit": "GB/s"}
-    roof["frac"] = roof["achieved"] / roof["peak"]
-    roof.update({"traffic": None, "kernel": kernel_family, "kernel_us": k_s * 1e6, "peaks": peaks["source"],
+        roof = {"bound": "hbm", "achieved": k_bytes / k_s / 1e9 if k_s else None, "peak": peaks["hbm"], "unit": "GB/s"}
+    roof["frac"] = roof["achieved"] / roof["peak"] if k_s else None
+    roof.update({"traffic": None, "kernel": kernel_family, "kernel_us": k_s * 1e6 if k_s else None, "peaks": peaks["source"],
                  "timing": k_timing})
+    if k_error:
+        roof["error"] = k_error
 
     out = {
         "metric": "quantized_linear_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -785,11 +792,16 @@ def main():
         # buffers captured in CUDA graphs have kept ranks from ending in interpreter teardown on this
         # software stack (results printed, processes never exited), so after a last barrier the ranks
         # skip that teardown; the driver reclaims the context with the process.
-        torch.cuda.synchronize()
-        dist.barrier()
+        rc = 0
+        try:
+            torch.cuda.synchronize()
+            dist.barrier()
+        except Exception as e:  # noqa: BLE001  (the result line is out already; say what happened and leave)
+            sys.stderr.write(f"bench: final barrier failed ({e!r})\n")
+            rc = 1
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(rc)
     return 0
 
 
