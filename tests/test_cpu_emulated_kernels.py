@@ -918,6 +918,32 @@ def test_tcgen05_peer_destinations(oracle, emu_tc):
             assert np.all(buf[:, 140:] == (7.0 if buf is y else 5.0))
 
 
+def test_tcgen05_down_projection_shard_split_along_k_with_peers(oracle, emu_tc):
+    # the sharded block's second layer: few channel tiles per rank (4096 / 4 = 1024 rows = 8 tiles) over the FULL
+    # hidden width, so its k-loop does not shrink with the number of GPUs; split-K on 128-token tiles is what lets it
+    # use the idle SMs.  Reduced: 2 channel tiles (the second ragged), 2 token tiles (the second ragged), 11 rounds of
+    # 128 k in 3 splits (4 + 4 + 3), bf16 into a column slice of a wider row and into three peer buffers.
+    emu_tc.emu_set_peers.argtypes = [_vp, _ci]
+    M, N, K, world, rank = 130, 200, 1408, 4, 1
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, 17)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
+    ldy, n0 = world * N, rank * N
+    full = [np.full((M, ldy), 0x4100, np.uint16) for _ in range(world)]
+    arr = (ctypes.c_void_p * 3)(*[f[:, n0:].ctypes.data for i, f in enumerate(full) if i != rank])
+    emu_tc.emu_set_peers(arr, 3)
+    try:
+        y = _tc_forward(emu_tc, q, scales, bias, x_bits, 128, 3, splits=3, y_bf16=True, ldy=ldy,
+                        y_init=np.full((M, ldy), 0x4100, np.uint16))
+    finally:
+        emu_tc.emu_set_peers(None, 0)
+    got = [y[:, :N]] + [f[:, n0:n0 + N] for i, f in enumerate(full) if i != rank]
+    for g in got:
+        assert oracle.rel_err((g.astype(np.uint32) << 16).view(np.float32), ref) < 1e-2
+        assert np.array_equal(g, got[0])
+    assert np.all(y[:, N:] == 0x4100) and all(np.all(np.delete(f, np.s_[n0:n0 + N], axis=1) == 0x4100) for i, f in enumerate(full) if i != rank)
+    assert np.all(full[rank] == 0x4100)        # the own copy is the kernel's y, not a peer
+
+
 def test_tcgen05_gated_shard_of_eight_ranks_with_seven_peers(oracle, emu_tc):
     # the benchmark's MLP block over 8 GPUs: each rank owns 11008 / 8 = 1376 = 21 x 64 + 32 hidden channels, so its
     # gated launch ends in a half-full channel tile, writes bf16 into columns [n0, n0 + n_local) of the full-width
