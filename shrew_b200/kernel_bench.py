@@ -10,6 +10,7 @@ host launch cost is excluded; the weights rotate through a ring larger than twic
     (mma-w4 = packed INT4 weights, also needs SHREWQ_EXPERIMENTAL_MODES=1; "+suffix"es set a tuning variable
     for that measurement: tcgen05+af16, tcgen05+waves+maxtok, tcgen05-2cta+tail, gemv+pdl, tcgen05+tok256 ...)
     python -m shrew_b200.kernel_bench mlp 512    # the Llama MLP block (gate/up + down) under every prepared tuning setting
+    python -m shrew_b200.kernel_bench mlp 512 default,split-large 4   # one rank's kernels of the block sharded over 4 GPUs
     python -m shrew_b200.build --trace && SHREWQ_LIB=shrew_b200/libshrewq_trace.so \
         python -m shrew_b200.kernel_bench trace 4096 4096 16,1024  # in-kernel cycle trace of CTA 0
         (a fifth argument `tcgen05-2cta` traces the leader CTA of the CTA-pair kernel; SHREWQ_TC_A_F16=1 etc. apply)
@@ -198,6 +199,7 @@ MLP_SETTINGS = [
     ("tok256", {"SHREWQ_TC_TOK": "256"}),
     ("tok256+tail", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1"}),
     ("tok256+tail+split", {"SHREWQ_TC_TOK": "256", "SHREWQ_TC_TAILSPLIT": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}),
+    ("split-large", {"SHREWQ_TC_SPLITK_MAXTOK": "256"}),
     ("waves", {"SHREWQ_TC_SPLIT_WAVES": "1"}),
     ("waves+maxtok", {"SHREWQ_TC_SPLIT_WAVES": "1", "SHREWQ_TC_SPLITK_MAXTOK": "256"}),
     ("pdl", {"SHREWQ_GEMV_PDL": "1"}),
@@ -219,16 +221,20 @@ if os.environ.get("SHREWQ_BENCH_AF16", "0") == "1":
 _TUNING_VARS = sorted({k for _, env in MLP_SETTINGS for k in env})
 
 
-def bench_mlp(batches, d_model=4096, d_ff=11008, only=None):
+def bench_mlp(batches, d_model=4096, d_ff=11008, only=None, shards=1):
     """gate/up (one fused launch) + down of the Llama MLP block, per setting: microseconds per block, tokens/s and
     TFLOP/s, and whether the result equals the default setting's (same bits expected unless the accumulation order
-    changes: split-K, another kernel family)."""
-    nbuf = max(2, int(2 * L2_BYTES // (3 * d_ff * d_model)) + 1)
-    gates, ups, downs = _layers(d_ff, d_model, nbuf), _layers(d_ff, d_model, nbuf), _layers(d_model, d_ff, nbuf)
+    changes: split-K, another kernel family).  shards = g times the kernels of ONE rank of a block sharded over g GPUs
+    (gate/up with d_ff / g output channels, down with d_model / g output channels over the full hidden width): what a
+    rank computes between two exchanges, measured on one GPU."""
+    n_up, n_down = -(-d_ff // shards), -(-d_model // shards)
+    nbuf = max(2, int(2 * L2_BYTES // (2 * n_up * d_model + n_down * d_ff)) + 1)
+    gates, ups, downs = _layers(n_up, d_model, nbuf), _layers(n_up, d_model, nbuf), _layers(n_down, d_ff, nbuf)
     for M in batches:
         x = torch.randn(M, d_model, device="cuda").to(torch.bfloat16)
-        h = torch.empty(M, d_ff, device="cuda", dtype=torch.bfloat16)
-        y = torch.empty(M, d_model, device="cuda", dtype=torch.bfloat16)
+        hfull = torch.randn(M, d_ff, device="cuda").to(torch.bfloat16)   # the gathered hidden activation the down shard reads
+        h = hfull[:, :n_up]                                              # this rank's column slice of it
+        y = torch.empty(M, n_down, device="cuda", dtype=torch.bfloat16)
         ref = None
         for name, env in MLP_SETTINGS:
             if only and name not in only:
@@ -240,7 +246,7 @@ def bench_mlp(batches, d_model=4096, d_ff=11008, only=None):
             def f():
                 for g, u, d in zip(gates, ups, downs):
                     g.forward_gate_up_silu(u, x, out=h)
-                    d.forward(h, out=y)
+                    d.forward(hfull, out=y)
             try:
                 t = _time_graph(f, iters=5, warm=2) / nbuf
                 Device.get("cuda:0").synchronize()
@@ -251,7 +257,8 @@ def bench_mlp(batches, d_model=4096, d_ff=11008, only=None):
             if ref is None:
                 ref = out
             err = float((out - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
-            print(json.dumps(dict(setting=name, M=M, us=t * 1e6, tokens_per_s=M / t, TFs=6 * M * d_ff * d_model / t / 1e12,
+            print(json.dumps(dict(setting=name, M=M, shards=shards, us=t * 1e6, tokens_per_s=M / t,
+                                  TFs=2 * M * (2 * n_up * d_model + n_down * d_ff) / t / 1e12,
                                   kernels=[gates[0].last_kernel(), downs[0].last_kernel()], rel_diff_vs_first=err)), flush=True)
     for k in _TUNING_VARS:
         os.environ.pop(k, None)
@@ -263,7 +270,8 @@ def main(argv):
         bench_quant([(int(argv[2]), int(argv[3]))] if len(argv) >= 4 else None)
     elif which == "mlp":
         bench_mlp([int(b) for b in argv[2].split(",")] if len(argv) > 2 else [512, 1],
-                  only=set(argv[3].split(",")) if len(argv) > 3 else None)
+                  only=set(argv[3].split(",")) if len(argv) > 3 and argv[3] != "all" else None,
+                  shards=int(argv[4]) if len(argv) > 4 else 1)
     elif which == "trace":
         bench_trace(int(argv[2]), int(argv[3]), [int(b) for b in argv[4].split(",")], argv[5] if len(argv) > 5 else "tcgen05")
     else:
