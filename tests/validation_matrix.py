@@ -124,7 +124,8 @@ def main():
     unknown = [n for n in names if n not in {m[0] for m in MATRIX}]
     if unknown:
         raise SystemExit(f"unknown entries: {unknown}")
-    todo = [m for m in MATRIX if not names or m[0] in names]
+    by_name = {m[0]: m for m in MATRIX}
+    todo = [by_name[n] for n in names] if names else list(MATRIX)     # --only keeps the order given
     if a.list:
         for name, env, args in todo:
             print(name, " ".join(f"{k}={v}" for k, v in env.items()), "::", " ".join(args))
