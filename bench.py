@@ -430,6 +430,18 @@ def main():
         # far was made with it off
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
+        # A rank that waits for a peer that is gone would wait for ever (the device-side barrier of the fused exchange
+        # has no time limit of its own): after a generous wall-clock limit every rank says so and ends, so that the
+        # launcher is never left with a hung job.  A normal run takes a minute or two.
+        limit_s = float(os.environ.get("SHREWQ_BENCH_WATCHDOG_S", "1200"))
+
+        def give_up():
+            sys.stderr.write(f"bench: rank {rank} still running after {limit_s:.0f} s; giving up\n")
+            sys.stderr.flush()
+            os._exit(3)
+        watchdog = threading.Timer(limit_s, give_up)
+        watchdog.daemon = True
+        watchdog.start()
     sdev = Device.get(dev)
     if args.force_kernel != "auto":
         _lib.check(_lib.lib().shrewq_force_kernel(args.force_kernel.encode()), None)
