@@ -19,6 +19,8 @@
  *    the first time a call needs more than it holds; a call that would have to grow one while its
  *    stream is being captured fails with SHREWQ_ERR_UNSUPPORTED instead of breaking the capture —
  *    make the same call once outside the capture first.
+ *    A captured graph holds the workspace address it was captured with: a later call on the same context that
+ *    grows the workspace (a larger shape) frees that address, so graphs captured before must be re-captured.
  *  - Device entry points enqueue work on the context's stream and return without
  *    synchronising.  Host entry points (suffix _host) copy in, run, copy out and
  *    synchronise the stream before returning.
