@@ -50,14 +50,11 @@ struct Tuning {
     bool splitk;  // allow split-K when the grid would leave SMs idle
     int tok;      // 0 = choose; else force the token tile
     int tok_gated;  // 0 = as above; else the token tile of gate/up launches only (NOT yet run on a GPU at 256)
-    bool a_f16;   // weights as f16 in tensor memory (cheaper conversion); off by default and held off the GPU: an
-                  // earlier form of this f16 / bf16 operand mix failed on every launch, cause not established
 };
 
 Tuning read_tuning() {
-    Tuning t{3, true, 0, 0, false};
+    Tuning t{3, true, 0, 0};
     if (const char *e = getenv("SHREWQ_TC_TOK_GATED")) t.tok_gated = atoi(e);
-    if (const char *e = getenv("SHREWQ_TC_A_F16")) t.a_f16 = atoi(e) != 0;
     if (const char *e = getenv("SHREWQ_TC_GROUPS")) t.groups = atoi(e);
     if (const char *e = getenv("SHREWQ_TC_SPLITK")) t.splitk = atoi(e) != 0;
     if (const char *e = getenv("SHREWQ_TC_TOK")) t.tok = atoi(e);
@@ -119,7 +116,7 @@ LaunchPlan plan_launch(const ForwardArgs &a, int chan_per_tile, int sm_count, bo
 
 // scratch == nullptr: use (and grow) the context's scratch; otherwise a caller-provided
 // region of scratch_bytes laid out as [0,4096) counters, partial sums from 4096.
-template <int TOK, int KSUB, int G, bool GATED, typename YT, bool AF16 = false>
+template <int TOK, int KSUB, int G, bool GATED, typename YT>
 int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, bool allow_split,
                void *fixed_scratch, size_t fixed_scratch_bytes) {
     using C = Cfg<TOK, KSUB>;
@@ -127,7 +124,7 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
     int rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, a.K, a.M, kBlockK, TOK,
                        CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SHREWQ_OK) return rc;
-    auto kern = linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT, AF16>;
+    auto kern = linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT>;
     static bool attr_set[64] = {false};  // per instantiation and per device (the attribute is per device)
     if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
         SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemRequest));
@@ -211,8 +208,6 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
 template <int TOK, int KSUB, bool GATED, typename YT>
 int launch_groups(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, const Tuning &t,
                   void *fs, size_t fsb) {
-    // the f16-weights variant exists for the default three converter groups only
-    if (t.a_f16 && t.groups == 3) return launch_cfg<TOK, KSUB, 3, GATED, YT, true>(ctx, a, tw, tw2, t.splitk, fs, fsb);
     if (t.groups == 1) return launch_cfg<TOK, KSUB, 1, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);
     if (t.groups == 2) return launch_cfg<TOK, KSUB, 2, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);
     return launch_cfg<TOK, KSUB, 3, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);

@@ -34,12 +34,12 @@ int encode_x_half(shrewq_ctx *ctx, CUtensorMap *out, const void *x, size_t K, si
     return SHREWQ_OK;
 }
 
-template <typename YT, bool GATED, bool AF16 = false>
+template <typename YT, bool GATED>
 int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2) {
     CUtensorMap tx;
     int rc = encode_x_half(ctx, &tx, a.x, a.K, a.M);
     if (rc != SHREWQ_OK) return rc;
-    auto kern = linear_i8_tcgen05_pair_kernel<YT, GATED, AF16>;
+    auto kern = linear_i8_tcgen05_pair_kernel<YT, GATED>;
     static bool attr_set[64] = {false};
     if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
         SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
@@ -126,19 +126,6 @@ extern "C" __attribute__((visibility("default"))) int shrewq_debug_set_trace_pai
 // 64-row boxes of the gate and of the up handle (the descriptors the single-CTA kernel uses).
 int launch_gemm_tcgen05_2cta(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap) {
     const CUtensorMap &tw = *static_cast<const CUtensorMap *>(w_tmap);
-    // SHREWQ_TC_A_F16=1: f16 weights in tensor memory, as for the single-CTA kernel
-    const char *e = getenv("SHREWQ_TC_A_F16");  // read per launch, like the single-CTA kernel's tuning
-    const bool a_f16 = e && atoi(e) != 0;
-    if (a_f16) {
-        if (a.q_up) {
-            if (!w_up_tmap) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "tcgen05-2cta: the up matrix has no tensor map");
-            const CUtensorMap &tw2 = *static_cast<const CUtensorMap *>(w_up_tmap);
-            if (a.y_dtype == SHREWQ_BF16) return launch_pair<__nv_bfloat16, true, true>(ctx, a, tw, tw2);
-            return launch_pair<float, true, true>(ctx, a, tw, tw2);
-        }
-        if (a.y_dtype == SHREWQ_BF16) return launch_pair<__nv_bfloat16, false, true>(ctx, a, tw, tw);
-        return launch_pair<float, false, true>(ctx, a, tw, tw);
-    }
     if (a.q_up) {
         if (!w_up_tmap) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "tcgen05-2cta: the up matrix has no tensor map");
         const CUtensorMap &tw2 = *static_cast<const CUtensorMap *>(w_up_tmap);

@@ -129,13 +129,6 @@ __device__ __forceinline__ void cvt_i8x4_bf16(uint32_t w, uint32_t &lo, uint32_t
     hi = pack_bf16x2_rn(f3, f2);
 }
 
-// the same codes as f16, exactly, in 5 instructions per word instead of 11: halves 0x64uu = 1024 + u
-__device__ __forceinline__ void cvt_i8x4_half(uint32_t w, uint32_t &lo, uint32_t &hi) {
-    const uint32_t u = w ^ 0x80808080u;
-    lo = sub_f16x2(__byte_perm(u, 0x64646464u, 0x4140), 0x64806480u);
-    hi = sub_f16x2(__byte_perm(u, 0x64646464u, 0x4342), 0x64806480u);
-}
-
 // K-major, 128-byte swizzle, 8-row groups 1024 B apart, descriptor version 1
 __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -181,9 +174,7 @@ struct SplitK2 {
 // GATED: as in the single-CTA kernel, the 128 lanes of a CTA carry 64 rows of a gate matrix (tmap_w,
 // 64-row boxes) and the same 64 rows of an up matrix (tmap_w2); the epilogue pairs lane r with lane
 // r + 64 and writes silu(gate) * up for 64 channels per CTA, 128 per pair.
-// AF16: the weights go to tensor memory as f16 (exact like bf16, cheaper to produce); the activations
-// stay bf16 and the instruction descriptor names the two formats separately.
-template <typename YT, bool GATED, bool AF16 = false>
+template <typename YT, bool GATED>
 __global__ void SHREWQ_CLUSTER_OF_2 __launch_bounds__(kThreads, 1)
 linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
                               const __grid_constant__ CUtensorMap tmap_x, Operands2 ops, YT *__restrict__ y, Dests extra,
@@ -274,7 +265,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
         // ---------------- MMA issuer (one thread of the leader CTA) ----------------
         if (lane == 0 && rank == 0) {
             // D=f32, A=bf16 (K-major, TMEM), B=bf16 (K-major), M=256 (two CTAs), N=256
-            constexpr uint32_t idesc = (1u << 4) | (AF16 ? 0u : (1u << 7)) | (1u << 10) | ((uint32_t)(kTokPair >> 3) << 17) |
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTokPair >> 3) << 17) |
                                        ((uint32_t)((2 * kLanes) >> 4) << 24);
             const uint64_t bdesc0 = make_b_desc(smem_base + kXOff);
             const uint32_t a0 = tmem_base + kABase;
@@ -332,17 +323,10 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const uint4 v = *reinterpret_cast<const uint4 *>(rowp + ((c ^ swz) << 4));
-                    if constexpr (AF16) {
-                        cvt_i8x4_half(v.x, packed[8 * c + 0], packed[8 * c + 1]);
-                        cvt_i8x4_half(v.y, packed[8 * c + 2], packed[8 * c + 3]);
-                        cvt_i8x4_half(v.z, packed[8 * c + 4], packed[8 * c + 5]);
-                        cvt_i8x4_half(v.w, packed[8 * c + 6], packed[8 * c + 7]);
-                    } else {
-                        cvt_i8x4_bf16(v.x, packed[8 * c + 0], packed[8 * c + 1]);
-                        cvt_i8x4_bf16(v.y, packed[8 * c + 2], packed[8 * c + 3]);
-                        cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
-                        cvt_i8x4_bf16(v.w, packed[8 * c + 6], packed[8 * c + 7]);
-                    }
+                    cvt_i8x4_bf16(v.x, packed[8 * c + 0], packed[8 * c + 1]);
+                    cvt_i8x4_bf16(v.y, packed[8 * c + 2], packed[8 * c + 3]);
+                    cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
+                    cvt_i8x4_bf16(v.w, packed[8 * c + 6], packed[8 * c + 7]);
                 }
                 tc_st32(tmem_base + lane_addr + kABase + s * kAColsPerStage + j * (kBlockK / 2), packed);
             }

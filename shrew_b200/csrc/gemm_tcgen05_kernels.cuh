@@ -137,15 +137,6 @@ __device__ __forceinline__ void cvt_i8x4_bf16(uint32_t w, uint32_t &lo, uint32_t
     hi = pack_bf16x2_rn(f3, f2);
 }
 
-// 4 INT8 codes -> two packed f16x2 words, exactly, in fewer instructions than the bf16 route:
-// the halves 0x64uu are the f16 values 1024 + u (u = q + 128); one packed subtraction of 1152
-// leaves q.  Used by the variant that gives the tensor core f16 weights beside bf16 activations.
-__device__ __forceinline__ void cvt_i8x4_half(uint32_t w, uint32_t &lo, uint32_t &hi) {
-    const uint32_t u = w ^ 0x80808080u;
-    lo = sub_f16x2(__byte_perm(u, 0x64646464u, 0x4140), 0x64806480u);
-    hi = sub_f16x2(__byte_perm(u, 0x64646464u, 0x4342), 0x64806480u);
-}
-
 // Shared-memory matrix descriptor for the activation tile: K-major, 128-byte swizzle,
 // rows of 128 B, 8-row groups 1024 B apart (stride byte offset), descriptor version 1.
 __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
@@ -209,10 +200,7 @@ struct Operands {
     const float *bias2;
 };
 
-// AF16: the weights go to tensor memory as f16 instead of bf16 (both hold every INT8 code exactly, so
-// the products and the result are the same); the activations stay bf16.  The instruction descriptor
-// names the two operand formats in separate fields.
-template <int TOK, int KSUB, int G, bool GATED, typename YT, bool AF16 = false>
+template <int TOK, int KSUB, int G, bool GATED, typename YT>
 __global__ void __launch_bounds__(64 + 128 * G, 1)
 linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
                          const __grid_constant__ CUtensorMap tmap_x, Operands ops, YT *__restrict__ y, Dests extra, int M, int N,
@@ -299,8 +287,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         // ---------------- MMA issuer (one thread) ----------------
         if (lane == 0) {
             // instruction descriptor: D=f32, A=bf16 (K-major, from TMEM), B=bf16 (K-major), M=128, N=TOK
-            // (with AF16 the A format field [7,10) is 0 = f16)
-            constexpr uint32_t idesc = (1u << 4) | (AF16 ? 0u : (1u << 7)) | (1u << 10) |
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                                        ((uint32_t)(TOK >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
             const uint64_t bdesc0 = make_b_desc(smem_base + C::kXOff);
             const uint32_t a0 = tmem_base + C::kABase;
@@ -362,17 +349,10 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const uint4 v = *reinterpret_cast<const uint4 *>(rowp + ((c ^ swz) << 4));
-                    if constexpr (AF16) {
-                        cvt_i8x4_half(v.x, packed[8 * c + 0], packed[8 * c + 1]);
-                        cvt_i8x4_half(v.y, packed[8 * c + 2], packed[8 * c + 3]);
-                        cvt_i8x4_half(v.z, packed[8 * c + 4], packed[8 * c + 5]);
-                        cvt_i8x4_half(v.w, packed[8 * c + 6], packed[8 * c + 7]);
-                    } else {
-                        cvt_i8x4_bf16(v.x, packed[8 * c + 0], packed[8 * c + 1]);
-                        cvt_i8x4_bf16(v.y, packed[8 * c + 2], packed[8 * c + 3]);
-                        cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
-                        cvt_i8x4_bf16(v.w, packed[8 * c + 6], packed[8 * c + 7]);
-                    }
+                    cvt_i8x4_bf16(v.x, packed[8 * c + 0], packed[8 * c + 1]);
+                    cvt_i8x4_bf16(v.y, packed[8 * c + 2], packed[8 * c + 3]);
+                    cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
+                    cvt_i8x4_bf16(v.w, packed[8 * c + 6], packed[8 * c + 7]);
                 }
                 tc_st32(tmem_base + lane_addr + C::kABase + s * C::kAColsPerStage + j * (kBlockK / 2), packed);
             }

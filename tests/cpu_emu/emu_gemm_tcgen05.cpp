@@ -26,9 +26,7 @@ CUtensorMap map2d(const void *base, uint32_t elem, uint64_t inner, uint64_t oute
     return CUtensorMap{base, elem, inner, outer, inner * elem, box_inner, box_outer, sw};
 }
 
-bool g_a_f16 = false;  // next launches use the variant with f16 weights in tensor memory (three groups only)
-
-template <int TOK, int KSUB, int G, bool GATED, typename YT, bool AF16 = false>
+template <int TOK, int KSUB, int G, bool GATED, typename YT>
 int run(const Args &a, DeviceStatus *status) {
     using C = Cfg<TOK, KSUB>;
     const int chan = GATED ? 64 : 128;
@@ -50,7 +48,7 @@ int run(const Args &a, DeviceStatus *status) {
     }
     Operands ops{a.scales, a.bias, a.scales_up, a.bias_up};
     auto body = [&] {
-        linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT, AF16>(tw, tw2, tx, ops, static_cast<YT *>(a.y), g_peers, a.M, a.N, a.K, a.ldy,
+        linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT>(tw, tw2, tx, ops, static_cast<YT *>(a.y), g_peers, a.M, a.N, a.K, a.ldy,
                                                           a.epilogue, sk, status);
     };
     if (a.tile_list >= 2) {
@@ -82,7 +80,6 @@ int run(const Args &a, DeviceStatus *status) {
 
 template <int TOK, int KSUB, bool GATED, typename YT>
 int run_g(const Args &a, int groups, DeviceStatus *st) {
-    if (g_a_f16) return groups == 3 ? run<TOK, KSUB, 3, GATED, YT, true>(a, st) : -1;
     if (groups == 1) return run<TOK, KSUB, 1, GATED, YT>(a, st);
     if (groups == 2) return run<TOK, KSUB, 2, GATED, YT>(a, st);
     return run<TOK, KSUB, 3, GATED, YT>(a, st);
@@ -119,7 +116,6 @@ extern "C" int emu_gemm_tcgen05(const int8_t *q, const float *scales, const floa
     return rc;
 }
 
-extern "C" void emu_set_a_f16(int on) { g_a_f16 = on != 0; }
 extern "C" int emu_last_a_format() { return emu::g_last_a_format.load(); }  // 0 = f16, 1 = bf16
 
 // peer destinations of the next launches: every output value is also stored at the same offset there

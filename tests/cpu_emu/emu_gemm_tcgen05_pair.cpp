@@ -9,14 +9,8 @@
 using namespace shrewq;
 
 namespace {
-bool g_a_f16 = false;  // next launches use the variant with f16 weights in tensor memory
-
 template <typename YT, bool GATED>
 int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
-        int epilogue, int splits, int tile_list, DeviceStatus *st);
-
-template <typename YT, bool GATED, bool AF16>
-int run_as(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
         int epilogue, int splits, int tile_list, DeviceStatus *st) {
     const uint32_t box_rows = GATED ? 64 : 128;
     const CUtensorMap tw{q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
@@ -35,7 +29,7 @@ int run_as(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint
     std::vector<unsigned int> counters(ctas, 0u);
     SplitK2 sk{splits > 1 ? partials.data() : nullptr, splits > 1 ? counters.data() : nullptr, rps, 0, 0};
     auto body = [&] {
-        linear_i8_tcgen05_pair_kernel<YT, GATED, AF16>(tw, tw2, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, sk, st);
+        linear_i8_tcgen05_pair_kernel<YT, GATED>(tw, tw2, tx, ops, static_cast<YT *>(y), none, M, N, K, ldy, epilogue, sk, st);
     };
     if (tile_list >= 2) {
         // the two-launch scheme of launch_pair for a short last wave, `tile_list` standing for the pair tiles
@@ -56,21 +50,14 @@ int run_as(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint
         if (c != 0) return -3;  // the kernel leaves the tile counters at zero for the next launch
     return 0;
 }
-template <typename YT, bool GATED>
-int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
-        int epilogue, int splits, int tile_list, DeviceStatus *st) {
-    return g_a_f16 ? run_as<YT, GATED, true>(q, q_up, ops, x, y, M, N, K, ldy, epilogue, splits, tile_list, st)
-                   : run_as<YT, GATED, false>(q, q_up, ops, x, y, M, N, K, ldy, epilogue, splits, tile_list, st);
-}
 }  // namespace
 
-extern "C" void emu_set_a_f16(int on) { g_a_f16 = on != 0; }
 extern "C" int emu_last_a_format() { return emu::g_last_a_format.load(); }  // 0 = f16, 1 = bf16
 
 // q_up == NULL: plain forward; else silu(gate) * up.  splits: K splits (blockIdx.z).  Returns 0; -1 for a shape
 // the launcher refuses; -2 when a bounded wait of the kernel gave up; -3 when a tile counter was left set;
 // -4 when a rule of the model was violated.  tile_list: 0 = (channel pair, token tile) grid; 1 = 1-D list of
-// pair tiles; >= 2 = two launches (see run_as).
+// pair tiles; >= 2 = two launches (see run).
 extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const float *bias, const int8_t *q_up,
                                      const float *scales_up, const float *bias_up, const void *x, void *y, int M, int N, int K,
                                      size_t ldy, int epilogue, int y_bf16, int splits, int tile_list) {

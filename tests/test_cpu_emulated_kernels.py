@@ -576,38 +576,10 @@ def test_tcgen05_bf16_output_and_accumulate_epilogue(oracle, emu_tc):
     assert oracle.rel_err(y, ref + prev) < 2e-6
 
 
-@pytest.mark.parametrize("tok,M,N,K,splits,gated", [(16, 7, 130, 640, 2, False), (128, 100, 129, 1280, 1, False),
-                                                    (256, 300, 140, 704, 1, False), (128, 128, 70, 384, 1, True),
-                                                    (64, 50, 64, 640, 2, True)])
-def test_tcgen05_f16_weights_give_the_same_bits(oracle, emu_tc, tok, M, N, K, splits, gated):
-    # SHREWQ_TC_A_F16 (not yet run on a GPU): the converters hand the tensor core f16 weights (5 instructions
-    # per 4 codes instead of 11) beside bf16 activations.  Every code is exact in both formats, so each
-    # product, and with the same order of accumulation the whole result, is bit-identical.  All 255 code
-    # values occur.
-    q, scales, bias, x_bits, x = _tc_case(M, N, K, tok + 40)
-    q[0, :255] = np.arange(-127, 128, dtype=np.int16).astype(np.int8)
-    q[0, 255] = -128                                    # never produced by the quantizer; still converted exactly
-    up = None
-    if gated:
-        rng = np.random.default_rng(tok)
-        up = (rng.integers(-127, 128, size=(N, K)).astype(np.int8), rng.random(N) * 1e-2 + 1e-4, None)
-    y_bf = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, 3, splits=splits, up=up)
-    assert emu_tc.emu_last_a_format() == 1
-    emu_tc.emu_set_a_f16(1)
-    try:
-        y_h = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, 3, splits=splits, up=up)
-        assert emu_tc.emu_last_a_format() == 0             # the tensor core was told f16, and got f16
-    finally:
-        emu_tc.emu_set_a_f16(0)
-    np.testing.assert_array_equal(y_h, y_bf)
-    if not gated:
-        assert oracle.rel_err(y_h, oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)) < 2e-6
-
-
 @pytest.mark.parametrize("seed", range(36))
 def test_tcgen05_random_configurations(oracle, emu_tc, seed):
     # a seeded sweep over what the launcher can combine: token tile, converter groups, K splits, plain or
-    # gate/up tile, output type, elementwise op, f16 or bf16 weights in tensor memory, grid or tile list,
+    # gate/up tile, output type, elementwise op, grid or tile list,
     # ragged M / N / K (K a multiple of 16 only)
     rng = np.random.default_rng(1000 + seed)
     tok = int(rng.choice([16, 32, 64, 128, 256]))
@@ -621,7 +593,6 @@ def test_tcgen05_random_configurations(oracle, emu_tc, seed):
     kblk = 64 if tok == 256 else 128
     rounds = -(-K // kblk)
     splits = int(rng.integers(1, min(4, rounds) + 1))
-    af16 = groups == 3 and bool(rng.integers(0, 2))
     tile_list = int(rng.integers(0, 2))
     q, scales, bias, x_bits, x = _tc_case(M, N, K, seed)
     up = None
@@ -633,9 +604,8 @@ def test_tcgen05_random_configurations(oracle, emu_tc, seed):
         ref = _gated_ref(oracle, q, scales, bias, qu, su, bu, x)
     else:
         ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=relu)
-    what = dict(tok=tok, M=M, N=N, K=K, groups=groups, gated=gated, y_bf16=y_bf16, relu=relu, splits=splits, af16=af16,
+    what = dict(tok=tok, M=M, N=N, K=K, groups=groups, gated=gated, y_bf16=y_bf16, relu=relu, splits=splits,
                 tile_list=tile_list)
-    emu_tc.emu_set_a_f16(int(af16))
     emu_tc.emu_tma_async.argtypes = [_cu, _cu]
     if seed % 3 == 0:                                  # loads land late and newest first
         emu_tc.emu_tma_async(seed + 1, int(rng.choice([8, 200, 1500])))
@@ -644,7 +614,6 @@ def test_tcgen05_random_configurations(oracle, emu_tc, seed):
         y = _tc_forward(emu_tc, q, scales, bias, x_bits, tok, groups, splits=splits, y_bf16=y_bf16, epilogue=int(relu), up=up,
                         tile_list=tile_list)
     finally:
-        emu_tc.emu_set_a_f16(0)
         emu_tc.emu_tma_async(0, 0)
     if y_bf16:
         y = (y.astype(np.uint32) << 16).view(np.float32)
@@ -711,35 +680,6 @@ def test_cta_pair_forward_matches_oracle(oracle, emu_pair, M, N, K):
     assert oracle.rel_err((y16.astype(np.uint32) << 16).view(np.float32), ref_nb) < 1e-2
 
 
-@pytest.mark.parametrize("M,N,K,splits,gated", [(300, 300, 320, 1, False), (260, 256, 1024, 2, False), (257, 130, 256, 1, True)])
-def test_cta_pair_f16_weights_give_the_same_bits(emu_pair, M, N, K, splits, gated):
-    # SHREWQ_TC_A_F16 on the pair kernel: f16 weights beside bf16 activations, bit-identical results
-    q, scales, bias, x_bits, x = _tc_case(M, N, K, M + 1)
-    q[0, :255] = np.arange(-127, 128, dtype=np.int16).astype(np.int8)
-    qa, xa = _aligned(q.shape, np.int8), _aligned(x_bits.shape, np.uint16)
-    qa[...] = q
-    xa[...] = x_bits
-    s32 = scales.astype(np.float32)
-    up = (None, None, None)
-    if gated:
-        rng = np.random.default_rng(9)
-        qu = _aligned(q.shape, np.int8)
-        qu[...] = rng.integers(-127, 128, size=q.shape).astype(np.int8)
-        su = (rng.random(N) * 1e-2 + 1e-4).astype(np.float32)
-        up = (_p(qu), _p(su), None)
-    ys = []
-    for on, fmt in ((0, 1), (1, 0)):
-        emu_pair.emu_set_a_f16(on)
-        try:
-            y = np.full((M, N), 7.0, np.float32)
-            assert emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), *up, _p(xa), _p(y), M, N, K, N, 0, 0, splits, 0) == 0
-            assert emu_pair.emu_last_a_format() == fmt
-        finally:
-            emu_pair.emu_set_a_f16(0)
-        ys.append(y)
-    np.testing.assert_array_equal(ys[0], ys[1])
-
-
 @pytest.mark.parametrize("seed", range(15))
 def test_cta_pair_random_configurations(oracle, emu_pair, seed):
     rng = np.random.default_rng(2000 + seed)
@@ -751,7 +691,6 @@ def test_cta_pair_random_configurations(oracle, emu_pair, seed):
     relu = (not gated) and bool(rng.integers(0, 2))
     rounds = -(-K // 128)
     splits = int(rng.integers(1, min(3, rounds) + 1))
-    af16 = bool(rng.integers(0, 2))
     tile_list = int(rng.integers(0, 2))
     q, scales, bias, x_bits, x = _tc_case(M, N, K, seed)
     qa, xa = _aligned(q.shape, np.int8), _aligned(x_bits.shape, np.uint16)
@@ -769,9 +708,8 @@ def test_cta_pair_random_configurations(oracle, emu_pair, seed):
         ref = _gated_ref(oracle, q, scales, bias, qu, su, bu, x)
     else:
         ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=relu)
-    what = dict(M=M, N=N, K=K, gated=gated, y_bf16=y_bf16, relu=relu, splits=splits, af16=af16, tile_list=tile_list)
+    what = dict(M=M, N=N, K=K, gated=gated, y_bf16=y_bf16, relu=relu, splits=splits, tile_list=tile_list)
     y = np.full((M, N), 0x4100, np.uint16) if y_bf16 else np.full((M, N), 7.0, np.float32)
-    emu_pair.emu_set_a_f16(int(af16))
     emu_pair.emu_tma_async.argtypes = [_cu, _cu]
     if seed % 3 == 0:                                  # loads land late and newest first
         emu_pair.emu_tma_async(seed + 1, int(rng.choice([8, 200, 1500])))
@@ -780,7 +718,6 @@ def test_cta_pair_random_configurations(oracle, emu_pair, seed):
         rc = emu_pair.emu_gemm_tcgen05_pair(_p(qa), _p(s32), _p(bias), *up, _p(xa), _p(y), M, N, K, N, int(relu), int(y_bf16), splits,
                                             tile_list)
     finally:
-        emu_pair.emu_set_a_f16(0)
         emu_pair.emu_tma_async(0, 0)
     if rc == -4:
         emu_pair.emu_fail_message.restype = ctypes.c_char_p

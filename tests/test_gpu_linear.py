@@ -344,7 +344,6 @@ def test_f32_activations_on_tensor_cores(oracle, M, N, K):
     _check(oracle, ql, x_t, x_np, b, 1, TOL_F32, relu=True, force="tcgen05-f32")
 
 
-@_UNVALIDATED
 @pytest.mark.parametrize("N,K,dtype", [(256, 256, "f32"), (1024, 256, "f32"), (256, 1024, "f32"), (50257, 256, "f32"),
                                        (50257, 256, "bf16"), (1024, 256, "bf16")])
 def test_config2_tinygpt_shaped_linears(oracle, N, K, dtype):
@@ -387,32 +386,6 @@ def test_cta_pair_gate_up_parity(oracle):
 
 
 
-# Held off the GPU: an earlier implementation of this operand mix (f16 A beside bf16 B under kind::f16) failed with a
-# CUDA error on every launch, in three runs, and the cause was never established.  Not part of SHREWQ_TEST_UNVALIDATED.
-@pytest.mark.skipif(__import__("os").environ.get("SHREWQ_TEST_AF16", "0") != "1",
-                    reason="mixed f16 / bf16 operands faulted in an earlier form, cause unknown; SHREWQ_TEST_AF16=1 runs it")
-@pytest.mark.parametrize("M,N,K", [(8, 523, 1024), (64, 4096, 4096), (128, 1000, 1040), (512, 4096, 4096), (1024, 1000, 2048)])
-def test_f16_weights_in_tensor_memory_give_the_same_bits(oracle, monkeypatch, M, N, K):
-    # SHREWQ_TC_A_F16=1: the converters write f16 instead of bf16 weights (every code exact in both), the
-    # activations stay bf16: same products, same accumulation order, so the very same output bits
-    from shrew_b200 import _lib
-    from shrew_b200.quantize import Device
-    ql, w, b = _make(N, K, 1, seed=N + K)
-    x_t, x_np = _x(M, K, "bf16", seed=M)
-    monkeypatch.setenv("SHREWQ_TC_A_F16", "1")
-    _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, force="tcgen05")
-    _lib.lib().shrewq_force_kernel(b"tcgen05")
-    try:
-        y_h = ql.forward(x_t)
-        monkeypatch.setenv("SHREWQ_TC_A_F16", "0")
-        y_b = ql.forward(x_t)
-        Device.get("cuda:0").synchronize()
-    finally:
-        _lib.lib().shrewq_force_kernel(b"auto")
-    assert torch.equal(y_h, y_b)
-
-
-@_UNVALIDATED
 @pytest.mark.parametrize("M,N,K,dtype", [(1, 300, 512, "bf16"), (40, 256, 784, "f32"), (200, 1000, 1024, "bf16")])
 def test_forward_from_host_buffers(oracle, M, N, K, dtype):
     # shrewq_linear_forward_host: host activations in, host result out, the copies inside the call; the same kernels as
