@@ -24,8 +24,13 @@
  *  - Device entry points enqueue work on the context's stream and return without
  *    synchronising.  Host entry points (suffix _host) copy in, run, copy out and
  *    synchronise the stream before returning.
- *  - A context belongs to one host thread at a time.  A shrewq_linear is immutable after
- *    creation.
+ *  - A context belongs to one host thread at a time: its stream, workspaces and error text are not
+ *    locked.  A shrewq_linear is immutable after creation (a forward reads it and writes nothing to
+ *    it) but is bound to the context it was created on, so threads that share a handle share that
+ *    context and must serialise their calls.  The reference's `Module: Send + Sync` bound
+ *    (distributed.rs:175-179) is met by a shim that keeps the context behind a mutex, or by one
+ *    context and one set of handles per thread over the same device buffers (handles are cheap: a
+ *    copy of the scales and two tensor maps).
  *  - There is no CPU fallback: without a CUDA device every compute call fails with
  *    SHREWQ_ERR_NO_DEVICE.
  */
@@ -81,6 +86,17 @@ typedef struct shrewq_linear shrewq_linear;
  * cudaStream_t (NULL = the default stream). */
 SHREWQ_API int shrewq_ctx_create(int device, void *stream, shrewq_ctx **out);
 SHREWQ_API int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream);
+/* Launch options of a context (no counterpart in the reference); the defaults are the measured choices and
+ * need no setting.  name / value:
+ *   "tc_groups"    1..3   converter groups of the tensor-core kernel (default 3)
+ *   "tc_splitk"    0/1    split K when the tile grid leaves SMs idle (default 1)
+ *   "tc_tok"       0, 16, 32, 64, 128, 256   force the token tile (default 0 = choose)
+ *   "tc_tok_gated" the same for gate/up launches only
+ *   "tc_tailsplit" 0/1    issue a short last wave as a second launch split along K (default 0)
+ *   "tc_pair"      0/1    batches above 128 tokens on CTA pairs (tcgen05.mma.cta_group::2)
+ *   "gemv_pdl"     0/1    programmatic dependent launch of the small-batch kernel (default 0)
+ * Unknown names and values out of range return SHREWQ_ERR_INVALID_ARG. */
+SHREWQ_API int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value);
 SHREWQ_API int shrewq_ctx_synchronize(shrewq_ctx *ctx);
 SHREWQ_API void shrewq_ctx_destroy(shrewq_ctx *ctx);
 SHREWQ_API const char *shrewq_last_error(const shrewq_ctx *ctx);
@@ -105,8 +121,7 @@ SHREWQ_API int shrewq_quantize_f32(shrewq_ctx *ctx, const float *w_dev, size_t r
  * in all (one per 64 tensors per-channel, three per-tensor) instead of one to three each, which is what
  * a model of many small matrices needs; results are the same bits as shrewq_quantize_f32 gives.  Tuned
  * for small tensors (a warp per row): tensors of many MB are better quantized one by one.  No device
- * memory is allocated beyond the context's scratch.  Built and checked on the CPU model; not yet run on
- * a GPU.
+ * memory is allocated beyond the context's scratch.
  */
 typedef struct shrewq_quant_item {
     const float *w_dev;
@@ -137,7 +152,7 @@ SHREWQ_API int shrewq_dequantize(shrewq_ctx *ctx, const int8_t *q_dev, const dou
  * job), then every rank calls shrewq_quantize_f32_given_amax with the reduced value.  Codes and
  * scale are then bit-identical to quantizing the unsplit tensor.  Per-channel shards need none of
  * this: shrewq_quantize_f32 on the shard is already identical.  No counterpart in the reference
- * (which is single-device); not yet run on a GPU (the kernels are those of the per-tensor path).
+ * (which is single-device).
  */
 SHREWQ_API int shrewq_absmax_f32(shrewq_ctx *ctx, const float *w_dev, size_t n, float *amax_dev);
 SHREWQ_API int shrewq_quantize_f32_given_amax(shrewq_ctx *ctx, const float *w_dev, size_t n,
@@ -148,9 +163,8 @@ SHREWQ_API int shrewq_quantize_f32_given_amax(shrewq_ctx *ctx, const float *w_de
  * codes are stored one per byte, as the reference's Vec<i8> does, within [-8, 7]), mode =
  * SHREWQ_SYMMETRIC or SHREWQ_ASYMMETRIC (compute_scale_zp, :353-364: scale from max - min, zero
  * point round(qmin - min / scale)).  zero_points_dev receives 1 or `rows` f64 values (0.0 in
- * symmetric mode).  bits = 8 with SHREWQ_SYMMETRIC runs the kernels of shrewq_quantize_f32.  The
- * kernels of the other modes are built but have not run on a GPU yet: they answer
- * SHREWQ_ERR_UNSUPPORTED unless the environment sets SHREWQ_EXPERIMENTAL_MODES=1.
+ * symmetric mode).  bits = 8 with SHREWQ_SYMMETRIC runs the kernels of shrewq_quantize_f32; the other
+ * modes replay the reference's f64 operations one for one (correct first, not tuned).
  * shrewq_dequantize_ex with zero_points_dev = NULL is shrewq_dequantize.
  */
 SHREWQ_API int shrewq_quantize_f32_ex(shrewq_ctx *ctx, const float *w_dev, size_t rows, size_t cols,
@@ -158,8 +172,8 @@ SHREWQ_API int shrewq_quantize_f32_ex(shrewq_ctx *ctx, const float *w_dev, size_
                            double *zero_points_dev);
 /* quantize_tensor for a tensor of any float storage type (quantize.rs:194-205 widens every dtype with
  * to_f64_vec): w_dtype = SHREWQ_F32, SHREWQ_BF16, SHREWQ_F16 or SHREWQ_F64, any bits / mode.  All
- * arithmetic in f64 as in the reference.  Experimental like the other modes (f32 INT8 symmetric input
- * should use shrewq_quantize_f32, the tuned path).  shrewq_dequantize_ex likewise narrows to any of the
+ * arithmetic in f64 as in the reference (f32 INT8 symmetric input should use shrewq_quantize_f32, the
+ * tuned path).  shrewq_dequantize_ex likewise narrows to any of the
  * four types when given SHREWQ_F16 / SHREWQ_F64 (dequantize_tensor, quantize.rs:210-225). */
 SHREWQ_API int shrewq_quantize_any(shrewq_ctx *ctx, const void *w_dev, int w_dtype, size_t rows, size_t cols,
                         int granularity, int bits, int mode, int8_t *q_dev, double *scales_dev,
@@ -185,8 +199,7 @@ SHREWQ_API int shrewq_linear_create(shrewq_ctx *ctx, const int8_t *q_dev, const 
 /* QuantizedLinear::new for a weight quantized with zero points (asymmetric mode): the forward
  * computes scale * sum(q x) + bias - (scale * zero_point) * sum(x), which equals the reference's
  * x . dequant(W)^T + bias up to f32 rounding.  zero_points_dev = NULL is shrewq_linear_create.
- * Same experimental status and environment switch as shrewq_quantize_f32_ex; such a handle is
- * not accepted by the gate/up, peer-destination and no-allocation forwards. */
+ * Such a handle is not accepted by the gate/up, peer-destination and no-allocation forwards. */
 SHREWQ_API int shrewq_linear_create_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *scales_dev,
                             const double *zero_points_dev, const float *bias_dev, size_t out_features,
                             size_t in_features, int granularity, shrewq_linear **out);
@@ -197,7 +210,6 @@ SHREWQ_API int shrewq_linear_create_ex(shrewq_ctx *ctx, const int8_t *q_dev, con
  * code 2j + 8 in the low and code 2j+1 + 8 in the high nibble; shrewq_linear_create_int4 builds a
  * QuantizedLinear over such rows (symmetric scales).  Its forward streams half the bytes of INT8; it
  * is served by the warp-MMA kernel only: bf16 activations, M <= 32, in_features a multiple of 128.
- * Experimental (SHREWQ_EXPERIMENTAL_MODES=1), not yet run on a GPU.
  */
 SHREWQ_API int shrewq_pack_int4(shrewq_ctx *ctx, const int8_t *q_dev, size_t rows, size_t cols, uint8_t *packed_dev);
 SHREWQ_API int shrewq_linear_create_int4(shrewq_ctx *ctx, const uint8_t *packed_dev, const double *scales_dev,
@@ -237,11 +249,15 @@ SHREWQ_API int shrewq_linear_forward_host(shrewq_linear *lin, const void *x_host
  *    and weights.  Anything else returns SHREWQ_ERR_UNSUPPORTED.
  *  - Limit: a shape whose split-K scratch (4096 B + tiles * splits * TOK * 128 * 4 B, with
  *    TOK the token tile of 16, 32 or 64) exceeds 4 MiB is refused with
- *    SHREWQ_ERR_UNSUPPORTED and a message giving both sizes; batches above 64 tokens are
- *    never split along K and never touch the array.
+ *    SHREWQ_ERR_UNSUPPORTED and a message giving both sizes.  This entry point splits K for
+ *    token tiles of up to 64 tokens only (with the default options: batches above 64 tokens
+ *    are not split and do not touch the array; option "tc_tok" can force a small tile for a
+ *    larger batch, which the size check then covers like any other shape).
  *  - Every GPU that loads the library holds the 4 MiB until the process exits.
  *  - The first call on each device looks up the array's device address (a host-side
- *    query, done once and cached); make that first call before any stream capture begins.
+ *    query, done once and cached; safe from several threads) and, like the first use of any
+ *    kernel, may make the CUDA runtime load the library's device code, which can allocate:
+ *    make that first call at start-up, before memory is tight and before any stream capture.
  *  - All calls on a device share the one array, which keeps the previous call's contents
  *    (the tile counters are cleared at the start of every call).  Two calls that overlap
  *    on the GPU — different streams, or different contexts on one device — race on it;
@@ -275,22 +291,47 @@ SHREWQ_API int shrewq_linear_forward_peers(shrewq_linear *lin, shrewq_linear *up
                                            size_t M, void *y_dev, void *const *peer_y_dev, int n_peers, int y_dtype,
                                            size_t ldy, int epilogue);
 
+/*
+ * Barrier between the GPUs of a sharded layer, on the device (no counterpart in the reference:
+ * DataParallel::forward, distributed.rs:188-201, is a sequential loop in one process).
+ * shrewq_linear_forward_peers writes into other GPUs' buffers; before a rank reads its copy of the
+ * output every rank's stores must have landed, and before a rank overwrites a peer's copy again that
+ * peer must be done with it.  shrewq_exchange_barrier enqueues one small kernel on the context's
+ * stream: it tells every peer "all work enqueued on my stream before this point is complete and
+ * visible" and waits until every peer has said the same.
+ *
+ * flag_blocks_dev[r] (r < world <= 8) is rank r's flag block as mapped into THIS process
+ * (flag_blocks_dev[rank] is this GPU's own memory): SHREWQ_EXCHANGE_FLAG_BYTES bytes each, 4-byte
+ * aligned, zeroed once by its owner before any rank's first barrier (with a host-side barrier between
+ * the zeroing and the first use).  Every rank must enqueue the same sequence of barriers.  The barrier
+ * count lives in device memory, so a barrier captured in a CUDA graph stays correct when replayed.
+ *
+ * The wait is bounded (about a second): a rank whose peer never arrives gives up, the kernel ends and
+ * the next shrewq_ctx_synchronize returns SHREWQ_ERR_TIMEOUT naming the missing rank.  After a timeout
+ * the ranks' counts no longer agree: zero the flag blocks (all ranks, host barrier) and create a new
+ * exchange before using the buffers again.
+ */
+#define SHREWQ_EXCHANGE_FLAG_BYTES 256
+typedef struct shrewq_exchange shrewq_exchange;
+SHREWQ_API int shrewq_exchange_create(shrewq_ctx *ctx, int rank, int world, void *const *flag_blocks_dev,
+                                      shrewq_exchange **out);
+SHREWQ_API int shrewq_exchange_barrier(shrewq_exchange *ex);
+SHREWQ_API void shrewq_exchange_destroy(shrewq_exchange *ex);
+
 /* Accessors mirroring QuantizedLinear's public fields / methods (quantize.rs:392-394,
  * :455-459). */
 SHREWQ_API size_t shrewq_linear_in_features(const shrewq_linear *lin);
 SHREWQ_API size_t shrewq_linear_out_features(const shrewq_linear *lin);
 SHREWQ_API size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin);
 
-/* Name of the kernel family the last forward on this handle dispatched to ("gemv",
- * "tcgen05", "simt"); for tests and benchmarks. */
+/* Name of the kernel family the calling thread's latest forward dispatched to ("gemv", "mma", "tcgen05",
+ * "tcgen05-2cta", "tcgen05-f32", "simt", "mma-w4"); for tests and benchmarks.  Kept per thread, not in the
+ * handle, so that a forward writes nothing to the handle it reads. */
 SHREWQ_API const char *shrewq_linear_last_kernel(const shrewq_linear *lin);
-/* Forces the kernel family used by forwards issued from the calling thread: "gemv",
- * "tcgen05", "simt", or "auto"/NULL to restore the built-in choice.  Two further names select
- * kernels that are built but not yet validated on a GPU and are never chosen automatically:
- * "mma" (warp-level MMA for M <= 64), "mma-f16" (the same with f16 operands: activations
- * rescaled per token row by a power of two, codes widened in one instruction each),
- * "tcgen05-f32" (f32 activations split into bf16 hi + lo and run as two tensor-core passes)
- * and "tcgen05-2cta" (CTA pairs, tcgen05.mma.cta_group::2).  A forced kernel that
+/* Forces the kernel family used by forwards issued from the calling thread: "gemv" (CUDA cores, M <= 16),
+ * "mma" (warp-level MMA, M <= 64), "tcgen05" (single-CTA tensor-core kernel), "tcgen05-2cta" (CTA pairs,
+ * tcgen05.mma.cta_group::2), "tcgen05-f32" (f32 activations as a bf16 hi/lo pair on the tensor cores),
+ * "simt" (general f32 kernel), or "auto"/NULL to restore the built-in choice.  A forced kernel that
  * cannot take a shape makes the forward fail with SHREWQ_ERR_UNSUPPORTED (it never falls
  * back silently).  For tests and benchmarks; no counterpart in the reference. */
 SHREWQ_API int shrewq_force_kernel(const char *name);

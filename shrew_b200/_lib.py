@@ -15,6 +15,7 @@ PER_TENSOR, PER_CHANNEL = 0, 1
 SYMMETRIC, ASYMMETRIC = 0, 1
 F32, BF16, F16, F64 = 0, 1, 2, 3
 EPILOGUE_NONE, EPILOGUE_RELU = 0, 1
+EXCHANGE_FLAG_BYTES = 256
 
 # SHREWQ_LIB points at another build of the same library (e.g. the tracing build)
 LIB_PATH = os.environ.get("SHREWQ_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libshrewq.so")
@@ -25,6 +26,7 @@ _pp = ctypes.POINTER(ctypes.c_void_p)
 SIGNATURES = {
     "shrewq_ctx_create": (_ci, [_ci, _vp, _pp]),
     "shrewq_ctx_set_stream": (_ci, [_vp, _vp]),
+    "shrewq_ctx_set_option": (_ci, [_vp, ctypes.c_char_p, _ci]),
     "shrewq_ctx_synchronize": (_ci, [_vp]),
     "shrewq_ctx_destroy": (None, [_vp]),
     "shrewq_last_error": (ctypes.c_char_p, [_vp]),
@@ -48,6 +50,9 @@ SIGNATURES = {
     "shrewq_linear_forward_noalloc": (_ci, [_vp, _vp, _sz, _vp, _ci, _sz, _ci]),
     "shrewq_linear_forward_peers": (_ci, [_vp, _vp, _vp, _ci, _sz, _vp, _pp, _ci, _ci, _sz, _ci]),
     "shrewq_linear_forward_gate_up_silu": (_ci, [_vp, _vp, _vp, _ci, _sz, _vp, _ci, _sz]),
+    "shrewq_exchange_create": (_ci, [_vp, _ci, _ci, _pp, _pp]),
+    "shrewq_exchange_barrier": (_ci, [_vp]),
+    "shrewq_exchange_destroy": (None, [_vp]),
     "shrewq_linear_in_features": (_sz, [_vp]),
     "shrewq_linear_out_features": (_sz, [_vp]),
     "shrewq_linear_memory_savings_bytes": (_sz, [_vp]),

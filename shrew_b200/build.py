@@ -15,7 +15,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libshrewq.so")
-SOURCES = ["api.cu", "quantize.cu", "quantize_batch.cu", "quantize_modes.cu", "gemv.cu", "gemv_mma.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu"]
+SOURCES = ["api.cu", "quantize.cu", "quantize_batch.cu", "quantize_modes.cu", "gemv.cu", "gemv_mma.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu", "exchange.cu"]
 HEADERS = sorted(os.path.join(CSRC, h) for h in os.listdir(CSRC) if h.endswith(".cuh")) + [os.path.join(HERE, "..", "include", "shrewq.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

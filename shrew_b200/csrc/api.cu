@@ -69,7 +69,7 @@ static int bind(shrewq_ctx *ctx) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceMmaF16, kForceTcF32, kForceTc2Cta };
+enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceTcF32, kForceTc2Cta };
 
 }  // namespace shrewq
 
@@ -77,6 +77,9 @@ using namespace shrewq;
 
 // kernel family forced by shrewq_force_kernel for this thread (tests and benchmarks)
 static thread_local int g_forced_kernel = kAuto;
+// kernel family of this thread's latest forward (shrewq_linear_last_kernel): per thread, so that
+// forwards issued from several threads on handles they share do not write to the handle
+static thread_local const char *g_last_kernel = "none";
 
 extern "C" {
 
@@ -122,6 +125,25 @@ int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream) {
     return SHREWQ_OK;
 }
 
+int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value) {
+    if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "set_option: ctx is NULL");
+    if (!name) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: name is NULL");
+    Tuning &t = ctx->tuning;
+    if (!strcmp(name, "tc_groups")) {
+        if (value < 1 || value > 3) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: tc_groups is 1, 2 or 3");
+        t.tc_groups = value;
+    } else if (!strcmp(name, "tc_splitk")) t.tc_splitk = value != 0;
+    else if (!strcmp(name, "tc_tok") || !strcmp(name, "tc_tok_gated")) {
+        if (value != 0 && value != 16 && value != 32 && value != 64 && value != 128 && value != 256)
+            return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: %s is 0 (choose), 16, 32, 64, 128 or 256", name);
+        (name[6] == '_' ? t.tc_tok_gated : t.tc_tok) = value;
+    } else if (!strcmp(name, "tc_tailsplit")) t.tc_tailsplit = value != 0;
+    else if (!strcmp(name, "tc_pair")) t.tc_pair = value != 0;
+    else if (!strcmp(name, "gemv_pdl")) t.gemv_pdl = value != 0;
+    else return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);
+    return SHREWQ_OK;
+}
+
 int shrewq_ctx_synchronize(shrewq_ctx *ctx) {
     if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "synchronize: ctx is NULL");
     int rc = bind(ctx);
@@ -153,12 +175,15 @@ void shrewq_ctx_destroy(shrewq_ctx *ctx) {
 
 const char *shrewq_last_error(const shrewq_ctx *ctx) { return ctx ? ctx->err : g_create_err; }
 
-uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx) { return ctx ? ctx->launches : 0; }
+uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx) { return ctx ? ctx->launches.load() : 0; }
 
-// The default kernel family of a forward: the one rule, shared by forward_impl and shrewq_plan_forward.
-static int default_family(size_t M, bool gemv_ok, bool tc_ok) {
-    if (gemv_ok && (M <= 4 || !tc_ok)) return kForceGemv;
-    return tc_ok ? kForceTc : kForceSimt;
+// The default kernel family of a forward with bf16 activations: the one rule, shared by forward_impl and
+// shrewq_plan_forward.  Measured on 4096 x 4096: the CUDA-core GEMV wins up to 2 tokens, the warp-MMA kernel
+// from 3 to 32, the tcgen05 kernel above.
+static int default_family(size_t M, bool gemv_ok, bool mma_ok, bool tc_ok) {
+    if (gemv_ok && (M <= 2 || (!mma_ok && (M <= 4 || !tc_ok)))) return kForceGemv;
+    if (mma_ok && M <= 32) return kForceMma;
+    return tc_ok ? kForceTc : (gemv_ok ? kForceGemv : kForceSimt);
 }
 
 int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, int sm_count, char *kernel, size_t kernel_len,
@@ -171,8 +196,11 @@ int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, 
     const bool vec16 = (K % 16) == 0;
     const bool small = M < (1u << 31) && N < (1u << 31) && K < (1u << 31);
     const bool tc_ok = x_is_bf16 && vec16 && M >= 1 && small;
-    const int fam = default_family(M, vec16 && M <= 16, tc_ok);
-    const char *name = fam == kForceGemv ? "gemv" : fam == kForceTc ? "tcgen05" : "simt";
+    const bool mma_ok = x_is_bf16 && (K % 64) == 0 && M <= 64 && small;
+    int fam = default_family(M, vec16 && M <= 16, mma_ok, tc_ok);
+    if (!x_is_bf16 && vec16 && small && M > 16 && !gated) fam = kForceTcF32;   // f32 activations: the hi/lo tensor-core pass
+    const char *name = fam == kForceGemv ? "gemv" : fam == kForceMma ? "mma" : fam == kForceTc ? "tcgen05"
+                       : fam == kForceTcF32 ? "tcgen05-f32" : "simt";
     snprintf(kernel, kernel_len, "%s", name);
     if (!strcmp(name, "tcgen05"))
         return plan_gemm_tcgen05(M, N, K, gated != 0, sm_count, tok, n_tiles, m_tiles, splits, rounds_per_split);
@@ -185,7 +213,6 @@ int shrewq_force_kernel(const char *name) {
     else if (!strcmp(name, "tcgen05")) g_forced_kernel = kForceTc;
     else if (!strcmp(name, "simt")) g_forced_kernel = kForceSimt;
     else if (!strcmp(name, "mma")) g_forced_kernel = kForceMma;
-    else if (!strcmp(name, "mma-f16")) g_forced_kernel = kForceMmaF16;
     else if (!strcmp(name, "tcgen05-f32")) g_forced_kernel = kForceTcF32;
     else if (!strcmp(name, "tcgen05-2cta")) g_forced_kernel = kForceTc2Cta;
     else return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "force_kernel: unknown kernel '%s'", name);
@@ -301,26 +328,10 @@ int shrewq_quantize_f32_given_amax(shrewq_ctx *ctx, const float *w_dev, size_t n
     return launch_quantize_given_amax(ctx, w_dev, n, amax_dev, q_dev, scale_dev);
 }
 
-// ---- the reference's other modes (asymmetric INT8, INT4) ------------------------------------
-// Built and checked against the CPU restatement by reading only: until they have run on a GPU
-// they answer SHREWQ_ERR_UNSUPPORTED unless the environment sets SHREWQ_EXPERIMENTAL_MODES=1.
-static bool env_flag(const char *name) {
-    const char *e = getenv(name);
-    return e && atoi(e) != 0;
-}
-
-static bool experimental_modes() {
-    const char *e = getenv("SHREWQ_EXPERIMENTAL_MODES");
-    return e && atoi(e) != 0;
-}
-
+// ---- the reference's other modes (asymmetric INT8, INT4: quantize.rs:99-139,353-364) -----------------
 static int check_mode(shrewq_ctx *ctx, int bits, int mode, const char *who) {
     if ((bits != 8 && bits != 4) || (mode != SHREWQ_SYMMETRIC && mode != SHREWQ_ASYMMETRIC))
         return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "%s: bits must be 8 or 4, mode SHREWQ_SYMMETRIC or SHREWQ_ASYMMETRIC", who);
-    if (!(bits == 8 && mode == SHREWQ_SYMMETRIC) && !experimental_modes())
-        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
-                       "%s: only INT8 symmetric is validated; INT4 and asymmetric kernels are built but have not run on a "
-                       "GPU yet (SHREWQ_EXPERIMENTAL_MODES=1 enables them)", who);
     return SHREWQ_OK;
 }
 
@@ -357,10 +368,6 @@ int shrewq_quantize_any(shrewq_ctx *ctx, const void *w_dev, int w_dtype, size_t 
         return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_any: w_dtype must be SHREWQ_F32, _BF16, _F16 or _F64");
     if ((bits != 8 && bits != 4) || (mode != SHREWQ_SYMMETRIC && mode != SHREWQ_ASYMMETRIC))
         return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_any: bits must be 8 or 4, mode SHREWQ_SYMMETRIC or SHREWQ_ASYMMETRIC");
-    if (!experimental_modes())
-        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
-                       "quantize_any: the any-dtype kernels are built but have not run on a GPU yet (SHREWQ_EXPERIMENTAL_MODES=1 "
-                       "enables them; f32 INT8 symmetric has shrewq_quantize_f32)");
     const size_t n = rows * cols;
     if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "quantize_any: rows*cols overflows");
     const size_t ns = granularity == SHREWQ_PER_CHANNEL ? rows : 1;
@@ -381,8 +388,6 @@ int shrewq_dequantize_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *sca
     if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: ctx is NULL");
     int rc = check_gran(ctx, granularity, "dequantize_ex");
     if (rc != SHREWQ_OK) return rc;
-    if (!experimental_modes())
-        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "dequantize_ex: zero points and f16 / f64 outputs need SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
     if (out_dtype != SHREWQ_F32 && out_dtype != SHREWQ_BF16 && out_dtype != SHREWQ_F16 && out_dtype != SHREWQ_F64)
         return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "dequantize_ex: out_dtype must be SHREWQ_F32, _BF16, _F16 or _F64");
     const size_t n = rows * cols;
@@ -394,8 +399,6 @@ int shrewq_dequantize_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *sca
 
 int shrewq_pack_int4(shrewq_ctx *ctx, const int8_t *q_dev, size_t rows, size_t cols, uint8_t *packed_dev) {
     if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "pack_int4: ctx is NULL");
-    if (!experimental_modes())
-        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "pack_int4: needs SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
     if (cols % 2 != 0) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "pack_int4: cols must be even (two codes per byte)");
     const size_t n = rows * cols;
     if (cols != 0 && n / cols != rows) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "pack_int4: rows*cols overflows");
@@ -454,10 +457,6 @@ int shrewq_linear_create_ex(shrewq_ctx *ctx, const int8_t *q_dev, const double *
     if (!zero_points_dev)
         return shrewq_linear_create(ctx, q_dev, scales_dev, bias_dev, out_features, in_features, granularity, out);
     if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "linear_create_ex: ctx is NULL");
-    if (!experimental_modes()) {
-        if (out) *out = nullptr;
-        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "linear_create_ex: zero points need SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
-    }
     int rc = shrewq_linear_create(ctx, q_dev, scales_dev, bias_dev, out_features, in_features, granularity, out);
     if (rc != SHREWQ_OK) return rc;
     shrewq_linear *lin = *out;
@@ -481,8 +480,6 @@ int shrewq_linear_create_int4(shrewq_ctx *ctx, const uint8_t *packed_dev, const 
     if (!ctx) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "linear_create_int4: ctx is NULL");
     if (!out) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_create_int4: out is NULL");
     *out = nullptr;
-    if (!experimental_modes())
-        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "linear_create_int4: needs SHREWQ_EXPERIMENTAL_MODES=1 (kernels not yet run on a GPU)");
     if (in_features % 2 != 0) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "linear_create_int4: in_features must be even");
     // the plain constructor does everything but the TMA descriptors, which describe an INT8 [N,K] matrix
     // and must not be used with packed rows: build the handle, then mark it
@@ -510,36 +507,23 @@ size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin) {
     if (!lin) return 0;
     return lin->n * lin->k * 4 - (lin->int4_packed ? lin->n * lin->k / 2 : lin->n * lin->k);
 }
-const char *shrewq_linear_last_kernel(const shrewq_linear *lin) { return lin ? lin->last_kernel : "none"; }
+const char *shrewq_linear_last_kernel(const shrewq_linear *lin) { return lin ? g_last_kernel : "none"; }
 
-// f32 activations on the tensor cores: x is split into bf16 hi + lo (exact to ~2^-17), the
-// hi pass writes scale*acc to the f32 output, the lo pass adds its own scale*acc, the bias and
-// the elementwise op on top.  Two passes over the codes instead of one, but on the tensor
-// pipe instead of f32 FMAs.  Built and compiled, NOT yet run on a GPU: reachable only with
-// shrewq_force_kernel("tcgen05-f32"); the automatic choice for f32 stays the general f32 kernel.
+// f32 activations on the tensor cores: x is split into bf16 hi + lo (exact to ~2^-17 of each value), the
+// two matrices are stacked in one workspace and the kernel issues two MMAs per k-step into the same
+// accumulator, so the codes are read and converted once and the result keeps the f32 path's 1e-4 tolerance.
 static int forward_f32_on_tensor_cores(shrewq_linear *lin, const ForwardArgs &orig, const char *who) {
     shrewq_ctx *ctx = lin->ctx;
-    const size_t n = orig.M * orig.K, half = align_up(n * 2, 256);
-    int rc = ensure_xsplit(ctx, 2 * half);
+    const size_t n = orig.M * orig.K;
+    int rc = ensure_xsplit(ctx, 2 * n * 2);
     if (rc != SHREWQ_OK) return rc;
-    char *hi = static_cast<char *>(ctx->xsplit), *lo = hi + half;
+    char *hi = static_cast<char *>(ctx->xsplit), *lo = hi + n * 2;
     if ((rc = launch_split_f32(ctx, static_cast<const float *>(orig.x), n, hi, lo)) != SHREWQ_OK) return rc;
     ForwardArgs a = orig;
     a.x_dtype = SHREWQ_BF16;
     a.x = hi;
-    a.bias = nullptr;
-    a.epilogue = SHREWQ_EPILOGUE_NONE;
-    Dests none = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0};
-    a.extra = none;  // peers receive the final values from the second pass only
-    if (!tcgen05_supported(a)) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05 cannot take this shape", who);
-    if ((rc = launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr)) != SHREWQ_OK) return rc;
-    a.x = lo;
-    a.bias = orig.bias;
-    a.epilogue = orig.epilogue | kEpilogueAccumulate;
-    a.extra = orig.extra;
-    rc = launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
-    lin->last_kernel = "tcgen05";
-    return rc;
+    if (!tcgen05_supported(a)) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: the tensor-core kernel cannot take this shape", who);
+    return launch_gemm_tcgen05_xsplit(ctx, a, lin->w_tmap);
 }
 
 static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev, int x_dtype, size_t M, void *y_dev,
@@ -587,7 +571,7 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
                            "%s: packed INT4 weights need bf16 activations, M <= 32, in_features a multiple of 128", who);
         rc = launch_gemv_mma_w4(ctx, a);
-        lin->last_kernel = "mma-w4";
+        g_last_kernel = "mma-w4";
         return rc;
     }
 
@@ -597,9 +581,8 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
     const bool zp_route = lin->czp != nullptr || (up && up->czp != nullptr);
     float *zp_acc = nullptr, *zp_xsum = nullptr;
     if (zp_route) {
-        if (up || n_peers > 0 || g_forced_kernel == kForceTc2Cta || g_forced_kernel == kForceTcF32)
-            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
-                           "%s: zero points are not supported with a gate/up pair, peer destinations or this forced kernel", who);
+        if (up || n_peers > 0)
+            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: zero points are not supported with a gate/up pair or peer destinations", who);
         const size_t acc_bytes = align_up(M * lin->n * sizeof(float), 256);
         if ((rc = grow(ctx, &ctx->ytmp, &ctx->ytmp_bytes, acc_bytes + M * sizeof(float), false)) != SHREWQ_OK) return rc;
         zp_acc = static_cast<float *>(ctx->ytmp);
@@ -613,6 +596,9 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
                        (!up || (reinterpret_cast<uintptr_t>(up->q) & 15) == 0);
     const bool gemv_ok = vec16 && M <= 16;
     const bool tc_ok = tcgen05_supported(a) && lin->tmap_ok && (!up || up->tmap_ok);
+    const bool mma_ok = gemv_mma_supported(a);
+    // f32 activations as bf16 hi + lo on the tensor cores (plain layers only)
+    const bool f32_tc_ok = x_dtype == SHREWQ_F32 && !up && lin->tmap_ok && vec16 && n_peers == 0;
     int choice;
     switch (g_forced_kernel) {
         case kForceGemv:
@@ -620,52 +606,46 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             choice = kForceGemv; break;
         case kForceTc2Cta:
             if (!tc_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05-2cta cannot take this shape/dtype", who);
-            rc = up ? launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap, nullptr);
-            lin->last_kernel = "tcgen05";
-            return rc;
+            choice = kForceTc2Cta; break;
         case kForceTcF32:
-            if (x_dtype == SHREWQ_F32 && y_dtype == SHREWQ_F32 && !up && lin->tmap_ok)
-                return forward_f32_on_tensor_cores(lin, a, who);
-            return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05-f32 needs f32 activations and output, no gate/up pair", who);
+            if (!f32_tc_ok)
+                return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05-f32 needs f32 activations, 16-byte aligned buffers, no gate/up pair", who);
+            choice = kForceTcF32; break;
         case kForceTc:
             if (!tc_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05 cannot take this shape/dtype", who);
             choice = kForceTc; break;
         case kForceSimt: choice = kForceSimt; break;
         case kForceMma:
-        case kForceMmaF16:
-            if (!gemv_mma_supported(a)) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced mma kernel cannot take this shape/dtype", who);
-            choice = g_forced_kernel; break;
+            if (!mma_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced mma kernel cannot take this shape/dtype", who);
+            choice = kForceMma; break;
         default:
-            // Candidate rules, off unless the environment asks (kernels not yet run on a GPU): the f16
-            // warp-MMA kernel for batches up to 64 (SHREWQ_AUTO_MMA_F16=1), CTA pairs for batches above
-            // 128 (SHREWQ_AUTO_PAIR=1).  They let the whole test-suite and the benchmark run on those
-            // kernels before the rule below is changed.
-            if (env_flag("SHREWQ_AUTO_MMA_F16") && M <= 64 && gemv_mma_supported(a)) { choice = kForceMmaF16; break; }
-            // SHREWQ_AUTO_TC_F32=1: f32 activations of batches above 16 through the two bf16 passes on the
-            // tensor cores instead of the f32 FMA kernel (same status: not yet run on a GPU)
-            if (env_flag("SHREWQ_AUTO_TC_F32") && x_dtype == SHREWQ_F32 && y_dtype == SHREWQ_F32 && !up && !zp_route &&
-                lin->tmap_ok && M > 16 && (a.K % 16) == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0)
-                return forward_f32_on_tensor_cores(lin, a, who);
-            if (env_flag("SHREWQ_AUTO_PAIR") && M > 128 && tc_ok && !zp_route) {
-                rc = up ? launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap, nullptr);
-                lin->last_kernel = "tcgen05-2cta";
-                return rc;
+            if (x_dtype == SHREWQ_F32) {
+                // a few tokens: the GEMV reads f32 activations directly; beyond, the tensor cores on the
+                // bf16 hi/lo pair; the general f32 kernel takes what neither can (misaligned, odd widths)
+                choice = gemv_ok ? kForceGemv : f32_tc_ok ? kForceTcF32 : kForceSimt;
+            } else if (ctx->tuning.tc_pair && M > 128 && tc_ok) {
+                choice = kForceTc2Cta;
+            } else {
+                choice = default_family(M, gemv_ok, mma_ok, tc_ok);
             }
-            // CUDA-core GEMV keeps up with HBM only for a few tokens; beyond that the tensor
-            // cores take over (bf16 activations), else the general f32 kernel.
-            choice = default_family(M, gemv_ok, tc_ok);
     }
     const char *name;
     if (choice == kForceGemv) { rc = launch_gemv(ctx, a); name = "gemv"; }
-    else if (choice == kForceMma) { rc = launch_gemv_mma(ctx, a, false); name = "mma"; }
-    else if (choice == kForceMmaF16) { rc = launch_gemv_mma(ctx, a, true); name = "mma-f16"; }
-    else if (choice == kForceTc) { rc = up ? launch_gemm_tcgen05(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
-        name = "tcgen05"; }
-    else {
-        if (n_peers > 0) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: peer destinations need the gemv or tcgen05 kernel", who);
+    else if (choice == kForceMma) { rc = launch_gemv_mma(ctx, a); name = "mma"; }
+    else if (choice == kForceTc) {
+        rc = up ? launch_gemm_tcgen05(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
+        name = "tcgen05";
+    } else if (choice == kForceTc2Cta) {
+        rc = up ? launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05_2cta(ctx, a, lin->w_tmap, nullptr);
+        name = "tcgen05-2cta";
+    } else if (choice == kForceTcF32) {
+        rc = forward_f32_on_tensor_cores(lin, a, who);
+        name = "tcgen05-f32";
+    } else {
+        if (n_peers > 0) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: peer destinations need the gemv, mma or tcgen05 kernel", who);
         rc = launch_gemm_simt(ctx, a); name = "simt";
     }
-    lin->last_kernel = name;
+    g_last_kernel = name;
     if (zp_route && rc == SHREWQ_OK)
         rc = launch_zero_point_fix(ctx, zp_acc, lin->czp, zp_xsum, M, lin->n, ldy, epilogue == SHREWQ_EPILOGUE_RELU, y_dtype, y_dev);
     return rc;
@@ -701,7 +681,7 @@ int shrewq_linear_forward_noalloc(shrewq_linear *lin, const void *x_dev, size_t 
         return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
                        "forward_noalloc: needs bf16 activations, 16-byte aligned x and weights, in_features a multiple of 16");
     rc = launch_gemm_tcgen05_noalloc(ctx, a, lin->w_tmap);
-    lin->last_kernel = "tcgen05";
+    g_last_kernel = "tcgen05";
     return rc;
 }
 

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -16,6 +17,17 @@ namespace shrewq {
 
 constexpr int kErrLen = 512;
 
+// Launch options of a context (shrewq_ctx_set_option); the defaults are the measured choices.
+struct Tuning {
+    int tc_groups = 3;      // converter groups of the tcgen05 kernel (1..3)
+    int tc_splitk = 1;      // split K when the tile grid leaves SMs idle
+    int tc_tok = 0;         // 0 = choose; else force the token tile (16, 32, 64, 128, 256)
+    int tc_tok_gated = 0;   // the same for gate/up launches only
+    int tc_tailsplit = 0;   // issue a short last wave as a second launch split along K
+    int tc_pair = 0;        // batches above 128 tokens on CTA pairs (tcgen05.mma.cta_group::2)
+    int gemv_pdl = 0;       // programmatic dependent launch of the small-batch kernels
+};
+
 }  // namespace shrewq
 
 // Opaque in the ABI.
@@ -24,7 +36,8 @@ struct shrewq_ctx {
     cudaStream_t stream = nullptr;
     int sm_count = 0;
     char err[shrewq::kErrLen] = {0};
-    uint64_t launches = 0;
+    std::atomic<uint64_t> launches{0};
+    shrewq::Tuning tuning;
     // scratch: per-tensor amax word, split-K partial sums and tile counters
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
@@ -54,7 +67,6 @@ struct shrewq_linear {
     bool int4_packed = false;     // q points at packed INT4 rows (in_features / 2 bytes each)
     size_t n = 0, k = 0;
     int granularity = 0;
-    const char *last_kernel = "none";
     // TMA descriptors for the INT8 weight matrix (128 B each, opaque CUtensorMap), valid when
     // tmap_ok: 64-byte k boxes over 128 weight rows, and over 64 rows (gate / up halves).
     alignas(64) unsigned char w_tmap[128];
@@ -119,7 +131,7 @@ struct ForwardArgs {
 int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a);
 int launch_gemm_simt(shrewq_ctx *ctx, const ForwardArgs &a);
 bool gemv_mma_supported(const ForwardArgs &a);
-int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a, bool f16);
+int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a);
 bool gemv_mma_w4_supported(const ForwardArgs &a);
 int launch_gemv_mma_w4(shrewq_ctx *ctx, const ForwardArgs &a);
 int launch_pack_int4(shrewq_ctx *ctx, const int8_t *q, size_t n_pairs, uint8_t *packed);
@@ -129,6 +141,7 @@ int plan_gemm_tcgen05(size_t M, size_t N, size_t K, bool gated, int sm_count, in
                       int *splits, int *rounds_per_split);
 int launch_gemm_tcgen05_2cta(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap, const void *w_up_tmap);
 int launch_gemm_tcgen05_noalloc(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap);
+int launch_gemm_tcgen05_xsplit(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap);
 int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, int box_rows, void *tmap_out);
 
 // bf16 <-> f32 helpers usable on host and device

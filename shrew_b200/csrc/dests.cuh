@@ -19,8 +19,4 @@ struct DeviceStatus {
     unsigned int parity;
 };
 
-// internal epilogue flag (above the public SHREWQ_EPILOGUE_* values): add the f32 value already
-// stored at the output position before the elementwise op
-constexpr int kEpilogueAccumulate = 0x100;
-
 }  // namespace shrewq

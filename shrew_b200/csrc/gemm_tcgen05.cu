@@ -2,6 +2,7 @@
 // description: gemm_tcgen05_kernels.cuh).
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -45,66 +46,26 @@ int encode_2d(shrewq_ctx *ctx, CUtensorMap *out, CUtensorMapDataType dt, int ele
 }
 
 // ---- launch ---------------------------------------------------------------------------
-struct Tuning {
-    int groups;   // converter groups (1..3)
-    bool splitk;  // allow split-K when the grid would leave SMs idle
-    int tok;      // 0 = choose; else force the token tile
-    int tok_gated;  // 0 = as above; else the token tile of gate/up launches only (NOT yet run on a GPU at 256)
-};
-
-Tuning read_tuning() {
-    Tuning t{3, true, 0, 0};
-    if (const char *e = getenv("SHREWQ_TC_TOK_GATED")) t.tok_gated = atoi(e);
-    if (const char *e = getenv("SHREWQ_TC_GROUPS")) t.groups = atoi(e);
-    if (const char *e = getenv("SHREWQ_TC_SPLITK")) t.splitk = atoi(e) != 0;
-    if (const char *e = getenv("SHREWQ_TC_TOK")) t.tok = atoi(e);
-    if (t.groups < 1) t.groups = 1;
-    if (t.groups > 3) t.groups = 3;
-    return t;
-}
-
 constexpr size_t kScratchCounterOff = 4096, kScratchPartialOff = 8192;
 
 struct LaunchPlan {
     int n_tiles, m_tiles, splits, rounds_per_split;
 };
 
+// Split-K when the output tiles alone leave most SMs idle: as many splits as fit in one wave, each with at
+// least 2 pipeline rounds (token tiles up to 64, whose partial sums are small) or 8 (larger tiles).
+// split_max_tok: the widest token tile that may be split (the no-allocation entry point keeps its
+// partial sums in a fixed array and splits the small tiles only).
 template <int TOK, int KSUB>
-LaunchPlan plan_launch(const ForwardArgs &a, int chan_per_tile, int sm_count, bool allow_split) {
+LaunchPlan plan_launch(const ForwardArgs &a, int chan_per_tile, int sm_count, bool allow_split, int split_max_tok = 256) {
     LaunchPlan p;
     p.n_tiles = (int)((a.N + chan_per_tile - 1) / chan_per_tile);
     p.m_tiles = (int)((a.M + TOK - 1) / TOK);
     const int rounds = (int)((a.K + kBlockK * KSUB - 1) / (kBlockK * KSUB));
-    // split-K only for small token tiles (their partial sums are small) when the output
-    // tiles alone leave most SMs idle: as many splits as fit in one wave, >= 2 rounds each
     int splits = 1;
     const long tiles = (long)p.n_tiles * p.m_tiles;
-    // SHREWQ_TC_SPLITK_MAXTOK=128|256 (NOT yet run on a GPU, default 64) extends the rule to the
-    // large token tiles, with at least 8 rounds per split: batches 65..256 on layers with few
-    // channel tiles (N = 4096: 32 tiles) otherwise run on a fraction of the SMs.  The kernel's
-    // split path is the same code for every tile width.
-    const int max_tok = [] {  // read at every launch, so that one process can compare settings
-        const char *e = getenv("SHREWQ_TC_SPLITK_MAXTOK");
-        const int v = e ? atoi(e) : 64;
-        return v < 64 ? 64 : v;
-    }();
     const int min_rounds = TOK <= 64 ? 2 : 8;
-    // SHREWQ_TC_SPLIT_WAVES=1 (NOT yet run on a GPU; same kernel path, another launch rule): choose the
-    // split count by waves instead of "as many as fit in one wave".  86 tiles on 148 SMs (N = 11008) take
-    // one wave whole, but 3 splits take 2 waves of a third each (0.67 of the time) and 5 splits 3 waves of
-    // a fifth (0.6): the rule below minimises waves / splits plus a charge per split for the reduction.
-    const char *wv = getenv("SHREWQ_TC_SPLIT_WAVES");
-    if (allow_split && wv && atoi(wv) != 0 && TOK <= max_tok && tiles <= 2L * sm_count) {
-        // (grids of many waves lose little to the last one, and their partial sums would be many: the
-        // two-launch tail split is the tool there)
-        double best = 1e30;
-        for (int sp = 1; sp <= 8 && (sp == 1 || rounds / sp >= min_rounds); ++sp) {
-            const long ctas = tiles * sp;
-            const long waves = (ctas + sm_count - 1) / sm_count;
-            const double cost = (double)waves / sp + (sp > 1 ? 0.03 * sp : 0.0);
-            if (cost < best - 1e-9) { best = cost; splits = sp; }
-        }
-    } else if (allow_split && TOK <= max_tok && tiles <= 1024) {
+    if (allow_split && TOK <= split_max_tok && tiles <= 1024) {
         int want = (int)(sm_count / tiles);
         if (want > rounds / min_rounds) want = rounds / min_rounds;
         if (want > 1) splits = want;
@@ -114,30 +75,37 @@ LaunchPlan plan_launch(const ForwardArgs &a, int chan_per_tile, int sm_count, bo
     return p;
 }
 
+// cudaFuncSetAttribute once per kernel instantiation and device (bit d of `done`: device d has it)
+template <typename Kern>
+int set_smem_attr_once(shrewq_ctx *ctx, Kern kern, int bytes, std::atomic<unsigned long long> &done) {
+    const int d = ctx->device;
+    if (d >= 0 && d < 64 && ((done.load(std::memory_order_acquire) >> d) & 1ull)) return SHREWQ_OK;
+    SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    if (d >= 0 && d < 64) done.fetch_or(1ull << d, std::memory_order_release);
+    return SHREWQ_OK;
+}
+
 // scratch == nullptr: use (and grow) the context's scratch; otherwise a caller-provided
 // region of scratch_bytes laid out as [0,4096) counters, partial sums from 4096.
-template <int TOK, int KSUB, int G, bool GATED, typename YT>
+// XSPLIT: a.x is the bf16 hi/lo pair of f32 activations, lo rows stacked under the M hi rows
+template <int TOK, int KSUB, int G, bool GATED, typename YT, bool XSPLIT = false>
 int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, bool allow_split,
                void *fixed_scratch, size_t fixed_scratch_bytes) {
-    using C = Cfg<TOK, KSUB>;
+    using C = Cfg<TOK, KSUB, XSPLIT>;
     CUtensorMap tx;
-    int rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, a.K, a.M, kBlockK, TOK,
+    int rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.x, a.K, XSPLIT ? 2 * a.M : a.M, kBlockK, TOK,
                        CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != SHREWQ_OK) return rc;
-    auto kern = linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT>;
-    static bool attr_set[64] = {false};  // per instantiation and per device (the attribute is per device)
-    if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
-        SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemRequest));
-        if (ctx->device >= 0 && ctx->device < 64) attr_set[ctx->device] = true;
-    }
-    const LaunchPlan p = plan_launch<TOK, KSUB>(a, GATED ? 64 : 128, ctx->sm_count, allow_split);
+    auto kern = linear_i8_tcgen05_kernel<TOK, KSUB, G, GATED, YT, XSPLIT>;
+    static std::atomic<unsigned long long> attr_done{0};  // per instantiation
+    if ((rc = set_smem_attr_once(ctx, kern, C::kSmemRequest, attr_done)) != SHREWQ_OK) return rc;
+    const LaunchPlan p = plan_launch<TOK, KSUB>(a, GATED ? 64 : 128, ctx->sm_count, allow_split, fixed_scratch ? 64 : 256);
     SplitK sk{nullptr, nullptr, p.rounds_per_split, 0, 0};
     Operands ops{a.scales, a.bias, a.scales_up, a.bias_up};
-    // SHREWQ_TC_TAILSPLIT=1 (built, NOT yet run on a GPU, off by default): when large tiles
-    // leave a short last wave, issue the full waves as one launch and the tiles of the last
-    // wave as a second launch split along K so that it also fills the SMs.
-    const char *ts = getenv("SHREWQ_TC_TAILSPLIT");
-    const bool tail_split = ts && atoi(ts) != 0;
+    // Option tc_tailsplit: when large tiles leave a short last wave, issue the full waves as one
+    // launch and the tiles of the last wave as a second launch split along K so that it also fills
+    // the SMs.
+    const bool tail_split = ctx->tuning.tc_tailsplit != 0;
     if (tail_split && !fixed_scratch && TOK >= 128 && p.splits == 1) {
         const int tiles = p.n_tiles * p.m_tiles, rem = tiles % ctx->sm_count;
         const int rounds = p.rounds_per_split;
@@ -206,54 +174,44 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
 }
 
 template <int TOK, int KSUB, bool GATED, typename YT>
-int launch_groups(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, const Tuning &t,
-                  void *fs, size_t fsb) {
-    if (t.groups == 1) return launch_cfg<TOK, KSUB, 1, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);
-    if (t.groups == 2) return launch_cfg<TOK, KSUB, 2, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);
-    return launch_cfg<TOK, KSUB, 3, GATED, YT>(ctx, a, tw, tw2, t.splitk, fs, fsb);
+int launch_groups(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, void *fs, size_t fsb) {
+    const bool sk = ctx->tuning.tc_splitk != 0;
+    if (ctx->tuning.tc_groups == 1) return launch_cfg<TOK, KSUB, 1, GATED, YT>(ctx, a, tw, tw2, sk, fs, fsb);
+    if (ctx->tuning.tc_groups == 2) return launch_cfg<TOK, KSUB, 2, GATED, YT>(ctx, a, tw, tw2, sk, fs, fsb);
+    return launch_cfg<TOK, KSUB, 3, GATED, YT>(ctx, a, tw, tw2, sk, fs, fsb);
 }
 
-// Token tile: the smallest tile that covers M up to 256; above that 256 tokens, unless
-// 128-token tiles fill the SMs markedly better (few channel tiles, e.g. N = 4096 at M = 512).
-int choose_tok(const ForwardArgs &a, int chan_per_tile, int sm_count) {
+// Token tile: the smallest tile that covers M up to 128.  Above that a gate/up launch takes 256 tokens
+// (twice the tokens per converted weight byte; measured 12 % shorter on the 4096 -> 11008 block at batch 512),
+// a plain launch 256 tokens unless 128-token tiles fill the SMs markedly better (few channel tiles, e.g.
+// N = 4096 at M = 512: 128 CTAs instead of 64).
+int choose_tok(const ForwardArgs &a, bool gated, int sm_count, const Tuning &t) {
+    const int forced = (gated && t.tc_tok_gated) ? t.tc_tok_gated : t.tc_tok;
+    if (forced == 16 || forced == 32 || forced == 64 || forced == 128 || forced == 256) return forced;
     if (a.M <= 16) return 16;
     if (a.M <= 32) return 32;
     if (a.M <= 64) return 64;
     if (a.M <= 128) return 128;
-    const long n_tiles = (long)((a.N + chan_per_tile - 1) / chan_per_tile);
+    if (gated) return 256;
+    const long n_tiles = (long)((a.N + 127) / 128);
     auto fill = [&](int tok) {
         const long tiles = n_tiles * (long)((a.M + tok - 1) / tok);
         const long waves = (tiles + sm_count - 1) / sm_count;
         return (double)tiles / (double)(waves * sm_count);
     };
-    // SHREWQ_TC_TILE_RULE=cost (opt-in; a launch rule only, but it sends gate/up launches to the 256-token tile, whose
-    // parity has been checked on the CPU model only): compare waves x cost of a tile's k-loop instead of SM fill.
-    // The issuing thread needs ~1100 cycles per 128 k with 128-token tiles and ~1400 with 256-token tiles that carry
-    // twice the tokens (in-kernel trace), so a 128-token tile is only worth 0.64 of its tokens.
-    if (const char *e = getenv("SHREWQ_TC_TILE_RULE")) {
-        if (!strcmp(e, "cost")) {
-            auto waves = [&](int tok) {
-                const long tiles = n_tiles * (long)((a.M + tok - 1) / tok);
-                return (tiles + sm_count - 1) / sm_count;
-            };
-            return waves(128) * 1100 < waves(256) * 1400 ? 128 : 256;
-        }
-    }
     return fill(128) * 0.85 > fill(256) ? 128 : 256;
 }
 
 template <bool GATED, typename YT>
 int launch_y(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, const CUtensorMap &tw2, void *fs, size_t fsb) {
-    const Tuning t = read_tuning();
-    const int tok = (GATED && t.tok_gated) ? t.tok_gated : t.tok ? t.tok : choose_tok(a, GATED ? 64 : 128, ctx->sm_count);
-    switch (tok) {
+    switch (choose_tok(a, GATED, ctx->sm_count, ctx->tuning)) {
         // small token tiles are HBM-bound: 2 sub-blocks per stage keeps the pipeline 6-7 stages
         // deep (TMEM columns limit the depth), i.e. ~100 KB of codes in flight per SM
-        case 16: return launch_groups<16, 2, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
-        case 32: return launch_groups<32, 2, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
-        case 64: return launch_groups<64, 2, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
-        case 128: return launch_groups<128, 2, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
-        default: return launch_groups<256, 1, GATED, YT>(ctx, a, tw, tw2, t, fs, fsb);
+        case 16: return launch_groups<16, 2, GATED, YT>(ctx, a, tw, tw2, fs, fsb);
+        case 32: return launch_groups<32, 2, GATED, YT>(ctx, a, tw, tw2, fs, fsb);
+        case 64: return launch_groups<64, 2, GATED, YT>(ctx, a, tw, tw2, fs, fsb);
+        case 128: return launch_groups<128, 2, GATED, YT>(ctx, a, tw, tw2, fs, fsb);
+        default: return launch_groups<256, 1, GATED, YT>(ctx, a, tw, tw2, fs, fsb);
     }
 }
 
@@ -267,20 +225,20 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 // In host code the array's name is only a handle for the runtime, not a device address:
 // the address is looked up once per device (with that device current) and cached.
 constexpr int kMaxDevices = 64;
-static void *g_static_scratch_addr[kMaxDevices] = {nullptr};
+static std::atomic<void *> g_static_scratch_addr[kMaxDevices];
 
 int static_scratch_for_device(shrewq_ctx *ctx, void **out) {
     if (ctx->device < 0 || ctx->device >= kMaxDevices)
         return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "forward_noalloc: device index %d above %d", ctx->device, kMaxDevices - 1);
-    if (!g_static_scratch_addr[ctx->device]) {
+    if (!g_static_scratch_addr[ctx->device].load(std::memory_order_acquire)) {
         void *p = nullptr;
         SHREWQ_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
         cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess || !p)
             return set_err(ctx, SHREWQ_ERR_CUDA, "forward_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-        g_static_scratch_addr[ctx->device] = p;
+        g_static_scratch_addr[ctx->device].store(p, std::memory_order_release);  // every thread looks up the same address
     }
-    *out = g_static_scratch_addr[ctx->device];
+    *out = g_static_scratch_addr[ctx->device].load(std::memory_order_acquire);
     return SHREWQ_OK;
 }
 
@@ -305,6 +263,14 @@ int encode_weight_tmap(shrewq_ctx *ctx, const int8_t *q, size_t n, size_t k, int
                      box_rows, CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
+// f32 activations: a.x points at the bf16 hi matrix [M,K] with the lo matrix right behind it
+int launch_gemm_tcgen05_xsplit(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap) {
+    const CUtensorMap &tw = *static_cast<const CUtensorMap *>(w_tmap);
+    const bool sk = ctx->tuning.tc_splitk != 0;
+    if (a.y_dtype == SHREWQ_BF16) return launch_cfg<128, 1, 3, false, __nv_bfloat16, true>(ctx, a, tw, tw, sk, nullptr, 0);
+    return launch_cfg<128, 1, 3, false, float, true>(ctx, a, tw, tw, sk, nullptr, 0);
+}
+
 int launch_gemm_tcgen05_noalloc(shrewq_ctx *ctx, const ForwardArgs &a, const void *w_tmap) {
     const CUtensorMap &tw = *static_cast<const CUtensorMap *>(w_tmap);
     void *base = nullptr;
@@ -322,16 +288,16 @@ int plan_gemm_tcgen05(size_t M, size_t N, size_t K, bool gated, int sm_count, in
                       int *splits, int *rounds_per_split) {
     ForwardArgs a{};
     a.M = M; a.N = N; a.K = K;
-    const Tuning t = read_tuning();
+    const Tuning t;  // the defaults
     const int chan = gated ? 64 : 128;
-    const int tk = (gated && t.tok_gated) ? t.tok_gated : t.tok ? t.tok : choose_tok(a, chan, sm_count);
+    const int tk = choose_tok(a, gated, sm_count, t);
     LaunchPlan p;
     switch (tk) {
-        case 16: p = plan_launch<16, 2>(a, chan, sm_count, t.splitk); break;
-        case 32: p = plan_launch<32, 2>(a, chan, sm_count, t.splitk); break;
-        case 64: p = plan_launch<64, 2>(a, chan, sm_count, t.splitk); break;
-        case 128: p = plan_launch<128, 2>(a, chan, sm_count, t.splitk); break;
-        case 256: p = plan_launch<256, 1>(a, chan, sm_count, t.splitk); break;
+        case 16: p = plan_launch<16, 2>(a, chan, sm_count, true); break;
+        case 32: p = plan_launch<32, 2>(a, chan, sm_count, true); break;
+        case 64: p = plan_launch<64, 2>(a, chan, sm_count, true); break;
+        case 128: p = plan_launch<128, 2>(a, chan, sm_count, true); break;
+        case 256: p = plan_launch<256, 1>(a, chan, sm_count, true); break;
         default: return SHREWQ_ERR_INVALID_ARG;
     }
     *tok = tk; *n_tiles = p.n_tiles; *m_tiles = p.m_tiles; *splits = p.splits; *rounds_per_split = p.rounds_per_split;

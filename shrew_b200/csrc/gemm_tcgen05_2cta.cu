@@ -1,6 +1,7 @@
 // Host side of the CTA-pair forward (device code and its description: gemm_tcgen05_2cta_kernels.cuh).
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -40,10 +41,10 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
     int rc = encode_x_half(ctx, &tx, a.x, a.K, a.M);
     if (rc != SHREWQ_OK) return rc;
     auto kern = linear_i8_tcgen05_pair_kernel<YT, GATED>;
-    static bool attr_set[64] = {false};
-    if (ctx->device < 0 || ctx->device >= 64 || !attr_set[ctx->device]) {
+    static std::atomic<unsigned long long> attr_done{0};  // per instantiation: bit d = device d has the attribute
+    if (ctx->device < 0 || ctx->device >= 64 || !((attr_done.load(std::memory_order_acquire) >> ctx->device) & 1ull)) {
         SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        if (ctx->device >= 0 && ctx->device < 64) attr_set[ctx->device] = true;
+        if (ctx->device >= 0 && ctx->device < 64) attr_done.fetch_or(1ull << ctx->device, std::memory_order_release);
     }
     constexpr int kChanPair = GATED ? kLanes : 2 * kLanes;  // output channels per CTA pair
     const unsigned pairs = (unsigned)((a.N + kChanPair - 1) / kChanPair);
@@ -60,12 +61,11 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
     const int rps = (rounds + splits - 1) / splits;
     splits = (rounds + rps - 1) / rps;  // no empty split
     SplitK2 sk{nullptr, nullptr, rps, 0, 0};
-    Operands2 ops{a.scales, a.bias, a.scales_up, a.bias_up};
-    // SHREWQ_TC_TAILSPLIT=1 (as for the single-CTA kernel; NOT yet run on a GPU, off by default): when
-    // the pair tiles leave a short last wave, the full waves go out as one launch of whole-K tiles and
-    // the tiles of the last wave as a second launch split along K, so that it fills the SMs too.
-    const char *ts = getenv("SHREWQ_TC_TAILSPLIT");
-    if (ts && atoi(ts) != 0 && splits == 1) {
+    Operands ops{a.scales, a.bias, a.scales_up, a.bias_up};
+    // Option tc_tailsplit (as for the single-CTA kernel): when the pair tiles leave a short last wave, the
+    // full waves go out as one launch of whole-K tiles and the tiles of the last wave as a second launch
+    // split along K, so that it fills the SMs too.
+    if (ctx->tuning.tc_tailsplit != 0 && splits == 1) {
         const int per_wave = ctx->sm_count / 2;  // pair tiles resident at once, one CTA per SM
         const int tiles = (int)(pairs * m_tiles), rem = per_wave > 0 ? tiles % per_wave : 0;
         int s_tail = rem > 0 ? per_wave / rem : 0;

@@ -1,8 +1,5 @@
 // Quantized Linear forward on CTA PAIRS (tcgen05.mma.cta_group::2), sm_100a only.
 //
-// STATUS: built and compiled, NOT yet run on a GPU.  Never chosen automatically;
-// shrewq_force_kernel("tcgen05-2cta") selects it (bf16 activations, M >= 1).
-//
 // Why: in the single-CTA kernel (gemm_tcgen05.cu) one thread issues every MMA; at ~80 cycles
 // per issue plus ~380 cycles of wait / fence / commit per pipeline stage it needs ~700 cycles
 // for a 128x256x64 block whose tensor work is 512 cycles.  A CTA pair doubles the work of each
@@ -22,8 +19,8 @@
 //                     on the leader's barrier; the leader expects the bytes of both)
 //   aready[s] leader: 8 converter warps (4 per CTA) wrote and fenced their A stage (remote
 //                     arrive from the peer)                                        -> MMA issuer
-//   empty[s]  both  : tcgen05.commit.cta_group::2, one commit per CTA's barrier    -> producers
-//   accfull   both  : the same pair of commits after the last stage              -> epilogues
+//   empty[s]  both  : tcgen05.commit.cta_group::2 multicast to both CTAs' barriers -> producers
+//   accfull   both  : the same commit after the last stage                        -> epilogues
 // Tensor memory is allocated and freed by both CTAs with the cta_group::2 forms, with a
 // cluster barrier before the free.  Every mbarrier wait is bounded as in the single-CTA
 // kernel; the cluster barriers are reached by every thread on every path.
@@ -37,6 +34,7 @@
 #include "dests.cuh"
 #include "ptx_small.cuh"
 #include "ptx_tcgen05_pair.cuh"
+#include "tcgen05_epilogue.cuh"
 
 namespace shrewq {
 namespace {
@@ -67,6 +65,7 @@ constexpr uint32_t kSpinFast = SHREWQ_SPIN_FAST_LIMIT;  // polls, then polls wit
 constexpr uint32_t kSpinSlow = SHREWQ_SPIN_SLOW_LIMIT;
 static_assert(kABase + kStages * kAColsPerStage <= 512, "TMEM columns");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory");
+static_assert(kStages * kStageBytes >= kGroups * kEpiGroupBytes, "the epilogue's staging tiles reuse the pipeline stages");
 
 struct Ctl {
     volatile int abort_flag;
@@ -140,22 +139,6 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
     return d;
 }
 
-template <typename YT>
-__device__ __forceinline__ void store_out(YT *p, float v);
-template <>
-__device__ __forceinline__ void store_out<float>(float *p, float v) { *p = v; }
-template <>
-__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
-
-struct Operands2 {
-    const float *scales;
-    const float *bias;
-    const float *scales2;  // up matrix (GATED)
-    const float *bias2;
-};
-
-__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
-
 // Split-K (gridDim.z > 1): CTA (x, y, z) walks pipeline rounds [z * rounds_per_split, ...) of its tile
 // and parks its raw accumulators in `partials`; the CTA arriving last at the tile's counter adds the
 // slices in split order, applies the epilogue and resets the counter.  Every CTA of a pair is a tile
@@ -177,7 +160,7 @@ struct SplitK2 {
 template <typename YT, bool GATED>
 __global__ void SHREWQ_CLUSTER_OF_2 __launch_bounds__(kThreads, 1)
 linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
-                              const __grid_constant__ CUtensorMap tmap_x, Operands2 ops, YT *__restrict__ y, Dests extra,
+                              const __grid_constant__ CUtensorMap tmap_x, Operands ops, YT *__restrict__ y, Dests extra,
                               int M, int N, int K, size_t ldy, int epilogue, SplitK2 sk, DeviceStatus *status) {
     constexpr int kChan = GATED ? kLanes / 2 : kLanes;  // output channels per CTA
     TRACE2_INIT
@@ -340,17 +323,6 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
         // epilogue: this CTA's channels x the pair's 256 tokens; 16-column chunks dealt to the groups
         if (ok) ok = mbar_wait_warp(bars_u32 + kAcc, 0, ctl, status, 4, 0);
         if (ok) tc_fence_after();
-        const bool is_up = GATED && row >= kLanes / 2;
-        const int n = n0 + (GATED ? (row & (kLanes / 2 - 1)) : row);
-        const bool n_ok = n < N;
-        const float *sc_p = is_up ? ops.scales2 : ops.scales;
-        const float *bs_p = is_up ? ops.bias2 : ops.bias;
-        const float sc = n_ok ? sc_p[n] : 0.0f;
-        const float bs = (n_ok && bs_p) ? bs_p[n] : 0.0f;
-        // gate/up: the up half hands its values to the gate half through shared memory (the pipeline
-        // stages are idle once the accumulators are complete); the named barriers are reached by every
-        // thread of the group whether or not its waits succeeded
-        float *xch = reinterpret_cast<float *>(smem) + group * (16 * 64);
         const int splits = (int)gridDim.z;
         if (splits > 1) {
             const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
@@ -374,79 +346,16 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             named_bar_sync(1, 128 * kGroups);
             if (*s_is_last) {
                 __threadfence();
-                const float *base = sk.partials + tile * splits * (size_t)(kTokPair * kLanes);
-                if (ok && !is_up) {
-#pragma unroll 1
-                    for (int c = group; c < kTokPair / 16; c += kGroups) {
-#pragma unroll 4
-                        for (int i = 0; i < 16; ++i) {
-                            const int ml = c * 16 + i, m = m0_pair + ml;
-                            float acc = 0.0f, acc2 = 0.0f;
-                            for (int z = 0; z < splits; ++z) {
-                                const float *p = base + (size_t)z * (kTokPair * kLanes) + ml * kLanes + row;
-                                acc += __ldcg(p);
-                                if constexpr (GATED) acc2 += __ldcg(p + kLanes / 2);
-                            }
-                            float o = acc * sc + bs;
-                            if constexpr (GATED) {
-                                const float u = acc2 * (n_ok ? ops.scales2[n] : 0.0f) + ((n_ok && ops.bias2) ? ops.bias2[n] : 0.0f);
-                                o = silu_f(o) * u;
-                            } else if ((epilogue & 0xFF) == SHREWQ_EPILOGUE_RELU) {
-                                o = fmaxf(o, 0.0f);
-                            }
-                            if (n_ok && m < M) {
-                                const size_t off = (size_t)m * ldy + n;
-                                store_out<YT>(y + off, o);
-                                for (int d = 0; d < extra.n; ++d) store_out<YT>(static_cast<YT *>(extra.p[d]) + off, o);
-                            }
-                        }
-                    }
-                }
+                epilogue_tile<kTokPair, kGroups, GATED, YT>(tmem_base, smem, group, quad, lane, ok, ops, y, extra, M, N, ldy, epilogue,
+                                                            n0, m0_pair,
+                                                            PartialSums{sk.partials + tile * splits * (size_t)(kTokPair * kLanes), splits});
                 named_bar_sync(1, 128 * kGroups);
                 if (threadIdx.x == 64) sk.counters[tile] = 0;  // ready for the next launch
             }
         } else {
-#pragma unroll 1
-        for (int c = group; c < kTokPair / 16; c += kGroups) {
-            uint32_t r[16];
-            if (ok) {
-                tc_ld16(tmem_base + lane_addr + c * 16, r);
-                tc_wait_ld();
-            }
-            if constexpr (GATED) {
-                if (is_up && ok) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) xch[i * 64 + (row - 64)] = __uint_as_float(r[i]) * sc + bs;
-                }
-                named_bar_sync(2 + group, 128);
-                if (!is_up && ok) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int m = m0_pair + c * 16 + i;
-                        const float o = silu_f(__uint_as_float(r[i]) * sc + bs) * xch[i * 64 + row];
-                        if (n_ok && m < M) {
-                            const size_t off = (size_t)m * ldy + n;
-                            store_out<YT>(y + off, o);
-                            for (int d = 0; d < extra.n; ++d) store_out<YT>(static_cast<YT *>(extra.p[d]) + off, o);
-                        }
-                    }
-                }
-                named_bar_sync(2 + group, 128);  // xch is rewritten by the next chunk
-            } else if (ok) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int m = m0_pair + c * 16 + i;
-                    float o = __uint_as_float(r[i]) * sc + bs;
-                    if ((epilogue & 0xFF) == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
-                    if (n_ok && m < M) {
-                        const size_t off = (size_t)m * ldy + n;
-                        store_out<YT>(y + off, o);
-                        for (int d = 0; d < extra.n; ++d) store_out<YT>(static_cast<YT *>(extra.p[d]) + off, o);
-                    }
-                }
-            }
+            epilogue_tile<kTokPair, kGroups, GATED, YT>(tmem_base, smem, group, quad, lane, ok, ops, y, extra, M, N, ldy, epilogue, n0,
+                                                        m0_pair, PartialSums{nullptr, 0});
         }
-        }  // splits == 1
     }
 
     // ---------------- teardown: both CTAs are done with tensor memory before it is freed ----------------

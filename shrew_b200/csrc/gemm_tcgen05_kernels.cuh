@@ -12,13 +12,17 @@
 //   B  = TOK tokens of bf16 activations, TMA-loaded with the 128-byte swizzle and read by
 //        the MMA through a shared-memory descriptor (K-major).
 //   D  = f32 accumulators in TMEM: lane = output channel, column = token.
-// The epilogue reads D with tcgen05.ld (one thread per channel), applies the per-channel
-// scale, bias and the elementwise op, and stores; for a fixed token the 32 lanes of a warp
-// write 32 consecutive channels.
+// The epilogue (tcgen05_epilogue.cuh) reads D with tcgen05.ld, applies the per-channel scale, bias and
+// the elementwise op, transposes through shared memory and stores whole token rows with 16-byte stores.
 //
 // GATED: the 128 lanes carry 64 rows of a gate matrix and the same 64 rows of an up matrix
 // (two 64-row TMA boxes per sub-block); the epilogue pairs lane r with lane r+64 and
 // writes silu(gate)*up for 64 channels.
+//
+// XSPLIT (f32 activations): x arrives as two bf16 matrices hi = bf16(x) and lo = bf16(x - hi), stacked
+// as rows [0,M) and [M,2M) of one array; a stage holds both token tiles and every k-step issues two
+// MMAs into the same accumulator, so the codes are converted once and the sum carries ~16 significand
+// bits of x (the f32 path's 1e-4 tolerance) in one pass.
 //
 // Warp roles: warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer, then G groups of
 // 4 converter warps (one TMEM lane quadrant each) which also run the epilogue.  A pipeline
@@ -39,6 +43,7 @@
 #include "dests.cuh"
 #include "ptx_small.cuh"
 #include "ptx_tcgen05.cuh"
+#include "tcgen05_epilogue.cuh"
 
 namespace shrewq {
 namespace {
@@ -57,10 +62,11 @@ constexpr int kUmmaK = 16;
 constexpr uint32_t kSpinFast = SHREWQ_SPIN_FAST_LIMIT;
 constexpr uint32_t kSpinSlow = SHREWQ_SPIN_SLOW_LIMIT;
 
-template <int TOK, int KSUB>
+template <int TOK, int KSUB, bool XSPLIT = false>
 struct Cfg {
     static constexpr int kWSub = kTileN * kBlockK;                   // 8192 B of codes per sub-block
-    static constexpr int kXSub = TOK * kBlockK * 2;                  // bf16 activations per sub-block
+    static constexpr int kXTile = TOK * kBlockK * 2;                 // one bf16 token tile of a sub-block
+    static constexpr int kXSub = kXTile * (XSPLIT ? 2 : 1);          // bf16 activations per sub-block (hi, then lo)
     static constexpr int kStageBytes = KSUB * (kWSub + kXSub);
     static constexpr int kXOff = KSUB * kWSub;                       // activations follow the codes
     static constexpr int kAColsPerStage = KSUB * (kBlockK / 2);      // 32-bit TMEM columns
@@ -76,6 +82,7 @@ struct Cfg {
     static_assert(kABase + kStages * kAColsPerStage <= 512, "TMEM columns");
     static_assert(kSmemRequest <= 227 * 1024, "shared memory");
     static_assert(kStageBytes % 1024 == 0, "stage bases must keep the 1024-byte swizzle alignment");
+    static_assert(kStages * kStageBytes >= 3 * kEpiGroupBytes, "the epilogue's staging tiles reuse the pipeline stages");
 };
 
 struct Ctl {  // lives in shared memory
@@ -149,27 +156,6 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
     return d;
 }
 
-template <typename YT>
-__device__ __forceinline__ void store_out(YT *p, float v);
-// the local store plus one store per peer destination (same element offset in each buffer)
-template <typename YT>
-__device__ __forceinline__ void store_all(YT *y, const Dests &extra, size_t off, float v);
-template <>
-__device__ __forceinline__ void store_out<float>(float *p, float v) { *p = v; }
-template <>
-__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ float load_prev(const float *p) { return *p; }
-__device__ __forceinline__ float load_prev(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
-
-template <typename YT>
-__device__ __forceinline__ void store_all(YT *y, const Dests &extra, size_t off, float v) {
-    store_out<YT>(y + off, v);
-    for (int d = 0; d < extra.n; ++d) store_out<YT>(static_cast<YT *>(extra.p[d]) + off, v);
-}
-
-__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
-
 #ifdef SHREWQ_TRACE
 __device__ long long *g_trace = nullptr;  // [role 0..3][stage index 0..255][tag 0..3]
 __device__ __forceinline__ void trace_rec(long long *tr, int role, int kb, int tag) {
@@ -193,19 +179,13 @@ struct SplitK {
     int n_tiles_total;
 };
 
-struct Operands {
-    const float *scales;   // per output channel
-    const float *bias;     // or null
-    const float *scales2;  // up matrix (GATED)
-    const float *bias2;
-};
-
-template <int TOK, int KSUB, int G, bool GATED, typename YT>
+template <int TOK, int KSUB, int G, bool GATED, typename YT, bool XSPLIT = false>
 __global__ void __launch_bounds__(64 + 128 * G, 1)
 linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
                          const __grid_constant__ CUtensorMap tmap_x, Operands ops, YT *__restrict__ y, Dests extra, int M, int N,
                          int K, size_t ldy, int epilogue, SplitK sk, DeviceStatus *status) {
-    using C = Cfg<TOK, KSUB>;
+    using C = Cfg<TOK, KSUB, XSPLIT>;
+    static_assert(!(XSPLIT && GATED), "the hi/lo form exists for plain tiles");
     constexpr int kChan = GATED ? 64 : 128;  // output channels per CTA
     TRACE_INIT
     SHREWQ_DYNAMIC_SMEM(uint8_t, smem_raw);
@@ -276,6 +256,8 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                         tma_load_2d(dst + j * C::kWSub, &tmap_w, kc + j * kBlockK, n0, fb);
                     }
                     tma_load_2d(dst + C::kXOff + j * C::kXSub, &tmap_x, kc + j * kBlockK, m0, fb);
+                    if constexpr (XSPLIT)  // the lo rows follow the M hi rows in the same array
+                        tma_load_2d(dst + C::kXOff + j * C::kXSub + C::kXTile, &tmap_x, kc + j * kBlockK, m0 + M, fb);
                 }
                 TRACE(0, i, 2);
                 kc += KSUB * kBlockK;
@@ -306,10 +288,14 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 #pragma unroll
                 for (int j = 0; j < KSUB; ++j) {
 #pragma unroll
-                    for (int jj = 0; jj < kBlockK / kUmmaK; ++jj)
+                    for (int jj = 0; jj < kBlockK / kUmmaK; ++jj) {
                         tc_mma_ts(tmem_base, a_tmem + j * (kBlockK / 2) + jj * (kUmmaK / 2),
                                   bdesc + (uint64_t)((j * C::kXSub + jj * kUmmaK * 2) >> 4), idesc,
                                   (i > 0 || j > 0 || jj > 0) ? 1u : 0u);
+                        if constexpr (XSPLIT)
+                            tc_mma_ts(tmem_base, a_tmem + j * (kBlockK / 2) + jj * (kUmmaK / 2),
+                                      bdesc + (uint64_t)((j * C::kXSub + C::kXTile + jj * kUmmaK * 2) >> 4), idesc, 1u);
+                    }
                 }
                 tc_commit(bars_u32 + kEmptyBar + s * 8);  // frees smem stage s and TMEM A stage s
                 TRACE(1, i, 3);
@@ -367,55 +353,11 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         if (warp == 2) TRACE(3, 0, 0);  // (tracing build: role 3 = the epilogue of the first converter warp)
         if (ok) ok = mbar_wait_warp(bars_u32 + kAccBar, 0, ctl, status, 4, 0);
         if (warp == 2) TRACE(3, 0, 1);  // accumulators complete
-        // this lane's channel: plain tiles map lane -> n0 + lane; gated tiles map lanes 0..63 to
-        // the gate rows and lanes 64..127 to the up rows of channels n0 .. n0+63
-        const bool is_up = GATED && row >= 64;
-        const int n = n0 + (GATED ? (row & 63) : row);
-        const bool n_ok = n < N;
-        const float *sc_p = is_up ? ops.scales2 : ops.scales;
-        const float *bs_p = is_up ? ops.bias2 : ops.bias;
-        const float sc = n_ok ? sc_p[n] : 0.0f;
-        const float bs = (n_ok && bs_p) ? bs_p[n] : 0.0f;
         const int splits = gridDim.z;
         if (splits == 1) {
             if (ok) tc_fence_after();
-            // gated tiles: the up half hands its values to the gate half through shared memory
-            // (the pipeline stages are idle once the accumulators are complete)
-            float *xch = reinterpret_cast<float *>(smem) + group * (16 * 64);
-#pragma unroll 1
-            for (int c = group; c < TOK / 16; c += G) {
-                uint32_t r[16];
-                if (ok) {
-                    tc_ld16(tmem_base + lane_addr + c * 16, r);
-                    tc_wait_ld();
-                }
-                if constexpr (GATED) {
-                    if (is_up && ok) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) xch[i * 64 + (row - 64)] = __uint_as_float(r[i]) * sc + bs;
-                    }
-                    named_bar_sync(2 + group, 128);
-                    if (!is_up && ok) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int m = m0 + c * 16 + i;
-                            const float g = __uint_as_float(r[i]) * sc + bs;
-                            const float o = silu_f(g) * xch[i * 64 + row];
-                            if (n_ok && m < M) store_all<YT>(y, extra, (size_t)m * ldy + n, o);
-                        }
-                    }
-                    named_bar_sync(2 + group, 128);  // xch is rewritten by the next chunk
-                } else if (ok) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int m = m0 + c * 16 + i;
-                        float o = __uint_as_float(r[i]) * sc + bs;
-                        if ((epilogue & kEpilogueAccumulate) && n_ok && m < M) o += load_prev(y + (size_t)m * ldy + n);
-                        if ((epilogue & 0xFF) == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
-                        if (n_ok && m < M) store_all<YT>(y, extra, (size_t)m * ldy + n, o);
-                    }
-                }
-            }
+            epilogue_tile<TOK, G, GATED, YT>(tmem_base, smem, group, quad, lane, ok, ops, y, extra, M, N, ldy, epilogue, n0, m0,
+                                             PartialSums{nullptr, 0});
         } else {
             // split-K: every CTA parks its raw accumulators in scratch; the CTA that arrives
             // last at the tile's counter adds the slices in split order (so the sum does not
@@ -444,31 +386,8 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             if (warp == 2) TRACE(3, 0, 3);  // this CTA's arrival counted
             if (*s_is_last) {
                 __threadfence();
-                const float *base = sk.partials + tile * splits * (size_t)(TOK * kTileN);
-                if (ok && !is_up) {
-#pragma unroll 1
-                    for (int c = group; c < TOK / 16; c += G) {
-#pragma unroll 4
-                        for (int i = 0; i < 16; ++i) {
-                            const int ml = c * 16 + i, m = m0 + ml;
-                            float acc = 0.0f, acc2 = 0.0f;
-                            for (int z = 0; z < splits; ++z) {
-                                const float *p = base + (size_t)z * (TOK * kTileN) + ml * kTileN + row;
-                                acc += __ldcg(p);
-                                if constexpr (GATED) acc2 += __ldcg(p + 64);
-                            }
-                            float o = acc * sc + bs;
-                            if constexpr (GATED) {
-                                const float u = acc2 * (n_ok ? ops.scales2[n] : 0.0f) + ((n_ok && ops.bias2) ? ops.bias2[n] : 0.0f);
-                                o = silu_f(o) * u;
-                            } else {
-                                if ((epilogue & kEpilogueAccumulate) && n_ok && m < M) o += load_prev(y + (size_t)m * ldy + n);
-                                if ((epilogue & 0xFF) == SHREWQ_EPILOGUE_RELU) o = fmaxf(o, 0.0f);
-                            }
-                            if (n_ok && m < M) store_all<YT>(y, extra, (size_t)m * ldy + n, o);
-                        }
-                    }
-                }
+                epilogue_tile<TOK, G, GATED, YT>(tmem_base, smem, group, quad, lane, ok, ops, y, extra, M, N, ldy, epilogue, n0,
+                                                 m0, PartialSums{sk.partials + tile * splits * (size_t)(TOK * kTileN), splits});
                 named_bar_sync(1, 128 * G);
                 if (threadIdx.x == 64) sk.counters[tile] = 0;  // ready for the next launch
             }

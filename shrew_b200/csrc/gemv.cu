@@ -11,12 +11,10 @@ template <int MT, int R, typename XT, typename YT, bool GATED>
 void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     constexpr int NR = GATED ? R / 2 : R;
     const unsigned grid = (unsigned)((a.N + NR - 1) / NR);
-    // SHREWQ_GEMV_PDL=1 launches the PDL variant of the kernel with programmatic stream
+    // Option gemv_pdl launches the PDL variant of the kernel with programmatic stream
     // serialization: back-to-back GEMVs overlap launch latency, prologue and the first weight
-    // loads with the tail of the kernel before.  Built, compiled, NOT yet run on a GPU: off unless
-    // the variable is set (the default instantiations are the validated kernel, unchanged).
-    const char *pe = getenv("SHREWQ_GEMV_PDL");
-    const bool pdl = pe && atoi(pe) != 0;
+    // loads with the tail of the kernel before.
+    const bool pdl = ctx->tuning.gemv_pdl != 0;
     if (pdl) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);

@@ -17,36 +17,6 @@ void launch_one(shrewq_ctx *ctx, const ForwardArgs &a, const void *x, const int 
         static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
 }
 
-// batch 1..4, f16: one launch, every CTA stages its own f16 copy of x in shared memory
-template <typename YT, bool GATED>
-void launch_staged(shrewq_ctx *ctx, const ForwardArgs &a) {
-    constexpr int kChan = GATED ? 8 : 8 * NB;
-    const unsigned grid = (unsigned)((a.N + kChan - 1) / kChan);
-    const size_t smem = a.M * a.K * sizeof(uint16_t);  // <= kStageMaxBytes: static + dynamic stay below 48 KB
-    // SHREWQ_GEMV_PDL=1 (as for the CUDA-core GEMV): programmatic stream serialization, so that a chain
-    // of batch-1 forwards keeps the weight stream going across kernel boundaries
-    const char *e = getenv("SHREWQ_GEMV_PDL");
-    if (e && atoi(e) != 0) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = ctx->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        cudaLaunchKernelEx(&cfg, gemv_mma_kernel<1, YT, GATED, true, true>, a.q, a.scales, a.bias, a.q_up, a.scales_up,
-                           a.bias_up, static_cast<const uint16_t *>(a.x), static_cast<const int *>(nullptr),
-                           static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
-        return;
-    }
-    gemv_mma_kernel<1, YT, GATED, true, true><<<grid, kThreads, smem, ctx->stream>>>(
-        a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const uint16_t *>(a.x), nullptr,
-        static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
-}
-
 template <typename YT, bool GATED, bool F16>
 void dispatch_m(shrewq_ctx *ctx, const ForwardArgs &a, const void *x, const int *xshift) {
     if (a.M <= 16) launch_one<1, YT, GATED, F16>(ctx, a, x, xshift);
@@ -125,35 +95,12 @@ bool gemv_mma_supported(const ForwardArgs &a) {
            (!a.q_up || (reinterpret_cast<uintptr_t>(a.q_up) & 15) == 0) && a.N <= 0x7FFFFFFF && a.K <= 0x7FFFFFFF;
 }
 
-int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a, bool f16) {
+int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a) {
     if (a.M == 0 || a.N == 0) return SHREWQ_OK;
     if (!gemv_mma_supported(a))
         return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "mma gemv: needs bf16 activations, M<=64, K a multiple of 64, 16-byte alignment");
-    if (f16 && a.M <= (size_t)kStageMaxTokens && a.M * a.K * sizeof(uint16_t) <= (size_t)kStageMaxBytes) {
-        const bool gated = a.q_up != nullptr;
-        if (a.y_dtype == SHREWQ_BF16) {
-            if (gated) launch_staged<__nv_bfloat16, true>(ctx, a);
-            else launch_staged<__nv_bfloat16, false>(ctx, a);
-        } else {
-            if (gated) launch_staged<float, true>(ctx, a);
-            else launch_staged<float, false>(ctx, a);
-        }
-        ctx->launches += 1;
-    } else if (f16) {
-        // [M,K] f16 activations, then M shift words (K % 64 == 0 keeps the words aligned)
-        const size_t xbytes = a.M * a.K * sizeof(__half);
-        int rc = ensure_xsplit(ctx, xbytes + a.M * sizeof(int));
-        if (rc != SHREWQ_OK) return rc;
-        __half *x16 = static_cast<__half *>(ctx->xsplit);
-        int *xshift = reinterpret_cast<int *>(static_cast<char *>(ctx->xsplit) + xbytes);
-        x_to_f16_kernel<<<(unsigned)a.M, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16 *>(a.x), x16, xshift,
-                                                                (int)a.K);
-        dispatch_y<true>(ctx, a, x16, xshift);
-        ctx->launches += 2;
-    } else {
-        dispatch_y<false>(ctx, a, a.x, nullptr);
-        ctx->launches += 1;
-    }
+    dispatch_y<false>(ctx, a, a.x, nullptr);
+    ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;
 }

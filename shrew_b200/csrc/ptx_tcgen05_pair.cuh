@@ -41,13 +41,12 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void *tmap,
         : "memory");
 }
 
-// completion of all prior MMAs of this thread arrives on the barrier at this offset in BOTH CTAs:
-// two commits, one per CTA's copy of the barrier (each commit arrives once on its barrier when
-// every MMA issued so far has completed)
+// completion of all prior MMAs of this thread arrives once on the barrier at this shared-memory offset in
+// BOTH CTAs of the pair (CTA mask 0b11)
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-    const uint32_t b0 = map_to_cta(bar, 0), b1 = map_to_cta(bar, 1);
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(b0) : "memory");
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(b1) : "memory");
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
 }
 
 // D[256 x 256] (+)= A[256 x 16, TMEM of both CTAs] * B[256 x 16, shared memory of both CTAs]^T

@@ -82,8 +82,7 @@ class QuantConfig:
     def _require_int8_symmetric(self) -> None:
         if not self._is_int8_symmetric():
             raise ShrewError(_lib.ERR_UNSUPPORTED,
-                             "only INT8 symmetric quantization is validated on the device (INT4 and asymmetric kernels are "
-                             "experimental: SHREWQ_EXPERIMENTAL_MODES=1)")
+                             "this entry point takes INT8 symmetric quantization only")
 
     def _abi_mode(self) -> Tuple[int, int]:
         return (8 if self.bits is QuantBits.Int8 else 4, _lib.SYMMETRIC if self.mode is QuantMode.Symmetric else _lib.ASYMMETRIC)
@@ -124,6 +123,10 @@ class Device:
 
     def launch_count(self) -> int:
         return int(_lib.lib().shrewq_ctx_launch_count(self.handle))
+
+    def set_option(self, name: str, value: int) -> None:
+        """A launch option of this device's context (shrewq_ctx_set_option: "tc_pair", "tc_tailsplit", ...)."""
+        _lib.check(_lib.lib().shrewq_ctx_set_option(self.handle, name.encode(), int(value)), self.handle)
 
 
 def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
@@ -177,9 +180,9 @@ class QuantizedTensor:
 
 
 def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTensor:
-    """quantize.rs:194-205 on the GPU.  `tensor` is an f32 CUDA tensor.  INT8 symmetric runs the
-    validated kernels; the other modes go through shrewq_quantize_f32_ex, which refuses them
-    unless SHREWQ_EXPERIMENTAL_MODES=1 is set."""
+    """quantize.rs:194-205 on the GPU.  `tensor` is a float CUDA tensor.  f32 INT8 symmetric runs the
+    tuned kernels (shrewq_quantize_f32); the other modes and storage types go through
+    shrewq_quantize_f32_ex / shrewq_quantize_any."""
     dev = Device.get(tensor.device)
     if tensor.dtype not in _STORAGE_CODE:
         raise ShrewError(_lib.ERR_UNSUPPORTED, f"quantize_tensor: dtype {tensor.dtype} is not a float storage type")
@@ -499,12 +502,12 @@ class QuantizedLinear:
 
 
 # ---- model-level helpers (quantize.rs:500-586) ------------------------------------------------------
-def quantize_named_parameters(module, config: QuantConfig) -> List[Tuple[str, QuantizedTensor]]:
+def quantize_named_parameters(module, config: QuantConfig, batched: bool = True) -> List[Tuple[str, QuantizedTensor]]:
     """Every parameter of rank >= 2 is quantized — including a Linear's [1,out] bias, which
-    is rank 2 in Shrew (quantize.rs:507-513, :760-766)."""
+    is rank 2 in Shrew (quantize.rs:507-513, :760-766).  INT8 symmetric f32 parameters go out as one
+    batched call (a few launches for the whole model, the same bits); batched=False quantizes tensor by tensor."""
     params = [(name, t.detach()) for name, t in module.named_parameters() if t.dim() >= 2]
-    # SHREWQ_BATCH_QUANTIZE=1: all tensors in a few launches (quantize_tensors; not yet run on a GPU)
-    if (os.environ.get("SHREWQ_BATCH_QUANTIZE", "0") == "1" and config._is_int8_symmetric() and params
+    if (batched and config._is_int8_symmetric() and params
             and all(t.dtype is torch.float32 for _, t in params)):
         return list(zip([n for n, _ in params], quantize_tensors([t for _, t in params], config)))
     return [(name, quantize_tensor(t, config)) for name, t in params]

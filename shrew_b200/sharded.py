@@ -139,11 +139,20 @@ class ShardedGatedMLP:
 class PeerOutput:
     """The full [m_max, n] output of a sharded layer, allocated as symmetric memory so that
     every rank holds a mapping of every other rank's copy.  A shard's kernel stores its
-    column slice into all copies itself; `barrier()` (a device-side signal exchange on the
-    current stream) then makes the whole matrix readable everywhere."""
+    column slice into all copies itself; `barrier()` (the library's device-side exchange barrier on the
+    current stream: shrewq_exchange_barrier, bounded waits, SHREWQ_ERR_TIMEOUT at the next synchronize
+    if a peer never arrives) then makes the whole matrix readable everywhere."""
 
     def __init__(self, m_max: int, n: int, dtype: torch.dtype, device, group=None):
+        import ctypes
+        import os
+
+        # nothing here uses multimem: keep the buffers off NVLink multicast objects where torch lets us
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+        from .quantize import Device
         self.group = group if group is not None else dist.group.WORLD
         self.buf = symm.empty((m_max, n), dtype=dtype, device=device)
         self.hdl = symm.rendezvous(self.buf, self.group)
@@ -151,6 +160,18 @@ class PeerOutput:
         self.n = n
         self.esize = self.buf.element_size()
         self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        # the exchange barrier's flag block: zeroed by its owner before any rank's first barrier
+        self.flags = symm.empty((_lib.EXCHANGE_FLAG_BYTES // 4,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.flag_hdl = symm.rendezvous(self.flags, self.group)
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)
+        self.dev = Device.get(device)
+        blocks = (ctypes.c_void_p * self.world)(*[int(p) for p in self.flag_hdl.buffer_ptrs])
+        h = ctypes.c_void_p()
+        _lib.check(_lib.lib().shrewq_exchange_create(self.dev.handle, self.rank, self.world, blocks, ctypes.byref(h)),
+                   self.dev.handle)
+        self._ex = h
 
     def slice_ptrs(self, n0: int):
         """(own pointer, [peer pointers]) of element [0, n0] in every copy."""
@@ -159,7 +180,18 @@ class PeerOutput:
         return own, [p + off for r, p in enumerate(self.ptrs) if r != self.rank]
 
     def barrier(self):
-        self.hdl.barrier()
+        from . import _lib
+        self.dev.bind_stream()
+        _lib.check(_lib.lib().shrewq_exchange_barrier(self._ex), self.dev.handle)
+
+    def __del__(self):
+        try:
+            from . import _lib
+            if getattr(self, "_ex", None):
+                _lib.lib().shrewq_exchange_destroy(self._ex)
+                self._ex = None
+        except Exception:
+            pass
 
 
 class FusedShardedLinear:

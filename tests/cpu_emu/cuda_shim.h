@@ -25,6 +25,7 @@
 #include <algorithm>
 #include <atomic>
 #include <barrier>
+#include <chrono>
 #include <functional>
 #include <map>
 #include <memory>
@@ -264,6 +265,19 @@ static inline unsigned long long atomicMin(unsigned long long *p, unsigned long 
     while (old > v && !__atomic_compare_exchange_n(p, &old, v, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST)) {}
     return old;
 }
+
+static inline unsigned atomicCAS(unsigned *p, unsigned cmp, unsigned val) {
+    __atomic_compare_exchange_n(p, &cmp, val, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST);
+    return cmp;
+}
+static inline unsigned atomicAdd(unsigned *p, unsigned v) { return __atomic_fetch_add(p, v, __ATOMIC_SEQ_CST); }
+static inline void __threadfence() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
+static inline void __nanosleep(unsigned) { std::this_thread::sleep_for(std::chrono::microseconds(50)); }
+// flags another GPU reads or writes: sequentially consistent atomics here
+static inline void st_release_sys_u32(uint32_t *p, uint32_t v) { __atomic_store_n(p, v, __ATOMIC_SEQ_CST); }
+static inline uint32_t ld_acquire_sys_u32(const uint32_t *p) { return __atomic_load_n(p, __ATOMIC_SEQ_CST); }
+static inline void fence_sys() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
+static inline void sleep_ns(uint32_t) { std::this_thread::sleep_for(std::chrono::microseconds(20)); }
 
 using std::max;
 using std::min;

@@ -240,6 +240,13 @@ static inline void tc_ld16(uint32_t taddr, uint32_t *r) {
     for (int i = 0; i < 16; ++i) r[i] = emu::g_block->tmem[lane * 512 + col + i];
 }
 
+static inline void tc_ld32(uint32_t taddr, uint32_t *r) {
+    const uint32_t lane = (taddr >> 16) + (threadIdx.x & 31), col = taddr & 0xFFFF;
+    if (!(lane < 128 && col + 32 <= 512)) { emu::fail("tcgen05.ld outside tensor memory"); return; }
+    EMU_CHECK((taddr >> 16) == 32 * ((threadIdx.x >> 5) & 3), "a warp may only touch the lane quadrant warp % 4");
+    for (int i = 0; i < 32; ++i) r[i] = emu::g_block->tmem[lane * 512 + col + i];
+}
+
 // tcgen05.mma.cta_group::1.kind::f16 [d], [a], b_desc, idesc, p:  D[128 x N] (+)= A[128 x 16] * B[N x 16]^T,
 // bf16 B, bf16 or f16 A (the descriptor's format fields), f32 accumulators.  A: tensor-memory lane m, 8 columns
 // of two 16-bit values (even k in the lower half).  B: shared memory, K-major rows of 128 bytes, 8-row groups `stride byte offset` apart, 128-byte swizzle.
@@ -313,10 +320,3 @@ static inline int __all_sync(unsigned, T pred) {
     b->warp[me >> 5]->arrive_and_wait();
     return all;
 }
-static inline unsigned atomicCAS(unsigned *p, unsigned cmp, unsigned val) {
-    __atomic_compare_exchange_n(p, &cmp, val, false, __ATOMIC_SEQ_CST, __ATOMIC_SEQ_CST);
-    return cmp;
-}
-static inline unsigned atomicAdd(unsigned *p, unsigned v) { return __atomic_fetch_add(p, v, __ATOMIC_SEQ_CST); }
-static inline void __threadfence() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
-static inline void __nanosleep(unsigned) { std::this_thread::sleep_for(std::chrono::microseconds(50)); }

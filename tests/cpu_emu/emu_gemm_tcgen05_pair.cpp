@@ -10,7 +10,7 @@ using namespace shrewq;
 
 namespace {
 template <typename YT, bool GATED>
-int run(const int8_t *q, const int8_t *q_up, const Operands2 &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
+int run(const int8_t *q, const int8_t *q_up, const Operands &ops, const uint16_t *x, void *y, int M, int N, int K, size_t ldy,
         int epilogue, int splits, int tile_list, DeviceStatus *st) {
     const uint32_t box_rows = GATED ? 64 : 128;
     const CUtensorMap tw{q, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, kBlockK, box_rows, 64};
@@ -64,7 +64,7 @@ extern "C" int emu_gemm_tcgen05_pair(const int8_t *q, const float *scales, const
     if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || M < 1) return -1;
     DeviceStatus st{0, 0, 0, 0};
     emu::g_failed = false;
-    const Operands2 ops{scales, bias, scales_up, bias_up};
+    const Operands ops{scales, bias, scales_up, bias_up};
     const uint16_t *xs = static_cast<const uint16_t *>(x);
     int rc;
     if (q_up) {

@@ -562,18 +562,25 @@ def test_tcgen05_gate_up_tile(oracle, emu_tc, tok, M, N, K, splits):
     assert oracle.rel_err(y, ref) < 1e-5
 
 
-def test_tcgen05_bf16_output_and_accumulate_epilogue(oracle, emu_tc):
+def test_tcgen05_bf16_output(oracle, emu_tc):
     q, scales, bias, x_bits, x = _tc_case(70, 130, 384, 11)
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
     y16 = _tc_forward(emu_tc, q, scales, bias, x_bits, 128, 3, y_bf16=True)
     assert oracle.rel_err((y16.astype(np.uint32) << 16).view(np.float32), ref) < 1e-2
-    # internal accumulate flag (0x100): adds what the output already holds before the elementwise op;
-    # used by the two-pass f32-activation route, which has not run on a GPU yet
-    prev = np.random.default_rng(1).standard_normal((70, 130)).astype(np.float32)
-    y = _tc_forward(emu_tc, q, scales, bias, x_bits, 128, 3, epilogue=0x100 | 1, y_init=prev)
-    assert oracle.rel_err(y, np.maximum(ref + prev, 0.0)) < 2e-6
-    y = _tc_forward(emu_tc, q, scales, bias, x_bits, 64, 3, splits=2, epilogue=0x100, y_init=prev)
-    assert oracle.rel_err(y, ref + prev) < 2e-6
+
+
+@pytest.mark.parametrize("M,N,K,ldy,y_bf16", [(70, 130, 384, 130, True), (33, 129, 128, 133, False), (40, 64, 192, 72, True),
+                                              (20, 200, 64, 203, True)])
+def test_tcgen05_rows_that_do_not_start_on_16_bytes(oracle, emu_tc, M, N, K, ldy, y_bf16):
+    # the epilogue's wide stores need 16-byte aligned rows; an odd row stride (or a ragged last channel
+    # segment) takes the element-wise stores out of the same staging tile, and nothing outside [M, N] is touched
+    q, scales, bias, x_bits, x = _tc_case(M, N, K, ldy)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
+    y = _tc_forward(emu_tc, q, scales, bias, x_bits, 64 if M <= 64 else 128, 3, y_bf16=y_bf16, ldy=ldy)
+    got = (y.astype(np.uint32) << 16).view(np.float32) if y_bf16 else y
+    assert oracle.rel_err(got[:, :N], ref) < (1e-2 if y_bf16 else 2e-6)
+    fill = 0x4100 if y_bf16 else np.float32(7.0)
+    assert np.all(y[:, N:] == fill)
 
 
 @pytest.mark.parametrize("seed", range(36))
@@ -629,24 +636,32 @@ def test_tcgen05_tile_list_grid(oracle, emu_tc):
         assert oracle.rel_err(y, ref) < 2e-6
 
 
-def test_f32_activations_through_two_tensor_core_passes(oracle, emu, emu_tc):
-    # forward_f32_on_tensor_cores (not yet run on a GPU): x = hi + lo in bf16, the hi pass writes
-    # scale * acc, the lo pass adds its own on top together with bias and the elementwise op
+@pytest.mark.parametrize("M,N,K,splits,y_bf16", [(90, 140, 784 // 16 * 16, 1, False), (200, 129, 256, 1, False),
+                                                  (130, 64, 1024, 2, False), (17, 300, 128, 1, True)])
+def test_f32_activations_as_hi_lo_pair_on_the_tensor_cores(oracle, emu, emu_tc, M, N, K, splits, y_bf16):
+    # forward_f32_on_tensor_cores: x = hi + lo in bf16, both token tiles in one stage, two MMAs per k-step
+    # into the same accumulator; the lo rows sit under the M hi rows of one array
     emu.emu_split_f32.argtypes = [_vp, _sz, _cu, _vp, _vp]
-    rng = np.random.default_rng(3)
-    M, N, K = 90, 140, 784 // 16 * 16
-    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    emu_tc.emu_gemm_tcgen05_xsplit.argtypes = [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci]
+    rng = np.random.default_rng(3 + M)
+    q = _aligned((N, K), np.int8)
+    q[...] = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
     scales = rng.random(N) * 1e-2 + 1e-4
     bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
     x = rng.random((M, K)).astype(np.float32)                 # U(0,1) like the MLP config's inputs
+    pair = _aligned((2 * M, K), np.uint16)
     hi, lo = np.zeros((M, K), np.uint16), np.zeros((M, K), np.uint16)
     emu.emu_split_f32(_p(x), x.size, 3, _p(hi), _p(lo))
+    pair[:M], pair[M:] = hi, lo
     hi_f, lo_f = (hi.astype(np.uint32) << 16).view(np.float32), (lo.astype(np.uint32) << 16).view(np.float32)
     assert np.max(np.abs((hi_f.astype(np.float64) + lo_f) - x)) <= 2.0 ** -16 * np.max(np.abs(x))
-    y1 = _tc_forward(emu_tc, q, scales, None, hi, 128, 3, epilogue=0)
-    y2 = _tc_forward(emu_tc, q, scales, bias, lo, 128, 3, epilogue=0x100 | 1, y_init=y1)
+    s32 = scales.astype(np.float32)
+    y = np.full((M, N), 0x4100, np.uint16) if y_bf16 else np.full((M, N), 7.0, np.float32)
+    rc = emu_tc.emu_gemm_tcgen05_xsplit(_p(q), _p(s32), _p(bias), _p(pair), _p(y), M, N, K, N, 1, int(y_bf16), splits)
+    assert rc == 0
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
-    assert oracle.rel_err(y2, ref) < 1e-4                      # the f32 path's tolerance
+    got = (y.astype(np.uint32) << 16).view(np.float32) if y_bf16 else y
+    assert oracle.rel_err(got, ref) < (1e-2 if y_bf16 else 1e-4)   # the f32 path's tolerance
 
 
 # ---- the CTA-pair kernel (cta_group::2), never run on a GPU: two blocks of a cluster run concurrently --

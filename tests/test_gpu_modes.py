@@ -1,18 +1,11 @@
-"""GPU: the reference's other quantization modes (asymmetric INT8, INT4) through the C ABI against
-the oracle and its golden vectors.  These kernels are built but have not run on a GPU yet, so the
-library refuses them unless SHREWQ_EXPERIMENTAL_MODES=1; the parity tests below run only when
-SHREWQ_TEST_UNVALIDATED=1 asks for them.  The refusal itself is tested unconditionally."""
-import os
-
+"""GPU: the reference's other quantization modes (asymmetric INT8, INT4: quantize.rs:99-139,353-364) through the C ABI
+against the oracle and its golden vectors: codes, scales and zero points bit for bit, the zero-point forward and the
+packed INT4 forward within the layer tolerances."""
 import numpy as np
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
-
-_UNVALIDATED = pytest.mark.skipif(os.environ.get("SHREWQ_TEST_UNVALIDATED", "0") != "1",
-                                  reason="kernels built and CPU-checked but not yet validated on a GPU; set SHREWQ_TEST_UNVALIDATED=1")
-
 
 def _cfg(bits, mode, gran):
     from shrew_b200.quantize import QuantBits, QuantConfig, QuantGranularity, QuantMode
@@ -21,26 +14,14 @@ def _cfg(bits, mode, gran):
                        QuantGranularity.PerChannel if gran else QuantGranularity.PerTensor)
 
 
-def test_other_modes_are_refused_by_default(monkeypatch):
-    from shrew_b200 import ShrewError, _lib, quantize_tensor
-    monkeypatch.delenv("SHREWQ_EXPERIMENTAL_MODES", raising=False)
-    w = torch.zeros(4, 8, device="cuda")
-    for bits, mode in ((4, 0), (8, 1), (4, 1)):
-        with pytest.raises(ShrewError) as e:
-            quantize_tensor(w, _cfg(bits, mode, 1))
-        assert e.value.code == _lib.ERR_UNSUPPORTED
-
-
 def _modes_golden():
     from tests.test_oracle_modes import MODES
     return MODES
 
 
-@_UNVALIDATED
 @pytest.mark.parametrize("case", _modes_golden(), ids=[c["name"] for c in _modes_golden()])
-def test_quantize_modes_match_golden(monkeypatch, case):
+def test_quantize_modes_match_golden(case):
     from shrew_b200 import quantize_tensor
-    monkeypatch.setenv("SHREWQ_EXPERIMENTAL_MODES", "1")
     w = torch.from_numpy(np.require(case["data"], dtype=np.float32, requirements="C")).cuda()
     qt = quantize_tensor(w, _cfg(case["bits"], case["mode"], case["granularity"]))
     torch.cuda.synchronize()
@@ -50,12 +31,10 @@ def test_quantize_modes_match_golden(monkeypatch, case):
     assert zps.tobytes() == case["zps"].tobytes()
 
 
-@_UNVALIDATED
 @pytest.mark.parametrize("bits,mode", [(8, 1), (4, 0), (4, 1)])
 @pytest.mark.parametrize("shape,gran", [((64, 300), 1), ((1000, 33), 1), ((257, 129), 0), ((3, 100000), 1), ((1 << 20,), 0)])
-def test_quantize_dequantize_modes_match_oracle(oracle, monkeypatch, bits, mode, shape, gran):
+def test_quantize_dequantize_modes_match_oracle(oracle, bits, mode, shape, gran):
     from shrew_b200 import dequantize_tensor, quantize_tensor
-    monkeypatch.setenv("SHREWQ_EXPERIMENTAL_MODES", "1")
     rng = np.random.default_rng(bits * 10 + mode)
     w = (rng.standard_normal(shape) * 0.3 + (0.2 if mode else 0.0)).astype(np.float32)
     w.reshape(-1)[::997] *= 40.0
@@ -71,13 +50,11 @@ def test_quantize_dequantize_modes_match_oracle(oracle, monkeypatch, bits, mode,
     np.testing.assert_array_equal(back, ref)
 
 
-@_UNVALIDATED
 @pytest.mark.parametrize("M,dtype", [(1, "bf16"), (7, "f32"), (48, "bf16"), (300, "bf16")])
-def test_forward_with_zero_points(oracle, monkeypatch, M, dtype):
+def test_forward_with_zero_points(oracle, M, dtype):
     # QuantizedLinear::forward with an asymmetric weight (quantize.rs:463-476): x . dequant(W)^T + bias
     from shrew_b200 import Linear, QuantizedLinear, _lib
     from shrew_b200.quantize import Device
-    monkeypatch.setenv("SHREWQ_EXPERIMENTAL_MODES", "1")
     rng = np.random.default_rng(M)
     N, K = 384, 1024
     w = (rng.standard_normal((N, K)) * 0.05 + 0.1).astype(np.float32)      # one-sided-ish: large zero points
@@ -97,13 +74,11 @@ def test_forward_with_zero_points(oracle, monkeypatch, M, dtype):
     assert oracle.rel_err(y.float().cpu().numpy(), ref) < (1e-2 if dtype == "bf16" else 1e-4)
 
 
-@_UNVALIDATED
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float64])
 @pytest.mark.parametrize("gran", [0, 1])
-def test_quantize_any_storage_type(oracle, monkeypatch, dtype, gran):
+def test_quantize_any_storage_type(oracle, dtype, gran):
     # quantize_tensor widens every storage type to f64 (quantize.rs:198); dequantize_tensor narrows back
     from shrew_b200 import dequantize_tensor, quantize_tensor
-    monkeypatch.setenv("SHREWQ_EXPERIMENTAL_MODES", "1")
     rng = np.random.default_rng(gran)
     w64 = rng.standard_normal((40, 700)) * 0.2
     t = torch.from_numpy(w64).to(dtype).cuda()
@@ -124,13 +99,11 @@ def test_quantize_any_storage_type(oracle, monkeypatch, dtype, gran):
     assert torch.equal(back.cpu(), ref)
 
 
-@_UNVALIDATED
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (3, 300, 1024), (16, 523, 2048), (32, 1000, 1152)])
-def test_packed_int4_forward(oracle, monkeypatch, M, N, K):
+def test_packed_int4_forward(oracle, M, N, K):
     # INT4 symmetric per-channel codes packed two per byte, small-batch forward on the warp-MMA kernel
     from shrew_b200 import quantize_tensor
     from shrew_b200.quantize import Device, QuantizedLinear
-    monkeypatch.setenv("SHREWQ_EXPERIMENTAL_MODES", "1")
     rng = np.random.default_rng(M + N)
     w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
     b = (rng.standard_normal(N) * 0.1).astype(np.float32)

@@ -52,28 +52,34 @@ def _worker(rank, world, port, q):
                 yf = fl.forward(x)
                 torch.cuda.synchronize()
                 res[f"fused_{M}_{it}"] = oracle.rel_err(yf.float().cpu().numpy(), ref)
-        if os.environ.get("SHREWQ_TEST_UNVALIDATED", "0") == "1":
-            # the gated MLP block with both exchanges fused (not yet validated against the oracle)
-            from shrew_b200.sharded import FusedShardedGatedMLP
-            dm, dff, M = 512, 1408, 96
-            ws = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in ((dff, dm), (dff, dm), (dm, dff))]
+        # the gated MLP block with both exchanges fused (the path `bench.py --gpus N` times): a small ragged shape, then
+        # the benchmark's own 4096 / 11008 block at batch 512 against the oracle on a subset of the token rows
+        from shrew_b200.sharded import FusedShardedGatedMLP
+        for tag, dm, dff, M, rows in (("small", 512, 1408, 96, None), ("llama", 4096, 11008, 512, [0, 1, 255, 256, 300, 511])):
+            ws = [(rng.standard_normal(s, dtype=np.float32) * np.float32(0.02)) for s in ((dff, dm), (dff, dm), (dm, dff))]
             x = torch.from_numpy(rng.standard_normal((M, dm)).astype(np.float32)).to(dev).to(torch.bfloat16)
             shards = []
             for wfull in ws:
                 n0, n1 = plan_shards(wfull.shape[0], world).rows(rank)
                 shards.append(QuantizedLinear.from_linear(Linear(torch.from_numpy(wfull[n0:n1].copy()).to(dev), None),
                                                           QuantConfig.int8_per_channel()))
-            mlp = FusedShardedGatedMLP(shards[0], shards[1], shards[2], dff, dm, 128)
-            y = mlp.forward(x)
-            torch.cuda.synchronize()
+            mlp = FusedShardedGatedMLP(shards[0], shards[1], shards[2], dff, dm, M)
+            for it in range(2):                    # the second step reuses the symmetric buffers
+                y = mlp.forward(x)
+                torch.cuda.synchronize()
+            from shrew_b200.quantize import Device
+            Device.get(dev).synchronize()          # surfaces a barrier that gave up
             qs = [oracle.quantize_f32(wfull, oracle.PER_CHANNEL) for wfull in ws]
             xn = x.float().cpu().numpy()
+            yn = y.float().cpu().numpy()
+            if rows is not None:
+                xn, yn = xn[rows], yn[rows]
             g = oracle.np_linear_forward(qs[0][0], qs[0][1], 1, None, xn)
             u = oracle.np_linear_forward(qs[1][0], qs[1][1], 1, None, xn)
             h = ((g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u)
             h16 = torch.from_numpy(h).to(torch.bfloat16).float().numpy()
             ref = oracle.np_linear_forward(qs[2][0], qs[2][1], 1, None, h16)
-            res["fused_mlp"] = oracle.rel_err(y.float().cpu().numpy(), ref)
+            res[f"fused_mlp_{tag}"] = oracle.rel_err(yn, ref)
         q.put((rank, res))
         dist.barrier()
     finally:
@@ -86,12 +92,22 @@ def test_sharded_linear_two_gpus():
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    out = [q.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.start()
+        out = [q.get(timeout=600) for _ in procs]
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        # never leave a child behind on a shared GPU, whatever failed above
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=30)
     for rank, res in out:
         for k, err in res.items():
             assert err <= 1e-2, f"rank {rank} {k}: rel err {err:.3e}"

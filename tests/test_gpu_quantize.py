@@ -153,8 +153,6 @@ def test_bad_arguments_return_errors():
     assert L.shrewq_dequantize(dev.handle, t.data_ptr(), t.data_ptr(), 4, 4, 1, 9, t.data_ptr()) == _lib.ERR_INVALID_ARG
 
 
-@pytest.mark.skipif(__import__("os").environ.get("SHREWQ_TEST_UNVALIDATED", "0") != "1",
-                    reason="entry points built from validated kernels but not yet run on a GPU; set SHREWQ_TEST_UNVALIDATED=1")
 @pytest.mark.parametrize("rows,cols,split", [(64, 128, 40), (1000, 333, 1), (7, 5, 7), (2048, 4096, 1024)])
 def test_per_tensor_quantization_of_row_shards(oracle, rows, cols, split):
     # two "ranks" on one GPU: amax per shard, max of the two on the host (the all-reduce), then each
@@ -174,8 +172,6 @@ def test_per_tensor_quantization_of_row_shards(oracle, rows, cols, split):
         assert g.scales.cpu().numpy().tobytes() == s_ref.tobytes()
 
 
-@pytest.mark.skipif(__import__("os").environ.get("SHREWQ_TEST_UNVALIDATED", "0") != "1",
-                    reason="kernels built and checked on the CPU model but not yet run on a GPU; set SHREWQ_TEST_UNVALIDATED=1")
 @pytest.mark.parametrize("gran", [0, 1])
 def test_many_tensors_per_launch_match_one_by_one(oracle, gran, monkeypatch):
     # the parameter list of config 2's model shape (4 blocks of 256-wide layers, scaled-down head), plus
@@ -198,9 +194,7 @@ def test_many_tensors_per_launch_match_one_by_one(oracle, gran, monkeypatch):
     assert got[4].scales.cpu().numpy().tobytes() == s_ref.tobytes()
     # and through the model-level helper
     lin = Linear(ws[1], torch.randn(256, device="cuda"))
-    monkeypatch.setenv("SHREWQ_BATCH_QUANTIZE", "1")
-    a = quantize_named_parameters(lin, cfg)
-    monkeypatch.setenv("SHREWQ_BATCH_QUANTIZE", "0")
-    b = quantize_named_parameters(lin, cfg)
+    a = quantize_named_parameters(lin, cfg)                  # one batched call
+    b = quantize_named_parameters(lin, cfg, batched=False)   # tensor by tensor
     assert [n for n, _ in a] == [n for n, _ in b] and all(torch.equal(x.data, y.data) and torch.equal(x.scales, y.scales)
                                                           for (_, x), (_, y) in zip(a, b))

@@ -65,12 +65,11 @@ def test_quantize_tensors_refuses_what_the_kernels_do_not_take(fake):
     assert Q.quantize_tensors([], QuantConfig.int8()) == [] and fake.calls == []
 
 
-def test_named_parameters_walk_uses_the_batch_only_on_request(fake, monkeypatch):
+def test_named_parameters_walk_goes_out_as_one_batch(fake):
     class M:
         def named_parameters(self):
             return [("weight", torch.zeros(4, 8)), ("bias", torch.zeros(1, 4)), ("gain", torch.zeros(4))]
 
-    monkeypatch.setenv("SHREWQ_BATCH_QUANTIZE", "1")
     out = Q.quantize_named_parameters(M(), QuantConfig.int8())
     assert [n for n, _ in out] == ["weight", "bias"]            # rank >= 2 only, the [1, out] bias included (quantize.rs:507-513)
     assert len(fake.calls) == 1 and len(fake.calls[0][1]) == 2

@@ -21,17 +21,25 @@ def plan(M, N, K, bf16=1, gated=0, sms=SMS):
     return rc, name.value.decode(), dict(zip(("tok", "n_tiles", "m_tiles", "splits", "rounds"), (v.value for v in out)))
 
 
-def test_a_few_tokens_go_to_the_cuda_core_gemv():
-    for M in (1, 2, 4):
+def test_small_batches_go_to_the_streaming_kernels():
+    for M in (1, 2):
         rc, name, p = plan(M, 4096, 4096)
         assert (rc, name) == (0, "gemv") and not any(p.values())
+    for M in (3, 4, 8, 16, 32):
+        rc, name, p = plan(M, 4096, 4096)
+        assert (rc, name) == (0, "mma") and not any(p.values())
+    assert plan(33, 4096, 4096)[1] == "tcgen05"
+    assert plan(8, 4096, 4112)[1] == "tcgen05"          # the warp-MMA kernel wants in_features in blocks of 64
+    assert plan(4, 4096, 4112)[1] == "gemv"
 
 
-def test_f32_activations_never_reach_the_tensor_cores():
+def test_f32_activations_take_the_hi_lo_pass_on_the_tensor_cores():
     assert plan(8, 4096, 4096, bf16=0)[1] == "gemv"
     assert plan(16, 4096, 4096, bf16=0)[1] == "gemv"
-    assert plan(17, 4096, 4096, bf16=0)[1] == "simt"
-    assert plan(512, 4096, 4096, bf16=0)[1] == "simt"
+    assert plan(17, 4096, 4096, bf16=0)[1] == "tcgen05-f32"
+    assert plan(512, 4096, 4096, bf16=0)[1] == "tcgen05-f32"
+    assert plan(512, 4096, 4100, bf16=0)[1] == "simt"    # ragged in_features: the general kernel
+    assert plan(512, 4096, 4096, bf16=0, gated=1)[1] == "simt"
 
 
 def test_ragged_in_features_fall_back_to_the_general_kernel():
@@ -42,7 +50,7 @@ def test_ragged_in_features_fall_back_to_the_general_kernel():
 
 @pytest.mark.parametrize("gated", [0, 1])
 @pytest.mark.parametrize("M,N,K", list(itertools.product(
-    (5, 16, 17, 33, 64, 100, 128, 129, 256, 512, 1000, 2048, 8192),
+    (33, 64, 100, 128, 129, 256, 512, 1000, 2048, 8192),
     (128, 1000, 4096, 11008, 32000),
     (16, 64, 128, 4096, 11008))))
 def test_the_plan_covers_the_problem(M, N, K, gated):
@@ -63,37 +71,30 @@ def test_the_plan_covers_the_problem(M, N, K, gated):
     # K is split only to fill SMs that the tile grid leaves idle, and never below a useful pipeline length
     tiles = p["n_tiles"] * p["m_tiles"]
     if p["splits"] > 1:
-        assert p["tok"] <= 64                      # partial sums of large tiles are not worth their traffic
         assert tiles * p["splits"] <= SMS          # all splits of all tiles run in one wave
-        assert p["rounds"] >= 2
+        assert p["rounds"] >= (2 if p["tok"] <= 64 else 8)
 
 
 def test_headline_shapes():
-    # decode-sized batches of a 4096x4096 projection: 32 channel tiles cannot fill 148 SMs, so K is split
-    assert plan(16, 4096, 4096)[2] == dict(tok=16, n_tiles=32, m_tiles=1, splits=4, rounds=8)
+    # a 4096x4096 projection at 64 tokens: 32 channel tiles cannot fill 148 SMs, so K is split
+    assert plan(64, 4096, 4096)[2] == dict(tok=64, n_tiles=32, m_tiles=1, splits=4, rounds=8)
     # wide projections fill the GPU by themselves
-    assert plan(16, 11008, 4096)[2] == dict(tok=16, n_tiles=86, m_tiles=1, splits=1, rounds=32)
+    assert plan(64, 11008, 4096)[2] == dict(tok=64, n_tiles=86, m_tiles=1, splits=1, rounds=32)
     # prefill: 128-token tiles until the grid is several waves deep, then 256
     assert plan(512, 4096, 4096)[2]["tok"] == 128
     assert plan(2048, 4096, 4096)[2] == dict(tok=256, n_tiles=32, m_tiles=8, splits=1, rounds=64)
-    # gate and up halves share a tile: twice the channel tiles
-    assert plan(512, 11008, 4096, gated=1)[2]["n_tiles"] == 172
+    # gate and up halves share a tile: twice the channel tiles, 256 tokens above a batch of 128
+    assert plan(512, 11008, 4096, gated=1)[2] == dict(tok=256, n_tiles=172, m_tiles=2, splits=1, rounds=64)
+    assert plan(128, 11008, 4096, gated=1)[2]["tok"] == 128
+    # the down projection of a block sharded over 8 GPUs: 4 channel tiles x 4 token tiles, K split to fill the SMs
+    p = plan(512, 512, 11008)[2]
+    assert p["tok"] == 128 and p["splits"] == 9 and p["rounds"] == 10
 
 
 def test_fewer_sms_split_less():
-    full = plan(16, 4096, 4096, sms=148)[2]["splits"]
-    small = plan(16, 4096, 4096, sms=40)[2]["splits"]
+    full = plan(64, 4096, 4096, sms=148)[2]["splits"]
+    small = plan(64, 4096, 4096, sms=40)[2]["splits"]
     assert small <= full and small == 1
-
-
-def test_forced_token_tile(monkeypatch):
-    monkeypatch.setenv("SHREWQ_TC_TOK", "256")
-    assert plan(512, 4096, 4096)[2]["tok"] == 256
-    monkeypatch.setenv("SHREWQ_TC_TOK", "48")
-    assert plan(512, 4096, 4096)[0] != 0
-    monkeypatch.setenv("SHREWQ_TC_TOK", "0")
-    monkeypatch.setenv("SHREWQ_TC_SPLITK", "0")
-    assert plan(16, 4096, 4096)[2]["splits"] == 1
 
 
 def test_bad_arguments_are_refused():
@@ -107,45 +108,3 @@ def test_bad_arguments_are_refused():
     assert L.shrewq_plan_forward(8, 0, 4096, 1, 0, 148, name, 32, *refs) != 0
     assert L.shrewq_plan_forward(8, 4096, 0, 1, 0, 148, name, 32, *refs) != 0
     assert L.shrewq_plan_forward(8, 4096, 4096, 1, 0, 148, name, 32, None, *refs[1:]) != 0
-
-
-def test_wave_aware_split_rule(monkeypatch):
-    # SHREWQ_TC_SPLIT_WAVES=1 (opt-in): 86 channel tiles on 148 SMs are one wave whole, two waves of a third
-    # each when split 3 ways, three waves of a fifth when split 5 ways
-    assert plan(16, 11008, 4096)[2]["splits"] == 1
-    monkeypatch.setenv("SHREWQ_TC_SPLIT_WAVES", "1")
-    p = plan(16, 11008, 4096)[2]
-    assert (p["splits"], p["rounds"]) == (5, 7)
-    assert plan(16, 4096, 4096)[2]["splits"] == 4                 # 32 tiles: as before, one wave of 128
-    assert plan(128, 11008, 4096)[2]["splits"] == 1               # large tiles stay whole ...
-    assert plan(512, 11008, 4096, gated=1)[2]["splits"] == 1      # ... and so do grids of many waves
-    monkeypatch.setenv("SHREWQ_TC_SPLITK_MAXTOK", "256")
-    assert plan(128, 11008, 4096)[2]["splits"] == 3               # ... unless split-K is extended to them
-    assert plan(512, 11008, 4096, gated=1)[2]["splits"] == 1
-    for M, N, K in [(16, 11008, 4096), (64, 4096, 11008), (128, 11008, 4096), (256, 4096, 4096), (100, 1000, 4096)]:
-        q = plan(M, N, K)[2]
-        kblk = 64 if q["tok"] == 256 else 128
-        total = -(-K // kblk)
-        assert q["splits"] * q["rounds"] >= total and (q["splits"] - 1) * q["rounds"] < total
-
-
-def test_token_tile_of_gate_up_launches_can_be_set_on_its_own(monkeypatch):
-    # the benchmark's block at batch 512: 128-token tiles by default for both launches; SHREWQ_TC_TOK_GATED moves the
-    # gate/up launch alone (the down projection has too few channel tiles to afford 256-token tiles)
-    assert plan(512, 11008, 4096, gated=1)[2]["tok"] == 128
-    monkeypatch.setenv("SHREWQ_TC_TOK_GATED", "256")
-    rc, name, p = plan(512, 11008, 4096, gated=1)
-    assert (rc, name) == (0, "tcgen05") and (p["tok"], p["n_tiles"], p["m_tiles"], p["splits"]) == (256, 172, 2, 1)
-    assert plan(512, 4096, 11008, gated=0)[2]["tok"] == 128
-
-
-def test_cost_rule_for_the_token_tile(monkeypatch):
-    # SHREWQ_TC_TILE_RULE=cost: waves x (1100 | 1400 cycles per 128 k) instead of SM fill.  The benchmark's block at
-    # batch 512: gate/up (172 channel tiles) 5 x 1100 > 3 x 1400 -> 256 tokens; down (32 tiles) 1 x 1100 < 1 x 1400 -> 128
-    assert plan(512, 11008, 4096, gated=1)[2]["tok"] == 128
-    monkeypatch.setenv("SHREWQ_TC_TILE_RULE", "cost")
-    assert plan(512, 11008, 4096, gated=1)[2]["tok"] == 256
-    assert plan(512, 4096, 11008, gated=0)[2]["tok"] == 128
-    assert plan(1024, 4096, 4096)[2]["tok"] == 256        # 2 waves of 128-token tiles against 1 of 256
-    assert plan(512, 4096, 4096)[2]["tok"] == 128
-    assert plan(100, 4096, 4096)[2]["tok"] == 128         # up to 128 tokens the smallest covering tile, as before
