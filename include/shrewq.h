@@ -93,7 +93,8 @@ SHREWQ_API int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream);
  *   "tc_tok"       0, 16, 32, 64, 128, 256   force the token tile (default 0 = choose)
  *   "tc_tok_gated" the same for gate/up launches only
  *   "tc_tailsplit" 0/1    issue a short last wave as a second launch split along K (default 0)
- *   "tc_pair"      0/1    batches above 128 tokens on CTA pairs (tcgen05.mma.cta_group::2)
+ *   "tc_pair"      0..2   CTA pairs (tcgen05.mma.cta_group::2) for batches above 128 tokens: 0 never, 1 where
+ *                         they win by measurement (default), 2 always
  *   "gemv_pdl"     0/1    programmatic dependent launch of the small-batch kernel (default 0)
  * Unknown names and values out of range return SHREWQ_ERR_INVALID_ARG. */
 SHREWQ_API int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value);

@@ -138,7 +138,10 @@ int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value) {
             return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: %s is 0 (choose), 16, 32, 64, 128 or 256", name);
         (name[6] == '_' ? t.tc_tok_gated : t.tc_tok) = value;
     } else if (!strcmp(name, "tc_tailsplit")) t.tc_tailsplit = value != 0;
-    else if (!strcmp(name, "tc_pair")) t.tc_pair = value != 0;
+    else if (!strcmp(name, "tc_pair")) {
+        if (value < 0 || value > 2) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: tc_pair is 0 (never), 1 (where pairs win) or 2 (always above 128 tokens)");
+        t.tc_pair = value;
+    }
     else if (!strcmp(name, "gemv_pdl")) t.gemv_pdl = value != 0;
     else return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);
     return SHREWQ_OK;
@@ -186,6 +189,16 @@ static int default_family(size_t M, bool gemv_ok, bool mma_ok, bool tc_ok) {
     return tc_ok ? kForceTc : (gemv_ok ? kForceGemv : kForceSimt);
 }
 
+// CTA pairs against the single-CTA kernel, from measurements on 148 SMs (Llama-MLP block and 4096 x 4096 layers,
+// batches 256..4096): a pair tile is 256 channels (128 gated) x 256 tokens and does twice the work per issued MMA,
+// but a grid that leaves many SMs idle, or needs a deep K split to fill them, is better served by the smaller
+// tiles of the single-CTA kernel.  Pairs win from one full wave of pair tiles (64) up, and from half a wave when
+// the reduction is long enough (K >= 8192) for a two-way K split to keep every pair busy.
+static bool pair_kernel_wins(size_t M, size_t N, size_t K, bool gated) {
+    const size_t pair_tiles = ((N + (gated ? 127 : 255)) / (gated ? 128 : 256)) * ((M + 255) / 256);
+    return pair_tiles >= 64 || (pair_tiles >= 32 && K >= 8192);
+}
+
 int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, int sm_count, char *kernel, size_t kernel_len,
                         int *tok, int *n_tiles, int *m_tiles, int *splits, int *rounds_per_split) {
     if (!kernel || kernel_len < 16 || !tok || !n_tiles || !m_tiles || !splits || !rounds_per_split || sm_count < 1 || N == 0 ||
@@ -199,8 +212,9 @@ int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, 
     const bool mma_ok = x_is_bf16 && (K % 64) == 0 && M <= 64 && small;
     int fam = default_family(M, vec16 && M <= 16, mma_ok, tc_ok);
     if (!x_is_bf16 && vec16 && small && M > 16 && !gated) fam = kForceTcF32;   // f32 activations: the hi/lo tensor-core pass
+    if (fam == kForceTc && M > 128 && pair_kernel_wins(M, N, K, gated != 0)) fam = kForceTc2Cta;
     const char *name = fam == kForceGemv ? "gemv" : fam == kForceMma ? "mma" : fam == kForceTc ? "tcgen05"
-                       : fam == kForceTcF32 ? "tcgen05-f32" : "simt";
+                       : fam == kForceTc2Cta ? "tcgen05-2cta" : fam == kForceTcF32 ? "tcgen05-f32" : "simt";
     snprintf(kernel, kernel_len, "%s", name);
     if (!strcmp(name, "tcgen05"))
         return plan_gemm_tcgen05(M, N, K, gated != 0, sm_count, tok, n_tiles, m_tiles, splits, rounds_per_split);
@@ -623,7 +637,7 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
                 // a few tokens: the GEMV reads f32 activations directly; beyond, the tensor cores on the
                 // bf16 hi/lo pair; the general f32 kernel takes what neither can (misaligned, odd widths)
                 choice = gemv_ok ? kForceGemv : f32_tc_ok ? kForceTcF32 : kForceSimt;
-            } else if (ctx->tuning.tc_pair && M > 128 && tc_ok) {
+            } else if (M > 128 && tc_ok && (ctx->tuning.tc_pair == 2 || (ctx->tuning.tc_pair == 1 && pair_kernel_wins(M, lin->n, lin->k, up != nullptr)))) {
                 choice = kForceTc2Cta;
             } else {
                 choice = default_family(M, gemv_ok, mma_ok, tc_ok);

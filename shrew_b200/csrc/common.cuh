@@ -24,7 +24,7 @@ struct Tuning {
     int tc_tok = 0;         // 0 = choose; else force the token tile (16, 32, 64, 128, 256)
     int tc_tok_gated = 0;   // the same for gate/up launches only
     int tc_tailsplit = 0;   // issue a short last wave as a second launch split along K
-    int tc_pair = 0;        // batches above 128 tokens on CTA pairs (tcgen05.mma.cta_group::2)
+    int tc_pair = 1;        // CTA pairs (tcgen05.mma.cta_group::2) for large batches: 0 never, 1 where they win, 2 whenever M > 128
     int gemv_pdl = 0;       // programmatic dependent launch of the small-batch kernels
 };
 

@@ -34,6 +34,7 @@
 #include "dests.cuh"
 #include "ptx_small.cuh"
 #include "ptx_tcgen05_pair.cuh"
+#include "tcgen05_common.cuh"
 #include "tcgen05_epilogue.cuh"
 
 namespace shrewq {
@@ -55,22 +56,9 @@ constexpr int kXOff = kSub * kWSub;
 constexpr int kAColsPerStage = kSub * (kBlockK / 2);  // 64
 constexpr int kABase = kTokPair;                      // D occupies columns [0,256)
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
-#ifndef SHREWQ_SPIN_FAST_LIMIT
-#define SHREWQ_SPIN_FAST_LIMIT (1u << 14)
-#endif
-#ifndef SHREWQ_SPIN_SLOW_LIMIT
-#define SHREWQ_SPIN_SLOW_LIMIT (1u << 21)
-#endif
-constexpr uint32_t kSpinFast = SHREWQ_SPIN_FAST_LIMIT;  // polls, then polls with ~100 ns sleeps
-constexpr uint32_t kSpinSlow = SHREWQ_SPIN_SLOW_LIMIT;
 static_assert(kABase + kStages * kAColsPerStage <= 512, "TMEM columns");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 static_assert(kStages * kStageBytes >= kGroups * kEpiGroupBytes, "the epilogue's staging tiles reuse the pipeline stages");
-
-struct Ctl {
-    volatile int abort_flag;
-    uint32_t tmem_base;
-};
 
 // In-kernel cycle trace (tracing build only): CTA (0,0,0), the pair's leader, stamps clock64() per role
 // and pipeline round; layout and meaning as in the single-CTA kernel.
@@ -86,57 +74,12 @@ __device__ __forceinline__ void trace_rec_pair(long long *tr, int role, int kb, 
 #define TRACE2_INIT
 #endif
 
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role,
-                                            uint32_t stage) {
-    for (uint32_t i = 0; i < kSpinFast; ++i)
-        if (mbar_try(bar, parity)) return true;
-    for (uint32_t i = 0; i < kSpinSlow; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if (ctl->abort_flag) return false;
-        __nanosleep(100);
-    }
-    ctl->abort_flag = 1;
-    if (atomicCAS(&st->timeout_flag, 0u, 2u) == 0u) {
-        st->where = (blockIdx.x << 8) | role;
-        st->stage = stage;
-        st->parity = parity;
-    }
-    return false;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role,
-                                          uint32_t stage) {
-    if (mbar_try(bar, parity)) return true;
-    if (mbar_try(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, ctl, st, role, stage);
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role, uint32_t stage) {
+    return mbar_wait_c<2>(bar, parity, ctl, st, role, stage);
 }
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role,
                                                uint32_t stage) {
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, st, role, stage) ? 1 : 0;
-    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-    if (ok) ok = mbar_try(bar, parity) ? 1 : 0;  // every lane acquires the phase itself
-    return __all_sync(0xFFFFFFFFu, ok) != 0;
-}
-
-__device__ __forceinline__ void cvt_i8x4_bf16(uint32_t w, uint32_t &lo, uint32_t &hi) {
-    const uint32_t u = w ^ 0x80808080u;
-    const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440)) - 8388736.0f;
-    const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7441)) - 8388736.0f;
-    const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7442)) - 8388736.0f;
-    const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)) - 8388736.0f;
-    lo = pack_bf16x2_rn(f1, f0);
-    hi = pack_bf16x2_rn(f3, f2);
-}
-
-// K-major, 128-byte swizzle, 8-row groups 1024 B apart, descriptor version 1
-__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
+    return mbar_wait_warp_c<2>(bar, parity, ctl, st, role, stage);
 }
 
 // Split-K (gridDim.z > 1): CTA (x, y, z) walks pipeline rounds [z * rounds_per_split, ...) of its tile
@@ -283,9 +226,11 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
         // ---------------- converters, then epilogue (both CTAs) ----------------
         const int group = (warp - 2) >> 2;
         const int quad = warp & 3;
-        const int row = quad * 32 + lane;
+        const int row = quad * 32 + lane;  // TMEM lane
+        // gated tiles: gate row r (shared-memory row r) goes to lane 2r, up row r (row 64 + r) to lane 2r + 1
+        const int srow = GATED ? ((row & 1) * (kLanes / 2) + (row >> 1)) : row;
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        const int swz = (row >> 1) & 3;
+        const int swz = (srow >> 1) & 3;
         const uint32_t aready_leader = map_to_cta(bars_u32 + kAready, 0);
         bool ok = true;
         // a group owns pipeline stages (s % kGroups), so that it passes through every phase of the
@@ -301,16 +246,8 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             if (quad == 0) TRACE2(2, i, 1);
 #pragma unroll
             for (int j = 0; j < kSub; ++j) {
-                const uint8_t *rowp = smem + s * kStageBytes + j * kWSub + row * kBlockK;
                 uint32_t packed[32];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(rowp + ((c ^ swz) << 4));
-                    cvt_i8x4_bf16(v.x, packed[8 * c + 0], packed[8 * c + 1]);
-                    cvt_i8x4_bf16(v.y, packed[8 * c + 2], packed[8 * c + 3]);
-                    cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
-                    cvt_i8x4_bf16(v.w, packed[8 * c + 6], packed[8 * c + 7]);
-                }
+                convert_row64(smem + s * kStageBytes + j * kWSub + srow * kBlockK, swz, packed);
                 tc_st32(tmem_base + lane_addr + kABase + s * kAColsPerStage + j * (kBlockK / 2), packed);
             }
             if (quad == 0) TRACE2(2, i, 2);
@@ -328,14 +265,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
             float *mine = sk.partials + (tile * splits + blockIdx.z) * (size_t)(kTokPair * kLanes);
             if (ok) {
-#pragma unroll 1
-                for (int c = group; c < kTokPair / 16; c += kGroups) {
-                    uint32_t r[16];
-                    tc_ld16(tmem_base + lane_addr + c * 16, r);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) __stcg(mine + (c * 16 + i) * kLanes + row, __uint_as_float(r[i]));
-                }
+                dump_partials<kTokPair, kGroups>(tmem_base, mine, group, quad, lane);
             }
             __threadfence();
             named_bar_sync(1, 128 * kGroups);
@@ -348,13 +278,13 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                 __threadfence();
                 epilogue_tile<kTokPair, kGroups, GATED, YT>(tmem_base, smem, group, quad, lane, ok, ops, y, extra, M, N, ldy, epilogue,
                                                             n0, m0_pair,
-                                                            PartialSums{sk.partials + tile * splits * (size_t)(kTokPair * kLanes), splits});
+                                                            PartialSums{sk.partials + tile * splits * (size_t)(kTokPair * kLanes), splits, (size_t)(kTokPair * kLanes)});
                 named_bar_sync(1, 128 * kGroups);
                 if (threadIdx.x == 64) sk.counters[tile] = 0;  // ready for the next launch
             }
         } else {
             epilogue_tile<kTokPair, kGroups, GATED, YT>(tmem_base, smem, group, quad, lane, ok, ops, y, extra, M, N, ldy, epilogue, n0,
-                                                        m0_pair, PartialSums{nullptr, 0});
+                                                        m0_pair, PartialSums{nullptr, 0, 0});
         }
     }
 

@@ -16,8 +16,8 @@
 // the elementwise op, transposes through shared memory and stores whole token rows with 16-byte stores.
 //
 // GATED: the 128 lanes carry 64 rows of a gate matrix and the same 64 rows of an up matrix
-// (two 64-row TMA boxes per sub-block); the epilogue pairs lane r with lane r+64 and
-// writes silu(gate)*up for 64 channels.
+// (two 64-row TMA boxes per sub-block), interleaved by the converters: gate row r in lane 2r, up row r in
+// lane 2r+1; the epilogue pairs neighbouring lanes with a shuffle and writes silu(gate)*up for 64 channels.
 //
 // XSPLIT (f32 activations): x arrives as two bf16 matrices hi = bf16(x) and lo = bf16(x - hi), stacked
 // as rows [0,M) and [M,2M) of one array; a stage holds both token tiles and every k-step issues two
@@ -43,6 +43,7 @@
 #include "dests.cuh"
 #include "ptx_small.cuh"
 #include "ptx_tcgen05.cuh"
+#include "tcgen05_common.cuh"
 #include "tcgen05_epilogue.cuh"
 
 namespace shrewq {
@@ -51,17 +52,6 @@ namespace {
 constexpr int kTileN = 128;  // TMEM lanes = weight rows per CTA (64 + 64 when GATED)
 constexpr int kBlockK = 64;  // k per sub-block (one 64-byte-swizzled INT8 box)
 constexpr int kUmmaK = 16;
-// limits of a bounded wait: polls, then polls with ~100 ns sleeps (a fraction of a second in all);
-// the CPU tests that make a wait run out on purpose compile with smaller limits
-#ifndef SHREWQ_SPIN_FAST_LIMIT
-#define SHREWQ_SPIN_FAST_LIMIT (1u << 14)
-#endif
-#ifndef SHREWQ_SPIN_SLOW_LIMIT
-#define SHREWQ_SPIN_SLOW_LIMIT (1u << 21)
-#endif
-constexpr uint32_t kSpinFast = SHREWQ_SPIN_FAST_LIMIT;
-constexpr uint32_t kSpinSlow = SHREWQ_SPIN_SLOW_LIMIT;
-
 template <int TOK, int KSUB, bool XSPLIT = false>
 struct Cfg {
     static constexpr int kWSub = kTileN * kBlockK;                   // 8192 B of codes per sub-block
@@ -85,75 +75,12 @@ struct Cfg {
     static_assert(kStages * kStageBytes >= 3 * kEpiGroupBytes, "the epilogue's staging tiles reuse the pipeline stages");
 };
 
-struct Ctl {  // lives in shared memory
-    volatile int abort_flag;
-    uint32_t tmem_base;
-};
-
-// Slow path of the bounded wait, kept out of line so the hot loops only carry one try_wait.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st,
-                                            uint32_t role, uint32_t stage) {
-    for (uint32_t i = 0; i < kSpinFast; ++i)
-        if (mbar_try(bar, parity)) return true;
-    for (uint32_t i = 0; i < kSpinSlow; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if (ctl->abort_flag) return false;
-        __nanosleep(100);
-    }
-    ctl->abort_flag = 1;
-    if (atomicCAS(&st->timeout_flag, 0u, 1u) == 0u) {
-        st->where = (blockIdx.x << 8) | role;
-        st->stage = stage;
-        st->parity = parity;
-    }
-    return false;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role, uint32_t stage) {
+    return mbar_wait_c<1>(bar, parity, ctl, st, role, stage);
 }
-
-// Bounded wait.  Returns false if it gave up or another role already did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st,
-                                          uint32_t role, uint32_t stage) {
-    if (mbar_try(bar, parity)) return true;
-    if (mbar_try(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, ctl, st, role, stage);
-}
-
-// Warp-level wait: lane 0 polls, the outcome is broadcast with a shuffle (which also
-// synchronises the warp and orders memory among its lanes).  32 lanes polling the same
-// mbarrier word serialise in the shared-memory pipe.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st,
-                                               uint32_t role, uint32_t stage) {
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, st, role, stage) ? 1 : 0;
-    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-    // every lane observes the completed phase itself (one try_wait that succeeds at once), so
-    // each has its own acquire on the data the barrier guards
-    if (ok) ok = mbar_try(bar, parity) ? 1 : 0;
-    return __all_sync(0xFFFFFFFFu, ok) != 0;
-}
-
-// 4 INT8 codes (one 32-bit word) -> two packed bf16x2 words, exactly.
-// byte ^ 0x80 = q + 128 as an unsigned byte u; 0x4B0000uu is the float 2^23 + u; subtracting
-// 2^23 + 128 leaves q; cvt.rn.bf16x2.f32 packs two of them (exact, |q| <= 128).
-__device__ __forceinline__ void cvt_i8x4_bf16(uint32_t w, uint32_t &lo, uint32_t &hi) {
-    const uint32_t u = w ^ 0x80808080u;
-    const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440)) - 8388736.0f;
-    const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7441)) - 8388736.0f;
-    const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7442)) - 8388736.0f;
-    const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)) - 8388736.0f;
-    lo = pack_bf16x2_rn(f1, f0);
-    hi = pack_bf16x2_rn(f3, f2);
-}
-
-// Shared-memory matrix descriptor for the activation tile: K-major, 128-byte swizzle,
-// rows of 128 B, 8-row groups 1024 B apart (stride byte offset), descriptor version 1.
-__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);        // start address  [0,14)
-    d |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset [32,46)
-    d |= (uint64_t)1 << 46;                             // version = 1 (sm_100)
-    d |= (uint64_t)2 << 61;                             // layout: SWIZZLE_128B
-    return d;
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, Ctl *ctl, DeviceStatus *st, uint32_t role,
+                                               uint32_t stage) {
+    return mbar_wait_warp_c<1>(bar, parity, ctl, st, role, stage);
 }
 
 #ifdef SHREWQ_TRACE
@@ -310,9 +237,13 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         // ---------------- converters, then epilogue ----------------
         const int group = (warp - 2) >> 2;
         const int quad = warp & 3;                 // TMEM lane quadrant this warp may access
-        const int row = quad * 32 + lane;          // weight row inside the tile == TMEM lane
+        const int row = quad * 32 + lane;          // TMEM lane
+        // the weight row of the tile this lane converts: plain tiles lane = row; gated tiles interleave the gate box
+        // (shared-memory rows 0..63) and the up box (64..127), gate rows on even lanes, so that a channel's
+        // gate and up accumulators sit in neighbouring lanes for the epilogue
+        const int srow = GATED ? ((row & 1) * 64 + (row >> 1)) : row;
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        const int swz = (row >> 1) & 3;
+        const int swz = (srow >> 1) & 3;
         bool ok = true;
         // A group owns pipeline STAGES (stage s belongs to group s % G), not every G-th round: its
         // warps then pass through every phase of the barriers they poll, so a parity wait can never
@@ -328,18 +259,8 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             if (((warp - 2) & 3) == 0) TRACE(2, i, 1);
 #pragma unroll
             for (int j = 0; j < KSUB; ++j) {
-                // 64 codes of this row; TMA wrote them with the 64-byte swizzle: the 16-byte
-                // chunk c of row r sits at chunk position c ^ ((r >> 1) & 3)
-                const uint8_t *rowp = smem + s * C::kStageBytes + j * C::kWSub + row * kBlockK;
                 uint32_t packed[32];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(rowp + ((c ^ swz) << 4));
-                    cvt_i8x4_bf16(v.x, packed[8 * c + 0], packed[8 * c + 1]);
-                    cvt_i8x4_bf16(v.y, packed[8 * c + 2], packed[8 * c + 3]);
-                    cvt_i8x4_bf16(v.z, packed[8 * c + 4], packed[8 * c + 5]);
-                    cvt_i8x4_bf16(v.w, packed[8 * c + 6], packed[8 * c + 7]);
-                }
+                convert_row64(smem + s * C::kStageBytes + j * C::kWSub + srow * kBlockK, swz, packed);
                 tc_st32(tmem_base + lane_addr + C::kABase + s * C::kAColsPerStage + j * (kBlockK / 2), packed);
             }
             if (((warp - 2) & 3) == 0) TRACE(2, i, 2);
@@ -357,7 +278,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
         if (splits == 1) {
             if (ok) tc_fence_after();
             epilogue_tile<TOK, G, GATED, YT>(tmem_base, smem, group, quad, lane, ok, ops, y, extra, M, N, ldy, epilogue, n0, m0,
-                                             PartialSums{nullptr, 0});
+                                             PartialSums{nullptr, 0, 0});
         } else {
             // split-K: every CTA parks its raw accumulators in scratch; the CTA that arrives
             // last at the tile's counter adds the slices in split order (so the sum does not
@@ -366,14 +287,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             float *mine = sk.partials + (tile * splits + blockIdx.z) * (size_t)(TOK * kTileN);
             if (ok) {
                 tc_fence_after();
-#pragma unroll 1
-                for (int c = group; c < TOK / 16; c += G) {
-                    uint32_t r[16];
-                    tc_ld16(tmem_base + lane_addr + c * 16, r);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) __stcg(mine + (c * 16 + i) * kTileN + row, __uint_as_float(r[i]));
-                }
+                dump_partials<TOK, G>(tmem_base, mine, group, quad, lane);
             }
             if (warp == 2) TRACE(3, 0, 2);  // partial sums written
             __threadfence();
@@ -387,7 +301,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             if (*s_is_last) {
                 __threadfence();
                 epilogue_tile<TOK, G, GATED, YT>(tmem_base, smem, group, quad, lane, ok, ops, y, extra, M, N, ldy, epilogue, n0,
-                                                 m0, PartialSums{sk.partials + tile * splits * (size_t)(TOK * kTileN), splits});
+                                                 m0, PartialSums{sk.partials + tile * splits * (size_t)(TOK * kTileN), splits, (size_t)(TOK * kTileN)});
                 named_bar_sync(1, 128 * G);
                 if (threadIdx.x == 64) sk.counters[tile] = 0;  // ready for the next launch
             }

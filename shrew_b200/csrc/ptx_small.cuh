@@ -51,6 +51,15 @@ __device__ __forceinline__ void mma_f16_16816(float *d, uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// One f32 from L2 (not kept in L1), as an instruction the compiler may not reorder or merge with its
+// neighbours: a run of these is issued back to back, so that all of them are in flight before the first
+// value is consumed.
+__device__ __forceinline__ float ld_cg_ordered(const float *p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 // system-scope release store / acquire load of one word (flags that another GPU reads or writes)
 __device__ __forceinline__ void st_release_sys_u32(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

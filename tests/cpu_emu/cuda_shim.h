@@ -290,7 +290,9 @@ static inline unsigned __byte_perm(unsigned x, unsigned y, unsigned sel) {
     return out;
 }
 #define __expf expf
+static inline float __fdividef(float a, float b) { return a / b; }
 static inline uint4 ld_stream_16(const void *p) { uint4 v; memcpy(&v, p, 16); return v; }
+static inline float ld_cg_ordered(const float *p) { return *p; }
 static inline void pdl_launch_dependents() {}   // launches are sequential here
 static inline void pdl_wait() {}
 static inline uint32_t pack_bf16x2_rn(float hi, float lo) {

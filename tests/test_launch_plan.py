@@ -55,7 +55,11 @@ def test_ragged_in_features_fall_back_to_the_general_kernel():
     (16, 64, 128, 4096, 11008))))
 def test_the_plan_covers_the_problem(M, N, K, gated):
     rc, name, p = plan(M, N, K, gated=gated)
-    assert (rc, name) == (0, "tcgen05")
+    assert rc == 0 and name in ("tcgen05", "tcgen05-2cta")
+    if name == "tcgen05-2cta":          # CTA pairs: at least a full wave of pair tiles, or half a wave over a long K
+        pair_tiles = -(-N // (128 if gated else 256)) * -(-M // 256)
+        assert M > 128 and (pair_tiles >= 64 or (pair_tiles >= 32 and K >= 8192))
+        return
     chan = 64 if gated else 128
     assert p["tok"] in (16, 32, 64, 128, 256)
     assert p["n_tiles"] == -(-N // chan)
@@ -82,9 +86,15 @@ def test_headline_shapes():
     assert plan(64, 11008, 4096)[2] == dict(tok=64, n_tiles=86, m_tiles=1, splits=1, rounds=32)
     # prefill: 128-token tiles until the grid is several waves deep, then 256
     assert plan(512, 4096, 4096)[2]["tok"] == 128
-    assert plan(2048, 4096, 4096)[2] == dict(tok=256, n_tiles=32, m_tiles=8, splits=1, rounds=64)
-    # gate and up halves share a tile: twice the channel tiles, 256 tokens above a batch of 128
-    assert plan(512, 11008, 4096, gated=1)[2] == dict(tok=256, n_tiles=172, m_tiles=2, splits=1, rounds=64)
+    assert plan(768, 4096, 4096)[2] == dict(tok=256, n_tiles=32, m_tiles=3, splits=1, rounds=64)
+    # the benchmark's block at batch 512 runs on CTA pairs: 172 pair tiles (gate/up), 32 pair tiles over K = 11008 (down)
+    assert plan(512, 11008, 4096, gated=1)[1] == "tcgen05-2cta"
+    assert plan(512, 4096, 11008)[1] == "tcgen05-2cta"
+    assert plan(512, 4096, 4096)[1] == "tcgen05"
+    assert plan(2048, 4096, 4096)[1] == "tcgen05-2cta"
+    # one rank's share of that block sharded over 4 GPUs stays on the single-CTA kernel: gate and up halves share a
+    # tile (twice the channel tiles), 256 tokens above a batch of 128
+    assert plan(512, 2752, 4096, gated=1) == (0, "tcgen05", dict(tok=256, n_tiles=43, m_tiles=2, splits=1, rounds=64))
     assert plan(128, 11008, 4096, gated=1)[2]["tok"] == 128
     # the down projection of a block sharded over 8 GPUs: 4 channel tiles x 4 token tiles, K split to fill the SMs
     p = plan(512, 512, 11008)[2]
