@@ -44,6 +44,13 @@ import torch  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
 
+# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures summarised under profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum; the capture's workload and command are in the file named):
+# (workload, kernel family, GPUs) -> bytes
+KNOWN_TRAFFIC = {
+    ("llama_mlp_m512", "tcgen05-2cta", 1): 152.3e6,   # profiles/tcgen05_pair_llama_mlp_m512.md: gate/up launch, 137.8 MB read + 14.4 MB written
+}
+
 WORKLOADS = {
     # name: (kind, M, dims...)
     "llama_mlp_m512": dict(kind="mlp", M=512, d_model=4096, d_ff=11008),
@@ -104,7 +111,7 @@ def run_quantize_reference(args, wl, name):
         "impl": "reference", "metric": "quantize_gb_per_s", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 -> int8 (f64 arithmetic)", "data": "synthetic",
-        "config": {"workload": name, **config_of(wl)},
+        "config": config_line(args, wl, name),
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
     return 0
@@ -171,9 +178,9 @@ def run_quantize_gpu(args, wl, name):
         "metric": "quantize_gb_per_s", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32 -> int8 (f32 with an exact f64 path for near-ties)", "data": "synthetic",
-        "config": {"workload": name, **config_of(wl), "granularity": "per-channel",
-                   "l2": f"ring of {ring} matrices ({ring * 4 * R * C / 1e6:.0f} MB of f32)"
-                         + (" > 2x L2" if ring * 4 * R * C > 2 * L2_BYTES else "")},
+        "config": config_line(args, wl, name),
+        "notes": {"l2": f"ring of {ring} matrices ({ring * 4 * R * C / 1e6:.0f} MB of f32)"
+                        + (" > 2x L2" if ring * 4 * R * C > 2 * L2_BYTES else "")},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * R * C, "d2h_bytes_per_step": R * C + 8 * R,
                 "steps": n_e2e},
         "gpu_launches": int(launches), "launch_mode": "host launches", "clocks": clocks,
@@ -193,6 +200,28 @@ def run_quantize_gpu(args, wl, name):
                                "kind": "port", "sample": f"{n} x " + sample}
     print(json.dumps(out), flush=True)
     return 0
+
+
+def host_threads():
+    """All host cores this process may use.  torchrun exports OMP_NUM_THREADS=1 to its workers, which would make the
+    CPU arm of a multi-GPU launch single-threaded: the CPU legs set the thread count themselves."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def config_line(args, wl, name):
+    """`config` of the JSON line: the same keys and values in both arms and at every GPU count (what differs between
+    runs of one workload is said in `notes`)."""
+    c = {"workload": name, **config_of(wl)}
+    if wl["kind"] != "quantize":
+        c["weights"] = f"INT8 {args.granularity.replace('_', '-')}, N(0,{wl.get('std', 0.02)})"
+    else:
+        c["granularity"] = "per-channel"
+    if getattr(args, "force_kernel", "auto") != "auto":
+        c["forced_kernel"] = args.force_kernel
+    return c
 
 
 def config_of(wl):
@@ -308,6 +337,7 @@ def cpu_step_factory(wl, per_tensor=False):
     GEMM on all cores (torch CPU as stand-in for the `gemm` crate), then bias / activation."""
     from oracle import shrew_oracle as oracle
     oracle.build()
+    torch.set_num_threads(host_threads())
     gran = oracle.PER_TENSOR if per_tensor else oracle.PER_CHANNEL
     M = wl["M"]
     rng = np.random.default_rng(1)
@@ -372,7 +402,7 @@ def run_reference_arm(args, wl, name):
         "impl": "reference", "metric": "quantized_linear_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, **config_of(wl), "weights": f"INT8 {args.granularity.replace('_', '-')}"},
+        "config": config_line(args, wl, name),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "Rust reference (shrew-cpu: gemm 0.18.2 + rayon) cannot be built on this image; this is the CPU port of "
@@ -430,18 +460,8 @@ def main():
         # far was made with it off
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
-        # A rank that waits for a peer that is gone would wait for ever (the device-side barrier of the fused exchange
-        # has no time limit of its own): after a generous wall-clock limit every rank says so and ends, so that the
-        # launcher is never left with a hung job.  A normal run takes a minute or two.
-        limit_s = float(os.environ.get("SHREWQ_BENCH_WATCHDOG_S", "1200"))
-
-        def give_up():
-            sys.stderr.write(f"bench: rank {rank} still running after {limit_s:.0f} s; giving up\n")
-            sys.stderr.flush()
-            os._exit(3)
-        watchdog = threading.Timer(limit_s, give_up)
-        watchdog.daemon = True
-        watchdog.start()
+        # (every device-side wait of the exchange is bounded: a rank whose peer is gone gets SHREWQ_ERR_TIMEOUT from
+        # its next synchronize instead of waiting for ever)
     sdev = Device.get(dev)
     if args.force_kernel != "auto":
         _lib.check(_lib.lib().shrewq_force_kernel(args.force_kernel.encode()), None)
@@ -579,6 +599,34 @@ def main():
             return outs[i % ring]
         return eager_step(i, x)
 
+    # ---- several GPUs: is what the ranks compute the layer's output?  (outside every timed region) ----
+    # Rank 0 builds the UNSPLIT layers from the same seeds and runs the one-GPU forward (the path the GPU parity tests hold
+    # against the oracle); every rank compares its own copy of the exchanged result with it.
+    parity = None
+    if world > 1 and not replicas and wl["kind"] in ("mlp", "linear"):
+        y_mine = step(0, x_static).float()
+        torch.cuda.synchronize()
+        y_ref = torch.empty_like(y_mine)
+        if rank == 0:
+            def full(n, k, seed):
+                return QuantizedLinear.from_linear(Linear(gpu_weight(n, k, seed, dev), None), cfg)
+            if wl["kind"] == "mlp":
+                g_f, u_f, d_f = full(dff, dm, 0), full(dff, dm, 1), full(dm, dff, 2)
+                y_ref.copy_(d_f.forward(g_f.forward_gate_up_silu(u_f, x_static)).float())
+                del g_f, u_f, d_f
+            else:
+                q_f = full(wl["N"], wl["K"], 0)
+                y_ref.copy_(q_f.forward(x_static).float())
+                del q_f
+            sdev.synchronize()
+        dist.broadcast(y_ref, src=0)
+        err = ((y_mine - y_ref).abs().max() / y_ref.abs().max().clamp_min(1e-30)).reshape(1)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        parity = {"max_rel_err_vs_one_gpu_forward": float(err.item()), "tolerance": 1e-2, "ok": bool(err.item() <= 1e-2),
+                  "checked": "every rank's copy of the exchanged output against rank 0's unsplit forward of the same weights"}
+        del y_ref, y_mine
+        torch.cuda.empty_cache()
+
     # ---- device-resident metric ----
     for i in range(args.warmup):
         step(i, x_static)
@@ -623,8 +671,57 @@ def main():
     if world > 1:
         dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
     e2e_value = rows_per_step * args.steps / float(t_e2e.item())
-    e2e_info = {"mode": "sequential: copy in, compute, copy out, synchronize, per step",
+    e2e_info = {"mode": "sequential: torch copy in, the device entry points, torch copy out, synchronize, per step",
                 "sequential_value": e2e_value}
+
+    # ---- end to end through the library's host-buffer entry points (one GPU): the call a host-tensor caller makes ----
+    # shrewq_mlp_forward_host / shrewq_linear_forward_host take pinned host x and deliver host y, copies and kernels
+    # inside the call.  Sequential = one synchronising call per step.  Pipelined (the block) = the same entry point
+    # asked not to synchronise: it keeps two staging slots and its own copy streams, so the copies of one step overlap
+    # the kernels of the next; every step still moves its x in and its y out inside the timed region.
+    if world == 1 and wl["kind"] in ("mlp", "linear"):
+        try:
+            from shrew_b200.quantize import mlp_forward_host
+            y_pins = [torch.empty_like(y_host).pin_memory() for _ in range(2)]
+
+            def abi_step(i, sync, out):
+                m = models[i % ring]
+                if wl["kind"] == "mlp":
+                    return mlp_forward_host(m.gate, m.up, m.down, x_host, out=out, synchronize=sync)
+                out.copy_(m.shard.forward_host(x_host))
+                return out
+            for i in range(3):
+                abi_step(i, True, y_pins[0])
+            y_ref = y_pins[0].clone()
+            t0 = time.perf_counter()
+            for i in range(args.steps):
+                abi_step(i, True, y_pins[i & 1])
+            abi_seq = M * args.steps / (time.perf_counter() - t0)
+            e2e_info.update({"abi_sequential_value": abi_seq,
+                             "abi_entry": "shrewq_mlp_forward_host" if wl["kind"] == "mlp" else "shrewq_linear_forward_host"})
+            e2e_value, e2e_info["mode"] = abi_seq, f"{e2e_info['abi_entry']}, one synchronising call per step"
+            if wl["kind"] == "mlp":
+                for i in range(4):
+                    abi_step(i, False, y_pins[i & 1])
+                sdev.synchronize()
+                same = all(torch.equal(yp, y_ref) for yp in y_pins) if ring == 1 else True
+                t0 = time.perf_counter()
+                for i in range(args.steps):
+                    abi_step(i, False, y_pins[i & 1])
+                sdev.synchronize()
+                abi_pipe = M * args.steps / (time.perf_counter() - t0)
+                e2e_info["abi_pipelined_value"] = abi_pipe
+                if same and abi_pipe > e2e_value:
+                    e2e_value = abi_pipe
+                    e2e_info["mode"] = ("shrewq_mlp_forward_host without a synchronise per call (two staging slots and copy streams "
+                                        "inside the library: the copies of a step overlap the kernels of its neighbours); "
+                                        "one synchronise after the last step")
+        except Exception as e:  # noqa: BLE001  (the torch-copy figure measured above stays)
+            sys.stderr.write(f"bench: end-to-end run through the host-buffer entry points failed ({e!r})\n")
+            try:
+                torch.cuda.synchronize()
+            except Exception:  # noqa: BLE001
+                pass
 
     # ---- dominant kernel alone, for the roofline ----
     peaks = measured_peaks()
@@ -694,68 +791,6 @@ def main():
             except Exception:  # noqa: BLE001  (the figures measured so far are still reported)
                 pass
 
-    # ---- end to end, pipelined: the copies of neighbouring steps overlap the compute ----
-    # (the last GPU measurement of the run: it is optional, and nothing after it needs the device)
-    # Every step still brings its input from pinned host memory and delivers its result to
-    # pinned host memory inside the timed region; the three phases of consecutive steps run
-    # on three streams (copy-in, compute, copy-out), at most two steps in flight.  One GPU
-    # only: on several GPUs the ring entries share one output buffer that peers write into.
-    # Any failure, or a result that differs from the sequential one, keeps the sequential figure.
-    if use_graphs and world == 1 and wl["kind"] != "stack":   # (a stack's ring entries share their output buffers)
-        try:
-            y_ref = y_host.clone()
-            ring_of = lambda i: i % ring  # noqa: E731
-            s_in, s_out, s_cmp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
-            x_stage = [torch.empty_like(x_static) for _ in range(2)]
-            y_pin = [torch.empty_like(y_host).pin_memory() for _ in range(2)]
-            ev_h2d = [torch.cuda.Event() for _ in range(2)]       # x_stage[j] filled
-            ev_used = [torch.cuda.Event() for _ in range(2)]      # x_stage[j] consumed by the compute stream
-            ev_cmp = [torch.cuda.Event() for _ in range(ring)]    # outs[r] complete
-            ev_d2h = [torch.cuda.Event() for _ in range(ring)]    # outs[r] copied out, free to be overwritten
-            ev_step = [torch.cuda.Event() for _ in range(2)]      # step's result is in y_pin[j]
-
-            def run_pipelined(n_steps):
-                for i in range(n_steps):
-                    j, r = i % 2, ring_of(i)
-                    with torch.cuda.stream(s_in):
-                        if i >= 2:
-                            s_in.wait_event(ev_used[j])
-                        x_stage[j].copy_(x_host, non_blocking=True)
-                        ev_h2d[j].record(s_in)
-                    s_cmp.wait_event(ev_h2d[j])
-                    x_static.copy_(x_stage[j], non_blocking=True)
-                    ev_used[j].record(s_cmp)
-                    if i >= ring:
-                        s_cmp.wait_event(ev_d2h[r])
-                    graphs[r].replay()
-                    ev_cmp[r].record(s_cmp)
-                    with torch.cuda.stream(s_out):
-                        s_out.wait_event(ev_cmp[r])
-                        if i >= 2:
-                            ev_step[j].synchronize()          # host: the result of step i-2 has been delivered
-                        y_pin[j].copy_(outs[r], non_blocking=True)
-                        ev_d2h[r].record(s_out)
-                        ev_step[j].record(s_out)
-                for j in range(2):
-                    ev_step[j].synchronize()
-                torch.cuda.synchronize()
-
-            run_pipelined(4)
-            if not (torch.equal(y_pin[0], y_ref) and torch.equal(y_pin[1], y_ref)):
-                raise RuntimeError("pipelined result differs from the sequential one")
-            t0 = time.perf_counter()
-            run_pipelined(args.steps)
-            dt = time.perf_counter() - t0
-            e2e_value = M * args.steps / dt
-            e2e_info["mode"] = ("pipelined: copy-in, compute and copy-out of consecutive steps overlap on three "
-                                "streams, at most two steps in flight; result checked against the sequential run")
-        except Exception as e:  # noqa: BLE001
-            sys.stderr.write(f"bench: pipelined end-to-end run failed ({e!r}); keeping the sequential figure\n")
-            try:
-                torch.cuda.synchronize()
-            except Exception:  # noqa: BLE001  (the figures measured so far are still reported)
-                pass
-
     # the sampler ran from the start of the device-resident timed region through the end-to-end and
     # kernel-alone timed regions: the device-resident one alone lasts ~10 ms, one nvidia-smi period
     clocks = sampler.stop() if rank == 0 else None
@@ -764,13 +799,15 @@ def main():
     if wl["kind"] == "stack":   # decided by the dominant layer's own arithmetic intensity
         tensor_bound = k_flops / (peaks["tc_sustained"] * 1e12) > k_bytes / (peaks["hbm"] * 1e9)
     if tensor_bound:
-        roof = {"bound": "tensor", "achieved": k_flops / k_s / 1e12 if k_s else None, "peak": peaks["tc_sustained"],
-                "unit": "TFLOP/s", "peak_burst": peaks["tc_burst"]}
+        # the kernel is timed alone, in bursts of a few milliseconds: the burst figure of the measured peaks is its denominator
+        roof = {"bound": "tensor", "achieved": k_flops / k_s / 1e12 if k_s else None, "peak": peaks["tc_burst"],
+                "unit": "TFLOP/s", "peak_sustained": peaks["tc_sustained"]}
     else:
         roof = {"bound": "hbm", "achieved": k_bytes / k_s / 1e9 if k_s else None, "peak": peaks["hbm"], "unit": "GB/s"}
     roof["frac"] = roof["achieved"] / roof["peak"] if k_s else None
-    roof.update({"traffic": None, "kernel": kernel_family, "kernel_us": k_s * 1e6 if k_s else None, "peaks": peaks["source"],
-                 "timing": k_timing})
+    roof.update({"traffic": KNOWN_TRAFFIC.get((args.workload, kernel_family, world)), "kernel": kernel_family,
+                 "kernel_us": k_s * 1e6 if k_s else None, "peaks": peaks["source"], "timing": k_timing,
+                 "algorithmic": (k_flops if tensor_bound else k_bytes)})
     if k_error:
         roof["error"] = k_error
 
@@ -778,14 +815,16 @@ def main():
         "metric": "quantized_linear_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "weak" if replicas else "strong", "vs_baseline": None, "dtype": ("f32" if wl["kind"] == "stack" else "bf16") + " x int8 -> f32 accumulate", "data": "synthetic",
-        "config": {"workload": args.workload, **({"forced_kernel": args.force_kernel} if args.force_kernel != "auto" else {}), **config_of(wl),
-                   "weights": f"INT8 {args.granularity.replace('_', '-')}, N(0,{wl.get('std', 0.02)})", "sharding": "none (single GPU)" if world == 1 else f"none: {world} independent replicas, each on its own batch of {M} rows, no collective" if replicas else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + device barrier" if fused else "NCCL all-gather"),
-                   "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU)" + (" > 2x L2" if ring * shard_bytes > 2 * L2_BYTES else "; the whole configuration is smaller than L2, so the weights stay L2-resident as they would in use")},
+        "config": config_line(args, wl, args.workload),
+        "notes": {"sharding": "none (single GPU)" if world == 1 else f"none: {world} independent replicas, each on its own batch of {M} rows, no collective" if replicas else f"output channels over {world} GPUs, " + ("all-gather fused into the kernel epilogue (peer stores) + the library's bounded device barrier" if fused else "NCCL all-gather"),
+                  "l2": f"ring of {ring} weight copies ({ring * shard_bytes / 1e6:.0f} MB per GPU)" + (" > 2x L2" if ring * shard_bytes > 2 * L2_BYTES else "; the whole configuration is smaller than L2, so the weights stay L2-resident as they would in use")},
         "tflops": flops_step * (world if replicas else 1) * args.steps / (ms_total * 1e-3) / 1e12,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * (world if replicas else 1),
                 "d2h_bytes_per_step": y_host.numel() * y_host.element_size() * (world if replicas else 1), **e2e_info},
         "gpu_launches": int(launches), "launch_mode": "cuda graph replay (one graph per ring entry)" if use_graphs else "host launches", "clocks": clocks, "roofline": roof,
     }
+    if parity is not None:
+        out["parity_checked"] = parity
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cstep, tokens, sample = cpu_step_factory(wl, args.granularity == "per_tensor")
         cstep()

@@ -278,6 +278,19 @@ SHREWQ_API int shrewq_linear_forward_gate_up_silu(shrewq_linear *gate, shrewq_li
                                        int x_dtype, size_t M, void *h_dev, int h_dtype, size_t ldh);
 
 /*
+ * The gated MLP block for a caller whose activations live in HOST memory: y = down( silu(gate(x)) * up(x) ), i.e.
+ * three <QuantizedLinear as Module>::forward calls (quantize.rs:463-476) with the tensor ops silu and mul between
+ * them, as a Llama-style block composes them.  x_host is [M, in_features] bf16, y_host [M, down.out_features] of
+ * y_dtype; the hidden activation stays on the device.  The call copies x in, runs the two kernels on the context's
+ * stream and copies y out, using two staging slots and two internal copy streams: with synchronize = 0 it returns as
+ * soon as the work is enqueued, and the copies of one call overlap the kernels of the next.  The caller then keeps
+ * x_host and y_host untouched (pinned memory, a y_host of its own per call in flight) until shrewq_ctx_synchronize,
+ * which also waits for the results of such calls.  With synchronize = 1 the result is in y_host on return.
+ */
+SHREWQ_API int shrewq_mlp_forward_host(shrewq_linear *gate, shrewq_linear *up, shrewq_linear *down, const void *x_host,
+                                       size_t M, void *y_host, int y_dtype, int synchronize);
+
+/*
  * Forward of a row shard with the all-gather fused into the epilogue (no counterpart in the
  * reference, whose `distributed.rs` is single-process).  The slice y[:, n0:n1] this shard
  * computes is stored into y_dev and, with the same element offsets, into each of the

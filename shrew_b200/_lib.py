@@ -47,6 +47,7 @@ SIGNATURES = {
     "shrewq_linear_destroy": (None, [_vp]),
     "shrewq_linear_forward": (_ci, [_vp, _vp, _ci, _sz, _vp, _ci, _sz, _ci]),
     "shrewq_linear_forward_host": (_ci, [_vp, _vp, _ci, _sz, _vp, _ci, _ci]),
+    "shrewq_mlp_forward_host": (_ci, [_vp, _vp, _vp, _vp, _sz, _vp, _ci, _ci]),
     "shrewq_linear_forward_noalloc": (_ci, [_vp, _vp, _sz, _vp, _ci, _sz, _ci]),
     "shrewq_linear_forward_peers": (_ci, [_vp, _vp, _vp, _ci, _sz, _vp, _pp, _ci, _ci, _sz, _ci]),
     "shrewq_linear_forward_gate_up_silu": (_ci, [_vp, _vp, _vp, _ci, _sz, _vp, _ci, _sz]),

@@ -152,6 +152,7 @@ int shrewq_ctx_synchronize(shrewq_ctx *ctx) {
     int rc = bind(ctx);
     if (rc != SHREWQ_OK) return rc;
     SHREWQ_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->copy_out) SHREWQ_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->copy_out));  // results of *_host calls in flight
     DeviceStatus st;
     SHREWQ_CUDA_TRY(ctx, cudaMemcpy(&st, ctx->dev_status, sizeof(st), cudaMemcpyDeviceToHost));
     if (st.timeout_flag) {
@@ -172,6 +173,14 @@ void shrewq_ctx_destroy(shrewq_ctx *ctx) {
     if (ctx->xsplit) cudaFree(ctx->xsplit);
     if (ctx->ytmp) cudaFree(ctx->ytmp);
     if (ctx->stage_pinned) cudaFreeHost(ctx->stage_pinned);
+    if (ctx->mlp_stage) cudaFree(ctx->mlp_stage);
+    for (int i = 0; i < 2; ++i) {
+        if (ctx->ev_in[i]) cudaEventDestroy(ctx->ev_in[i]);
+        if (ctx->ev_cmp[i]) cudaEventDestroy(ctx->ev_cmp[i]);
+        if (ctx->ev_out[i]) cudaEventDestroy(ctx->ev_out[i]);
+    }
+    if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+    if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     delete ctx;
 }
@@ -731,6 +740,61 @@ int shrewq_linear_forward_host(shrewq_linear *lin, const void *x_host, int x_dty
     if (rc != SHREWQ_OK) return rc;
     SHREWQ_CUDA_TRY(ctx, cudaMemcpyAsync(y_host, base + off_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
     return shrewq_ctx_synchronize(ctx);
+}
+
+int shrewq_mlp_forward_host(shrewq_linear *gate, shrewq_linear *up, shrewq_linear *down, const void *x_host, size_t M,
+                            void *y_host, int y_dtype, int synchronize) {
+    if (!gate || !up || !down) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "mlp_forward_host: a handle is NULL");
+    shrewq_ctx *ctx = gate->ctx;
+    if (up->ctx != ctx || down->ctx != ctx || up->n != gate->n || up->k != gate->k || down->k != gate->n)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG,
+                       "mlp_forward_host: gate and up must have one shape, down must take their width, all on one context");
+    if (y_dtype != SHREWQ_F32 && y_dtype != SHREWQ_BF16)
+        return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "mlp_forward_host: y_dtype must be SHREWQ_F32 or SHREWQ_BF16");
+    if (M == 0) return SHREWQ_OK;
+    if (!x_host || !y_host) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "mlp_forward_host: x / y is NULL");
+    int rc = bind(ctx);
+    if (rc != SHREWQ_OK) return rc;
+    if (!ctx->copy_in) {
+        SHREWQ_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+        SHREWQ_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            SHREWQ_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
+            SHREWQ_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_cmp[i], cudaEventDisableTiming));
+            SHREWQ_CUDA_TRY(ctx, cudaEventCreateWithFlags(&ctx->ev_out[i], cudaEventDisableTiming));
+        }
+    }
+    const size_t xb = align_up(M * gate->k * 2, 256), hb = align_up(M * gate->n * 2, 256);
+    const size_t yb = align_up(M * down->n * (y_dtype == SHREWQ_BF16 ? 2 : 4), 256), slot_bytes = xb + hb + yb;
+    if (ctx->mlp_stage_bytes < 2 * slot_bytes) {
+        // (growing synchronises everything that may still use the old slots)
+        if (ctx->copy_out) SHREWQ_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->copy_out));
+        if ((rc = grow(ctx, &ctx->mlp_stage, &ctx->mlp_stage_bytes, 2 * slot_bytes, false)) != SHREWQ_OK) return rc;
+        ctx->mlp_calls = 0;
+    }
+    const int slot = (int)(ctx->mlp_calls & 1);
+    const bool reused = ctx->mlp_calls >= 2;
+    ctx->mlp_calls += 1;
+    char *base = static_cast<char *>(ctx->mlp_stage) + (size_t)slot * (ctx->mlp_stage_bytes / 2 / 256 * 256);
+    char *x_dev = base, *h_dev = base + xb, *y_dev = base + xb + hb;
+    // copy-in: after the kernels of the call two back have read this slot's x
+    if (reused) SHREWQ_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->ev_cmp[slot], 0));
+    SHREWQ_CUDA_TRY(ctx, cudaMemcpyAsync(x_dev, x_host, M * gate->k * 2, cudaMemcpyHostToDevice, ctx->copy_in));
+    SHREWQ_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_in[slot], ctx->copy_in));
+    // kernels on the context's stream: after this call's x has landed and the slot's previous y has left
+    SHREWQ_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_in[slot], 0));
+    if (reused) SHREWQ_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_out[slot], 0));
+    rc = forward_impl(gate, up, x_dev, SHREWQ_BF16, M, h_dev, SHREWQ_BF16, gate->n, SHREWQ_EPILOGUE_NONE, "mlp_forward_host");
+    if (rc != SHREWQ_OK) return rc;
+    rc = forward_impl(down, nullptr, h_dev, SHREWQ_BF16, M, y_dev, y_dtype, down->n, SHREWQ_EPILOGUE_NONE, "mlp_forward_host");
+    if (rc != SHREWQ_OK) return rc;
+    SHREWQ_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_cmp[slot], ctx->stream));
+    // copy-out
+    SHREWQ_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->ev_cmp[slot], 0));
+    SHREWQ_CUDA_TRY(ctx, cudaMemcpyAsync(y_host, y_dev, M * down->n * (y_dtype == SHREWQ_BF16 ? 2 : 4), cudaMemcpyDeviceToHost,
+                                         ctx->copy_out));
+    SHREWQ_CUDA_TRY(ctx, cudaEventRecord(ctx->ev_out[slot], ctx->copy_out));
+    return synchronize ? shrewq_ctx_synchronize(ctx) : SHREWQ_OK;
 }
 
 }  // extern "C"

@@ -43,6 +43,13 @@ struct shrewq_ctx {
     size_t scratch_bytes = 0;
     // split-K tile counters live in scratch; they are zeroed once and reset by the kernels
     bool counters_zeroed = false;
+    // the gated block's host-buffer entry point: two staging slots and two copy streams, so that the copies of
+    // one call overlap the kernels of its neighbours (created on first use)
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_cmp[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+    void *mlp_stage = nullptr;
+    size_t mlp_stage_bytes = 0;
+    uint64_t mlp_calls = 0;
     // staging for the *_host entry points
     void *stage_dev = nullptr;
     size_t stage_dev_bytes = 0;

@@ -501,6 +501,28 @@ class QuantizedLinear:
                 f"bits={self.weight_q.config.bits.name}, compression={self.weight_q.compression_ratio():.1f}x)")
 
 
+def mlp_forward_host(gate: "QuantizedLinear", up: "QuantizedLinear", down: "QuantizedLinear", x: torch.Tensor,
+                     out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                     synchronize: bool = True) -> torch.Tensor:
+    """down(silu(gate(x)) * up(x)) for HOST activations (shrewq_mlp_forward_host): x is a CPU bf16 tensor
+    [M, in_features], the result a CPU tensor [M, down.out_features].  synchronize=False returns once the work is
+    enqueued (x and out pinned and left alone until Device.synchronize()); consecutive calls then overlap their
+    copies with each other's kernels."""
+    if x.device.type != "cpu" or x.dtype is not torch.bfloat16 or x.dim() != 2 or x.shape[1] != gate.in_features:
+        raise ShrewError(_lib.ERR_INVALID_ARG, f"mlp_forward_host: expected a CPU bf16 tensor [M,{gate.in_features}]")
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty((x.shape[0], down.out_features), dtype=out_dtype or x.dtype)
+    if out.device.type != "cpu" or out.dtype not in _DTYPE_CODE or not out.is_contiguous() or \
+            list(out.shape) != [x.shape[0], down.out_features]:
+        raise ShrewError(_lib.ERR_INVALID_ARG, "mlp_forward_host: bad output buffer")
+    gate.device.bind_stream()
+    rc = _lib.lib().shrewq_mlp_forward_host(gate._h, up._h, down._h, _ptr(x), x.shape[0], _ptr(out), _DTYPE_CODE[out.dtype],
+                                            1 if synchronize else 0)
+    _lib.check(rc, gate.device.handle)
+    return out
+
+
 # ---- model-level helpers (quantize.rs:500-586) ------------------------------------------------------
 def quantize_named_parameters(module, config: QuantConfig, batched: bool = True) -> List[Tuple[str, QuantizedTensor]]:
     """Every parameter of rank >= 2 is quantized — including a Linear's [1,out] bias, which

@@ -348,3 +348,31 @@ def test_forward_from_host_buffers(oracle, M, N, K, dtype):
     q = ql.weight_q.data.cpu().numpy().reshape(N, K)
     ref = oracle.np_linear_forward(q, ql.weight_q.scales.cpu().numpy(), 1, b, x_np, relu=True)
     assert oracle.rel_err(y_host.float().numpy(), ref) < (TOL_BF16 if dtype == "bf16" else TOL_F32)
+
+
+def test_gated_block_from_host_buffers(oracle):
+    # shrewq_mlp_forward_host: host x in, host y out; synchronising calls and the pipelined form (no synchronise per
+    # call, results after Device.synchronize) must both give the device entry points' bits
+    from shrew_b200.quantize import Device, mlp_forward_host
+    gate, _, _ = _make(1408, 512, 1, seed=0, bias=False)
+    up, _, _ = _make(1408, 512, 1, seed=1, bias=False)
+    down, _, _ = _make(512, 1408, 1, seed=2, bias=False)
+    xs = [_x(300, 512, "bf16", seed=s)[0] for s in range(5)]
+    refs = [down.forward(gate.forward_gate_up_silu(up, x)).cpu() for x in xs]
+    torch.cuda.synchronize()
+    for x, ref in zip(xs[:2], refs):
+        assert torch.equal(mlp_forward_host(gate, up, down, x.cpu()), ref)
+    x_pins = [x.cpu().pin_memory() for x in xs]
+    y_pins = [torch.empty_like(refs[0]).pin_memory() for _ in xs]
+    for xp, yp in zip(x_pins, y_pins):                      # five calls in flight over two staging slots
+        mlp_forward_host(gate, up, down, xp, out=yp, synchronize=False)
+    Device.get("cuda:0").synchronize()
+    for yp, ref in zip(y_pins, refs):
+        assert torch.equal(yp, ref)
+    q = [l.weight_q.data.cpu().numpy().reshape(l.out_features, l.in_features) for l in (gate, up, down)]
+    sc = [l.weight_q.scales.cpu().numpy() for l in (gate, up, down)]
+    xn = xs[0].float().cpu().numpy()
+    g, u = oracle.np_linear_forward(q[0], sc[0], 1, None, xn), oracle.np_linear_forward(q[1], sc[1], 1, None, xn)
+    h = ((g / (1.0 + np.exp(-g.astype(np.float64)))).astype(np.float32) * u)
+    h16 = torch.from_numpy(h).to(torch.bfloat16).float().numpy()
+    assert oracle.rel_err(refs[0].float().numpy(), oracle.np_linear_forward(q[2], sc[2], 1, None, h16)) < TOL_BF16
