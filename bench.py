@@ -562,6 +562,34 @@ def main():
     def eager_step(i, x):
         return models[i % ring].forward(x)
 
+    # ---- several GPUs: is what the ranks compute the layer's output?  (outside every timed region) ----
+    # Rank 0 builds the UNSPLIT layers from the same seeds and runs the one-GPU forward (the path the GPU parity tests hold
+    # against the oracle); every rank compares its own copy of the exchanged result with it.
+    parity = None
+    if world > 1 and not replicas and wl["kind"] in ("mlp", "linear"):
+        y_mine = eager_step(0, x_dev).float()
+        torch.cuda.synchronize()
+        y_ref = torch.empty_like(y_mine)
+        if rank == 0:
+            def full(n, k, seed):
+                return QuantizedLinear.from_linear(Linear(gpu_weight(n, k, seed, dev), None), cfg)
+            if wl["kind"] == "mlp":
+                g_f, u_f, d_f = full(dff, dm, 0), full(dff, dm, 1), full(dm, dff, 2)
+                y_ref.copy_(d_f.forward(g_f.forward_gate_up_silu(u_f, x_dev)).float())
+                del g_f, u_f, d_f
+            else:
+                q_f = full(wl["N"], wl["K"], 0)
+                y_ref.copy_(q_f.forward(x_dev).float())
+                del q_f
+            sdev.synchronize()
+        dist.broadcast(y_ref, src=0)
+        err = ((y_mine - y_ref).abs().max() / y_ref.abs().max().clamp_min(1e-30)).reshape(1)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        parity = {"max_rel_err_vs_one_gpu_forward": float(err.item()), "tolerance": 1e-2, "ok": bool(err.item() <= 1e-2),
+                  "checked": "every rank's copy of the exchanged output against rank 0's unsplit forward of the same weights"}
+        del y_ref, y_mine
+        torch.cuda.empty_cache()
+
     # One CUDA graph per ring entry: a step is a handful of short kernels (and, on several
     # GPUs, device-side barriers), so replaying a captured graph removes the host launch
     # path from the measurement.  x_static is the graph's input buffer, outs[i] its result.
@@ -598,34 +626,6 @@ def main():
             graphs[i % ring].replay()
             return outs[i % ring]
         return eager_step(i, x)
-
-    # ---- several GPUs: is what the ranks compute the layer's output?  (outside every timed region) ----
-    # Rank 0 builds the UNSPLIT layers from the same seeds and runs the one-GPU forward (the path the GPU parity tests hold
-    # against the oracle); every rank compares its own copy of the exchanged result with it.
-    parity = None
-    if world > 1 and not replicas and wl["kind"] in ("mlp", "linear"):
-        y_mine = step(0, x_static).float()
-        torch.cuda.synchronize()
-        y_ref = torch.empty_like(y_mine)
-        if rank == 0:
-            def full(n, k, seed):
-                return QuantizedLinear.from_linear(Linear(gpu_weight(n, k, seed, dev), None), cfg)
-            if wl["kind"] == "mlp":
-                g_f, u_f, d_f = full(dff, dm, 0), full(dff, dm, 1), full(dm, dff, 2)
-                y_ref.copy_(d_f.forward(g_f.forward_gate_up_silu(u_f, x_static)).float())
-                del g_f, u_f, d_f
-            else:
-                q_f = full(wl["N"], wl["K"], 0)
-                y_ref.copy_(q_f.forward(x_static).float())
-                del q_f
-            sdev.synchronize()
-        dist.broadcast(y_ref, src=0)
-        err = ((y_mine - y_ref).abs().max() / y_ref.abs().max().clamp_min(1e-30)).reshape(1)
-        dist.all_reduce(err, op=dist.ReduceOp.MAX)
-        parity = {"max_rel_err_vs_one_gpu_forward": float(err.item()), "tolerance": 1e-2, "ok": bool(err.item() <= 1e-2),
-                  "checked": "every rank's copy of the exchanged output against rank 0's unsplit forward of the same weights"}
-        del y_ref, y_mine
-        torch.cuda.empty_cache()
 
     # ---- device-resident metric ----
     for i in range(args.warmup):

@@ -19,8 +19,8 @@
  *    the first time a call needs more than it holds; a call that would have to grow one while its
  *    stream is being captured fails with SHREWQ_ERR_UNSUPPORTED instead of breaking the capture —
  *    make the same call once outside the capture first.
- *    A captured graph holds the workspace address it was captured with: a later call on the same context that
- *    grows the workspace (a larger shape) frees that address, so graphs captured before must be re-captured.
+ *    A workspace that is outgrown is kept until the context is destroyed (a graph captured earlier still launches
+ *    kernels with its address), so graphs stay valid when a later call needs a larger workspace.
  *  - Device entry points enqueue work on the context's stream and return without
  *    synchronising.  Host entry points (suffix _host) copy in, run, copy out and
  *    synchronise the stream before returning.
@@ -95,7 +95,12 @@ SHREWQ_API int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream);
  *   "tc_tailsplit" 0/1    issue a short last wave as a second launch split along K (default 0)
  *   "tc_pair"      0..2   CTA pairs (tcgen05.mma.cta_group::2) for batches above 128 tokens: 0 never, 1 where
  *                         they win by measurement (default), 2 always
- *   "gemv_pdl"     0/1    programmatic dependent launch of the small-batch kernel (default 0)
+ *   "gemv_pdl"     0/1    programmatic dependent launch of the small-batch kernels (default 1): from a handle's
+ *                         second forward on, a forward of up to 16 tokens may request its WEIGHTS while the
+ *                         previous kernel of the stream still runs; it reads activations and writes outputs only
+ *                         after that kernel has completed.  The first forward of a handle is always fully
+ *                         ordered behind the stream, so weights quantized on the same stream just before are
+ *                         complete; a caller that rewrites a handle's weights in place LATER must set 0.
  * Unknown names and values out of range return SHREWQ_ERR_INVALID_ARG. */
 SHREWQ_API int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value);
 SHREWQ_API int shrewq_ctx_synchronize(shrewq_ctx *ctx);
@@ -338,12 +343,14 @@ SHREWQ_API size_t shrewq_linear_in_features(const shrewq_linear *lin);
 SHREWQ_API size_t shrewq_linear_out_features(const shrewq_linear *lin);
 SHREWQ_API size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin);
 
-/* Name of the kernel family the calling thread's latest forward dispatched to ("gemv", "mma", "tcgen05",
- * "tcgen05-2cta", "tcgen05-f32", "simt", "mma-w4"); for tests and benchmarks.  Kept per thread, not in the
- * handle, so that a forward writes nothing to the handle it reads. */
+/* Name of the kernel family the calling thread's latest forward dispatched to ("gemv", "mma", "mma-ring",
+ * "tcgen05", "tcgen05-2cta", "tcgen05-f32", "simt", "mma-w4"); for tests and benchmarks.  Kept per thread, not
+ * in the handle: the one thing a forward writes to the handle it reads is an atomic flag saying that a
+ * forward has been enqueued. */
 SHREWQ_API const char *shrewq_linear_last_kernel(const shrewq_linear *lin);
 /* Forces the kernel family used by forwards issued from the calling thread: "gemv" (CUDA cores, M <= 16),
- * "mma" (warp-level MMA, M <= 64), "tcgen05" (single-CTA tensor-core kernel), "tcgen05-2cta" (CTA pairs,
+ * "mma" (warp-level MMA, weights streamed through registers, M <= 64), "mma-ring" (warp-level MMA, weights
+ * streamed through a shared-memory ring by bulk copies, M <= 32), "tcgen05" (single-CTA tensor-core kernel), "tcgen05-2cta" (CTA pairs,
  * tcgen05.mma.cta_group::2), "tcgen05-f32" (f32 activations as a bf16 hi/lo pair on the tensor cores),
  * "simt" (general f32 kernel), or "auto"/NULL to restore the built-in choice.  A forced kernel that
  * cannot take a shape makes the forward fail with SHREWQ_ERR_UNSUPPORTED (it never falls

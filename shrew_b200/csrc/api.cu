@@ -28,14 +28,14 @@ static int grow(shrewq_ctx *ctx, void **p, size_t *have, size_t want, bool pinne
         return set_err(ctx, SHREWQ_ERR_UNSUPPORTED,
                        "this call needs %zu bytes of library workspace (have %zu) and cannot allocate while its stream is "
                        "being captured: make the same call once outside the capture first", want, *have);
-    // work already enqueued may still use the old buffer
-    SHREWQ_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    // Work already enqueued, and graphs captured earlier, may still use the old buffer: it is retired, not freed
+    // (sizes grow geometrically, so the retired buffers together stay below the live one).
     if (*p) {
-        if (pinned) cudaFreeHost(*p); else cudaFree(*p);
+        ctx->retired.emplace_back(*p, pinned);
         *p = nullptr;
         *have = 0;
     }
-    size_t sz = want + want / 4 + 4096;
+    size_t sz = want + want / 2 + 4096;
     cudaError_t e = pinned ? cudaMallocHost(p, sz) : cudaMalloc(p, sz);
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -69,7 +69,7 @@ static int bind(shrewq_ctx *ctx) {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceTcF32, kForceTc2Cta };
+enum ForcedKernel { kAuto = 0, kForceGemv, kForceTc, kForceSimt, kForceMma, kForceTcF32, kForceTc2Cta, kForceRing };
 
 }  // namespace shrewq
 
@@ -174,6 +174,9 @@ void shrewq_ctx_destroy(shrewq_ctx *ctx) {
     if (ctx->ytmp) cudaFree(ctx->ytmp);
     if (ctx->stage_pinned) cudaFreeHost(ctx->stage_pinned);
     if (ctx->mlp_stage) cudaFree(ctx->mlp_stage);
+    for (auto &r : ctx->retired) {
+        if (r.second) cudaFreeHost(r.first); else cudaFree(r.first);
+    }
     for (int i = 0; i < 2; ++i) {
         if (ctx->ev_in[i]) cudaEventDestroy(ctx->ev_in[i]);
         if (ctx->ev_cmp[i]) cudaEventDestroy(ctx->ev_cmp[i]);
@@ -190,11 +193,17 @@ const char *shrewq_last_error(const shrewq_ctx *ctx) { return ctx ? ctx->err : g
 uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx) { return ctx ? ctx->launches.load() : 0; }
 
 // The default kernel family of a forward with bf16 activations: the one rule, shared by forward_impl and
-// shrewq_plan_forward.  Measured on 4096 x 4096: the CUDA-core GEMV wins up to 2 tokens, the warp-MMA kernel
-// from 3 to 32, the tcgen05 kernel above.
-static int default_family(size_t M, bool gemv_ok, bool mma_ok, bool tc_ok) {
+// shrewq_plan_forward.  Measured on 4096 x 4096, 11008 x 4096 and 4096 x 11008: the CUDA-core GEMV wins up to 2
+// tokens, a warp-MMA kernel from 3 to 32, the tcgen05 kernel above.  Of the two warp-MMA kernels the ring kernel
+// (bulk copies into shared memory) wins up to 16 tokens while all its CTAs are resident at once (two per SM), the
+// register-streaming one otherwise.
+static bool ring_kernel_wins(size_t M, size_t N, bool gated, int sm_count) {
+    const size_t ctas = (N + (gated ? 7 : 15)) / (gated ? 8 : 16);
+    return M >= 3 && M <= 16 && ctas <= (size_t)2 * sm_count;
+}
+static int default_family(size_t M, size_t N, bool gated, int sm_count, bool gemv_ok, bool mma_ok, bool tc_ok) {
     if (gemv_ok && (M <= 2 || (!mma_ok && (M <= 4 || !tc_ok)))) return kForceGemv;
-    if (mma_ok && M <= 32) return kForceMma;
+    if (mma_ok && M <= 32) return ring_kernel_wins(M, N, gated, sm_count) ? kForceRing : kForceMma;
     return tc_ok ? kForceTc : (gemv_ok ? kForceGemv : kForceSimt);
 }
 
@@ -219,10 +228,10 @@ int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, 
     const bool small = M < (1u << 31) && N < (1u << 31) && K < (1u << 31);
     const bool tc_ok = x_is_bf16 && vec16 && M >= 1 && small;
     const bool mma_ok = x_is_bf16 && (K % 64) == 0 && M <= 64 && small;
-    int fam = default_family(M, vec16 && M <= 16, mma_ok, tc_ok);
+    int fam = default_family(M, N, gated != 0, sm_count, vec16 && M <= 16, mma_ok, tc_ok);
     if (!x_is_bf16 && vec16 && small && M > 16 && !gated) fam = kForceTcF32;   // f32 activations: the hi/lo tensor-core pass
     if (fam == kForceTc && M > 128 && pair_kernel_wins(M, N, K, gated != 0)) fam = kForceTc2Cta;
-    const char *name = fam == kForceGemv ? "gemv" : fam == kForceMma ? "mma" : fam == kForceTc ? "tcgen05"
+    const char *name = fam == kForceGemv ? "gemv" : fam == kForceMma ? "mma" : fam == kForceRing ? "mma-ring" : fam == kForceTc ? "tcgen05"
                        : fam == kForceTc2Cta ? "tcgen05-2cta" : fam == kForceTcF32 ? "tcgen05-f32" : "simt";
     snprintf(kernel, kernel_len, "%s", name);
     if (!strcmp(name, "tcgen05"))
@@ -236,6 +245,7 @@ int shrewq_force_kernel(const char *name) {
     else if (!strcmp(name, "tcgen05")) g_forced_kernel = kForceTc;
     else if (!strcmp(name, "simt")) g_forced_kernel = kForceSimt;
     else if (!strcmp(name, "mma")) g_forced_kernel = kForceMma;
+    else if (!strcmp(name, "mma-ring")) g_forced_kernel = kForceRing;
     else if (!strcmp(name, "tcgen05-f32")) g_forced_kernel = kForceTcF32;
     else if (!strcmp(name, "tcgen05-2cta")) g_forced_kernel = kForceTc2Cta;
     else return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "force_kernel: unknown kernel '%s'", name);
@@ -583,6 +593,8 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
         a.extra.p[i] = peers[i];
     }
     a.extra.n = n_peers;
+    a.pdl = ctx->tuning.gemv_pdl != 0 && lin->forwarded.load(std::memory_order_relaxed) &&
+            (!up || up->forwarded.load(std::memory_order_relaxed));
 
     // Packed INT4 rows: only the warp-MMA forward reads them (batch <= 32 for now)
     if (lin->int4_packed || (up && up->int4_packed)) {
@@ -638,6 +650,9 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             if (!tc_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05 cannot take this shape/dtype", who);
             choice = kForceTc; break;
         case kForceSimt: choice = kForceSimt; break;
+        case kForceRing:
+            if (!gemv_ring_supported(a)) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced mma-ring kernel cannot take this shape/dtype", who);
+            choice = kForceRing; break;
         case kForceMma:
             if (!mma_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced mma kernel cannot take this shape/dtype", who);
             choice = kForceMma; break;
@@ -649,12 +664,13 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             } else if (M > 128 && tc_ok && (ctx->tuning.tc_pair == 2 || (ctx->tuning.tc_pair == 1 && pair_kernel_wins(M, lin->n, lin->k, up != nullptr)))) {
                 choice = kForceTc2Cta;
             } else {
-                choice = default_family(M, gemv_ok, mma_ok, tc_ok);
+                choice = default_family(M, lin->n, up != nullptr, ctx->sm_count, gemv_ok, mma_ok, tc_ok);
             }
     }
     const char *name;
     if (choice == kForceGemv) { rc = launch_gemv(ctx, a); name = "gemv"; }
     else if (choice == kForceMma) { rc = launch_gemv_mma(ctx, a); name = "mma"; }
+    else if (choice == kForceRing) { rc = launch_gemv_ring(ctx, a); name = "mma-ring"; }
     else if (choice == kForceTc) {
         rc = up ? launch_gemm_tcgen05(ctx, a, lin->w_tmap64, up->w_tmap64) : launch_gemm_tcgen05(ctx, a, lin->w_tmap, nullptr);
         name = "tcgen05";
@@ -669,6 +685,10 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
         rc = launch_gemm_simt(ctx, a); name = "simt";
     }
     g_last_kernel = name;
+    if (rc == SHREWQ_OK) {
+        lin->forwarded.store(true, std::memory_order_relaxed);
+        if (up) up->forwarded.store(true, std::memory_order_relaxed);
+    }
     if (zp_route && rc == SHREWQ_OK)
         rc = launch_zero_point_fix(ctx, zp_acc, lin->czp, zp_xsum, M, lin->n, ldy, epilogue == SHREWQ_EPILOGUE_RELU, y_dtype, y_dev);
     return rc;

@@ -7,6 +7,7 @@
 
 #include <atomic>
 #include <cstdarg>
+#include <vector>
 #include <cstdio>
 #include <cstring>
 
@@ -25,7 +26,7 @@ struct Tuning {
     int tc_tok_gated = 0;   // the same for gate/up launches only
     int tc_tailsplit = 0;   // issue a short last wave as a second launch split along K
     int tc_pair = 1;        // CTA pairs (tcgen05.mma.cta_group::2) for large batches: 0 never, 1 where they win, 2 whenever M > 128
-    int gemv_pdl = 0;       // programmatic dependent launch of the small-batch kernels
+    int gemv_pdl = 1;       // programmatic dependent launch of the small-batch kernels (after a handle's first forward)
 };
 
 }  // namespace shrewq
@@ -61,6 +62,9 @@ struct shrewq_ctx {
     // f32 [M,N] accumulators + per-token activation sums of a forward through zero points
     void *ytmp = nullptr;
     size_t ytmp_bytes = 0;
+    // Workspaces that were outgrown: kept until the context is destroyed, because a CUDA graph captured earlier
+    // still launches kernels with their addresses (device pointers, and pinned host pointers with the flag set)
+    std::vector<std::pair<void *, bool>> retired;
     // device status block + pinned mirror
     shrewq::DeviceStatus *dev_status = nullptr;
 };
@@ -79,6 +83,9 @@ struct shrewq_linear {
     alignas(64) unsigned char w_tmap[128];
     alignas(64) unsigned char w_tmap64[128];
     bool tmap_ok = false;
+    // a forward of this handle has been enqueued: its weights, scales and bias are then older than every later
+    // kernel of the stream, which is what lets later small-batch forwards prefetch them early
+    std::atomic<bool> forwarded{false};
 };
 
 namespace shrewq {
@@ -133,12 +140,17 @@ struct ForwardArgs {
     const float *scales_up = nullptr;
     const float *bias_up = nullptr;
     Dests extra = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0};
+    // launch with programmatic stream serialization: the kernel may fetch WEIGHTS before the previous kernel of the
+    // stream has completed (set only when the weights are known to be older than that kernel)
+    bool pdl = false;
 };
 
 int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a);
 int launch_gemm_simt(shrewq_ctx *ctx, const ForwardArgs &a);
 bool gemv_mma_supported(const ForwardArgs &a);
 int launch_gemv_mma(shrewq_ctx *ctx, const ForwardArgs &a);
+bool gemv_ring_supported(const ForwardArgs &a);
+int launch_gemv_ring(shrewq_ctx *ctx, const ForwardArgs &a);
 bool gemv_mma_w4_supported(const ForwardArgs &a);
 int launch_gemv_mma_w4(shrewq_ctx *ctx, const ForwardArgs &a);
 int launch_pack_int4(shrewq_ctx *ctx, const int8_t *q, size_t n_pairs, uint8_t *packed);

@@ -53,14 +53,13 @@ __device__ __forceinline__ bool exchange_reached(const uint32_t *p, uint32_t epo
 }
 
 __global__ void __launch_bounds__(32) exchange_barrier_kernel(ExchangeArgs a, DeviceStatus *status) {
-    __shared__ uint32_t s_epoch;
     uint32_t *mine = a.flags[a.rank];
+    uint32_t epoch = 0;
     if (threadIdx.x == 0) {
-        s_epoch = mine[kEpochWord] + 1;
-        mine[kEpochWord] = s_epoch;
+        epoch = mine[kEpochWord] + 1;
+        mine[kEpochWord] = epoch;
     }
-    __syncthreads();
-    const uint32_t epoch = s_epoch;
+    epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);  // one warp: no shared memory needed
     const int r = (int)threadIdx.x;
     if (r >= a.world || r == a.rank) return;
     fence_sys();

@@ -1,8 +1,11 @@
 // Launchers of the CUDA-core GEMV (device code and its description: gemv_kernels.cuh).
 #include <cstdlib>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "gemv_kernels.cuh"
+#include "gemv_stream_kernels.cuh"
 
 namespace shrewq {
 namespace {
@@ -14,7 +17,7 @@ void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     // Option gemv_pdl launches the PDL variant of the kernel with programmatic stream
     // serialization: back-to-back GEMVs overlap launch latency, prologue and the first weight
     // loads with the tail of the kernel before.
-    const bool pdl = ctx->tuning.gemv_pdl != 0;
+    const bool pdl = a.pdl;
     if (pdl) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
@@ -45,6 +48,41 @@ void dispatch_m(shrewq_ctx *ctx, const ForwardArgs &a) {
     else launch_one<16, 2, XT, YT, GATED>(ctx, a);
 }
 
+// ---- the ring kernel (1..32 tokens, bf16 activations): bulk copies into a shared-memory ring + warp MMA ----
+template <int NT, typename YT, bool GATED>
+int launch_ring_one(shrewq_ctx *ctx, const ForwardArgs &a) {
+    constexpr int NCH = GATED ? kRingRows / 2 : kRingRows;
+    constexpr size_t kSmem = RingCfg<kRingKC>::kSmemBytes;
+    auto kern = gemv_i8_ring_kernel<NT, kRingKC, kRingConsumers, YT, GATED>;
+    static std::atomic<unsigned long long> attr_done{0};  // per instantiation: bit d = device d has the attribute
+    const int d = ctx->device;
+    if (d < 0 || d >= 64 || !((attr_done.load(std::memory_order_acquire) >> d) & 1ull)) {
+        SHREWQ_CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem));
+        if (d >= 0 && d < 64) attr_done.fetch_or(1ull << d, std::memory_order_release);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((a.N + NCH - 1) / NCH));
+    cfg.blockDim = dim3((kRingConsumers + 1) * 32);
+    cfg.dynamicSmemBytes = kSmem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    SHREWQ_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up,
+                                            static_cast<const uint16_t *>(a.x), static_cast<YT *>(a.y), a.extra, (int)a.M,
+                                            (int)a.N, (int)a.K, a.ldy, a.epilogue, ctx->dev_status));
+    return SHREWQ_OK;
+}
+
+template <typename YT, bool GATED>
+int launch_ring_m(shrewq_ctx *ctx, const ForwardArgs &a) {
+    if (a.M <= 8) return launch_ring_one<1, YT, GATED>(ctx, a);
+    if (a.M <= 16) return launch_ring_one<2, YT, GATED>(ctx, a);
+    return launch_ring_one<4, YT, GATED>(ctx, a);
+}
+
 }  // namespace
 
 int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a) {
@@ -63,6 +101,26 @@ int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a) {
     else if (!xb && !yb) SHREWQ_GEMV_CASE(float, float);
     else SHREWQ_GEMV_CASE(float, __nv_bfloat16);
 #undef SHREWQ_GEMV_CASE
+    ctx->launches += 1;
+    SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
+    return SHREWQ_OK;
+}
+
+bool gemv_ring_supported(const ForwardArgs &a) {
+    return a.x_dtype == SHREWQ_BF16 && a.M >= 1 && a.M <= 32 && a.K >= 64 && (a.K % 64) == 0 &&
+           (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0 &&
+           (!a.q_up || (reinterpret_cast<uintptr_t>(a.q_up) & 15) == 0) && a.N <= 0x7FFFFFFF && a.K <= 0x7FFFFFFF;
+}
+
+int launch_gemv_ring(shrewq_ctx *ctx, const ForwardArgs &a) {
+    if (a.M == 0 || a.N == 0) return SHREWQ_OK;
+    if (!gemv_ring_supported(a))
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "ring gemv: needs bf16 activations, M <= 32, K a multiple of 64, 16-byte alignment");
+    const bool gated = a.q_up != nullptr;
+    int rc;
+    if (a.y_dtype == SHREWQ_BF16) rc = gated ? launch_ring_m<__nv_bfloat16, true>(ctx, a) : launch_ring_m<__nv_bfloat16, false>(ctx, a);
+    else rc = gated ? launch_ring_m<float, true>(ctx, a) : launch_ring_m<float, false>(ctx, a);
+    if (rc != SHREWQ_OK) return rc;
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;

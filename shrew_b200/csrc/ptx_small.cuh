@@ -27,6 +27,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float hi, float lo) {
 }
 
 // per-half f16 subtraction a - b
+// (a0, a1) += (b0, b1) as one packed f32x2 instruction (sm_100: half the issue slots of two scalar adds)
+__device__ __forceinline__ void add_f32x2(float &a0, float &a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\tadd.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(a0), "+f"(a1)
+        : "f"(b0), "f"(b1));
+}
+
 __device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));

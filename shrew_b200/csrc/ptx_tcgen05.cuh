@@ -42,6 +42,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int 
         : "memory");
 }
 
+// 1-D bulk copy global -> shared memory (16-byte aligned addresses, size a multiple of 16), bytes counted on the mbarrier
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

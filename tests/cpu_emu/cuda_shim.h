@@ -295,6 +295,7 @@ static inline uint4 ld_stream_16(const void *p) { uint4 v; memcpy(&v, p, 16); re
 static inline float ld_cg_ordered(const float *p) { return *p; }
 static inline void pdl_launch_dependents() {}   // launches are sequential here
 static inline void pdl_wait() {}
+static inline void add_f32x2(float &a0, float &a1, float b0, float b1) { a0 += b0; a1 += b1; }
 static inline uint32_t pack_bf16x2_rn(float hi, float lo) {
     return ((uint32_t)__float2bfloat16_rn(hi).bits << 16) | __float2bfloat16_rn(lo).bits;
 }

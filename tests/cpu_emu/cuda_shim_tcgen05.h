@@ -139,6 +139,16 @@ inline void tma_progress() {
 }
 }  // namespace emu
 
+// cp.async.bulk (1-D): `bytes` from global memory to shared memory, counted on the barrier
+static inline void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    EMU_CHECK((dst & 15u) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (bytes & 15u) == 0, "bulk copy: 16-byte alignment and size");
+    memcpy(emu::smem_ptr(dst), src, bytes);
+    std::lock_guard<std::mutex> g(emu::g_mbar_mu);
+    auto *b = reinterpret_cast<emu::MBar *>(emu::smem_ptr(bar));
+    b->tx -= (int32_t)bytes;
+    emu::mbar_settle(b);
+}
+
 static inline void tma_load_2d(uint32_t dst, const void *tmap_v, int c0, int c1, uint32_t bar) {
     const CUtensorMap &tm = *static_cast<const CUtensorMap *>(tmap_v);
     if (emu::g_tma_count.fetch_add(1) == emu::g_drop_tma.load()) return;  // injected fault: this load never lands

@@ -70,7 +70,7 @@ def test_null_handles_are_rejected_not_crashed(shrewq):
     assert L.shrewq_quantize_f32_given_amax(None, None, 1, None, None, None) == shrewq.ERR_INVALID_ARG
     assert L.shrewq_linear_create_ex(None, None, None, None, None, 1, 1, 0, ctypes.byref(out)) == shrewq.ERR_INVALID_ARG
     assert L.shrewq_linear_forward_noalloc(None, None, 1, None, 0, 1, 0) == shrewq.ERR_INVALID_ARG
-    for kind in (b"gemv", b"tcgen05", b"simt", b"mma", b"tcgen05-f32", b"tcgen05-2cta", b"auto"):
+    for kind in (b"gemv", b"tcgen05", b"simt", b"mma", b"mma-ring", b"tcgen05-f32", b"tcgen05-2cta", b"auto"):
         assert L.shrewq_force_kernel(kind) == shrewq.OK
 
 

@@ -981,9 +981,66 @@ def test_gemv_matches_oracle(oracle, emu_cc, M, x_bf16):
     assert oracle.rel_err(y[:, :N], ref) < 2e-6 and np.all(y[:, N:] == 7.0)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("y_bf16", [0, 1], ids=["f32-out", "bf16-out"])
+@pytest.mark.parametrize("N,K,kc", [(37, 576, 512), (20, 64 * 137, 512), (20, 64 * 137, 1024), (18, 64 * 137, 2048), (5, 64, 1024)],
+                         ids=["one-partial-stage", "ring-reused-512", "ring-reused-1024", "ring-reused-2048", "one-k-block"])
+def test_ring_kernel_matches_oracle(oracle, emu_cc, M, y_bf16, N, K, kc):
+    # bulk copies into the ring + warp MMA: ragged last CTA (rows clamped), a last stage shorter than 512 codes, a
+    # K longer than the ring (8 stages of 512: slots are reused through the empty barriers), a row pitch wider
+    # than N, relu; several sizes of bulk copy (the launcher instantiates 2048)
+    rng = np.random.default_rng(M + K)
+    q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
+    scales = rng.random(N) * 1e-2 + 1e-4
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    bits, xb = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, xb, relu=True)
+    emu_cc.emu_set_ring_kc(kc)
+    try:
+        y = _cc_forward(emu_cc, 2, q, scales, bias, bits, 1, y_bf16, relu=True, ldy=N + 1)
+    finally:
+        emu_cc.emu_set_ring_kc(2048)
+    if y_bf16:
+        assert oracle.rel_err((y[:, :N].astype(np.uint32) << 16).view(np.float32), ref) < 1e-2 and np.all(y[:, N:] == 0x4100)
+    else:
+        assert oracle.rel_err(y[:, :N], ref) < 2e-6 and np.all(y[:, N:] == 7.0)
+
+
+@pytest.mark.parametrize("M", [3, 12])
+def test_ring_kernel_gate_up_and_peer_destinations(oracle, emu_cc, M):
+    rng = np.random.default_rng(14 + M)
+    N, K = 50, 1280
+    qg, qu = (rng.integers(-127, 128, size=(N, K)).astype(np.int8) for _ in range(2))
+    sg, su = rng.random(N) * 1e-2 + 1e-4, rng.random(N) * 1e-2 + 1e-4
+    bg, bu = ((rng.standard_normal(N) * 0.1).astype(np.float32) for _ in range(2))
+    bits, xb = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    g = oracle.np_linear_forward(qg, sg, 1, bg, xb).astype(np.float64)
+    u = oracle.np_linear_forward(qu, su, 1, bu, xb).astype(np.float64)
+    ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    peers = [np.full((M, N), 5.0, np.float32) for _ in range(7)]
+    arr = (ctypes.c_void_p * 7)(*[p.ctypes.data for p in peers])
+    emu_cc.emu_set_peers(arr, 7)
+    try:
+        y = _cc_forward(emu_cc, 2, qg, sg, bg, bits, 1, 0, up=(qu, su, bu))
+    finally:
+        emu_cc.emu_set_peers(None, 0)
+    for buf in [y] + peers:
+        assert oracle.rel_err(buf, ref) < 1e-5
+
+
+def test_ring_kernel_refuses_what_its_launcher_would(emu_cc):
+    q = _aligned((4, 96), np.int8); q[...] = 1
+    x = _aligned((33, 96), np.uint16); x[...] = 0x3F80
+    s = np.ones(4, np.float32); y = np.zeros((33, 4), np.float32)
+    args = (_p(q), _p(s), None, None, None, None, _p(x), _p(y))
+    assert emu_cc.emu_forward_cuda_cores(2, *args, 33, 4, 64, 4, 0, 1, 0, 0) == -1   # more than 32 tokens
+    assert emu_cc.emu_forward_cuda_cores(2, *args, 1, 4, 96, 4, 0, 1, 0, 0) == -1    # K not a multiple of 64
+    assert emu_cc.emu_forward_cuda_cores(2, *args, 1, 4, 64, 4, 0, 0, 0, 0) == -1    # f32 activations
+
+
 @pytest.mark.parametrize("M,K", [(1, 16 * 296), (4, 16 * 130), (8, 16 * 128), (2, 16 * 5)])
 def test_gemv_pdl_variant_gives_the_same_bits(oracle, emu_cc, M, K):
-    # SHREWQ_GEMV_PDL (not yet run on a GPU): the first weights are fetched before the wait for the
+    # the programmatic-dependent-launch variant: the first weights are fetched before the wait for the
     # previous kernel, the remaining chunks in the usual loop; same operations in the same order
     rng = np.random.default_rng(K)
     N = 9

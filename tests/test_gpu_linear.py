@@ -266,7 +266,55 @@ def test_mma_small_batch_parity(oracle, M, N, K):
     _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, force="mma")
 
 
-@pytest.mark.parametrize("kind", ["mma"])
+@pytest.mark.parametrize("M,N,K", [(1, 523, 1024), (5, 16, 64), (8, 4096, 4096), (16, 4096, 4096), (23, 300, 1088), (32, 1000, 11008),
+                                   (3, 4096, 11008)])
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_ring_kernel_small_batch_parity(oracle, M, N, K, pdl):
+    # bulk copies into the shared-memory ring + warp MMA: one partial stage, a ring reused several times (K = 11008 is
+    # 5.4 stages of 2048 over 3 slots), ragged last CTA; twice, so that the second forward runs with programmatic
+    # dependent launch when the option is on (the first forward of a handle never does)
+    from shrew_b200.quantize import Device
+    dev = Device.get("cuda:0")
+    ql, w, b = _make(N, K, 1, seed=N + K)
+    x_t, x_np = _x(M, K, "bf16", seed=M)
+    dev.set_option("gemv_pdl", pdl)
+    try:
+        _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, force="mma-ring")
+        _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, relu=True, force="mma-ring")
+    finally:
+        dev.set_option("gemv_pdl", 1)
+
+
+def test_small_batch_chain_with_dependent_launch(oracle):
+    # h = relu(x W1^T), y = h W2^T back to back on one stream, ten times: with programmatic dependent launch the second
+    # kernel requests its weights while the first still runs and must not read h early, nor may the next
+    # iteration's first kernel overwrite h while the second still reads it
+    from shrew_b200 import _lib
+    from shrew_b200.quantize import Device
+    for force, M in (("gemv", 2), ("mma-ring", 8)):
+        l1, w1, b1 = _make(2048, 1024, 1, seed=1)
+        l2, w2, b2 = _make(1024, 2048, 1, seed=2)
+        xs = [_x(M, 1024, "bf16", seed=10 + i) for i in range(10)]
+        h = torch.empty(M, 2048, dtype=torch.bfloat16, device="cuda")
+        ys = [torch.empty(M, 1024, dtype=torch.float32, device="cuda") for _ in range(10)]
+        _lib.lib().shrewq_force_kernel(force.encode())
+        try:
+            for (x_t, _), y in zip(xs, ys):
+                l1.forward(x_t, out=h, epilogue=_lib.EPILOGUE_RELU)
+                l2.forward(h, out=y)
+            Device.get("cuda:0").synchronize()
+        finally:
+            _lib.lib().shrewq_force_kernel(b"auto")
+        q1 = l1.weight_q.data.cpu().numpy().reshape(2048, 1024)
+        q2 = l2.weight_q.data.cpu().numpy().reshape(1024, 2048)
+        for (_, x_np), y in zip(xs, ys):
+            h_ref = oracle.np_linear_forward(q1, l1.weight_q.scales.cpu().numpy(), 1, b1, x_np, relu=True)
+            h_bf = torch.from_numpy(h_ref).to(torch.bfloat16).float().numpy()
+            ref = oracle.np_linear_forward(q2, l2.weight_q.scales.cpu().numpy(), 1, b2, h_bf)
+            assert oracle.rel_err(y.cpu().numpy(), ref) < TOL_BF16
+
+
+@pytest.mark.parametrize("kind", ["mma", "mma-ring"])
 def test_mma_gated_parity(oracle, kind):
     from shrew_b200 import _lib
     from shrew_b200.quantize import Device

@@ -55,6 +55,36 @@ def test_noalloc_matches_allocating_forward_twice(M, N, K):
         L.shrewq_force_kernel(b"auto")
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 1024, 4096), (300, 384, 1024)])
+def test_noalloc_leaves_free_device_memory_unchanged(M, N, K):
+    # the claim itself: once the module is loaded (the first call may load it), a call allocates nothing on the
+    # device.  cudaMemGetInfo (torch.cuda.mem_get_info) before and after a run of warmed calls must agree, with
+    # every input and output allocated beforehand.
+    from shrew_b200 import _lib
+    from shrew_b200.quantize import Device
+    L = _lib.lib()
+    dev = Device.get("cuda:0")
+    ql = _make(N, K, seed=3)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+
+    def call():
+        dev.bind_stream()
+        _lib.check(L.shrewq_linear_forward_noalloc(ql._h, ctypes.c_void_p(x.data_ptr()), M, ctypes.c_void_p(y.data_ptr()),
+                                                   _lib.BF16, N, _lib.EPILOGUE_NONE), dev.handle)
+
+    call()                                  # warm: module load, function attributes
+    dev.synchronize()
+    torch.cuda.synchronize()
+    free_before, total = torch.cuda.mem_get_info()
+    for _ in range(5):
+        call()
+    dev.synchronize()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"free device memory changed by {free_before - free_after} bytes of {total}"
+
+
 def test_noalloc_refuses_shapes_beyond_its_scratch_and_wrong_inputs():
     from shrew_b200 import _lib
     from shrew_b200.quantize import Device
