@@ -48,7 +48,10 @@ L2_BYTES = 126 * 1024 * 1024
 # (dram__bytes_read.sum + dram__bytes_write.sum; the capture's workload and command are in the file named):
 # (workload, kernel family, GPUs) -> bytes
 KNOWN_TRAFFIC = {
-    ("llama_mlp_m512", "tcgen05-2cta", 1): 152.3e6,   # profiles/tcgen05_pair_llama_mlp_m512.md: gate/up launch, 137.8 MB read + 14.4 MB written
+    ("llama_mlp_m512", "tcgen05-2cta", 1): 151.4e6,   # profiles/tcgen05_pair_llama_mlp_m512.md: gate/up launch, 136.5 MB read + 14.9 MB written
+    ("linear4096_m1", "gemv", 1): 16.81e6,            # profiles/gemv_linear4096_m1.md: the codes once; the 8 KB of output stay in L2
+    ("linear4096_m16", "mma-ring", 1): 16.95e6,       # profiles/mma_ring_linear4096_m16.md
+    ("quantize_8192x8192", "quantize_rows_reg", 1): 306.6e6,   # profiles/quantize_rows_reg_8192x8192.md: 268.5 MB read + 38.1 MB written (the rest of the 67 MB still in L2)
 }
 
 WORKLOADS = {
@@ -185,7 +188,8 @@ def run_quantize_gpu(args, wl, name):
                 "steps": n_e2e},
         "gpu_launches": int(launches), "launch_mode": "host launches", "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm"], "unit": "GB/s", "frac": value / peaks["hbm"],
-                     "traffic": None, "kernel": "quantize_rows_reg" if C % 4 == 0 and C <= 32768 else "quantize_rows_generic",
+                     "traffic": KNOWN_TRAFFIC.get((name, "quantize_rows_reg", 1)),
+                     "kernel": "quantize_rows_reg" if C % 4 == 0 and C <= 32768 else "quantize_rows_generic",
                      "kernel_us": ms / args.steps * 1e3, "peaks": peaks["source"],
                      "timing": "CUDA events around the timed steps (one launch per step)"},
     }

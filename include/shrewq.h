@@ -348,7 +348,8 @@ SHREWQ_API size_t shrewq_linear_memory_savings_bytes(const shrewq_linear *lin);
  * in the handle: the one thing a forward writes to the handle it reads is an atomic flag saying that a
  * forward has been enqueued. */
 SHREWQ_API const char *shrewq_linear_last_kernel(const shrewq_linear *lin);
-/* Forces the kernel family used by forwards issued from the calling thread: "gemv" (CUDA cores, M <= 16),
+/* Forces the kernel family used by forwards issued from the calling thread: "gemv" (CUDA cores, M <= 16; up to 128 in
+ * slices of 16 tokens),
  * "mma" (warp-level MMA, weights streamed through registers, M <= 64), "mma-ring" (warp-level MMA, weights
  * streamed through a shared-memory ring by bulk copies, M <= 32), "tcgen05" (single-CTA tensor-core kernel), "tcgen05-2cta" (CTA pairs,
  * tcgen05.mma.cta_group::2), "tcgen05-f32" (f32 activations as a bf16 hi/lo pair on the tensor cores),

@@ -31,7 +31,7 @@ def _stale(target: str, deps: list[str]) -> bool:
 
 def build_library(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
     """trace=True builds libshrewq_trace.so: the same library with -DSHREWQ_TRACE, whose
-    tcgen05 kernel stamps clock64() per pipeline role and stage (see kernel_bench trace)."""
+    tcgen05 kernel stamps clock64() per pipeline role and stage."""
     if trace:
         return _build(os.path.join(CSRC, "build_trace"), os.path.join(HERE, "libshrewq_trace.so"),
                       FLAGS + ["-DSHREWQ_TRACE"], force, verbose)

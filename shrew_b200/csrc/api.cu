@@ -197,6 +197,13 @@ uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx) { return ctx ? ctx->laun
 // tokens, a warp-MMA kernel from 3 to 32, the tcgen05 kernel above.  Of the two warp-MMA kernels the ring kernel
 // (bulk copies into shared memory) wins up to 16 tokens while all its CTAs are resident at once (two per SM), the
 // register-streaming one otherwise.
+// f32 activations on SMALL layers (config 1: 784 -> 256 -> 10 at 64 tokens): the whole forward is a few MFLOP and
+// what counts is the number and latency of launches; the CUDA-core GEMV in slices of 16 tokens is one short launch
+// where the tensor-core route is a split pass plus a pipelined kernel that never fills.
+constexpr size_t kGemvSlicedMaxTokens = 128;
+static bool gemv_slices_win(size_t M, size_t N, size_t K) {
+    return M > 16 && M <= kGemvSlicedMaxTokens && M * N * K <= ((size_t)1 << 26);
+}
 static bool ring_kernel_wins(size_t M, size_t N, bool gated, int sm_count) {
     const size_t ctas = (N + (gated ? 7 : 15)) / (gated ? 8 : 16);
     return M >= 3 && M <= 16 && ctas <= (size_t)2 * sm_count;
@@ -230,6 +237,7 @@ int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, 
     const bool mma_ok = x_is_bf16 && (K % 64) == 0 && M <= 64 && small;
     int fam = default_family(M, N, gated != 0, sm_count, vec16 && M <= 16, mma_ok, tc_ok);
     if (!x_is_bf16 && vec16 && small && M > 16 && !gated) fam = kForceTcF32;   // f32 activations: the hi/lo tensor-core pass
+    if (!x_is_bf16 && vec16 && small && gemv_slices_win(M, N, K)) fam = kForceGemv;
     if (fam == kForceTc && M > 128 && pair_kernel_wins(M, N, K, gated != 0)) fam = kForceTc2Cta;
     const char *name = fam == kForceGemv ? "gemv" : fam == kForceMma ? "mma" : fam == kForceRing ? "mma-ring" : fam == kForceTc ? "tcgen05"
                        : fam == kForceTc2Cta ? "tcgen05-2cta" : fam == kForceTcF32 ? "tcgen05-f32" : "simt";
@@ -630,6 +638,7 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
                        (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 &&
                        (!up || (reinterpret_cast<uintptr_t>(up->q) & 15) == 0);
     const bool gemv_ok = vec16 && M <= 16;
+    const bool gemv_sliced_ok = vec16 && gemv_slices_win(M, lin->n, lin->k);
     const bool tc_ok = tcgen05_supported(a) && lin->tmap_ok && (!up || up->tmap_ok);
     const bool mma_ok = gemv_mma_supported(a);
     // f32 activations as bf16 hi + lo on the tensor cores (plain layers only)
@@ -637,7 +646,8 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
     int choice;
     switch (g_forced_kernel) {
         case kForceGemv:
-            if (!gemv_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced gemv cannot take this shape", who);
+            if (!gemv_ok && !(vec16 && M <= kGemvSlicedMaxTokens))
+                return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced gemv cannot take this shape", who);
             choice = kForceGemv; break;
         case kForceTc2Cta:
             if (!tc_ok) return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "%s: forced tcgen05-2cta cannot take this shape/dtype", who);
@@ -660,7 +670,7 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
             if (x_dtype == SHREWQ_F32) {
                 // a few tokens: the GEMV reads f32 activations directly; beyond, the tensor cores on the
                 // bf16 hi/lo pair; the general f32 kernel takes what neither can (misaligned, odd widths)
-                choice = gemv_ok ? kForceGemv : f32_tc_ok ? kForceTcF32 : kForceSimt;
+                choice = (gemv_ok || gemv_sliced_ok) ? kForceGemv : f32_tc_ok ? kForceTcF32 : kForceSimt;
             } else if (M > 128 && tc_ok && (ctx->tuning.tc_pair == 2 || (ctx->tuning.tc_pair == 1 && pair_kernel_wins(M, lin->n, lin->k, up != nullptr)))) {
                 choice = kForceTc2Cta;
             } else {

@@ -5,7 +5,7 @@
 
 #include "common.cuh"
 #include "gemv_kernels.cuh"
-#include "gemv_stream_kernels.cuh"
+#include "gemv_ring_kernels.cuh"
 
 namespace shrewq {
 namespace {
@@ -13,14 +13,16 @@ namespace {
 template <int MT, int R, typename XT, typename YT, bool GATED>
 void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     constexpr int NR = GATED ? R / 2 : R;
-    const unsigned grid = (unsigned)((a.N + NR - 1) / NR);
+    // batches above MT tokens run as slices of MT tokens along grid.y (small layers with f32 activations: the
+    // weights come from L2 for every slice but the first)
+    const dim3 grid((unsigned)((a.N + NR - 1) / NR), (unsigned)((a.M + MT - 1) / MT));
     // Option gemv_pdl launches the PDL variant of the kernel with programmatic stream
     // serialization: back-to-back GEMVs overlap launch latency, prologue and the first weight
     // loads with the tail of the kernel before.
     const bool pdl = a.pdl;
     if (pdl) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
+        cfg.gridDim = grid;
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = 0;
         cfg.stream = ctx->stream;
@@ -87,8 +89,8 @@ int launch_ring_m(shrewq_ctx *ctx, const ForwardArgs &a) {
 
 int launch_gemv(shrewq_ctx *ctx, const ForwardArgs &a) {
     if (a.M == 0 || a.N == 0) return SHREWQ_OK;
-    if (a.M > 16 || (a.K % 16) != 0 || a.K == 0 || a.N > 0x7FFFFFFF || a.K > 0x7FFFFFFF)
-        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "gemv: needs M<=16 and K a positive multiple of 16");
+    if (a.M > 128 || (a.K % 16) != 0 || a.K == 0 || a.N > 0x7FFFFFFF || a.K > 0x7FFFFFFF)
+        return set_err(ctx, SHREWQ_ERR_UNSUPPORTED, "gemv: needs M<=128 and K a positive multiple of 16");
     const bool gated = a.q_up != nullptr;
     const bool xb = a.x_dtype == SHREWQ_BF16, yb = a.y_dtype == SHREWQ_BF16;
 #define SHREWQ_GEMV_CASE(XT, YT)                       \

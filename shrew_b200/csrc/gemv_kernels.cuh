@@ -86,6 +86,10 @@ gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                size_t ldy, int epilogue) {
     constexpr int NR = GATED ? R / 2 : R;  // distinct output columns per CTA
     if constexpr (PDL) pdl_launch_dependents();
+    // grid.y > 1: this CTA's slice of MT tokens (batches above MT on small layers)
+    const int mb = (int)blockIdx.y * MT;
+    x += (size_t)mb * K;
+    M = M - mb < MT ? M - mb : MT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * NR;
     const int chunks = K >> 4;
@@ -186,8 +190,8 @@ gemv_i8_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
             out = s * scales[n] + (bias ? bias[n] : 0.0f);
             if (epilogue == SHREWQ_EPILOGUE_RELU) out = fmaxf(out, 0.0f);
         }
-        store_y<YT>(y + (size_t)m * ldy + n, out);
-        for (int d = 0; d < extra.n; ++d) store_y<YT>(static_cast<YT *>(extra.p[d]) + (size_t)m * ldy + n, out);
+        store_y<YT>(y + (size_t)(mb + m) * ldy + n, out);
+        for (int d = 0; d < extra.n; ++d) store_y<YT>(static_cast<YT *>(extra.p[d]) + (size_t)(mb + m) * ldy + n, out);
     }
 }
 

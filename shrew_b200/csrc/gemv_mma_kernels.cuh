@@ -1,8 +1,7 @@
 // Weight-only INT8 forward for small batches (M <= 64) on warp-level MMA, sm_100a.
 //
-// STATUS: built and compiled, its index arithmetic is checked on the CPU
-// (tests/test_mma_layout.py emulates the fragment layouts), but it has NOT yet run on a GPU.
-// It is never chosen automatically; shrewq_force_kernel("mma") selects it.
+// The default for 3..32 tokens where the ring kernel (gemv_ring_kernels.cuh) does not win; also the forward of
+// packed INT4 weights.  Its index arithmetic is also checked on the CPU (tests/test_mma_layout.py).
 //
 // Why it exists: for 4 < M <= 64 the layer is HBM-bound, but the tcgen05 kernel feeds the
 // tensor core from ONE issuing thread per CTA (about 80 cycles per instruction, each covering

@@ -15,8 +15,6 @@
 // The arithmetic is that of quantize_kernels.cuh (make_params, quant_one), so codes and scales are the
 // same bits as the one-tensor kernels produce, which are the reference's.
 //
-// STATUS: built, run on the CPU stand-in against the one-tensor kernels; NOT yet run on a GPU.
-//
 // Device code only (no launch syntax, no runtime calls): it also compiles as plain C++ against the CUDA
 // stand-in of the CPU tests (tests/cpu_emu/).
 #pragma once

@@ -1,10 +1,6 @@
 // Quantize / dequantize in the reference's other modes: asymmetric INT8, INT4 symmetric and
 // asymmetric (one code per byte, as the reference stores them), sm_100a.
 //
-// STATUS: compiled, checked against the CPU restatement only by reading; NOT yet run on a GPU.
-// Reachable only when the environment sets SHREWQ_EXPERIMENTAL_MODES=1; otherwise the entry
-// points answer SHREWQ_ERR_UNSUPPORTED for anything but INT8 symmetric.
-//
 // Reference semantics (crates/shrew/src/quantize.rs), all in f64 on a widened copy:
 //   qmax = 127 | 7;  qmin = -127 | -7 (symmetric), -128 | -8 (asymmetric)          (:124-139)
 //   symmetric : scale = amax < 1e-30 ? 1 : amax / qmax,  zp = 0                     (:349-352)

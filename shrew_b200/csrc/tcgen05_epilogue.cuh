@@ -219,14 +219,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_d, uint8_t *stage_ba
             }
         }
         named_bar_sync(2 + group, 128);  // the staging tile is complete
-        if (ok) {
+        if (ok && vec_ok) {
 #pragma unroll
             for (int p = t; p < PIECES; p += 128) {
                 const int tr = p / PPR, seg = p % PPR;
                 const int m = m0 + c * CW + tr, nn = n0 + seg * EPV;
                 if (m < M && nn < N) {
                     const size_t off = (size_t)m * ldy + nn;
-                    if (vec_ok && nn + EPV <= N) {
+                    if (nn + EPV <= N) {
                         const uint4 w = *reinterpret_cast<const uint4 *>(stage + tr * RB + seg * 16);
                         *reinterpret_cast<uint4 *>(y + off) = w;
                         for (int d = 0; d < extra.n; ++d) *reinterpret_cast<uint4 *>(static_cast<YT *>(extra.p[d]) + off) = w;
@@ -237,6 +237,20 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tmem_d, uint8_t *stage_ba
                             for (int d = 0; d < extra.n; ++d) static_cast<YT *>(extra.p[d])[off + e] = w;
                         }
                     }
+                }
+            }
+        } else if (ok) {
+            // rows that do not start on 16-byte boundaries (e.g. 50257 f32 channels): element stores, consecutive
+            // threads on consecutive channels of one token, so that every store instruction writes whole sectors
+#pragma unroll 4
+            for (int e = t; e < CW * CH; e += 128) {
+                const int tr = e / CH, cn = e % CH;
+                const int m = m0 + c * CW + tr, nn = n0 + cn;
+                if (m < M && nn < N) {
+                    const size_t off = (size_t)m * ldy + nn;
+                    const YT w = out_st[tr * CH + cn];
+                    y[off] = w;
+                    for (int d = 0; d < extra.n; ++d) static_cast<YT *>(extra.p[d])[off] = w;
                 }
             }
         }

@@ -215,7 +215,7 @@ def quantize_tensor(tensor: torch.Tensor, config: QuantConfig) -> QuantizedTenso
 def quantize_tensors(tensors: Sequence[torch.Tensor], config: QuantConfig) -> List[QuantizedTensor]:
     """`quantize_tensor` for many tensors in a few launches in all (shrewq_quantize_f32_batch): what a model
     of many small matrices needs, where a launch per tensor costs more than the data.  F32 CUDA tensors on
-    one device, INT8 symmetric; same codes and scales as `quantize_tensor`.  Not yet run on a GPU."""
+    one device, INT8 symmetric; same codes and scales as `quantize_tensor`."""
     if not tensors:
         return []
     if not config._is_int8_symmetric():

@@ -4,7 +4,7 @@
 #include "cuda_shim.h"
 #include "cuda_shim_tcgen05.h"
 #include "../../shrew_b200/csrc/gemv_kernels.cuh"
-#include "../../shrew_b200/csrc/gemv_stream_kernels.cuh"
+#include "../../shrew_b200/csrc/gemv_ring_kernels.cuh"
 #include "../../shrew_b200/csrc/gemm_simt_kernels.cuh"
 
 using namespace shrewq;
@@ -25,16 +25,16 @@ struct Args {
 template <int MT, int R, typename XT, typename YT, bool GATED>
 void gemv_one(const Args &a) {
     constexpr int NR = GATED ? R / 2 : R;
-    const unsigned grid = (unsigned)((a.N + NR - 1) / NR);
+    const unsigned grid = (unsigned)((a.N + NR - 1) / NR), gy = (unsigned)((a.M + MT - 1) / MT);  // as launch_one
     // pdl: the variant that fetches its first weights before waiting for the previous kernel
     if (a.pdl)
-        emu::launch(grid, kThreads, [&] {
+        emu::launch3(grid, gy, 1, kThreads, 0, [&] {
             gemv_i8_kernel<MT, R, XT, YT, GATED, true>(a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up,
                                                        static_cast<const XT *>(a.x), static_cast<YT *>(a.y), g_peers, a.M, a.N,
                                                        a.K, a.ldy, a.epilogue);
         });
     else
-        emu::launch(grid, kThreads, [&] {
+        emu::launch3(grid, gy, 1, kThreads, 0, [&] {
             gemv_i8_kernel<MT, R, XT, YT, GATED>(a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const XT *>(a.x),
                                                  static_cast<YT *>(a.y), g_peers, a.M, a.N, a.K, a.ldy, a.epilogue);
         });
@@ -102,7 +102,7 @@ extern "C" void emu_set_peers(void **p, int n) {
     g_peers.n = n;
 }
 
-// kernel: 0 = gemv (M <= 16, K % 16 == 0, 16-byte aligned q and x), 1 = general f32 kernel, 2 = ring kernel
+// kernel: 0 = gemv (M <= 128, in slices of 16 tokens above 16; K % 16 == 0, 16-byte aligned q and x), 1 = general f32 kernel, 2 = ring kernel
 // (bf16 activations, M <= 32, K % 64 == 0, same alignment).
 // x_bf16 / y_bf16: element types.  Returns -1 for a shape the launcher refuses.
 extern "C" int emu_forward_cuda_cores(int kernel, const int8_t *q, const float *scales, const float *bias, const int8_t *q_up,
@@ -110,7 +110,7 @@ extern "C" int emu_forward_cuda_cores(int kernel, const int8_t *q, const float *
                                       size_t ldy, int epilogue, int x_bf16, int y_bf16, int pdl) {
     const Args a{q, q_up, scales, bias, scales_up, bias_up, x, y, M, N, K, ldy, epilogue, pdl};
     if (kernel == 0) {
-        if (M < 1 || M > 16 || K % 16 != 0 || K == 0 || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
+        if (M < 1 || M > 128 || K % 16 != 0 || K == 0 || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
         if (x_bf16 && y_bf16) gemv_g<__nv_bfloat16, __nv_bfloat16>(a);
         else if (x_bf16) gemv_g<__nv_bfloat16, float>(a);
         else if (!y_bf16) gemv_g<float, float>(a);

@@ -7,9 +7,8 @@ activation_f16.cuh; their PTX instructions sit behind ptx_small.cuh, ptx_tcgen05
 ptx_tcgen05_pair.cuh); g++ compiles them here as plain C++, with mma.sync, mbarriers, TMA, tensor memory
 and tcgen05.mma modelled from their documented behaviour.  This is a check of kernel LOGIC (indexing, block and warp reductions, the
 f32 shortcut and its f64 replay, special values); it says nothing about speed and is no substitute
-for the GPU parity tests.  The INT8 symmetric kernels have run on B200s and pass the same golden
-vectors there, which is what validates the stand-in itself; the kernels of the other modes have not
-run on a GPU yet, so this is their first execution of any kind."""
+for the GPU parity tests.  The kernels have run on B200s and pass the same golden vectors there, which is
+what validates the stand-in itself."""
 import ctypes
 import os
 import subprocess
@@ -137,7 +136,7 @@ def _quantize_batch(emu, tensors, per_channel, grid, misalign=False):
 
 @pytest.mark.parametrize("per_channel", [1, 0], ids=["per_channel", "per_tensor"])
 def test_batched_quantizer_on_the_golden_vectors(emu, per_channel):
-    # every golden tensor of the granularity, all in one table (not yet run on a GPU)
+    # every golden tensor of the granularity, all in one table
     cases = [c for c in GOLDEN if len(c["shape"]) >= 1 and c["granularity"] == per_channel]
     assert len(cases) >= 5
     for grid in (1, 7):
@@ -475,8 +474,7 @@ def test_warp_mma_refuses_unsupported_shapes(emu_mma):
 
 # ---- the tcgen05 forward kernel: mbarriers, TMA, tensor memory and tcgen05.mma modelled ---------------
 # (tests/cpu_emu/cuda_shim_tcgen05.h).  This kernel has passed its parity tests on B200s; that it
-# also produces the oracle's results on top of the model is what ties the model to the hardware.  The
-# variants below that have NOT run on a GPU yet are marked.
+# also produces the oracle's results on top of the model is what ties the model to the hardware.
 @pytest.fixture(scope="module")
 def emu_tc():
     L = _build("emu_gemm_tcgen05")
@@ -536,8 +534,8 @@ def test_tcgen05_forward_matches_oracle(oracle, emu_tc, tok, groups, M, N, K):
 
 
 @pytest.mark.parametrize("tok,M,N,K,splits", [(16, 3, 128, 1024, 4), (64, 40, 130, 768, 3), (32, 20, 64, 1100 // 4 * 4, 2),
-                                              (128, 100, 200, 2048, 3),      # large-tile split-K: not yet run on a GPU
-                                              (256, 260, 128, 1024, 2)])     # large-tile split-K: not yet run on a GPU
+                                              (128, 100, 200, 2048, 3),      # large-tile split-K
+                                              (256, 260, 128, 1024, 2)])     # large-tile split-K
 def test_tcgen05_split_k(oracle, emu_tc, tok, M, N, K, splits):
     K = K // 16 * 16
     q, scales, bias, x_bits, x = _tc_case(M, N, K, splits)
@@ -628,7 +626,7 @@ def test_tcgen05_random_configurations(oracle, emu_tc, seed):
 
 
 def test_tcgen05_tile_list_grid(oracle, emu_tc):
-    # the 1-D tile list of the two-launch tail-split scheme (not yet run on a GPU)
+    # the 1-D tile list of the two-launch tail-split scheme
     q, scales, bias, x_bits, x = _tc_case(300, 260, 512, 5)
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x)
     for splits in (1, 2):
@@ -745,7 +743,7 @@ def test_cta_pair_random_configurations(oracle, emu_pair, seed):
 
 @pytest.mark.parametrize("gated", [False, True])
 def test_cta_pair_tile_list_and_tail_split(oracle, emu_pair, gated):
-    # SHREWQ_TC_TAILSPLIT on the pair kernel (not yet run on a GPU): the 1-D list of pair tiles as one launch,
+    # the tail split (option tc_tailsplit) on the pair kernel: the 1-D list of pair tiles as one launch,
     # then the two-launch scheme with 4 (5) pair tiles "resident at once": 4 (5) whole-K tiles in the first
     # launch, the remaining 2 (1) split 2 (3) ways along K in the second
     M, N, K = 300, (300 if gated else 600), 2048           # 3 channel pairs x 2 token tiles = 6 pair tiles
@@ -842,7 +840,7 @@ def test_cta_pair_wait_that_runs_out_ends_both_blocks():
 
 
 def test_tcgen05_two_launch_tail_split(oracle, emu_tc):
-    # SHREWQ_TC_TAILSPLIT (not yet run on a GPU): with "5 SMs", 12 tiles = two full waves as whole-K tiles
+    # the tail split (option tc_tailsplit): with "5 SMs", 12 tiles = two full waves as whole-K tiles
     # plus 2 tiles split along K in a second launch; both launches index tiles through the 1-D list
     q, scales, bias, x_bits, x = _tc_case(260, 500, 1024, 21)       # 4 channel tiles x 3 token tiles
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
@@ -965,9 +963,10 @@ def _cc_forward(emu_cc, kernel, q, scales, bias, x, x_bf16, y_bf16, relu=False, 
     return y
 
 
-@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 16])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 16, 17, 40, 64])
 @pytest.mark.parametrize("x_bf16", [0, 1], ids=["f32", "bf16"])
 def test_gemv_matches_oracle(oracle, emu_cc, M, x_bf16):
+    # above 16 tokens the launch is sliced along grid.y (16 tokens per slice, a ragged last slice)
     rng = np.random.default_rng(M)
     N, K = 37, 528
     q = rng.integers(-127, 128, size=(N, K)).astype(np.int8)

@@ -45,6 +45,10 @@ def test_f32_activations_take_the_hi_lo_pass_on_the_tensor_cores():
     assert plan(8, 4096, 4096, bf16=0)[1] == "gemv"
     assert plan(16, 4096, 4096, bf16=0)[1] == "gemv"
     assert plan(17, 4096, 4096, bf16=0)[1] == "tcgen05-f32"
+    assert plan(64, 256, 784, bf16=0)[1] == "gemv"       # config 1: a few MFLOP, one short sliced launch
+    assert plan(64, 10, 256, bf16=0)[1] == "gemv"
+    assert plan(129, 256, 784, bf16=0)[1] == "tcgen05-f32"
+    assert plan(128, 1024, 1024, bf16=0)[1] == "tcgen05-f32"
     assert plan(512, 4096, 4096, bf16=0)[1] == "tcgen05-f32"
     assert plan(512, 4096, 4100, bf16=0)[1] == "simt"    # ragged in_features: the general kernel
     assert plan(512, 4096, 4096, bf16=0, gated=1)[1] == "simt"
