@@ -116,20 +116,20 @@ extern "C" int emu_gemm_tcgen05(const int8_t *q, const float *scales, const floa
     return rc;
 }
 
-// f32 activations as a bf16 hi/lo pair (x: [2M, K] bf16 bits, the lo rows under the hi rows), 128-token tiles, one
-// sub-block per stage, as launch_gemm_tcgen05_xsplit sets the launch up.  Same return codes as above.
-extern "C" int emu_gemm_tcgen05_xsplit(const int8_t *q, const float *scales, const float *bias, const void *x_hi_lo, void *y, int M,
-                                       int N, int K, size_t ldy, int epilogue, int y_bf16, int splits) {
-    if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(x_hi_lo) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || M < 1) return -1;
-    using C = Cfg<128, 1, true>;
+// f32 activations as a bf16 hi/lo pair (x: [2M, K] bf16 bits, the lo rows under the hi rows), 128- or 256-token
+// tiles, one sub-block per stage, as launch_gemm_tcgen05_xsplit sets the launch up.  Same return codes as above.
+template <int TOK>
+static int run_xsplit(const int8_t *q, const float *scales, const float *bias, const void *x_hi_lo, void *y, int M, int N, int K,
+                      size_t ldy, int epilogue, int y_bf16, int splits) {
+    using C = Cfg<TOK, 1, true>;
     const CUtensorMap tw = map2d(q, 1, K, N, kBlockK, 128, 64);
-    const CUtensorMap tx = map2d(x_hi_lo, 2, K, 2 * (uint64_t)M, kBlockK, 128, 128);
-    const int n_tiles = (N + 127) / 128, m_tiles = (M + 127) / 128;
+    const CUtensorMap tx = map2d(x_hi_lo, 2, K, 2 * (uint64_t)M, kBlockK, TOK, 128);
+    const int n_tiles = (N + 127) / 128, m_tiles = (M + TOK - 1) / TOK;
     const int rounds = (K + kBlockK - 1) / kBlockK;
     if (splits < 1) splits = 1;
     const int rps = (rounds + splits - 1) / splits;
     splits = (rounds + rps - 1) / rps;
-    std::vector<float> partials(splits > 1 ? (size_t)n_tiles * m_tiles * splits * 128 * kTileN : 0, -12345.0f);
+    std::vector<float> partials(splits > 1 ? (size_t)n_tiles * m_tiles * splits * TOK * kTileN : 0, -12345.0f);
     std::vector<unsigned int> counters((size_t)n_tiles * m_tiles, 0u);
     SplitK sk{splits > 1 ? partials.data() : nullptr, splits > 1 ? counters.data() : nullptr, rps, 0, 0};
     Operands ops{scales, bias, nullptr, nullptr};
@@ -137,8 +137,8 @@ extern "C" int emu_gemm_tcgen05_xsplit(const int8_t *q, const float *scales, con
     emu::g_failed = false;
     Dests none{};
     auto body = [&] {
-        if (y_bf16) linear_i8_tcgen05_kernel<128, 1, 3, false, __nv_bfloat16, true>(tw, tw, tx, ops, static_cast<__nv_bfloat16 *>(y), none, M, N, K, ldy, epilogue, sk, &st);
-        else linear_i8_tcgen05_kernel<128, 1, 3, false, float, true>(tw, tw, tx, ops, static_cast<float *>(y), none, M, N, K, ldy, epilogue, sk, &st);
+        if (y_bf16) linear_i8_tcgen05_kernel<TOK, 1, 3, false, __nv_bfloat16, true>(tw, tw, tx, ops, static_cast<__nv_bfloat16 *>(y), none, M, N, K, ldy, epilogue, sk, &st);
+        else linear_i8_tcgen05_kernel<TOK, 1, 3, false, float, true>(tw, tw, tx, ops, static_cast<float *>(y), none, M, N, K, ldy, epilogue, sk, &st);
     };
     emu::launch3((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)splits, 64 + 128 * 3, C::kSmemRequest, body);
     if (emu::g_failed) return -4;
@@ -146,6 +146,12 @@ extern "C" int emu_gemm_tcgen05_xsplit(const int8_t *q, const float *scales, con
     for (unsigned int c : counters)
         if (c != 0) return -3;
     return 0;
+}
+extern "C" int emu_gemm_tcgen05_xsplit(const int8_t *q, const float *scales, const float *bias, const void *x_hi_lo, void *y, int M,
+                                       int N, int K, size_t ldy, int epilogue, int y_bf16, int splits, int tok) {
+    if (K % 16 != 0 || (reinterpret_cast<uintptr_t>(x_hi_lo) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || M < 1) return -1;
+    if (tok == 256) return run_xsplit<256>(q, scales, bias, x_hi_lo, y, M, N, K, ldy, epilogue, y_bf16, splits);
+    return run_xsplit<128>(q, scales, bias, x_hi_lo, y, M, N, K, ldy, epilogue, y_bf16, splits);
 }
 
 extern "C" int emu_last_a_format() { return emu::g_last_a_format.load(); }  // 0 = f16, 1 = bf16

@@ -634,13 +634,14 @@ def test_tcgen05_tile_list_grid(oracle, emu_tc):
         assert oracle.rel_err(y, ref) < 2e-6
 
 
-@pytest.mark.parametrize("M,N,K,splits,y_bf16", [(90, 140, 784 // 16 * 16, 1, False), (200, 129, 256, 1, False),
-                                                  (130, 64, 1024, 2, False), (17, 300, 128, 1, True)])
-def test_f32_activations_as_hi_lo_pair_on_the_tensor_cores(oracle, emu, emu_tc, M, N, K, splits, y_bf16):
+@pytest.mark.parametrize("M,N,K,splits,y_bf16,tok", [(90, 140, 784 // 16 * 16, 1, False, 128), (200, 129, 256, 1, False, 128),
+                                                      (130, 64, 1024, 2, False, 128), (17, 300, 128, 1, True, 128),
+                                                      (300, 129, 256, 1, False, 256), (260, 70, 512, 2, True, 256)])
+def test_f32_activations_as_hi_lo_pair_on_the_tensor_cores(oracle, emu, emu_tc, M, N, K, splits, y_bf16, tok):
     # forward_f32_on_tensor_cores: x = hi + lo in bf16, both token tiles in one stage, two MMAs per k-step
     # into the same accumulator; the lo rows sit under the M hi rows of one array
     emu.emu_split_f32.argtypes = [_vp, _sz, _cu, _vp, _vp]
-    emu_tc.emu_gemm_tcgen05_xsplit.argtypes = [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci]
+    emu_tc.emu_gemm_tcgen05_xsplit.argtypes = [_vp, _vp, _vp, _vp, _vp, _ci, _ci, _ci, _sz, _ci, _ci, _ci, _ci]
     rng = np.random.default_rng(3 + M)
     q = _aligned((N, K), np.int8)
     q[...] = rng.integers(-127, 128, size=(N, K)).astype(np.int8)
@@ -655,17 +656,16 @@ def test_f32_activations_as_hi_lo_pair_on_the_tensor_cores(oracle, emu, emu_tc, 
     assert np.max(np.abs((hi_f.astype(np.float64) + lo_f) - x)) <= 2.0 ** -16 * np.max(np.abs(x))
     s32 = scales.astype(np.float32)
     y = np.full((M, N), 0x4100, np.uint16) if y_bf16 else np.full((M, N), 7.0, np.float32)
-    rc = emu_tc.emu_gemm_tcgen05_xsplit(_p(q), _p(s32), _p(bias), _p(pair), _p(y), M, N, K, N, 1, int(y_bf16), splits)
+    rc = emu_tc.emu_gemm_tcgen05_xsplit(_p(q), _p(s32), _p(bias), _p(pair), _p(y), M, N, K, N, 1, int(y_bf16), splits, tok)
     assert rc == 0
     ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, bias, x, relu=True)
     got = (y.astype(np.uint32) << 16).view(np.float32) if y_bf16 else y
     assert oracle.rel_err(got, ref) < (1e-2 if y_bf16 else 1e-4)   # the f32 path's tolerance
 
 
-# ---- the CTA-pair kernel (cta_group::2), never run on a GPU: two blocks of a cluster run concurrently --
-# over modelled cluster shared memory.  The single-CTA parts of the model are tied to the hardware by the
-# kernel above; the cta_group::2 parts (tests/cpu_emu/cuda_shim_tcgen05_pair.h) state how the documentation
-# is read here, and are what the first GPU run of this kernel has to confirm.
+# ---- the CTA-pair kernel (cta_group::2): two blocks of a cluster run concurrently over modelled cluster
+# shared memory.  The cta_group::2 parts of the model (tests/cpu_emu/cuda_shim_tcgen05_pair.h) state how the
+# documentation is read here; the kernel's GPU parity tests have since confirmed that reading.
 @pytest.fixture(scope="module")
 def emu_pair():
     L = _build("emu_gemm_tcgen05_pair")
