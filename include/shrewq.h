@@ -95,12 +95,13 @@ SHREWQ_API int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream);
  *   "tc_tailsplit" 0/1    issue a short last wave as a second launch split along K (default 0)
  *   "tc_pair"      0..2   CTA pairs (tcgen05.mma.cta_group::2) for batches above 128 tokens: 0 never, 1 where
  *                         they win by measurement (default), 2 always
- *   "gemv_pdl"     0/1    programmatic dependent launch of the small-batch kernels (default 1): from a handle's
- *                         second forward on, a forward of up to 16 tokens may request its WEIGHTS while the
- *                         previous kernel of the stream still runs; it reads activations and writes outputs only
- *                         after that kernel has completed.  The first forward of a handle is always fully
- *                         ordered behind the stream, so weights quantized on the same stream just before are
- *                         complete; a caller that rewrites a handle's weights in place LATER must set 0.
+ *   "pdl"          0/1    programmatic dependent launch of the forward kernels (default 1): from a handle's second
+ *                         forward on, a forward kernel may start while the previous kernel of the stream still runs
+ *                         and request its WEIGHTS; it reads activations and writes outputs, partial sums and
+ *                         counters only after that kernel has completed (griddepcontrol.wait).  The first forward
+ *                         of a handle is always fully ordered behind the stream, so weights quantized on the same
+ *                         stream just before are complete; a caller that rewrites a handle's weights in place
+ *                         LATER must set 0.  ("gemv_pdl" is accepted as an older name of the same option.)
  * Unknown names and values out of range return SHREWQ_ERR_INVALID_ARG. */
 SHREWQ_API int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value);
 SHREWQ_API int shrewq_ctx_synchronize(shrewq_ctx *ctx);

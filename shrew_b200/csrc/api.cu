@@ -142,7 +142,7 @@ int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value) {
         if (value < 0 || value > 2) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: tc_pair is 0 (never), 1 (where pairs win) or 2 (always above 128 tokens)");
         t.tc_pair = value;
     }
-    else if (!strcmp(name, "gemv_pdl")) t.gemv_pdl = value != 0;
+    else if (!strcmp(name, "pdl") || !strcmp(name, "gemv_pdl")) t.pdl = value != 0;
     else return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);
     return SHREWQ_OK;
 }
@@ -601,7 +601,7 @@ static int forward_impl(shrewq_linear *lin, shrewq_linear *up, const void *x_dev
         a.extra.p[i] = peers[i];
     }
     a.extra.n = n_peers;
-    a.pdl = ctx->tuning.gemv_pdl != 0 && lin->forwarded.load(std::memory_order_relaxed) &&
+    a.pdl = ctx->tuning.pdl != 0 && lin->forwarded.load(std::memory_order_relaxed) &&
             (!up || up->forwarded.load(std::memory_order_relaxed));
 
     // Packed INT4 rows: only the warp-MMA forward reads them (batch <= 32 for now)

@@ -26,7 +26,7 @@ struct Tuning {
     int tc_tok_gated = 0;   // the same for gate/up launches only
     int tc_tailsplit = 0;   // issue a short last wave as a second launch split along K
     int tc_pair = 1;        // CTA pairs (tcgen05.mma.cta_group::2) for large batches: 0 never, 1 where they win, 2 whenever M > 128
-    int gemv_pdl = 1;       // programmatic dependent launch of the small-batch kernels (after a handle's first forward)
+    int pdl = 1;            // programmatic dependent launch of the forward kernels (after a handle's first forward)
 };
 
 }  // namespace shrewq
@@ -101,6 +101,23 @@ int ensure_stage(shrewq_ctx *ctx, size_t dev_bytes, size_t pinned_bytes);
             return shrewq::set_err((ctx), SHREWQ_ERR_CUDA, "%s failed: %s", #expr,          \
                                    cudaGetErrorString(e__));                               \
     } while (0)
+
+// Launch with or without programmatic stream serialization (the attribute lets the kernel start while the previous
+// kernel of the stream still runs; the kernels wait for it before they touch anything but weights).
+template <typename Kern, typename... Args>
+inline cudaError_t launch_maybe_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
 
 // ---- launchers implemented in the kernel translation units -------------------------
 int launch_quantize_batch(shrewq_ctx *ctx, const shrewq_quant_item *items, size_t n_items, int granularity);

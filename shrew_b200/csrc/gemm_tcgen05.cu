@@ -165,9 +165,9 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
         }
     }
     dim3 grid((unsigned)p.n_tiles, (unsigned)p.m_tiles, (unsigned)p.splits);
-    kern<<<grid, 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M,
-                                                                (int)a.N, (int)a.K, a.ldy, a.epilogue, sk,
-                                                                ctx->dev_status);
+    SHREWQ_CUDA_TRY(ctx, launch_maybe_pdl(kern, grid, dim3(64 + 128 * G), (size_t)C::kSmemRequest, ctx->stream, a.pdl, tw, tw2, tx, ops,
+                                          static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, sk,
+                                          ctx->dev_status));
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;

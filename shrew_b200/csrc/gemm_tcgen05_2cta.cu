@@ -107,8 +107,9 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
         sk.partials = reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + 8192);
     }
     dim3 grid(2 * pairs, m_tiles, (unsigned)splits);
-    kern<<<grid, kThreads, kSmemBytes, ctx->stream>>>(tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N,
-                                                      (int)a.K, a.ldy, a.epilogue, sk, ctx->dev_status);
+    SHREWQ_CUDA_TRY(ctx, launch_maybe_pdl(kern, grid, dim3(kThreads), (size_t)kSmemBytes, ctx->stream, a.pdl, tw, tw2, tx, ops,
+                                          static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, sk,
+                                          ctx->dev_status));
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;

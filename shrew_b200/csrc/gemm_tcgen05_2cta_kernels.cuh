@@ -107,6 +107,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                               int M, int N, int K, size_t ldy, int epilogue, SplitK2 sk, DeviceStatus *status) {
     constexpr int kChan = GATED ? kLanes / 2 : kLanes;  // output channels per CTA
     TRACE2_INIT
+    pdl_launch_dependents();  // the next kernel of the stream may start its prologue (a no-op in an ordinary launch)
     SHREWQ_DYNAMIC_SMEM(uint8_t, smem_raw);
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *bar_area = smem + kStages * kStageBytes;
@@ -120,6 +121,12 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
         const int t = sk.tile_begin + pair;
         pair = t % sk.pairs_total;
         m_tile = t / sk.pairs_total;
+    } else {
+        // token tiles fastest in launch order: the pairs that share a weight tile start together, so the tile
+        // comes from DRAM once and from L2 for the others
+        const int t = (int)blockIdx.y * (int)(gridDim.x >> 1) + pair;
+        m_tile = t % (int)gridDim.y;
+        pair = t / (int)gridDim.y;
     }
     const int n0 = pair * 2 * kChan + (int)rank * kChan;      // this CTA's first channel
     const int m0 = m_tile * kTokPair + (int)rank * kTokHalf;  // this CTA's first token (B half)
@@ -160,17 +167,11 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
 
     if (warp == 0) {
         // ---------------- TMA producer (one thread per CTA) ----------------
+        // Programmatic dependent launch: the WEIGHTS of the first stages are requested at once (they never depend on
+        // an earlier kernel), the activations only when the previous kernel of the stream, whose output they may be,
+        // has completed (griddepcontrol.wait; it returns at once in an ordinary launch).
         if (lane == 0) {
-            uint32_t s = 0, ph = 1;
-            uint32_t dst = smem_base;
-            int kc = r_begin * kSub * kBlockK;
-            for (int i = 0; i < rounds; ++i) {
-                TRACE2(0, i, 0);
-                if (!mbar_wait(bars_u32 + kEmpty + s * 8, ph, ctl, status, 0, s)) break;
-                TRACE2(0, i, 1);
-                const uint32_t wb = bars_u32 + kWFull + s * 8, xb = bars_u32 + kXFull + s * 8;
-                mbar_expect_tx(wb, kSub * kWSub);
-                if (rank == 0) mbar_expect_tx(xb, 2 * kSub * kXSub);  // the halves of both CTAs
+            auto load_w = [&](uint32_t dst, int kc, uint32_t wb) {
 #pragma unroll
                 for (int j = 0; j < kSub; ++j) {
                     if constexpr (GATED) {
@@ -179,8 +180,36 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
                     } else {
                         tma_load_2d(dst + j * kWSub, &tmap_w, kc + j * kBlockK, n0, wb);
                     }
-                    tma_load_2d_pair(dst + kXOff + j * kXSub, &tmap_x, kc + j * kBlockK, m0, xb);
                 }
+            };
+            auto load_x = [&](uint32_t dst, int kc, uint32_t xb) {
+                if (rank == 0) mbar_expect_tx(xb, 2 * kSub * kXSub);  // the halves of both CTAs
+#pragma unroll
+                for (int j = 0; j < kSub; ++j) tma_load_2d_pair(dst + kXOff + j * kXSub, &tmap_x, kc + j * kBlockK, m0, xb);
+            };
+            const int kc0 = r_begin * kSub * kBlockK;
+            const int pre = rounds < kStages ? rounds : kStages;  // the stages that are free at the start
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t wb = bars_u32 + kWFull + i * 8;
+                mbar_expect_tx(wb, kSub * kWSub);
+                load_w(smem_base + i * kStageBytes, kc0 + i * kSub * kBlockK, wb);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                load_x(smem_base + i * kStageBytes, kc0 + i * kSub * kBlockK, bars_u32 + kXFull + i * 8);
+                TRACE2(0, i, 2);
+            }
+            uint32_t s = 0, ph = 0;  // the ring wrapped once: the producer now waits for the first release of a stage
+            uint32_t dst = smem_base;
+            int kc = kc0 + pre * kSub * kBlockK;
+            for (int i = pre; i < rounds; ++i) {
+                TRACE2(0, i, 0);
+                if (!mbar_wait(bars_u32 + kEmpty + s * 8, ph, ctl, status, 0, s)) break;
+                TRACE2(0, i, 1);
+                const uint32_t wb = bars_u32 + kWFull + s * 8;
+                mbar_expect_tx(wb, kSub * kWSub);
+                load_w(dst, kc, wb);
+                load_x(dst, kc, bars_u32 + kXFull + s * 8);
                 TRACE2(0, i, 2);
                 kc += kSub * kBlockK;
                 dst += kStageBytes;
@@ -258,6 +287,7 @@ linear_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const 
             if (quad == 0) TRACE2(2, i, 3);
         }
         // epilogue: this CTA's channels x the pair's 256 tokens; 16-column chunks dealt to the groups
+        pdl_wait();  // outputs, partial sums and counters may still be in use by the previous kernel of the stream
         if (ok) ok = mbar_wait_warp(bars_u32 + kAcc, 0, ctl, status, 4, 0);
         if (ok) tc_fence_after();
         const int splits = (int)gridDim.z;

@@ -115,6 +115,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
     static_assert(!(XSPLIT && GATED), "the hi/lo form exists for plain tiles");
     constexpr int kChan = GATED ? 64 : 128;  // output channels per CTA
     TRACE_INIT
+    pdl_launch_dependents();  // the next kernel of the stream may start its prologue (a no-op in an ordinary launch)
     SHREWQ_DYNAMIC_SMEM(uint8_t, smem_raw);
     // 1024-byte alignment: required by the 128-byte swizzle with base_offset 0
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -164,16 +165,11 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
 
     if (warp == 0) {
         // ---------------- TMA producer (one thread) ----------------
+        // Programmatic dependent launch: the WEIGHTS of the first stages are requested at once (they never depend on
+        // an earlier kernel), the activations only when the previous kernel of the stream, whose output they may be,
+        // has completed (griddepcontrol.wait; it returns at once in an ordinary launch).
         if (lane == 0) {
-            uint32_t s = 0, ph = 1;  // waiting on parity 1 of a fresh barrier returns at once
-            uint32_t dst = smem_base;
-            int kc = r_begin * KSUB * kBlockK;
-            for (int i = 0; i < nr; ++i) {
-                TRACE(0, i, 0);
-                if (!mbar_wait(bars_u32 + kEmptyBar + s * 8, ph, ctl, status, 0, s)) break;
-                TRACE(0, i, 1);
-                const uint32_t fb = bars_u32 + kFullBar + s * 8;
-                mbar_expect_tx(fb, C::kStageBytes);
+            auto load_w = [&](uint32_t dst, int kc, uint32_t fb) {
 #pragma unroll
                 for (int j = 0; j < KSUB; ++j) {
                     if constexpr (GATED) {
@@ -182,10 +178,39 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
                     } else {
                         tma_load_2d(dst + j * C::kWSub, &tmap_w, kc + j * kBlockK, n0, fb);
                     }
+                }
+            };
+            auto load_x = [&](uint32_t dst, int kc, uint32_t fb) {
+#pragma unroll
+                for (int j = 0; j < KSUB; ++j) {
                     tma_load_2d(dst + C::kXOff + j * C::kXSub, &tmap_x, kc + j * kBlockK, m0, fb);
                     if constexpr (XSPLIT)  // the lo rows follow the M hi rows in the same array
                         tma_load_2d(dst + C::kXOff + j * C::kXSub + C::kXTile, &tmap_x, kc + j * kBlockK, m0 + M, fb);
                 }
+            };
+            const int kc0 = r_begin * KSUB * kBlockK;
+            const int pre = nr < C::kStages ? nr : C::kStages;  // the stages that are free at the start
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t fb = bars_u32 + kFullBar + i * 8;
+                mbar_expect_tx(fb, C::kStageBytes);
+                load_w(smem_base + i * C::kStageBytes, kc0 + i * KSUB * kBlockK, fb);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                load_x(smem_base + i * C::kStageBytes, kc0 + i * KSUB * kBlockK, bars_u32 + kFullBar + i * 8);
+                TRACE(0, i, 2);
+            }
+            uint32_t s = 0, ph = 0;  // the ring wrapped once: the producer now waits for the first release of a stage
+            uint32_t dst = smem_base;
+            int kc = kc0 + pre * KSUB * kBlockK;
+            for (int i = pre; i < nr; ++i) {
+                TRACE(0, i, 0);
+                if (!mbar_wait(bars_u32 + kEmptyBar + s * 8, ph, ctl, status, 0, s)) break;
+                TRACE(0, i, 1);
+                const uint32_t fb = bars_u32 + kFullBar + s * 8;
+                mbar_expect_tx(fb, C::kStageBytes);
+                load_w(dst, kc, fb);
+                load_x(dst, kc, fb);
                 TRACE(0, i, 2);
                 kc += KSUB * kBlockK;
                 dst += C::kStageBytes;
@@ -271,6 +296,7 @@ linear_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gri
             if (((warp - 2) & 3) == 0) TRACE(2, i, 3);
         }
         // ---------------- epilogue: 16-column chunks dealt round-robin to the groups ----------------
+        pdl_wait();  // outputs, partial sums and counters may still be in use by the previous kernel of the stream
         if (warp == 2) TRACE(3, 0, 0);  // (tracing build: role 3 = the epilogue of the first converter warp)
         if (ok) ok = mbar_wait_warp(bars_u32 + kAccBar, 0, ctl, status, 4, 0);
         if (warp == 2) TRACE(3, 0, 1);  // accumulators complete

@@ -16,7 +16,7 @@ void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     // batches above MT tokens run as slices of MT tokens along grid.y (small layers with f32 activations: the
     // weights come from L2 for every slice but the first)
     const dim3 grid((unsigned)((a.N + NR - 1) / NR), (unsigned)((a.M + MT - 1) / MT));
-    // Option gemv_pdl launches the PDL variant of the kernel with programmatic stream
+    // With a.pdl the launch takes the PDL variant of the kernel with programmatic stream
     // serialization: back-to-back GEMVs overlap launch latency, prologue and the first weight
     // loads with the tail of the kernel before.
     const bool pdl = a.pdl;

@@ -277,12 +277,12 @@ def test_ring_kernel_small_batch_parity(oracle, M, N, K, pdl):
     dev = Device.get("cuda:0")
     ql, w, b = _make(N, K, 1, seed=N + K)
     x_t, x_np = _x(M, K, "bf16", seed=M)
-    dev.set_option("gemv_pdl", pdl)
+    dev.set_option("pdl", pdl)
     try:
         _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, force="mma-ring")
         _check(oracle, ql, x_t, x_np, b, 1, TOL_BF16, relu=True, force="mma-ring")
     finally:
-        dev.set_option("gemv_pdl", 1)
+        dev.set_option("pdl", 1)
 
 
 def test_small_batch_chain_with_dependent_launch(oracle):
