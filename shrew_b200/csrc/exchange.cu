@@ -41,7 +41,10 @@ int shrewq_exchange_barrier(shrewq_exchange *ex) {
     if (!ex) return set_err(nullptr, SHREWQ_ERR_INVALID_ARG, "exchange_barrier: handle is NULL");
     shrewq_ctx *ctx = ex->ctx;
     SHREWQ_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    exchange_barrier_kernel<<<1, 32, 0, ctx->stream>>>(ex->args, ctx->dev_status);
+    // with programmatic stream serialization the barrier kernel may start (and let ITS successor start its prologue)
+    // while the kernel before it still runs; it signals nothing before that kernel has completed
+    SHREWQ_CUDA_TRY(ctx, launch_maybe_pdl(exchange_barrier_kernel, dim3(1), dim3(32), (size_t)0, ctx->stream, ctx->tuning.pdl != 0,
+                                          ex->args, ctx->dev_status));
     ctx->launches += 1;
     SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
     return SHREWQ_OK;

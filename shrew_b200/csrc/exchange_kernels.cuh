@@ -53,6 +53,10 @@ __device__ __forceinline__ bool exchange_reached(const uint32_t *p, uint32_t epo
 }
 
 __global__ void __launch_bounds__(32) exchange_barrier_kernel(ExchangeArgs a, DeviceStatus *status) {
+    // Programmatic dependent launch: the kernel after the barrier may start its prologue now; this kernel says
+    // "everything before me is done" only once the kernel before it has completed and its stores are visible.
+    pdl_launch_dependents();
+    pdl_wait();
     uint32_t *mine = a.flags[a.rank];
     uint32_t epoch = 0;
     if (threadIdx.x == 0) {
