@@ -143,6 +143,7 @@ int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value) {
         t.tc_pair = value;
     }
     else if (!strcmp(name, "pdl") || !strcmp(name, "gemv_pdl")) t.pdl = value != 0;
+    else if (!strcmp(name, "ring_stages")) t.ring_stages = value == 2 || value == 3 ? value : 0;
     else return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: unknown option '%s'", name);
     return SHREWQ_OK;
 }
@@ -193,10 +194,11 @@ const char *shrewq_last_error(const shrewq_ctx *ctx) { return ctx ? ctx->err : g
 uint64_t shrewq_ctx_launch_count(const shrewq_ctx *ctx) { return ctx ? ctx->launches.load() : 0; }
 
 // The default kernel family of a forward with bf16 activations: the one rule, shared by forward_impl and
-// shrewq_plan_forward.  Measured on 4096 x 4096, 11008 x 4096 and 4096 x 11008: the CUDA-core GEMV wins up to 2
-// tokens, a warp-MMA kernel from 3 to 32, the tcgen05 kernel above.  Of the two warp-MMA kernels the ring kernel
-// (bulk copies into shared memory) wins up to 16 tokens while all its CTAs are resident at once (two per SM), the
-// register-streaming one otherwise.
+// shrewq_plan_forward.  Measured on 4096 x 4096, 11008 x 4096, 4096 x 11008, 1376 x 4096 and 32000 x 4096: the
+// CUDA-core GEMV wins up to 2 tokens, a warp-MMA kernel from 3 to 32, the tcgen05 kernel above.  Of the two warp-MMA
+// kernels the ring kernel (bulk copies into shared memory) wins up to 16 tokens on grids of up to five CTAs per SM
+// (three stages while all CTAs are resident at once, two stages beyond: see launch_ring_one), the register-streaming
+// one on larger grids (32000 x 4096: 37 against 41 us) and above 16 tokens.
 // f32 activations on SMALL layers (config 1: 784 -> 256 -> 10 at 64 tokens): the whole forward is a few MFLOP and
 // what counts is the number and latency of launches; the CUDA-core GEMV in slices of 16 tokens is one short launch
 // where the tensor-core route is a split pass plus a pipelined kernel that never fills.
@@ -206,7 +208,7 @@ static bool gemv_slices_win(size_t M, size_t N, size_t K) {
 }
 static bool ring_kernel_wins(size_t M, size_t N, bool gated, int sm_count) {
     const size_t ctas = (N + (gated ? 7 : 15)) / (gated ? 8 : 16);
-    return M >= 3 && M <= 16 && ctas <= (size_t)2 * sm_count;
+    return M >= 3 && M <= 16 && ctas <= (size_t)5 * sm_count;
 }
 static int default_family(size_t M, size_t N, bool gated, int sm_count, bool gemv_ok, bool mma_ok, bool tc_ok) {
     if (gemv_ok && (M <= 2 || (!mma_ok && (M <= 4 || !tc_ok)))) return kForceGemv;

@@ -26,6 +26,7 @@ struct Tuning {
     int tc_tok_gated = 0;   // the same for gate/up launches only
     int tc_tailsplit = 0;   // issue a short last wave as a second launch split along K
     int tc_pair = 1;        // CTA pairs (tcgen05.mma.cta_group::2) for large batches: 0 never, 1 where they win, 2 whenever M > 128
+    int ring_stages = 0;    // stages of the ring kernel: 0 = by grid size, 2 or 3 forced
     int pdl = 1;            // programmatic dependent launch of the forward kernels (after a handle's first forward)
 };
 

@@ -51,11 +51,11 @@ void dispatch_m(shrewq_ctx *ctx, const ForwardArgs &a) {
 }
 
 // ---- the ring kernel (1..32 tokens, bf16 activations): bulk copies into a shared-memory ring + warp MMA ----
-template <int NT, typename YT, bool GATED>
-int launch_ring_one(shrewq_ctx *ctx, const ForwardArgs &a) {
+template <int NT, typename YT, bool GATED, int STAGES>
+int launch_ring_stages(shrewq_ctx *ctx, const ForwardArgs &a) {
     constexpr int NCH = GATED ? kRingRows / 2 : kRingRows;
-    constexpr size_t kSmem = RingCfg<kRingKC>::kSmemBytes;
-    auto kern = gemv_i8_ring_kernel<NT, kRingKC, kRingConsumers, YT, GATED>;
+    constexpr size_t kSmem = RingCfg<kRingKC, STAGES>::kSmemBytes;
+    auto kern = gemv_i8_ring_kernel<NT, kRingKC, kRingConsumers, YT, GATED, STAGES>;
     static std::atomic<unsigned long long> attr_done{0};  // per instantiation: bit d = device d has the attribute
     const int d = ctx->device;
     if (d < 0 || d >= 64 || !((attr_done.load(std::memory_order_acquire) >> d) & 1ull)) {
@@ -76,6 +76,17 @@ int launch_ring_one(shrewq_ctx *ctx, const ForwardArgs &a) {
                                             static_cast<const uint16_t *>(a.x), static_cast<YT *>(a.y), a.extra, (int)a.M,
                                             (int)a.N, (int)a.K, a.ldy, a.epilogue, ctx->dev_status));
     return SHREWQ_OK;
+}
+
+// three stages (two CTAs per SM) while all CTAs are resident at once, two stages (three CTAs per SM) for larger grids
+template <int NT, typename YT, bool GATED>
+int launch_ring_one(shrewq_ctx *ctx, const ForwardArgs &a) {
+    constexpr int NCH = GATED ? kRingRows / 2 : kRingRows;
+    const size_t ctas = (a.N + NCH - 1) / NCH;
+    const int stages = ctx->tuning.ring_stages == 2 || ctx->tuning.ring_stages == 3 ? ctx->tuning.ring_stages
+                                                                                     : (ctas <= (size_t)2 * ctx->sm_count ? 3 : 2);
+    if (stages == 2) return launch_ring_stages<NT, YT, GATED, 2>(ctx, a);
+    return launch_ring_stages<NT, YT, GATED, 3>(ctx, a);
 }
 
 template <typename YT, bool GATED>

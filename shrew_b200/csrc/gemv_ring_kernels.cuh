@@ -54,13 +54,14 @@ constexpr unsigned int kTimeoutRing = 4;               // DeviceStatus::timeout_
 // measured on a B200 at 4096 x 4096, batch 1, the kernel takes 9.0 us with 512-byte, 7.3 us with 1 KB and 6.8 us
 // with 2 KB copies.  Rows are KC + 64 bytes apart in shared memory, so the 16-byte reads of a quarter warp (rows
 // g, g + 1; four 16-byte columns) fall into distinct banks.  Three stages of 2 KB rows are 99 KB: two CTAs per SM
-// with ~200 KB of weights in flight.
+// with ~200 KB of weights in flight, the choice for grids of up to two CTAs per SM; grids of several waves take two
+// stages (66 KB, three CTAs per SM: the same bytes in flight, half as many more warps to widen codes).
 constexpr int kRingMaxStages = 8;
-template <int KC>
+template <int KC, int STAGES = (KC >= 2048 ? 3 : KC >= 1024 ? 5 : 8)>
 struct RingCfg {
     static constexpr int kPitch = KC + 64;
     static constexpr int kStageBytes = kRingRows * kPitch;
-    static constexpr int kStages = KC >= 2048 ? 3 : KC >= 1024 ? 5 : 8;
+    static constexpr int kStages = STAGES;
     static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 2 * kRingMaxStages * 8;
 };
 constexpr int kRingKC = 2048;     // what the launcher instantiates
@@ -102,13 +103,13 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, DeviceS
 
 // NT: token blocks of 8 (M <= 8 * NT).  K a multiple of 64; q, q_up and x 16-byte aligned.
 // GATED: rows 0..7 of the CTA are gate rows, rows 8..15 the up rows of the same 8 channels.
-template <int NT, int KC, int W, typename YT, bool GATED>
+template <int NT, int KC, int W, typename YT, bool GATED, int STAGES = RingCfg<KC>::kStages>
 __global__ void __launch_bounds__((W + 1) * 32)
 gemv_i8_ring_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales, const float *__restrict__ bias,
                     const int8_t *__restrict__ q_up, const float *__restrict__ scales_up,
                     const float *__restrict__ bias_up, const uint16_t *__restrict__ x, YT *__restrict__ y, Dests extra,
                     int M, int N, int K, size_t ldy, int epilogue, DeviceStatus *status) {
-    using C = RingCfg<KC>;
+    using C = RingCfg<KC, STAGES>;
     static_assert(KC / 64 >= W, "every consumer warp needs a k-block in every full stage");
     constexpr int kRingWarps = W, kRingThreads = (W + 1) * 32;
     constexpr int NCH = GATED ? kRingRows / 2 : kRingRows;  // output channels per CTA

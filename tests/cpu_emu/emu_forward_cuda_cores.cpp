@@ -55,10 +55,19 @@ void gemv_g(const Args &a) {
 // the ring kernel (bulk copies into a shared-memory ring + warp MMA), instantiated as launch_gemv_ring does
 DeviceStatus g_ring_status{};
 int g_ring_kc = kRingKC;
+bool g_ring_two_stages = false;
 template <int NT, int KC, typename YT, bool GATED>
 void ring_one_kc(const Args &a) {
     constexpr int NCH = GATED ? kRingRows / 2 : kRingRows;
     const unsigned grid = (unsigned)((a.N + NCH - 1) / NCH);
+    if (g_ring_two_stages) {  // the launcher's choice for grids of several waves
+        emu::launch(grid, (kRingConsumers + 1) * 32, RingCfg<KC, 2>::kSmemBytes, [&] {
+            gemv_i8_ring_kernel<NT, KC, kRingConsumers, YT, GATED, 2>(a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up,
+                                                                      static_cast<const uint16_t *>(a.x), static_cast<YT *>(a.y),
+                                                                      g_peers, a.M, a.N, a.K, a.ldy, a.epilogue, &g_ring_status);
+        });
+        return;
+    }
     emu::launch(grid, (kRingConsumers + 1) * 32, RingCfg<KC>::kSmemBytes, [&] {
         gemv_i8_ring_kernel<NT, KC, kRingConsumers, YT, GATED>(a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up,
                                                                static_cast<const uint16_t *>(a.x), static_cast<YT *>(a.y), g_peers,
@@ -95,6 +104,7 @@ void simt_t(const Args &a) {
 }  // namespace
 
 extern "C" void emu_set_ring_kc(int kc) { g_ring_kc = kc; }
+extern "C" void emu_set_ring_two_stages(int on) { g_ring_two_stages = on != 0; }
 
 extern "C" void emu_set_peers(void **p, int n) {
     g_peers = Dests{};

@@ -1005,6 +1005,27 @@ def test_ring_kernel_matches_oracle(oracle, emu_cc, M, y_bf16, N, K, kc):
         assert oracle.rel_err(y[:, :N], ref) < 2e-6 and np.all(y[:, N:] == 7.0)
 
 
+@pytest.mark.parametrize("M,gated", [(5, False), (16, True), (32, False)])
+def test_ring_kernel_with_two_stages(oracle, emu_cc, M, gated):
+    # the launcher's choice for grids of several waves: a ring of two 2 KB stages, reused many times over a long K
+    rng = np.random.default_rng(M)
+    N, K = 21, 64 * 170
+    q, qu = (rng.integers(-127, 128, size=(N, K)).astype(np.int8) for _ in range(2))
+    scales, su = rng.random(N) * 1e-2 + 1e-4, rng.random(N) * 1e-2 + 1e-4
+    bits, xb = _bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    emu_cc.emu_set_ring_kc(2048)
+    emu_cc.emu_set_ring_two_stages(1)
+    try:
+        y = _cc_forward(emu_cc, 2, q, scales, None, bits, 1, 0, up=(qu, su, None) if gated else None)
+    finally:
+        emu_cc.emu_set_ring_two_stages(0)
+    ref = oracle.np_linear_forward(q, scales, oracle.PER_CHANNEL, None, xb)
+    if gated:
+        g, u = ref.astype(np.float64), oracle.np_linear_forward(qu, su, 1, None, xb).astype(np.float64)
+        ref = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+    assert oracle.rel_err(y, ref) < 1e-5
+
+
 @pytest.mark.parametrize("M", [3, 12])
 def test_ring_kernel_gate_up_and_peer_destinations(oracle, emu_cc, M):
     rng = np.random.default_rng(14 + M)

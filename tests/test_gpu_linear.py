@@ -267,11 +267,11 @@ def test_mma_small_batch_parity(oracle, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 523, 1024), (5, 16, 64), (8, 4096, 4096), (16, 4096, 4096), (23, 300, 1088), (32, 1000, 11008),
-                                   (3, 4096, 11008)])
+                                   (3, 4096, 11008), (4, 6000, 4160), (16, 11008, 4096)])
 @pytest.mark.parametrize("pdl", [0, 1])
 def test_ring_kernel_small_batch_parity(oracle, M, N, K, pdl):
     # bulk copies into the shared-memory ring + warp MMA: one partial stage, a ring reused several times (K = 11008 is
-    # 5.4 stages of 2048 over 3 slots), ragged last CTA; twice, so that the second forward runs with programmatic
+    # 5.4 stages of 2048 over 3 slots), ragged last CTA, grids of more than two CTAs per SM (two-stage ring); twice, so that the second forward runs with programmatic
     # dependent launch when the option is on (the first forward of a handle never does)
     from shrew_b200.quantize import Device
     dev = Device.get("cuda:0")

@@ -29,10 +29,11 @@ def test_small_batches_go_to_the_streaming_kernels():
         rc, name, p = plan(M, 4096, 4096)        # 256 CTAs of 16 rows: resident at once on 148 SMs
         assert (rc, name) == (0, "mma-ring") and not any(p.values())
         assert plan(M, 4096, 11008)[1] == "mma-ring"
-        assert plan(M, 11008, 4096)[1] == "mma"              # 688 CTAs: more than two per SM
-        assert plan(M, 2368, 4096, gated=1)[1] == "mma-ring"  # gated: 8 channels per CTA, 296 CTAs
-        assert plan(M, 2376, 4096, gated=1)[1] == "mma"
-        assert plan(M, 4096, 4096, sms=100)[1] == "mma"
+        assert plan(M, 11008, 4096)[1] == "mma-ring"          # 688 CTAs: the two-stage ring
+        assert plan(M, 5920, 4096, gated=1)[1] == "mma-ring"  # gated: 8 channels per CTA, 740 CTAs = five per SM
+        assert plan(M, 5928, 4096, gated=1)[1] == "mma"
+        assert plan(M, 32000, 4096)[1] == "mma"               # 2000 CTAs: the register-streaming kernel
+        assert plan(M, 4096, 4096, sms=50)[1] == "mma"
     for M in (17, 32):
         rc, name, p = plan(M, 4096, 4096)
         assert (rc, name) == (0, "mma") and not any(p.values())
