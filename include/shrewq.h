@@ -95,6 +95,8 @@ SHREWQ_API int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream);
  *   "tc_tailsplit" 0/1    issue a short last wave as a second launch split along K (default 0)
  *   "tc_pair"      0..2   CTA pairs (tcgen05.mma.cta_group::2) for batches above 128 tokens: 0 never, 1 where
  *                         they win by measurement (default), 2 always
+ *   "ring_stages"  0, 2, 3  stages of the ring kernel's shared-memory ring (default 0 = three while all its CTAs are
+ *                         resident at once, two for larger grids)
  *   "pdl"          0/1    programmatic dependent launch of the forward kernels (default 1): from a handle's second
  *                         forward on, a forward kernel may start while the previous kernel of the stream still runs
  *                         and request its WEIGHTS; it reads activations and writes outputs, partial sums and
