@@ -621,7 +621,12 @@ def main():
             sys.stderr.write(f"bench: graph capture failed ({e!r}); running eagerly\n")
             graphs, outs, use_graphs = [], [], False
 
-    launches_per_step = 2 if wl["kind"] == "mlp" else len(layers) if wl["kind"] == "stack" else 1
+    # kernels of this library per step, counted by the library (one eager step; the graphs replay the same launches):
+    # forward kernels, the f32 split passes, a K-split tail launch where the launcher issues one, exchange barriers
+    _l0 = sdev.launch_count()
+    eager_step(0, x_static)
+    sdev.synchronize()
+    launches_per_step = int(sdev.launch_count() - _l0)
 
     def step(i, x):
         if use_graphs:

@@ -92,7 +92,8 @@ SHREWQ_API int shrewq_ctx_set_stream(shrewq_ctx *ctx, void *stream);
  *   "tc_splitk"    0/1    split K when the tile grid leaves SMs idle (default 1)
  *   "tc_tok"       0, 16, 32, 64, 128, 256   force the token tile (default 0 = choose)
  *   "tc_tok_gated" the same for gate/up launches only
- *   "tc_tailsplit" 0/1    issue a short last wave as a second launch split along K (default 0)
+ *   "tc_tailsplit" 0..2   a short last wave of tiles as a second launch split along K: 0 (default) = the CTA-pair
+ *                         kernel does so for tails of up to a quarter wave, 1 = whenever a tail exists, 2 = never
  *   "tc_pair"      0..2   CTA pairs (tcgen05.mma.cta_group::2) for batches above 128 tokens: 0 never, 1 where
  *                         they win by measurement (default), 2 always
  *   "ring_stages"  0, 2, 3  stages of the ring kernel's shared-memory ring (default 0 = three while all its CTAs are

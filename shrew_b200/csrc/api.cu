@@ -137,7 +137,7 @@ int shrewq_ctx_set_option(shrewq_ctx *ctx, const char *name, int value) {
         if (value != 0 && value != 16 && value != 32 && value != 64 && value != 128 && value != 256)
             return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: %s is 0 (choose), 16, 32, 64, 128 or 256", name);
         (name[6] == '_' ? t.tc_tok_gated : t.tc_tok) = value;
-    } else if (!strcmp(name, "tc_tailsplit")) t.tc_tailsplit = value != 0;
+    } else if (!strcmp(name, "tc_tailsplit")) t.tc_tailsplit = value >= 0 && value <= 2 ? value : 0;
     else if (!strcmp(name, "tc_pair")) {
         if (value < 0 || value > 2) return set_err(ctx, SHREWQ_ERR_INVALID_ARG, "set_option: tc_pair is 0 (never), 1 (where pairs win) or 2 (always above 128 tokens)");
         t.tc_pair = value;
@@ -219,11 +219,12 @@ static int default_family(size_t M, size_t N, bool gated, int sm_count, bool gem
 // CTA pairs against the single-CTA kernel, from measurements on 148 SMs (Llama-MLP block and 4096 x 4096 layers,
 // batches 256..4096): a pair tile is 256 channels (128 gated) x 256 tokens and does twice the work per issued MMA,
 // but a grid that leaves many SMs idle, or needs a deep K split to fill them, is better served by the smaller
-// tiles of the single-CTA kernel.  Pairs win from one full wave of pair tiles (64) up, and from half a wave when
-// the reduction is long enough (K >= 8192) for a two-way K split to keep every pair busy.
+// tiles of the single-CTA kernel.  Pairs win from one full wave of pair tiles (64) up, and from a quarter of a wave
+// when the reduction is long enough (K >= 8192) for a K split to keep every pair busy (16 pair tiles, K = 11008:
+// 33.4 against 36.5 us; 8 pair tiles: 37 against 27 us).
 static bool pair_kernel_wins(size_t M, size_t N, size_t K, bool gated) {
     const size_t pair_tiles = ((N + (gated ? 127 : 255)) / (gated ? 128 : 256)) * ((M + 255) / 256);
-    return pair_tiles >= 64 || (pair_tiles >= 32 && K >= 8192);
+    return pair_tiles >= 64 || (pair_tiles >= 16 && K >= 8192);
 }
 
 int shrewq_plan_forward(size_t M, size_t N, size_t K, int x_is_bf16, int gated, int sm_count, char *kernel, size_t kernel_len,

@@ -24,7 +24,7 @@ struct Tuning {
     int tc_splitk = 1;      // split K when the tile grid leaves SMs idle
     int tc_tok = 0;         // 0 = choose; else force the token tile (16, 32, 64, 128, 256)
     int tc_tok_gated = 0;   // the same for gate/up launches only
-    int tc_tailsplit = 0;   // issue a short last wave as a second launch split along K
+    int tc_tailsplit = 0;   // a short last wave as a second launch split along K: 0 = pair kernel, tails up to a quarter wave; 1 = always; 2 = never
     int tc_pair = 1;        // CTA pairs (tcgen05.mma.cta_group::2) for large batches: 0 never, 1 where they win, 2 whenever M > 128
     int ring_stages = 0;    // stages of the ring kernel: 0 = by grid size, 2 or 3 forced
     int pdl = 1;            // programmatic dependent launch of the forward kernels (after a handle's first forward)

@@ -105,7 +105,7 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
     // Option tc_tailsplit: when large tiles leave a short last wave, issue the full waves as one
     // launch and the tiles of the last wave as a second launch split along K so that it also fills
     // the SMs.
-    const bool tail_split = ctx->tuning.tc_tailsplit != 0;
+    const bool tail_split = ctx->tuning.tc_tailsplit == 1;
     if (tail_split && !fixed_scratch && TOK >= 128 && p.splits == 1) {
         const int tiles = p.n_tiles * p.m_tiles, rem = tiles % ctx->sm_count;
         const int rounds = p.rounds_per_split;
@@ -121,17 +121,17 @@ int launch_cfg(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, con
                 ctx->counters_zeroed = true;
             }
             SplitK head{nullptr, nullptr, rounds, 0, p.n_tiles};
-            kern<<<dim3((unsigned)(tiles - rem), 1, 1), 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(
-                tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, head,
-                ctx->dev_status);
+            SHREWQ_CUDA_TRY(ctx, launch_maybe_pdl(kern, dim3((unsigned)(tiles - rem), 1, 1), dim3(64 + 128 * G), (size_t)C::kSmemRequest,
+                                                  ctx->stream, a.pdl, tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M,
+                                                  (int)a.N, (int)a.K, a.ldy, a.epilogue, head, ctx->dev_status));
             const int rps = (rounds + s_tail - 1) / s_tail;
             const int splits = (rounds + rps - 1) / rps;
             SplitK tail{reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + kScratchPartialOff),
                         reinterpret_cast<unsigned int *>(static_cast<char *>(ctx->scratch) + kScratchCounterOff), rps,
                         tiles - rem, p.n_tiles};
-            kern<<<dim3((unsigned)rem, 1, (unsigned)splits), 64 + 128 * G, C::kSmemRequest, ctx->stream>>>(
-                tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, tail,
-                ctx->dev_status);
+            SHREWQ_CUDA_TRY(ctx, launch_maybe_pdl(kern, dim3((unsigned)rem, 1, (unsigned)splits), dim3(64 + 128 * G),
+                                                  (size_t)C::kSmemRequest, ctx->stream, a.pdl, tw, tw2, tx, ops, static_cast<YT *>(a.y),
+                                                  a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, tail, ctx->dev_status));
             ctx->launches += 2;
             SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
             return SHREWQ_OK;

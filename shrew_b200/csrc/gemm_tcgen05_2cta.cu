@@ -65,13 +65,17 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
     // Option tc_tailsplit (as for the single-CTA kernel): when the pair tiles leave a short last wave, the
     // full waves go out as one launch of whole-K tiles and the tiles of the last wave as a second launch
     // split along K, so that it fills the SMs too.
-    if (ctx->tuning.tc_tailsplit != 0 && splits == 1) {
+    // By default (0) the tail goes out split when it is at most a quarter of a wave: measured on the MLP block at
+    // batch 512, a tail of 12 of 74 pair tiles (the 2-GPU shard) 57.6 -> 53.4 us, a tail of 24 (one GPU) no gain.
+    // 1 = whenever a tail exists, 2 = never.
+    if (ctx->tuning.tc_tailsplit != 2 && splits == 1) {
         const int per_wave = ctx->sm_count / 2;  // pair tiles resident at once, one CTA per SM
         const int tiles = (int)(pairs * m_tiles), rem = per_wave > 0 ? tiles % per_wave : 0;
         int s_tail = rem > 0 ? per_wave / rem : 0;
         if (s_tail > 4) s_tail = 4;
         if (s_tail > rounds / 8) s_tail = rounds / 8;
-        if (tiles > per_wave && rem > 0 && s_tail >= 2) {
+        const bool wanted = ctx->tuning.tc_tailsplit == 1 || rem * 4 <= per_wave;
+        if (wanted && tiles > per_wave && rem > 0 && s_tail >= 2) {
             const int rps_t = (rounds + s_tail - 1) / s_tail;
             const int splits_t = (rounds + rps_t - 1) / rps_t;
             const size_t part_bytes = (size_t)2 * rem * splits_t * kTokPair * kLanes * sizeof(float);
@@ -81,15 +85,16 @@ int launch_pair(shrewq_ctx *ctx, const ForwardArgs &a, const CUtensorMap &tw, co
                 ctx->counters_zeroed = true;
             }
             SplitK2 head{nullptr, nullptr, rounds, 0, (int)pairs};
-            kern<<<dim3(2u * (unsigned)(tiles - rem), 1, 1), kThreads, kSmemBytes, ctx->stream>>>(
-                tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, head,
-                ctx->dev_status);
+            SHREWQ_CUDA_TRY(ctx, launch_maybe_pdl(kern, dim3(2u * (unsigned)(tiles - rem), 1, 1), dim3(kThreads), (size_t)kSmemBytes,
+                                                  ctx->stream, a.pdl, tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M,
+                                                  (int)a.N, (int)a.K, a.ldy, a.epilogue, head, ctx->dev_status));
             SplitK2 tail{reinterpret_cast<float *>(static_cast<char *>(ctx->scratch) + 8192),
                          reinterpret_cast<unsigned int *>(static_cast<char *>(ctx->scratch) + 4096), rps_t, tiles - rem,
                          (int)pairs};
-            kern<<<dim3(2u * (unsigned)rem, 1, (unsigned)splits_t), kThreads, kSmemBytes, ctx->stream>>>(
-                tw, tw2, tx, ops, static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, tail,
-                ctx->dev_status);
+            // (the tail launch may start under the head launch's last wave: the two write disjoint tiles)
+            SHREWQ_CUDA_TRY(ctx, launch_maybe_pdl(kern, dim3(2u * (unsigned)rem, 1, (unsigned)splits_t), dim3(kThreads),
+                                                  (size_t)kSmemBytes, ctx->stream, a.pdl, tw, tw2, tx, ops, static_cast<YT *>(a.y),
+                                                  a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue, tail, ctx->dev_status));
             ctx->launches += 2;
             SHREWQ_CUDA_TRY(ctx, cudaGetLastError());
             return SHREWQ_OK;
