@@ -15,8 +15,10 @@ the TinyGPT-shaped stack; its vocabulary head is bound by the 823 MB f32 output 
 5 B/element + 8 B/row, with the single-threaded CPU restatement beside it.
 
 Prints ONE JSON line on rank 0.  Timing: CUDA events on the launching stream, barrier and
-synchronize on both sides, max over ranks.  L2: every step uses a different copy of the
-weights out of a ring larger than twice the 126 MB L2.
+synchronize on both sides, max over ranks; the K timed steps are captured as one CUDA graph (as the
+layers of a model would be; `--graph-per-step` replays one graph per step instead, `--no-graph`
+launches from the host).  L2: every step uses a different copy of the weights out of a ring larger
+than twice the 126 MB L2.
 
 `--gpus N --parallel replicas` is the data-parallel alternative (every GPU the whole block on its own
 batch, weak scaling, no collective); the default `shard` is the configured output-channel split.
@@ -428,6 +430,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying a CUDA graph")
+    ap.add_argument("--graph-per-step", action="store_true", help="time one graph replay per step instead of one graph of all timed steps")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU exchange: 'fused' = peer stores from the kernel epilogue, 'nccl' = all-gather")
     ap.add_argument("--granularity", default="per_channel", choices=["per_channel", "per_tensor"],
@@ -637,8 +640,30 @@ def main():
         return eager_step(i, x)
 
     # ---- device-resident metric ----
+    # The K timed steps are captured as ONE graph (step i on ring entry i % ring, as in the loop it replaces), the way a
+    # model's layers reach the GPU: with the kernels' programmatic dependent launch a step's first kernel then starts
+    # its prologue under the previous step's last wave instead of behind a host-side graph launch.
+    timed_graph = None
+    if use_graphs and not args.graph_per_step and args.steps <= 512:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                tg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(tg, stream=side):
+                    for i in range(args.steps):
+                        eager_step(i, x_static)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            timed_graph = tg
+        except Exception as e:  # noqa: BLE001
+            sys.stderr.write(f"bench: capture of the timed steps as one graph failed ({e!r}); one graph replay per step\n")
+            timed_graph = None
     for i in range(args.warmup):
         step(i, x_static)
+    if timed_graph is not None:
+        timed_graph.replay()   # one untimed pass of the graph itself
+        torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -647,8 +672,11 @@ def main():
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        step(i, x_static)
+    if timed_graph is not None:
+        timed_graph.replay()          # the K steps as one graph: no host launch between them
+    else:
+        for i in range(args.steps):
+            step(i, x_static)
     e1.record()
     barrier()
     sdev.synchronize()  # also surfaces a kernel that gave up a bounded wait
@@ -830,7 +858,7 @@ def main():
         "tflops": flops_step * (world if replicas else 1) * args.steps / (ms_total * 1e-3) / 1e12,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size() * (world if replicas else 1),
                 "d2h_bytes_per_step": y_host.numel() * y_host.element_size() * (world if replicas else 1), **e2e_info},
-        "gpu_launches": int(launches), "launch_mode": "cuda graph replay (one graph per ring entry)" if use_graphs else "host launches", "clocks": clocks, "roofline": roof,
+        "gpu_launches": int(launches), "launch_mode": ("cuda graph replay (the K timed steps as one graph)" if timed_graph is not None else "cuda graph replay (one graph per ring entry)") if use_graphs else "host launches", "clocks": clocks, "roofline": roof,
     }
     if parity is not None:
         out["parity_checked"] = parity
