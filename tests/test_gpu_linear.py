@@ -285,13 +285,13 @@ def test_ring_kernel_small_batch_parity(oracle, M, N, K, pdl):
         dev.set_option("pdl", 1)
 
 
-def test_small_batch_chain_with_dependent_launch(oracle):
+def test_chained_forwards_with_dependent_launch(oracle):
     # h = relu(x W1^T), y = h W2^T back to back on one stream, ten times: with programmatic dependent launch the second
     # kernel requests its weights while the first still runs and must not read h early, nor may the next
     # iteration's first kernel overwrite h while the second still reads it
     from shrew_b200 import _lib
     from shrew_b200.quantize import Device
-    for force, M in (("gemv", 2), ("mma-ring", 8)):
+    for force, M in (("gemv", 2), ("mma-ring", 8), ("tcgen05", 160), ("tcgen05-2cta", 512)):
         l1, w1, b1 = _make(2048, 1024, 1, seed=1)
         l2, w2, b2 = _make(1024, 2048, 1, seed=2)
         xs = [_x(M, 1024, "bf16", seed=10 + i) for i in range(10)]
