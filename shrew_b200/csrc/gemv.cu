@@ -13,16 +13,21 @@ namespace {
 template <int MT, int R, typename XT, typename YT, bool GATED>
 void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
     constexpr int NR = GATED ? R / 2 : R;
-    // batches above MT tokens run as slices of MT tokens along grid.y (small layers with f32 activations: the
-    // weights come from L2 for every slice but the first)
-    const dim3 grid((unsigned)((a.N + NR - 1) / NR), (unsigned)((a.M + MT - 1) / MT));
-    // With a.pdl the launch takes the PDL variant of the kernel with programmatic stream
-    // serialization: back-to-back GEMVs overlap launch latency, prologue and the first weight
-    // loads with the tail of the kernel before.
-    const bool pdl = a.pdl;
-    if (pdl) {
+    const unsigned gx = (unsigned)((a.N + NR - 1) / NR);
+    if (a.M > (size_t)MT) {
+        // batches above MT tokens run as slices of MT tokens along grid.y (small layers with f32 activations: the
+        // weights come from L2 for every slice but the first)
+        gemv_i8_kernel<MT, R, XT, YT, GATED, false, true><<<dim3(gx, (unsigned)((a.M + MT - 1) / MT)), kThreads, 0, ctx->stream>>>(
+            a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const XT *>(a.x), static_cast<YT *>(a.y), a.extra,
+            (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
+        return;
+    }
+    // With a.pdl (and one or two tokens: from four tokens on the early weight fetch costs more registers than the
+    // overlap returns) the launch takes the PDL variant of the kernel with programmatic stream serialization:
+    // back-to-back GEMVs overlap launch latency, prologue and the first weight loads with the tail of the kernel before.
+    if (a.pdl && MT <= 2) {
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
+        cfg.gridDim = dim3(gx);
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = 0;
         cfg.stream = ctx->stream;
@@ -36,7 +41,7 @@ void launch_one(shrewq_ctx *ctx, const ForwardArgs &a) {
                            (int)a.K, a.ldy, a.epilogue);
         return;
     }
-    gemv_i8_kernel<MT, R, XT, YT, GATED><<<grid, kThreads, 0, ctx->stream>>>(
+    gemv_i8_kernel<MT, R, XT, YT, GATED><<<gx, kThreads, 0, ctx->stream>>>(
         a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const XT *>(a.x),
         static_cast<YT *>(a.y), a.extra, (int)a.M, (int)a.N, (int)a.K, a.ldy, a.epilogue);
 }

@@ -26,15 +26,23 @@ template <int MT, int R, typename XT, typename YT, bool GATED>
 void gemv_one(const Args &a) {
     constexpr int NR = GATED ? R / 2 : R;
     const unsigned grid = (unsigned)((a.N + NR - 1) / NR), gy = (unsigned)((a.M + MT - 1) / MT);  // as launch_one
+    if (gy > 1) {  // as launch_one: the sliced instantiation
+        emu::launch3(grid, gy, 1, kThreads, 0, [&] {
+            gemv_i8_kernel<MT, R, XT, YT, GATED, false, true>(a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up,
+                                                              static_cast<const XT *>(a.x), static_cast<YT *>(a.y), g_peers, a.M,
+                                                              a.N, a.K, a.ldy, a.epilogue);
+        });
+        return;
+    }
     // pdl: the variant that fetches its first weights before waiting for the previous kernel
     if (a.pdl)
-        emu::launch3(grid, gy, 1, kThreads, 0, [&] {
+        emu::launch(grid, kThreads, [&] {
             gemv_i8_kernel<MT, R, XT, YT, GATED, true>(a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up,
                                                        static_cast<const XT *>(a.x), static_cast<YT *>(a.y), g_peers, a.M, a.N,
                                                        a.K, a.ldy, a.epilogue);
         });
     else
-        emu::launch3(grid, gy, 1, kThreads, 0, [&] {
+        emu::launch(grid, kThreads, [&] {
             gemv_i8_kernel<MT, R, XT, YT, GATED>(a.q, a.scales, a.bias, a.q_up, a.scales_up, a.bias_up, static_cast<const XT *>(a.x),
                                                  static_cast<YT *>(a.y), g_peers, a.M, a.N, a.K, a.ldy, a.epilogue);
         });
